@@ -1,0 +1,134 @@
+/*
+ * Thin C-ABI launch layer between the C++ host code (validation, plan, tile selection) and the CUDA kernels.
+ *
+ * Plain pointers and sizes only. Every launcher enqueues on `stream` (a cudaStream_t passed as void*), never
+ * synchronises, never allocates, and returns 0 or a cudaError_t value. All pointers are device pointers.
+ * There is no CPU implementation behind any of these: without a CUDA device they return an error.
+ *
+ * The aclnn entry points (include/aclnnop/) are the public surface; these are what they call in phase 2, and they
+ * are exported so that a host written in another language can bind the kernels directly.
+ */
+#ifndef OPSNN_B200_KERNELS_H_
+#define OPSNN_B200_KERNELS_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OPSNN_API __attribute__((visibility("default")))
+
+/* Element type codes = aclDataType values (include/aclnn_compat/acl_base.h). */
+
+/* ---- full-quant matmul (aclnnQuantMatmulV5 path) --------------------------------------------------------- */
+
+typedef enum {
+    OPSNN_QMM_DEQ = 0,      /* int8 (or fp8 with fp32 scales): out = f32(acc [+ibias]) * sB[n|0] [* sA[m|0]] [+ fbias] */
+    OPSNN_QMM_PERBLOCK = 1, /* out = sum_kb part_kb * (sA[m/gm,kb] * sB[kb,n/gn]), fp32 */
+    OPSNN_QMM_MX = 2        /* e8m0 scale per 32 along k on both operands, + fp32 bias */
+} OpsnnQmmMode;
+
+/* The reference's fixpipe keeps only the top 19 bits of some fp32 scales
+ * (matmul/common/tests/st/arch35/matmul_quant_util.py:50-72, qbmmv3_kernel_golden.py:435-443). */
+#define OPSNN_DEQ_TRUNC_SCALE_B 1 /* x2Scale &= 0xFFFFE000 before use */
+#define OPSNN_DEQ_MERGE_TRUNC 2   /* (x2Scale * x1Scale) &= 0xFFFFE000, one multiply */
+#define OPSNN_DEQ_FBIAS_BEFORE_SCALE 4 /* a float bias is added to the fp32 accumulator before the scale multiply */
+
+typedef enum {
+    OPSNN_KERNEL_AUTO = 0,    /* host tile selection decides */
+    OPSNN_KERNEL_GENERIC = 1, /* CUDA-core kernel: any shape, stride and transpose */
+    OPSNN_KERNEL_UMMA = 2     /* TMA + tcgen05 kernel: needs 16-byte aligned rows */
+} OpsnnKernelChoice;
+
+typedef struct OpsnnQmmParams {
+    int32_t mode;
+    int32_t a_dtype, b_dtype, out_dtype;
+    int32_t bias_dtype;     /* ACL_DT_UNDEFINED (-1) when bias == NULL */
+    int32_t scale_b_dtype;  /* ACL_FLOAT, ACL_BF16, ACL_UINT64 (packed: low 32 bits & 0xFFFFE000 is the fp32 scale), ACL_FLOAT8_E8M0 */
+    int32_t trans_a;        /* 0: a is (m,k) row-major; 1: a is stored (k,m) */
+    int32_t trans_b;        /* 0: b is (k,n) row-major; 1: b is stored (n,k) */
+    int64_t batch, m, n, k;
+    const void* a;
+    const void* b;
+    int64_t a_ld, b_ld;     /* elements between consecutive stored rows */
+    int64_t a_bs, b_bs;     /* elements between batches; 0 broadcasts the operand over the batch */
+    const void* scale_a;    /* x1Scale: NULL | fp32 (m,) or (1,) | fp32 per-block | e8m0 */
+    const void* scale_b;    /* x2Scale */
+    int64_t scale_a_len;    /* DEQ: 1 or m */
+    int64_t scale_b_len;    /* DEQ: 1 or n */
+    int64_t sa_bs, sb_bs;   /* elements between batches of the scales (PERBLOCK / MX); 0 broadcasts */
+    int32_t group_m, group_n, group_k; /* PERBLOCK: 1|128,128,128; MX: 1,1,32 */
+    int32_t deq_flags;      /* DEQ only: OPSNN_DEQ_* bits */
+    const void* bias;
+    int64_t bias_bs;        /* 0: (n,) shared by all batches; n: (batch,1,n) */
+    void* out;
+    int64_t out_ld, out_bs;
+    void* workspace;
+    uint64_t workspace_size;
+} OpsnnQmmParams;
+
+/* Bytes of device workspace `opsnn_qmm_launch` needs for these parameters with this kernel choice. */
+OPSNN_API uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice);
+/* Returns the OpsnnKernelChoice the host tile selection resolves AUTO to (never AUTO). */
+OPSNN_API int32_t opsnn_qmm_select_kernel(const OpsnnQmmParams* p);
+OPSNN_API int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* stream);
+
+/* ---- weight-only quant matmul (aclnnWeightQuantBatchMatmulV2/V3 path) ------------------------------------ */
+
+typedef enum {
+    OPSNN_WQ_KERNEL_AUTO = 0,
+    OPSNN_WQ_KERNEL_GENERIC = 1, /* dequantise the whole weight into workspace, then a bf16/fp16 tensor-core GEMM */
+    OPSNN_WQ_KERNEL_DECODE = 2   /* fused streaming kernel for small m: int4 (n-packed) per-group/-channel */
+} OpsnnWqKernelChoice;
+
+typedef struct OpsnnWqbmmParams {
+    int32_t x_dtype;        /* ACL_BF16 | ACL_FLOAT16; y has the same dtype */
+    int32_t w_dtype;        /* ACL_INT4 (packed nibbles, low first, along the stored inner axis) | ACL_INT8 */
+    int32_t bias_dtype;     /* -1 | x_dtype | ACL_FLOAT */
+    int32_t trans_w;        /* 0: weight stored (k,n); 1: stored (n,k) */
+    int64_t m, n, k;
+    const void* x;          /* (m,k) row-major, x_ld elements per row */
+    int64_t x_ld;
+    const void* w;
+    int64_t w_ld;           /* elements (int4 count for ACL_INT4) between consecutive stored rows */
+    const void* scale;      /* x_dtype */
+    const void* offset;     /* x_dtype or NULL */
+    int64_t group_size;     /* 0: per-channel/-tensor; else k-group length */
+    int64_t scale_sg;       /* elements between consecutive k-groups of scale/offset (0 when group_size == 0) */
+    int64_t scale_sn;       /* elements between consecutive n of scale/offset (0: per-tensor) */
+    const void* bias;
+    void* y;
+    int64_t y_ld;
+    void* workspace;
+    uint64_t workspace_size;
+} OpsnnWqbmmParams;
+
+OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice);
+OPSNN_API int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p);
+OPSNN_API int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream);
+
+/* ---- dynamic MX quant (aclnnDynamicMxQuant path) ---------------------------------------------------------- */
+
+typedef struct OpsnnMxQuantParams {
+    int32_t x_dtype;   /* ACL_BF16 | ACL_FLOAT16 */
+    int32_t y_dtype;   /* ACL_FLOAT8_E4M3FN | ACL_FLOAT8_E5M2 | ACL_FLOAT4_E2M1 */
+    int64_t rows, k;   /* x is (rows,k) contiguous; blocks of 32 along k */
+    const void* x;
+    void* y;           /* (rows,k) fp8, or (rows, k/2) bytes for fp4 */
+    void* scale;       /* (rows, 2*ceil(ceil(k/32)/2)) e8m0 bytes */
+} OpsnnMxQuantParams;
+
+OPSNN_API int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream);
+
+/* ---- misc ---------------------------------------------------------------------------------------------------- */
+
+/* Number of kernel launches issued through this library since load (all streams, all threads). */
+OPSNN_API uint64_t opsnn_launch_count(void);
+/* Name of the last kernel family launched on the calling thread (static string; "" if none). */
+OPSNN_API const char* opsnn_last_kernel_name(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPSNN_B200_KERNELS_H_ */

@@ -1,0 +1,106 @@
+// Device helpers shared by every kernel: element decoding, output casts, launch bookkeeping.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "aclnn_compat/acl_base.h"
+#include "opsnn_b200_kernels.h"
+
+namespace opsnn {
+
+// Host: count a launch and remember which kernel family ran (read back through opsnn_launch_count /
+// opsnn_last_kernel_name).
+void note_launch(const char* name, uint64_t n = 1);
+
+__device__ __forceinline__ float e8m0_to_float(uint8_t b)
+{
+    // 2^(b-127); b == 0 is 2^-127 (an fp32 subnormal), b == 255 is NaN
+    if (b == 0) return __uint_as_float(0x00400000u);
+    if (b == 255) return __uint_as_float(0x7FC00000u);
+    return __uint_as_float((uint32_t)b << 23);
+}
+
+__device__ __forceinline__ float fp4_e2m1_to_float(uint32_t nib)
+{
+    // sign | 2-bit exponent | 1-bit mantissa: magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6
+    const float lut[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+    float v = lut[nib & 7];
+    return (nib & 8) ? -v : v;
+}
+
+__device__ __forceinline__ float fp8_to_float(uint8_t v, int dtype)
+{
+    __half_raw h = __nv_cvt_fp8_to_halfraw(v, dtype == ACL_FLOAT8_E5M2 ? __NV_E5M2 : __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Element `idx` (in elements) of a tensor of `dtype` as float; 4-bit types are packed two per byte, low nibble first.
+__device__ __forceinline__ float load_as_float(const void* base, int64_t idx, int dtype)
+{
+    switch (dtype) {
+        case ACL_INT8: return (float)reinterpret_cast<const int8_t*>(base)[idx];
+        case ACL_FLOAT8_E4M3FN:
+        case ACL_FLOAT8_E5M2: return fp8_to_float(reinterpret_cast<const uint8_t*>(base)[idx], dtype);
+        case ACL_FLOAT4_E2M1: {
+            uint8_t b = reinterpret_cast<const uint8_t*>(base)[idx >> 1];
+            return fp4_e2m1_to_float((idx & 1) ? (b >> 4) : (b & 0xF));
+        }
+        case ACL_INT4: {
+            uint8_t b = reinterpret_cast<const uint8_t*>(base)[idx >> 1];
+            int v = (idx & 1) ? (b >> 4) : (b & 0xF);
+            return (float)((v ^ 8) - 8);
+        }
+        case ACL_FLOAT: return reinterpret_cast<const float*>(base)[idx];
+        case ACL_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+        case ACL_FLOAT16: return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+        case ACL_INT32: return (float)reinterpret_cast<const int32_t*>(base)[idx];
+        default: return 0.f;
+    }
+}
+
+// Dequant scale element as the reference's golden decodes it: fp32 as is, bf16 widened, uint64 = low word with the low
+// 13 bits cleared (matmul/common/tests/st/arch35/matmul_quant_util.py:129-134 of the reference).
+__device__ __forceinline__ float load_deq_scale(const void* base, int64_t idx, int dtype)
+{
+    if (dtype == ACL_FLOAT) return reinterpret_cast<const float*>(base)[idx];
+    if (dtype == ACL_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+    uint32_t lo = (uint32_t)(reinterpret_cast<const unsigned long long*>(base)[idx] & 0xFFFFFFFFull);
+    return __uint_as_float(lo & 0xFFFFE000u);
+}
+
+__device__ __forceinline__ float trunc19(float f) { return __uint_as_float(__float_as_uint(f) & 0xFFFFE000u); }
+
+__device__ __forceinline__ void store_out(void* base, int64_t idx, float v, int dtype)
+{
+    switch (dtype) {
+        case ACL_BF16: reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v); break;
+        case ACL_FLOAT16: reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v); break;
+        case ACL_FLOAT: reinterpret_cast<float*>(base)[idx] = v; break;
+        default: break;
+    }
+}
+
+// The dequantisation epilogue of the per-tensor / per-channel / per-token modes, with the reference's rounding
+// points: int32 accumulate (+int32 bias) -> RNE to fp32 -> * x2Scale -> * x1Scale -> + float bias -> RNE to out dtype
+// (qbmmv3_kernel_golden.py:361-462; kernel quant_batch_matmul_v3/op_kernel/arch35/qbmm_mix_online_dynamic.h:674-720).
+// `f` is the accumulator already converted to fp32 (after the int32 bias add for integer inputs).
+__device__ __forceinline__ float deq_epilogue(float f, float sb, float sa, bool has_sa, float fbias, bool has_fbias,
+                                              int flags)
+{
+    if (has_fbias && (flags & OPSNN_DEQ_FBIAS_BEFORE_SCALE)) f = __fadd_rn(f, fbias);
+    if (flags & OPSNN_DEQ_TRUNC_SCALE_B) sb = trunc19(sb);
+    if (flags & OPSNN_DEQ_MERGE_TRUNC) {
+        f = __fmul_rn(f, trunc19(__fmul_rn(sb, sa)));
+    } else {
+        f = __fmul_rn(f, sb);
+        if (has_sa) f = __fmul_rn(f, sa);
+    }
+    if (has_fbias && !(flags & OPSNN_DEQ_FBIAS_BEFORE_SCALE)) f = __fadd_rn(f, fbias);
+    return f;
+}
+
+}  // namespace opsnn

@@ -1,0 +1,99 @@
+// C-ABI launch layer (include/opsnn_b200_kernels.h): host-side tile/kernel selection and dispatch.
+//
+// This is what is left of the reference's host tiling framework (common/inc/op_host/tiling_base.h:70-103: an ordered list
+// of tiling templates, each with IsCapable(); the first capable one wins) once the target is a single GPU
+// architecture: a capability test per kernel family, tried fastest first.
+#include <atomic>
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace opsnn {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local const char* g_last_kernel = "";
+
+void note_launch(const char* name, uint64_t n)
+{
+    g_launches.fetch_add(n, std::memory_order_relaxed);
+    g_last_kernel = name;
+}
+
+int32_t qmm_generic_launch(const OpsnnQmmParams* p, cudaStream_t stream);
+bool qmm_umma_eligible(const OpsnnQmmParams* p);
+uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p);
+int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream);
+
+int32_t wqbmm_generic_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p);
+uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
+int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+
+int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
+
+}  // namespace opsnn
+
+using namespace opsnn;
+
+extern "C" {
+
+int32_t opsnn_qmm_select_kernel(const OpsnnQmmParams* p)
+{
+    if (p == nullptr) return OPSNN_KERNEL_GENERIC;
+    return qmm_umma_eligible(p) ? OPSNN_KERNEL_UMMA : OPSNN_KERNEL_GENERIC;
+}
+
+uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice)
+{
+    if (p == nullptr) return 0;
+    if (kernel_choice == OPSNN_KERNEL_AUTO) kernel_choice = opsnn_qmm_select_kernel(p);
+    return kernel_choice == OPSNN_KERNEL_UMMA ? qmm_umma_workspace_size(p) : 0;
+}
+
+int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* stream)
+{
+    if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
+    if (p->m <= 0 || p->n <= 0 || p->batch <= 0) return 0;
+    if (kernel_choice == OPSNN_KERNEL_AUTO) kernel_choice = opsnn_qmm_select_kernel(p);
+    if (kernel_choice == OPSNN_KERNEL_UMMA) {
+        if (!qmm_umma_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return qmm_umma_launch(p, static_cast<cudaStream_t>(stream));
+    }
+    return qmm_generic_launch(p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
+{
+    if (p == nullptr) return OPSNN_WQ_KERNEL_GENERIC;
+    return wqbmm_decode_eligible(p) ? OPSNN_WQ_KERNEL_DECODE : OPSNN_WQ_KERNEL_GENERIC;
+}
+
+uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice)
+{
+    if (p == nullptr) return 0;
+    if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    return kernel_choice == OPSNN_WQ_KERNEL_DECODE ? wqbmm_decode_workspace_size(p) : 0;
+}
+
+int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream)
+{
+    if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
+    if (p->m <= 0 || p->n <= 0) return 0;
+    if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE) {
+        if (!wqbmm_decode_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return wqbmm_decode_launch(p, static_cast<cudaStream_t>(stream));
+    }
+    return wqbmm_generic_launch(p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream)
+{
+    if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
+    return mx_quant_launch(p, static_cast<cudaStream_t>(stream));
+}
+
+uint64_t opsnn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* opsnn_last_kernel_name(void) { return g_last_kernel; }
+
+}  // extern "C"

@@ -1,0 +1,720 @@
+// aclnnQuantMatmulV5: phase-1 validation + plan, phase-2 dispatch.
+//
+// Behavioural mirror (Ascend 950 column only) of the reference's
+//   matmul/quant_batch_matmul_v4/op_host/op_api/aclnn_quant_matmul_v5.cpp:245-283 (input existence),
+//   :285-325 (dim range), :967-1016 (pre-process), :1063-1183 (common process / routing), :1189-1227 (entry points)
+//   matmul/quant_batch_matmul_v3/op_api/quant_matmul_checker.cpp:597-722 (groupSize inference), :724-967 (shape),
+//   :1137-1195 (groupSize / CheckShape), :1574-1916 (dtype tables, CheckParams order).
+// The rule order is kept (dtype -> shape -> format -> empty tensor) so the first failure yields the same status.
+#include <algorithm>
+#include <memory>
+
+#include "aclnnop/aclnn_quant_matmul_v5.h"
+#include "internal.h"
+
+using namespace opsnn;
+
+namespace {
+
+constexpr uint64_t kGroupMask = 0xFFFF;
+
+struct Group {
+    uint64_t m = 0, n = 0, k = 0;
+};
+Group decode_group(int64_t g)
+{
+    Group r;
+    r.k = (uint64_t)g & kGroupMask;
+    r.n = ((uint64_t)g >> 16) & kGroupMask;
+    r.m = ((uint64_t)g >> 32) & kGroupMask;
+    return r;
+}
+int64_t encode_group(const Group& g) { return (int64_t)((g.m << 32) | (g.n << 16) | g.k); }
+
+bool is_fp8(int dt) { return dt == ACL_FLOAT8_E4M3FN || dt == ACL_FLOAT8_E5M2; }
+bool in(int dt, std::initializer_list<int> l) { return std::find(l.begin(), l.end(), dt) != l.end(); }
+
+// Working copy of the arguments; views are normalised in place like the reference's executor->CreateView.
+struct Ctx {
+    aclTensor x1, x2, out;
+    bool has_x1s = false, has_x2o = false, has_bias = false, has_ys = false, has_yo = false;
+    aclTensor x1s, x2s, x2o, bias, ys, yo;
+    bool t1 = false, t2 = false;
+    int64_t group = 0;
+    int64_t m = 0, n = 0, k1 = 0, k2 = 0;
+
+    bool int8_in() const { return x1.dtype == ACL_INT8 && x2.dtype == ACL_INT8; }
+    bool int4_in() const { return x1.dtype == ACL_INT4 && x2.dtype == ACL_INT4; }
+    bool fp8_in() const { return is_fp8(x1.dtype) && is_fp8(x2.dtype); }
+    bool hif8_in() const { return x1.dtype == ACL_HIFLOAT8 && x2.dtype == ACL_HIFLOAT8; }
+    bool fp4_in() const { return x1.dtype == ACL_FLOAT4_E2M1 && x2.dtype == ACL_FLOAT4_E2M1; }
+    bool mx() const { return has_x1s && x1s.dtype == ACL_FLOAT8_E8M0 && x2s.dtype == ACL_FLOAT8_E8M0; }
+    bool perblock() const
+    {
+        return has_x1s && (int8_in() || fp8_in() || hif8_in()) && x1s.dtype == ACL_FLOAT && x1s.rank() > 1 &&
+               x2s.dtype == ACL_FLOAT && x2s.rank() > 1;
+    }
+    void dims()
+    {
+        size_t r1 = x1.rank(), r2 = x2.rank();
+        if (r1 >= 2 && r2 >= 2) {
+            k1 = t1 ? x1.shape[r1 - 2] : x1.shape[r1 - 1];
+            m = t1 ? x1.shape[r1 - 1] : x1.shape[r1 - 2];
+            k2 = t2 ? x2.shape[r2 - 1] : x2.shape[r2 - 2];
+            n = t2 ? x2.shape[r2 - 2] : x2.shape[r2 - 1];
+        }
+    }
+};
+
+// quant_matmul_common_check.cpp:106-123 — a strided-transposed view flips the flag instead of being copied.
+void normalise_view(aclTensor& t, bool* transpose)
+{
+    if (is_transposed_last_two(&t)) {
+        size_t r = t.rank();
+        std::swap(t.shape[r - 1], t.shape[r - 2]);
+        std::swap(t.strides[r - 1], t.strides[r - 2]);
+        if (transpose) *transpose = !*transpose;
+    }
+}
+
+// quant_matmul_checker.cpp:354-395
+bool a4w4_pergroup_nonsym(const Ctx& c, uint64_t gk)
+{
+    if (!c.has_x1s || !c.has_x2o) return false;
+    if (c.x1s.dtype != ACL_FLOAT || c.x1s.rank() <= 1) return false;
+    if (c.x2s.dtype != ACL_FLOAT || c.x2s.rank() <= 1) return false;
+    if (c.x2o.dtype != ACL_FLOAT16 || c.x2o.rank() <= 1) return false;
+    if (c.has_bias) return false;
+    int64_t m = c.t1 ? c.x1.shape[1] : c.x1.shape[0];
+    int64_t k = c.t2 ? c.x2.shape[1] : c.x2.shape[0];
+    int64_t n = c.t2 ? c.x2.shape[0] : c.x2.shape[1];
+    if (k % 1024 != 0 || n % 256 != 0) return false;
+    return c.int4_in() && c.x1s.shape[0] == m && c.x1s.shape[1] == 1 && c.x2s.shape[0] == ceil_div(k, (int64_t)gk) &&
+           c.x2s.shape[1] == n && c.x2o.shape[0] == ceil_div(k, (int64_t)gk) && c.x2o.shape[1] == n;
+}
+
+// quant_matmul_checker.cpp:597-722
+bool recalc_group(int64_t input, int64_t scale, uint64_t& g, const char* which)
+{
+    if (scale == 0) {
+        set_err("aclnnQuantMatmulV5: the %s dimension of the scale is 0", which);
+        return false;
+    }
+    if (g == 0) {
+        if (input % scale != 0) {
+            set_err("aclnnQuantMatmulV5: groupSize %s cannot be inferred: %ld is not divisible by %ld", which,
+                    (long)input, (long)scale);
+            return false;
+        }
+        g = (uint64_t)(input / scale);
+    }
+    return true;
+}
+
+bool infer_group(const Ctx& c, int64_t& group)
+{
+    if (!c.has_x1s || c.x1s.rank() < 2 || c.x2s.rank() < 2) return true;
+    Group g = decode_group(group);
+    size_t r1 = c.x1.rank(), r2 = c.x2.rank(), s1 = c.x1s.rank(), s2 = c.x2s.rank();
+    int64_t in_m = c.t1 ? c.x1.shape[r1 - 1] : c.x1.shape[r1 - 2];
+    int64_t in_k = c.t1 ? c.x1.shape[r1 - 2] : c.x1.shape[r1 - 1];
+    int64_t in_n = c.t2 ? c.x2.shape[r2 - 2] : c.x2.shape[r2 - 1];
+    int64_t sm, sk, sn;
+    if (c.mx()) {
+        if (s1 < 3 || s2 < 3) return true;  // rejected later by the dim-range check
+        size_t b1 = s1 - 3, b2 = s2 - 3;
+        sm = c.x1s.shape[b1 + (c.t1 ? 1 : 0)];
+        sk = c.x1s.shape[b1 + (c.t1 ? 0 : 1)] * 2;
+        sn = c.x2s.shape[b2 + (c.t2 ? 0 : 1)];
+        int64_t d0 = c.x2s.shape[b2], d1 = c.x2s.shape[b2 + 1];
+        if ((d0 == 1 && d1 == in_n) || (d0 == in_n && d1 == 1) || (in_n == 1 && (d0 == 1 || d1 == 1))) sn = in_n;
+    } else {
+        sm = c.t1 ? c.x1s.shape[s1 - 1] : c.x1s.shape[s1 - 2];
+        sk = c.t1 ? c.x1s.shape[s1 - 2] : c.x1s.shape[s1 - 1];
+        if (a4w4_pergroup_nonsym(c, g.k)) sn = c.t2 ? c.x2s.shape[s2 - 1] : c.x2s.shape[s2 - 2];
+        else sn = c.t2 ? c.x2s.shape[s2 - 2] : c.x2s.shape[s2 - 1];
+    }
+    if (!recalc_group(in_m, sm, g.m, "m")) return false;
+    if (!recalc_group(in_k, sk, g.k, "k")) return false;
+    if (!recalc_group(in_n, sn, g.n, "n")) return false;
+    group = encode_group(g);
+    return true;
+}
+
+#define FAIL(...)             \
+    do {                      \
+        set_err(__VA_ARGS__); \
+        return false;         \
+    } while (0)
+
+// ---- dtype rules, quant_matmul_checker.cpp:1574-1852 (DAV_3510 branch) ---------------------------------------
+bool check_dtype(const Ctx& c)
+{
+    const int out = c.out.dtype, s2 = c.x2s.dtype;
+    const int bias = c.has_bias ? (int)c.bias.dtype : -1;
+    if (out == ACL_INT32 && c.has_x1s) FAIL("out INT32 does not take x1Scale");
+    if (!c.has_x1s) {  // per-tensor / per-channel
+        if (out == ACL_INT32 && !c.int8_in()) FAIL("out INT32 needs INT8 x1/x2");
+        if (c.int8_in() || c.int4_in()) {
+            if (out == ACL_BF16) {
+                if (!in(s2, {ACL_UINT64, ACL_INT64, ACL_FLOAT, ACL_BF16})) FAIL("x2Scale dtype %s not supported for BF16 out", dtype_name(s2));
+            } else if (out == ACL_INT8 || out == ACL_FLOAT16) {
+                if (!in(s2, {ACL_UINT64, ACL_INT64})) FAIL("x2Scale must be UINT64/INT64 for %s out", dtype_name(out));
+            } else if (out == ACL_INT32) {
+                if (!in(s2, {ACL_FLOAT, ACL_BF16})) FAIL("x2Scale must be FLOAT/BF16 for INT32 out");
+            }
+            if (c.has_bias) {
+                if (out == ACL_INT32 && bias != ACL_INT32) FAIL("bias must be INT32 for INT32 out");
+                if (out == ACL_BF16 && (s2 == ACL_FLOAT || s2 == ACL_BF16) && !in(bias, {ACL_INT32, ACL_BF16, ACL_FLOAT}))
+                    FAIL("bias dtype %s not supported", dtype_name(bias));
+                if ((out == ACL_INT8 || out == ACL_FLOAT16 || out == ACL_BF16) && (s2 == ACL_UINT64 || s2 == ACL_INT64) &&
+                    bias != ACL_INT32)
+                    FAIL("bias must be INT32 with a packed UINT64 scale");
+            }
+            if (c.has_x2o) {
+                if (out != ACL_INT8) FAIL("x2Offset only with INT8 out");
+                if (c.x2o.dtype != ACL_FLOAT) FAIL("x2Offset must be FLOAT");
+            }
+            if (!in(out, {ACL_INT8, ACL_FLOAT16, ACL_BF16, ACL_INT32})) FAIL("out dtype %s not supported", dtype_name(out));
+        } else if (c.hif8_in() || c.fp8_in()) {
+            if (!in(s2, {ACL_UINT64, ACL_INT64})) FAIL("x2Scale must be UINT64/INT64 for fp8 per-tensor/per-channel");
+            if (c.has_bias && bias != ACL_FLOAT) FAIL("bias must be FLOAT");
+            if (c.has_x2o) FAIL("x2Offset not supported");
+            if (!in(out, {ACL_FLOAT16, ACL_BF16, ACL_FLOAT})) FAIL("out dtype %s not supported", dtype_name(out));
+        } else {
+            FAIL("x1/x2 dtype combination %s/%s not supported", dtype_name(c.x1.dtype), dtype_name(c.x2.dtype));
+        }
+    } else if (c.mx()) {
+        if (!c.fp4_in() && !c.fp8_in()) FAIL("mx needs fp8 x fp8 or fp4 x fp4 inputs");
+        if (c.has_bias && bias != ACL_FLOAT) FAIL("mx bias must be FLOAT");
+        if (!in(out, {ACL_FLOAT16, ACL_BF16, ACL_FLOAT})) FAIL("out dtype %s not supported", dtype_name(out));
+        if (c.has_x2o) FAIL("x2Offset not supported");
+    } else if (c.int4_in() && c.has_x2o) {  // per-token per-group asymmetric int4
+        if (!in(out, {ACL_FLOAT16, ACL_BF16})) FAIL("out dtype not supported");
+        if (c.x1s.dtype != ACL_FLOAT || s2 != ACL_FLOAT || c.x2o.dtype != ACL_FLOAT16) FAIL("scale/offset dtype not supported");
+        if (c.t1 || !c.t2) FAIL("A4W4 per-group needs transposeX1=false, transposeX2=true");
+    } else if (c.int8_in() || c.int4_in()) {  // per-token
+        if (!in(out, {ACL_FLOAT16, ACL_BF16})) FAIL("per-token out dtype %s not supported", dtype_name(out));
+        if (c.x1s.dtype != ACL_FLOAT) FAIL("x1Scale must be FLOAT");
+        if (c.has_x2o) FAIL("x2Offset not supported");
+        if (out == ACL_BF16) {
+            if (!in(s2, {ACL_BF16, ACL_FLOAT})) FAIL("x2Scale must be BF16/FLOAT");
+            if (c.has_bias && !in(bias, {ACL_INT32, ACL_BF16, ACL_FLOAT})) FAIL("bias dtype not supported");
+        } else {
+            if (s2 != ACL_FLOAT) FAIL("x2Scale must be FLOAT for FLOAT16 out");
+            if (c.has_bias && !in(bias, {ACL_INT32, ACL_FLOAT16, ACL_FLOAT})) FAIL("bias dtype not supported");
+        }
+    } else if (c.hif8_in() || c.fp8_in()) {  // double scale, fp8 per-token, per-block
+        if (c.x1s.dtype != ACL_FLOAT) FAIL("x1Scale must be FLOAT");
+        if (s2 != ACL_FLOAT) FAIL("x2Scale must be FLOAT");
+        if (!in(out, {ACL_FLOAT16, ACL_BF16, ACL_FLOAT})) FAIL("out dtype not supported");
+        if (c.perblock() && c.has_bias) FAIL("per-block does not take bias");
+        if (c.has_bias && bias != ACL_FLOAT) FAIL("bias must be FLOAT");
+        if (c.has_x2o) FAIL("x2Offset not supported");
+    } else {
+        FAIL("x1/x2 dtype combination %s/%s not supported", dtype_name(c.x1.dtype), dtype_name(c.x2.dtype));
+    }
+    return true;
+}
+
+// ---- shape rules, quant_matmul_checker.cpp:477-967, 1008-1195 ----------------------------------------------
+bool check_mx_dims(const Ctx& c)
+{
+    size_t b1 = c.x1s.rank() - 3, b2 = c.x2s.rank() - 3;
+    int64_t s1m = c.x1s.shape[b1 + (c.t1 ? 1 : 0)], s1k = c.x1s.shape[b1 + (c.t1 ? 0 : 1)];
+    int64_t s2n = c.x2s.shape[b2 + (c.t2 ? 0 : 1)], s2k = c.x2s.shape[b2 + (c.t2 ? 1 : 0)];
+    int64_t kq1 = ceil_div(c.k1, 64), kq2 = ceil_div(c.k2, 64);
+    bool one1 = (s1m == 1 && s1k == c.m) || (s1m == c.m && s1k == 1) || (s1m == 1 && s1k == kq1) || (s1m == kq1 && s1k == 1);
+    bool one2 = (s2n == 1 && s2k == c.n) || (s2n == c.n && s2k == 1) || (s2n == 1 && s2k == kq2) || (s2n == kq2 && s2k == 1);
+    if ((!one1 && s1m != c.m) || (!one2 && s2n != c.n)) FAIL("mx: scale M/N dimension does not match x1/x2");
+    if ((!one1 && kq1 != s1k) || (!one2 && kq2 != s2k)) FAIL("mx: scale K dimension must be ceil(k/64)");
+    if (c.x1s.dim(-1) != 2 || c.x2s.dim(-1) != 2) FAIL("mx: last dimension of the scales must be 2");
+    if (c.fp4_in()) {
+        // fp4 packs two values per byte along the inner axis (CheckMXFP4FP8ParamsNDOrNZ, :453-475)
+        if (c.k1 % 2 != 0) FAIL("mxfp4: k must be even");
+        if (c.t1 && c.m % 2 != 0) FAIL("mxfp4: inner axis m must be even when x1 is transposed");
+        if (!c.t2 && c.n % 2 != 0) FAIL("mxfp4: inner axis n must be even when x2 is not transposed");
+    }
+    return true;
+}
+
+bool check_perblock_dims(const Ctx& c)
+{
+    size_t r1 = c.x1.rank(), r2 = c.x2.rank();
+    uint64_t gm = std::max<uint64_t>(((uint64_t)c.group >> 32) & kGroupMask, 1);
+    if (c.x1s.rank() != r1 || c.x2s.rank() != r2) FAIL("per-block: scale rank must equal input rank");
+    for (int64_t i = (int64_t)r1 - 3; i >= 0; --i)
+        if (c.x1s.shape[i] != c.x1.shape[i]) FAIL("per-block: x1Scale batch dims must equal x1's");
+    for (int64_t i = (int64_t)r2 - 3; i >= 0; --i)
+        if (c.x2s.shape[i] != c.x2.shape[i]) FAIL("per-block: x2Scale batch dims must equal x2's");
+    size_t mi = r1 - (c.t1 ? 1 : 2), k1i = r1 - (c.t1 ? 2 : 1), ni = r2 - (c.t2 ? 2 : 1), k2i = r2 - (c.t2 ? 1 : 2);
+    if (ceil_div(c.x1.shape[mi], (int64_t)gm) != c.x1s.shape[mi]) FAIL("per-block: x1Scale m dim must be ceil(m/groupSizeM)");
+    if (ceil_div(c.x1.shape[k1i], 128) != c.x1s.shape[k1i]) FAIL("per-block: x1Scale k dim must be ceil(k/128)");
+    if (ceil_div(c.x2.shape[ni], 128) != c.x2s.shape[ni]) FAIL("per-block: x2Scale n dim must be ceil(n/128)");
+    if (ceil_div(c.x2.shape[k2i], 128) != c.x2s.shape[k2i]) FAIL("per-block: x2Scale k dim must be ceil(k/128)");
+    return true;
+}
+
+bool check_shape(const Ctx& c)
+{
+    const Group g = decode_group(c.group);
+    // scale dim range (:1115-1135)
+    if (!c.has_x1s) {
+        if (c.x2s.rank() != 1) FAIL("x2Scale must be 1-D without x1Scale");
+    } else if (c.mx()) {
+        size_t s1 = c.x1s.rank(), s2 = c.x2s.rank();
+        if (s1 < 3 || s2 < 3) FAIL("mx: scales must have at least 3 dims");
+        size_t ib1 = c.x1.rank() > 2 ? c.x1.rank() - 2 : 0, ib2 = c.x2.rank() > 2 ? c.x2.rank() - 2 : 0;
+        if (s1 - 3 != ib1 || s2 - 3 != ib2) FAIL("mx: scale batch dim count must match the input's");
+        for (size_t i = 0; i < s1 - 3; ++i)
+            if (c.x1s.shape[i] != c.x1.shape[i]) FAIL("mx: x1Scale batch dims must equal x1's");
+        for (size_t i = 0; i < s2 - 3; ++i)
+            if (c.x2s.shape[i] != c.x2.shape[i]) FAIL("mx: x2Scale batch dims must equal x2's");
+    } else if (a4w4_pergroup_nonsym(c, g.k)) {
+    } else {
+        bool pb = c.perblock();
+        if ((pb && c.x1s.rank() != c.x1.rank()) || (!pb && c.x1s.rank() != 1)) FAIL("x1Scale rank not supported");
+        if ((pb && c.x2s.rank() != c.x2.rank()) || (!pb && c.x2s.rank() != 1)) FAIL("x2Scale rank not supported");
+    }
+    // groupSize (:1137-1159)
+    if (a4w4_pergroup_nonsym(c, g.k)) {
+        if (g.k != 256) FAIL("A4W4 per-group: groupSizeK must be 256");
+    } else if (c.mx()) {
+        if (g.k != 32 || g.m != 1 || g.n != 1) FAIL("mx: groupSize must resolve to [1,1,32] (4295032864), got [%lu,%lu,%lu]", g.m, g.n, g.k);
+    } else if (c.perblock()) {
+        if (g.k != 128 || g.n != 128 || (g.m != 128 && g.m != 1)) FAIL("per-block: groupSize must be [1|128,128,128], got [%lu,%lu,%lu]", g.m, g.n, g.k);
+    } else if (c.group != 0) {
+        FAIL("groupSize must be 0 for this quantization mode");
+    }
+    if (c.int4_in()) {
+        // CheckShapeInt4 (:969-1006): the packed inner axis must be even
+        if (c.x1.dim(-1) % 2 != 0 || c.x2.dim(-1) % 2 != 0) FAIL("int4 inner axis must be even");
+    }
+    if (c.k1 != c.k2) FAIL("k of x1 (%ld) and x2 (%ld) differ", (long)c.k1, (long)c.k2);
+    // CheckDimValue (:805-852)
+    bool skip_rest = false;
+    if (c.has_x1s) {
+        if (c.mx()) {
+            if (!check_mx_dims(c)) return false;
+            skip_rest = true;
+        } else if (c.perblock()) {
+            if (!check_perblock_dims(c)) return false;
+            skip_rest = true;
+        } else {
+            int64_t s0 = c.x1s.shape[0];
+            if (c.m == 1) {
+                if (s0 != 1) FAIL("x1Scale must have 1 element when m is 1");
+            } else if (s0 == 1 && !c.int8_in()) {
+                if (c.x2s.shape[0] != 1 && c.x2s.shape[0] != c.n) FAIL("x2Scale must have 1 or n elements");
+            } else if (s0 != c.m) {
+                FAIL("x1Scale must have m (%ld) elements, got %ld", (long)c.m, (long)s0);
+            }
+        }
+    }
+    if (!skip_rest) {
+        bool a4 = a4w4_pergroup_nonsym(c, g.k);
+        if (!a4 && c.x2s.shape[0] != c.n && c.x2s.shape[0] != 1) FAIL("x2Scale must have 1 or n (%ld) elements", (long)c.n);
+        if (c.has_x2o && !a4) {
+            if (c.x2o.rank() != 1) FAIL("x2Offset must be 1-D");
+            if (c.x2o.shape[0] != c.n && c.x2o.shape[0] != 1) FAIL("x2Offset must have 1 or n elements");
+        }
+    }
+    // output batch inference (:854-877)
+    std::vector<int64_t> batch;
+    int64_t batch_prod = 1;
+    {
+        size_t r1 = c.x1.rank(), r2 = c.x2.rank(), ro = std::max(r1, r2), off = ro - std::min(r1, r2);
+        const aclTensor& lg = r1 > r2 ? c.x1 : c.x2;
+        const aclTensor& sh = r1 > r2 ? c.x2 : c.x1;
+        for (size_t i = 0; i + 2 < ro; ++i) {
+            int64_t a = lg.shape[i], b = i < off ? 1 : sh.shape[i - off];
+            if (a > 1 && b > 1 && a != b) FAIL("batch dims of x1 and x2 cannot be broadcast");
+            batch.push_back(std::max(a, b));
+            batch_prod *= std::max(a, b);
+        }
+    }
+    if (c.has_bias) {  // :879-927
+        size_t br = c.bias.rank();
+        if (br != 3 && br != 1) FAIL("bias must be 1-D or 3-D");
+        if (br == 1) {
+            if (c.bias.shape[0] != c.n) FAIL("bias must have n (%ld) elements", (long)c.n);
+        } else {
+            if (batch.size() != 1) FAIL("3-D bias needs exactly one output batch dim");
+            if (c.bias.shape[1] != 1) FAIL("bias second dim must be 1");
+            if (c.bias.shape[2] != c.n) FAIL("bias third dim must be n");
+            if (c.bias.shape[0] != batch_prod) FAIL("bias first dim must equal the output batch");
+        }
+    }
+    {  // :929-967
+        size_t ro = c.out.rank();
+        int64_t om = c.out.shape[ro - 2], on = c.out.shape[ro - 1];
+        size_t inferred = batch.size() + 2;
+        bool two_d = c.x1.rank() == 2 && c.x2.rank() == 2;
+        if (om == 1 && inferred == 2 && ro == 3 && two_d) {
+            ro -= 1;
+            om = c.out.shape[0];
+        }
+        if (inferred != ro) FAIL("out rank %zu does not match the inferred rank %zu", ro, inferred);
+        if (om != c.m) FAIL("out m (%ld) must equal x1 m (%ld)", (long)om, (long)c.m);
+        if (on != c.n) FAIL("out n (%ld) must equal x2 n (%ld)", (long)on, (long)c.n);
+        for (size_t i = 0; i + 2 < ro; ++i)
+            if (c.out.shape[i] != batch[i]) FAIL("out batch dim %zu must be %ld", i, (long)batch[i]);
+    }
+    return true;
+}
+
+// ---- A8W4 (fp8 x fp4) rules, aclnn_quant_matmul_v5.cpp:193-243, 327-398, 414-480, 560-760 -------------------------
+aclnnStatus check_a8w4_float(const Ctx& c, const aclTensor* x1Scale, int64_t group_k)
+{
+    bool is_mx = c.mx();
+    bool is_tcg = !c.has_x1s && (c.x2s.dtype == ACL_BF16 || c.x2s.dtype == ACL_FLOAT16);
+    if (!is_mx && !is_tcg) {
+        set_err("A8W4: neither mx (e8m0 scales) nor T-CG (x1Scale null, x2Scale BF16/FLOAT16)");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    (void)x1Scale;
+    if (c.t1) { set_err("A8W4: transposeX1 must be false"); return ACLNN_ERR_PARAM_INVALID; }
+    if (!c.t2) { set_err("A8W4 ND: transposeX2 must be true"); return ACLNN_ERR_PARAM_INVALID; }
+    if (group_k != 32) { set_err("A8W4: groupSizeK must be 32"); return ACLNN_ERR_PARAM_INVALID; }
+    // dim range
+    if (c.x1.rank() != 2 || c.x2.rank() != 2 || c.out.rank() != 2) { set_err("A8W4: x1, x2, out must be 2-D"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.has_bias && c.bias.rank() != 2) { set_err("A8W4: bias must be 2-D"); return ACLNN_ERR_PARAM_INVALID; }
+    size_t want = is_mx ? 3 : 2;
+    if (c.has_x1s && c.x1s.rank() != want) { set_err("A8W4: x1Scale rank"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.x2s.rank() != want) { set_err("A8W4: x2Scale rank"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.has_ys && c.ys.rank() != 2) { set_err("A8W4: yScale must be 2-D"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.has_yo && c.yo.rank() != 1) { set_err("A8W4: yOffset must be 1-D"); return ACLNN_ERR_PARAM_INVALID; }
+    // dtype
+    if (!is_fp8(c.x1.dtype) || c.x2.dtype != ACL_FLOAT4_E2M1 || !in(c.out.dtype, {ACL_BF16, ACL_FLOAT16})) {
+        set_err("A8W4: dtype combination not supported");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (c.x1.dtype != ACL_FLOAT8_E4M3FN) { set_err("A8W4: x1 must be FLOAT8_E4M3FN"); return ACLNN_ERR_PARAM_INVALID; }
+    if (!c.has_x1s) {
+        if (c.has_bias) { set_err("A8W4 T-CG: bias must be null"); return ACLNN_ERR_PARAM_INVALID; }
+        if (!c.has_ys) { set_err("A8W4 T-CG: yScale is required"); return ACLNN_ERR_PARAM_INVALID; }
+        if (!in(c.ys.dtype, {ACL_UINT64, ACL_INT64})) { set_err("A8W4 T-CG: yScale must be UINT64"); return ACLNN_ERR_PARAM_INVALID; }
+    } else {
+        if (c.has_bias && c.bias.dtype != c.out.dtype) { set_err("MxA8W4: bias dtype must equal out dtype"); return ACLNN_ERR_PARAM_INVALID; }
+        if (c.has_ys) { set_err("MxA8W4: yScale must be null"); return ACLNN_ERR_PARAM_INVALID; }
+    }
+    // shape
+    if (c.m <= 0 || c.k1 <= 0 || c.n <= 0 || c.k1 != c.k2) { set_err("A8W4: bad m/k/n"); return ACLNN_ERR_PARAM_INVALID; }
+    if (is_tcg && (c.k1 % 32 != 0 || c.k1 <= 32)) { set_err("A8W4 T-CG: k must be a multiple of 32 and > 32"); return ACLNN_ERR_PARAM_INVALID; }
+    if (is_mx && c.k1 % 8 != 0) { set_err("MxA8W4: k must be a multiple of 8"); return ACLNN_ERR_PARAM_INVALID; }
+    int64_t gd = ceil_div(c.k2, 32);
+    if (is_mx) {
+        if (c.x1s.shape[0] != c.m || c.x1s.shape[1] != ceil_div(gd, 2) || c.x1s.shape[2] != 2) { set_err("MxA8W4: x1Scale shape"); return ACLNN_ERR_PARAM_INVALID; }
+        if (c.x2s.shape[0] != c.n || c.x2s.shape[1] != ceil_div(gd, 2) || c.x2s.shape[2] != 2) { set_err("MxA8W4: x2Scale shape"); return ACLNN_ERR_PARAM_INVALID; }
+    } else {
+        if (c.x2s.shape[0] != c.n || c.x2s.shape[1] != gd) { set_err("A8W4 T-CG: x2Scale must be (n, k/32)"); return ACLNN_ERR_PARAM_INVALID; }
+    }
+    if (c.has_ys && (c.ys.shape[0] != 1 || c.ys.shape[1] != c.n)) { set_err("A8W4: yScale must be (1,n)"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.has_bias && (c.bias.shape[0] != 1 || c.bias.shape[1] != c.n)) { set_err("A8W4: bias must be (1,n)"); return ACLNN_ERR_PARAM_INVALID; }
+    if (c.out.shape[0] != c.m || c.out.shape[1] != c.n) { set_err("A8W4: out must be (m,n)"); return ACLNN_ERR_PARAM_INVALID; }
+    return ACLNN_SUCCESS;
+}
+
+// Batch stride (elements) of an operand whose leading dims either equal the output batch dims or are absent/1.
+bool operand_batch(const aclTensor& t, size_t core_rank, const std::vector<int64_t>& out_batch, int64_t core_elems,
+                   int64_t* bs)
+{
+    size_t nb = t.rank() - core_rank;
+    bool all_one = true;
+    for (size_t i = 0; i < nb; ++i) all_one &= (t.shape[i] == 1);
+    if (all_one) {
+        *bs = 0;
+        return true;
+    }
+    // must match the trailing out_batch dims exactly and be dense
+    if (nb > out_batch.size()) return false;
+    size_t off = out_batch.size() - nb;
+    for (size_t i = 0; i < off; ++i)
+        if (out_batch[i] != 1) return false;
+    for (size_t i = 0; i < nb; ++i)
+        if (t.shape[i] != out_batch[off + i]) return false;
+    *bs = core_elems;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTensor* x2, const aclTensor* x1Scale,
+                                               const aclTensor* x2Scale, const aclTensor* yScale,
+                                               const aclTensor* x1Offset, const aclTensor* x2Offset,
+                                               const aclTensor* yOffset, const aclTensor* bias, bool transposeX1,
+                                               bool transposeX2, int64_t groupSize, aclTensor* out,
+                                               uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    clear_err();
+    if (workspaceSize == nullptr || executor == nullptr) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: workspaceSize/executor is nullptr");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (x2 == nullptr) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: x2 is nullptr");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (x2->format == ACL_FORMAT_FRACTAL_NZ || x2->format == ACL_FORMAT_FRACTAL_NZ_C0_32) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: x2 format FRACTAL_NZ is not accepted by this entry point, use ND");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    // CheckInputExistence (:245-283)
+    if (x1 == nullptr || x2Scale == nullptr || out == nullptr) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: x1, x2Scale and out are required");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    const bool a8w4f = is_fp8(x1->dtype) && x2->dtype == ACL_FLOAT4_E2M1;
+    const bool a8w4i = x1->dtype == ACL_INT8 && x2->dtype == ACL_INT32;
+    const bool a8w4 = a8w4f || a8w4i;
+    if (!a8w4 && yScale != nullptr && !yScale->empty()) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: yScale must be nullptr or empty");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (x1Offset != nullptr && !x1Offset->empty()) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: x1Offset must be nullptr or empty");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (a8w4 && x2Offset != nullptr) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: x2Offset must be nullptr in A8W4 mode");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (yOffset != nullptr && !yOffset->empty() && !a8w4i) {
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: yOffset must be nullptr or empty");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    int64_t group = groupSize;
+    if (a8w4f) {  // A8W4InferGroupSize (:1045-1061)
+        Group g = decode_group(group);
+        if (!((g.m == 0 && g.n == 0) || (g.m == 1 && g.n == 1))) {
+            set_err("A8W4: groupSizeM and groupSizeN must both be 0 or both be 1");
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+        group = (int64_t)g.k;
+    }
+
+    auto exec = std::make_unique<aclOpExecutor>();
+    exec->kind = ExecKind::kQmm;
+
+    // empty output short-cut (:1088-1108)
+    if (!a8w4 && x1->rank() >= 2 && x2->rank() >= 2) {
+        int64_t mm = transposeX1 ? x1->dim(-1) : x1->dim(-2);
+        int64_t nn = transposeX2 ? x2->dim(-2) : x2->dim(-1);
+        if (mm == 0 || nn == 0) {
+            exec->nothing_to_do = true;
+            *workspaceSize = 0;
+            *executor = exec.release();
+            return ACLNN_SUCCESS;
+        }
+    }
+
+    Ctx c;
+    c.x1 = *x1;
+    c.x2 = *x2;
+    c.out = *out;
+    c.x2s = *x2Scale;
+    if (x1Scale) { c.has_x1s = true; c.x1s = *x1Scale; }
+    if (x2Offset) { c.has_x2o = true; c.x2o = *x2Offset; }
+    if (bias) { c.has_bias = true; c.bias = *bias; }
+    if (yScale && !yScale->empty()) { c.has_ys = true; c.ys = *yScale; }
+    if (yOffset && !yOffset->empty()) { c.has_yo = true; c.yo = *yOffset; }
+    if (yScale && yScale->empty() && a8w4) { c.has_ys = true; c.ys = *yScale; }
+    c.t1 = transposeX1;
+    c.t2 = transposeX2;
+    c.group = group;
+    if (c.x2s.dtype == ACL_INT64) c.x2s.dtype = ACL_UINT64;
+
+    // PreMatmulCalcProcess (:967-1016): strided-transposed views flip the flags
+    if (c.x1.rank() >= 2) normalise_view(c.x1, &c.t1);
+    if (c.x2.rank() >= 2) normalise_view(c.x2, &c.t2);
+    c.dims();
+
+    if (a8w4f) {
+        aclnnStatus st = check_a8w4_float(c, x1Scale, group);
+        if (st != ACLNN_SUCCESS) return st;
+        exec->unsupported = true;
+        exec->unsupported_why = "fp8 x fp4 (A8W4) kernels are not built yet";
+        *workspaceSize = 0;
+        *executor = exec.release();
+        return ACLNN_SUCCESS;
+    }
+    if (a8w4i) {
+        // CheckParamsA8W4Int (:736-752): only Atlas A2/A3 implement int8 x packed-int4; other targets report a runtime error
+        set_err("aclnnQuantMatmulV5GetWorkspaceSize: INT8 x INT32(int4) pseudo-quant is not implemented for this target");
+        return ACLNN_ERR_RUNTIME_ERROR;
+    }
+    // CheckDimRange (:285-325)
+    if (c.x2.storage_shape.size() < 2 || c.x2.storage_shape.size() > 6) {
+        set_err("x2 must have 2..6 dims, got %zu", c.x2.storage_shape.size());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (c.x1.rank() < 2 || c.x1.rank() > 6) {
+        set_err("x1 must have 2..6 dims, got %zu", c.x1.rank());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (c.out.rank() < 2 || c.out.rank() > 6) {
+        set_err("out must have 2..6 dims, got %zu", c.out.rank());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (c.x2.rank() < 2 || c.x2.rank() > 6) {
+        set_err("x2 must have 2..6 dims, got %zu", c.x2.rank());
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    // A4W4CaseProcess: INT32 words are re-viewed as 8 INT4 along the inner axis (quant_matmul_common_check.cpp:140-169)
+    for (aclTensor* t : {&c.x1, &c.x2}) {
+        if (t->dtype == ACL_INT32) {
+            t->shape.back() *= 8;
+            for (size_t i = 0; i + 1 < t->rank(); ++i) t->strides[i] *= 8;
+            t->offset *= 8;
+            t->dtype = ACL_INT4;
+        }
+    }
+    c.dims();
+    if (!infer_group(c, c.group)) return ACLNN_ERR_PARAM_INVALID;
+    if (!check_dtype(c)) return ACLNN_ERR_PARAM_INVALID;
+    if (!check_shape(c)) return ACLNN_ERR_PARAM_INVALID;
+    for (const aclTensor* t : {&c.x1, &c.x2s, &c.out}) {
+        if (t->format != ACL_FORMAT_ND) {
+            set_err("only ACL_FORMAT_ND tensors are accepted");
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+    }
+    if (c.x1.empty() || c.x2.empty()) {
+        set_err("x1 and x2 can not be empty");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+
+    // ---------------- plan ----------------
+    OpsnnQmmParams& p = exec->qmm;
+    p.a_dtype = c.x1.dtype;
+    p.b_dtype = c.x2.dtype;
+    p.out_dtype = c.out.dtype;
+    p.bias_dtype = c.has_bias ? (int)c.bias.dtype : -1;
+    p.scale_b_dtype = c.x2s.dtype;
+    p.trans_a = c.t1;
+    p.trans_b = c.t2;
+    p.m = c.m;
+    p.n = c.n;
+    p.k = c.k1;
+    std::vector<int64_t> ob(c.out.shape.begin(), c.out.shape.end() - 2);
+    if (c.out.rank() == 3 && c.x1.rank() == 2 && c.x2.rank() == 2 && c.out.shape[1] == 1 && c.m != 1) ob.clear();
+    p.batch = 1;
+    for (auto d : ob) p.batch *= d;
+    auto why_unsupported = [&](const char* w) {
+        exec->unsupported = true;
+        exec->unsupported_why = w;
+    };
+    int64_t ld = 0, bs = 0;
+    if (!row_strided_view(&c.x1, &ld, &bs)) why_unsupported("x1 is neither contiguous, row-strided nor a transposed view");
+    p.a_ld = ld;
+    if (!operand_batch(c.x1, 2, ob, bs, &p.a_bs)) why_unsupported("x1 batch dims broadcast partially");
+    if (c.x1.rank() > 2 && p.a_bs != 0 && bs == 0) p.a_bs = c.x1.dim(-2) * ld;
+    if (!row_strided_view(&c.x2, &ld, &bs)) why_unsupported("x2 is neither contiguous, row-strided nor a transposed view");
+    p.b_ld = ld;
+    if (!operand_batch(c.x2, 2, ob, bs, &p.b_bs)) why_unsupported("x2 batch dims broadcast partially");
+    if (c.x2.rank() > 2 && p.b_bs != 0 && bs == 0) p.b_bs = c.x2.dim(-2) * ld;
+    if (!row_strided_view(&c.out, &ld, &bs)) why_unsupported("out must be contiguous or row-strided");
+    p.out_ld = ld;
+    p.out_bs = bs != 0 ? bs : c.m * ld;
+    p.a = data_ptr(&c.x1);
+    p.b = data_ptr(&c.x2);
+    p.out = const_cast<uint8_t*>(data_ptr(&c.out));
+    p.scale_a = c.has_x1s ? data_ptr(&c.x1s) : nullptr;
+    p.scale_b = data_ptr(&c.x2s);
+    p.bias = c.has_bias ? data_ptr(&c.bias) : nullptr;
+    p.bias_bs = (c.has_bias && c.bias.rank() == 3) ? c.n : 0;
+    for (const aclTensor* t : {&c.x2s, c.has_x1s ? &c.x1s : nullptr, c.has_bias ? &c.bias : nullptr}) {
+        if (t != nullptr && !is_contiguous(t)) why_unsupported("scale/bias tensors must be contiguous");
+    }
+    const Group g = decode_group(c.group);
+    p.group_m = (int32_t)g.m;
+    p.group_n = (int32_t)g.n;
+    p.group_k = (int32_t)g.k;
+    if (c.mx()) {
+        p.mode = OPSNN_QMM_MX;
+        // canonical layouts only: x1Scale follows transposeX1, x2Scale follows transposeX2
+        size_t b1 = c.x1s.rank() - 3, b2 = c.x2s.rank() - 3;
+        int64_t kq = ceil_div(c.k1, 64);
+        bool ok1 = c.x1s.shape[b1 + (c.t1 ? 1 : 0)] == c.m && c.x1s.shape[b1 + (c.t1 ? 0 : 1)] == kq;
+        bool ok2 = c.x2s.shape[b2 + (c.t2 ? 0 : 1)] == c.n && c.x2s.shape[b2 + (c.t2 ? 1 : 0)] == kq;
+        if (!ok1 || !ok2) why_unsupported("mx scale stored with a transposition different from its operand");
+        if (!operand_batch(c.x1s, 3, ob, c.m * kq * 2, &p.sa_bs)) why_unsupported("x1Scale batch dims");
+        if (!operand_batch(c.x2s, 3, ob, c.n * kq * 2, &p.sb_bs)) why_unsupported("x2Scale batch dims");
+    } else if (c.perblock()) {
+        p.mode = OPSNN_QMM_PERBLOCK;
+        if (c.int8_in()) why_unsupported("INT8 per-block (G-B) kernels are not built yet");
+        if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
+        if (!operand_batch(c.x1s, 2, ob, c.x1s.dim(-1) * c.x1s.dim(-2), &p.sa_bs)) why_unsupported("x1Scale batch dims");
+        if (!operand_batch(c.x2s, 2, ob, c.x2s.dim(-1) * c.x2s.dim(-2), &p.sb_bs)) why_unsupported("x2Scale batch dims");
+    } else {
+        p.mode = OPSNN_QMM_DEQ;
+        p.scale_b_len = c.x2s.shape[0];
+        p.scale_a_len = c.has_x1s ? c.x1s.shape[0] : 0;
+        if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
+        if (c.int4_in()) why_unsupported("INT4 x INT4 kernels are not built yet");
+        if (c.out.dtype == ACL_INT8) why_unsupported("INT8 (requant) output is not built yet");
+        // Rounding-point rules of the reference golden (qbmmv3_kernel_golden.py:566-577, 641-692;
+        // matmul_quant_util.py:62-72): which scales lose their low 13 bits, and where a float bias is added.
+        const bool float_bias = c.has_bias && in(c.bias.dtype, {ACL_FLOAT, ACL_BF16, ACL_FLOAT16});
+        const bool double_scale = c.fp8_in() && c.has_x1s && c.x1s.shape[0] == 1;
+        if (c.int8_in() && !c.has_x1s && c.x2s.dtype != ACL_UINT64 && c.x2s.shape[0] == 1 &&
+            !(c.has_bias && in(c.bias.dtype, {ACL_BF16, ACL_FLOAT})))
+            p.deq_flags |= OPSNN_DEQ_TRUNC_SCALE_B;
+        if (double_scale && c.x2s.shape[0] == 1 && !float_bias) p.deq_flags |= OPSNN_DEQ_MERGE_TRUNC;
+        if (c.fp8_in() && !c.has_x1s && float_bias) p.deq_flags |= OPSNN_DEQ_FBIAS_BEFORE_SCALE;
+    }
+    exec->kernel_choice = OPSNN_KERNEL_AUTO;
+    if (const char* e = std::getenv("OPSNN_QMM_KERNEL")) exec->kernel_choice = std::atoi(e);
+    if (!exec->unsupported) {
+        if (exec->kernel_choice == OPSNN_KERNEL_AUTO) exec->kernel_choice = opsnn_qmm_select_kernel(&p);
+        exec->workspace_size = opsnn_qmm_workspace_size(&p, exec->kernel_choice);
+    }
+    *workspaceSize = exec->workspace_size;
+    log_info("aclnnQuantMatmulV5 plan: mode=%d b=%ld m=%ld n=%ld k=%ld tA=%d tB=%d kernel=%d ws=%lu%s", p.mode,
+             (long)p.batch, (long)p.m, (long)p.n, (long)p.k, p.trans_a, p.trans_b, exec->kernel_choice,
+             (unsigned long)exec->workspace_size, exec->unsupported ? " (no kernel)" : "");
+    *executor = exec.release();
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    clear_err();
+    if (executor == nullptr) {
+        set_err("aclnnQuantMatmulV5: executor is nullptr");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    std::unique_ptr<aclOpExecutor> exec(executor);  // phase 2 consumes the executor
+    if (exec->magic != 0x4F50534E || exec->kind != ExecKind::kQmm) {
+        exec.release();
+        set_err("aclnnQuantMatmulV5: executor was not created by aclnnQuantMatmulV5GetWorkspaceSize");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    exec->magic = 0;
+    if (exec->nothing_to_do) return ACLNN_SUCCESS;
+    if (exec->unsupported) {
+        set_err("aclnnQuantMatmulV5: %s", exec->unsupported_why.c_str());
+        return ACLNN_ERR_INNER_FIND_KERNEL_ERROR;
+    }
+    if (workspaceSize < exec->workspace_size || (exec->workspace_size > 0 && workspace == nullptr)) {
+        set_err("aclnnQuantMatmulV5: workspace too small (%lu < %lu)", (unsigned long)workspaceSize,
+                (unsigned long)exec->workspace_size);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (exec->qmm.a == nullptr || exec->qmm.b == nullptr || exec->qmm.out == nullptr || exec->qmm.scale_b == nullptr) {
+        set_err("aclnnQuantMatmulV5: a tensor was created without a device address");
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    exec->qmm.workspace = workspace;
+    exec->qmm.workspace_size = workspaceSize;
+    int32_t rc = opsnn_qmm_launch(&exec->qmm, exec->kernel_choice, stream);
+    if (rc != 0) {
+        set_err("aclnnQuantMatmulV5: kernel launch failed with CUDA error %d", rc);
+        return ACLNN_ERR_RUNTIME_ERROR;
+    }
+    return ACLNN_SUCCESS;
+}
+
+}  // extern "C"

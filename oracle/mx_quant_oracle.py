@@ -1,0 +1,44 @@
+"""numpy restatement of the reference's dynamic MX quantisation golden (aclnnDynamicMxQuant, last axis, OCP scale).
+
+Follows quant/dynamic_mx_quant/tests/assets/golden.py of the reference: shared exponent :141-154, element quantisation
+:197-217, _mx_quantize :272-336 (scale padded to an even count with 2^-127, shaped (.., ceil(k/64), 2)).
+
+Test infrastructure only (see oracle/__init__.py).
+"""
+import ml_dtypes
+import numpy as np
+
+_FMT = {
+    "float8_e4m3fn": (ml_dtypes.float8_e4m3fn, 4, 3, 448.0),
+    "float8_e5m2": (ml_dtypes.float8_e5m2, 5, 2, 57344.0),
+    "float4_e2m1": (ml_dtypes.float4_e2m1fn, 2, 1, 6.0),
+}
+
+
+def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32):
+    """x (.., k) bf16|fp16|fp32 -> (y in dst dtype (.., k), scale bytes uint8 (.., ceil(k/64), 2))."""
+    np_dt, ebits, mbits, max_norm = _FMT[dst]
+    xf = x.astype(np.float32)
+    k = xf.shape[-1]
+    nblk = -(-k // block)
+    pad = nblk * block - k
+    if pad:
+        xf = np.pad(xf, [(0, 0)] * (xf.ndim - 1) + [(0, pad)])
+    blk = xf.reshape(xf.shape[:-1] + (nblk, block))
+    amax = np.max(np.abs(blk), axis=-1, keepdims=True)
+    emax = int(np.log2(max_norm))
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(amax == 0, np.float32(2.0 ** -126), amax))) - emax
+    e[amax == 0] = -np.inf
+    e = np.where(e < -127, -127.0, e)
+    r = blk / np.exp2(e).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        pe = np.floor(np.log2(np.abs(r) + (r == 0)))
+    pe = np.maximum(pe, -(2 ** (ebits - 1)) + 2)
+    q = np.rint(r / np.exp2(pe) * (2 ** mbits)) / (2 ** mbits) * np.exp2(pe)
+    q = np.clip(q, -max_norm, max_norm).astype(np.float32)
+    y = q.reshape(xf.shape)[..., :k].astype(np_dt)
+    sbytes = (e[..., 0] + 127).astype(np.uint8)
+    if nblk % 2:
+        sbytes = np.concatenate([sbytes, np.zeros(sbytes.shape[:-1] + (1,), np.uint8)], axis=-1)
+    return y, sbytes.reshape(sbytes.shape[:-1] + (sbytes.shape[-1] // 2, 2))

@@ -1,0 +1,76 @@
+"""numpy restatement of the reference's weight-only quant matmul golden (aclnnWeightQuantBatchMatmulV2/V3 path).
+
+Follows matmul/weight_quant_batch_matmul_v2/tests/assets/wqbmmv2_kernel_golden.py of the reference
+(prepare_* :41-82, matmul_and_finalize/finalize :85-103, _compute_tc :199-239, _compute_pergroup :242-297) and the
+int32 -> int4 unpack of wqbmmv2_aclnn_golden.py:128-144 / matmul_quant_util.py:228-273 (element j of a word at bits 4j).
+
+Test infrastructure only (see oracle/__init__.py).
+"""
+import ml_dtypes
+import numpy as np
+
+BF16 = ml_dtypes.bfloat16
+
+
+def unpack_int4_words(packed):
+    """int32 (.., c) -> int8 (.., 8c), sign-extended nibbles, low nibble first."""
+    u = np.ascontiguousarray(packed).view(np.uint32)
+    out = np.empty(u.shape + (8,), dtype=np.int8)
+    for j in range(8):
+        nib = ((u >> np.uint32(4 * j)) & np.uint32(0xF)).astype(np.int8)
+        out[..., j] = (nib ^ 8) - 8
+    return out.reshape(u.shape[:-1] + (u.shape[-1] * 8,))
+
+
+def pack_int4_words(vals):
+    """int8 values in [-8,7], (.., 8c) -> int32 (.., c)."""
+    v = (np.asarray(vals).astype(np.int64) & 0xF).reshape(vals.shape[:-1] + (vals.shape[-1] // 8, 8))
+    out = np.zeros(v.shape[:-1], dtype=np.int64)
+    for j in range(8):
+        out |= v[..., j] << (4 * j)
+    return out.astype(np.uint32).view(np.int32)
+
+
+def dequant_weight(w, scale, offset, group_size, inter):
+    """w (k,n) integer values; scale/offset (1|groups, 1|n) or (n,) in `inter` dtype. Two roundings in `inter`."""
+    wf = w.astype(np.float32)
+    sf = np.atleast_2d(scale.astype(np.float32))
+    of = None if offset is None else np.atleast_2d(offset.astype(np.float32))
+    k = wf.shape[0]
+    if group_size and group_size > 0:
+        reps = -(-k // group_size)
+        sf = np.repeat(sf, group_size, axis=0)[:k] if sf.shape[0] == reps else sf
+        if of is not None:
+            of = np.repeat(of, group_size, axis=0)[:k] if of.shape[0] == reps else of
+    if of is not None:
+        wf = (wf + of).astype(inter).astype(np.float32)
+    return (wf * sf).astype(inter).astype(np.float32)
+
+
+def weight_quant_batch_matmul(x, w, scale, offset=None, bias=None, group_size=0):
+    """x (m,k) bf16|fp16; w (k,n) integer values (already unpacked, already in (k,n) orientation);
+    scale/offset in (groups|1, n|1) orientation. Returns y in x's dtype."""
+    inter = x.dtype.type
+    wf = dequant_weight(w, scale, offset, group_size, inter)
+    out = np.matmul(x.astype(np.float32), wf)
+    if bias is not None:
+        out = out + bias.astype(np.float32)
+    return out.astype(inter)
+
+
+def fp32_dequant_product(x, w, scale, offset=None, bias=None, group_size=0):
+    """The tolerance yardstick: x @ ((w + offset) * scale) with no intermediate rounding, float64 accumulate."""
+    wf = w.astype(np.float64)
+    sf = np.atleast_2d(scale.astype(np.float64))
+    of = None if offset is None else np.atleast_2d(offset.astype(np.float64))
+    k = wf.shape[0]
+    if group_size and group_size > 0:
+        sf = np.repeat(sf, group_size, axis=0)[:k]
+        if of is not None:
+            of = np.repeat(of, group_size, axis=0)[:k]
+    if of is not None:
+        wf = wf + of
+    out = np.matmul(x.astype(np.float64), wf * sf)
+    if bias is not None:
+        out = out + bias.astype(np.float64)
+    return out
