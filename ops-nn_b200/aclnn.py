@@ -1,0 +1,239 @@
+"""ctypes bindings of the aclnn entry points exported by libopsnn_b200.so, plus torch-tensor conveniences.
+
+Mirrors the reference's operator interface (names, argument order and meaning, status codes):
+  aclnnQuantMatmulV5[GetWorkspaceSize]            matmul/quant_batch_matmul_v4/op_host/op_api/aclnn_quant_matmul_v5.h:43-60
+  aclnnWeightQuantBatchMatmulV2/V3[GetWorkspaceSize]  matmul/weight_quant_batch_matmul_v2/op_host/op_api/*.h
+  aclnnDynamicMxQuant[GetWorkspaceSize]           quant/dynamic_mx_quant/docs/aclnnDynamicMxQuant.md:76-95
+
+There is no CPU or PyTorch fallback: if the shared library is missing, loading fails; if no CUDA device is present,
+phase 2 fails with ACLNN_ERR_RUNTIME_ERROR.
+"""
+import ctypes
+import os
+from ctypes import POINTER, byref, c_bool, c_char_p, c_int, c_int32, c_int64, c_uint64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libopsnn_b200.so")
+
+ACLNN_SUCCESS = 0
+ACLNN_ERR_PARAM_NULLPTR = 161001
+ACLNN_ERR_PARAM_INVALID = 161002
+ACLNN_ERR_RUNTIME_ERROR = 361001
+ACLNN_ERR_INNER_FIND_KERNEL_ERROR = 561003
+
+STATUS_NAMES = {0: "ACLNN_SUCCESS", 161001: "ACLNN_ERR_PARAM_NULLPTR", 161002: "ACLNN_ERR_PARAM_INVALID",
+                361001: "ACLNN_ERR_RUNTIME_ERROR", 561003: "ACLNN_ERR_INNER_FIND_KERNEL_ERROR"}
+
+# aclDataType
+ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_UINT8, ACL_INT64, ACL_UINT64 = 0, 1, 2, 3, 4, 9, 10
+ACL_BF16, ACL_INT4, ACL_HIFLOAT8, ACL_FLOAT8_E5M2, ACL_FLOAT8_E4M3FN, ACL_FLOAT8_E8M0 = 27, 29, 34, 35, 36, 37
+ACL_FLOAT4_E2M1, ACL_FLOAT4_E1M2 = 40, 41
+DTYPE_BY_NAME = {"float32": 0, "float16": 1, "int8": 2, "int32": 3, "uint8": 4, "int64": 9, "uint64": 10, "bfloat16": 27,
+                 "int4": 29, "hifloat8": 34, "float8_e5m2": 35, "float8_e4m3fn": 36, "float8_e8m0": 37,
+                 "float4_e2m1": 40, "float4_e1m2": 41}
+for _k, _v in list(DTYPE_BY_NAME.items()):
+    DTYPE_BY_NAME["ACL_" + {"float32": "FLOAT", "bfloat16": "BF16"}.get(_k, _k.upper())] = _v
+DTYPE_BITS = {0: 32, 1: 16, 2: 8, 3: 32, 4: 8, 9: 64, 10: 64, 27: 16, 29: 4, 34: 8, 35: 8, 36: 8, 37: 8, 40: 4, 41: 4}
+ACL_FORMAT_ND, ACL_FORMAT_FRACTAL_NZ = 2, 29
+
+_lib = None
+
+
+def lib():
+    """Loads the shared library (once). Raises if it has not been built: there is nothing to fall back to."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError("libopsnn_b200.so is not built (%s); run `python ops-nn_b200/build.py`" % LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    P64 = POINTER(c_int64)
+    L.aclCreateTensor.restype = c_void_p
+    L.aclCreateTensor.argtypes = [P64, c_uint64, c_int, P64, c_int64, c_int, P64, c_uint64, c_void_p]
+    L.aclDestroyTensor.argtypes = [c_void_p]
+    L.aclDestroyAclOpExecutor.argtypes = [c_void_p]
+    L.aclGetRecentErrMsg.restype = c_char_p
+    T = c_void_p
+    L.aclnnQuantMatmulV5GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, T, T, c_bool, c_bool, c_int64, T,
+                                                      POINTER(c_uint64), POINTER(c_void_p)]
+    L.aclnnWeightQuantBatchMatmulV2GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, T, POINTER(c_uint64),
+                                                                 POINTER(c_void_p)]
+    L.aclnnWeightQuantBatchMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, c_int, T, POINTER(c_uint64),
+                                                                 POINTER(c_void_p)]
+    L.aclnnDynamicMxQuantGetWorkspaceSize.argtypes = [T, c_int64, c_char_p, c_int64, c_int64, c_int64, T, T,
+                                                       POINTER(c_uint64), POINTER(c_void_p)]
+    for name in ("aclnnQuantMatmulV5", "aclnnWeightQuantBatchMatmulV2", "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant"):
+        getattr(L, name).argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
+        getattr(L, name).restype = c_int32
+        getattr(L, name + "GetWorkspaceSize").restype = c_int32
+    L.opsnn_launch_count.restype = c_uint64
+    L.opsnn_last_kernel_name.restype = c_char_p
+    _lib = L
+    return L
+
+
+def last_error():
+    return lib().aclGetRecentErrMsg().decode()
+
+
+def launch_count():
+    return int(lib().opsnn_launch_count())
+
+
+def last_kernel_name():
+    return lib().opsnn_last_kernel_name().decode()
+
+
+class AclnnError(RuntimeError):
+    def __init__(self, api, status):
+        self.status = status
+        super().__init__("%s returned %s (%d): %s" % (api, STATUS_NAMES.get(status, "?"), status, last_error()))
+
+
+class Tensor:
+    """An aclTensor descriptor. `data` is a device address (int) or a torch tensor whose storage backs the view."""
+
+    def __init__(self, shape, dtype, data=0, strides=None, offset=0, fmt=ACL_FORMAT_ND, storage_shape=None):
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = DTYPE_BY_NAME[dtype] if isinstance(dtype, str) else int(dtype)
+        self._keep = data
+        ptr = data if isinstance(data, int) else (data.data_ptr() if data is not None else 0)
+        n = len(self.shape)
+        dims = (c_int64 * max(n, 1))(*self.shape)
+        st = None if strides is None else (c_int64 * max(n, 1))(*[int(s) for s in strides])
+        sshape = self.shape if storage_shape is None else tuple(storage_shape)
+        sd = (c_int64 * max(len(sshape), 1))(*sshape)
+        self.handle = lib().aclCreateTensor(dims, n, self.dtype, st, int(offset), int(fmt), sd, len(sshape), c_void_p(ptr))
+        if not self.handle:
+            raise ValueError("aclCreateTensor rejected the arguments")
+
+    def __del__(self):
+        try:
+            if getattr(self, "handle", None):
+                lib().aclDestroyTensor(c_void_p(self.handle))
+                self.handle = None
+        except Exception:
+            pass
+
+
+def _h(t):
+    return None if t is None else c_void_p(t.handle)
+
+
+def _torch_dtype_code(t):
+    import torch
+
+    m = {torch.float32: ACL_FLOAT, torch.float16: ACL_FLOAT16, torch.bfloat16: ACL_BF16, torch.int8: ACL_INT8,
+         torch.int32: ACL_INT32, torch.uint8: ACL_UINT8, torch.int64: ACL_INT64}
+    for name, code in (("float8_e4m3fn", ACL_FLOAT8_E4M3FN), ("float8_e5m2", ACL_FLOAT8_E5M2), ("uint64", ACL_UINT64)):
+        if hasattr(torch, name):
+            m[getattr(torch, name)] = code
+    return m[t.dtype]
+
+
+def from_torch(t, dtype=None, shape=None, strides=None):
+    """Descriptor over a torch tensor's memory. `dtype`/`shape` override the torch view for types torch lacks
+    (e.g. a uint8 tensor of packed fp4 described as ACL_FLOAT4_E2M1 with twice the inner extent)."""
+    if t is None:
+        return None
+    code = _torch_dtype_code(t) if dtype is None else (DTYPE_BY_NAME[dtype] if isinstance(dtype, str) else dtype)
+    if shape is None:
+        shape, strides = tuple(t.shape), tuple(t.stride())
+    return Tensor(shape, code, t, strides)
+
+
+def _stream():
+    import torch
+
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _workspace(nbytes, like):
+    import torch
+
+    if nbytes == 0:
+        return None, c_void_p(0)
+    ws = torch.empty(int(nbytes), dtype=torch.uint8, device=like.device)
+    return ws, c_void_p(ws.data_ptr())
+
+
+# ---- phase-1-only helpers (return the raw status; used by the argument-validation tests) -----------------------
+
+def quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, y_scale, x1_offset, x2_offset, y_offset, bias,
+                                       transpose_x1, transpose_x2, group_size, out):
+    ws, ex = c_uint64(0), c_void_p(0)
+    st = lib().aclnnQuantMatmulV5GetWorkspaceSize(_h(x1), _h(x2), _h(x1_scale), _h(x2_scale), _h(y_scale), _h(x1_offset),
+                                                  _h(x2_offset), _h(y_offset), _h(bias), bool(transpose_x1),
+                                                  bool(transpose_x2), int(group_size), _h(out), byref(ws), byref(ex))
+    return st, ws.value, ex
+
+
+def weight_quant_batch_matmul_get_workspace_size(x, weight, antiquant_scale, antiquant_offset, quant_scale, quant_offset,
+                                                 bias, antiquant_group_size, y, inner_precise=None):
+    ws, ex = c_uint64(0), c_void_p(0)
+    L = lib()
+    if inner_precise is None:
+        st = L.aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(_h(x), _h(weight), _h(antiquant_scale), _h(antiquant_offset),
+                                                             _h(quant_scale), _h(quant_offset), _h(bias),
+                                                             int(antiquant_group_size), _h(y), byref(ws), byref(ex))
+    else:
+        st = L.aclnnWeightQuantBatchMatmulV3GetWorkspaceSize(_h(x), _h(weight), _h(antiquant_scale), _h(antiquant_offset),
+                                                             _h(quant_scale), _h(quant_offset), _h(bias),
+                                                             int(antiquant_group_size), int(inner_precise), _h(y),
+                                                             byref(ws), byref(ex))
+    return st, ws.value, ex
+
+
+def destroy_executor(ex):
+    if ex is not None and ex.value:
+        lib().aclDestroyAclOpExecutor(ex)
+
+
+# ---- both phases on device tensors -------------------------------------------------------------------------------
+
+def quant_matmul_v5(x1, x2, x1_scale, x2_scale, out, bias=None, transpose_x1=False, transpose_x2=False, group_size=0,
+                    x2_offset=None, workspace=None):
+    """Runs aclnnQuantMatmulV5 on the current torch CUDA stream. Arguments are `Tensor` descriptors over device memory;
+    `out` is written in place. Returns the workspace size used."""
+    st, ws_size, ex = quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, None, None, x2_offset, None, bias,
+                                                         transpose_x1, transpose_x2, group_size, out)
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnQuantMatmulV5GetWorkspaceSize", st)
+    if workspace is not None and workspace.numel() >= ws_size:
+        keep, wp = workspace, c_void_p(workspace.data_ptr())
+    else:
+        keep, wp = _workspace(ws_size, out._keep)
+    st = lib().aclnnQuantMatmulV5(wp, c_uint64(ws_size if keep is None else keep.numel()), ex, _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnQuantMatmulV5", st)
+    return ws_size
+
+
+def weight_quant_batch_matmul(x, weight, antiquant_scale, y, antiquant_offset=None, bias=None, antiquant_group_size=0,
+                              inner_precise=None, workspace=None):
+    """Runs aclnnWeightQuantBatchMatmulV2 (or V3 when `inner_precise` is given) on the current torch CUDA stream."""
+    st, ws_size, ex = weight_quant_batch_matmul_get_workspace_size(x, weight, antiquant_scale, antiquant_offset, None, None,
+                                                                   bias, antiquant_group_size, y, inner_precise)
+    api = "aclnnWeightQuantBatchMatmulV2" if inner_precise is None else "aclnnWeightQuantBatchMatmulV3"
+    if st != ACLNN_SUCCESS:
+        raise AclnnError(api + "GetWorkspaceSize", st)
+    if workspace is not None and workspace.numel() >= ws_size:
+        keep, wp = workspace, c_void_p(workspace.data_ptr())
+    else:
+        keep, wp = _workspace(ws_size, y._keep)
+    st = getattr(lib(), api)(wp, c_uint64(ws_size if keep is None else keep.numel()), ex, _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError(api, st)
+    return ws_size
+
+
+def dynamic_mx_quant(x, y_out, mxscale_out, dst_type, axis=-1, round_mode=b"rint", blocksize=32, scale_alg=0):
+    ws, ex = c_uint64(0), c_void_p(0)
+    code = DTYPE_BY_NAME[dst_type] if isinstance(dst_type, str) else dst_type
+    st = lib().aclnnDynamicMxQuantGetWorkspaceSize(_h(x), int(axis), round_mode, int(code), int(blocksize), int(scale_alg),
+                                                   _h(y_out), _h(mxscale_out), byref(ws), byref(ex))
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnDynamicMxQuantGetWorkspaceSize", st)
+    st = lib().aclnnDynamicMxQuant(c_void_p(0), c_uint64(0), ex, _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnDynamicMxQuant", st)

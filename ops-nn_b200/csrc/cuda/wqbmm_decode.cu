@@ -22,8 +22,10 @@
 // gridDim = SMs x resident CTAs, so every SM streams the same number of bytes regardless of n and k. A strip whose k
 // range is shared by several CTAs is summed through workspace: every contributor stores its fp32 fragment, then a
 // launch nonce; whichever contributor observes all nonces present (at least one does: store, fence.sc, load) adds
-// the fragments in CTA order - so the result does not depend on arrival order - and writes y. No atomics, no spinning,
-// no zero-initialised workspace.
+// the fragments in CTA order - so the result does not depend on arrival order - and writes y, then zeroes the strip's
+// nonces. No atomics, no spinning, no zero-initialised workspace (stale bytes never equal a fresh 64-bit nonce), and a
+// replayed launch with an unchanged nonce still works because the previous run retired its tags. Two launches must
+// not share one workspace concurrently.
 #include <atomic>
 #include <chrono>
 
@@ -300,6 +302,12 @@ __global__ void __launch_bounds__(kThreads, 3) wqbmm_decode_kernel(const DecodeA
                 }
             }
             __syncthreads();  // s_reduce is reused by the next strip of this CTA
+            if (do_write && tid == 0) {
+                // every contributor's fragment has been consumed: retire the strip's tags, so that a replay of this very
+                // launch (same nonce, e.g. from a captured CUDA graph) starts from a clean slate
+                for (int64_t cc = c_lo; cc <= c_hi; ++cc)
+                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + cc + strip), "l"(0ull) : "memory");
+            }
         }
         if (do_write) {
             // D fragment: rows g, g+8; tile-local columns 2q, 2q+1 = lane groups 2q, 2q+1 of the loader

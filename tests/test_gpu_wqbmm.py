@@ -1,0 +1,118 @@
+"""GPU parity: aclnnWeightQuantBatchMatmulV2/V3 and aclnnDynamicMxQuant through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import golden_names, load_golden
+from oracle import mx_quant_oracle, wqbmm_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref64(a, meta):
+    t = meta["transpose_weight"]
+    w = a["w"].T if t else a["w"]
+    sc = a["scale"].T if (t and a["scale"].ndim == 2) else a["scale"]
+    of = a.get("offset")
+    if of is not None and t and of.ndim == 2:
+        of = of.T
+    return wqbmm_oracle.fp32_dequant_product(a["x"], w, sc, of, a.get("bias"), meta["group_size"])
+
+
+@pytest.mark.parametrize("kernel", [1, 0], ids=["generic", "auto"])
+@pytest.mark.parametrize("name", golden_names("wq_"))
+def test_fixture(aclnn, name, kernel):
+    from gpu_util import check_close, np_name, run_wq_fixture
+
+    a, meta = load_golden(name)
+    got = run_wq_fixture(aclnn, a, meta, kernel=kernel)
+    # cancellation in x @ w' amplifies the (specified) double rounding of w' relative to an unrounded product,
+    # so the yardstick's denominator is floored at the output rms here
+    check_close(got, a["out"], _ref64(a, meta), np_name(a["out"]), floor_rms=1.0)
+
+
+def test_decode_kernel_is_selected_and_matches_golden_tightly(aclnn):
+    """The small-m int4 fixtures must run on the streaming decode kernel, and since it reproduces the reference's two
+    roundings per weight its output may differ from the golden only by fp32 summation order: <= 1 ulp of the output
+    dtype, on a small fraction of elements."""
+    from gpu_util import np_name, run_wq_fixture
+
+    for name in ("wq_bf16_s4_group128_offset_m16", "wq_bf16_s4_group160_m1_fbias", "wq_fp16_s4_group64_bias_m8",
+                 "wq_fp16_s4_channel_offset_bias"):
+        a, meta = load_golden(name)
+        got = run_wq_fixture(aclnn, a, meta, kernel=0, api="v3")
+        assert aclnn.last_kernel_name() == "wqbmm_decode", name
+        g = got.astype(np.float64)
+        w = a["out"].astype(np.float64)
+        ulp = 2.0 ** -7 if np_name(a["out"]) == "bfloat16" else 2.0 ** -10
+        rms = np.sqrt(np.mean(w ** 2))
+        assert np.all(np.abs(g - w) <= ulp * np.maximum(np.abs(w), 0.05 * rms) * 1.01), name
+        assert np.mean(g != w) < 0.05, name
+
+
+def test_decode_c2_shape_properties(aclnn):
+    """Full benchmark shape (m16 k8192 n28672 g128): checked through size-independent properties and a sampled oracle.
+      * linearity in x: f(2x) == 2 f(x) bit for bit (powers of two commute with every rounding here);
+      * zero rows of x give exactly-zero rows of y; rows are independent (row i of a 16-row call == the 1-row call);
+      * 512 sampled output columns against the numpy oracle."""
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    m, k, n, g = 16, 8192, 28672, 128
+    gen = torch.Generator(device=DEV).manual_seed(1002)
+    x = torch.randn((m, k), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    x[5].zero_()
+    w = torch.randint(-8, 8, (k, n), generator=gen, device=DEV, dtype=torch.int32)
+    words = torch.zeros((k, n // 8), dtype=torch.int32, device=DEV)
+    for j in range(8):
+        words |= (w[:, j::8] & 0xF) << (4 * j)
+    scale = (torch.rand((k // g, n), generator=gen, device=DEV) * 0.015 + 0.005).to(torch.bfloat16)
+    offset = (torch.rand((k // g, n), generator=gen, device=DEV) * 2 - 1).to(torch.bfloat16)
+
+    def run(xx):
+        y = torch.full((xx.shape[0], n), -7777.0, dtype=torch.bfloat16, device=DEV)
+        aclnn.weight_quant_batch_matmul(aclnn.from_torch(xx), aclnn.from_torch(words), aclnn.from_torch(scale),
+                                        aclnn.from_torch(y), aclnn.from_torch(offset), None, g)
+        torch.cuda.synchronize()
+        assert aclnn.last_kernel_name() == "wqbmm_decode"
+        return y
+
+    y1 = run(x)
+    y1b = run(x)
+    assert torch.equal(y1, y1b), "two identical calls must agree bit for bit (the cross-CTA sum has a fixed order)"
+    assert not bool((y1 == -7777.0).any())
+    assert bool((y1[5] == 0).all())
+    y2 = run(x * 2)
+    assert torch.equal(y2.float(), y1.float() * 2)
+    y_row = run(x[3:4].contiguous())
+    assert torch.equal(y_row[0], y1[3])
+    cols = np.sort(np.random.default_rng(3).choice(n, 512, replace=False))
+    ct = torch.from_numpy(cols).to(DEV)
+    wn = w[:, ct].cpu().numpy().astype(np.int8)
+    want = wqbmm_oracle.weight_quant_batch_matmul(out_to_np(x), wn, out_to_np(scale[:, ct].contiguous()),
+                                                  out_to_np(offset[:, ct].contiguous()), None, g)
+    got = out_to_np(y1[:, ct].contiguous())
+    gw, ww = got.astype(np.float64), want.astype(np.float64)
+    rms = np.sqrt(np.mean(ww ** 2))
+    assert np.all(np.abs(gw - ww) <= 2.0 ** -7 * np.maximum(np.abs(ww), 0.05 * rms) * 1.01)
+
+
+@pytest.mark.parametrize("name", golden_names("mxq_"))
+def test_dynamic_mx_quant_fixture(aclnn, name):
+    import torch
+
+    from gpu_util import DEV, desc
+
+    a, meta = load_golden(name)
+    x = a["x"]
+    dst = meta["dst"]
+    ybytes = x.shape[:-1] + ((x.shape[-1] // 2,) if dst == "float4_e2m1" else (x.shape[-1],))
+    y = torch.full(ybytes, 0xAA, dtype=torch.uint8, device=DEV)
+    s = torch.full(a["scale"].shape, 0xAA, dtype=torch.uint8, device=DEV)
+    aclnn.dynamic_mx_quant(desc(aclnn, x), aclnn.Tensor(x.shape, dst, y), aclnn.Tensor(a["scale"].shape, "float8_e8m0", s), dst)
+    torch.cuda.synchronize()
+    want_y = a["y"].view(np.uint8)
+    if dst == "float4_e2m1":
+        want_y = (want_y[..., 0::2] & 0xF) | ((want_y[..., 1::2] & 0xF) << 4)
+    assert np.array_equal(s.cpu().numpy(), a["scale"].view(np.uint8)), "e8m0 scales differ"
+    assert np.array_equal(y.cpu().numpy(), want_y), "quantised elements differ"
