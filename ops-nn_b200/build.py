@@ -25,6 +25,9 @@ COMMON = [
     "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(CSRC, "host"), "-I" + os.path.join(CSRC, "cuda"),
     "--expt-relaxed-constexpr", "-diag-suppress", "177,550",
 ]
+for _m in ("OPSNN_DECODE_PF", "OPSNN_DECODE_MINB"):  # tuning knobs of the decode kernel, unset in normal builds
+    if os.environ.get(_m):
+        COMMON.append("-D%s=%s" % (_m, os.environ[_m]))
 
 
 def sources():

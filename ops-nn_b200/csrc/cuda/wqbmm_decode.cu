@@ -7,22 +7,24 @@
 //
 // Data layout. w is int4 packed 8 per 32-bit word along n, element j of a word at bits [4j,4j+4), word (k,c) holds
 // columns 8c..8c+7 (reference: aclnn_weight_quant_batch_matmul_v2.cpp:1482-1524). scale/offset are (groups, n) in x's
-// dtype. The weight (k*n/2 bytes) is read exactly once from HBM with 8-byte loads, 128 contiguous bytes per row per
-// warp-row; x (m*k*2 bytes) and the scales stay in L2/L1.
+// dtype. The weight (k*n/2 bytes) is read exactly once from HBM; x (m*k*2 bytes) is staged through shared memory with
+// cp.async (double buffered, 512 k at a time); the scales stay in L2/L1.
 //
-// Mapping. One warp owns 128 columns. Lane (g = lane/4, q = lane%4) loads the word pair 2g,2g+1 (16 columns) of the four
-// rows {2q, 2q+1, 2q+8, 2q+9} of every 16-row k-step: exactly the rows an m16n8k16 B fragment wants from this lane.
-// A byte permute pairs the two rows' words so that one mask-xor turns nibble j of both rows into a bf16x2 {136+w_k,
-// 136+w_k+1} (0x4300 | (nibble ^ 8) == 128 + 8 + w, exact); then, per the reference's rounding points,
-//     w' = hmul2( hadd2( hsub2(v, 136), offset ), scale )          // each a single bf16 (fp16) rounding, no FMA
-// feeds mma.sync.m16n8k16 (fp32 accumulate). Nibble j of word h of the pair is MMA tile 8h+j, so no data is shuffled
-// between lanes; the column permutation this implies is undone when y is written.
+// Mapping. One warp owns 64 columns, one CTA (8 warps) a strip of 512. Lane (g = lane/4, q = lane%4) loads word g of
+// the warp (8 columns) of the four rows {2q, 2q+1, 2q+8, 2q+9} of every 16-row k-step: exactly the rows an m16n8k16 B
+// fragment wants from this lane. Eight k-steps of words are kept in flight in registers. A byte permute pairs the two
+// rows' words so that one three-input logic op turns nibble j of both rows into a bf16x2 {136+w_k, 136+w_k+1}
+// (0x4300 | (nibble ^ 8) == 128 + 8 + w, exact); then, per the reference's rounding points,
+//     w' = mul.rn( add.rn( sub.rn(v, 136), offset ), scale )       // each a single bf16 (fp16) rounding, no FMA
+// feeds mma.sync.m16n8k16 (fp32 accumulate). Nibble j of the word is MMA tile j, so no data is shuffled between
+// lanes; the column permutation this implies is undone when y is written.
 //
-// Work split. The (column strip of 512) x (k-step of 16) space is cut into equal contiguous runs, one per CTA, with
-// gridDim = SMs x resident CTAs, so every SM streams the same number of bytes regardless of n and k. A strip whose k
-// range is shared by several CTAs is summed through workspace: every contributor stores its fp32 fragment, then a
-// launch nonce; whichever contributor observes all nonces present (at least one does: store, fence.sc, load) adds
-// the fragments in CTA order - so the result does not depend on arrival order - and writes y, then zeroes the strip's
+// Work split. gridDim = strips x Q: CTA c owns column strip (c % strips) of 512 columns and the q-th of Q equal k ranges,
+// q = c / strips, with Q = resident CTAs / strips. CTAs that run side by side therefore read side-by-side 256-byte pieces
+// of the same weight rows, so DRAM sees whole rows being streamed instead of hundreds of narrow strided streams.
+// A strip's Q contributors are summed through workspace: every contributor stores its fp32 fragment, then a launch
+// nonce; whichever contributor observes all nonces present (at least one does: store, fence.sc, load) adds the
+// fragments in CTA order - so the result does not depend on arrival order - and writes y, then zeroes the strip's
 // nonces. No atomics, no spinning, no zero-initialised workspace (stale bytes never equal a fresh 64-bit nonce), and a
 // replayed launch with an unchanged nonce still works because the previous run retired its tags. Two launches must
 // not share one workspace concurrently.
@@ -35,11 +37,20 @@ namespace opsnn {
 
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStripCols = kWarps * 128;  // 512
-constexpr int kPrefetch = 4;              // k-steps of weight words held in registers ahead of use
-constexpr int kTiles = 16;                // m16n8 tiles per warp
+constexpr int kWarpCols = 64;               // one packed word (8 columns) per lane-group g
+constexpr int kStripCols = kWarps * kWarpCols;  // 512
+#ifndef OPSNN_DECODE_PF
+#define OPSNN_DECODE_PF 8
+#endif
+#ifndef OPSNN_DECODE_MINB
+#define OPSNN_DECODE_MINB 2
+#endif
+constexpr int kPrefetch = OPSNN_DECODE_PF;  // k-steps of weight words held in registers ahead of use
+constexpr int kTiles = 8;                 // m16n8 tiles per warp: nibble j of the lane's word is tile j
+constexpr int kChunk = 32;                // k-steps of x staged in shared memory at a time (double buffered)
+constexpr int kXPitch = kChunk * 16 + 8;  // elements; the +8 skews rows over the banks so fragment reads do not conflict
 
 struct DecodeArgs {
     const uint32_t* w;     // packed words
@@ -56,16 +67,17 @@ struct DecodeArgs {
     int64_t y_ld;
     int32_t m;
     int64_t n, k;
-    int64_t strips, ksteps, total, steps_per_group;
-    unsigned long long* tags;  // [gridDim + strips]
-    float4* partials;          // [gridDim + strips][kWarps][kTiles][32]
+    int64_t strips, ksteps, splits, steps_per_group;
+    unsigned long long* tags;  // [gridDim]
+    float4* partials;          // [gridDim][kWarps][kTiles][32]
     unsigned long long nonce;
+    uint32_t c_mask, c_magic, c_bias;  // 0x000F000F, Num::kMagic, Num::kBias
 };
 
-__device__ __forceinline__ uint2 ldg_stream(const uint2* p)
+__device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p)
 {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
 
@@ -76,14 +88,32 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
     return d;
 }
 
+// 16-bit pair arithmetic on raw 32-bit registers (no type punning through memory): each op rounds once, to nearest even.
 template <bool kBf16>
 struct Num;
 template <>
 struct Num<true> {
-    using T2 = __nv_bfloat162;
-    static constexpr uint32_t kMagic = 0x43084308u;  // (nibble ^ 8) | 0x4300  ->  128 + 8 + w
+    static constexpr uint32_t kMagic = 0x43084308u;  // (nibble ^ 8) | 0x4300  ->  bf16 128 + 8 + w
     static constexpr uint32_t kBias = 0x43084308u;   // bf16x2 {136, 136}
-    __device__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    __device__ __forceinline__ static uint32_t sub(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static uint32_t add(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
     {
         asm volatile(
             "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -93,10 +123,27 @@ struct Num<true> {
 };
 template <>
 struct Num<false> {
-    using T2 = __half2;
-    static constexpr uint32_t kMagic = 0x64086408u;  // (nibble ^ 8) | 0x6400  ->  1024 + 8 + w
+    static constexpr uint32_t kMagic = 0x64086408u;  // (nibble ^ 8) | 0x6400  ->  fp16 1024 + 8 + w
     static constexpr uint32_t kBias = 0x64086408u;   // half2 {1032, 1032}
-    __device__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    __device__ __forceinline__ static uint32_t sub(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static uint32_t add(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b)
+    {
+        uint32_t d;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
+    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
     {
         asm volatile(
             "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -105,175 +152,188 @@ struct Num<false> {
     }
 };
 
-template <class T2>
-__device__ __forceinline__ T2 as_t2(uint32_t v)
-{
-    return *reinterpret_cast<T2*>(&v);
-}
-template <class T2>
-__device__ __forceinline__ uint32_t as_u32(T2 v)
-{
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
 // Two nibbles (bits [3:0] and [19:16] of t) -> dequantised 16-bit pair, with the reference's two roundings.
+// mask / magic / bias come from kernel parameters, i.e. the constant bank, so that they cost neither a register nor a
+// re-materialising move in front of every use; (t & mask) ^ magic is a single three-input logic op.
 template <bool kBf16, bool kHasOffset>
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t t, uint32_t scale2, uint32_t off2)
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t t, uint32_t scale2, uint32_t off2, uint32_t mask, uint32_t magic,
+                                                 uint32_t bias)
 {
     using N = Num<kBf16>;
-    using T2 = typename N::T2;
-    T2 v = as_t2<T2>((t & 0x000F000Fu) ^ N::kMagic);
-    v = __hsub2(v, as_t2<T2>(N::kBias));                       // exact: w in [-8, 7]
-    if (kHasOffset) v = __hadd2(v, as_t2<T2>(off2));           // rounding #1
-    v = __hmul2(v, as_t2<T2>(scale2));                         // rounding #2
-    return as_u32(v);
+    uint32_t v;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(t), "r"(mask), "r"(magic));
+    v = N::sub(v, bias);                      // exact: w in [-8, 7]
+    if (kHasOffset) v = N::add(v, off2);      // rounding #1
+    return N::mul(v, scale2);                 // rounding #2
 }
 
 template <bool kBf16, bool kHasOffset>
-__global__ void __launch_bounds__(kThreads, 3) wqbmm_decode_kernel(const DecodeArgs a)
+__global__ void __launch_bounds__(kThreads, OPSNN_DECODE_MINB) wqbmm_decode_kernel(const DecodeArgs a)
 {
     using N = Num<kBf16>;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // tells the compiler the warp index is warp-uniform
     __shared__ int s_reduce;
+    __shared__ __align__(16) uint16_t xs[2][16][kXPitch];
 
-    const int64_t P = gridDim.x, c = blockIdx.x;
-    int64_t t0 = (c * a.total) / P;
-    const int64_t t1 = ((c + 1) * a.total) / P;
+    const int64_t c = blockIdx.x;
+    const int64_t strip = c % a.strips;
+    const int64_t chunk = c / a.strips;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a.x);
+    {
+        const int64_t sa = (chunk * a.ksteps) / a.splits;
+        const int64_t sb = ((chunk + 1) * a.ksteps) / a.splits;
 
-    while (t0 < t1) {
-        const int64_t strip = t0 / a.ksteps;
-        const int64_t sa = t0 % a.ksteps;
-        const int64_t sb = min(a.ksteps, sa + (t1 - t0));
-        t0 += sb - sa;
-
-        const int64_t col0 = strip * kStripCols + warp * 128 + 16 * g;  // first of this lane's 16 columns
+        const int64_t col0 = strip * kStripCols + warp * kWarpCols + 8 * g;  // first of this lane's 8 columns
         const bool col_ok = col0 < a.n;
-        const uint2* wp = reinterpret_cast<const uint2*>(a.w + (col_ok ? col0 / 8 : 0));
 
         float acc[kTiles][4];
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
 
-        uint32_t sc[16], of[16];
-        int64_t cur_group = -1;
+        uint32_t sc[kTiles], of[kTiles];
 
-        uint2 wbuf[kPrefetch][4];
-        auto fetch = [&](uint2(&dst)[4], int64_t step) {
-            const bool ok = col_ok && step < sb;
+        // Next step to fetch = warp-uniform 64-bit base (advances 16 rows per fetch, clamped to the last k-step of this
+        // CTA's range, which the prefetch running ahead of the compute then merely re-reads from L1/L2) + per-lane 32-bit
+        // offsets of the lane's four rows and its 4-byte column slot (lanes past n re-read column 0 and are discarded).
+        const int64_t pitch_b = a.w_ld32 * 4;  // row pitch in bytes
+        const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
+        const char* wbase = reinterpret_cast<const char*>(a.w) + (warp_col < a.n ? warp_col : 0) / 2;
+        const char* ubase = wbase + sa * 16 * pitch_b;
+        const char* ulast = wbase + (sb - 1) * 16 * pitch_b;
+        uint32_t loff[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const int64_t row = step * 16 + 2 * q + (r & 1) + (r >> 1) * 8;
-                dst[r] = ok ? ldg_stream(wp + row * (a.w_ld32 / 2)) : make_uint2(0u, 0u);
-            }
+        for (int r = 0; r < 4; ++r)
+            loff[r] = (uint32_t)((2 * q + (r & 1) + (r >> 1) * 8) * pitch_b) + (col_ok ? 4 * g : 0);
+        const int nsteps = (int)(sb - sa);
+        uint32_t wbuf[kPrefetch][4];
+        auto fetch = [&](uint32_t(&dst)[4]) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) dst[r] = ldg_stream(reinterpret_cast<const uint32_t*>(ubase + loff[r]));
+            ubase = (ubase + 16 * pitch_b <= ulast) ? ubase + 16 * pitch_b : ulast;
         };
 #pragma unroll
-        for (int i = 0; i < kPrefetch; ++i) fetch(wbuf[i], sa + i);
+        for (int i = 0; i < kPrefetch; ++i) fetch(wbuf[i]);
 
-        for (int64_t base = sa; base < sb; base += kPrefetch) {
+        // x[:, this run's k range] goes through shared memory in chunks of kChunk steps, double buffered with cp.async:
+        // a fragment read is then a 30-cycle shared load instead of an L2 round trip in front of every MMA group.
+        auto stage_x = [&](int chunk_idx) {
+            const int64_t k_first = (sa + (int64_t)chunk_idx * kChunk) * 16;
+            const int64_t k_end = sb * 16;
+            uint16_t(*dst)[kXPitch] = xs[chunk_idx & 1];
+            for (int e = tid; e < 16 * (kChunk * 2); e += kThreads) {  // 16-byte pieces: 16 rows x (kChunk*16/8)
+                const int row = e / (kChunk * 2), piece = e % (kChunk * 2);
+                const int64_t kk = k_first + piece * 8;
+                uint16_t* d = &dst[row][piece * 8];
+                if (row < a.m && kk < k_end) {
+                    const uint32_t saddr = (uint32_t)__cvta_generic_to_shared(d);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(x16 + (int64_t)row * a.x_ld + kk) : "memory");
+                } else {
+                    *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        const int nchunks = (nsteps + kChunk - 1) / kChunk;
+        stage_x(0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+
+        // k-group bookkeeping without a per-step division: `group_left` steps remain in the current group
+        int64_t group = sa / a.steps_per_group - 1;
+        int first_skip = (int)(sa % a.steps_per_group);  // steps of the first group that precede this run
+        int group_left = 0;                              // 0 forces the scale load on the first step
+        const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+        for (int chunk_idx = 0; chunk_idx < nchunks; ++chunk_idx) {
+          if (chunk_idx + 1 < nchunks) stage_x(chunk_idx + 1);
+          const uint16_t* xrow0 = &xs[chunk_idx & 1][g][2 * q];
+          const uint16_t* xrow1 = &xs[chunk_idx & 1][g + 8][2 * q];
+          const int chunk_end = min(nsteps, (chunk_idx + 1) * kChunk);
+          for (int base = chunk_idx * kChunk; base < chunk_end; base += kPrefetch) {
 #pragma unroll
             for (int i = 0; i < kPrefetch; ++i) {
-                const int64_t step = base + i;
-                uint2 cur[4] = {wbuf[i][0], wbuf[i][1], wbuf[i][2], wbuf[i][3]};
-                fetch(wbuf[i], step + kPrefetch);
-                if (step >= sb) continue;
+                const int step_rel = base + i;
+                const uint32_t wa = wbuf[i][0], wb = wbuf[i][1], wc = wbuf[i][2], wd = wbuf[i][3];
+                fetch(wbuf[i]);
+                if (step_rel >= nsteps) continue;
 
-                const int64_t group = step / a.steps_per_group;
-                if (group != cur_group) {
-                    cur_group = group;
-                    // 16 consecutive columns of scale (and offset) -> one duplicated 16-bit pair per column
-                    uint32_t raw_s[8], raw_o[8];
+                if (group_left == 0) {
+                    ++group;
+                    group_left = spg - first_skip;
+                    first_skip = 0;
+                    // 8 consecutive columns of scale (and offset) -> one duplicated 16-bit pair per column
+                    uint32_t raw_s[4], raw_o[4];
                     if (a.scale_sn != 0) {
                         const int64_t sidx = group * a.scale_sg + (col_ok ? col0 : 0);
-                        const uint4* ps = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.scale) + sidx);
-                        uint4 s0 = __ldg(ps), s1 = __ldg(ps + 1);
+                        const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.scale) + sidx));
                         raw_s[0] = s0.x; raw_s[1] = s0.y; raw_s[2] = s0.z; raw_s[3] = s0.w;
-                        raw_s[4] = s1.x; raw_s[5] = s1.y; raw_s[6] = s1.z; raw_s[7] = s1.w;
                         if (kHasOffset) {
-                            const uint4* po = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.offset) + sidx);
-                            uint4 o0 = __ldg(po), o1 = __ldg(po + 1);
+                            const uint4 o0 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.offset) + sidx));
                             raw_o[0] = o0.x; raw_o[1] = o0.y; raw_o[2] = o0.z; raw_o[3] = o0.w;
-                            raw_o[4] = o1.x; raw_o[5] = o1.y; raw_o[6] = o1.z; raw_o[7] = o1.w;
                         }
                     } else {
-                        const uint32_t s = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
-                        const uint32_t o = kHasOffset ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
+                        const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+                        const uint32_t ov = kHasOffset ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
 #pragma unroll
-                        for (int i2 = 0; i2 < 8; ++i2) {
-                            raw_s[i2] = s | (s << 16);
-                            raw_o[i2] = o | (o << 16);
+                        for (int i2 = 0; i2 < 4; ++i2) {
+                            raw_s[i2] = sv | (sv << 16);
+                            raw_o[i2] = ov | (ov << 16);
                         }
                     }
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
+                    for (int e = 0; e < kTiles; ++e) {
                         const uint32_t sel = (e & 1) ? 0x3232u : 0x1010u;
                         sc[e] = prmt(raw_s[e >> 1], raw_s[e >> 1], sel);
                         if (kHasOffset) of[e] = prmt(raw_o[e >> 1], raw_o[e >> 1], sel);
                     }
                 }
+                --group_left;
 
-                // A fragment: x[rows g, g+8][k0 + 2q .. +1, +8 .. +9]
+                // A fragment: x[rows g, g+8][k0 + 2q .. +1, +8 .. +9] from the staged chunk
                 uint32_t af[4];
                 {
-                    const int64_t k0 = step * 16 + 2 * q;
-                    const uint32_t* r0 = reinterpret_cast<const uint32_t*>(x16 + (int64_t)g * a.x_ld + k0);
-                    const uint32_t* r1 = reinterpret_cast<const uint32_t*>(x16 + (int64_t)(g + 8) * a.x_ld + k0);
-                    af[0] = g < a.m ? __ldg(r0) : 0u;
-                    af[1] = g + 8 < a.m ? __ldg(r1) : 0u;
-                    af[2] = g < a.m ? __ldg(r0 + 4) : 0u;
-                    af[3] = g + 8 < a.m ? __ldg(r1 + 4) : 0u;
+                    const int ls = (step_rel - chunk_idx * kChunk) * 16;
+                    af[0] = *reinterpret_cast<const uint32_t*>(xrow0 + ls);
+                    af[1] = *reinterpret_cast<const uint32_t*>(xrow1 + ls);
+                    af[2] = *reinterpret_cast<const uint32_t*>(xrow0 + ls + 8);
+                    af[3] = *reinterpret_cast<const uint32_t*>(xrow1 + ls + 8);
+                }
+                // low half: nibbles 0..3 of row a | nibbles 0..3 of row b; high half: nibbles 4..7
+                const uint32_t lo01 = prmt(wa, wb, 0x5410u), hi01 = prmt(wa, wb, 0x7632u);
+                const uint32_t lo23 = prmt(wc, wd, 0x5410u), hi23 = prmt(wc, wd, 0x7632u);
+                // dequantise all 16 pairs first (independent chains the scheduler can interleave), then issue the 8 MMAs
+                uint32_t b0[kTiles], b1[kTiles];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    b0[j] = dequant_pair<kBf16, kHasOffset>(lo01 >> (4 * j), sc[j], of[j], a.c_mask, a.c_magic, a.c_bias);
+                    b1[j] = dequant_pair<kBf16, kHasOffset>(lo23 >> (4 * j), sc[j], of[j], a.c_mask, a.c_magic, a.c_bias);
+                    b0[4 + j] = dequant_pair<kBf16, kHasOffset>(hi01 >> (4 * j), sc[4 + j], of[4 + j], a.c_mask, a.c_magic, a.c_bias);
+                    b1[4 + j] = dequant_pair<kBf16, kHasOffset>(hi23 >> (4 * j), sc[4 + j], of[4 + j], a.c_mask, a.c_magic, a.c_bias);
                 }
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t wa = h ? cur[0].y : cur[0].x, wb = h ? cur[1].y : cur[1].x;
-                    const uint32_t wc = h ? cur[2].y : cur[2].x, wd = h ? cur[3].y : cur[3].x;
-                    // low half: nibbles 0..3 of row a | nibbles 0..3 of row b; high half: nibbles 4..7
-                    const uint32_t lo01 = prmt(wa, wb, 0x5410u), hi01 = prmt(wa, wb, 0x7632u);
-                    const uint32_t lo23 = prmt(wc, wd, 0x5410u), hi23 = prmt(wc, wd, 0x7632u);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        {
-                            const int t = h * 8 + j;
-                            const uint32_t b0 = dequant_pair<kBf16, kHasOffset>(lo01 >> (4 * j), sc[t], of[t]);
-                            const uint32_t b1 = dequant_pair<kBf16, kHasOffset>(lo23 >> (4 * j), sc[t], of[t]);
-                            N::mma(acc[t], af, b0, b1);
-                        }
-                        {
-                            const int t = h * 8 + 4 + j;
-                            const uint32_t b0 = dequant_pair<kBf16, kHasOffset>(hi01 >> (4 * j), sc[t], of[t]);
-                            const uint32_t b1 = dequant_pair<kBf16, kHasOffset>(hi23 >> (4 * j), sc[t], of[t]);
-                            N::mma(acc[t], af, b0, b1);
-                        }
-                    }
-                }
+                for (int t = 0; t < kTiles; ++t) N::mma(acc[t], af, b0[t], b1[t]);
             }
+          }
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          __syncthreads();
         }
 
         // ---- this CTA's share of the strip is in acc; combine with the other contributors if there are any ----
-        const bool whole = (sa == 0 && sb == a.ksteps);
+        const bool whole = a.splits == 1;
         bool do_write = whole;
-        int64_t c_lo = c, c_hi = c;
         if (!whole) {
-            float4* mine = a.partials + (((c + strip) * kWarps + warp) * kTiles) * 32 + lane;
+            float4* mine = a.partials + ((c * kWarps + warp) * kTiles) * 32 + lane;
 #pragma unroll
             for (int t = 0; t < kTiles; ++t) mine[t * 32] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
             asm volatile("fence.sc.gpu;" ::: "memory");
             __syncthreads();
             if (tid == 0) {
-                // contributors: CTAs whose run intersects [strip*ksteps, (strip+1)*ksteps)
-                const int64_t first = strip * a.ksteps, last = first + a.ksteps - 1;
-                c_lo = (first * P) / a.total;
-                while (c_lo > 0 && (c_lo * a.total) / P > first) --c_lo;
-                while (((c_lo + 1) * a.total) / P <= first) ++c_lo;
-                c_hi = (last * P) / a.total;
-                while (c_hi > 0 && (c_hi * a.total) / P > last) --c_hi;
-                while (((c_hi + 1) * a.total) / P <= last) ++c_hi;
-                asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(a.tags + c + strip), "l"(a.nonce) : "memory");
+                asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(a.tags + c), "l"(a.nonce) : "memory");
                 asm volatile("fence.sc.gpu;" ::: "memory");
                 int all = 1;
-                for (int64_t cc = c_lo; cc <= c_hi; ++cc) {
+                for (int64_t j = 0; j < a.splits; ++j) {
                     unsigned long long seen;
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.tags + cc + strip) : "memory");
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.tags + strip + j * a.strips) : "memory");
                     all &= (seen == a.nonce);
                 }
                 asm volatile("fence.sc.gpu;" ::: "memory");
@@ -282,18 +342,10 @@ __global__ void __launch_bounds__(kThreads, 3) wqbmm_decode_kernel(const DecodeA
             __syncthreads();
             do_write = s_reduce != 0;
             if (do_write) {
-                // every thread recomputes the contributor range (cheap) and sums in CTA order
-                const int64_t first = strip * a.ksteps, last = first + a.ksteps - 1;
-                c_lo = (first * P) / a.total;
-                while (c_lo > 0 && (c_lo * a.total) / P > first) --c_lo;
-                while (((c_lo + 1) * a.total) / P <= first) ++c_lo;
-                c_hi = (last * P) / a.total;
-                while (c_hi > 0 && (c_hi * a.total) / P > last) --c_hi;
-                while (((c_hi + 1) * a.total) / P <= last) ++c_hi;
 #pragma unroll
                 for (int t = 0; t < kTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-                for (int64_t cc = c_lo; cc <= c_hi; ++cc) {
-                    const float4* theirs = a.partials + (((cc + strip) * kWarps + warp) * kTiles) * 32 + lane;
+                for (int64_t j = 0; j < a.splits; ++j) {
+                    const float4* theirs = a.partials + (((strip + j * a.strips) * kWarps + warp) * kTiles) * 32 + lane;
 #pragma unroll
                     for (int t = 0; t < kTiles; ++t) {
                         const float4 v = __ldcg(theirs + t * 32);
@@ -301,23 +353,23 @@ __global__ void __launch_bounds__(kThreads, 3) wqbmm_decode_kernel(const DecodeA
                     }
                 }
             }
-            __syncthreads();  // s_reduce is reused by the next strip of this CTA
+            __syncthreads();
             if (do_write && tid == 0) {
                 // every contributor's fragment has been consumed: retire the strip's tags, so that a replay of this very
                 // launch (same nonce, e.g. from a captured CUDA graph) starts from a clean slate
-                for (int64_t cc = c_lo; cc <= c_hi; ++cc)
-                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + cc + strip), "l"(0ull) : "memory");
+                for (int64_t j = 0; j < a.splits; ++j)
+                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + strip + j * a.strips), "l"(0ull) : "memory");
             }
         }
         if (do_write) {
             // D fragment: rows g, g+8; tile-local columns 2q, 2q+1 = lane groups 2q, 2q+1 of the loader
-            const int64_t colw = strip * kStripCols + warp * 128;
+            const int64_t colw = strip * kStripCols + warp * kWarpCols;
 #pragma unroll
             for (int t = 0; t < kTiles; ++t) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int row = g + (e >> 1) * 8;
-                    const int64_t col = colw + 16 * (2 * q + (e & 1)) + t;
+                    const int64_t col = colw + 8 * (2 * q + (e & 1)) + t;
                     if (row < a.m && col < a.n) {
                         float f = acc[t][e];
                         if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
@@ -363,11 +415,12 @@ constexpr int kMaxGrid = 148 * 4 * 2;  // workspace is sized for at most this ma
 
 }  // namespace
 
-// Upper bound used by phase 1, which runs without a device: tags + fragments for (max grid + strips) slots.
+// Upper bound used by phase 1, which runs without a device: one tag + one fp32 fragment set per CTA of the largest grid
+// that ever splits k (a grid with more strips than that runs one CTA per strip and needs no workspace).
 uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p)
 {
-    const int64_t strips = (p->n + kStripCols - 1) / kStripCols;
-    const uint64_t slots = (uint64_t)kMaxGrid + (uint64_t)strips;
+    (void)p;
+    const uint64_t slots = (uint64_t)kMaxGrid;
     const uint64_t tags = ((slots * 8 + 255) / 256) * 256;
     return tags + slots * kWarps * kTiles * 32 * sizeof(float4);
 }
@@ -376,12 +429,12 @@ bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p)
 {
     if (p->w_dtype != ACL_INT4 || p->trans_w != 0) return false;
     if (p->m < 1 || p->m > 16) return false;
-    if (p->k % 16 != 0 || p->n % 16 != 0 || p->w_ld % 16 != 0 || p->x_ld % 2 != 0) return false;
+    if (p->k % 16 != 0 || p->n % 8 != 0 || p->w_ld % 8 != 0 || p->x_ld % 8 != 0) return false;
     if (p->group_size != 0 && p->group_size % 16 != 0) return false;
     if (p->scale_sn != 0 && p->scale_sn != 1) return false;
     if (p->scale_sn == 1 && (p->scale_sg % 8 != 0)) return false;
     auto aligned = [](const void* q, uintptr_t a) { return (reinterpret_cast<uintptr_t>(q) % a) == 0; };
-    if (!aligned(p->w, 8) || !aligned(p->x, 4)) return false;
+    if (!aligned(p->w, 4) || !aligned(p->x, 16)) return false;
     if (p->scale_sn == 1 && (!aligned(p->scale, 16) || (p->offset && !aligned(p->offset, 16)))) return false;
     return true;
 }
@@ -406,29 +459,37 @@ int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     a.k = p->k;
     a.strips = (p->n + kStripCols - 1) / kStripCols;
     a.ksteps = p->k / 16;
-    a.total = a.strips * a.ksteps;
     a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
     const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
     const int variant = (bf16 ? 2 : 0) + (has_off ? 1 : 0);
-    int grid = 0;
+    int resident = 0;
     switch (variant) {
-        case 0: grid = decode_grid<false, false>(0); break;
-        case 1: grid = decode_grid<false, true>(1); break;
-        case 2: grid = decode_grid<true, false>(2); break;
-        default: grid = decode_grid<true, true>(3); break;
+        case 0: resident = decode_grid<false, false>(0); break;
+        case 1: resident = decode_grid<false, true>(1); break;
+        case 2: resident = decode_grid<true, false>(2); break;
+        default: resident = decode_grid<true, true>(3); break;
     }
-    if (grid > kMaxGrid) grid = kMaxGrid;
-    if ((int64_t)grid > a.total) grid = (int)a.total;
-    if (const char* e = getenv("OPSNN_WQ_DECODE_GRID")) {
+    // host tile selection: as many equal k ranges per strip as keep every CTA resident at once
+    int64_t splits = resident / a.strips;
+    if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
         int v = atoi(e);
-        if (v > 0 && v <= kMaxGrid && v <= a.total) grid = v;
+        if (v > 0) splits = v;
     }
-    const uint64_t slots = (uint64_t)kMaxGrid + (uint64_t)a.strips;
-    const uint64_t tag_bytes = ((slots * 8 + 255) / 256) * 256;
-    if (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+    if (splits > a.ksteps) splits = a.ksteps;
+    if (splits * a.strips > kMaxGrid) splits = kMaxGrid / a.strips;
+    if (splits < 1) splits = 1;
+    a.splits = splits;
+    const int64_t grid64 = a.strips * splits;
+    if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+    const int grid = (int)grid64;
+    const uint64_t tag_bytes = (((uint64_t)kMaxGrid * 8 + 255) / 256) * 256;
+    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
     a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
     a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
     a.nonce = next_nonce();
+    a.c_mask = 0x000F000Fu;
+    a.c_magic = bf16 ? Num<true>::kMagic : Num<false>::kMagic;
+    a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
     switch (variant) {
         case 0: wqbmm_decode_kernel<false, false><<<grid, kThreads, 0, stream>>>(a); break;
         case 1: wqbmm_decode_kernel<false, true><<<grid, kThreads, 0, stream>>>(a); break;

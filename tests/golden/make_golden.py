@@ -171,7 +171,7 @@ def gen_qmm(G):
     rng = np.random.default_rng(22)
     qmm_case(G, "bb_fp8_fp16_transA", 22, q_fp8(rng, (283, 300), E5M2), q_fp8(rng, (283, 261), E4M3),
              f32(rng, (3, 3), .5, 2), f32(rng, (3, 3), .5, 2), None, True, False, (128 << 32) | (128 << 16) | 128, "float16",
-             "B-B with x1 stored (k,m); the API call passes groupSize with M and N fields 0 and infers them", api_group=128)
+             "B-B with x1 stored (k,m): scales are stored (k/128, m/128)")
     # fp8 double scale / per-tensor
     rng = np.random.default_rng(23)
     qmm_case(G, "tt_fp8_doublescale_fp16", 23, q_fp8(rng, (48, 96), E4M3), q_fp8(rng, (96, 80), E4M3), f32(rng, (1,), .5, 2),
@@ -187,14 +187,15 @@ def gen_qmm(G):
              "bfloat16", "mx fp8, x2 stored (k,n)")
     rng = np.random.default_rng(26)
     qmm_case(G, "mxfp8_transB_oddgroups", 26, q_fp8(rng, (70, 160), E4M3), q_fp8(rng, (90, 160), E5M2), e8m0(rng, (70, 3, 2)),
-             e8m0(rng, (90, 3, 2)), None, False, True, 0, "float16", "k=160: 5 groups, the 6th scale is padding")
+             e8m0(rng, (90, 3, 2)), None, False, True, (1 << 32) | (1 << 16) | 32, "float16",
+             "k=160: 5 groups, the 6th scale is padding (groupSize must be explicit: 160 is not divisible by 6)")
     rng = np.random.default_rng(27)
     qmm_case(G, "mxfp4_transB_fp32", 27, q_fp4(rng, (197, 960)), q_fp4(rng, (154, 960)), e8m0(rng, (197, 15, 2)),
              e8m0(rng, (154, 15, 2)), None, False, True, (1 << 32) | (1 << 16) | 32, "float32",
              "qbmm_MXFP4_case0001 (n scaled down): k=960 = 30 groups")
     rng = np.random.default_rng(28)
     qmm_case(G, "mxfp4_bf16", 28, q_fp4(rng, (33, 128)), q_fp4(rng, (128, 72)), e8m0(rng, (33, 2, 2)), e8m0(rng, (2, 72, 2)),
-             None, False, False, 0, "bfloat16", "mx fp4 with x2 stored (k,n)")
+             None, False, False, 0, "bfloat16", "mx fp4 with x2 stored (k,n); groupSize 0 is inferred as [1,1,32]")
     rng = np.random.default_rng(29)
     qmm_case(G, "mxfp8_batched_bias", 29, q_fp8(rng, (3, 40, 128), E4M3), q_fp8(rng, (3, 128, 56), E4M3),
              e8m0(rng, (3, 40, 2, 2)), e8m0(rng, (3, 2, 56, 2)), rng.uniform(-1, 1, (56,)).astype(np.float32), False, False,

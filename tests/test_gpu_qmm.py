@@ -14,8 +14,6 @@ EXACT = {n for n in golden_names("qmm_") if "_int8_" in n}
 def _ref32(a, meta):
     u64 = meta["dtypes"].get("x2_scale") == "uint64"
     g = meta["group_size"]
-    if g == 128:
-        g = (128 << 32) | (128 << 16) | 128
     out = "int32" if meta["out_dtype"] == "int32" else "float32"
     return qbmm_oracle.quant_matmul_v5(a["x1"], a["x2"], a.get("x1_scale"), a["x2_scale"], a.get("bias"), meta["transpose_x1"],
                                        meta["transpose_x2"], g, out, x2_scale_is_u64=u64)

@@ -31,10 +31,7 @@ def test_qmm_oracle_matches_reference_golden(name):
 
 
 def _full_group(meta, a):
-    g = meta["group_size"]
-    if g == 128:  # fixture whose API call leaves the M/N fields for inference
-        return (128 << 32) | (128 << 16) | 128
-    return g
+    return meta["group_size"]
 
 
 @pytest.mark.parametrize("name", golden_names("wq_"))
