@@ -67,6 +67,8 @@ def lib():
         getattr(L, name).restype = c_int32
         getattr(L, name + "GetWorkspaceSize").restype = c_int32
     L.opsnn_launch_count.restype = c_uint64
+    L.opsnn_qmm_umma_status.restype = ctypes.c_uint32
+    L.opsnn_qmm_umma_status.argtypes = [c_int32]
     L.opsnn_last_kernel_name.restype = c_char_p
     _lib = L
     return L

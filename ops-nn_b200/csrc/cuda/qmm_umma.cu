@@ -1,7 +1,534 @@
-// placeholder replaced below
+// Full-quant matmul on the 5th-generation tensor cores: TMA -> 128B-swizzled shared memory -> tcgen05.mma -> TMEM ->
+// fused dequantisation epilogue. Hand-written for sm_100a; no CUTLASS.
+//
+// Replaces the reference's arch35 kernels for the V3-routed modes of aclnnQuantMatmulV5:
+//   int8 per-tensor/-channel(/-token)   quant_batch_matmul_v3/op_kernel/arch35/qbmm_mix_online_dynamic.h:56-147, 646-736
+//   fp8 per-block (G-B / B-B)           matmul/common/cmct/kernel/kernel_qbmm_pertile.h:171-443,
+//                                        block/block_mmad_pertile.h:262-447, epilogue/block_epilogue_pertile.h:501-883
+// and their host tiling (op_host/op_tiling/arch35/adaptive_sliding_window_tiling.cpp:151-327, 563-781): what is left of it
+// is the choice of the N tile and the persistent tile order below.
+//
+// CTA = one 128 x BN output tile at a time, persistent over tiles (tile index = blockIdx.x + i * gridDim.x; consecutive
+// CTAs take consecutive M blocks of the same N block, so a wave shares one weight panel through L2).
+//   warp EW     : TMA producer. One stage = 128 k-bytes of A (16 KB) and of B (BN x 128 B), 128-byte swizzle.
+//   warp EW + 1 : MMA issuer (one elected lane): 4 x tcgen05.mma (K = 32 bytes each) per stage into a TMEM accumulator,
+//                 tcgen05.commit releases the stage back to the producer and hands finished accumulators to the epilogue.
+//   warps 0..EW-1 : epilogue. Warp w reads TMEM lanes 32*(w%4).. (its output rows) with tcgen05.ld.
+// Modes:
+//   DEQ       the accumulator (int32 for kind::i8, fp32 for kind::f8f6f4) covers the whole k range; two TMEM buffers let
+//             the epilogue of tile i overlap the MMAs of tile i+1. Epilogue = common.cuh::deq_epilogue (exact rounding order).
+//   PERBLOCK  every 128-k stage is its own accumulation group: the MMA warp alternates between two TMEM buffers and the
+//             epilogue warps (8 of them for BN = 256, each thread owning one row x 128 columns) promote each partial with
+//             acc += part * (s1[m, kb] * s2[kb, n/128]) in registers while the next group is being multiplied.
+// Operand majorness follows the storage: x1 (m,k) / x2 (n,k) are K-major; x1 (k,m) / x2 (k,n) are MN-major, which
+// tcgen05 reads directly for 8-bit types, so no operand is ever transposed in memory.
+// Every mbarrier wait is bounded; a wait that gives up raises a CTA-wide abort flag, records the failure in a device
+// status word (opsnn_qmm_umma_status) and the CTA tears down normally (TMEM freed).
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+
 namespace opsnn {
-bool qmm_umma_eligible(const OpsnnQmmParams*) { return false; }
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;  // bytes of k per stage
+constexpr int kATile = BM * BK;
+
+struct UmmaArgs {
+    int32_t mode, is_int;
+    int32_t a_mn_major, b_mn_major;
+    uint32_t idesc;
+    int64_t batch, m, n, k;
+    int32_t tiles_m, tiles_n, kblocks, stages;
+    int64_t num_tiles;
+    int32_t a_batched, b_batched;
+    int32_t out_dtype, bias_dtype, scale_b_dtype, deq_flags;
+    const void* scale_a;
+    const void* scale_b;
+    int64_t scale_a_len, scale_b_len, sa_bs, sb_bs;
+    int32_t group_m, trans_a, trans_b;
+    const void* bias;
+    int64_t bias_bs;
+    void* out;
+    int64_t out_ld, out_bs;
+};
+
+__device__ unsigned int g_umma_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first failed wait
+
+template <int BN>
+struct Smem {
+    static constexpr int kBTile = BN * BK;
+    static constexpr int kStage = kATile + kBTile;
+};
+
+__device__ __forceinline__ void report(volatile uint32_t* abort_flag, unsigned int code)
+{
+    *abort_flag = 1u;
+    atomicCAS(&g_umma_status, 0u, code);
+}
+
+// Converts 32 accumulator columns of one output row and stores them. `col` is the first column (global), valid = number
+// of columns inside n.
+__device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int64_t row, int64_t col, const float (&f)[32],
+                                            int valid)
+{
+    if (a.out_dtype == ACL_FLOAT) {
+        float* o = reinterpret_cast<float*>(out) + row * a.out_ld + col;
+        if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+        } else {
+            for (int i = 0; i < valid; ++i) o[i] = f[i];
+        }
+        return;
+    }
+    uint32_t pk[16];
+    if (a.out_dtype == ACL_BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            pk[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            pk[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    uint16_t* o = reinterpret_cast<uint16_t*>(out) + row * a.out_ld + col;
+    if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+    } else {
+        for (int i = 0; i < valid; ++i) o[i] = (uint16_t)((i & 1) ? (pk[i >> 1] >> 16) : (pk[i >> 1] & 0xFFFFu));
+    }
+}
+
+template <int BN, bool kPerBlock, ptx::MmaKind kKind>
+__global__ void __launch_bounds__((((kPerBlock && BN == 256) ? 8 : 4) + 2) * 32, 1)
+qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
+{
+    constexpr int EW = (kPerBlock && BN == 256) ? 8 : 4;  // epilogue warps
+    constexpr int kCols = (kPerBlock && BN == 256) ? 128 : BN;  // accumulator columns one epilogue thread handles
+    constexpr int kStage = Smem<BN>::kStage;
+    constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)a.stages * kStage);
+    uint64_t* full = bars;                    // [stages]
+    uint64_t* empty = bars + a.stages;        // [stages]
+    uint64_t* tfull = bars + 2 * a.stages;    // [2]
+    uint64_t* tempty = tfull + 2;             // [2]
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile uint32_t* abort_flag = tmem_ptr + 1;
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&tfull[b], 1);
+            ptx::mbar_init(&tempty[b], EW * 32);
+        }
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == EW + 1) ptx::tmem_alloc(tmem_ptr, kTmemCols);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    const int64_t tiles_per_batch = (int64_t)a.tiles_m * a.tiles_n;
+
+    if (warp == EW) {
+        // ======================= TMA producer =======================
+        if (lane == 0) {
+            ptx::tma_prefetch_desc(&map_a);
+            ptx::tma_prefetch_desc(&map_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
+                const int64_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+                const int32_t m0 = (int32_t)(r % a.tiles_m) * BM, n0 = (int32_t)(r / a.tiles_m) * BN;
+                const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
+                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
+                    const uint32_t s = it % a.stages, par = (it / a.stages) & 1;
+                    if (!ptx::mbar_wait(&empty[s], par ^ 1, abort_flag)) {
+                        report(abort_flag, (1u << 8) | 1u);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + (size_t)s * kStage;
+                    uint8_t* sb = sa + kATile;
+                    ptx::mbar_expect_tx(&full[s], (uint32_t)kStage);
+                    if (a.a_mn_major) ptx::tma_load_3d(sa, &map_a, &full[s], m0, kb * BK, ba);
+                    else ptx::tma_load_3d(sa, &map_a, &full[s], kb * BK, m0, ba);
+                    if (a.b_mn_major) {
+#pragma unroll
+                        for (int c = 0; c < (BN + 127) / 128; ++c)
+                            ptx::tma_load_3d(sb + c * (128 * BK), &map_b, &full[s], n0 + c * 128, kb * BK, bb);
+                    } else {
+                        ptx::tma_load_3d(sb, &map_b, &full[s], kb * BK, n0, bb);
+                    }
+                }
+            }
+        }
+    } else if (warp == EW + 1) {
+        // ======================= MMA issuer =======================
+        if (lane == 0) {
+            uint32_t it = 0, grp = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
+                    const bool group_start = kPerBlock || kb == 0;
+                    const bool group_end = kPerBlock || kb == a.kblocks - 1;
+                    const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
+                    if (group_start && !ptx::mbar_wait(&tempty[buf], gpar ^ 1, abort_flag)) {
+                        report(abort_flag, (2u << 8) | 1u);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t s = it % a.stages, par = (it / a.stages) & 1;
+                    if (!ptx::mbar_wait(&full[s], par, abort_flag)) {
+                        report(abort_flag, (2u << 8) | 2u);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(smem + (size_t)s * kStage), sb = sa + kATile;
+                    const uint32_t d = tmem_base + buf * BN;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // K-major: 32 bytes further along the swizzled row; MN-major: 32 k-rows (4 KB) further
+                        const uint64_t da = a.a_mn_major ? ptx::make_smem_desc(sa + k * 4096, 128 * BK, 1024, 2)
+                                                         : ptx::make_smem_desc(sa + k * 32, 0, 1024, 2);
+                        const uint64_t db = a.b_mn_major ? ptx::make_smem_desc(sb + k * 4096, 128 * BK, 1024, 2)
+                                                         : ptx::make_smem_desc(sb + k * 32, 0, 1024, 2);
+                        ptx::umma<kKind>(d, da, db, a.idesc, (group_start && k == 0) ? 0u : 1u);
+                    }
+                    ptx::umma_commit(&empty[s]);
+                    if (group_end) {
+                        ptx::umma_commit(&tfull[buf]);
+                        ++grp;
+                    }
+                }
+            }
+        }
+    } else {
+        // ======================= epilogue warps =======================
+        const int quad = warp & 3, half = warp >> 2;
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        uint32_t grp = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
+            const int64_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int64_t m0 = (r % a.tiles_m) * BM, n0 = (r / a.tiles_m) * BN;
+            const int64_t row = m0 + quad * 32 + lane;
+            const bool row_ok = row < a.m;
+            const int out_bytes = (a.out_dtype == ACL_FLOAT || a.out_dtype == ACL_INT32) ? 4 : 2;
+            uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + b * a.out_bs * out_bytes;
+            const int64_t colbase = n0 + half * kCols;
+            if (!kPerBlock) {
+                const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
+                if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) {
+                    report(abort_flag, (3u << 8) | 1u);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint8_t* bias = reinterpret_cast<const uint8_t*>(a.bias);
+                if (bias != nullptr) bias += b * a.bias_bs * ((a.bias_dtype == ACL_FLOAT || a.bias_dtype == ACL_INT32) ? 4 : 2);
+                const bool has_sa = a.scale_a != nullptr;
+                const float sav = (has_sa && row_ok) ? reinterpret_cast<const float*>(a.scale_a)[a.scale_a_len == 1 ? 0 : row] : 1.f;
+                const bool has_fbias = bias != nullptr && a.bias_dtype != ACL_INT32;
+#pragma unroll 1
+                for (int c = 0; c < kCols; c += 32) {
+                    uint32_t v[32];
+                    ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + half * kCols + c, v);
+                    ptx::tmem_ld_wait();
+                    const int64_t col = colbase + c;
+                    const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
+                    if (row_ok && valid > 0) {
+                        if (a.out_dtype == ACL_INT32) {
+                            int32_t* o = reinterpret_cast<int32_t*>(out) + row * a.out_ld + col;
+                            for (int i = 0; i < valid; ++i) {
+                                int32_t x = (int32_t)v[i];
+                                if (a.bias_dtype == ACL_INT32) x += reinterpret_cast<const int32_t*>(bias)[col + i];
+                                o[i] = x;
+                            }
+                        } else {
+                            float f[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const int64_t cc = (i < valid) ? col + i : col;  // clamp: never read past n
+                                float x;
+                                if (a.is_int) {
+                                    int32_t iv = (int32_t)v[i];
+                                    if (a.bias_dtype == ACL_INT32) iv += __ldg(reinterpret_cast<const int32_t*>(bias) + cc);
+                                    x = (float)iv;
+                                } else {
+                                    x = __uint_as_float(v[i]);
+                                }
+                                const float sb = load_deq_scale(a.scale_b, a.scale_b_len == 1 ? 0 : cc, a.scale_b_dtype);
+                                const float fb = has_fbias ? load_as_float(bias, cc, a.bias_dtype) : 0.f;
+                                f[i] = deq_epilogue(x, sb, sav, has_sa, fb, has_fbias, a.deq_flags);
+                            }
+                            store_row32(a, out, row, col, f, valid);
+                        }
+                    }
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&tempty[buf]);
+                ++grp;
+            } else {
+                float acc[kCols];
+#pragma unroll
+                for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
+                const float* s1 = reinterpret_cast<const float*>(a.scale_a) + b * a.sa_bs;
+                const float* s2 = reinterpret_cast<const float*>(a.scale_b) + b * a.sb_bs;
+                const int64_t mg = (row_ok ? row : 0) / a.group_m;
+                const int64_t n_mg = (a.m + a.group_m - 1) / a.group_m, n_ng = (a.n + 127) / 128;
+                const int64_t ng = min(colbase / 128, n_ng - 1);
+                for (int kb = 0; kb < a.kblocks; ++kb, ++grp) {
+                    const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
+                    // scale of this (row, k-block, n-block): x1Scale is (m/gm, kblocks) or, transposed, (kblocks, m/gm);
+                    // x2Scale is (kblocks, n/128) or, transposed, (n/128, kblocks)
+                    const float sv1 = a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
+                    const float sv2 = a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
+                    const float sc = __fmul_rn(sv1, sv2);
+                    if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) {
+                        report(abort_flag, (3u << 8) | 2u);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < kCols; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + half * kCols + c, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc, acc[c + i]);
+                    }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(&tempty[buf]);
+                }
+                if (ok && row_ok) {
+#pragma unroll
+                    for (int c = 0; c < kCols; c += 32) {
+                        const int64_t col = colbase + c;
+                        const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
+                        if (valid > 0) {
+                            float f[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) f[i] = acc[c + i];
+                            store_row32(a, out, row, col, f, valid);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: everyone meets here, also after an aborted wait; then the allocating warp frees TMEM ----
+    if (*abort_flag != 0u) __nanosleep(200000);  // lets bulk copies that are still in flight land before the CTA leaves
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == EW + 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+// =================================================== host side ===================================================
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode()
+{
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// 3-D byte tensor (inner bytes, rows, batch) with a (128, box_rows, 1) box and 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t row_pitch,
+              uint64_t batch_pitch, uint32_t box_rows)
+{
+    EncodeFn enc = get_encode();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[3] = {inner, rows, batch};
+    cuuint64_t strides[2] = {row_pitch, batch_pitch ? batch_pitch : row_pitch * rows};
+    if (strides[1] % 16 != 0) strides[1] = ((strides[1] + 15) / 16) * 16;  // only reached when batch == 1
+    cuuint32_t box[3] = {128, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_sms = 0;
+int sm_count()
+{
+    if (g_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sms <= 0) g_sms = 148;
+    }
+    return g_sms;
+}
+
+bool is_fp8(int dt) { return dt == ACL_FLOAT8_E4M3FN || dt == ACL_FLOAT8_E5M2; }
+
+// Host tile selection: the widest N tile that still yields about one tile per SM; MN-major B needs whole 128-column boxes.
+int pick_bn(const OpsnnQmmParams* p)
+{
+    if (const char* e = getenv("OPSNN_QMM_BN")) {
+        int v = atoi(e);
+        if (v == 32 || v == 64 || v == 128 || v == 256) return v;
+    }
+    const int64_t tiles_m = (p->m + BM - 1) / BM;
+    const int sms = 148;
+    const int lo = (p->mode == OPSNN_QMM_PERBLOCK || !p->trans_b) ? 128 : 32;
+    for (int bn = 256; bn > lo; bn /= 2) {
+        if (bn / 2 >= p->n) continue;  // half the width still covers n
+        const int64_t tiles = p->batch * tiles_m * ((p->n + bn - 1) / bn);
+        if (tiles >= sms) return bn;
+    }
+    return lo;
+}
+
+template <int BN, bool PB, ptx::MmaKind KIND>
+int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
+{
+    constexpr int EW = (PB && BN == 256) ? 8 : 4;
+    constexpr int kStage = Smem<BN>::kStage;
+    int stages = (227 * 1024 - 2048) / kStage;
+    if (stages > 8) stages = 8;
+    if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * kStage + 1024 + 256;
+    static bool configured = false;
+    auto kern = qmm_umma_kernel<BN, PB, KIND>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return (int32_t)cudaGetLastError();
+        configured = true;
+    }
+    int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
+    kern<<<(unsigned)grid, (EW + 2) * 32, smem, stream>>>(ma, mb, a);
+    note_launch(PB ? "qmm_umma_perblock" : "qmm_umma_deq");
+    return (int32_t)cudaGetLastError();
+}
+
+template <bool PB, ptx::MmaKind KIND>
+int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
+{
+    switch (bn) {
+        case 256: return launch_one<256, PB, KIND>(ma, mb, a, stream);
+        case 128: return launch_one<128, PB, KIND>(ma, mb, a, stream);
+        case 64: if (!PB) return launch_one<64, false, KIND>(ma, mb, a, stream); break;
+        case 32: if (!PB) return launch_one<32, false, KIND>(ma, mb, a, stream); break;
+        default: break;
+    }
+    return (int32_t)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool qmm_umma_eligible(const OpsnnQmmParams* p)
+{
+    if (getenv("OPSNN_QMM_NO_UMMA")) return false;
+    const bool i8 = p->a_dtype == ACL_INT8 && p->b_dtype == ACL_INT8;
+    const bool f8 = is_fp8(p->a_dtype) && is_fp8(p->b_dtype);
+    if (p->mode == OPSNN_QMM_DEQ) {
+        if (!i8 && !f8) return false;
+    } else if (p->mode == OPSNN_QMM_PERBLOCK) {
+        if (!f8 || p->group_k != 128 || p->group_n != 128 || (p->group_m != 1 && p->group_m != 128)) return false;
+        if (p->bias != nullptr) return false;
+    } else {
+        return false;
+    }
+    if (p->out_dtype != ACL_BF16 && p->out_dtype != ACL_FLOAT16 && p->out_dtype != ACL_FLOAT &&
+        !(p->out_dtype == ACL_INT32 && i8 && p->mode == OPSNN_QMM_DEQ))
+        return false;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (p->a != nullptr && (!al16(p->a) || !al16(p->b))) return false;
+    if (p->a_ld % 16 != 0 || p->b_ld % 16 != 0 || p->a_bs % 16 != 0 || p->b_bs % 16 != 0) return false;
+    if (p->m < 1 || p->n < 1 || p->k < 1 || p->batch < 1 || p->batch > 0x7FFFFFFF) return false;
+    if (p->m > 0x7FFFFF00 || p->n > 0x7FFFFF00 || p->k > 0x7FFFFF00) return false;
+    return true;
+}
+
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams*) { return 0; }
-int32_t qmm_umma_launch(const OpsnnQmmParams*, cudaStream_t) { return (int32_t)cudaErrorNotSupported; }
+
+int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
+{
+    const int bn = pick_bn(p);
+    UmmaArgs a{};
+    a.mode = p->mode;
+    a.is_int = p->a_dtype == ACL_INT8;
+    a.a_mn_major = p->trans_a ? 1 : 0;   // stored (k,m): m contiguous
+    a.b_mn_major = p->trans_b ? 0 : 1;   // stored (k,n): n contiguous
+    a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
+    a.tiles_m = (int32_t)((p->m + BM - 1) / BM);
+    a.tiles_n = (int32_t)((p->n + bn - 1) / bn);
+    a.kblocks = (int32_t)((p->k + BK - 1) / BK);
+    a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
+    a.a_batched = p->a_bs != 0;
+    a.b_batched = p->b_bs != 0;
+    a.out_dtype = p->out_dtype; a.bias_dtype = p->bias_dtype; a.scale_b_dtype = p->scale_b_dtype; a.deq_flags = p->deq_flags;
+    a.scale_a = p->scale_a; a.scale_b = p->scale_b; a.scale_a_len = p->scale_a_len; a.scale_b_len = p->scale_b_len;
+    a.sa_bs = p->sa_bs; a.sb_bs = p->sb_bs; a.group_m = p->group_m > 0 ? p->group_m : 1;
+    a.trans_a = p->trans_a; a.trans_b = p->trans_b;
+    a.bias = p->bias; a.bias_bs = p->bias_bs; a.out = p->out; a.out_ld = p->out_ld; a.out_bs = p->out_bs;
+    const uint32_t fa = a.is_int ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
+    const uint32_t fb = a.is_int ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
+    a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)bn);
+
+    CUtensorMap ma, mb;
+    const uint64_t nb_a = a.a_batched ? (uint64_t)p->batch : 1, nb_b = a.b_batched ? (uint64_t)p->batch : 1;
+    bool ok;
+    if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
+    else ok = make_map(&ma, p->a, (uint64_t)p->k, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
+    if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, (uint32_t)bn);
+    if (!ok) return (int32_t)cudaErrorInvalidValue;
+
+    if (p->mode == OPSNN_QMM_PERBLOCK) return launch_bn<true, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
+    if (a.is_int) return launch_bn<false, ptx::MmaKind::kI8>(bn, ma, mb, a, stream);
+    return launch_bn<false, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
+}
+
+}  // namespace opsnn
+
+extern "C" __attribute__((visibility("default"))) uint32_t opsnn_qmm_umma_status(int32_t reset)
+{
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, opsnn::g_umma_status, sizeof(v));
+    if (reset) {
+        unsigned int z = 0;
+        cudaMemcpyToSymbol(opsnn::g_umma_status, &z, sizeof(z));
+    }
+    return v;
 }

@@ -69,6 +69,8 @@ def run_qmm_fixture(aclnn, a, meta, kernel=None):
     finally:
         os.environ.pop("OPSNN_QMM_KERNEL", None)
     torch.cuda.synchronize()
+    status = aclnn.lib().opsnn_qmm_umma_status(1)
+    assert status == 0, "tensor-core kernel reported a timed-out wait: 0x%x" % status
     return out_to_np(out)
 
 

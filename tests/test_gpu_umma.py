@@ -1,0 +1,125 @@
+"""GPU parity of the tcgen05 (TMA + tensor-memory) kernels against the oracle, on seeded inputs whose row pitches satisfy
+the 16-byte rule of TMA, over every operand majorness, tile width, tail and batch form the kernel claims."""
+import ml_dtypes
+import numpy as np
+import pytest
+
+from oracle import qbmm_oracle
+
+pytestmark = pytest.mark.gpu
+
+E4M3, E5M2 = ml_dtypes.float8_e4m3fn, ml_dtypes.float8_e5m2
+
+
+def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, group, out_name, expect_kernel, bn=None):
+    import os
+
+    from gpu_util import desc, out_tensor, out_to_np
+    import torch
+
+    m = x1.shape[-1] if t1 else x1.shape[-2]
+    n = x2.shape[-2] if t2 else x2.shape[-1]
+    batch = tuple(x1.shape[:-2]) if x1.ndim > 2 else (tuple(x2.shape[:-2]) if x2.ndim > 2 else ())
+    out = out_tensor(batch + (m, n), out_name)
+    if bn:
+        os.environ["OPSNN_QMM_BN"] = str(bn)
+    try:
+        aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
+                              aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), t1, t2, group)
+    finally:
+        os.environ.pop("OPSNN_QMM_BN", None)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == expect_kernel, aclnn.last_kernel_name()
+    assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
+    return out_to_np(out)
+
+
+INT8_CASES = [
+    # m, k, n, t1, t2, bn, per-token, bias kind, out
+    (128, 256, 512, False, False, None, True, "i32", "bfloat16"),
+    (300, 400, 384, False, False, 128, True, None, "bfloat16"),      # tails in m and k, mn-major B
+    (300, 400, 384, False, False, 256, True, "f32", "float16"),
+    (130, 1040, 208, False, True, 32, True, "i32", "bfloat16"),      # k-major B, narrow tiles
+    (130, 1040, 208, False, True, 64, False, None, "bfloat16"),
+    (130, 1040, 208, False, True, 256, True, "bf16", "bfloat16"),
+    (272, 528, 400, True, False, 128, True, None, "float16"),        # mn-major A (x1 stored (k,m)), mn-major B
+    (272, 528, 400, True, True, 64, True, "i32", "bfloat16"),        # mn-major A, k-major B
+    (64, 4096, 1024, False, False, None, False, "i32", "int32"),     # int32 accumulator out
+    (1, 128, 16, False, True, None, True, None, "bfloat16"),
+]
+
+
+@pytest.mark.parametrize("case", INT8_CASES, ids=[str(c) for c in INT8_CASES])
+def test_int8_dequant_bit_exact(aclnn, case):
+    m, k, n, t1, t2, bn, pertoken, bias_kind, out_name = case
+    rng = np.random.default_rng(hash(case) % (2 ** 31))
+    x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32) if (pertoken and out_name != "int32") else None
+    bias = {None: None, "i32": rng.integers(-1000, 1001, n).astype(np.int32), "f32": rng.uniform(-1, 1, n).astype(np.float32),
+            "bf16": rng.uniform(-1, 1, n).astype(np.float32).astype(ml_dtypes.bfloat16)}[bias_kind]
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, 0, out_name)
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, 0, out_name, "qmm_umma_deq", bn)
+    assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(want).view(np.uint8)), \
+        "%d of %d elements differ" % ((np.asarray(got).astype(np.float64) != np.asarray(want).astype(np.float64)).sum(), got.size)
+
+
+def test_int8_batched_and_broadcast(aclnn):
+    rng = np.random.default_rng(77)
+    x1 = rng.integers(-127, 128, (3, 160, 256), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (256, 320), dtype=np.int8)  # broadcast over the batch
+    s2 = rng.uniform(1e-3, 1e-2, 320).astype(np.float32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, None, s2, None, False, False, 0, "bfloat16")
+    got = _run(aclnn, x1, x2, None, s2, None, False, False, 0, "bfloat16", "qmm_umma_deq")
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    x2b = rng.integers(-127, 128, (3, 320, 256), dtype=np.int8)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2b, None, s2, None, False, True, 0, "bfloat16")
+    got = _run(aclnn, x1, x2b, None, s2, None, False, True, 0, "bfloat16", "qmm_umma_deq")
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def _fp8(rng, shape, dt):
+    return rng.standard_normal(shape).astype(np.float32).astype(dt)
+
+
+PB_CASES = [
+    # m, k, n, t1, t2, group_m, bn, da, db, out
+    (256, 512, 512, False, False, 1, 256, E4M3, E4M3, "bfloat16"),
+    (200, 400, 304, False, False, 1, 128, E4M3, E4M3, "bfloat16"),    # tails everywhere (pitches still 16-byte multiples)
+    (200, 400, 304, False, True, 128, 256, E4M3, E5M2, "float16"),    # B-B, k-major B
+    (208, 400, 304, True, False, 128, 128, E5M2, E4M3, "float32"),    # x1 stored (k,m)
+    (208, 400, 304, True, True, 1, 256, E4M3, E4M3, "bfloat16"),
+]
+
+
+@pytest.mark.parametrize("case", PB_CASES, ids=[str(c[:7]) for c in PB_CASES])
+def test_fp8_perblock(aclnn, case):
+    from gpu_util import check_close
+
+    m, k, n, t1, t2, gm, bn, da, db, out_name = case
+    rng = np.random.default_rng(abs(hash(case[:7])) % (2 ** 31))
+    x1 = _fp8(rng, (k, m) if t1 else (m, k), da)
+    x2 = _fp8(rng, (n, k) if t2 else (k, n), db)
+    kb, mg, ng = -(-k // 128), -(-m // gm), -(-n // 128)
+    s1 = rng.uniform(0.5, 2, (kb, mg) if t1 else (mg, kb)).astype(np.float32)
+    s2 = rng.uniform(0.5, 2, (ng, kb) if t2 else (kb, ng)).astype(np.float32)
+    group = (gm << 32) | (128 << 16) | 128
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, t1, t2, group, out_name)
+    ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, t1, t2, group, "float32")
+    got = _run(aclnn, x1, x2, s1, s2, None, t1, t2, group, out_name, "qmm_umma_perblock", bn)
+    check_close(got, want, ref32, out_name)
+
+
+def test_fp8_dequant_doublescale(aclnn):
+    from gpu_util import check_close
+
+    rng = np.random.default_rng(5)
+    x1, x2 = _fp8(rng, (144, 256), E4M3), _fp8(rng, (256, 208), E4M3)
+    s1 = rng.uniform(0.5, 2, 1).astype(np.float32)
+    s2 = rng.uniform(0.5, 2, 208).astype(np.float32)
+    bias = rng.uniform(-1, 1, 208).astype(np.float32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, False, False, 0, "bfloat16")
+    ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, False, False, 0, "float32")
+    got = _run(aclnn, x1, x2, s1, s2, bias, False, False, 0, "bfloat16", "qmm_umma_deq")
+    check_close(got, want, ref32, "bfloat16")
