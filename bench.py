@@ -159,6 +159,75 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+QMM_WORKLOADS = {
+    # name: (batch, m, k, n, kind)
+    "c1": (1, 128, 4096, 4096, "int8_kc"),
+    "c3": (1, 4096, 7168, 18432, "fp8_perblock"),
+    "c3i8": (1, 4096, 7168, 18432, "int8_kc"),
+    "c1t": (1, 128, 4096, 4096, "int8_kc_t"),      # same with x2 stored (n,k) and transposeX2 = true
+    "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
+}
+
+
+def run_qmm_workload(args):
+    """Secondary workloads (`--workload c1|c3|c3i8`): aclnnQuantMatmulV5 timed on device, TFLOPS against the measured bf16
+    GEMM ceiling x2 (8-bit operands) and the datasheet dense peak. Same timing discipline as the headline workload."""
+    import torch
+
+    aclnn = load_package().aclnn
+    dev = torch.device("cuda", 0)
+    b, m, k, n, kind = QMM_WORKLOADS[args.workload]
+    gen = torch.Generator(device=dev).manual_seed(1001)
+    sets = max(2, min(8, int(300e6 // (k * n)) + 1))  # rotate weights so they do not sit in L2
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    if kind.startswith("int8_kc"):
+        tb = kind.endswith("_t")
+        x1 = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
+        x2s = [torch.randint(-127, 128, (n, k) if tb else (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
+        s1 = torch.rand((m,), generator=gen, device=dev) * 9e-3 + 1e-3
+        s2 = torch.rand((n,), generator=gen, device=dev) * 9e-3 + 1e-3
+        bias = torch.randint(-1000, 1001, (n,), generator=gen, device=dev, dtype=torch.int32)
+        d = [aclnn.from_torch(t) for t in (x1, s1, s2, bias)]
+        dx2 = [aclnn.from_torch(t) for t in x2s]
+        dout = aclnn.from_torch(out)
+        call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, d[3], False, tb)  # noqa: E731
+        nbytes = m * k + k * n + 4 * (m + 2 * n) + 2 * m * n
+    else:
+        x1 = torch.randn((m, k), generator=gen, device=dev).to(torch.float8_e4m3fn)
+        x2s = [torch.randn((k, n), generator=gen, device=dev).to(torch.float8_e4m3fn) for _ in range(sets)]
+        s1 = torch.rand((m, k // 128), generator=gen, device=dev) + 0.5
+        s2 = torch.rand((k // 128, n // 128), generator=gen, device=dev) + 0.5
+        d = [aclnn.from_torch(t) for t in (x1, s1, s2)]
+        dx2 = [aclnn.from_torch(t) for t in x2s]
+        dout = aclnn.from_torch(out)
+        group = (1 << 32) | (128 << 16) | 128
+        call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, None, False, False, group)  # noqa: E731
+        nbytes = m * k + k * n + 4 * (m * k // 128 + k * n // 16384) + 2 * m * n
+    for i in range(max(args.warmup, 3)):
+        call(i)
+    torch.cuda.synchronize()
+    steps = args.steps
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    sampler = ClockSampler(0)
+    sampler.start()
+    torch.cuda._sleep(60_000_000)
+    for i in range(steps):
+        evs[i][0].record()
+        call(i)
+        evs[i][1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ts = sorted(a.elapsed_time(b_) for a, b_ in evs)
+    ms = sum(ts) / len(ts)
+    flops = 2.0 * b * m * k * n
+    tf = flops / (ms * 1e-3) / 1e12
+    peak8 = 4500.0
+    print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
+                      "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
+                      "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_8bit_peak": tf / peak8,
+                      "hbm_gbs_on_algorithmic_bytes": nbytes / (ms * 1e-3) / 1e9, "clocks": clocks, "weight_sets": sets}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,6 +240,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload in QMM_WORKLOADS:
+        return run_qmm_workload(args)
     args.warmup = max(args.warmup, 3)
 
     import torch

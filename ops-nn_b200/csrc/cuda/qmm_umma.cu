@@ -55,6 +55,7 @@ struct UmmaArgs {
     int64_t bias_bs;
     void* out;
     int64_t out_ld, out_bs;
+    int32_t dbg;  // timing experiments only: 1 = no TMA traffic, 2 = no MMA
 };
 
 __device__ unsigned int g_umma_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first failed wait
@@ -72,7 +73,8 @@ __device__ __forceinline__ void report(volatile uint32_t* abort_flag, unsigned i
 }
 
 // Converts 32 accumulator columns of one output row and stores them. `col` is the first column (global), valid = number
-// of columns inside n.
+// of columns inside n. Register arrays are only ever indexed with compile-time constants (a run-time index would move
+// them to local memory).
 __device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int64_t row, int64_t col, const float (&f)[32],
                                             int valid)
 {
@@ -82,7 +84,9 @@ __device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int
 #pragma unroll
             for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
         } else {
-            for (int i = 0; i < valid; ++i) o[i] = f[i];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < valid) o[i] = f[i];
         }
         return;
     }
@@ -105,7 +109,11 @@ __device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int
 #pragma unroll
         for (int i = 0; i < 16; i += 4) *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
     } else {
-        for (int i = 0; i < valid; ++i) o[i] = (uint16_t)((i & 1) ? (pk[i >> 1] >> 16) : (pk[i >> 1] & 0xFFFFu));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (2 * i < valid) o[2 * i] = (uint16_t)(pk[i] & 0xFFFFu);
+            if (2 * i + 1 < valid) o[2 * i + 1] = (uint16_t)(pk[i] >> 16);
+        }
     }
 }
 
@@ -127,6 +135,8 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* tempty = tfull + 2;             // [2]
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile uint32_t* abort_flag = tmem_ptr + 1;
+    float* s_scale = reinterpret_cast<float*>(tmem_ptr + 4);  // [BN] x2Scale of the tile's columns, decoded to fp32
+    uint32_t* s_bias = reinterpret_cast<uint32_t*>(s_scale + BN);  // [BN] bias of the tile's columns: int32 bits or fp32 bits
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -171,6 +181,10 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     uint8_t* sa = smem + (size_t)s * kStage;
                     uint8_t* sb = sa + kATile;
+                    if (a.dbg & 1) {
+                        ptx::mbar_arrive(&full[s]);
+                        continue;
+                    }
                     ptx::mbar_expect_tx(&full[s], (uint32_t)kStage);
                     if (a.a_mn_major) ptx::tma_load_3d(sa, &map_a, &full[s], m0, kb * BK, ba);
                     else ptx::tma_load_3d(sa, &map_a, &full[s], kb * BK, m0, ba);
@@ -215,7 +229,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                                          : ptx::make_smem_desc(sa + k * 32, 0, 1024, 2);
                         const uint64_t db = a.b_mn_major ? ptx::make_smem_desc(sb + k * 4096, 128 * BK, 1024, 2)
                                                          : ptx::make_smem_desc(sb + k * 32, 0, 1024, 2);
-                        ptx::umma<kKind>(d, da, db, a.idesc, (group_start && k == 0) ? 0u : 1u);
+                        if (!(a.dbg & 2)) ptx::umma<kKind>(d, da, db, a.idesc, (group_start && k == 0) ? 0u : 1u);
                     }
                     ptx::umma_commit(&empty[s]);
                     if (group_end) {
@@ -241,8 +255,10 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int64_t colbase = n0 + half * kCols;
             if (!kPerBlock) {
                 const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
-                if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) {
-                    report(abort_flag, (3u << 8) | 1u);
+                if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) report(abort_flag, (3u << 8) | 1u);
+                // the four epilogue warps leave together: a named barrier is only safe if nobody has left the loop
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*abort_flag != 0u) {
                     ok = false;
                     break;
                 }
@@ -252,37 +268,42 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const bool has_sa = a.scale_a != nullptr;
                 const float sav = (has_sa && row_ok) ? reinterpret_cast<const float*>(a.scale_a)[a.scale_a_len == 1 ? 0 : row] : 1.f;
                 const bool has_fbias = bias != nullptr && a.bias_dtype != ACL_INT32;
+                const bool has_ibias = bias != nullptr && a.bias_dtype == ACL_INT32;
+                // stage the tile's column scales and bias once (128 epilogue threads, named barrier 1)
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers are done
+                for (int c = threadIdx.x; c < BN; c += 128) {
+                    const int64_t cc = min(n0 + c, a.n - 1);
+                    float sb = load_deq_scale(a.scale_b, a.scale_b_len == 1 ? 0 : cc, a.scale_b_dtype);
+                    if (a.deq_flags & OPSNN_DEQ_TRUNC_SCALE_B) sb = trunc19(sb);
+                    s_scale[c] = sb;
+                    uint32_t bv = 0u;
+                    if (has_ibias) bv = (uint32_t)__ldg(reinterpret_cast<const int32_t*>(bias) + cc);
+                    else if (has_fbias) bv = __float_as_uint(load_as_float(bias, cc, a.bias_dtype));
+                    s_bias[c] = bv;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int flags = a.deq_flags & ~OPSNN_DEQ_TRUNC_SCALE_B;  // already applied while staging
 #pragma unroll 1
                 for (int c = 0; c < kCols; c += 32) {
                     uint32_t v[32];
-                    ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + half * kCols + c, v);
+                    ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + c, v);
                     ptx::tmem_ld_wait();
                     const int64_t col = colbase + c;
                     const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
                     if (row_ok && valid > 0) {
                         if (a.out_dtype == ACL_INT32) {
                             int32_t* o = reinterpret_cast<int32_t*>(out) + row * a.out_ld + col;
-                            for (int i = 0; i < valid; ++i) {
-                                int32_t x = (int32_t)v[i];
-                                if (a.bias_dtype == ACL_INT32) x += reinterpret_cast<const int32_t*>(bias)[col + i];
-                                o[i] = x;
-                            }
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < valid) o[i] = (int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0);
                         } else {
                             float f[32];
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                const int64_t cc = (i < valid) ? col + i : col;  // clamp: never read past n
                                 float x;
-                                if (a.is_int) {
-                                    int32_t iv = (int32_t)v[i];
-                                    if (a.bias_dtype == ACL_INT32) iv += __ldg(reinterpret_cast<const int32_t*>(bias) + cc);
-                                    x = (float)iv;
-                                } else {
-                                    x = __uint_as_float(v[i]);
-                                }
-                                const float sb = load_deq_scale(a.scale_b, a.scale_b_len == 1 ? 0 : cc, a.scale_b_dtype);
-                                const float fb = has_fbias ? load_as_float(bias, cc, a.bias_dtype) : 0.f;
-                                f[i] = deq_epilogue(x, sb, sav, has_sa, fb, has_fbias, a.deq_flags);
+                                if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
+                                else x = __uint_as_float(v[i]);
+                                f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
                             }
                             store_row32(a, out, row, col, f, valid);
                         }
@@ -427,7 +448,7 @@ int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cu
     if (stages > 8) stages = 8;
     if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
     a.stages = stages;
-    const size_t smem = (size_t)stages * kStage + 1024 + 256;
+    const size_t smem = (size_t)stages * kStage + 1024 + 256 + 2 * BN * 4;
     static bool configured = false;
     auto kern = qmm_umma_kernel<BN, PB, KIND>;
     if (!configured) {
@@ -502,6 +523,7 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.sa_bs = p->sa_bs; a.sb_bs = p->sb_bs; a.group_m = p->group_m > 0 ? p->group_m : 1;
     a.trans_a = p->trans_a; a.trans_b = p->trans_b;
     a.bias = p->bias; a.bias_bs = p->bias_bs; a.out = p->out; a.out_ld = p->out_ld; a.out_bs = p->out_bs;
+    if (const char* e = getenv("OPSNN_QMM_DBG")) a.dbg = atoi(e);
     const uint32_t fa = a.is_int ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = a.is_int ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)bn);
