@@ -127,6 +127,10 @@ OPSNN_API int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* strea
 OPSNN_API uint64_t opsnn_launch_count(void);
 /* Name of the last kernel family launched on the calling thread (static string; "" if none). */
 OPSNN_API const char* opsnn_last_kernel_name(void);
+/* Error word of the tensor-core (tcgen05) quant matmul kernels on the current device: 0 when every bounded wait
+ * inside them completed; otherwise the code of the first wait that gave up (the kernel then returned early and its
+ * output is undefined). Synchronises the device. reset != 0 clears the word after reading it. */
+OPSNN_API uint32_t opsnn_qmm_umma_status(int32_t reset);
 
 #ifdef __cplusplus
 }

@@ -55,10 +55,11 @@ struct UmmaArgs {
     int64_t bias_bs;
     void* out;
     int64_t out_ld, out_bs;
-    int32_t dbg;  // timing experiments only: 1 = no TMA traffic, 2 = no MMA
+    int32_t dbg;  // timing experiments only: 1 = no TMA traffic, 2 = no MMA, 4 = plain arrive instead of commit
 };
 
-__device__ unsigned int g_umma_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first failed wait
+__device__ unsigned int g_umma_status = 0;
+  // 0 ok; otherwise (role << 8) | reason of the first failed wait
 
 template <int BN>
 struct Smem {
@@ -117,6 +118,29 @@ __device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int
     }
 }
 
+// 32 accumulator columns of one row -> dequantised values, for the common rounding order (no truncation flags):
+// f = float(acc + int_bias) * x2Scale [* x1Scale] [+ float_bias]. The flag combinations are template parameters so that
+// the per-element code is a handful of instructions; it runs on one warp per scheduler and is latency bound.
+template <bool kInt, bool kHasSa, bool kHasFb>
+__device__ __forceinline__ void deq_chunk(const uint32_t (&v)[32], const float* sc, const uint32_t* bi, float sav, float (&f)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 s4 = *reinterpret_cast<const float4*>(sc + i);
+        const uint4 b4 = *reinterpret_cast<const uint4*>(bi + i);
+        const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+        const uint32_t bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float x = kInt ? (float)((int32_t)v[i + j] + (kHasFb ? 0 : (int32_t)bb[j])) : __uint_as_float(v[i + j]);
+            x = __fmul_rn(x, ss[j]);
+            if (kHasSa) x = __fmul_rn(x, sav);
+            if (kHasFb) x = __fadd_rn(x, __uint_as_float(bb[j]));
+            f[i + j] = x;
+        }
+    }
+}
+
 template <int BN, bool kPerBlock, ptx::MmaKind kKind>
 __global__ void __launch_bounds__((((kPerBlock && BN == 256) ? 8 : 4) + 2) * 32, 1)
 qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
@@ -159,21 +183,27 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
 
-    const int64_t tiles_per_batch = (int64_t)a.tiles_m * a.tiles_n;
+    const uint32_t tiles_per_batch = (uint32_t)a.tiles_m * (uint32_t)a.tiles_n;
+    const uint32_t ntiles = (uint32_t)a.num_tiles;
 
     if (warp == EW) {
         // ======================= TMA producer =======================
         if (lane == 0) {
             ptx::tma_prefetch_desc(&map_a);
             ptx::tma_prefetch_desc(&map_b);
-            uint32_t it = 0;
+            // ring position kept as (stage, parity) counters: a division per k-block on a single thread costs more than the MMAs
+            uint32_t s = 0, par = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-                const int64_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-                const int32_t m0 = (int32_t)(r % a.tiles_m) * BM, n0 = (int32_t)(r / a.tiles_m) * BN;
+            // kernel parameters used per k-block are copied to registers: the "memory" clobbers of the barrier and copy
+            // instructions would otherwise make the compiler re-read them from parameter space every time
+            const uint32_t stages = (uint32_t)a.stages;
+            const int kblocks = a.kblocks;
+            const bool a_mn = a.a_mn_major != 0, b_mn = a.b_mn_major != 0, no_tma = (a.dbg & 1) != 0;
+            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+                const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN;
                 const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
-                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
-                    const uint32_t s = it % a.stages, par = (it / a.stages) & 1;
+                for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == stages) ? 0 : s + 1, par ^= (s == 0)) {
                     if (!ptx::mbar_wait(&empty[s], par ^ 1, abort_flag)) {
                         report(abort_flag, (1u << 8) | 1u);
                         ok = false;
@@ -181,14 +211,14 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     uint8_t* sa = smem + (size_t)s * kStage;
                     uint8_t* sb = sa + kATile;
-                    if (a.dbg & 1) {
+                    if (no_tma) {
                         ptx::mbar_arrive(&full[s]);
                         continue;
                     }
                     ptx::mbar_expect_tx(&full[s], (uint32_t)kStage);
-                    if (a.a_mn_major) ptx::tma_load_3d(sa, &map_a, &full[s], m0, kb * BK, ba);
+                    if (a_mn) ptx::tma_load_3d(sa, &map_a, &full[s], m0, kb * BK, ba);
                     else ptx::tma_load_3d(sa, &map_a, &full[s], kb * BK, m0, ba);
-                    if (a.b_mn_major) {
+                    if (b_mn) {
 #pragma unroll
                         for (int c = 0; c < (BN + 127) / 128; ++c)
                             ptx::tma_load_3d(sb + c * (128 * BK), &map_b, &full[s], n0 + c * 128, kb * BK, bb);
@@ -201,37 +231,44 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else if (warp == EW + 1) {
         // ======================= MMA issuer =======================
         if (lane == 0) {
-            uint32_t it = 0, grp = 0;
+            uint32_t s = 0, par = 0, grp = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < a.kblocks; ++kb, ++it) {
+            // K-major operand: a k step is 32 bytes along the swizzled row; MN-major: 32 k-rows = 4 KB (units of 16 bytes)
+            const uint32_t smem0 = ptx::smem_u32(smem);
+            const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
+            const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
+                                              : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+            const uint32_t a_kstep = a.a_mn_major ? 256u : 2u, b_kstep = a.b_mn_major ? 256u : 2u;
+            const uint32_t stages = (uint32_t)a.stages, idesc = a.idesc;
+            const int kblocks = a.kblocks;
+            const int dbg = a.dbg;
+            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == stages) ? 0 : s + 1, par ^= (s == 0)) {
                     const bool group_start = kPerBlock || kb == 0;
-                    const bool group_end = kPerBlock || kb == a.kblocks - 1;
+                    const bool group_end = kPerBlock || kb == kblocks - 1;
                     const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
                     if (group_start && !ptx::mbar_wait(&tempty[buf], gpar ^ 1, abort_flag)) {
                         report(abort_flag, (2u << 8) | 1u);
                         ok = false;
                         break;
                     }
-                    const uint32_t s = it % a.stages, par = (it / a.stages) & 1;
                     if (!ptx::mbar_wait(&full[s], par, abort_flag)) {
                         report(abort_flag, (2u << 8) | 2u);
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sa = ptx::smem_u32(smem + (size_t)s * kStage), sb = sa + kATile;
+                    // descriptors: only the 14-bit start-address field changes (stage base, then the k step inside the stage)
+                    const uint32_t stage_off = (s * (uint32_t)kStage) >> 4;
                     const uint32_t d = tmem_base + buf * BN;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        // K-major: 32 bytes further along the swizzled row; MN-major: 32 k-rows (4 KB) further
-                        const uint64_t da = a.a_mn_major ? ptx::make_smem_desc(sa + k * 4096, 128 * BK, 1024, 2)
-                                                         : ptx::make_smem_desc(sa + k * 32, 0, 1024, 2);
-                        const uint64_t db = a.b_mn_major ? ptx::make_smem_desc(sb + k * 4096, 128 * BK, 1024, 2)
-                                                         : ptx::make_smem_desc(sb + k * 32, 0, 1024, 2);
-                        if (!(a.dbg & 2)) ptx::umma<kKind>(d, da, db, a.idesc, (group_start && k == 0) ? 0u : 1u);
+                        const uint64_t da = da0 + (uint64_t)(stage_off + k * a_kstep);
+                        const uint64_t db = db0 + (uint64_t)(stage_off + k * b_kstep);
+                        if (!(dbg & 2)) ptx::umma<kKind>(d, da, db, idesc, (group_start && k == 0) ? 0u : 1u);
                     }
-                    ptx::umma_commit(&empty[s]);
+                    if (dbg & 4) ptx::mbar_arrive(&empty[s]);
+                    else ptx::umma_commit(&empty[s]);
                     if (group_end) {
                         ptx::umma_commit(&tfull[buf]);
                         ++grp;
@@ -245,9 +282,9 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         uint32_t grp = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < a.num_tiles && ok; tile += gridDim.x) {
-            const int64_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int64_t m0 = (r % a.tiles_m) * BM, n0 = (r / a.tiles_m) * BN;
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
             const int out_bytes = (a.out_dtype == ACL_FLOAT || a.out_dtype == ACL_INT32) ? 4 : 2;
@@ -255,21 +292,14 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int64_t colbase = n0 + half * kCols;
             if (!kPerBlock) {
                 const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
-                if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) report(abort_flag, (3u << 8) | 1u);
-                // the four epilogue warps leave together: a named barrier is only safe if nobody has left the loop
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*abort_flag != 0u) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
                 const uint8_t* bias = reinterpret_cast<const uint8_t*>(a.bias);
                 if (bias != nullptr) bias += b * a.bias_bs * ((a.bias_dtype == ACL_FLOAT || a.bias_dtype == ACL_INT32) ? 4 : 2);
                 const bool has_sa = a.scale_a != nullptr;
                 const float sav = (has_sa && row_ok) ? reinterpret_cast<const float*>(a.scale_a)[a.scale_a_len == 1 ? 0 : row] : 1.f;
                 const bool has_fbias = bias != nullptr && a.bias_dtype != ACL_INT32;
                 const bool has_ibias = bias != nullptr && a.bias_dtype == ACL_INT32;
-                // stage the tile's column scales and bias once (128 epilogue threads, named barrier 1)
+                // Stage the tile's column scales and bias (decoded to 32 bit) while the main loop is still running.
+                // 128 epilogue threads, named barrier 1; every epilogue warp executes every barrier of every tile.
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers are done
                 for (int c = threadIdx.x; c < BN; c += 128) {
                     const int64_t cc = min(n0 + c, a.n - 1);
@@ -281,8 +311,17 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     else if (has_fbias) bv = __float_as_uint(load_as_float(bias, cc, a.bias_dtype));
                     s_bias[c] = bv;
                 }
+                if (!ptx::mbar_wait_relaxed(&tfull[buf], gpar, abort_flag)) report(abort_flag, (3u << 8) | 1u);
+                // the four epilogue warps leave together: a named barrier is only safe if nobody has left the loop
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*abort_flag != 0u) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
                 const int flags = a.deq_flags & ~OPSNN_DEQ_TRUNC_SCALE_B;  // already applied while staging
+                const bool simple = flags == 0 && a.out_dtype != ACL_INT32;
+                const int variant = simple ? ((a.is_int ? 4 : 0) | (has_sa ? 2 : 0) | (has_fbias ? 1 : 0)) : -1;
 #pragma unroll 1
                 for (int c = 0; c < kCols; c += 32) {
                     uint32_t v[32];
@@ -298,12 +337,24 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 if (i < valid) o[i] = (int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0);
                         } else {
                             float f[32];
+                            switch (variant) {
+                                case 0: deq_chunk<false, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 1: deq_chunk<false, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 2: deq_chunk<false, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 3: deq_chunk<false, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 4: deq_chunk<true, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 5: deq_chunk<true, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 6: deq_chunk<true, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                case 7: deq_chunk<true, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                default:
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                float x;
-                                if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
-                                else x = __uint_as_float(v[i]);
-                                f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
+                                    for (int i = 0; i < 32; ++i) {
+                                        float x;
+                                        if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
+                                        else x = __uint_as_float(v[i]);
+                                        f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
+                                    }
+                                    break;
                             }
                             store_row32(a, out, row, col, f, valid);
                         }
@@ -497,6 +548,7 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
     if (p->a != nullptr && (!al16(p->a) || !al16(p->b))) return false;
     if (p->a_ld % 16 != 0 || p->b_ld % 16 != 0 || p->a_bs % 16 != 0 || p->b_bs % 16 != 0) return false;
     if (p->m < 1 || p->n < 1 || p->k < 1 || p->batch < 1 || p->batch > 0x7FFFFFFF) return false;
+    if (p->batch * ((p->m + 127) / 128) * ((p->n + 31) / 32) > 0x7FFFFFFF) return false;  // tile index is 32 bit
     if (p->m > 0x7FFFFF00 || p->n > 0x7FFFFF00 || p->k > 0x7FFFFF00) return false;
     return true;
 }

@@ -51,6 +51,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// Same, for waits that are expected to be long (an epilogue waiting for a whole main loop): sleeps between polls so
+// that the polling warps do not take issue slots from the single thread that feeds the tensor core.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    for (uint32_t i = 0; i < kSpinLimit / 16; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(200);
+        if ((i & 63u) == 63u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+
 // ---- TMA ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1,
                                             int32_t c2)
