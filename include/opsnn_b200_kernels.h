@@ -108,7 +108,26 @@ OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t
 OPSNN_API int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p);
 OPSNN_API int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream);
 
-/* ---- dynamic MX quant (aclnnDynamicMxQuant path) ---------------------------------------------------------- */
+/* The decode kernel again, for callers that cannot hand over workspace and must not cause a device allocation at the
+ * call: a hook running inside another runtime's memory-planned region, or a serving loop whose memory pool is frozen
+ * after warm-up, where a cudaMalloc would either fail the plan or synchronise the device. This entry point has no
+ * counterpart in the reference (there every operator gets its scratch through the two-phase workspace contract).
+ *
+ *   - The cross-CTA scratch is a 9,964,032-byte array inside the library's device image; p->workspace and
+ *     p->workspace_size are ignored. Neither this function nor anything it calls allocates host-visible device memory.
+ *   - Limits: the parameters must satisfy the decode kernel's range (opsnn_wqbmm_select_kernel(p) ==
+ *     OPSNN_WQ_KERNEL_DECODE) and n <= 155,648 columns (304 CTAs x 512). Anything else returns cudaErrorInvalidValue
+ *     and leaves the reason in aclGetRecentErrMsg().
+ *   - The first call on each device (with that device current) resolves the array's address; this may load the
+ *     library's device code. Make that first call during start-up, before any stream capture begins.
+ *   - The array is shared by every call on the device and keeps its last contents. Nothing in it has to start at
+ *     zero: each launch stamps its scratch with a fresh 64-bit nonce and clears its own stamps before it ends.
+ *   - Two calls that overlap in time on one device (two streams, two threads) race on the array and give wrong
+ *     results; order them on one stream or with events. The workspace entry point above has no such restriction.
+ */
+OPSNN_API int32_t opsnn_wqbmm_decode_static_launch(const OpsnnWqbmmParams* p, void* stream);
+
+/* ---- dynamic MX quant (aclnnDynamicMxQuant path)---------------------------------------------------------- */
 
 typedef struct OpsnnMxQuantParams {
     int32_t x_dtype;   /* ACL_BF16 | ACL_FLOAT16 */

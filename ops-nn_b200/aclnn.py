@@ -36,6 +36,18 @@ for _k, _v in list(DTYPE_BY_NAME.items()):
 DTYPE_BITS = {0: 32, 1: 16, 2: 8, 3: 32, 4: 8, 9: 64, 10: 64, 27: 16, 29: 4, 34: 8, 35: 8, 36: 8, 37: 8, 40: 4, 41: 4}
 ACL_FORMAT_ND, ACL_FORMAT_FRACTAL_NZ = 2, 29
 
+
+
+class WqbmmParams(ctypes.Structure):
+    """OpsnnWqbmmParams of include/opsnn_b200_kernels.h (the kernel-level C ABI below the aclnn layer)."""
+    _fields_ = [("x_dtype", c_int32), ("w_dtype", c_int32), ("bias_dtype", c_int32), ("trans_w", c_int32),
+                ("m", c_int64), ("n", c_int64), ("k", c_int64),
+                ("x", c_void_p), ("x_ld", c_int64), ("w", c_void_p), ("w_ld", c_int64),
+                ("scale", c_void_p), ("offset", c_void_p), ("group_size", c_int64), ("scale_sg", c_int64),
+                ("scale_sn", c_int64), ("bias", c_void_p), ("y", c_void_p), ("y_ld", c_int64),
+                ("workspace", c_void_p), ("workspace_size", c_uint64)]
+
+
 _lib = None
 
 
@@ -70,6 +82,14 @@ def lib():
     L.opsnn_qmm_umma_status.restype = ctypes.c_uint32
     L.opsnn_qmm_umma_status.argtypes = [c_int32]
     L.opsnn_last_kernel_name.restype = c_char_p
+    for name in ("opsnn_wqbmm_launch", "opsnn_wqbmm_decode_static_launch"):
+        getattr(L, name).restype = c_int32
+    L.opsnn_wqbmm_launch.argtypes = [POINTER(WqbmmParams), c_int32, c_void_p]
+    L.opsnn_wqbmm_decode_static_launch.argtypes = [POINTER(WqbmmParams), c_void_p]
+    L.opsnn_wqbmm_workspace_size.restype = c_uint64
+    L.opsnn_wqbmm_workspace_size.argtypes = [POINTER(WqbmmParams), c_int32]
+    L.opsnn_wqbmm_select_kernel.restype = c_int32
+    L.opsnn_wqbmm_select_kernel.argtypes = [POINTER(WqbmmParams)]
     _lib = L
     return L
 

@@ -500,4 +500,115 @@ int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     return (int32_t)cudaGetLastError();
 }
 
+// ---- entry point that allocates nothing -----------------------------------------------------------------------------
+//
+// Same kernel, same split selection, but the cross-CTA scratch (tags + fp32 fragments) is a fixed array in this module's
+// device image instead of caller-provided workspace. Meant for callers that hold no allocator at the point of the call.
+// The array covers kStaticGrid CTAs: two resident CTAs per SM on 148 SMs, rounded up.
+namespace {
+
+constexpr int kStaticGrid = 304;
+constexpr size_t kStaticTagBytes = (((size_t)kStaticGrid * 8 + 255) / 256) * 256;
+constexpr size_t kStaticBytes = kStaticTagBytes + (size_t)kStaticGrid * kWarps * kTiles * 32 * sizeof(float4);  // 9,964,032
+
+}  // namespace
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
+
+}  // namespace
+
+void set_err(const char* fmt, ...);  // thread-local text behind aclGetRecentErrMsg (host library)
+
+int32_t wqbmm_decode_static_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+{
+    if (p->n > (int64_t)kStaticGrid * kStripCols) {
+        set_err("opsnn_wqbmm_decode_static_launch: n=%lld exceeds the %lld columns the built-in scratch covers", (long long)p->n,
+                (long long)kStaticGrid * kStripCols);
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    // set-up, once per device with that device current: resolve the scratch array's address
+    int dev = -1;
+    cudaError_t rc = cudaGetDevice(&dev);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_err("opsnn_wqbmm_decode_static_launch: device ordinal %d out of range (max %d)", dev, kMaxDevices - 1);
+        return (int32_t)cudaErrorInvalidDevice;
+    }
+    void* scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
+        rc = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
+        if (rc != cudaSuccess || scratch == nullptr) {
+            set_err("opsnn_wqbmm_decode_static_launch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(rc));
+            return (int32_t)(rc != cudaSuccess ? rc : cudaErrorInvalidSymbol);
+        }
+        g_static_scratch_ptr[dev].store(scratch, std::memory_order_release);
+    }
+
+    DecodeArgs a{};
+    a.w = reinterpret_cast<const uint32_t*>(p->w);
+    a.w_ld32 = p->w_ld / 8;
+    a.x = p->x;
+    a.x_ld = p->x_ld;
+    a.scale = p->scale;
+    a.offset = p->offset;
+    a.scale_sg = p->group_size > 0 ? p->scale_sg : 0;
+    a.scale_sn = (int32_t)p->scale_sn;
+    a.bias = p->bias;
+    a.bias_dtype = p->bias_dtype;
+    a.y = p->y;
+    a.y_ld = p->y_ld;
+    a.m = (int32_t)p->m;
+    a.n = p->n;
+    a.k = p->k;
+    a.strips = (p->n + kStripCols - 1) / kStripCols;
+    a.ksteps = p->k / 16;
+    a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
+    const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
+    const int variant = (bf16 ? 2 : 0) + (has_off ? 1 : 0);
+    int resident = 0;
+    switch (variant) {
+        case 0: resident = decode_grid<false, false>(0); break;
+        case 1: resident = decode_grid<false, true>(1); break;
+        case 2: resident = decode_grid<true, false>(2); break;
+        default: resident = decode_grid<true, true>(3); break;
+    }
+    int64_t splits = resident / a.strips;
+    if (splits > a.ksteps) splits = a.ksteps;
+    if (splits * a.strips > kStaticGrid) splits = kStaticGrid / a.strips;
+    if (splits < 1) splits = 1;
+    a.splits = splits;
+    const int grid = (int)(a.strips * splits);  // <= kStaticGrid by the checks above
+    a.tags = reinterpret_cast<unsigned long long*>(scratch);
+    a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(scratch) + kStaticTagBytes);
+    a.nonce = next_nonce();
+    a.c_mask = 0x000F000Fu;
+    a.c_magic = bf16 ? Num<true>::kMagic : Num<false>::kMagic;
+    a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
+    switch (variant) {
+        case 0: wqbmm_decode_kernel<false, false><<<grid, kThreads, 0, stream>>>(a); break;
+        case 1: wqbmm_decode_kernel<false, true><<<grid, kThreads, 0, stream>>>(a); break;
+        case 2: wqbmm_decode_kernel<true, false><<<grid, kThreads, 0, stream>>>(a); break;
+        default: wqbmm_decode_kernel<true, true><<<grid, kThreads, 0, stream>>>(a); break;
+    }
+    note_launch("wqbmm_decode_static");
+    return (int32_t)cudaGetLastError();
+}
+
 }  // namespace opsnn
+
+extern "C" __attribute__((visibility("default"))) int32_t opsnn_wqbmm_decode_static_launch(const OpsnnWqbmmParams* p, void* stream)
+{
+    if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
+    if (p->m <= 0 || p->n <= 0) return 0;
+    if (!opsnn::wqbmm_decode_eligible(p)) {
+        opsnn::set_err("opsnn_wqbmm_decode_static_launch: parameters outside the decode kernel's range (int4 weight stored (k,n), "
+                       "m <= 16, k %% 16 == 0, n %% 8 == 0, 16-byte aligned x/scale rows)");
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    return opsnn::wqbmm_decode_static_launch(p, static_cast<cudaStream_t>(stream));
+}
