@@ -55,7 +55,6 @@ struct UmmaArgs {
     int64_t bias_bs;
     void* out;
     int64_t out_ld, out_bs;
-    int32_t dbg;  // timing experiments only: 1 = no TMA traffic, 2 = no MMA, 4 = plain arrive instead of commit
 };
 
 __device__ unsigned int g_umma_status = 0;
@@ -188,92 +187,109 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (warp == EW) {
         // ======================= TMA producer =======================
+        // The whole warp runs the loop (uniform control flow: waits, ring counters and coordinates stay cheap); one
+        // elected lane issues the copies. Ring position is kept as (stage, parity) counters, parameters in registers.
         if (lane == 0) {
             ptx::tma_prefetch_desc(&map_a);
             ptx::tma_prefetch_desc(&map_b);
-            // ring position kept as (stage, parity) counters: a division per k-block on a single thread costs more than the MMAs
-            uint32_t s = 0, par = 0;
-            bool ok = true;
-            // kernel parameters used per k-block are copied to registers: the "memory" clobbers of the barrier and copy
-            // instructions would otherwise make the compiler re-read them from parameter space every time
-            const uint32_t stages = (uint32_t)a.stages;
-            const int kblocks = a.kblocks;
-            const bool a_mn = a.a_mn_major != 0, b_mn = a.b_mn_major != 0, no_tma = (a.dbg & 1) != 0;
-            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-                const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN;
-                const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
-                for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == stages) ? 0 : s + 1, par ^= (s == 0)) {
-                    if (!ptx::mbar_wait(&empty[s], par ^ 1, abort_flag)) {
-                        report(abort_flag, (1u << 8) | 1u);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* sa = smem + (size_t)s * kStage;
-                    uint8_t* sb = sa + kATile;
-                    if (no_tma) {
-                        ptx::mbar_arrive(&full[s]);
-                        continue;
-                    }
-                    ptx::mbar_expect_tx(&full[s], (uint32_t)kStage);
-                    if (a_mn) ptx::tma_load_3d(sa, &map_a, &full[s], m0, kb * BK, ba);
-                    else ptx::tma_load_3d(sa, &map_a, &full[s], kb * BK, m0, ba);
-                    if (b_mn) {
-#pragma unroll
-                        for (int c = 0; c < (BN + 127) / 128; ++c)
-                            ptx::tma_load_3d(sb + c * (128 * BK), &map_b, &full[s], n0 + c * 128, kb * BK, bb);
-                    } else {
-                        ptx::tma_load_3d(sb, &map_b, &full[s], kb * BK, n0, bb);
-                    }
+        }
+        __syncwarp();
+        uint32_t s = 0, par = 0;
+        bool ok = true;
+        const uint32_t stages = (uint32_t)a.stages;
+        const int kblocks = a.kblocks;
+        const bool a_mn = a.a_mn_major != 0, b_mn = a.b_mn_major != 0;
+        const uint32_t smem0 = ptx::smem_u32(smem), full0 = ptx::smem_u32(full), empty0 = ptx::smem_u32(empty);
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN;
+            const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
+            int32_t kk = 0;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
+                    report(abort_flag, (1u << 8) | 1u);
+                    ok = false;
+                    break;
+                }
+                if (ptx::elect_one()) {
+                    const uint32_t fb = full0 + 8u * s, sa = smem0 + s * (uint32_t)kStage, sb = sa + (uint32_t)kATile;
+                    ptx::mbar_expect_tx_a(fb, (uint32_t)kStage);
+                    ptx::tma_load_3d_a(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
+                    ptx::tma_load_3d_a(sb, &map_b, fb, b_mn ? n0 : kk, b_mn ? kk : n0, bb);
+                    if (BN > 128 && b_mn) ptx::tma_load_3d_a(sb + 128u * BK, &map_b, fb, n0 + 128, kk, bb);
+                }
+                __syncwarp();
+                kk += BK;
+                if (++s == stages) {
+                    s = 0;
+                    par ^= 1u;
                 }
             }
         }
     } else if (warp == EW + 1) {
         // ======================= MMA issuer =======================
-        if (lane == 0) {
-            uint32_t s = 0, par = 0, grp = 0;
-            bool ok = true;
-            // K-major operand: a k step is 32 bytes along the swizzled row; MN-major: 32 k-rows = 4 KB (units of 16 bytes)
-            const uint32_t smem0 = ptx::smem_u32(smem);
-            const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
-            const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
-                                              : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
-            const uint32_t a_kstep = a.a_mn_major ? 256u : 2u, b_kstep = a.b_mn_major ? 256u : 2u;
-            const uint32_t stages = (uint32_t)a.stages, idesc = a.idesc;
-            const int kblocks = a.kblocks;
-            const int dbg = a.dbg;
-            for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == stages) ? 0 : s + 1, par ^= (s == 0)) {
-                    const bool group_start = kPerBlock || kb == 0;
-                    const bool group_end = kPerBlock || kb == kblocks - 1;
-                    const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
-                    if (group_start && !ptx::mbar_wait(&tempty[buf], gpar ^ 1, abort_flag)) {
+        // Same shape: whole warp, one elected lane issues the four MMAs of a stage and the commits. A stage of BN = 256
+        // is 512 tensor-core cycles; the loop below has to cost this warp less than that per stage.
+        uint32_t s = 0, par = 0, grp = 0;
+        bool ok = true;
+        const uint32_t smem0 = ptx::smem_u32(smem), full0 = ptx::smem_u32(full), empty0 = ptx::smem_u32(empty);
+        const uint32_t tfull0 = ptx::smem_u32(tfull), tempty0 = ptx::smem_u32(tempty);
+        // descriptors: only the 14-bit start-address field (low word) changes: stage base, then the k step inside the
+        // stage. K-major operand: a k step is 32 bytes along the swizzled row; MN-major: 32 k-rows = 4 KB (units of 16 B)
+        const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
+        const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
+                                          : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+        const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0;
+        const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull;
+        const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 256u : 2u;
+        const uint32_t stages = (uint32_t)a.stages, idesc = a.idesc;
+        const int kblocks = a.kblocks;
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            uint32_t acc = 0u;
+            if (!kPerBlock) {
+                if (!ptx::mbar_wait_a(tempty0 + 8u * (grp & 1u), ((grp >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report(abort_flag, (2u << 8) | 1u);
+                    ok = false;
+                    break;
+                }
+            }
+            for (int kb = 0; kb < kblocks; ++kb) {
+                if (kPerBlock) {
+                    if (!ptx::mbar_wait_a(tempty0 + 8u * (grp & 1u), ((grp >> 1) & 1u) ^ 1u, abort_flag)) {
                         report(abort_flag, (2u << 8) | 1u);
                         ok = false;
                         break;
                     }
-                    if (!ptx::mbar_wait(&full[s], par, abort_flag)) {
-                        report(abort_flag, (2u << 8) | 2u);
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
-                    // descriptors: only the 14-bit start-address field changes (stage base, then the k step inside the stage)
-                    const uint32_t stage_off = (s * (uint32_t)kStage) >> 4;
-                    const uint32_t d = tmem_base + buf * BN;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t da = da0 + (uint64_t)(stage_off + k * a_kstep);
-                        const uint64_t db = db0 + (uint64_t)(stage_off + k * b_kstep);
-                        if (!(dbg & 2)) ptx::umma<kKind>(d, da, db, idesc, (group_start && k == 0) ? 0u : 1u);
-                    }
-                    if (dbg & 4) ptx::mbar_arrive(&empty[s]);
-                    else ptx::umma_commit(&empty[s]);
-                    if (group_end) {
-                        ptx::umma_commit(&tfull[buf]);
-                        ++grp;
-                    }
                 }
+                if (!ptx::mbar_wait_a(full0 + 8u * s, par, abort_flag)) {
+                    report(abort_flag, (2u << 8) | 2u);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                if (ptx::elect_one()) {
+                    const uint32_t stage_off = (s * (uint32_t)kStage) >> 4;
+                    const uint32_t d = tmem_base + (grp & 1u) * BN;
+                    const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        ptx::umma<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * b_k1), idesc,
+                                         k == 0 ? acc : 1u);
+                    ptx::umma_commit_a(empty0 + 8u * s);
+                    if (kPerBlock) ptx::umma_commit_a(tfull0 + 8u * (grp & 1u));
+                }
+                __syncwarp();
+                if (kPerBlock) ++grp;
+                else acc = 1u;
+                if (++s == stages) {
+                    s = 0;
+                    par ^= 1u;
+                }
+            }
+            if (!kPerBlock && ok) {
+                if (ptx::elect_one()) ptx::umma_commit_a(tfull0 + 8u * (grp & 1u));
+                __syncwarp();
+                ++grp;
             }
         }
     } else {
@@ -575,7 +591,6 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.sa_bs = p->sa_bs; a.sb_bs = p->sb_bs; a.group_m = p->group_m > 0 ? p->group_m : 1;
     a.trans_a = p->trans_a; a.trans_b = p->trans_b;
     a.bias = p->bias; a.bias_bs = p->bias_bs; a.out = p->out; a.out_ld = p->out_ld; a.out_bs = p->out_bs;
-    if (const char* e = getenv("OPSNN_QMM_DBG")) a.dbg = atoi(e);
     const uint32_t fa = a.is_int ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = a.is_int ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)bn);

@@ -64,6 +64,58 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// ---- lean forms for the single-warp role loops -------------------------------------------------------------------------
+// A role loop (copy producer, MMA issuer) is one warp with nothing to hide its instruction latencies behind: every
+// instruction and every taken branch on its path costs its full latency per k-block. These take raw 32-bit shared
+// addresses (no generic->shared conversion per call) and keep the bounded spin out of line.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait_a(bar_addr, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+// Bounded wait whose common case (the phase has completed, or completes within one try_wait) is two instructions.
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    if (mbar_try_wait_a(bar_addr, parity)) return true;
+    return mbar_wait_slow_a(bar_addr, parity, abort_flag);
+}
+__device__ __forceinline__ void mbar_expect_tx_a(uint32_t bar_addr, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_a(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_addr, int32_t c0, int32_t c1,
+                                              int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_a(uint32_t bar_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+// One lane of a fully active warp; the same lane every time for the same (full) member mask.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- TMA ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1,
                                             int32_t c2)
