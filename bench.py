@@ -98,6 +98,9 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+WORKLOAD_C2 = "c2: W4A16 decode m16 k8192 n28672 group128 bf16 scale+offset, int4 packed 8/int32 along n"
+
+
 def make_inputs(torch, dev, seed, sets):
     gen = torch.Generator(device=dev).manual_seed(seed)
     x = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
@@ -123,6 +126,38 @@ def cpu_oracle_once(x_np, words_np, scale_np, offset_np):
     return time.perf_counter() - t0, y
 
 
+def cpu_c_oracle_once(x_np, words_np, scale_np, offset_np, cols):
+    """The plain-C restatement (oracle/c) on all host cores over the first `cols` columns; returns seconds scaled to the
+    full width, or None when the C oracle is not built and cannot be built here."""
+    import numpy as np
+
+    try:
+        from oracle import c_oracle
+
+        c_oracle.lib()
+    except Exception:
+        return None
+    threads = os.cpu_count() or 1
+    u16 = lambda a: a.view(np.uint16)
+    t0 = time.perf_counter()
+    c_oracle.wq_w4a16_group(u16(x_np), words_np, u16(scale_np), u16(offset_np), G, 0, cols, threads=threads)
+    return (time.perf_counter() - t0) * (N / cols)
+
+
+def cpu_baseline_c2(x_np, words_np, scale_np, offset_np):
+    """CPU baseline of the c2 workload: the faster of the numpy restatement of the reference golden (one full call, BLAS
+    threads) and the C restatement (all cores, a 2048-column panel scaled to the full width)."""
+    sec_np, _ = cpu_oracle_once(x_np, words_np, scale_np, offset_np)
+    sec_c = cpu_c_oracle_once(x_np, words_np, scale_np, offset_np, 2048)
+    use_c = sec_c is not None and sec_c < sec_np
+    sec = sec_c if use_c else sec_np
+    sample = ("C restatement of the reference golden, %d threads, 2048-column panel scaled x%d (numpy restatement, full call: %.2f s)"
+              % (os.cpu_count() or 1, N // 2048, sec_np)) if use_c else (
+        "one full call of the numpy restatement of the reference golden (%.2f s%s)"
+        % (sec_np, "" if sec_c is None else "; C restatement on all cores: %.2f s" % sec_c))
+    return sec, {"value": ALGO_BYTES / sec / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample}
+
+
 def to_np_bf16(t):
     import ml_dtypes
     import torch
@@ -144,17 +179,17 @@ def run_reference(args):
     scale = rng.uniform(0.005, 0.02, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
     offset = rng.uniform(-1, 1, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
     for _ in range(min(args.warmup, 1)):
-        cpu_oracle_once(x, words, scale, offset)
+        cpu_baseline_c2(x, words, scale, offset)
     steps = max(1, min(args.steps, 3))
-    ts = [cpu_oracle_once(x, words, scale, offset)[0] for _ in range(steps)]
-    sec = sum(ts) / len(ts)
+    runs = [cpu_baseline_c2(x, words, scale, offset) for _ in range(steps)]
+    sec = sum(r[0] for r in runs) / len(runs)
     gbs = ALGO_BYTES / sec / 1e9
+    base = dict(runs[-1][1], value=gbs)
     line = {"impl": "reference", "metric": "W4A16 decode HBM GB/s (weight_quant_batch_matmul_v2, algorithmic bytes / time)",
             "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": "c2: W4A16 decode m16 k8192 n28672 group128 bf16 scale+offset"},
-            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-                             "sample": "full workload, %d call(s), numpy restatement of the reference golden" % steps},
+            "data": "synthetic", "config": {"workload": WORKLOAD_C2},
+            "cpu_baseline": base,
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line))
 
@@ -350,7 +385,7 @@ def main():
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded; shapes and value ranges of BASELINE config 2)",
-            "config": {"workload": "c2: W4A16 decode m16 k8192 n28672 group128 bf16 scale+offset, int4 packed 8/int32 along n",
+            "config": {"workload": WORKLOAD_C2,
                        "sharding": "n-sharded, one [8192,28672] weight shard per GPU, x replicated, no collective",
                        "l2": "rotating %d weight sets (%d MB) > 126 MB L2" % (args.sets, args.sets * ALGO_BYTES // 1000000),
                        "kernel": kernel_name, "workspace_bytes": int(ws_bytes)},
@@ -370,9 +405,7 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             xs = to_np_bf16(x)
             w0, s0, o0 = data[0]
-            sec, y_cpu = cpu_oracle_once(xs, w0.cpu().numpy(), to_np_bf16(s0), to_np_bf16(o0))
-            line["cpu_baseline"] = {"value": ALGO_BYTES / sec / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-                                    "sample": "one full call of the numpy restatement of the reference golden (%.1f s)" % sec}
+            _, line["cpu_baseline"] = cpu_baseline_c2(xs, w0.cpu().numpy(), to_np_bf16(s0), to_np_bf16(o0))
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))

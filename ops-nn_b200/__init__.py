@@ -10,3 +10,4 @@ The folder name contains a hyphen; import it with `importlib` (see `load_package
 module name `ops_nn_b200`.
 """
 from . import aclnn  # noqa: F401
+from . import shard  # noqa: F401
