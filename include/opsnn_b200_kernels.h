@@ -79,7 +79,10 @@ OPSNN_API int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choic
 typedef enum {
     OPSNN_WQ_KERNEL_AUTO = 0,
     OPSNN_WQ_KERNEL_GENERIC = 1, /* dequantise the whole weight into workspace, then a bf16/fp16 tensor-core GEMM */
-    OPSNN_WQ_KERNEL_DECODE = 2   /* fused streaming kernel for small m: int4 (n-packed) per-group/-channel */
+    OPSNN_WQ_KERNEL_DECODE = 2,  /* fused streaming kernel for small m: int4 (n-packed) per-group/-channel; reproduces
+                                    the reference's two roundings per dequantised weight */
+    OPSNN_WQ_KERNEL_DECODE_FAST = 3 /* same regime, "high performance" precision mode (inner_precise = 1): scale and
+                                    offset applied per k-group after the MMA in fp32; not bit-identical to DECODE */
 } OpsnnWqKernelChoice;
 
 typedef struct OpsnnWqbmmParams {
@@ -102,6 +105,7 @@ typedef struct OpsnnWqbmmParams {
     int64_t y_ld;
     void* workspace;
     uint64_t workspace_size;
+    int32_t inner_precise;  /* innerPrecise of aclnnWeightQuantBatchMatmulV3: 0 high precision (default), 1 high performance */
 } OpsnnWqbmmParams;
 
 OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice);
@@ -116,7 +120,7 @@ OPSNN_API int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_c
  *   - The cross-CTA scratch is a 9,964,032-byte array inside the library's device image; p->workspace and
  *     p->workspace_size are ignored. Neither this function nor anything it calls allocates host-visible device memory.
  *   - Limits: the parameters must satisfy the decode kernel's range (opsnn_wqbmm_select_kernel(p) ==
- *     OPSNN_WQ_KERNEL_DECODE) and n <= 155,648 columns (304 CTAs x 512). Anything else returns cudaErrorInvalidValue
+ *     OPSNN_WQ_KERNEL_DECODE with inner_precise = 0; inner_precise is ignored here) and n <= 155,648 columns (304 CTAs x 512). Anything else returns cudaErrorInvalidValue
  *     and leaves the reason in aclGetRecentErrMsg().
  *   - The first call on each device (with that device current) resolves the array's address; this may load the
  *     library's device code. Make that first call during start-up, before any stream capture begins.

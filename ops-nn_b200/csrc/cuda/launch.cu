@@ -28,6 +28,8 @@ int32_t wqbmm_generic_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p);
 uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p);
+int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
 
@@ -65,6 +67,7 @@ int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* s
 int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
 {
     if (p == nullptr) return OPSNN_WQ_KERNEL_GENERIC;
+    if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
     return wqbmm_decode_eligible(p) ? OPSNN_WQ_KERNEL_DECODE : OPSNN_WQ_KERNEL_GENERIC;
 }
 
@@ -72,7 +75,7 @@ uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_ch
 {
     if (p == nullptr) return 0;
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
-    return kernel_choice == OPSNN_WQ_KERNEL_DECODE ? wqbmm_decode_workspace_size(p) : 0;
+    return (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) ? wqbmm_decode_workspace_size(p) : 0;
 }
 
 int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream)
@@ -83,6 +86,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE) {
         if (!wqbmm_decode_eligible(p)) return (int32_t)cudaErrorInvalidValue;
         return wqbmm_decode_launch(p, static_cast<cudaStream_t>(stream));
+    }
+    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) {
+        if (!wqbmm_decode_fast_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return wqbmm_decode_fast_launch(p, static_cast<cudaStream_t>(stream));
     }
     return wqbmm_generic_launch(p, static_cast<cudaStream_t>(stream));
 }

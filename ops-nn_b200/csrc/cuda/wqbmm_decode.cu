@@ -32,125 +32,11 @@
 #include <chrono>
 
 #include "common.cuh"
+#include "wqbmm_decode_common.cuh"
 
 namespace opsnn {
 
 namespace {
-
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kWarpCols = 64;               // one packed word (8 columns) per lane-group g
-constexpr int kStripCols = kWarps * kWarpCols;  // 512
-#ifndef OPSNN_DECODE_PF
-#define OPSNN_DECODE_PF 8
-#endif
-#ifndef OPSNN_DECODE_MINB
-#define OPSNN_DECODE_MINB 2
-#endif
-constexpr int kPrefetch = OPSNN_DECODE_PF;  // k-steps of weight words held in registers ahead of use
-constexpr int kTiles = 8;                 // m16n8 tiles per warp: nibble j of the lane's word is tile j
-constexpr int kChunk = 32;                // k-steps of x staged in shared memory at a time (double buffered)
-constexpr int kXPitch = kChunk * 16 + 8;  // elements; the +8 skews rows over the banks so fragment reads do not conflict
-
-struct DecodeArgs {
-    const uint32_t* w;     // packed words
-    int64_t w_ld32;        // words per k row
-    const void* x;
-    int64_t x_ld;
-    const void* scale;
-    const void* offset;
-    int64_t scale_sg;      // elements between groups
-    int32_t scale_sn;      // 1 per-channel/-group, 0 per-tensor
-    const void* bias;
-    int32_t bias_dtype;
-    void* y;
-    int64_t y_ld;
-    int32_t m;
-    int64_t n, k;
-    int64_t strips, ksteps, splits, steps_per_group;
-    unsigned long long* tags;  // [gridDim]
-    float4* partials;          // [gridDim][kWarps][kTiles][32]
-    unsigned long long nonce;
-    uint32_t c_mask, c_magic, c_bias;  // 0x000F000F, Num::kMagic, Num::kBias
-};
-
-__device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
-{
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
-// 16-bit pair arithmetic on raw 32-bit registers (no type punning through memory): each op rounds once, to nearest even.
-template <bool kBf16>
-struct Num;
-template <>
-struct Num<true> {
-    static constexpr uint32_t kMagic = 0x43084308u;  // (nibble ^ 8) | 0x4300  ->  bf16 128 + 8 + w
-    static constexpr uint32_t kBias = 0x43084308u;   // bf16x2 {136, 136}
-    __device__ __forceinline__ static uint32_t sub(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static uint32_t add(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
-    {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-};
-template <>
-struct Num<false> {
-    static constexpr uint32_t kMagic = 0x64086408u;  // (nibble ^ 8) | 0x6400  ->  fp16 1024 + 8 + w
-    static constexpr uint32_t kBias = 0x64086408u;   // half2 {1032, 1032}
-    __device__ __forceinline__ static uint32_t sub(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static uint32_t add(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b)
-    {
-        uint32_t d;
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-        return d;
-    }
-    __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
-    {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-};
 
 // Two nibbles (bits [3:0] and [19:16] of t) -> dequantised 16-bit pair, with the reference's two roundings.
 // mask / magic / bias come from kernel parameters, i.e. the constant bank, so that they cost neither a register nor a
@@ -318,66 +204,7 @@ __global__ void __launch_bounds__(kThreads, OPSNN_DECODE_MINB) wqbmm_decode_kern
           __syncthreads();
         }
 
-        // ---- this CTA's share of the strip is in acc; combine with the other contributors if there are any ----
-        const bool whole = a.splits == 1;
-        bool do_write = whole;
-        if (!whole) {
-            float4* mine = a.partials + ((c * kWarps + warp) * kTiles) * 32 + lane;
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) mine[t * 32] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
-            asm volatile("fence.sc.gpu;" ::: "memory");
-            __syncthreads();
-            if (tid == 0) {
-                asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(a.tags + c), "l"(a.nonce) : "memory");
-                asm volatile("fence.sc.gpu;" ::: "memory");
-                int all = 1;
-                for (int64_t j = 0; j < a.splits; ++j) {
-                    unsigned long long seen;
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.tags + strip + j * a.strips) : "memory");
-                    all &= (seen == a.nonce);
-                }
-                asm volatile("fence.sc.gpu;" ::: "memory");
-                s_reduce = all;
-            }
-            __syncthreads();
-            do_write = s_reduce != 0;
-            if (do_write) {
-#pragma unroll
-                for (int t = 0; t < kTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-                for (int64_t j = 0; j < a.splits; ++j) {
-                    const float4* theirs = a.partials + (((strip + j * a.strips) * kWarps + warp) * kTiles) * 32 + lane;
-#pragma unroll
-                    for (int t = 0; t < kTiles; ++t) {
-                        const float4 v = __ldcg(theirs + t * 32);
-                        acc[t][0] += v.x; acc[t][1] += v.y; acc[t][2] += v.z; acc[t][3] += v.w;
-                    }
-                }
-            }
-            __syncthreads();
-            if (do_write && tid == 0) {
-                // every contributor's fragment has been consumed: retire the strip's tags, so that a replay of this very
-                // launch (same nonce, e.g. from a captured CUDA graph) starts from a clean slate
-                for (int64_t j = 0; j < a.splits; ++j)
-                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + strip + j * a.strips), "l"(0ull) : "memory");
-            }
-        }
-        if (do_write) {
-            // D fragment: rows g, g+8; tile-local columns 2q, 2q+1 = lane groups 2q, 2q+1 of the loader
-            const int64_t colw = strip * kStripCols + warp * kWarpCols;
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int row = g + (e >> 1) * 8;
-                    const int64_t col = colw + 8 * (2 * q + (e & 1)) + t;
-                    if (row < a.m && col < a.n) {
-                        float f = acc[t][e];
-                        if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
-                        store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
-                    }
-                }
-            }
-        }
+        combine_and_store<kBf16>(a, acc, c, strip, warp, lane, tid, &s_reduce);
     }
 }
 
@@ -398,17 +225,6 @@ int decode_grid(int variant)
         g_decode_ctas_per_sm[variant] = nb > 0 ? nb : 1;
     }
     return g_sm_count * g_decode_ctas_per_sm[variant];
-}
-
-unsigned long long next_nonce()
-{
-    static std::atomic<unsigned long long> ctr{
-        (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() * 0x9E3779B97F4A7C15ull + 1};
-    unsigned long long z = ctr.fetch_add(0x9E3779B97F4A7C15ull);
-    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    z ^= z >> 31;
-    return z ? z : 1;
 }
 
 constexpr int kMaxGrid = 148 * 4 * 2;  // workspace is sized for at most this many CTAs

@@ -25,8 +25,8 @@ namespace {
 
 aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weight, const aclTensor* antiquantScale,
                       const aclTensor* antiquantOffset, const aclTensor* quantScale, const aclTensor* quantOffset,
-                      const aclTensor* bias, int antiquantGroupSize, const aclTensor* y, uint64_t* workspaceSize,
-                      aclOpExecutor** executor)
+                      const aclTensor* bias, int antiquantGroupSize, int innerPrecise, const aclTensor* y,
+                      uint64_t* workspaceSize, aclOpExecutor** executor)
 {
     clear_err();
     if (workspaceSize == nullptr || executor == nullptr) {
@@ -181,6 +181,9 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     if (wd != ACL_INT4 && wd != ACL_INT8) no_kernel("fp8/fp4/hifloat8 weight kernels are not built yet");
     if (sc.dtype == ACL_FLOAT8_E8M0) no_kernel("mx (e8m0) antiquant kernels are not built yet");
 
+    // innerPrecise = 1 asks for the high-performance mode; it only changes anything where the reference says it does
+    // (A16W4 per-group, small m: docs/aclnnWeightQuantBatchMatmulV3.md:389), i.e. where the fast decode kernel applies
+    p.inner_precise = innerPrecise;
     exec->kernel_choice = OPSNN_WQ_KERNEL_AUTO;
     if (const char* e = std::getenv("OPSNN_WQ_KERNEL")) exec->kernel_choice = std::atoi(e);
     if (!exec->unsupported) {
@@ -236,7 +239,9 @@ aclnnStatus wq_run(const char* api, void* workspace, uint64_t workspaceSize, acl
     if (choice == OPSNN_WQ_KERNEL_AUTO) {
         choice = opsnn_wqbmm_select_kernel(&p);
         // the plan sized the workspace for the decode kernel only if the shapes allowed it
-        if (choice == OPSNN_WQ_KERNEL_DECODE && workspaceSize < opsnn_wqbmm_workspace_size(&p, choice)) choice = OPSNN_WQ_KERNEL_GENERIC;
+        if ((choice == OPSNN_WQ_KERNEL_DECODE || choice == OPSNN_WQ_KERNEL_DECODE_FAST) &&
+            workspaceSize < opsnn_wqbmm_workspace_size(&p, choice))
+            choice = OPSNN_WQ_KERNEL_GENERIC;
     }
     int32_t rc = opsnn_wqbmm_launch(&p, choice, stream);
     if (rc != 0) {
@@ -260,7 +265,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(const aclTensor* x, co
                                                           aclOpExecutor** executor)
 {
     return wq_common("aclnnWeightQuantBatchMatmulV2GetWorkspaceSize", x, weight, antiquantScale, antiquantOffsetOptional,
-                     quantScaleOptional, quantOffsetOptional, biasOptional, antiquantGroupSize, y, workspaceSize, executor);
+                     quantScaleOptional, quantOffsetOptional, biasOptional, antiquantGroupSize, 0, y, workspaceSize, executor);
 }
 
 aclnnStatus aclnnWeightQuantBatchMatmulV2(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
@@ -284,7 +289,8 @@ aclnnStatus aclnnWeightQuantBatchMatmulV3GetWorkspaceSize(const aclTensor* x, co
         return ACLNN_ERR_PARAM_INVALID;
     }
     return wq_common("aclnnWeightQuantBatchMatmulV3GetWorkspaceSize", x, weight, antiquantScale, antiquantOffsetOptional,
-                     quantScaleOptional, quantOffsetOptional, biasOptional, antiquantGroupSize, y, workspaceSize, executor);
+                     quantScaleOptional, quantOffsetOptional, biasOptional, antiquantGroupSize, innerPrecise, y, workspaceSize,
+                     executor);
 }
 
 aclnnStatus aclnnWeightQuantBatchMatmulV3(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,

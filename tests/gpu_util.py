@@ -74,7 +74,7 @@ def run_qmm_fixture(aclnn, a, meta, kernel=None):
     return out_to_np(out)
 
 
-def run_wq_fixture(aclnn, a, meta, kernel=None, api="v2"):
+def run_wq_fixture(aclnn, a, meta, kernel=None, api="v2", inner_precise=0):
     import os
 
     x = a["x"]
@@ -115,7 +115,7 @@ def run_wq_fixture(aclnn, a, meta, kernel=None, api="v2"):
         os.environ["OPSNN_WQ_KERNEL"] = str(kernel)
     try:
         aclnn.weight_quant_batch_matmul(desc(aclnn, x), d_w, sc_desc(a["scale"]), d_y, sc_desc(a.get("offset")),
-                                        desc(aclnn, a.get("bias")), meta["group_size"], inner_precise=0 if api == "v3" else None)
+                                        desc(aclnn, a.get("bias")), meta["group_size"], inner_precise=inner_precise if api == "v3" else None)
     finally:
         os.environ.pop("OPSNN_WQ_KERNEL", None)
     torch.cuda.synchronize()
