@@ -28,6 +28,8 @@ COMMON = [
 for _m in ("OPSNN_DECODE_PF", "OPSNN_DECODE_MINB"):  # tuning knobs of the decode kernel, unset in normal builds
     if os.environ.get(_m):
         COMMON.append("-D%s=%s" % (_m, os.environ[_m]))
+for _d in filter(None, os.environ.get("OPSNN_EXTRA_DEFS", "").split(",")):  # extra -D switches for tuning experiments
+    COMMON.append("-D" + _d)
 
 
 def sources():

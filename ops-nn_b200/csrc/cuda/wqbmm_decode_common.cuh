@@ -41,6 +41,7 @@ struct DecodeArgs {
     int32_t m;
     int64_t n, k;
     int64_t strips, ksteps, splits, steps_per_group;
+    int64_t k_align;       // group-wise kernel only: k ranges start and end on multiples of this many k-steps (even)
     unsigned long long* tags;  // [gridDim]
     float4* partials;          // [gridDim][kWarps][kTiles][32]
     unsigned long long nonce;
@@ -86,6 +87,13 @@ struct Num<true> {
         asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
         return d;
     }
+    // same instruction, not volatile: the compiler may interleave it with the logic ops of the next k-step
+    __device__ __forceinline__ static void mma_free(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
     __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
     {
         asm volatile(
@@ -116,6 +124,12 @@ struct Num<false> {
         asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
         return d;
     }
+    __device__ __forceinline__ static void mma_free(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
     __device__ __forceinline__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
     {
         asm volatile(
@@ -129,7 +143,7 @@ struct Num<false> {
 // fragments, then a launch nonce; whichever contributor observes all nonces present (at least one does: store, fence.sc,
 // load) adds the fragments in CTA order - so the result does not depend on arrival order - writes y and zeroes the
 // strip's nonces. No atomics, no spinning, no zero-initialised workspace.
-template <bool kBf16>
+template <bool kBf16, int kLayout = 0>
 __device__ __forceinline__ void combine_and_store(const DecodeArgs& a, float (&acc)[kTiles][4], int64_t c, int64_t strip, int warp,
                                                   int lane, int tid, int* s_reduce_ptr)
 {
@@ -142,39 +156,52 @@ __device__ __forceinline__ void combine_and_store(const DecodeArgs& a, float (&a
                 float4* mine = a.partials + ((c * kWarps + warp) * kTiles) * 32 + lane;
     #pragma unroll
                 for (int t = 0; t < kTiles; ++t) mine[t * 32] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
-                asm volatile("fence.sc.gpu;" ::: "memory");
-                __syncthreads();
-                if (tid == 0) {
-                    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(a.tags + c), "l"(a.nonce) : "memory");
+                __syncthreads();  // every thread's fragment stores are ordered before warp 0's release below
+                if (warp == 0) {
+                    if (lane == 0) asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(a.tags + c), "l"(a.nonce) : "memory");
+                    __syncwarp();
+                    // own tag, then a sequentially consistent fence, then the others' tags: of two contributors at least
+                    // the later one sees the other's tag. The lanes look at 32 tags at a time.
                     asm volatile("fence.sc.gpu;" ::: "memory");
                     int all = 1;
-                    for (int64_t j = 0; j < a.splits; ++j) {
-                        unsigned long long seen;
-                        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.tags + strip + j * a.strips) : "memory");
+                    for (int64_t j0 = 0; j0 < a.splits; j0 += 32) {
+                        unsigned long long seen = a.nonce;
+                        if (j0 + lane < a.splits)
+                            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.tags + strip + (j0 + lane) * a.strips) : "memory");
                         all &= (seen == a.nonce);
                     }
-                    asm volatile("fence.sc.gpu;" ::: "memory");
-                    s_reduce = all;
+                    all = __all_sync(0xffffffffu, all);
+                    if (lane == 0) s_reduce = all;
                 }
                 __syncthreads();
                 do_write = s_reduce != 0;
                 if (do_write) {
     #pragma unroll
                     for (int t = 0; t < kTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-                    for (int64_t j = 0; j < a.splits; ++j) {
-                        const float4* theirs = a.partials + (((strip + j * a.strips) * kWarps + warp) * kTiles) * 32 + lane;
+                    // two contributors' fragments are fetched per round trip; the sums stay in contributor order
+                    for (int64_t j = 0; j < a.splits; j += 2) {
+                        const bool two = j + 1 < a.splits;
+                        const float4* pa = a.partials + (((strip + j * a.strips) * kWarps + warp) * kTiles) * 32 + lane;
+                        const float4* pb = a.partials + (((strip + (two ? j + 1 : j) * a.strips) * kWarps + warp) * kTiles) * 32 + lane;
+                        float4 va[kTiles], vb[kTiles];
+    #pragma unroll
+                        for (int t = 0; t < kTiles; ++t) va[t] = __ldcg(pa + t * 32);
+    #pragma unroll
+                        for (int t = 0; t < kTiles; ++t) vb[t] = __ldcg(pb + t * 32);
     #pragma unroll
                         for (int t = 0; t < kTiles; ++t) {
-                            const float4 v = __ldcg(theirs + t * 32);
-                            acc[t][0] += v.x; acc[t][1] += v.y; acc[t][2] += v.z; acc[t][3] += v.w;
+                            acc[t][0] += va[t].x; acc[t][1] += va[t].y; acc[t][2] += va[t].z; acc[t][3] += va[t].w;
+                            if (two) {
+                                acc[t][0] += vb[t].x; acc[t][1] += vb[t].y; acc[t][2] += vb[t].z; acc[t][3] += vb[t].w;
+                            }
                         }
                     }
                 }
                 __syncthreads();
-                if (do_write && tid == 0) {
+                if (do_write && warp == 0) {
                     // every contributor's fragment has been consumed: retire the strip's tags, so that a replay of this very
                     // launch (same nonce, e.g. from a captured CUDA graph) starts from a clean slate
-                    for (int64_t j = 0; j < a.splits; ++j)
+                    for (int64_t j = lane; j < a.splits; j += 32)
                         asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + strip + j * a.strips), "l"(0ull) : "memory");
                 }
             }
@@ -186,7 +213,8 @@ __device__ __forceinline__ void combine_and_store(const DecodeArgs& a, float (&a
     #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int row = g + (e >> 1) * 8;
-                        const int64_t col = colw + 8 * (2 * q + (e & 1)) + t;
+                        // kLayout 0: tile t is nibble t of the lane group's word; 1: the ldmatrix layout of the group-wise kernel
+                const int64_t col = colw + (kLayout == 0 ? 8 * (2 * q + (e & 1)) + t : 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3));
                         if (row < a.m && col < a.n) {
                             float f = acc[t][e];
                             if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));

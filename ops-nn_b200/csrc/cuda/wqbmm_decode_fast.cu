@@ -18,8 +18,11 @@
 // combination through workspace), but the weight words go global -> shared with cp.async (16 bytes per lane: one
 // instruction per warp moves one whole k-step of the warp's 64 columns, 16 rows x 32 bytes) into a per-warp ring of
 // 16 k-steps, so up to 8 KB per warp (128 KB per SM) is in flight without holding registers, and no thread ever waits
-// on another warp. The ring layout puts the four rows a lane needs ({2q, 2q+1, 2q+8, 2q+9}) 128 bytes apart and the
-// eight 16-byte pieces of one such row set on distinct bank groups, so the fragment reads are conflict free.
+// on another warp. A ring slot holds the step as four 8 x 16-byte matrices (rows 0-7 | 8-15) x (columns 0-31 | 32-63);
+// one ldmatrix.x4.trans then gives lane (g, q) the 16-bit column g of rows 2q and 2q+1 (and 2q+8, 2q+9) in one register
+// each: four nibbles of two k rows, already paired the way the MMA B fragment wants them, so a shift and one logic op
+// per tile finish the job. A 16-bit column is four packed weight columns; nibble j is MMA tile j of its 32-column half,
+// and the column permutation this implies is undone when y is written. x fragments come from ldmatrix.x4 as well.
 #include "common.cuh"
 #include "wqbmm_decode_common.cuh"
 
@@ -27,13 +30,13 @@ namespace opsnn {
 
 namespace {
 
-constexpr int kDepth = 16;                       // k-steps in a warp's ring (power of two)
+constexpr int kDepth = 12;                       // k-steps in a warp's ring (even)
 constexpr int kStepBytes = 512;                  // 16 rows x 32 bytes
-constexpr int kPending = kDepth / 2 - 1;         // commit groups (2 k-steps each) allowed in flight at a wait
-constexpr int kFChunk = 16;                      // k-steps of x per staged chunk (double buffered)
+constexpr int kFChunk = 112;                     // k-steps of x staged at a time (one buffer: a CTA's whole k range when it fits,
+                                                 // so that the warps of a CTA never meet at a barrier inside the main loop)
 constexpr int kFXPitch = kFChunk * 16 + 8;       // elements; +8 skews rows over the banks
 constexpr int kRingBytes = kWarps * kDepth * kStepBytes;
-constexpr int kFastSmem = kRingBytes + 2 * 16 * kFXPitch * 2;
+constexpr int kFastSmem = kRingBytes + 16 * kFXPitch * 2;
 
 template <bool kBf16>
 struct FastNum;
@@ -52,11 +55,19 @@ struct FastNum<false> {
     __device__ __forceinline__ static float hi(uint32_t r) { return __half2float(__ushort_as_half((unsigned short)(r >> 16))); }
 };
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+// Four 8x8 b16 matrices from shared memory, one register each. Non-transposed: lane (g,q) gets elements (2q, 2q+1) of row g.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4])
 {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// Transposed: lane (g,q) gets column g of rows 2q (low half) and 2q+1 (high half).
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
 }
 
 template <bool kBf16, bool kHasOffset>
@@ -68,14 +79,17 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     __shared__ int s_reduce;
     extern __shared__ __align__(128) uint8_t dyn[];
-    uint16_t(*xs)[16][kFXPitch] = reinterpret_cast<uint16_t(*)[16][kFXPitch]>(dyn + kRingBytes);
+    uint16_t(*xs)[kFXPitch] = reinterpret_cast<uint16_t(*)[kFXPitch]>(dyn + kRingBytes);
 
     const int64_t c = blockIdx.x;
     const int64_t strip = c % a.strips;
     const int64_t chunk = c / a.strips;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a.x);
-    const int64_t sa = (chunk * a.ksteps) / a.splits;
-    const int64_t sb = ((chunk + 1) * a.ksteps) / a.splits;
+    // this CTA's k range, in k-steps; both ends are multiples of k_align (a whole number of k-groups when there are enough
+    // groups to go round, else of step pairs), so a pair of steps never straddles a group
+    const int64_t units = a.ksteps / a.k_align;
+    const int64_t sa = ((chunk * units) / a.splits) * a.k_align;
+    const int64_t sb = (((chunk + 1) * units) / a.splits) * a.k_align;
     const int nsteps = (int)(sb - sa);
     const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
 
@@ -87,34 +101,36 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     }
     xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
 
-    // ---- weight copies: lane L moves the 16-byte piece (row L/2, half L%2) of every k-step of this warp's 64 columns ----
+    // ---- weight copies: lane L moves the 16-byte piece (row L/2, half L%2) of every k-step of this warp's 64 columns.
+    // Ring slot layout (512 B): piece (half, row) at ((half*2 + row/8)*8 + row%8)*16, i.e. four 8x16-byte matrices
+    // (rows 0-7 | 8-15) x (columns 0-31 | 32-63), each 128 contiguous bytes: what one ldmatrix.x4 wants. ----
     const int64_t pitch_b = a.w_ld32 * 4;
     const int crow = lane >> 1, chalf = lane & 1;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + (uint32_t)warp * (kDepth * kStepBytes);
-    const uint32_t cdst = ring + (uint32_t)(((crow & 1) + 2 * (crow >> 3)) * 128 + ((crow & 7) >> 1) * 32 + chalf * 16);
+    const uint32_t cdst = ring + (uint32_t)(((chalf * 2 + (crow >> 3)) * 8 + (crow & 7)) * 16);
     const bool c_ok = warp_col + chalf * 32 < a.n;
     const char* cptr = reinterpret_cast<const char*>(a.w) + (sa * 16 + crow) * pitch_b + (c_ok ? (warp_col + chalf * 32) / 2 : 0);
-    const uint32_t csize = c_ok ? 16u : 0u;  // 0: the piece is zero-filled, nothing is read
-    int issued = 0;
-    auto issue_pair = [&]() {
+    const int64_t step_b = 16 * pitch_b;
+    if (!c_ok) {  // columns past n (last strip only): this lane's pieces of every ring slot are zero and never copied into
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            if (issued < nsteps) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(cdst + (uint32_t)(issued & (kDepth - 1)) * kStepBytes),
-                             "l"(cptr), "r"(csize)
-                             : "memory");
-                cptr += 16 * pitch_b;
-            }
-            ++issued;
+        for (int sidx = 0; sidx < kDepth; ++sidx)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(cdst + (uint32_t)sidx * kStepBytes), "r"(0u) : "memory");
+    }
+    const int my_steps = c_ok ? nsteps : 0;
+    auto issue_pair = [&](int first_step, uint32_t dst) {  // steps first_step, first_step + 1 into ring bytes dst, dst + 512
+        if (first_step < my_steps) {  // ranges hold an even number of steps
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(cptr) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + kStepBytes), "l"(cptr + step_b) : "memory");
         }
+        cptr += 2 * step_b;
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    // ---- x[:, this run's k range] through shared memory in chunks of kFChunk steps ----
+    // ---- x[:, this run's k range] through shared memory, kFChunk steps at a time ----
     auto stage_x = [&](int chunk_idx) {
         const int64_t k_first = (sa + (int64_t)chunk_idx * kFChunk) * 16;
         const int64_t k_end = sb * 16;
-        uint16_t(*dst)[kFXPitch] = xs[chunk_idx & 1];
+        uint16_t(*dst)[kFXPitch] = xs;
         for (int e = tid; e < 16 * (kFChunk * 2); e += kThreads) {  // 16-byte pieces: 16 rows x (kFChunk*16/8)
             const int row = e / (kFChunk * 2), piece = e % (kFChunk * 2);
             const int64_t kk = k_first + piece * 8;
@@ -130,20 +146,17 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     };
     stage_x(0);
 #pragma unroll
-    for (int i = 0; i < kDepth / 2; ++i) issue_pair();
+    for (int i = 0; i < kDepth; i += 2) issue_pair(i, cdst + (uint32_t)i * kStepBytes);
 
-    // ---- group bookkeeping: scale/offset of the lane's 16 output columns (tile t, fragment column e&1 -> 8*(e&1)+t) ----
-    const int64_t scol = (warp_col + 16 * q < a.n) ? warp_col + 16 * q : 0;
+    // ---- scale/offset of the lane's 16 output columns: 8q..8q+7 of each 32-column half ----
+    const int64_t scol0 = (warp_col + 8 * q < a.n) ? warp_col + 8 * q : 0;
+    const int64_t scol1 = (warp_col + 32 + 8 * q < a.n) ? warp_col + 32 + 8 * q : 0;
     uint32_t raw_s[8], raw_o[8];
-    int64_t group = sa / a.steps_per_group - 1;
-    int first_skip = (int)(sa % a.steps_per_group);
-    int group_left = 0;
-    bool have_group = false;
     const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
 
     auto finish_group = [&]() {
 #pragma unroll
-        for (int idx = 0; idx < 16; ++idx) {
+        for (int idx = 0; idx < 16; ++idx) {  // idx = 8*half + 4*(e&1) + (t&3): position among the lane's 16 columns
             const uint32_t rs = raw_s[idx >> 1];
             const float sf = (idx & 1) ? F::hi(rs) : F::lo(rs);
             float of = -F::kB;
@@ -151,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
                 const uint32_t ro = raw_o[idx >> 1];
                 of += (idx & 1) ? F::hi(ro) : F::lo(ro);
             }
-            const int t = idx & 7, e0 = idx >> 3;  // fragment entries e0 (row g) and e0 + 2 (row g + 8)
+            const int t = (idx >> 3) * 4 + (idx & 3), e0 = (idx >> 2) & 1;  // fragment entries e0 (row g) and e0 + 2 (row g + 8)
             total[t][e0] = fmaf(sf, fmaf(of, xsum[0], part[t][e0]), total[t][e0]);
             total[t][e0 + 2] = fmaf(sf, fmaf(of, xsum[2], part[t][e0 + 2]), total[t][e0 + 2]);
         }
@@ -159,15 +172,15 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
         for (int t = 0; t < kTiles; ++t) part[t][0] = part[t][1] = part[t][2] = part[t][3] = 0.f;
         xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
     };
-    auto load_group = [&]() {
+    auto load_group = [&](int64_t group) {
         if (a.scale_sn != 0) {
-            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg + scol;
-            const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(sp)), s1 = __ldg(reinterpret_cast<const uint4*>(sp) + 1);
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+            const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(sp + scol0)), s1 = __ldg(reinterpret_cast<const uint4*>(sp + scol1));
             raw_s[0] = s0.x; raw_s[1] = s0.y; raw_s[2] = s0.z; raw_s[3] = s0.w;
             raw_s[4] = s1.x; raw_s[5] = s1.y; raw_s[6] = s1.z; raw_s[7] = s1.w;
             if (kHasOffset) {
-                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg + scol;
-                const uint4 o0 = __ldg(reinterpret_cast<const uint4*>(op)), o1 = __ldg(reinterpret_cast<const uint4*>(op) + 1);
+                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+                const uint4 o0 = __ldg(reinterpret_cast<const uint4*>(op + scol0)), o1 = __ldg(reinterpret_cast<const uint4*>(op + scol1));
                 raw_o[0] = o0.x; raw_o[1] = o0.y; raw_o[2] = o0.z; raw_o[3] = o0.w;
                 raw_o[4] = o1.x; raw_o[5] = o1.y; raw_o[6] = o1.z; raw_o[7] = o1.w;
             }
@@ -181,64 +194,77 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
             }
         }
     };
-
-    const uint32_t rd = ring + (uint32_t)(q * 32 + (g >> 2) * 16 + (g & 3) * 4);
-    for (int i = 0; i < nsteps; i += 2) {
-        // the copies of steps i, i+1 (and everything older, the x chunk included) have landed for this lane ...
-        asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
-        __syncwarp();  // ... and for the other lanes of the warp
-        if ((i & (kFChunk - 1)) == 0) {
-            __syncthreads();  // chunk boundary: every thread's pieces of this x chunk are visible; the other buffer is free
-            if (i + kFChunk < nsteps) stage_x(i / kFChunk + 1);
+    // one k-step: 4 registers of paired nibbles -> 16 B fragments (a shift and a logic op each) -> 8 MMAs + the row-sum MMA
+    auto compute = [&](const uint32_t(&w4)[4], const uint32_t(&af)[4]) {
+        uint32_t b0[kTiles], b1[kTiles];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(w4[0] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[t]) : "r"(w4[1] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[4 + t]) : "r"(w4[2] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[4 + t]) : "r"(w4[3] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
         }
-        const uint16_t* xrow0 = &xs[(i / kFChunk) & 1][g][2 * q];
-        const uint16_t* xrow1 = &xs[(i / kFChunk) & 1][g + 8][2 * q];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int s = i + j;
-            if (s >= nsteps) break;
-            if (group_left == 0) {
-                if (have_group) finish_group();
-                ++group;
-                group_left = spg - first_skip;
-                first_skip = 0;
-                load_group();
-                have_group = true;
-            }
-            --group_left;
+        for (int t = 0; t < kTiles; ++t) N::mma_free(part[t], af, b0[t], b1[t]);
+        N::mma_free(xsum, af, F::kOnes, F::kOnes);
+    };
 
-            const uint32_t slot = rd + (uint32_t)(s & (kDepth - 1)) * kStepBytes;
-            const uint32_t wa = lds32(slot), wb = lds32(slot + 128), wc = lds32(slot + 256), wd = lds32(slot + 384);
-            uint32_t af[4];
-            {
-                const int ls = (s & (kFChunk - 1)) * 16;
-                af[0] = *reinterpret_cast<const uint32_t*>(xrow0 + ls);
-                af[1] = *reinterpret_cast<const uint32_t*>(xrow1 + ls);
-                af[2] = *reinterpret_cast<const uint32_t*>(xrow0 + ls + 8);
-                af[3] = *reinterpret_cast<const uint32_t*>(xrow1 + ls + 8);
+    // per-lane ldmatrix row addresses: weights: matrix l/8, row l%8 = byte l*16 of the slot; x: rows (l%8) + 8*((l/8)&1),
+    // k offset 8*(l/16)
+    const uint32_t wlane = ring + (uint32_t)lane * 16;
+    const uint32_t xlane = (uint32_t)__cvta_generic_to_shared(&xs[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
+
+    // Commit groups so far, oldest first: X0, G0..G(kDepth/2-1); from here on every pair p adds G(p + kDepth/2). A wait
+    // for pair p's copies may therefore leave the kDepth/2 - 1 groups behind it in flight.
+    asm volatile("cp.async.wait_group %0;" ::"n"(kDepth / 2 - 1) : "memory");  // X0 and G0
+    __syncwarp();
+    __syncthreads();
+    uint32_t w0[4], a0[4], w1[4], a1[4];
+    ldsm_x4_trans(wlane, w0);
+    ldsm_x4(xlane, a0);
+
+    int i = 0;                      // k-step relative to sa, even
+    int x_left = kFChunk;           // steps left in the staged x chunk, counting step i
+    uint32_t roff = 0;              // ring byte offset of step i
+    uint32_t xcur = xlane;          // x fragment address of step i
+    int64_t group = sa / spg;
+    int seg_end = (int)min((int64_t)nsteps, (group + 1) * (int64_t)spg - sa);
+    while (i < nsteps) {
+        load_group(group);
+        for (; i < seg_end; i += 2) {
+            ldsm_x4_trans(wlane + roff + kStepBytes, w1);
+            ldsm_x4(xcur + 32, a1);
+            compute(w0, a0);
+            // the copies of the next pair (and everything older) have landed, for this lane and the others of the warp
+            asm volatile("cp.async.wait_group %0;" ::"n"(kDepth / 2 - 2) : "memory");
+            __syncwarp();
+            x_left -= 2;
+            xcur += 64;
+            if (x_left == 0 && i + 2 < nsteps) {
+                // the staged x is used up (k ranges longer than kFChunk steps only): everyone finishes reading it, the
+                // next piece is copied in, and the copies in flight are drained once
+                __syncthreads();
+                stage_x((i + 2) / kFChunk);
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncthreads();
+                x_left = kFChunk;
+                xcur = xlane;
             }
-            // low half: nibbles 0..3 of row a | nibbles 0..3 of row b; high half: nibbles 4..7
-            const uint32_t lo01 = prmt(wa, wb, 0x5410u), hi01 = prmt(wa, wb, 0x7632u);
-            const uint32_t lo23 = prmt(wc, wd, 0x5410u), hi23 = prmt(wc, wd, 0x7632u);
-            uint32_t b0[kTiles], b1[kTiles];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(lo01 >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[t]) : "r"(lo23 >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[4 + t]) : "r"(hi01 >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[4 + t]) : "r"(hi23 >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-            }
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) N::mma(part[t], af, b0[t], b1[t]);
-            N::mma(xsum, af, F::kOnes, F::kOnes);
+            const uint32_t roff_next = (roff + 2 * kStepBytes == kDepth * kStepBytes) ? 0u : roff + 2 * kStepBytes;
+            ldsm_x4_trans(wlane + roff_next, w0);  // stale bytes past the end of the range are loaded and never used
+            ldsm_x4(xcur, a0);
+            compute(w1, a1);
+            __syncwarp();  // every lane has read steps i, i+1: their ring slots may be overwritten
+            issue_pair(i + kDepth, cdst + roff);
+            roff = roff_next;
         }
-        __syncwarp();  // every lane has read steps i, i+1: their ring slots may be overwritten
-        issue_pair();
+        finish_group();
+        ++group;
+        seg_end = min(nsteps, seg_end + spg);
     }
-    if (have_group) finish_group();
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    combine_and_store<kBf16>(a, total, c, strip, warp, lane, tid, &s_reduce);
+    combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
 }
 
 int g_fast_ctas_per_sm[4] = {0, 0, 0, 0};
@@ -274,6 +300,7 @@ bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p)
     if (p->n % 32 != 0 || p->w_ld % 32 != 0) return false;                // 16-byte pieces of 32 columns, 16-byte aligned rows
     if ((reinterpret_cast<uintptr_t>(p->w) % 16) != 0) return false;
     if (p->scale_sn == 1 && (p->scale_sg % 8 != 0)) return false;
+    if (p->k % 32 != 0 || (p->group_size != 0 && p->group_size % 32 != 0)) return false;  // step pairs never straddle a group
     return true;
 }
 
@@ -314,6 +341,10 @@ int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     }
     if (splits > a.ksteps) splits = a.ksteps;
     if (splits * a.strips > kFastMaxGrid) splits = kFastMaxGrid / a.strips;
+    if (splits < 1) splits = 1;
+    // k ranges of whole groups when every split gets at least two of them, else of step pairs
+    a.k_align = (a.ksteps % a.steps_per_group == 0 && a.ksteps / a.steps_per_group >= 2 * splits) ? a.steps_per_group : 2;
+    if (splits > a.ksteps / a.k_align) splits = a.ksteps / a.k_align;
     if (splits < 1) splits = 1;
     a.splits = splits;
     const int64_t grid64 = a.strips * splits;
