@@ -201,6 +201,11 @@ QMM_WORKLOADS = {
     "c3i8": (1, 4096, 7168, 18432, "int8_kc"),
     "c1t": (1, 128, 4096, 4096, "int8_kc_t"),      # same with x2 stored (n,k) and transposeX2 = true
     "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
+    "c4": (8, 8192, 8192, 8192, "mxfp4"),           # both operands e2m1 + e8m0/32, x2 stored (n,k) with transposeX2 = true
+    "c4s": (2, 4096, 4096, 4096, "mxfp4"),          # small form of c4 (profiling)
+    "c5": (32, 2048, 4096, 14336, "mxfp8_dq"),      # bf16 activations -> dynamic mx quant -> mxfp8 matmul + fp32 bias
+    "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
+    "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
 }
 
 
@@ -215,7 +220,47 @@ def run_qmm_workload(args):
     gen = torch.Generator(device=dev).manual_seed(1001)
     sets = max(2, min(8, int(300e6 // (k * n)) + 1))  # rotate weights so they do not sit in L2
     out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    if kind.startswith("int8_kc"):
+    if kind.startswith("mx"):
+        # batched mx workloads: the operands (>= 270 MB per call) exceed L2 by themselves, one weight set
+        sets = 1
+        f4 = kind == "mxfp4"
+        kq = k // 64
+        out = torch.empty((b, m, n), dtype=torch.bfloat16, device=dev)
+        rnd_scale = lambda *shape: torch.randint(124, 131, shape, generator=gen, device=dev, dtype=torch.uint8)  # noqa: E731
+        if f4:
+            x1 = torch.randint(0, 256, (b, m, k // 2), generator=gen, device=dev, dtype=torch.uint8)  # two e2m1 per byte
+            x2 = torch.randint(0, 256, (b, n, k // 2), generator=gen, device=dev, dtype=torch.uint8)
+            d_x1 = aclnn.from_torch(x1, "float4_e2m1", (b, m, k), (m * k, k, 1))
+            d_x2 = aclnn.from_torch(x2, "float4_e2m1", (b, n, k), (n * k, k, 1))  # stored (n,k): transposeX2 = true
+            s1, s2 = rnd_scale(b, m, kq, 2), rnd_scale(b, n, kq, 2)
+            d_s1 = aclnn.from_torch(s1, "float8_e8m0")
+            d_s2 = aclnn.from_torch(s2, "float8_e8m0")
+            dout = aclnn.from_torch(out)
+            call = lambda i: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, None, False, True, (1 << 32) | (1 << 16) | 32)  # noqa: E731
+            nbytes = b * (m * k // 2 + n * k // 2 + (m + n) * kq * 2 + 2 * m * n)
+        else:
+            x2 = torch.randn((b, k, n), generator=gen, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+            s2 = rnd_scale(b, kq, n, 2)
+            bias = torch.randn((n,), generator=gen, device=dev, dtype=torch.float32)
+            x1q = torch.empty((b, m, k), dtype=torch.uint8, device=dev)
+            s1 = torch.empty((b, m, kq, 2), dtype=torch.uint8, device=dev)
+            d_x1 = aclnn.from_torch(x1q, "float8_e4m3fn")
+            d_s1 = aclnn.from_torch(s1, "float8_e8m0")
+            d_x2, d_s2, d_bias, dout = aclnn.from_torch(x2), aclnn.from_torch(s2, "float8_e8m0"), aclnn.from_torch(bias), aclnn.from_torch(out)
+            act = torch.randn((b, m, k), generator=gen, device=dev, dtype=torch.bfloat16)
+            act.view(-1)[torch.randint(0, act.numel(), (act.numel() // 1000,), generator=gen, device=dev)] *= 50  # 0.1 % outliers
+            d_act = aclnn.from_torch(act)
+            aclnn.dynamic_mx_quant(d_act, d_x1, d_s1, "float8_e4m3fn")
+            mm = lambda: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, d_bias, False, False, (1 << 32) | (1 << 16) | 32)  # noqa: E731
+            if kind == "mxfp8_dq":
+                def call(i):
+                    aclnn.dynamic_mx_quant(d_act, d_x1, d_s1, "float8_e4m3fn")
+                    mm()
+                nbytes = b * (2 * m * k + m * k + k * n + (m + n) * kq * 2 + 2 * m * n)
+            else:
+                call = lambda i: mm()  # noqa: E731
+                nbytes = b * (m * k + k * n + (m + n) * kq * 2 + 2 * m * n)
+    elif kind.startswith("int8_kc"):
         tb = kind.endswith("_t")
         x1 = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
         x2s = [torch.randint(-127, 128, (n, k) if tb else (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
@@ -256,10 +301,10 @@ def run_qmm_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 4500.0
+    peak8 = 9000.0 if kind == "mxfp4" else 4500.0
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
-                      "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_8bit_peak": tf / peak8,
+                      "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,
                       "hbm_gbs_on_algorithmic_bytes": nbytes / (ms * 1e-3) / 1e9, "clocks": clocks, "weight_sets": sets}))
 
 

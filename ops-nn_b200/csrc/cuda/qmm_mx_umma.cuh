@@ -1,0 +1,398 @@
+// Block-scaled (MX) quant matmul on tcgen05: e8m0 scale per 32 k on both operands, applied by the tensor core.
+// Included by qmm_umma.cu (same translation unit: shares the tensor-map helpers, the status word and the row store).
+//
+// Replaces the reference's MX kernel (matmul/common/cmct/kernel/kernel_qbmm_mx.h:137-361, block/block_mmad_mx.h:396-881;
+// golden quant_batch_matmul_v3/tests/assets/qbmmv3_kernel_golden.py:153-234): out = (x1 * 2^e1) @ (x2 * 2^e2) + bias, fp32
+// accumulate. MXFP8 uses kind::mxf8f6f4 (k = 32 per MMA, one scale byte per row per MMA), MXFP4 uses kind::mxf4 with
+// scale_vec::2X (k = 64 per MMA, two scale bytes per row per MMA); fp4 operands must be k-contiguous (the instruction has
+// no MN-major form for 4-bit data).
+//
+// Scale factors. The tensor core wants them in TMEM, 128 rows x 4 k-blocks as "32 lanes x 16 bytes": byte
+// (row % 32) * 16 + (row / 32) * 4 + kblock. The reference keeps them as (rows, ceil(k/64), 2) or (ceil(k/64), rows, 2)
+// e8m0 matrices, so a small pre-pass kernel rewrites both operands' scales into that 512-byte atom order in workspace,
+// [batch][row tile][k stage][atom]; the producer then fetches a stage's atoms with one untiled bulk copy per operand next to
+// the two TMA loads, and the MMA warp moves them shared -> TMEM with tcgen05.cp right before the stage's MMAs (tcgen05
+// operations of one thread execute in issue order, so one TMEM slot per operand is enough).
+namespace {
+
+constexpr int kMxBN = 128;
+constexpr uint32_t kMxSfaCol = 2 * kMxBN;  // TMEM columns: two accumulators, then the scale slots
+
+// One thread per 32-bit word of the atoms: rows (tile*128 + word%4... see index math), four consecutive k-blocks.
+__global__ void mx_sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows, int64_t kblocks,
+                                      int64_t kq, int transposed_layout, int64_t tiles, int64_t stages, int atoms, int64_t batch,
+                                      int64_t src_bs)
+{
+    const int64_t words = batch * tiles * stages * atoms * 128;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < words; w += (int64_t)gridDim.x * blockDim.x) {
+        const int l = (int)(w & 31), m1 = (int)((w >> 5) & 3);
+        int64_t r = w >> 7;
+        const int at = (int)(r % atoms); r /= atoms;
+        const int64_t st = r % stages; r /= stages;
+        const int64_t tile = r % tiles;
+        const int64_t b = r / tiles;
+        const int64_t row = tile * 128 + m1 * 32 + l;
+        const int64_t kb0 = (st * atoms + at) * 4;
+        const uint8_t* s = src + b * src_bs;
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t kb = kb0 + j;
+            uint32_t v = 127u;  // 2^0 for rows / k-blocks that do not exist (their data is zero-filled)
+            if (row < rows && kb < kblocks)
+                v = transposed_layout ? s[((kb >> 1) * rows + row) * 2 + (kb & 1)] : s[row * (2 * kq) + kb];
+            word |= v << (8 * j);
+        }
+        // destination: atom base + (row % 32) * 16 + (row / 32 % 4) * 4
+        const int64_t atom_idx = ((b * tiles + tile) * stages + st) * atoms + at;
+        *reinterpret_cast<uint32_t*>(dst + atom_idx * 512 + l * 16 + m1 * 4) = word;
+    }
+}
+
+template <bool kF4>
+__global__ void __launch_bounds__(192, 1)
+qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
+{
+    constexpr int BN = kMxBN, EW = 4;
+    constexpr int kAtoms = kF4 ? 2 : 1;  // scale atoms per operand per stage: a stage is 128 bytes of k = 4 (fp8) / 8 (fp4) k-blocks
+    constexpr uint32_t kSfBytes = kAtoms * 512;
+    constexpr uint32_t kBTile = BN * BK;
+    constexpr uint32_t kStage = kATile + kBTile + 2 * kSfBytes;
+    constexpr uint32_t kSfbCol = kMxSfaCol + 4 * kAtoms;
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)a.stages * kStage);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + a.stages;
+    uint64_t* tfull = bars + 2 * a.stages;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile uint32_t* abort_flag = tmem_ptr + 1;
+    float* s_bias = reinterpret_cast<float*>(tmem_ptr + 4);  // [BN]
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&tfull[b], 1);
+            ptx::mbar_init(&tempty[b], EW * 32);
+        }
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == EW + 1) ptx::tmem_alloc(tmem_ptr, kTmemCols);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    const uint32_t tiles_per_batch = (uint32_t)a.tiles_m * (uint32_t)a.tiles_n;
+    const uint32_t ntiles = (uint32_t)a.num_tiles;
+    const uint32_t smem0 = ptx::smem_u32(smem), full0 = ptx::smem_u32(full), empty0 = ptx::smem_u32(empty);
+    const uint32_t stages = (uint32_t)a.stages;
+    const int kstages = a.kblocks;  // 128-byte k stages per tile
+
+    if (warp == EW) {
+        // ======================= producer: two TMA loads and two scale-atom bulk copies per stage =======================
+        if (lane == 0) {
+            ptx::tma_prefetch_desc(&map_a);
+            ptx::tma_prefetch_desc(&map_b);
+        }
+        __syncwarp();
+        uint32_t s = 0, par = 0;
+        bool ok = true;
+        const bool b_mn = a.b_mn_major != 0, a_mn = a.a_mn_major != 0;
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const uint32_t tm = r % (uint32_t)a.tiles_m, tn = r / (uint32_t)a.tiles_m;
+            const int32_t m0 = (int32_t)tm * BM, n0 = (int32_t)tn * BN;
+            const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
+            const uint8_t* sfa = a.sfa + (int64_t)ba * a.sfa_bs + ((int64_t)tm * kstages) * kSfBytes;
+            const uint8_t* sfb = a.sfb + (int64_t)bb * a.sfb_bs + ((int64_t)tn * kstages) * kSfBytes;
+            int32_t kk = 0;
+            for (int kb = 0; kb < kstages; ++kb) {
+                if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
+                    report(abort_flag, (1u << 8) | 1u);
+                    ok = false;
+                    break;
+                }
+                if (ptx::elect_one()) {
+                    const uint32_t fb = full0 + 8u * s, sa = smem0 + s * kStage, sb = sa + (uint32_t)kATile;
+                    ptx::mbar_expect_tx_a(fb, kStage);
+                    ptx::tma_load_3d_a(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
+                    ptx::tma_load_3d_a(sb, &map_b, fb, b_mn ? n0 : kk, b_mn ? kk : n0, bb);
+                    ptx::bulk_load_a(sb + kBTile, sfa, kSfBytes, fb);
+                    ptx::bulk_load_a(sb + kBTile + kSfBytes, sfb, kSfBytes, fb);
+                }
+                __syncwarp();
+                sfa += kSfBytes;
+                sfb += kSfBytes;
+                kk += BK;
+                if (++s == stages) {
+                    s = 0;
+                    par ^= 1u;
+                }
+            }
+        }
+    } else if (warp == EW + 1) {
+        // ======================= MMA issuer =======================
+        uint32_t s = 0, par = 0, grp = 0;
+        bool ok = true;
+        const uint32_t tfull0 = ptx::smem_u32(tfull), tempty0 = ptx::smem_u32(tempty);
+        const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
+        const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
+                                          : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+        const uint64_t dsf0 = ptx::make_smem_desc(smem0 + kATile + kBTile, 0, 128, 0);  // 32 rows x 16 bytes, no swizzle
+        const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0, sf_lo = (uint32_t)dsf0;
+        const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull, sf_hi = dsf0 & 0xFFFFFFFF00000000ull;
+        const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 256u : 2u;
+        const uint32_t idesc = a.idesc;
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            uint32_t acc = 0u;
+            if (!ptx::mbar_wait_a(tempty0 + 8u * (grp & 1u), ((grp >> 1) & 1u) ^ 1u, abort_flag)) {
+                report(abort_flag, (2u << 8) | 1u);
+                ok = false;
+                break;
+            }
+            for (int kb = 0; kb < kstages; ++kb) {
+                if (!ptx::mbar_wait_a(full0 + 8u * s, par, abort_flag)) {
+                    report(abort_flag, (2u << 8) | 2u);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                if (ptx::elect_one()) {
+                    const uint32_t stage_off = (s * kStage) >> 4;
+                    const uint32_t d = tmem_base + (grp & 1u) * BN;
+                    const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off, sl = sf_lo + stage_off;
+#pragma unroll
+                    for (int at = 0; at < kAtoms; ++at) {
+                        ptx::tmem_cp_sf(tmem_base + kMxSfaCol + 4 * at, sf_hi | (uint64_t)(sl + at * 32));
+                        ptx::tmem_cp_sf(tmem_base + kSfbCol + 4 * at, sf_hi | (uint64_t)(sl + (kAtoms + at) * 32));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t sf_id = kF4 ? (uint32_t)(k & 1) * 2u : (uint32_t)k;
+                        const uint32_t col = kF4 ? 4u * (uint32_t)(k >> 1) : 0u;
+                        const uint32_t id = idesc | (sf_id << 29) | (sf_id << 4);
+                        const uint64_t da = a_hi | (uint64_t)(al + k * a_k1), db = b_hi | (uint64_t)(bl + k * b_k1);
+                        if (kF4) ptx::umma_mxf4(d, da, db, id, tmem_base + kMxSfaCol + col, tmem_base + kSfbCol + col, k == 0 ? acc : 1u);
+                        else ptx::umma_mxf8f6f4(d, da, db, id, tmem_base + kMxSfaCol, tmem_base + kSfbCol, k == 0 ? acc : 1u);
+                    }
+                    ptx::umma_commit_a(empty0 + 8u * s);
+                }
+                __syncwarp();
+                acc = 1u;
+                if (++s == stages) {
+                    s = 0;
+                    par ^= 1u;
+                }
+            }
+            if (ok) {
+                if (ptx::elect_one()) ptx::umma_commit_a(tfull0 + 8u * (grp & 1u));
+                __syncwarp();
+                ++grp;
+            }
+        }
+    } else {
+        // ======================= epilogue warps: acc (+ bias) -> output dtype =======================
+        const int quad = warp & 3;
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        uint32_t grp = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            const int64_t row = m0 + quad * 32 + lane;
+            const bool row_ok = row < a.m;
+            const int out_bytes = a.out_dtype == ACL_FLOAT ? 4 : 2;
+            uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + b * a.out_bs * out_bytes;
+            const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
+            const uint8_t* bias = reinterpret_cast<const uint8_t*>(a.bias);
+            if (bias != nullptr) bias += b * a.bias_bs * (a.bias_dtype == ACL_FLOAT ? 4 : 2);
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers of s_bias are done
+            for (int c = threadIdx.x; c < BN; c += 128)
+                s_bias[c] = bias != nullptr ? load_as_float(bias, min(n0 + c, a.n - 1), a.bias_dtype) : 0.f;
+            if (!ptx::mbar_wait_relaxed(&tfull[buf], gpar, abort_flag)) report(abort_flag, (3u << 8) | 1u);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*abort_flag != 0u) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + c, v);
+                ptx::tmem_ld_wait();
+                const int64_t col = n0 + c;
+                const int valid = (int)min((int64_t)32, a.n - col);
+                if (row_ok && valid > 0) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(s_bias + c + i);
+                        f[i] = __fadd_rn(__uint_as_float(v[i]), b4.x);
+                        f[i + 1] = __fadd_rn(__uint_as_float(v[i + 1]), b4.y);
+                        f[i + 2] = __fadd_rn(__uint_as_float(v[i + 2]), b4.z);
+                        f[i + 3] = __fadd_rn(__uint_as_float(v[i + 3]), b4.w);
+                    }
+                    store_row32(a, out, row, col, f, valid);
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&tempty[buf]);
+            ++grp;
+        }
+    }
+    if (*abort_flag != 0u) __nanosleep(200000);  // lets copies that are still in flight land before the CTA leaves
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == EW + 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+bool is_fp4(int dt) { return dt == ACL_FLOAT4_E2M1; }
+
+struct MxPlan {
+    bool f4;
+    int atoms;
+    int64_t tiles_m, tiles_n, kstages, kblocks32, kq;
+    uint64_t sfa_bytes_per_batch, sfb_bytes_per_batch, nb_a, nb_b;
+};
+
+MxPlan mx_plan(const OpsnnQmmParams* p)
+{
+    MxPlan q{};
+    q.f4 = is_fp4(p->a_dtype);
+    q.atoms = q.f4 ? 2 : 1;
+    const int64_t k_per_stage = q.f4 ? 256 : 128;
+    q.tiles_m = (p->m + BM - 1) / BM;
+    q.tiles_n = (p->n + kMxBN - 1) / kMxBN;
+    q.kstages = (p->k + k_per_stage - 1) / k_per_stage;
+    q.kblocks32 = (p->k + 31) / 32;
+    q.kq = (p->k + 63) / 64;
+    q.nb_a = p->sa_bs != 0 ? (uint64_t)p->batch : 1;
+    q.nb_b = p->sb_bs != 0 ? (uint64_t)p->batch : 1;
+    q.sfa_bytes_per_batch = (uint64_t)q.tiles_m * q.kstages * q.atoms * 512;
+    q.sfb_bytes_per_batch = (uint64_t)q.tiles_n * q.kstages * q.atoms * 512;
+    return q;
+}
+
+}  // namespace
+
+bool qmm_mx_umma_eligible(const OpsnnQmmParams* p)
+{
+    if (p->mode != OPSNN_QMM_MX) return false;
+    const bool f8 = is_fp8(p->a_dtype) && is_fp8(p->b_dtype);
+    const bool f4 = is_fp4(p->a_dtype) && is_fp4(p->b_dtype);
+    if (!f8 && !f4) return false;
+    if (p->scale_b_dtype != ACL_FLOAT8_E8M0 || p->scale_a == nullptr || p->scale_b == nullptr) return false;
+    if (p->group_k != 32 || p->k % 32 != 0) return false;
+    if (f4 && (p->trans_a != 0 || p->trans_b == 0)) return false;  // 4-bit operands must be k-contiguous
+    if (p->out_dtype != ACL_BF16 && p->out_dtype != ACL_FLOAT16 && p->out_dtype != ACL_FLOAT) return false;
+    if (p->bias != nullptr && p->bias_dtype != ACL_FLOAT && p->bias_dtype != ACL_BF16 && p->bias_dtype != ACL_FLOAT16) return false;
+    const int64_t div = f4 ? 2 : 1;  // elements per byte
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al16(p->a) || !al16(p->b)) return false;
+    if ((p->a_ld / div) % 16 != 0 || (p->b_ld / div) % 16 != 0 || (p->a_bs / div) % 16 != 0 || (p->b_bs / div) % 16 != 0) return false;
+    if (f4 && (p->a_ld % 2 != 0 || p->b_ld % 2 != 0 || p->a_bs % 2 != 0 || p->b_bs % 2 != 0)) return false;
+    if (p->m < 1 || p->n < 1 || p->k < 1 || p->batch < 1 || p->batch > 0x7FFFFFFF) return false;
+    if (p->batch * ((p->m + 127) / 128) * ((p->n + 127) / 128) > 0x7FFFFFFF) return false;
+    if (p->m > 0x7FFFFF00 || p->n > 0x7FFFFF00 || p->k > 0x7FFFFF00) return false;
+    return true;
+}
+
+uint64_t qmm_mx_umma_workspace_size(const OpsnnQmmParams* p)
+{
+    const MxPlan q = mx_plan(p);
+    return q.nb_a * q.sfa_bytes_per_batch + q.nb_b * q.sfb_bytes_per_batch + 256;
+}
+
+int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
+{
+    const MxPlan q = mx_plan(p);
+    if (p->workspace == nullptr || p->workspace_size < qmm_mx_umma_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+    uint8_t* sfa = ws;
+    uint8_t* sfb = ws + q.nb_a * q.sfa_bytes_per_batch;
+    // ---- pre-pass: both operands' scales into atom order ----
+    {
+        const int64_t wa = (int64_t)q.nb_a * q.tiles_m * q.kstages * q.atoms * 128;
+        const int64_t wb = (int64_t)q.nb_b * q.tiles_n * q.kstages * q.atoms * 128;
+        const int threads = 256;
+        const auto blocks = [&](int64_t w) { return (unsigned)std::min<int64_t>((w + threads - 1) / threads, 148 * 16); };
+        // x1Scale is (m, kq, 2), or (kq, m, 2) when x1 is stored (k,m); x2Scale is (kq, n, 2), or (n, kq, 2) when x2 is stored (n,k)
+        mx_sf_relayout_kernel<<<blocks(wa), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32, q.kq,
+                                                                  p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs);
+        mx_sf_relayout_kernel<<<blocks(wb), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32, q.kq,
+                                                                  p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, (int64_t)q.nb_b, p->sb_bs);
+        note_launch("mx_sf_relayout", 2);
+    }
+    UmmaArgs a{};
+    a.mode = p->mode;
+    a.a_mn_major = p->trans_a ? 1 : 0;
+    a.b_mn_major = p->trans_b ? 0 : 1;
+    a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
+    a.tiles_m = (int32_t)q.tiles_m;
+    a.tiles_n = (int32_t)q.tiles_n;
+    a.kblocks = (int32_t)q.kstages;
+    a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
+    a.a_batched = p->a_bs != 0;
+    a.b_batched = p->b_bs != 0;
+    a.out_dtype = p->out_dtype; a.bias_dtype = p->bias_dtype;
+    a.bias = p->bias; a.bias_bs = p->bias_bs; a.out = p->out; a.out_ld = p->out_ld; a.out_bs = p->out_bs;
+    a.sfa = sfa; a.sfb = sfb;
+    a.sfa_bs = q.nb_a > 1 ? (int64_t)q.sfa_bytes_per_batch : 0;
+    a.sfb_bs = q.nb_b > 1 ? (int64_t)q.sfb_bytes_per_batch : 0;
+    const uint32_t fa = q.f4 ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
+    const uint32_t fb = q.f4 ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
+    a.idesc = make_idesc_block_scaled(fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, kMxBN);
+
+    const uint64_t div = q.f4 ? 2 : 1;
+    CUtensorMap ma, mb;
+    const uint64_t nb_a = a.a_batched ? (uint64_t)p->batch : 1, nb_b = a.b_batched ? (uint64_t)p->batch : 1;
+    bool ok;
+    if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
+    else ok = make_map(&ma, p->a, (uint64_t)p->k / div, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld / div, (uint64_t)p->a_bs / div, 128);
+    if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k / div, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld / div, (uint64_t)p->b_bs / div, kMxBN);
+    if (!ok) return (int32_t)cudaErrorInvalidValue;
+
+    const uint32_t stage = (uint32_t)(kATile + kMxBN * BK + 2 * q.atoms * 512);
+    int stages = (227 * 1024 - 2048) / (int)stage;
+    if (stages > 8) stages = 8;
+    if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * stage + 1024 + 256 + kMxBN * 4;
+    const int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
+    cudaError_t rc;
+    if (q.f4) {
+        static bool configured = false;
+        if (!configured) {
+            rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (rc != cudaSuccess) return (int32_t)rc;
+            configured = true;
+        }
+        qmm_mx_umma_kernel<true><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
+        note_launch("qmm_umma_mxfp4");
+    } else {
+        static bool configured = false;
+        if (!configured) {
+            rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (rc != cudaSuccess) return (int32_t)rc;
+            configured = true;
+        }
+        qmm_mx_umma_kernel<false><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
+        note_launch("qmm_umma_mxfp8");
+    }
+    return (int32_t)cudaGetLastError();
+}

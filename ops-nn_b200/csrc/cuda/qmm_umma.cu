@@ -25,6 +25,7 @@
 // Every mbarrier wait is bounded; a wait that gives up raises a CTA-wide abort flag, records the failure in a device
 // status word (opsnn_qmm_umma_status) and the CTA tears down normally (TMEM freed).
 #include <cstdio>
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -55,6 +56,10 @@ struct UmmaArgs {
     int64_t bias_bs;
     void* out;
     int64_t out_ld, out_bs;
+    // block-scaled (MX) kernel only: scale-factor atoms in workspace (see qmm_mx_umma.cuh)
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    int64_t sfa_bs, sfb_bs;  // bytes between batches; 0 broadcasts
 };
 
 __device__ unsigned int g_umma_status = 0;
@@ -544,9 +549,12 @@ int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs
 
 }  // namespace
 
+#include "qmm_mx_umma.cuh"
+
 bool qmm_umma_eligible(const OpsnnQmmParams* p)
 {
     if (getenv("OPSNN_QMM_NO_UMMA")) return false;
+    if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_eligible(p);
     const bool i8 = p->a_dtype == ACL_INT8 && p->b_dtype == ACL_INT8;
     const bool f8 = is_fp8(p->a_dtype) && is_fp8(p->b_dtype);
     if (p->mode == OPSNN_QMM_DEQ) {
@@ -569,10 +577,11 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
     return true;
 }
 
-uint64_t qmm_umma_workspace_size(const OpsnnQmmParams*) { return 0; }
+uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p) { return p->mode == OPSNN_QMM_MX ? qmm_mx_umma_workspace_size(p) : 0; }
 
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
+    if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
     const int bn = pick_bn(p);
     UmmaArgs a{};
     a.mode = p->mode;

@@ -104,6 +104,13 @@ __device__ __forceinline__ void tma_load_3d_a(uint32_t smem_dst, const CUtensorM
         "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completing on an mbarrier.
+__device__ __forceinline__ void bulk_load_a(uint32_t smem_dst, const void* src, uint32_t bytes, uint32_t bar_addr)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst), "l"(src),
+                 "r"(bytes), "r"(bar_addr)
+                 : "memory");
+}
 __device__ __forceinline__ void umma_commit_a(uint32_t bar_addr)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");

@@ -1,0 +1,120 @@
+"""GPU parity of the block-scaled (MX) tcgen05 kernels against the oracle restatement of the reference golden
+(quant_batch_matmul_v3/tests/assets/qbmmv3_kernel_golden.py:153-234): MXFP8 via kind::mxf8f6f4, MXFP4 via kind::mxf4.
+
+Every product e4m3*e4m3*2^e (or e2m1*e2m1*2^e) is exact in fp32 and the sums here stay far below 2^24 ulps of cancellation,
+so the only differences from the golden are fp32 summation order; the stated tolerance (max relative error <= 1e-2 for
+bf16, 5e-3 for fp16/fp32, against the fp32 dequantised product) is asserted, and in fact a much tighter one holds."""
+import ml_dtypes
+import numpy as np
+import pytest
+
+from conftest import load_golden
+from oracle import qbmm_oracle
+
+pytestmark = pytest.mark.gpu
+
+E4M3, E5M2, E2M1, E8M0 = ml_dtypes.float8_e4m3fn, ml_dtypes.float8_e5m2, ml_dtypes.float4_e2m1fn, ml_dtypes.float8_e8m0fnu
+GROUP_MX = (1 << 32) | (1 << 16) | 32
+
+
+def _e8m0(rng, shape, lo=-3, hi=3):
+    return np.exp2(rng.integers(lo, hi + 1, shape).astype(np.float32)).astype(E8M0)
+
+
+def _q(rng, shape, dt):
+    return (rng.standard_normal(shape).astype(np.float32) * (2.0 if dt == E2M1 else 1.0)).astype(dt)
+
+
+def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel):
+    import torch
+
+    from gpu_util import desc, out_tensor, out_to_np
+
+    m = x1.shape[-1] if t1 else x1.shape[-2]
+    n = x2.shape[-2] if t2 else x2.shape[-1]
+    batch = tuple(x1.shape[:-2])
+    out = out_tensor(batch + (m, n), out_name)
+    aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
+                          aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), t1, t2, GROUP_MX)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == expect_kernel, aclnn.last_kernel_name()
+    assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
+    return out_to_np(out)
+
+
+def _oracle(x1, x2, s1, s2, bias, t1, t2, out_name):
+    if x1.ndim == 2:
+        return qbmm_oracle.compute_mx(x1, x2, s1, s2, bias, t1, t2, out_name)
+    return np.stack([qbmm_oracle.compute_mx(x1[i], x2[i], s1[i], s2[i], bias, t1, t2, out_name) for i in range(x1.shape[0])])
+
+
+def _check(got, want, out_name):
+    g, w = np.asarray(got).astype(np.float64), np.asarray(want).astype(np.float64)
+    assert not np.any(g == -7777.0)
+    rms = np.sqrt(np.mean(w ** 2))
+    rel = np.max(np.abs(g - w) / np.maximum(np.abs(w), 1e-3 * rms))
+    assert rel <= (1e-2 if out_name == "bfloat16" else 5e-3), rel
+    # summation order only: about one output ulp for the 16-bit outputs, a few dozen fp32 ulps (cancellation) for fp32
+    tight = {"bfloat16": 2.1 * 2.0 ** -8, "float16": 2.1 * 2.0 ** -11, "float32": 2e-5}[out_name]
+    assert np.max(np.abs(g - w) / np.maximum(np.abs(w), 0.05 * rms)) <= tight
+
+
+MX8_CASES = [
+    # batch, m, k, n, t1, t2, a dtype, b dtype, bias, out
+    ((), 128, 128, 128, False, True, E4M3, E4M3, None, "float32"),
+    ((), 128, 512, 128, False, False, E4M3, E4M3, None, "float32"),           # mn-major B
+    ((), 200, 640, 328, False, True, E4M3, E5M2, "f32", "bfloat16"),         # tails in m, n; k not a multiple of 128
+    ((), 200, 608, 336, False, False, E5M2, E4M3, "f32", "bfloat16"),        # k = 19 blocks of 32 (odd), mn-major B
+    ((), 144, 384, 208, True, True, E4M3, E4M3, None, "float16"),            # mn-major A
+    ((3,), 130, 256, 272, False, False, E4M3, E4M3, "f32", "bfloat16"),      # batched
+    ((), 1024, 2048, 1536, False, False, E4M3, E4M3, "f32", "bfloat16"),     # many tiles per CTA, deep k
+]
+
+
+@pytest.mark.parametrize("case", MX8_CASES, ids=[str(c[:6]) for c in MX8_CASES])
+def test_mxfp8_tcgen05(aclnn, case):
+    batch, m, k, n, t1, t2, da, db, bias_kind, out_name = case
+    rng = np.random.default_rng(abs(hash(str(case))) % (2 ** 31))
+    kq = -(-k // 64)
+    x1 = _q(rng, batch + ((k, m) if t1 else (m, k)), da)
+    x2 = _q(rng, batch + ((n, k) if t2 else (k, n)), db)
+    s1 = _e8m0(rng, batch + ((kq, m, 2) if t1 else (m, kq, 2)))
+    s2 = _e8m0(rng, batch + ((n, kq, 2) if t2 else (kq, n, 2)))
+    bias = None if bias_kind is None else rng.uniform(-2, 2, n).astype(np.float32)  # the API takes only fp32 bias in mx mode
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, "qmm_umma_mxfp8")
+    _check(got, _oracle(x1, x2, s1, s2, bias, t1, t2, out_name), out_name)
+
+
+MX4_CASES = [
+    ((), 128, 256, 128, None, "float32"),
+    ((), 128, 64, 128, None, "float32"),                # a quarter of a stage
+    ((), 197, 960, 154, "f32", "bfloat16"),
+    ((), 256, 1024, 384, None, "float16"),
+    ((2,), 140, 512, 264, "f32", "bfloat16"),
+    ((), 1024, 4096, 1280, None, "bfloat16"),
+]
+
+
+@pytest.mark.parametrize("case", MX4_CASES, ids=[str(c[:4]) for c in MX4_CASES])
+def test_mxfp4_tcgen05(aclnn, case):
+    batch, m, k, n, bias_kind, out_name = case
+    rng = np.random.default_rng(abs(hash(str(case))) % (2 ** 31))
+    kq = -(-k // 64)
+    x1 = _q(rng, batch + (m, k), E2M1)
+    x2 = _q(rng, batch + (n, k), E2M1)  # stored (n,k): transposeX2 = true
+    s1 = _e8m0(rng, batch + (m, kq, 2))
+    s2 = _e8m0(rng, batch + (n, kq, 2))
+    bias = None if bias_kind is None else rng.uniform(-2, 2, n).astype(np.float32)
+    got = _run(aclnn, x1, x2, s1, s2, bias, False, True, out_name, "qmm_umma_mxfp4")
+    _check(got, _oracle(x1, x2, s1, s2, bias, False, True, out_name), out_name)
+
+
+def test_mx_fixtures_run_on_the_tensor_core_kernels(aclnn):
+    from gpu_util import run_qmm_fixture
+
+    for name, kern in (("qmm_mxfp8_bias_bf16", "qmm_umma_mxfp8"), ("qmm_mxfp8_transB_oddgroups", "qmm_umma_mxfp8"),
+                       ("qmm_mxfp4_transB_fp32", "qmm_umma_mxfp4")):
+        a, meta = load_golden(name)
+        got = run_qmm_fixture(aclnn, a, meta, kernel=0)
+        assert aclnn.last_kernel_name() == kern, (name, aclnn.last_kernel_name())
+        _check(got, a["out"], meta["out_dtype"])
