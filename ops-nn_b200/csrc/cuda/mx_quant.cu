@@ -8,7 +8,11 @@
 //   e    clamped to [-127, 127]; stored as e8m0 byte e + 127
 //   q    = saturate( round_to_nearest_even( x / 2^e ) ) in the destination format
 //   the scale row is padded to an even count with byte 0 (2^-127) and shaped (.., ceil(k/64), 2)
-// One thread per 32-block: 64 bytes in, 32 (or 16) bytes + 1 scale byte out; purely HBM bound.
+// Purely HBM bound. Rows whose length is a multiple of 32 (16-byte aligned) take the streaming kernel: four lanes share a
+// 32-block, each moving 16 bytes in and 8 (4) bytes out, the block maximum combined with two shuffles; anything ragged
+// takes the one-thread-per-block kernel.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace opsnn {
@@ -94,6 +98,85 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const OpsnnMxQuantParams 
     }
 }
 
+__device__ __forceinline__ int mx_shared_exp(float amax, int emax)
+{
+    int e;
+    if (amax == 0.f || !(amax == amax)) {
+        e = -127;
+    } else {
+        const int field = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
+        if (field != 0) {
+            e = field - 127 - emax;  // floor(log2(amax)) of a normal float is its exponent
+        } else {
+            int ex;
+            frexpf(amax, &ex);
+            e = (ex - 1) - emax;
+        }
+    }
+    if (isinf(amax)) e = 128;
+    return max(-127, e);
+}
+
+// Streaming form: k % 32 == 0, x and y 16-byte aligned. One lane = 8 consecutive elements; lanes 4j..4j+3 = one block.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) mx_quant_stream_kernel(const OpsnnMxQuantParams p, int64_t blocks_per_row, int64_t scale_row)
+{
+    const int64_t pieces = p.rows * blocks_per_row * 4;  // 8-element pieces
+    const int emax = p.y_dtype == ACL_FLOAT4_E2M1 ? 2 : (p.y_dtype == ACL_FLOAT8_E4M3FN ? 8 : 15);
+    const uint4* src = reinterpret_cast<const uint4*>(p.x);
+    for (int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) & ~(int64_t)31; i0 < pieces; i0 += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = i0 + (threadIdx.x & 31);
+        const bool live = i < pieces;  // pieces is a multiple of 4, so a block's four lanes are live together
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = __ldcs(src + i);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (kBf16) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            } else {
+                const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                v[2 * j] = f2.x;
+                v[2 * j + 1] = f2.y;
+            }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const int e = mx_shared_exp(amax, emax);
+        if (!live) continue;
+        const int64_t blk_lin = i >> 2;
+        if ((i & 3) == 0) {
+            const int64_t row = blk_lin / blocks_per_row, blk = blk_lin % blocks_per_row;
+            uint8_t* sc = reinterpret_cast<uint8_t*>(p.scale) + row * scale_row + blk;
+            *sc = e > 127 ? 255 : (uint8_t)(e + 127);
+            if (blk == blocks_per_row - 1 && scale_row != blocks_per_row) sc[1] = 0;  // padding entry that makes the count even
+        }
+        const float inv = e > 127 ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(127 - e) << 23 | 0u);  // 2^-e, e in [-127, 127]
+        const float inv2 = (e == 127) ? 0.5f : 1.f;  // 2^-127 is subnormal: split the scale in two exact factors
+        const float s0 = (e == 127) ? __uint_as_float(1u << 23) : inv;  // 2^-126 when e == 127
+        if (p.y_dtype == ACL_FLOAT4_E2M1) {
+            uint32_t out = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) out |= (uint32_t)quant_fp4_e2m1(v[j] * s0 * inv2) << (4 * j);
+            reinterpret_cast<uint32_t*>(p.y)[i] = out;
+        } else {
+            const __nv_fp8_interpretation_t kind = p.y_dtype == ACL_FLOAT8_E4M3FN ? __NV_E4M3 : __NV_E5M2;
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                lo |= (uint32_t)__nv_cvt_float_to_fp8(v[j] * s0 * inv2, __NV_SATFINITE, kind) << (8 * j);
+                hi |= (uint32_t)__nv_cvt_float_to_fp8(v[4 + j] * s0 * inv2, __NV_SATFINITE, kind) << (8 * j);
+            }
+            reinterpret_cast<uint2*>(p.y)[i] = make_uint2(lo, hi);
+        }
+    }
+}
+
 }  // namespace
 
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream)
@@ -102,6 +185,17 @@ int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream)
     const int64_t scale_row = ((blocks_per_row + 1) / 2) * 2;
     const int64_t total = p->rows * scale_row;
     if (total == 0) return 0;
+    const bool stream_ok = p->k % 32 == 0 && (reinterpret_cast<uintptr_t>(p->x) & 15) == 0 && (reinterpret_cast<uintptr_t>(p->y) & 7) == 0 &&
+                           getenv("OPSNN_MXQ_GENERIC") == nullptr;
+    if (stream_ok) {
+        const int64_t pieces = p->rows * blocks_per_row * 4;
+        int64_t g2 = (pieces + 255) / 256;
+        if (g2 > 148 * 16) g2 = 148 * 16;
+        if (p->x_dtype == ACL_BF16) mx_quant_stream_kernel<true><<<(unsigned)g2, 256, 0, stream>>>(*p, blocks_per_row, scale_row);
+        else mx_quant_stream_kernel<false><<<(unsigned)g2, 256, 0, stream>>>(*p, blocks_per_row, scale_row);
+        note_launch("mx_quant_stream");
+        return (int32_t)cudaGetLastError();
+    }
     int64_t grid = (total + 255) / 256;
     if (grid > 148 * 32) grid = 148 * 32;
     if (p->x_dtype == ACL_BF16) mx_quant_kernel<true><<<(unsigned)grid, 256, 0, stream>>>(*p, blocks_per_row, scale_row);

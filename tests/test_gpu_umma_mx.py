@@ -118,3 +118,37 @@ def test_mx_fixtures_run_on_the_tensor_core_kernels(aclnn):
         got = run_qmm_fixture(aclnn, a, meta, kernel=0)
         assert aclnn.last_kernel_name() == kern, (name, aclnn.last_kernel_name())
         _check(got, a["out"], meta["out_dtype"])
+
+
+@pytest.mark.parametrize("dst", ["float8_e4m3fn", "float8_e5m2", "float4_e2m1"])
+@pytest.mark.parametrize("xdt", ["bfloat16", "float16"])
+def test_dynamic_mx_quant_streaming_kernel_matches_oracle(aclnn, dst, xdt):
+    """The coalesced quantiser (rows a multiple of 32 long) against the oracle of quant/dynamic_mx_quant/tests/assets/golden.py,
+    bit for bit, on inputs with outliers, zero blocks, subnormals and huge values."""
+    import torch
+
+    from gpu_util import DEV, desc
+    from oracle import mx_quant_oracle
+
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((96, 1024)).astype(np.float32)
+    x[rng.integers(0, 96, 200), rng.integers(0, 1024, 200)] *= 50.0
+    x[3, 64:96] = 0.0
+    x[4, :32] = 1e-30
+    x[5, 32:64] = 3e4
+    xs = x.astype(ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16)
+    want_y, want_s = mx_quant_oracle.dynamic_mx_quant(xs, dst)
+    ybytes = xs.shape[:-1] + ((xs.shape[-1] // 2,) if dst == "float4_e2m1" else (xs.shape[-1],))
+    y = torch.full(ybytes, 0xAA, dtype=torch.uint8, device=DEV)
+    s = torch.full(want_s.shape, 0xAA, dtype=torch.uint8, device=DEV)
+    aclnn.dynamic_mx_quant(desc(aclnn, xs), aclnn.Tensor(xs.shape, dst, y), aclnn.Tensor(want_s.shape, "float8_e8m0", s), dst)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == "mx_quant_stream"
+    assert np.array_equal(s.cpu().numpy(), np.asarray(want_s).view(np.uint8))
+    wy = np.asarray(want_y)
+    if dst == "float4_e2m1":
+        codes = wy.view(np.uint8)
+        wy_bytes = (codes[..., 0::2] & 0xF) | ((codes[..., 1::2] & 0xF) << 4)
+    else:
+        wy_bytes = wy.view(np.uint8)
+    assert np.array_equal(y.cpu().numpy(), wy_bytes)
