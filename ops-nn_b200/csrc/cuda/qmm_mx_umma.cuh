@@ -81,7 +81,7 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&tfull[b], 1);
-            ptx::mbar_init(&tempty[b], EW * 32);
+            ptx::mbar_init(&tempty[b], EW);  // one arrival per epilogue warp
         }
         *abort_flag = 0u;
         ptx::fence_mbar_init();
@@ -247,7 +247,8 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&tempty[buf]);
+            __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
             ++grp;
         }
     }

@@ -176,7 +176,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&tfull[b], 1);
-            ptx::mbar_init(&tempty[b], EW * 32);
+            ptx::mbar_init(&tempty[b], EW);  // one arrival per epilogue warp
         }
         *abort_flag = 0u;
         ptx::fence_mbar_init();
@@ -382,7 +382,8 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&tempty[buf]);
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
                 ++grp;
             } else {
                 float acc[kCols];
@@ -393,29 +394,69 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int64_t mg = (row_ok ? row : 0) / a.group_m;
                 const int64_t n_mg = (a.m + a.group_m - 1) / a.group_m, n_ng = (a.n + 127) / 128;
                 const int64_t ng = min(colbase / 128, n_ng - 1);
-                for (int kb = 0; kb < a.kblocks; ++kb, ++grp) {
-                    const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
-                    // scale of this (row, k-block, n-block): x1Scale is (m/gm, kblocks) or, transposed, (kblocks, m/gm);
-                    // x2Scale is (kblocks, n/128) or, transposed, (n/128, kblocks)
-                    const float sv1 = a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
-                    const float sv2 = a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
-                    const float sc = __fmul_rn(sv1, sv2);
-                    if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) {
-                        report(abort_flag, (3u << 8) | 2u);
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
+                // scale of a (row, k-block, n-block): x1Scale is (m/gm, kblocks) or, transposed, (kblocks, m/gm); x2Scale is
+                // (kblocks, n/128) or, transposed, (n/128, kblocks). Four k-blocks' products are fetched while the previous
+                // four are consumed: an L2 round trip in front of every k-block would otherwise bound the whole kernel.
+                auto load_s1 = [&](int kb) {
+                    kb = min(kb, a.kblocks - 1);
+                    return a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
+                };
+                auto load_s2 = [&](int kb) {
+                    kb = min(kb, a.kblocks - 1);
+                    return a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
+                };
+                // the raw values wait in registers; multiplying them here would stall on the loads just issued
+                float s1_next[4], s2_next[4];
 #pragma unroll
-                    for (int c = 0; c < kCols; c += 32) {
-                        uint32_t v[32];
-                        ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + half * kCols + c, v);
-                        ptx::tmem_ld_wait();
+                for (int j = 0; j < 4; ++j) {
+                    s1_next[j] = load_s1(j);
+                    s2_next[j] = load_s2(j);
+                }
+                for (int kb0 = 0; kb0 < a.kblocks && ok; kb0 += 4) {
+                    float sc_cur[4];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[c + i] = fmaf(__uint_as_float(v[i]), sc, acc[c + i]);
+                    for (int j = 0; j < 4; ++j) sc_cur[j] = __fmul_rn(s1_next[j], s2_next[j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        s1_next[j] = load_s1(kb0 + 4 + j);
+                        s2_next[j] = load_s2(kb0 + 4 + j);
                     }
-                    ptx::tc_fence_before();
-                    ptx::mbar_arrive(&tempty[buf]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (kb0 + j >= a.kblocks) break;
+                        const uint32_t buf = grp & 1, gpar = (grp >> 1) & 1;
+                        const float sc = sc_cur[j];
+                        if (!ptx::mbar_wait(&tfull[buf], gpar, abort_flag)) {
+                            report(abort_flag, (3u << 8) | 2u);
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        // TMEM -> registers in chunks of 16 columns, one chunk in flight while the previous one is folded into
+                        // acc; the buffer goes back to the MMA warp as soon as the last chunk has arrived
+                        constexpr int W = 16;
+                        const uint32_t t0 = tmem_base + lane_addr + buf * BN + half * kCols;
+                        uint32_t va[W], vb[W];
+                        ptx::tmem_ld16(t0, va);
+#pragma unroll
+                        for (int c = 0; c < kCols; c += 2 * W) {
+                            ptx::tmem_ld_wait();
+                            ptx::tmem_ld16(t0 + c + W, vb);
+#pragma unroll
+                            for (int i = 0; i < W; ++i) acc[c + i] = fmaf(__uint_as_float(va[i]), sc, acc[c + i]);
+                            ptx::tmem_ld_wait();
+                            if (c + 2 * W < kCols) {
+                                ptx::tmem_ld16(t0 + c + 2 * W, va);
+                            } else {
+                                ptx::tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < W; ++i) acc[c + W + i] = fmaf(__uint_as_float(vb[i]), sc, acc[c + W + i]);
+                        }
+                        ++grp;
+                    }
                 }
                 if (ok && row_ok) {
 #pragma unroll
@@ -500,6 +541,8 @@ int pick_bn(const OpsnnQmmParams* p)
         int v = atoi(e);
         if (v == 32 || v == 64 || v == 128 || v == 256) return v;
     }
+    // per-block: the promotion epilogue (registers: 128 accumulators per thread) keeps up with 128-column tiles only
+    if (p->mode == OPSNN_QMM_PERBLOCK) return 128;
     const int64_t tiles_m = (p->m + BM - 1) / BM;
     const int sms = 148;
     const int lo = (p->mode == OPSNN_QMM_PERBLOCK || !p->trans_b) ? 128 : 32;
