@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core kernels use: mbarrier, TMA (cp.async.bulk.tensor,
-// never with cluster multicast), tcgen05 (TMEM allocation, MMA, commit, ld, cp) and the shared-memory / instruction
+// every load addressed to the issuing CTA only), tcgen05 (TMEM allocation, MMA, commit, ld, cp) and the shared-memory / instruction
 // descriptors tcgen05.mma consumes. Every wait is bounded: it gives up after kSpinLimit polls and reports failure.
 #pragma once
 
