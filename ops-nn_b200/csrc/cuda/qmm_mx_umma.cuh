@@ -15,23 +15,33 @@
 // operations of one thread execute in issue order, so one TMEM slot per operand is enough).
 namespace {
 
-constexpr int kMxBN = 128;
-constexpr uint32_t kMxSfaCol = 2 * kMxBN;  // TMEM columns: two accumulators, then the scale slots
+// Tile widths: 224 columns is the widest whose two accumulators (at TMEM columns 0 and 256) leave room for the scale
+// slots (columns 224..247) in the 512 columns an SM has; 128 for narrow problems.
+template <int BN>
+struct MxTile {
+    static constexpr int kRowAtoms = BN > 128 ? 2 : 1;            // 128-row scale atoms covering the B tile's rows
+    static constexpr uint32_t kBSmem = BN > 128 ? 32768u : 16384u;  // bytes reserved for B per stage (two 128-column boxes when n-major)
+    static constexpr uint32_t kAcc1Col = BN > 128 ? 256u : 128u;    // second accumulator
+    static constexpr uint32_t kSfaCol = BN > 128 ? 224u : 256u;     // scale slots: A first, then B
+};
 
 // One thread per 32-bit word of the atoms: rows (tile*128 + word%4... see index math), four consecutive k-blocks.
 __global__ void mx_sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows, int64_t kblocks,
                                       int64_t kq, int transposed_layout, int64_t tiles, int64_t stages, int atoms, int64_t batch,
-                                      int64_t src_bs)
+                                      int64_t src_bs, int tile_rows, int row_atoms)
 {
-    const int64_t words = batch * tiles * stages * atoms * 128;
+    // atom order in workspace: [batch][tile][stage][k atom][row atom]; a row atom is 128 consecutive rows of the tile
+    const int64_t words = batch * tiles * stages * atoms * row_atoms * 128;
     for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < words; w += (int64_t)gridDim.x * blockDim.x) {
         const int l = (int)(w & 31), m1 = (int)((w >> 5) & 3);
         int64_t r = w >> 7;
+        const int ra = (int)(r % row_atoms); r /= row_atoms;
         const int at = (int)(r % atoms); r /= atoms;
         const int64_t st = r % stages; r /= stages;
         const int64_t tile = r % tiles;
         const int64_t b = r / tiles;
-        const int64_t row = tile * 128 + m1 * 32 + l;
+        const int in_tile = ra * 128 + m1 * 32 + l;
+        const int64_t row = in_tile < tile_rows ? tile * tile_rows + in_tile : rows;  // past the tile: no such row
         const int64_t kb0 = (st * atoms + at) * 4;
         const uint8_t* s = src + b * src_bs;
         uint32_t word = 0;
@@ -44,21 +54,24 @@ __global__ void mx_sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* 
             word |= v << (8 * j);
         }
         // destination: atom base + (row % 32) * 16 + (row / 32 % 4) * 4
-        const int64_t atom_idx = ((b * tiles + tile) * stages + st) * atoms + at;
+        const int64_t atom_idx = (((b * tiles + tile) * stages + st) * atoms + at) * row_atoms + ra;
         *reinterpret_cast<uint32_t*>(dst + atom_idx * 512 + l * 16 + m1 * 4) = word;
     }
 }
 
-template <bool kF4>
+template <int BN, bool kF4>
 __global__ void __launch_bounds__(192, 1)
 qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
 {
-    constexpr int BN = kMxBN, EW = 4;
-    constexpr int kAtoms = kF4 ? 2 : 1;  // scale atoms per operand per stage: a stage is 128 bytes of k = 4 (fp8) / 8 (fp4) k-blocks
-    constexpr uint32_t kSfBytes = kAtoms * 512;
-    constexpr uint32_t kBTile = BN * BK;
-    constexpr uint32_t kStage = kATile + kBTile + 2 * kSfBytes;
+    constexpr int EW = 4;
+    constexpr int kAtoms = kF4 ? 2 : 1;  // k atoms per stage: a stage is 128 bytes of k = 4 (fp8) / 8 (fp4) k-blocks of 32
+    constexpr int RA = MxTile<BN>::kRowAtoms;
+    constexpr uint32_t kSfaBytes = kAtoms * 512, kSfbBytes = kAtoms * RA * 512;
+    constexpr uint32_t kBTile = MxTile<BN>::kBSmem;
+    constexpr uint32_t kStage = kATile + kBTile + kSfaBytes + kSfbBytes;
+    constexpr uint32_t kMxSfaCol = MxTile<BN>::kSfaCol;
     constexpr uint32_t kSfbCol = kMxSfaCol + 4 * kAtoms;
+    constexpr uint32_t kAcc1 = MxTile<BN>::kAcc1Col;
     constexpr uint32_t kTmemCols = 512;
 
     extern __shared__ uint8_t smem_raw[];
@@ -70,7 +83,7 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile uint32_t* abort_flag = tmem_ptr + 1;
-    float* s_bias = reinterpret_cast<float*>(tmem_ptr + 4);  // [BN]
+    float* s_bias = reinterpret_cast<float*>(tmem_ptr + 4);  // [256]
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
@@ -113,8 +126,10 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const uint32_t tm = r % (uint32_t)a.tiles_m, tn = r / (uint32_t)a.tiles_m;
             const int32_t m0 = (int32_t)tm * BM, n0 = (int32_t)tn * BN;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
-            const uint8_t* sfa = a.sfa + (int64_t)ba * a.sfa_bs + ((int64_t)tm * kstages) * kSfBytes;
-            const uint8_t* sfb = a.sfb + (int64_t)bb * a.sfb_bs + ((int64_t)tn * kstages) * kSfBytes;
+            const uint8_t* sfa = a.sfa + (int64_t)ba * a.sfa_bs + ((int64_t)tm * kstages) * kSfaBytes;
+            const uint8_t* sfb = a.sfb + (int64_t)bb * a.sfb_bs + ((int64_t)tn * kstages) * kSfbBytes;
+            // bytes one stage's copies deliver: k-major B is one box of BN rows, n-major B whole 128-column boxes
+            const uint32_t tx = (uint32_t)kATile + (b_mn ? kBTile : (uint32_t)(BN * BK)) + kSfaBytes + kSfbBytes;
             int32_t kk = 0;
             for (int kb = 0; kb < kstages; ++kb) {
                 if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
@@ -124,15 +139,16 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 }
                 if (ptx::elect_one()) {
                     const uint32_t fb = full0 + 8u * s, sa = smem0 + s * kStage, sb = sa + (uint32_t)kATile;
-                    ptx::mbar_expect_tx_a(fb, kStage);
+                    ptx::mbar_expect_tx_a(fb, tx);
                     ptx::tma_load_3d_a(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
                     ptx::tma_load_3d_a(sb, &map_b, fb, b_mn ? n0 : kk, b_mn ? kk : n0, bb);
-                    ptx::bulk_load_a(sb + kBTile, sfa, kSfBytes, fb);
-                    ptx::bulk_load_a(sb + kBTile + kSfBytes, sfb, kSfBytes, fb);
+                    if (BN > 128 && b_mn) ptx::tma_load_3d_a(sb + 128u * BK, &map_b, fb, n0 + 128, kk, bb);
+                    ptx::bulk_load_a(sb + kBTile, sfa, kSfaBytes, fb);
+                    ptx::bulk_load_a(sb + kBTile + kSfaBytes, sfb, kSfbBytes, fb);
                 }
                 __syncwarp();
-                sfa += kSfBytes;
-                sfb += kSfBytes;
+                sfa += kSfaBytes;
+                sfb += kSfbBytes;
                 kk += BK;
                 if (++s == stages) {
                     s = 0;
@@ -169,21 +185,23 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 ptx::tc_fence_after();
                 if (ptx::elect_one()) {
                     const uint32_t stage_off = (s * kStage) >> 4;
-                    const uint32_t d = tmem_base + (grp & 1u) * BN;
+                    const uint32_t d = tmem_base + (grp & 1u) * kAcc1;
                     const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off, sl = sf_lo + stage_off;
+                    // scale atoms shared -> TMEM: A's k atoms, then B's (k atom, row atom) pairs, in shared-memory order
 #pragma unroll
-                    for (int at = 0; at < kAtoms; ++at) {
-                        ptx::tmem_cp_sf(tmem_base + kMxSfaCol + 4 * at, sf_hi | (uint64_t)(sl + at * 32));
+                    for (int at = 0; at < kAtoms; ++at) ptx::tmem_cp_sf(tmem_base + kMxSfaCol + 4 * at, sf_hi | (uint64_t)(sl + at * 32));
+#pragma unroll
+                    for (int at = 0; at < kAtoms * RA; ++at)
                         ptx::tmem_cp_sf(tmem_base + kSfbCol + 4 * at, sf_hi | (uint64_t)(sl + (kAtoms + at) * 32));
-                    }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const uint32_t sf_id = kF4 ? (uint32_t)(k & 1) * 2u : (uint32_t)k;
-                        const uint32_t col = kF4 ? 4u * (uint32_t)(k >> 1) : 0u;
+                        const uint32_t katom = kF4 ? (uint32_t)(k >> 1) : 0u;
                         const uint32_t id = idesc | (sf_id << 29) | (sf_id << 4);
                         const uint64_t da = a_hi | (uint64_t)(al + k * a_k1), db = b_hi | (uint64_t)(bl + k * b_k1);
-                        if (kF4) ptx::umma_mxf4(d, da, db, id, tmem_base + kMxSfaCol + col, tmem_base + kSfbCol + col, k == 0 ? acc : 1u);
-                        else ptx::umma_mxf8f6f4(d, da, db, id, tmem_base + kMxSfaCol, tmem_base + kSfbCol, k == 0 ? acc : 1u);
+                        const uint32_t ta = tmem_base + kMxSfaCol + 4u * katom, tb = tmem_base + kSfbCol + 4u * RA * katom;
+                        if (kF4) ptx::umma_mxf4(d, da, db, id, ta, tb, k == 0 ? acc : 1u);
+                        else ptx::umma_mxf8f6f4(d, da, db, id, ta, tb, k == 0 ? acc : 1u);
                     }
                     ptx::umma_commit_a(empty0 + 8u * s);
                 }
@@ -229,7 +247,7 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t v[32];
-                ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + c, v);
+                ptx::tmem_ld32(tmem_base + lane_addr + buf * kAcc1 + c, v);
                 ptx::tmem_ld_wait();
                 const int64_t col = n0 + c;
                 const int valid = (int)min((int64_t)32, a.n - col);
@@ -265,27 +283,62 @@ bool is_fp4(int dt) { return dt == ACL_FLOAT4_E2M1; }
 
 struct MxPlan {
     bool f4;
-    int atoms;
+    int bn, atoms, row_atoms;
     int64_t tiles_m, tiles_n, kstages, kblocks32, kq;
     uint64_t sfa_bytes_per_batch, sfb_bytes_per_batch, nb_a, nb_b;
 };
+
+// Host tile selection: 224-column tiles (less operand traffic per flop) whenever they still give every SM a tile.
+int mx_pick_bn(const OpsnnQmmParams* p)
+{
+    if (const char* e = getenv("OPSNN_QMM_MX_BN")) {
+        const int v = atoi(e);
+        if (v == 128 || v == 224) return v;
+    }
+    if (p->n <= 128) return 128;
+    const int64_t tiles = p->batch * ((p->m + BM - 1) / BM) * ((p->n + 223) / 224);
+    return tiles >= 148 ? 224 : 128;
+}
 
 MxPlan mx_plan(const OpsnnQmmParams* p)
 {
     MxPlan q{};
     q.f4 = is_fp4(p->a_dtype);
+    q.bn = mx_pick_bn(p);
     q.atoms = q.f4 ? 2 : 1;
+    q.row_atoms = q.bn > 128 ? 2 : 1;
     const int64_t k_per_stage = q.f4 ? 256 : 128;
     q.tiles_m = (p->m + BM - 1) / BM;
-    q.tiles_n = (p->n + kMxBN - 1) / kMxBN;
+    q.tiles_n = (p->n + q.bn - 1) / q.bn;
     q.kstages = (p->k + k_per_stage - 1) / k_per_stage;
     q.kblocks32 = (p->k + 31) / 32;
     q.kq = (p->k + 63) / 64;
     q.nb_a = p->sa_bs != 0 ? (uint64_t)p->batch : 1;
     q.nb_b = p->sb_bs != 0 ? (uint64_t)p->batch : 1;
     q.sfa_bytes_per_batch = (uint64_t)q.tiles_m * q.kstages * q.atoms * 512;
-    q.sfb_bytes_per_batch = (uint64_t)q.tiles_n * q.kstages * q.atoms * 512;
+    q.sfb_bytes_per_batch = (uint64_t)q.tiles_n * q.kstages * q.atoms * q.row_atoms * 512;
     return q;
+}
+
+template <int BN, bool kF4>
+int32_t mx_launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
+{
+    constexpr uint32_t stage = (uint32_t)kATile + MxTile<BN>::kBSmem + (kF4 ? 2 : 1) * 512 * (1 + MxTile<BN>::kRowAtoms);
+    int stages = (227 * 1024 - 2048) / (int)stage;
+    if (stages > 8) stages = 8;
+    if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * stage + 1024 + 256 + 256 * 4;
+    const int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<BN, kF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (rc != cudaSuccess) return (int32_t)rc;
+        configured = true;
+    }
+    qmm_mx_umma_kernel<BN, kF4><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
+    note_launch(kF4 ? "qmm_umma_mxfp4" : "qmm_umma_mxfp8");
+    return (int32_t)cudaGetLastError();
 }
 
 }  // namespace
@@ -328,14 +381,16 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     // ---- pre-pass: both operands' scales into atom order ----
     {
         const int64_t wa = (int64_t)q.nb_a * q.tiles_m * q.kstages * q.atoms * 128;
-        const int64_t wb = (int64_t)q.nb_b * q.tiles_n * q.kstages * q.atoms * 128;
+        const int64_t wb = (int64_t)q.nb_b * q.tiles_n * q.kstages * q.atoms * q.row_atoms * 128;
         const int threads = 256;
         const auto blocks = [&](int64_t w) { return (unsigned)std::min<int64_t>((w + threads - 1) / threads, 148 * 16); };
         // x1Scale is (m, kq, 2), or (kq, m, 2) when x1 is stored (k,m); x2Scale is (kq, n, 2), or (n, kq, 2) when x2 is stored (n,k)
         mx_sf_relayout_kernel<<<blocks(wa), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32, q.kq,
-                                                                  p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs);
+                                                                  p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs,
+                                                                  BM, 1);
         mx_sf_relayout_kernel<<<blocks(wb), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32, q.kq,
-                                                                  p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, (int64_t)q.nb_b, p->sb_bs);
+                                                                  p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, (int64_t)q.nb_b, p->sb_bs,
+                                                                  q.bn, q.row_atoms);
         note_launch("mx_sf_relayout", 2);
     }
     UmmaArgs a{};
@@ -356,7 +411,7 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.sfb_bs = q.nb_b > 1 ? (int64_t)q.sfb_bytes_per_batch : 0;
     const uint32_t fa = q.f4 ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = q.f4 ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
-    a.idesc = make_idesc_block_scaled(fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, kMxBN);
+    a.idesc = make_idesc_block_scaled(fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)q.bn);
 
     const uint64_t div = q.f4 ? 2 : 1;
     CUtensorMap ma, mb;
@@ -365,35 +420,9 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k / div, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld / div, (uint64_t)p->a_bs / div, 128);
     if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
-    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k / div, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld / div, (uint64_t)p->b_bs / div, kMxBN);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k / div, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld / div, (uint64_t)p->b_bs / div, (uint32_t)q.bn);
     if (!ok) return (int32_t)cudaErrorInvalidValue;
 
-    const uint32_t stage = (uint32_t)(kATile + kMxBN * BK + 2 * q.atoms * 512);
-    int stages = (227 * 1024 - 2048) / (int)stage;
-    if (stages > 8) stages = 8;
-    if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
-    a.stages = stages;
-    const size_t smem = (size_t)stages * stage + 1024 + 256 + kMxBN * 4;
-    const int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
-    cudaError_t rc;
-    if (q.f4) {
-        static bool configured = false;
-        if (!configured) {
-            rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (rc != cudaSuccess) return (int32_t)rc;
-            configured = true;
-        }
-        qmm_mx_umma_kernel<true><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
-        note_launch("qmm_umma_mxfp4");
-    } else {
-        static bool configured = false;
-        if (!configured) {
-            rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (rc != cudaSuccess) return (int32_t)rc;
-            configured = true;
-        }
-        qmm_mx_umma_kernel<false><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
-        note_launch("qmm_umma_mxfp8");
-    }
-    return (int32_t)cudaGetLastError();
+    if (q.bn == 224) return q.f4 ? mx_launch_one<224, true>(ma, mb, a, stream) : mx_launch_one<224, false>(ma, mb, a, stream);
+    return q.f4 ? mx_launch_one<128, true>(ma, mb, a, stream) : mx_launch_one<128, false>(ma, mb, a, stream);
 }

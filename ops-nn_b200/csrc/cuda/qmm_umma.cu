@@ -145,6 +145,74 @@ __device__ __forceinline__ void deq_chunk(const uint32_t (&v)[32], const float* 
     }
 }
 
+// Column scales and bias of an n tile, decoded to 32 bit, into shared memory (128 epilogue threads).
+template <int BN>
+__device__ __forceinline__ void deq_stage_cols(const UmmaArgs& a, const uint8_t* bias, bool has_ibias, bool has_fbias, int64_t n0,
+                                               float* s_scale, uint32_t* s_bias)
+{
+    for (int c = threadIdx.x; c < BN; c += 128) {
+        const int64_t cc = min(n0 + c, a.n - 1);
+        float sb = load_deq_scale(a.scale_b, a.scale_b_len == 1 ? 0 : cc, a.scale_b_dtype);
+        if (a.deq_flags & OPSNN_DEQ_TRUNC_SCALE_B) sb = trunc19(sb);
+        s_scale[c] = sb;
+        uint32_t bv = 0u;
+        if (has_ibias) bv = (uint32_t)__ldg(reinterpret_cast<const int32_t*>(bias) + cc);
+        else if (has_fbias) bv = __float_as_uint(load_as_float(bias, cc, a.bias_dtype));
+        s_bias[c] = bv;
+    }
+}
+
+// One thread's row of NCOLS accumulator columns starting at TMEM address tmem_addr / output column col0: dequantise in the
+// reference's order (qbmm_mix_online_dynamic.h:646-736) and store. s_scale / s_bias point at the tile's staged columns,
+// offset so that index 0 is col0's entry.
+template <int NCOLS>
+__device__ __forceinline__ void deq_store_cols(const UmmaArgs& a, uint32_t tmem_addr, uint8_t* out, int64_t row, bool row_ok,
+                                               int64_t col0, const float* s_scale, const uint32_t* s_bias, float sav, bool has_sa,
+                                               bool has_fbias, bool has_ibias)
+{
+                    const int flags = a.deq_flags & ~OPSNN_DEQ_TRUNC_SCALE_B;  // already applied while staging
+                    const bool simple = flags == 0 && a.out_dtype != ACL_INT32;
+                    const int variant = simple ? ((a.is_int ? 4 : 0) | (has_sa ? 2 : 0) | (has_fbias ? 1 : 0)) : -1;
+    #pragma unroll 1
+                    for (int c = 0; c < NCOLS; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(tmem_addr + c, v);
+                        ptx::tmem_ld_wait();
+                        const int64_t col = col0 + c;
+                        const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
+                        if (row_ok && valid > 0) {
+                            if (a.out_dtype == ACL_INT32) {
+                                int32_t* o = reinterpret_cast<int32_t*>(out) + row * a.out_ld + col;
+    #pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (i < valid) o[i] = (int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0);
+                            } else {
+                                float f[32];
+                                switch (variant) {
+                                    case 0: deq_chunk<false, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 1: deq_chunk<false, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 2: deq_chunk<false, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 3: deq_chunk<false, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 4: deq_chunk<true, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 5: deq_chunk<true, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 6: deq_chunk<true, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    case 7: deq_chunk<true, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
+                                    default:
+    #pragma unroll
+                                        for (int i = 0; i < 32; ++i) {
+                                            float x;
+                                            if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
+                                            else x = __uint_as_float(v[i]);
+                                            f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
+                                        }
+                                        break;
+                                }
+                                store_row32(a, out, row, col, f, valid);
+                            }
+                        }
+                    }
+}
+
 template <int BN, bool kPerBlock, ptx::MmaKind kKind>
 __global__ void __launch_bounds__((((kPerBlock && BN == 256) ? 8 : 4) + 2) * 32, 1)
 qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
@@ -322,16 +390,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // Stage the tile's column scales and bias (decoded to 32 bit) while the main loop is still running.
                 // 128 epilogue threads, named barrier 1; every epilogue warp executes every barrier of every tile.
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers are done
-                for (int c = threadIdx.x; c < BN; c += 128) {
-                    const int64_t cc = min(n0 + c, a.n - 1);
-                    float sb = load_deq_scale(a.scale_b, a.scale_b_len == 1 ? 0 : cc, a.scale_b_dtype);
-                    if (a.deq_flags & OPSNN_DEQ_TRUNC_SCALE_B) sb = trunc19(sb);
-                    s_scale[c] = sb;
-                    uint32_t bv = 0u;
-                    if (has_ibias) bv = (uint32_t)__ldg(reinterpret_cast<const int32_t*>(bias) + cc);
-                    else if (has_fbias) bv = __float_as_uint(load_as_float(bias, cc, a.bias_dtype));
-                    s_bias[c] = bv;
-                }
+                deq_stage_cols<BN>(a, bias, has_ibias, has_fbias, n0, s_scale, s_bias);
                 if (!ptx::mbar_wait_relaxed(&tfull[buf], gpar, abort_flag)) report(abort_flag, (3u << 8) | 1u);
                 // the four epilogue warps leave together: a named barrier is only safe if nobody has left the loop
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -340,47 +399,8 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     break;
                 }
                 ptx::tc_fence_after();
-                const int flags = a.deq_flags & ~OPSNN_DEQ_TRUNC_SCALE_B;  // already applied while staging
-                const bool simple = flags == 0 && a.out_dtype != ACL_INT32;
-                const int variant = simple ? ((a.is_int ? 4 : 0) | (has_sa ? 2 : 0) | (has_fbias ? 1 : 0)) : -1;
-#pragma unroll 1
-                for (int c = 0; c < kCols; c += 32) {
-                    uint32_t v[32];
-                    ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + c, v);
-                    ptx::tmem_ld_wait();
-                    const int64_t col = colbase + c;
-                    const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
-                    if (row_ok && valid > 0) {
-                        if (a.out_dtype == ACL_INT32) {
-                            int32_t* o = reinterpret_cast<int32_t*>(out) + row * a.out_ld + col;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < valid) o[i] = (int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0);
-                        } else {
-                            float f[32];
-                            switch (variant) {
-                                case 0: deq_chunk<false, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 1: deq_chunk<false, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 2: deq_chunk<false, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 3: deq_chunk<false, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 4: deq_chunk<true, false, false>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 5: deq_chunk<true, false, true>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 6: deq_chunk<true, true, false>(v, s_scale + c, s_bias + c, sav, f); break;
-                                case 7: deq_chunk<true, true, true>(v, s_scale + c, s_bias + c, sav, f); break;
-                                default:
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i) {
-                                        float x;
-                                        if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
-                                        else x = __uint_as_float(v[i]);
-                                        f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
-                                    }
-                                    break;
-                            }
-                            store_row32(a, out, row, col, f, valid);
-                        }
-                    }
-                }
+                deq_store_cols<kCols>(a, tmem_base + lane_addr + buf * BN, out, row, row_ok, colbase, s_scale, s_bias, sav, has_sa, has_fbias,
+                                      has_ibias);
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
@@ -593,6 +613,7 @@ int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs
 }  // namespace
 
 #include "qmm_mx_umma.cuh"
+#include "qmm_umma_pair.cuh"
 
 bool qmm_umma_eligible(const OpsnnQmmParams* p)
 {
@@ -625,14 +646,16 @@ uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p) { return p->mode == OP
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
-    const int bn = pick_bn(p);
+    const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32;
+    const int bn = pair ? 256 : pick_bn(p);
+    const int bm = pair ? 256 : BM;
     UmmaArgs a{};
     a.mode = p->mode;
     a.is_int = p->a_dtype == ACL_INT8;
     a.a_mn_major = p->trans_a ? 1 : 0;   // stored (k,m): m contiguous
     a.b_mn_major = p->trans_b ? 0 : 1;   // stored (k,n): n contiguous
     a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
-    a.tiles_m = (int32_t)((p->m + BM - 1) / BM);
+    a.tiles_m = (int32_t)((p->m + bm - 1) / bm);
     a.tiles_n = (int32_t)((p->n + bn - 1) / bn);
     a.kblocks = (int32_t)((p->k + BK - 1) / BK);
     a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
@@ -645,7 +668,7 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.bias = p->bias; a.bias_bs = p->bias_bs; a.out = p->out; a.out_ld = p->out_ld; a.out_bs = p->out_bs;
     const uint32_t fa = a.is_int ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = a.is_int ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
-    a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)bn);
+    a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, (uint32_t)bm, (uint32_t)bn);
 
     CUtensorMap ma, mb;
     const uint64_t nb_a = a.a_batched ? (uint64_t)p->batch : 1, nb_b = a.b_batched ? (uint64_t)p->batch : 1;
@@ -653,8 +676,9 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
-    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, (uint32_t)bn);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, pair ? 128u : (uint32_t)bn);
     if (!ok) return (int32_t)cudaErrorInvalidValue;
+    if (pair) return a.is_int ? launch_pair<ptx::MmaKind::kI8>(ma, mb, a, stream) : launch_pair<ptx::MmaKind::kF8F6F4>(ma, mb, a, stream);
 
     if (p->mode == OPSNN_QMM_PERBLOCK) return launch_bn<true, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
     if (a.is_int) return launch_bn<false, ptx::MmaKind::kI8>(bn, ma, mb, a, stream);

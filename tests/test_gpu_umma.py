@@ -123,3 +123,53 @@ def test_fp8_dequant_doublescale(aclnn):
     ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, False, False, 0, "float32")
     got = _run(aclnn, x1, x2, s1, s2, bias, False, False, 0, "bfloat16", "qmm_umma_deq")
     check_close(got, want, ref32, "bfloat16")
+
+
+PAIR_CASES = [
+    # m, k, n, t1, t2, per-token, bias kind, out
+    (256, 256, 256, False, True, True, "i32", "bfloat16"),
+    (512, 1024, 768, False, False, True, None, "bfloat16"),        # n-major B, each CTA loads its own 128 columns
+    (300, 400, 400, False, False, True, "f32", "float16"),         # tails in m (odd CTA partly / wholly past m), k and n
+    (640, 528, 336, True, True, True, "i32", "bfloat16"),          # x1 stored (k,m)
+    (257, 2048, 272, False, True, False, "bf16", "bfloat16"),      # one row in the second CTA's half
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES, ids=[str(c) for c in PAIR_CASES])
+def test_int8_dequant_cta_pairs_bit_exact(aclnn, case, monkeypatch):
+    """The cta_group::2 kernel (two CTAs of a cluster share a 256 x 256 tile), forced for shapes the host tile selection
+    would give to the single-CTA kernel, against the oracle: bit for bit."""
+    m, k, n, t1, t2, pertoken, bias_kind, out_name = case
+    monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32) if pertoken else None
+    bias = {None: None, "i32": rng.integers(-1000, 1001, n).astype(np.int32), "f32": rng.uniform(-1, 1, n).astype(np.float32),
+            "bf16": rng.uniform(-1, 1, n).astype(np.float32).astype(ml_dtypes.bfloat16)}[bias_kind]
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, 0, out_name)
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, 0, out_name, "qmm_umma_pair_deq")
+    assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(want).view(np.uint8))
+
+
+def test_cta_pairs_batched_fp8_and_auto_selection(aclnn, monkeypatch):
+    from gpu_util import check_close
+
+    # large enough for the host tile selection to pick pairs by itself: 3 x 1024 x 1024 -> 48 pair tiles... needs >= 74
+    rng = np.random.default_rng(9)
+    x1 = rng.integers(-127, 128, (5, 1024, 512), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (5, 1024, 512), dtype=np.int8)  # stored (n,k)
+    s2 = rng.uniform(1e-3, 1e-2, 1024).astype(np.float32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, None, s2, None, False, True, 0, "bfloat16")
+    got = _run(aclnn, x1, x2, None, s2, None, False, True, 0, "bfloat16", "qmm_umma_pair_deq")  # 5 * 4 * 4 = 80 tiles
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    # fp8 per-tensor/-channel dequant on pairs
+    monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    a1, a2 = _fp8(rng, (384, 512), E4M3), _fp8(rng, (512, 320), E5M2)
+    sc2 = rng.uniform(0.5, 2, 320).astype(np.float32)
+    sc1 = rng.uniform(0.5, 2, 384).astype(np.float32)
+    want = qbmm_oracle.quant_matmul_v5(a1, a2, sc1, sc2, None, False, False, 0, "bfloat16")
+    ref32 = qbmm_oracle.quant_matmul_v5(a1, a2, sc1, sc2, None, False, False, 0, "float32")
+    got = _run(aclnn, a1, a2, sc1, sc2, None, False, False, 0, "bfloat16", "qmm_umma_pair_deq")
+    check_close(got, want, ref32, "bfloat16")

@@ -25,7 +25,9 @@ def _q(rng, shape, dt):
     return (rng.standard_normal(shape).astype(np.float32) * (2.0 if dt == E2M1 else 1.0)).astype(dt)
 
 
-def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel):
+def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel, bn=None):
+    import os
+
     import torch
 
     from gpu_util import desc, out_tensor, out_to_np
@@ -34,8 +36,13 @@ def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel):
     n = x2.shape[-2] if t2 else x2.shape[-1]
     batch = tuple(x1.shape[:-2])
     out = out_tensor(batch + (m, n), out_name)
-    aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
-                          aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), t1, t2, GROUP_MX)
+    if bn:
+        os.environ["OPSNN_QMM_MX_BN"] = str(bn)  # host tile selection override: 128- or 224-column tiles
+    try:
+        aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
+                              aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), t1, t2, GROUP_MX)
+    finally:
+        os.environ.pop("OPSNN_QMM_MX_BN", None)
     torch.cuda.synchronize()
     assert aclnn.last_kernel_name() == expect_kernel, aclnn.last_kernel_name()
     assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
@@ -68,11 +75,14 @@ MX8_CASES = [
     ((), 144, 384, 208, True, True, E4M3, E4M3, None, "float16"),            # mn-major A
     ((3,), 130, 256, 272, False, False, E4M3, E4M3, "f32", "bfloat16"),      # batched
     ((), 1024, 2048, 1536, False, False, E4M3, E4M3, "f32", "bfloat16"),     # many tiles per CTA, deep k
+    ((), 256, 512, 1344, False, True, E4M3, E4M3, "f32", "bfloat16"),        # n = 6 x 224
+    ((), 256, 512, 1008, False, False, E4M3, E4M3, None, "float32"),         # n-major B, ragged last 224-tile
 ]
 
 
+@pytest.mark.parametrize("bn", [128, 224])
 @pytest.mark.parametrize("case", MX8_CASES, ids=[str(c[:6]) for c in MX8_CASES])
-def test_mxfp8_tcgen05(aclnn, case):
+def test_mxfp8_tcgen05(aclnn, case, bn):
     batch, m, k, n, t1, t2, da, db, bias_kind, out_name = case
     rng = np.random.default_rng(abs(hash(str(case))) % (2 ** 31))
     kq = -(-k // 64)
@@ -81,7 +91,7 @@ def test_mxfp8_tcgen05(aclnn, case):
     s1 = _e8m0(rng, batch + ((kq, m, 2) if t1 else (m, kq, 2)))
     s2 = _e8m0(rng, batch + ((n, kq, 2) if t2 else (kq, n, 2)))
     bias = None if bias_kind is None else rng.uniform(-2, 2, n).astype(np.float32)  # the API takes only fp32 bias in mx mode
-    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, "qmm_umma_mxfp8")
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, "qmm_umma_mxfp8", bn)
     _check(got, _oracle(x1, x2, s1, s2, bias, t1, t2, out_name), out_name)
 
 
@@ -95,8 +105,9 @@ MX4_CASES = [
 ]
 
 
+@pytest.mark.parametrize("bn", [128, 224])
 @pytest.mark.parametrize("case", MX4_CASES, ids=[str(c[:4]) for c in MX4_CASES])
-def test_mxfp4_tcgen05(aclnn, case):
+def test_mxfp4_tcgen05(aclnn, case, bn):
     batch, m, k, n, bias_kind, out_name = case
     rng = np.random.default_rng(abs(hash(str(case))) % (2 ** 31))
     kq = -(-k // 64)
@@ -105,7 +116,7 @@ def test_mxfp4_tcgen05(aclnn, case):
     s1 = _e8m0(rng, batch + (m, kq, 2))
     s2 = _e8m0(rng, batch + (n, kq, 2))
     bias = None if bias_kind is None else rng.uniform(-2, 2, n).astype(np.float32)
-    got = _run(aclnn, x1, x2, s1, s2, bias, False, True, out_name, "qmm_umma_mxfp4")
+    got = _run(aclnn, x1, x2, s1, s2, bias, False, True, out_name, "qmm_umma_mxfp4", bn)
     _check(got, _oracle(x1, x2, s1, s2, bias, False, True, out_name), out_name)
 
 
