@@ -206,6 +206,7 @@ QMM_WORKLOADS = {
     "c5": (32, 2048, 4096, 14336, "mxfp8_dq"),      # bf16 activations -> dynamic mx quant -> mxfp8 matmul + fp32 bias
     "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
     "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
+    "c5mmt": (32, 2048, 4096, 14336, "mxfp8_t"),    # same with the weight stored (n,k), transposeX2 = true
 }
 
 
@@ -239,8 +240,9 @@ def run_qmm_workload(args):
             call = lambda i: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, None, False, True, (1 << 32) | (1 << 16) | 32)  # noqa: E731
             nbytes = b * (m * k // 2 + n * k // 2 + (m + n) * kq * 2 + 2 * m * n)
         else:
-            x2 = torch.randn((b, k, n), generator=gen, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
-            s2 = rnd_scale(b, kq, n, 2)
+            tb = kind == "mxfp8_t"
+            x2 = torch.randn((b, n, k) if tb else (b, k, n), generator=gen, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+            s2 = rnd_scale(b, n, kq, 2) if tb else rnd_scale(b, kq, n, 2)
             bias = torch.randn((n,), generator=gen, device=dev, dtype=torch.float32)
             x1q = torch.empty((b, m, k), dtype=torch.uint8, device=dev)
             s1 = torch.empty((b, m, kq, 2), dtype=torch.uint8, device=dev)
@@ -251,7 +253,7 @@ def run_qmm_workload(args):
             act.view(-1)[torch.randint(0, act.numel(), (act.numel() // 1000,), generator=gen, device=dev)] *= 50  # 0.1 % outliers
             d_act = aclnn.from_torch(act)
             aclnn.dynamic_mx_quant(d_act, d_x1, d_s1, "float8_e4m3fn")
-            mm = lambda: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, d_bias, False, False, (1 << 32) | (1 << 16) | 32)  # noqa: E731
+            mm = lambda: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, d_bias, False, tb, (1 << 32) | (1 << 16) | 32)  # noqa: E731
             if kind == "mxfp8_dq":
                 def call(i):
                     aclnn.dynamic_mx_quant(d_act, d_x1, d_s1, "float8_e4m3fn")

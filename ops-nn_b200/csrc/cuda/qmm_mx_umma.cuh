@@ -281,8 +281,11 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
 bool is_fp4(int dt) { return dt == ACL_FLOAT4_E2M1; }
 
+template <bool kF4>
+int32_t mx_launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream);  // qmm_mx_umma_pair.cuh
+
 struct MxPlan {
-    bool f4;
+    bool f4, pair;
     int bn, atoms, row_atoms;
     int64_t tiles_m, tiles_n, kstages, kblocks32, kq;
     uint64_t sfa_bytes_per_batch, sfb_bytes_per_batch, nb_a, nb_b;
@@ -308,8 +311,11 @@ MxPlan mx_plan(const OpsnnQmmParams* p)
     q.atoms = q.f4 ? 2 : 1;
     q.row_atoms = q.bn > 128 ? 2 : 1;
     const int64_t k_per_stage = q.f4 ? 256 : 128;
-    q.tiles_m = (p->m + BM - 1) / BM;
+    q.tiles_m = (p->m + BM - 1) / BM;  // 128-row tiles: the unit of A's scale atoms, also when CTA pairs share 256-row tiles
     q.tiles_n = (p->n + q.bn - 1) / q.bn;
+    // CTA pairs (256 x 224 tiles, each CTA loading half of B) when there is a tile for about every pair of SMs
+    q.pair = q.bn == 224 && p->m >= 256 && p->batch * ((p->m + 255) / 256) * q.tiles_n >= 74;
+    if (const char* e = getenv("OPSNN_QMM_PAIR")) q.pair = atoi(e) != 0 && q.bn == 224;
     q.kstages = (p->k + k_per_stage - 1) / k_per_stage;
     q.kblocks32 = (p->k + 31) / 32;
     q.kq = (p->k + 63) / 64;
@@ -398,7 +404,7 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.a_mn_major = p->trans_a ? 1 : 0;
     a.b_mn_major = p->trans_b ? 0 : 1;
     a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
-    a.tiles_m = (int32_t)q.tiles_m;
+    a.tiles_m = q.pair ? (int32_t)((p->m + 255) / 256) : (int32_t)q.tiles_m;
     a.tiles_n = (int32_t)q.tiles_n;
     a.kblocks = (int32_t)q.kstages;
     a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
@@ -411,7 +417,7 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.sfb_bs = q.nb_b > 1 ? (int64_t)q.sfb_bytes_per_batch : 0;
     const uint32_t fa = q.f4 ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = q.f4 ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
-    a.idesc = make_idesc_block_scaled(fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, BM, (uint32_t)q.bn);
+    a.idesc = make_idesc_block_scaled(fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, q.pair ? 256u : (uint32_t)BM, (uint32_t)q.bn);
 
     const uint64_t div = q.f4 ? 2 : 1;
     CUtensorMap ma, mb;
@@ -420,9 +426,10 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k / div, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld / div, (uint64_t)p->a_bs / div, 128);
     if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
-    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k / div, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld / div, (uint64_t)p->b_bs / div, (uint32_t)q.bn);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k / div, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld / div, (uint64_t)p->b_bs / div, q.pair ? 112u : (uint32_t)q.bn);
     if (!ok) return (int32_t)cudaErrorInvalidValue;
 
+    if (q.pair) return q.f4 ? mx_launch_pair<true>(ma, mb, a, stream) : mx_launch_pair<false>(ma, mb, a, stream);
     if (q.bn == 224) return q.f4 ? mx_launch_one<224, true>(ma, mb, a, stream) : mx_launch_one<224, false>(ma, mb, a, stream);
     return q.f4 ? mx_launch_one<128, true>(ma, mb, a, stream) : mx_launch_one<128, false>(ma, mb, a, stream);
 }

@@ -614,6 +614,7 @@ int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs
 
 #include "qmm_mx_umma.cuh"
 #include "qmm_umma_pair.cuh"
+#include "qmm_mx_umma_pair.cuh"
 
 bool qmm_umma_eligible(const OpsnnQmmParams* p)
 {

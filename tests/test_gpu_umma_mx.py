@@ -26,6 +26,7 @@ def _q(rng, shape, dt):
 
 
 def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel, bn=None):
+    """bn: 128 | 224 (host tile selection override) | "pair" (224-column tiles on CTA pairs, tcgen05 cta_group::2)."""
     import os
 
     import torch
@@ -36,13 +37,19 @@ def _run(aclnn, x1, x2, s1, s2, bias, t1, t2, out_name, expect_kernel, bn=None):
     n = x2.shape[-2] if t2 else x2.shape[-1]
     batch = tuple(x1.shape[:-2])
     out = out_tensor(batch + (m, n), out_name)
-    if bn:
+    if bn == "pair":
+        os.environ["OPSNN_QMM_MX_BN"] = "224"
+        os.environ["OPSNN_QMM_PAIR"] = "1"
+        expect_kernel = expect_kernel.replace("qmm_umma_", "qmm_umma_pair_")
+    elif bn:
         os.environ["OPSNN_QMM_MX_BN"] = str(bn)  # host tile selection override: 128- or 224-column tiles
+        os.environ["OPSNN_QMM_PAIR"] = "0"
     try:
         aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
                               aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), t1, t2, GROUP_MX)
     finally:
         os.environ.pop("OPSNN_QMM_MX_BN", None)
+        os.environ.pop("OPSNN_QMM_PAIR", None)
     torch.cuda.synchronize()
     assert aclnn.last_kernel_name() == expect_kernel, aclnn.last_kernel_name()
     assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
@@ -80,7 +87,7 @@ MX8_CASES = [
 ]
 
 
-@pytest.mark.parametrize("bn", [128, 224])
+@pytest.mark.parametrize("bn", [128, 224, "pair"])
 @pytest.mark.parametrize("case", MX8_CASES, ids=[str(c[:6]) for c in MX8_CASES])
 def test_mxfp8_tcgen05(aclnn, case, bn):
     batch, m, k, n, t1, t2, da, db, bias_kind, out_name = case
@@ -105,7 +112,7 @@ MX4_CASES = [
 ]
 
 
-@pytest.mark.parametrize("bn", [128, 224])
+@pytest.mark.parametrize("bn", [128, 224, "pair"])
 @pytest.mark.parametrize("case", MX4_CASES, ids=[str(c[:4]) for c in MX4_CASES])
 def test_mxfp4_tcgen05(aclnn, case, bn):
     batch, m, k, n, bias_kind, out_name = case
