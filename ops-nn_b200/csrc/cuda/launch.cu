@@ -30,6 +30,7 @@ uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+int32_t wqbmm_decode_ring_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact);
 
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
 
@@ -85,6 +86,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE) {
         if (!wqbmm_decode_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        // same arithmetic, two data paths: shared-memory ring + ldmatrix where the layout allows it (32-column pieces, 16-byte
+        // aligned rows, groups of whole step pairs), register prefetch otherwise
+        if (wqbmm_decode_fast_eligible(p) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr)
+            return wqbmm_decode_ring_launch(p, static_cast<cudaStream_t>(stream), true);
         return wqbmm_decode_launch(p, static_cast<cudaStream_t>(stream));
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) {

@@ -70,7 +70,10 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4])
                  : "r"(addr));
 }
 
-template <bool kBf16, bool kHasOffset>
+// kExact = false: the group-wise form described above. kExact = true: the same data path (cp.async ring, ldmatrix
+// fragments, barrier-free main loop) with the reference's default arithmetic instead: every weight pair goes through
+// sub / add / mul in the activation dtype (two roundings, no FMA) before the MMA, exactly as in wqbmm_decode.cu.
+template <bool kBf16, bool kHasOffset, bool kExact>
 __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const DecodeArgs a)
 {
     using N = Num<kBf16>;
@@ -153,8 +156,14 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     const int64_t scol1 = (warp_col + 32 + 8 * q < a.n) ? warp_col + 32 + 8 * q : 0;
     uint32_t raw_s[8], raw_o[8];
     const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+    // exact mode: scale/offset of the lane's B-fragment columns (tile t < 4: column 4g + t, else 32 + 4g + t - 4), each
+    // duplicated into both halves of a register (the halves are two k rows of the same column)
+    const int64_t ecol0 = (warp_col + 4 * g < a.n) ? warp_col + 4 * g : 0;
+    const int64_t ecol1 = (warp_col + 32 + 4 * g < a.n) ? warp_col + 32 + 4 * g : 0;
+    uint32_t sc[kTiles], of[kTiles];
 
     auto finish_group = [&]() {
+        if (kExact) return;
 #pragma unroll
         for (int idx = 0; idx < 16; ++idx) {  // idx = 8*half + 4*(e&1) + (t&3): position among the lane's 16 columns
             const uint32_t rs = raw_s[idx >> 1];
@@ -173,6 +182,34 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
         xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
     };
     auto load_group = [&](int64_t group) {
+        if (kExact) {
+            uint32_t rs[4], ro[4] = {0u, 0u, 0u, 0u};
+            if (a.scale_sn != 0) {
+                const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+                const uint2 s0 = __ldg(reinterpret_cast<const uint2*>(sp + ecol0)), s1 = __ldg(reinterpret_cast<const uint2*>(sp + ecol1));
+                rs[0] = s0.x; rs[1] = s0.y; rs[2] = s1.x; rs[3] = s1.y;
+                if (kHasOffset) {
+                    const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+                    const uint2 o0 = __ldg(reinterpret_cast<const uint2*>(op + ecol0)), o1 = __ldg(reinterpret_cast<const uint2*>(op + ecol1));
+                    ro[0] = o0.x; ro[1] = o0.y; ro[2] = o1.x; ro[3] = o1.y;
+                }
+            } else {
+                const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+                const uint32_t ov = kHasOffset ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    rs[i] = sv | (sv << 16);
+                    ro[i] = ov | (ov << 16);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) {
+                const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
+                sc[t] = prmt(rs[t >> 1], rs[t >> 1], sel);
+                if (kHasOffset) of[t] = prmt(ro[t >> 1], ro[t >> 1], sel);
+            }
+            return;
+        }
         if (a.scale_sn != 0) {
             const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
             const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(sp + scol0)), s1 = __ldg(reinterpret_cast<const uint4*>(sp + scol1));
@@ -197,6 +234,26 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     // one k-step: 4 registers of paired nibbles -> 16 B fragments (a shift and a logic op each) -> 8 MMAs + the row-sum MMA
     auto compute = [&](const uint32_t(&w4)[4], const uint32_t(&af)[4]) {
         uint32_t b0[kTiles], b1[kTiles];
+        if (kExact) {
+            // (nibble ^ 8) | magic == B + w exactly; then the reference's rounding points: w' = mul(add(sub(v, B), offset), scale)
+            auto deq = [&](uint32_t tw, int t) {
+                uint32_t v;
+                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(tw), "r"(a.c_mask), "r"(a.c_magic));
+                v = N::sub(v, a.c_bias);
+                if (kHasOffset) v = N::add(v, of[t]);
+                return N::mul(v, sc[t]);
+            };
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                b0[t] = deq(w4[0] >> (4 * t), t);
+                b1[t] = deq(w4[1] >> (4 * t), t);
+                b0[4 + t] = deq(w4[2] >> (4 * t), 4 + t);
+                b1[4 + t] = deq(w4[3] >> (4 * t), 4 + t);
+            }
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) N::mma_free(total[t], af, b0[t], b1[t]);
+            return;
+        }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(w4[0] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
@@ -267,10 +324,10 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
 }
 
-int g_fast_ctas_per_sm[4] = {0, 0, 0, 0};
+int g_fast_ctas_per_sm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 int g_fast_sm_count = 0;
 
-template <bool kBf16, bool kHasOffset>
+template <bool kBf16, bool kHasOffset, bool kExact>
 int fast_grid(int variant)
 {
     if (g_fast_sm_count == 0) {
@@ -279,9 +336,9 @@ int fast_grid(int variant)
         cudaDeviceGetAttribute(&g_fast_sm_count, cudaDevAttrMultiProcessorCount, dev);
     }
     if (g_fast_ctas_per_sm[variant] == 0) {
-        cudaFuncSetAttribute(wqbmm_decode_fast_kernel<kBf16, kHasOffset>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFastSmem);
+        cudaFuncSetAttribute(wqbmm_decode_fast_kernel<kBf16, kHasOffset, kExact>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFastSmem);
         int nb = 0;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, wqbmm_decode_fast_kernel<kBf16, kHasOffset>, kThreads, kFastSmem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, wqbmm_decode_fast_kernel<kBf16, kHasOffset, kExact>, kThreads, kFastSmem);
         g_fast_ctas_per_sm[variant] = nb > 0 ? nb : 1;
     }
     return g_fast_sm_count * g_fast_ctas_per_sm[variant];
@@ -304,7 +361,8 @@ bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p)
     return true;
 }
 
-int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+// exact = false: group-wise high-performance mode; exact = true: the default arithmetic on the same data path.
+int32_t wqbmm_decode_ring_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact)
 {
     DecodeArgs a{};
     a.w = reinterpret_cast<const uint32_t*>(p->w);
@@ -326,13 +384,17 @@ int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     a.ksteps = p->k / 16;
     a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
     const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
-    const int variant = (bf16 ? 2 : 0) + (has_off ? 1 : 0);
+    const int variant = (exact ? 4 : 0) + (bf16 ? 2 : 0) + (has_off ? 1 : 0);
     int resident = 0;
     switch (variant) {
-        case 0: resident = fast_grid<false, false>(0); break;
-        case 1: resident = fast_grid<false, true>(1); break;
-        case 2: resident = fast_grid<true, false>(2); break;
-        default: resident = fast_grid<true, true>(3); break;
+        case 0: resident = fast_grid<false, false, false>(0); break;
+        case 1: resident = fast_grid<false, true, false>(1); break;
+        case 2: resident = fast_grid<true, false, false>(2); break;
+        case 3: resident = fast_grid<true, true, false>(3); break;
+        case 4: resident = fast_grid<false, false, true>(4); break;
+        case 5: resident = fast_grid<false, true, true>(5); break;
+        case 6: resident = fast_grid<true, false, true>(6); break;
+        default: resident = fast_grid<true, true, true>(7); break;
     }
     int64_t splits = resident / a.strips;
     if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
@@ -357,15 +419,21 @@ int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     a.nonce = next_nonce();
     a.c_mask = 0x000F000Fu;
     a.c_magic = bf16 ? Num<true>::kMagic : Num<false>::kMagic;
-    a.c_bias = 0;
+    a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
     switch (variant) {
-        case 0: wqbmm_decode_fast_kernel<false, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
-        case 1: wqbmm_decode_fast_kernel<false, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
-        case 2: wqbmm_decode_fast_kernel<true, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
-        default: wqbmm_decode_fast_kernel<true, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 0: wqbmm_decode_fast_kernel<false, false, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 1: wqbmm_decode_fast_kernel<false, true, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 2: wqbmm_decode_fast_kernel<true, false, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 3: wqbmm_decode_fast_kernel<true, true, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 4: wqbmm_decode_fast_kernel<false, false, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 5: wqbmm_decode_fast_kernel<false, true, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        case 6: wqbmm_decode_fast_kernel<true, false, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
+        default: wqbmm_decode_fast_kernel<true, true, true><<<grid, kThreads, kFastSmem, stream>>>(a); break;
     }
-    note_launch("wqbmm_decode_fast");
+    note_launch(exact ? "wqbmm_decode" : "wqbmm_decode_fast");
     return (int32_t)cudaGetLastError();
 }
+
+int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream) { return wqbmm_decode_ring_launch(p, stream, false); }
 
 }  // namespace opsnn
