@@ -41,6 +41,7 @@ struct DecodeArgs {
     int32_t m;
     int64_t n, k;
     int64_t strips, ksteps, splits, steps_per_group;
+    int32_t cluster;       // ring kernels: the k-splits of a strip form a thread-block cluster (CTA index = strip * splits + split)
     int64_t k_align;       // group-wise kernel only: k ranges start and end on multiples of this many k-steps (even)
     unsigned long long* tags;  // [gridDim]
     float4* partials;          // [gridDim][kWarps][kTiles][32]
@@ -139,6 +140,30 @@ struct Num<false> {
     }
 };
 
+// Writes one warp's 16 x 64 block of y from its accumulator fragments (+ bias), undoing the column permutation of the MMA tiles.
+template <bool kBf16, int kLayout>
+__device__ __forceinline__ void store_tile_y(const DecodeArgs& a, float (&acc)[kTiles][4], int64_t strip, int warp, int lane)
+{
+    const int g = lane >> 2, q = lane & 3;
+
+                // D fragment: rows g, g+8; tile-local columns 2q, 2q+1 = lane groups 2q, 2q+1 of the loader
+                const int64_t colw = strip * kStripCols + warp * kWarpCols;
+    #pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int row = g + (e >> 1) * 8;
+                        // kLayout 0: tile t is nibble t of the lane group's word; 1: the ldmatrix layout of the group-wise kernel
+                const int64_t col = colw + (kLayout == 0 ? 8 * (2 * q + (e & 1)) + t : 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3));
+                        if (row < a.m && col < a.n) {
+                            float f = acc[t][e];
+                            if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
+                            store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
+                        }
+                    }
+                }
+}
+
 // Cross-CTA combination of a strip's k-split contributors, then the write of y. Every contributor stores its fp32
 // fragments, then a launch nonce; whichever contributor observes all nonces present (at least one does: store, fence.sc,
 // load) adds the fragments in CTA order - so the result does not depend on arrival order - writes y and zeroes the
@@ -205,24 +230,7 @@ __device__ __forceinline__ void combine_and_store(const DecodeArgs& a, float (&a
                         asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.tags + strip + j * a.strips), "l"(0ull) : "memory");
                 }
             }
-            if (do_write) {
-                // D fragment: rows g, g+8; tile-local columns 2q, 2q+1 = lane groups 2q, 2q+1 of the loader
-                const int64_t colw = strip * kStripCols + warp * kWarpCols;
-    #pragma unroll
-                for (int t = 0; t < kTiles; ++t) {
-    #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int row = g + (e >> 1) * 8;
-                        // kLayout 0: tile t is nibble t of the lane group's word; 1: the ldmatrix layout of the group-wise kernel
-                const int64_t col = colw + (kLayout == 0 ? 8 * (2 * q + (e & 1)) + t : 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3));
-                        if (row < a.m && col < a.n) {
-                            float f = acc[t][e];
-                            if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
-                            store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
-                        }
-                    }
-                }
-            }
+            if (do_write) store_tile_y<kBf16, kLayout>(a, acc, strip, warp, lane);
 }
 
 }  // namespace

@@ -85,8 +85,8 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     uint16_t(*xs)[kFXPitch] = reinterpret_cast<uint16_t(*)[kFXPitch]>(dyn + kRingBytes);
 
     const int64_t c = blockIdx.x;
-    const int64_t strip = c % a.strips;
-    const int64_t chunk = c / a.strips;
+    const int64_t strip = a.cluster ? c / a.splits : c % a.strips;
+    const int64_t chunk = a.cluster ? c % a.splits : c / a.strips;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a.x);
     // this CTA's k range, in k-steps; both ends are multiples of k_align (a whole number of k-groups when there are enough
     // groups to go round, else of step pairs), so a pair of steps never straddles a group
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
             // (nibble ^ 8) | magic == B + w exactly; then the reference's rounding points: w' = mul(add(sub(v, B), offset), scale)
             auto deq = [&](uint32_t tw, int t) {
                 uint32_t v;
-                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(tw), "r"(a.c_mask), "r"(a.c_magic));
+                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(tw), "n"(0x000F000F), "n"(N::kMagic));
                 v = N::sub(v, a.c_bias);
                 if (kHasOffset) v = N::add(v, of[t]);
                 return N::mul(v, sc[t]);
@@ -256,10 +256,10 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
         }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(w4[0] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[t]) : "r"(w4[1] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[4 + t]) : "r"(w4[2] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
-            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[4 + t]) : "r"(w4[3] >> (4 * t)), "r"(a.c_mask), "r"(a.c_magic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(w4[0] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[t]) : "r"(w4[1] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[4 + t]) : "r"(w4[2] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[4 + t]) : "r"(w4[3] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
         }
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) N::mma_free(part[t], af, b0[t], b1[t]);
@@ -321,7 +321,41 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
+    if (!a.cluster) {
+        combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
+        return;
+    }
+    // ---- the strip's k-splits are one cluster: fragments go to each CTA's own shared memory (the warp's part of the ring, all
+    // of whose copies have landed and been read), the first CTA sums them over distributed shared memory in split order ----
+    const uint32_t frag = ring + (uint32_t)lane * 16;  // [tile][lane] float4, 4 KB of the warp's 6 KB
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(frag + t * 512), "f"(total[t][0]), "f"(total[t][1]), "f"(total[t][2]),
+                     "f"(total[t][3])
+                     : "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (chunk == 0) {
+        for (uint32_t j = 1; j < (uint32_t)a.splits; ++j) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(frag), "r"(j));
+            float4 v[kTiles];
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t)
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(v[t].x), "=f"(v[t].y), "=f"(v[t].z), "=f"(v[t].w)
+                             : "r"(remote + t * 512)
+                             : "memory");
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) {
+                total[t][0] += v[t].x; total[t][1] += v[t].y; total[t][2] += v[t].z; total[t][3] += v[t].w;
+            }
+        }
+    }
+    // nobody leaves (and frees its shared memory) before the first CTA has read everything
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (chunk == 0) store_tile_y<kBf16, 1>(a, total, strip, warp, lane);
 }
 
 int g_fast_ctas_per_sm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -413,13 +447,46 @@ int32_t wqbmm_decode_ring_launch(const OpsnnWqbmmParams* p, cudaStream_t stream,
     if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
     const int grid = (int)grid64;
     const uint64_t tag_bytes = (((uint64_t)kFastMaxGrid * 8 + 255) / 256) * 256;
-    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
+    // Opt-in (OPSNN_WQ_DECODE_CLUSTER=1): measured equal to the workspace combine on the benchmark shape (the tail is set by the
+    // slowest CTA's main loop, not by the combination), so the path that needs no cluster scheduling stays the default.
+    const bool want_cluster = splits >= 2 && splits <= 8 && getenv("OPSNN_WQ_DECODE_CLUSTER") != nullptr;
+    if (splits > 1 && !want_cluster && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p)))
+        return (int32_t)cudaErrorInvalidValue;
     a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
     a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
     a.nonce = next_nonce();
     a.c_mask = 0x000F000Fu;
     a.c_magic = bf16 ? Num<true>::kMagic : Num<false>::kMagic;
     a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
+    // the k-splits of a strip as one thread-block cluster (portable sizes only): the combination then needs no global memory
+    a.cluster = want_cluster ? 1 : 0;
+    if (a.cluster) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid, 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kFastSmem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = (unsigned)splits;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        cudaError_t rc;
+        switch (variant) {
+            case 0: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<false, false, false>, a); break;
+            case 1: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<false, true, false>, a); break;
+            case 2: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<true, false, false>, a); break;
+            case 3: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<true, true, false>, a); break;
+            case 4: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<false, false, true>, a); break;
+            case 5: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<false, true, true>, a); break;
+            case 6: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<true, false, true>, a); break;
+            default: rc = cudaLaunchKernelEx(&cfg, wqbmm_decode_fast_kernel<true, true, true>, a); break;
+        }
+        note_launch(exact ? "wqbmm_decode" : "wqbmm_decode_fast");
+        return (int32_t)rc;
+    }
     switch (variant) {
         case 0: wqbmm_decode_fast_kernel<false, false, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;
         case 1: wqbmm_decode_fast_kernel<false, true, false><<<grid, kThreads, kFastSmem, stream>>>(a); break;

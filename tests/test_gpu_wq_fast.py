@@ -90,3 +90,18 @@ def test_fast_mode_c2_shape_properties(aclnn):
     rms = np.sqrt(np.mean(ref ** 2))
     rel = np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 0.05 * rms))
     assert rel <= 2.0 ** -8 * 1.05, rel
+
+
+@pytest.mark.parametrize("inner_precise", [0, 1])
+def test_cluster_combine_matches_workspace_combine(aclnn, monkeypatch, inner_precise):
+    """The k-splits of a strip launched as one thread-block cluster (fragments summed over distributed shared memory, no
+    global scratch) give bit for bit what the workspace combination gives: same split boundaries, same summation order."""
+    from gpu_util import run_wq_fixture
+
+    a, meta = load_golden("wq_bf16_s4_group128_offset_m16")
+    monkeypatch.setenv("OPSNN_WQ_DECODE_SPLITS", "2")
+    y_ws = run_wq_fixture(aclnn, a, meta, kernel=0, api="v3", inner_precise=inner_precise)
+    monkeypatch.setenv("OPSNN_WQ_DECODE_CLUSTER", "1")
+    y_cl = run_wq_fixture(aclnn, a, meta, kernel=0, api="v3", inner_precise=inner_precise)
+    assert aclnn.last_kernel_name() == ("wqbmm_decode_fast" if inner_precise else "wqbmm_decode")
+    assert np.array_equal(y_ws.view(np.uint16), y_cl.view(np.uint16))
