@@ -181,33 +181,40 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
         for (int t = 0; t < kTiles; ++t) part[t][0] = part[t][1] = part[t][2] = part[t][3] = 0.f;
         xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
     };
+    uint32_t rs_next[4], ro_next[4] = {0u, 0u, 0u, 0u};
+    const int64_t n_groups = (a.ksteps + spg - 1) / spg;
+    auto fetch_exact = [&](int64_t group) {
+        if (a.scale_sn != 0) {
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+            const uint2 s0 = __ldg(reinterpret_cast<const uint2*>(sp + ecol0)), s1 = __ldg(reinterpret_cast<const uint2*>(sp + ecol1));
+            rs_next[0] = s0.x; rs_next[1] = s0.y; rs_next[2] = s1.x; rs_next[3] = s1.y;
+            if (kHasOffset) {
+                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+                const uint2 o0 = __ldg(reinterpret_cast<const uint2*>(op + ecol0)), o1 = __ldg(reinterpret_cast<const uint2*>(op + ecol1));
+                ro_next[0] = o0.x; ro_next[1] = o0.y; ro_next[2] = o1.x; ro_next[3] = o1.y;
+            }
+        } else {
+            const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+            const uint32_t ov = kHasOffset ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                rs_next[i] = sv | (sv << 16);
+                ro_next[i] = ov | (ov << 16);
+            }
+        }
+    };
+    if (kExact) fetch_exact(sa / spg);
     auto load_group = [&](int64_t group) {
         if (kExact) {
-            uint32_t rs[4], ro[4] = {0u, 0u, 0u, 0u};
-            if (a.scale_sn != 0) {
-                const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
-                const uint2 s0 = __ldg(reinterpret_cast<const uint2*>(sp + ecol0)), s1 = __ldg(reinterpret_cast<const uint2*>(sp + ecol1));
-                rs[0] = s0.x; rs[1] = s0.y; rs[2] = s1.x; rs[3] = s1.y;
-                if (kHasOffset) {
-                    const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
-                    const uint2 o0 = __ldg(reinterpret_cast<const uint2*>(op + ecol0)), o1 = __ldg(reinterpret_cast<const uint2*>(op + ecol1));
-                    ro[0] = o0.x; ro[1] = o0.y; ro[2] = o1.x; ro[3] = o1.y;
-                }
-            } else {
-                const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
-                const uint32_t ov = kHasOffset ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    rs[i] = sv | (sv << 16);
-                    ro[i] = ov | (ov << 16);
-                }
-            }
+            // the values fetched one group ago become this group's registers; the next group's are requested now, so that
+            // their L2 round trip is not in front of the group's first dequantisation
 #pragma unroll
             for (int t = 0; t < kTiles; ++t) {
                 const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
-                sc[t] = prmt(rs[t >> 1], rs[t >> 1], sel);
-                if (kHasOffset) of[t] = prmt(ro[t >> 1], ro[t >> 1], sel);
+                sc[t] = prmt(rs_next[t >> 1], rs_next[t >> 1], sel);
+                if (kHasOffset) of[t] = prmt(ro_next[t >> 1], ro_next[t >> 1], sel);
             }
+            fetch_exact(min(group + 1, n_groups - 1));
             return;
         }
         if (a.scale_sn != 0) {
