@@ -203,6 +203,7 @@ QMM_WORKLOADS = {
     "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
     "c4": (8, 8192, 8192, 8192, "mxfp4"),           # both operands e2m1 + e8m0/32, x2 stored (n,k) with transposeX2 = true
     "c4s": (2, 4096, 4096, 4096, "mxfp4"),          # small form of c4 (profiling)
+    "c4n": (8, 8192, 8192, 8192, "mxfp4_n"),        # c4 with the weight stored (k,n): transposed into workspace by a pre-pass
     "c5": (32, 2048, 4096, 14336, "mxfp8_dq"),      # bf16 activations -> dynamic mx quant -> mxfp8 matmul + fp32 bias
     "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
     "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
@@ -224,20 +225,22 @@ def run_qmm_workload(args):
     if kind.startswith("mx"):
         # batched mx workloads: the operands (>= 270 MB per call) exceed L2 by themselves, one weight set
         sets = 1
-        f4 = kind == "mxfp4"
+        f4 = kind.startswith("mxfp4")
         kq = k // 64
         out = torch.empty((b, m, n), dtype=torch.bfloat16, device=dev)
         rnd_scale = lambda *shape: torch.randint(124, 131, shape, generator=gen, device=dev, dtype=torch.uint8)  # noqa: E731
         if f4:
             x1 = torch.randint(0, 256, (b, m, k // 2), generator=gen, device=dev, dtype=torch.uint8)  # two e2m1 per byte
-            x2 = torch.randint(0, 256, (b, n, k // 2), generator=gen, device=dev, dtype=torch.uint8)
+            nmaj = kind == "mxfp4_n"
+            x2 = torch.randint(0, 256, (b, k, n // 2) if nmaj else (b, n, k // 2), generator=gen, device=dev, dtype=torch.uint8)
             d_x1 = aclnn.from_torch(x1, "float4_e2m1", (b, m, k), (m * k, k, 1))
-            d_x2 = aclnn.from_torch(x2, "float4_e2m1", (b, n, k), (n * k, k, 1))  # stored (n,k): transposeX2 = true
-            s1, s2 = rnd_scale(b, m, kq, 2), rnd_scale(b, n, kq, 2)
+            d_x2 = (aclnn.from_torch(x2, "float4_e2m1", (b, k, n), (n * k, n, 1)) if nmaj
+                    else aclnn.from_torch(x2, "float4_e2m1", (b, n, k), (n * k, k, 1)))  # stored (n,k): transposeX2 = true
+            s1, s2 = rnd_scale(b, m, kq, 2), (rnd_scale(b, kq, n, 2) if nmaj else rnd_scale(b, n, kq, 2))
             d_s1 = aclnn.from_torch(s1, "float8_e8m0")
             d_s2 = aclnn.from_torch(s2, "float8_e8m0")
             dout = aclnn.from_torch(out)
-            call = lambda i: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, None, False, True, (1 << 32) | (1 << 16) | 32)  # noqa: E731
+            call = lambda i: aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, dout, None, False, not nmaj, (1 << 32) | (1 << 16) | 32)  # noqa: E731
             nbytes = b * (m * k // 2 + n * k // 2 + (m + n) * kq * 2 + 2 * m * n)
         else:
             tb = kind == "mxfp8_t"
@@ -303,7 +306,7 @@ def run_qmm_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 9000.0 if kind == "mxfp4" else 4500.0
+    peak8 = 9000.0 if kind.startswith("mxfp4") else 4500.0
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
                       "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,

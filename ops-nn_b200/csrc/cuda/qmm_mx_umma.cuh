@@ -59,6 +59,64 @@ __global__ void mx_sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* 
     }
 }
 
+// fp4 operands stored along m / n (x1 given as (k,m), x2 as (k,n)) cannot be fed to the tensor core (kind::mxf4 has no MN-major
+// form); a pre-pass rewrites them k-contiguous into workspace: (R, C) packed along C -> (C, R) packed along R, two e2m1 per
+// byte, low nibble first. 64 x 64 element tiles through shared memory; ~1.5 % of the matmul's time at the benchmark shape.
+__global__ void __launch_bounds__(256) fp4_transpose_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t R, int64_t C,
+                                                            int64_t src_pitch, int64_t dst_pitch, int64_t src_bs, int64_t dst_bs)
+{
+    __shared__ __align__(16) uint8_t tile[64][68];  // one element per byte
+    const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+    const uint8_t* s = src + (int64_t)blockIdx.z * src_bs;
+    uint8_t* d = dst + (int64_t)blockIdx.z * dst_bs;
+    const int t = threadIdx.x;
+    const bool whole = r0 + 64 <= R && c0 + 64 <= C && (src_pitch & 7) == 0 && (dst_pitch & 7) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 7) == 0;
+    {
+        const int row = t >> 2, seg = t & 3;  // 8 source bytes = 16 elements of one row
+        const int64_t r = r0 + row;
+        if (whole) {
+            const uint2 v = *reinterpret_cast<const uint2*>(s + r * src_pitch + c0 / 2 + seg * 8);
+            const uint32_t w[2] = {v.x, v.y};
+            uint32_t* trow = reinterpret_cast<uint32_t*>(&tile[row][seg * 16]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                // 8 nibbles -> 8 bytes: even nibbles and odd nibbles separated, then interleaved byte-wise
+                const uint32_t lo = w[h] & 0x0F0F0F0Fu, hi = (w[h] >> 4) & 0x0F0F0F0Fu;
+                trow[2 * h] = __byte_perm(lo, hi, 0x5140);      // e0 e1 e2 e3
+                trow[2 * h + 1] = __byte_perm(lo, hi, 0x7362);  // e4 e5 e6 e7
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t c = c0 + seg * 16 + 2 * j;
+                uint8_t v = 0;
+                if (r < R && c < C) v = s[r * src_pitch + c / 2];
+                tile[row][seg * 16 + 2 * j] = v & 0xF;
+                tile[row][seg * 16 + 2 * j + 1] = (c + 1 < C) ? (v >> 4) : 0;
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const int crow = t >> 2, seg = t & 3;  // 8 destination bytes = 16 elements of one destination row
+        const int64_t c = c0 + crow;
+        if (whole) {
+            uint32_t o[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                o[j >> 2] |= (uint32_t)(tile[seg * 16 + 2 * j][crow] | (tile[seg * 16 + 2 * j + 1][crow] << 4)) << (8 * (j & 3));
+            *reinterpret_cast<uint2*>(d + c * dst_pitch + r0 / 2 + seg * 8) = make_uint2(o[0], o[1]);
+        } else if (c < C) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t r = r0 + seg * 16 + 2 * j;
+                if (r < R) d[c * dst_pitch + r / 2] = (uint8_t)(tile[seg * 16 + 2 * j][crow] | (tile[seg * 16 + 2 * j + 1][crow] << 4));
+            }
+        }
+    }
+}
+
 template <int BN, bool kF4>
 __global__ void __launch_bounds__(192, 1)
 qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
@@ -289,6 +347,8 @@ struct MxPlan {
     int bn, atoms, row_atoms;
     int64_t tiles_m, tiles_n, kstages, kblocks32, kq;
     uint64_t sfa_bytes_per_batch, sfb_bytes_per_batch, nb_a, nb_b;
+    bool tr_a, tr_b;               // fp4 operand stored along m / n: rewritten k-contiguous into workspace first
+    uint64_t tr_a_bytes, tr_b_bytes;  // whole operand, all batches
 };
 
 // Host tile selection: 224-column tiles (less operand traffic per flop) whenever they still give every SM a tile.
@@ -321,6 +381,10 @@ MxPlan mx_plan(const OpsnnQmmParams* p)
     q.kq = (p->k + 63) / 64;
     q.nb_a = p->sa_bs != 0 ? (uint64_t)p->batch : 1;
     q.nb_b = p->sb_bs != 0 ? (uint64_t)p->batch : 1;
+    q.tr_a = q.f4 && p->trans_a != 0;
+    q.tr_b = q.f4 && p->trans_b == 0;
+    q.tr_a_bytes = q.tr_a ? (uint64_t)(p->a_bs != 0 ? p->batch : 1) * (uint64_t)p->m * (uint64_t)(p->k / 2) : 0;
+    q.tr_b_bytes = q.tr_b ? (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * (uint64_t)(p->k / 2) : 0;
     q.sfa_bytes_per_batch = (uint64_t)q.tiles_m * q.kstages * q.atoms * 512;
     q.sfb_bytes_per_batch = (uint64_t)q.tiles_n * q.kstages * q.atoms * q.row_atoms * 512;
     return q;
@@ -357,7 +421,6 @@ bool qmm_mx_umma_eligible(const OpsnnQmmParams* p)
     if (!f8 && !f4) return false;
     if (p->scale_b_dtype != ACL_FLOAT8_E8M0 || p->scale_a == nullptr || p->scale_b == nullptr) return false;
     if (p->group_k != 32 || p->k % 32 != 0) return false;
-    if (f4 && (p->trans_a != 0 || p->trans_b == 0)) return false;  // 4-bit operands must be k-contiguous
     if (p->out_dtype != ACL_BF16 && p->out_dtype != ACL_FLOAT16 && p->out_dtype != ACL_FLOAT) return false;
     if (p->bias != nullptr && p->bias_dtype != ACL_FLOAT && p->bias_dtype != ACL_BF16 && p->bias_dtype != ACL_FLOAT16) return false;
     const int64_t div = f4 ? 2 : 1;  // elements per byte
@@ -374,7 +437,7 @@ bool qmm_mx_umma_eligible(const OpsnnQmmParams* p)
 uint64_t qmm_mx_umma_workspace_size(const OpsnnQmmParams* p)
 {
     const MxPlan q = mx_plan(p);
-    return q.nb_a * q.sfa_bytes_per_batch + q.nb_b * q.sfb_bytes_per_batch + 256;
+    return q.nb_a * q.sfa_bytes_per_batch + q.nb_b * q.sfb_bytes_per_batch + q.tr_a_bytes + q.tr_b_bytes + 3 * 256;
 }
 
 int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
@@ -399,6 +462,30 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
                                                                   q.bn, q.row_atoms);
         note_launch("mx_sf_relayout", 2);
     }
+    // ---- pre-pass: fp4 operands that are not k-contiguous ----
+    OpsnnQmmParams pk = *p;  // the operand views the matmul kernel sees
+    {
+        auto up = [](uint8_t* x) { return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(x) + 255) & ~(uintptr_t)255); };
+        uint8_t* next = up(sfb + q.nb_b * q.sfb_bytes_per_batch);
+        if (q.tr_a) {  // stored (k, m) -> (m, k)
+            const int64_t nb = p->a_bs != 0 ? p->batch : 1;
+            fp4_transpose_kernel<<<dim3((unsigned)((p->m + 63) / 64), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
+                reinterpret_cast<const uint8_t*>(p->a), next, p->k, p->m, p->a_ld / 2, p->k / 2, p->a_bs / 2, p->m * (p->k / 2));
+            pk.a = next; pk.a_ld = p->k; pk.a_bs = p->a_bs != 0 ? p->m * p->k : 0; pk.trans_a = 0;
+            next = up(next + q.tr_a_bytes);
+            note_launch("fp4_transpose");
+        }
+        if (q.tr_b) {  // stored (k, n) -> (n, k)
+            const int64_t nb = p->b_bs != 0 ? p->batch : 1;
+            fp4_transpose_kernel<<<dim3((unsigned)((p->n + 63) / 64), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
+                reinterpret_cast<const uint8_t*>(p->b), next, p->k, p->n, p->b_ld / 2, p->k / 2, p->b_bs / 2, p->n * (p->k / 2));
+            pk.b = next; pk.b_ld = p->k; pk.b_bs = p->b_bs != 0 ? p->n * p->k : 0; pk.trans_b = 1;
+            note_launch("fp4_transpose");
+        }
+    }
+    const OpsnnQmmParams* po = p;  // original: scale layouts follow the caller's storage
+    (void)po;
+    p = &pk;
     UmmaArgs a{};
     a.mode = p->mode;
     a.a_mn_major = p->trans_a ? 1 : 0;

@@ -170,3 +170,26 @@ def test_dynamic_mx_quant_streaming_kernel_matches_oracle(aclnn, dst, xdt):
     else:
         wy_bytes = wy.view(np.uint8)
     assert np.array_equal(y.cpu().numpy(), wy_bytes)
+
+
+MX4_LAYOUT_CASES = [
+    # batch, m, k, n, x1 stored (k,m), x2 stored (n,k)
+    ((), 128, 256, 160, False, False),     # x2 given as (k,n): rewritten k-contiguous by the pre-pass
+    ((), 192, 512, 352, True, True),       # x1 given as (k,m)
+    ((2,), 160, 384, 224, True, False),    # both, batched
+]
+
+
+@pytest.mark.parametrize("case", MX4_LAYOUT_CASES, ids=[str(c) for c in MX4_LAYOUT_CASES])
+def test_mxfp4_operands_stored_along_m_or_n(aclnn, case):
+    """kind::mxf4 only takes k-contiguous operands; the other storage orders the API allows go through a transpose pre-pass
+    into workspace and must give the same result as the oracle."""
+    batch, m, k, n, t1, t2 = case
+    rng = np.random.default_rng(abs(hash(str(case))) % (2 ** 31))
+    kq = -(-k // 64)
+    x1 = _q(rng, batch + ((k, m) if t1 else (m, k)), E2M1)
+    x2 = _q(rng, batch + ((n, k) if t2 else (k, n)), E2M1)
+    s1 = _e8m0(rng, batch + ((kq, m, 2) if t1 else (m, kq, 2)))
+    s2 = _e8m0(rng, batch + ((n, kq, 2) if t2 else (kq, n, 2)))
+    got = _run(aclnn, x1, x2, s1, s2, None, t1, t2, "bfloat16", "qmm_umma_mxfp4", 128)
+    _check(got, _oracle(x1, x2, s1, s2, None, t1, t2, "bfloat16"), "bfloat16")
