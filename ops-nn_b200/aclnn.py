@@ -74,7 +74,10 @@ def lib():
                                                                  POINTER(c_void_p)]
     L.aclnnDynamicMxQuantGetWorkspaceSize.argtypes = [T, c_int64, c_char_p, c_int64, c_int64, c_int64, T, T,
                                                        POINTER(c_uint64), POINTER(c_void_p)]
-    for name in ("aclnnQuantMatmulV5", "aclnnWeightQuantBatchMatmulV2", "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant"):
+    L.aclnnQuantMatmulV4GetWorkspaceSize.argtypes = [T, T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
+    L.aclnnQuantMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
+    for name in ("aclnnQuantMatmulV5", "aclnnQuantMatmulV4", "aclnnQuantMatmulV3", "aclnnWeightQuantBatchMatmulV2",
+                 "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant"):
         getattr(L, name).argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
         getattr(L, name).restype = c_int32
         getattr(L, name + "GetWorkspaceSize").restype = c_int32
@@ -188,6 +191,29 @@ def quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, y_scale, x1_o
                                                   _h(x2_offset), _h(y_offset), _h(bias), bool(transpose_x1),
                                                   bool(transpose_x2), int(group_size), _h(out), byref(ws), byref(ex))
     return st, ws.value, ex
+
+
+def quant_matmul_v4(x1, x2, scale, out, offset=None, pertoken_scale=None, bias=None, transpose_x1=False, transpose_x2=False,
+                    api="v4"):
+    """Runs aclnnQuantMatmulV4 (or V3 with api="v3": no per-token scale) on the current torch CUDA stream: the older entry
+    points of the same operator, argument order (scale, offset, pertokenScale, bias)."""
+    ws, ex = c_uint64(0), c_void_p(0)
+    L = lib()
+    if api == "v3":
+        st = L.aclnnQuantMatmulV3GetWorkspaceSize(_h(x1), _h(x2), _h(scale), _h(offset), _h(bias), bool(transpose_x1),
+                                                  bool(transpose_x2), _h(out), byref(ws), byref(ex))
+        name, run = "aclnnQuantMatmulV3", L.aclnnQuantMatmulV3
+    else:
+        st = L.aclnnQuantMatmulV4GetWorkspaceSize(_h(x1), _h(x2), _h(scale), _h(offset), _h(pertoken_scale), _h(bias),
+                                                  bool(transpose_x1), bool(transpose_x2), _h(out), byref(ws), byref(ex))
+        name, run = "aclnnQuantMatmulV4", L.aclnnQuantMatmulV4
+    if st != ACLNN_SUCCESS:
+        raise AclnnError(name + "GetWorkspaceSize", st)
+    keep, wp = _workspace(ws.value, out._keep)
+    st = run(wp, c_uint64(ws.value), ex, _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError(name, st)
+    return ws.value
 
 
 def weight_quant_batch_matmul_get_workspace_size(x, weight, antiquant_scale, antiquant_offset, quant_scale, quant_offset,

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <memory>
 
+#include "aclnnop/aclnn_quant_matmul_v4.h"
 #include "aclnnop/aclnn_quant_matmul_v5.h"
 #include "internal.h"
 
@@ -715,6 +716,36 @@ aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspaceSize, aclOpExe
         return ACLNN_ERR_RUNTIME_ERROR;
     }
     return ACLNN_SUCCESS;
+}
+
+// ---- older entry points of the same operator (matmul/quant_batch_matmul_v3/op_api/aclnn_quant_matmul_v4.h:41-60,
+// aclnn_quant_matmul_v3.h:40-58): argument order (scale, offset, pertokenScale, bias), no groupSize; same plans and kernels ----
+
+aclnnStatus aclnnQuantMatmulV4GetWorkspaceSize(const aclTensor* x1, const aclTensor* x2, const aclTensor* scale,
+                                               const aclTensor* offset, const aclTensor* pertokenScaleOptional,
+                                               const aclTensor* bias, bool transposeX1, bool transposeX2, const aclTensor* out,
+                                               uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    return aclnnQuantMatmulV5GetWorkspaceSize(x1, x2, pertokenScaleOptional, scale, nullptr, nullptr, offset, nullptr, bias, transposeX1,
+                                              transposeX2, 0, const_cast<aclTensor*>(out), workspaceSize, executor);
+}
+
+aclnnStatus aclnnQuantMatmulV4(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return aclnnQuantMatmulV5(workspace, workspaceSize, executor, stream);
+}
+
+aclnnStatus aclnnQuantMatmulV3GetWorkspaceSize(const aclTensor* x1, const aclTensor* x2, const aclTensor* scale,
+                                               const aclTensor* offset, const aclTensor* bias, bool transposeX1, bool transposeX2,
+                                               const aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    return aclnnQuantMatmulV5GetWorkspaceSize(x1, x2, nullptr, scale, nullptr, nullptr, offset, nullptr, bias, transposeX1, transposeX2, 0,
+                                              const_cast<aclTensor*>(out), workspaceSize, executor);
+}
+
+aclnnStatus aclnnQuantMatmulV3(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return aclnnQuantMatmulV5(workspace, workspaceSize, executor, stream);
 }
 
 }  // extern "C"

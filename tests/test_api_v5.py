@@ -120,3 +120,31 @@ def test_phase1_is_thread_safe(aclnn):
     [t.start() for t in ts]
     [t.join() for t in ts]
     assert not errors, errors
+
+
+def test_older_entry_points_share_the_v5_validator(aclnn):
+    """aclnnQuantMatmulV4 / V3 (argument order scale, offset, pertokenScale, bias) go through the same phase 1."""
+    import ctypes
+
+    L = aclnn.lib()
+    ws, ex = ctypes.c_uint64(7), ctypes.c_void_p(0)
+    x1 = aclnn.Tensor((128, 256), "int8")
+    x2 = aclnn.Tensor((256, 64), "int8")
+    sc = aclnn.Tensor((64,), "float32")
+    pt = aclnn.Tensor((128,), "float32")
+    out = aclnn.Tensor((128, 64), "bfloat16")
+    st = L.aclnnQuantMatmulV4GetWorkspaceSize(x1.handle, x2.handle, sc.handle, None, pt.handle, None, False, False, out.handle,
+                                              ctypes.byref(ws), ctypes.byref(ex))
+    assert st == aclnn.ACLNN_SUCCESS and ws.value == 0 and ex.value
+    aclnn.destroy_executor(ex)
+    st = L.aclnnQuantMatmulV3GetWorkspaceSize(x1.handle, x2.handle, sc.handle, None, None, False, False, out.handle,
+                                              ctypes.byref(ws), ctypes.byref(ex))
+    assert st == aclnn.ACLNN_SUCCESS
+    aclnn.destroy_executor(ex)
+    st = L.aclnnQuantMatmulV4GetWorkspaceSize(x1.handle, None, sc.handle, None, pt.handle, None, False, False, out.handle,
+                                              ctypes.byref(ws), ctypes.byref(ex))
+    assert st == aclnn.ACLNN_ERR_PARAM_NULLPTR
+    bad = aclnn.Tensor((128, 65), "bfloat16")
+    st = L.aclnnQuantMatmulV4GetWorkspaceSize(x1.handle, x2.handle, sc.handle, None, pt.handle, None, False, False, bad.handle,
+                                              ctypes.byref(ws), ctypes.byref(ex))
+    assert st == aclnn.ACLNN_ERR_PARAM_INVALID

@@ -173,3 +173,31 @@ def test_cta_pairs_batched_fp8_and_auto_selection(aclnn, monkeypatch):
     ref32 = qbmm_oracle.quant_matmul_v5(a1, a2, sc1, sc2, None, False, False, 0, "float32")
     got = _run(aclnn, a1, a2, sc1, sc2, None, False, False, 0, "bfloat16", "qmm_umma_pair_deq")
     check_close(got, want, ref32, "bfloat16")
+
+
+def test_older_entry_points_v4_v3_match_v5(aclnn):
+    """aclnnQuantMatmulV4 / V3 run the same plan and kernel as V5: bit-identical output."""
+    import torch
+
+    from gpu_util import desc, out_tensor, out_to_np
+
+    rng = np.random.default_rng(31)
+    m, k, n = 192, 512, 320
+    x1 = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, False, False, 0, "bfloat16")
+    out = out_tensor((m, n), "bfloat16")
+    aclnn.quant_matmul_v4(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s2), aclnn.Tensor(out.shape, "bfloat16", out),
+                          pertoken_scale=desc(aclnn, s1), bias=desc(aclnn, bias))
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == "qmm_umma_deq"
+    assert np.array_equal(out_to_np(out).view(np.uint16), want.view(np.uint16))
+    want3 = qbmm_oracle.quant_matmul_v5(x1, x2, None, s2, bias, False, False, 0, "bfloat16")
+    out3 = out_tensor((m, n), "bfloat16")
+    aclnn.quant_matmul_v4(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s2), aclnn.Tensor(out3.shape, "bfloat16", out3),
+                          bias=desc(aclnn, bias), api="v3")
+    torch.cuda.synchronize()
+    assert np.array_equal(out_to_np(out3).view(np.uint16), want3.view(np.uint16))
