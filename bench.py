@@ -199,6 +199,7 @@ QMM_WORKLOADS = {
     "c1": (1, 128, 4096, 4096, "int8_kc"),
     "c3": (1, 4096, 7168, 18432, "fp8_perblock"),
     "c3i8": (1, 4096, 7168, 18432, "int8_kc"),
+    "c3i8pb": (1, 4096, 7168, 18432, "int8_perblock"),  # int8 operands with the 1x128 / 128x128 fp32 scales of c3
     "c1t": (1, 128, 4096, 4096, "int8_kc_t"),      # same with x2 stored (n,k) and transposeX2 = true
     "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
     "c4": (8, 8192, 8192, 8192, "mxfp4"),           # both operands e2m1 + e8m0/32, x2 stored (n,k) with transposeX2 = true
@@ -278,8 +279,12 @@ def run_qmm_workload(args):
         call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, d[3], False, tb)  # noqa: E731
         nbytes = m * k + k * n + 4 * (m + 2 * n) + 2 * m * n
     else:
-        x1 = torch.randn((m, k), generator=gen, device=dev).to(torch.float8_e4m3fn)
-        x2s = [torch.randn((k, n), generator=gen, device=dev).to(torch.float8_e4m3fn) for _ in range(sets)]
+        if kind == "int8_perblock":
+            x1 = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
+            x2s = [torch.randint(-127, 128, (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
+        else:
+            x1 = torch.randn((m, k), generator=gen, device=dev).to(torch.float8_e4m3fn)
+            x2s = [torch.randn((k, n), generator=gen, device=dev).to(torch.float8_e4m3fn) for _ in range(sets)]
         s1 = torch.rand((m, k // 128), generator=gen, device=dev) + 0.5
         s2 = torch.rand((k // 128, n // 128), generator=gen, device=dev) + 0.5
         d = [aclnn.from_torch(t) for t in (x1, s1, s2)]

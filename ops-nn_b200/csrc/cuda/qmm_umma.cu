@@ -213,12 +213,28 @@ __device__ __forceinline__ void deq_store_cols(const UmmaArgs& a, uint32_t tmem_
                     }
 }
 
-template <int BN, bool kPerBlock, ptx::MmaKind kKind>
-__global__ void __launch_bounds__((((kPerBlock && BN == 256) ? 8 : 4) + 2) * 32, 1)
+// Per-block promotion of one accumulator value into the running fp32 sum. fp8: one fused multiply-add. int8: the
+// reference rounds the product and the sum separately (float32(int32 partial) * (s1 * s2), then +=), and the int8 mode is
+// tested bit for bit, so it is a multiply and an add here too; |partial| <= 128 * 127 * 127 < 2^22, so the conversion is
+// the exact add-a-constant form (integer add + float subtract) rather than the slower convert instruction.
+template <ptx::MmaKind kKind>
+__device__ __forceinline__ float promote(uint32_t v, float sc, float acc)
+{
+    if (kKind == ptx::MmaKind::kI8) {
+        const float f = __fsub_rn(__uint_as_float(v + 0x4B400000u), 12582912.f);
+        return __fadd_rn(acc, __fmul_rn(f, sc));
+    }
+    return fmaf(__uint_as_float(v), sc, acc);
+}
+
+template <int BN, bool kPerBlock, ptx::MmaKind kKind, int EW = 4>
+__global__ void __launch_bounds__((EW + 2) * 32, 1)
 qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
 {
-    constexpr int EW = (kPerBlock && BN == 256) ? 8 : 4;  // epilogue warps
-    constexpr int kCols = (kPerBlock && BN == 256) ? 128 : BN;  // accumulator columns one epilogue thread handles
+    // EW epilogue warps: warp w reads TMEM lane quarter w % 4 (a hardware rule) and the column slice w / 4
+    static_assert(EW % 4 == 0 && (kPerBlock || EW == 4), "dequant epilogue is written for four warps");
+    constexpr int kCols = BN * 4 / EW;  // accumulator columns one epilogue thread handles
+    static_assert(kCols >= 32, "one epilogue thread handles at least 32 columns");
     constexpr int kStage = Smem<BN>::kStage;
     constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulator buffers
 
@@ -463,7 +479,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             ptx::tmem_ld_wait();
                             ptx::tmem_ld16(t0 + c + W, vb);
 #pragma unroll
-                            for (int i = 0; i < W; ++i) acc[c + i] = fmaf(__uint_as_float(va[i]), sc, acc[c + i]);
+                            for (int i = 0; i < W; ++i) acc[c + i] = promote<kKind>(va[i], sc, acc[c + i]);
                             ptx::tmem_ld_wait();
                             if (c + 2 * W < kCols) {
                                 ptx::tmem_ld16(t0 + c + 2 * W, va);
@@ -473,7 +489,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
                             }
 #pragma unroll
-                            for (int i = 0; i < W; ++i) acc[c + W + i] = fmaf(__uint_as_float(vb[i]), sc, acc[c + W + i]);
+                            for (int i = 0; i < W; ++i) acc[c + W + i] = promote<kKind>(vb[i], sc, acc[c + W + i]);
                         }
                         ++grp;
                     }
@@ -487,6 +503,13 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             float f[32];
 #pragma unroll
                             for (int i = 0; i < 32; ++i) f[i] = acc[c + i];
+                            if (a.bias != nullptr) {
+                                const uint8_t* bias = reinterpret_cast<const uint8_t*>(a.bias) +
+                                                      b * a.bias_bs * ((a.bias_dtype == ACL_FLOAT || a.bias_dtype == ACL_INT32) ? 4 : 2);
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (i < valid) f[i] = __fadd_rn(f[i], load_as_float(bias, col + i, a.bias_dtype));
+                            }
                             store_row32(a, out, row, col, f, valid);
                         }
                     }
@@ -574,10 +597,9 @@ int pick_bn(const OpsnnQmmParams* p)
     return lo;
 }
 
-template <int BN, bool PB, ptx::MmaKind KIND>
+template <int BN, bool PB, ptx::MmaKind KIND, int EW = 4>
 int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
 {
-    constexpr int EW = (PB && BN == 256) ? 8 : 4;
     constexpr int kStage = Smem<BN>::kStage;
     int stages = (227 * 1024 - 2048) / kStage;
     if (stages > 8) stages = 8;
@@ -585,7 +607,7 @@ int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cu
     a.stages = stages;
     const size_t smem = (size_t)stages * kStage + 1024 + 256 + 2 * BN * 4;
     static bool configured = false;
-    auto kern = qmm_umma_kernel<BN, PB, KIND>;
+    auto kern = qmm_umma_kernel<BN, PB, KIND, EW>;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return (int32_t)cudaGetLastError();
@@ -597,12 +619,26 @@ int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cu
     return (int32_t)cudaGetLastError();
 }
 
+// Per-block epilogue width. The promotion is bound by instruction issue (one warp instruction per clock and SM
+// sub-partition): fp8 needs one fused multiply-add per element and four warps keep up; int8 needs four instructions
+// per element (exact conversion, multiply, add) and a second warp per sub-partition hides the TMEM load waits.
+template <ptx::MmaKind KIND>
+int32_t launch_pb(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
+{
+    if (bn == 256) return launch_one<256, true, KIND, 8>(ma, mb, a, stream);
+    int ew = KIND == ptx::MmaKind::kI8 ? 8 : 4;
+    if (const char* e = getenv("OPSNN_QMM_PB_EW")) ew = atoi(e);
+    if (ew == 8) return launch_one<128, true, KIND, 8>(ma, mb, a, stream);
+    return launch_one<128, true, KIND, 4>(ma, mb, a, stream);
+}
+
 template <bool PB, ptx::MmaKind KIND>
 int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
 {
+    if (PB) return launch_pb<KIND>(bn, ma, mb, a, stream);
     switch (bn) {
-        case 256: return launch_one<256, PB, KIND>(ma, mb, a, stream);
-        case 128: return launch_one<128, PB, KIND>(ma, mb, a, stream);
+        case 256: return launch_one<256, false, KIND>(ma, mb, a, stream);
+        case 128: return launch_one<128, false, KIND>(ma, mb, a, stream);
         case 64: if (!PB) return launch_one<64, false, KIND>(ma, mb, a, stream); break;
         case 32: if (!PB) return launch_one<32, false, KIND>(ma, mb, a, stream); break;
         default: break;
@@ -625,8 +661,7 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
     if (p->mode == OPSNN_QMM_DEQ) {
         if (!i8 && !f8) return false;
     } else if (p->mode == OPSNN_QMM_PERBLOCK) {
-        if (!f8 || p->group_k != 128 || p->group_n != 128 || (p->group_m != 1 && p->group_m != 128)) return false;
-        if (p->bias != nullptr) return false;
+        if ((!f8 && !i8) || p->group_k != 128 || p->group_n != 128 || (p->group_m != 1 && p->group_m != 128)) return false;
     } else {
         return false;
     }
@@ -681,7 +716,9 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (!ok) return (int32_t)cudaErrorInvalidValue;
     if (pair) return a.is_int ? launch_pair<ptx::MmaKind::kI8>(ma, mb, a, stream) : launch_pair<ptx::MmaKind::kF8F6F4>(ma, mb, a, stream);
 
-    if (p->mode == OPSNN_QMM_PERBLOCK) return launch_bn<true, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
+    if (p->mode == OPSNN_QMM_PERBLOCK)
+        return a.is_int ? launch_bn<true, ptx::MmaKind::kI8>(bn, ma, mb, a, stream)
+                        : launch_bn<true, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
     if (a.is_int) return launch_bn<false, ptx::MmaKind::kI8>(bn, ma, mb, a, stream);
     return launch_bn<false, ptx::MmaKind::kF8F6F4>(bn, ma, mb, a, stream);
 }

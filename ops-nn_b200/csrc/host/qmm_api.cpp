@@ -645,7 +645,6 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         if (!operand_batch(c.x2s, 3, ob, c.n * kq * 2, &p.sb_bs)) why_unsupported("x2Scale batch dims");
     } else if (c.perblock()) {
         p.mode = OPSNN_QMM_PERBLOCK;
-        if (c.int8_in()) why_unsupported("INT8 per-block (G-B) kernels are not built yet");
         if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
         if (!operand_batch(c.x1s, 2, ob, c.x1s.dim(-1) * c.x1s.dim(-2), &p.sa_bs)) why_unsupported("x1Scale batch dims");
         if (!operand_batch(c.x2s, 2, ob, c.x2s.dim(-1) * c.x2s.dim(-2), &p.sb_bs)) why_unsupported("x2Scale batch dims");

@@ -156,7 +156,9 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, t
         return compute_mx(x1, x2, x1_scale, x2_scale, bias, transpose_x1, transpose_x2, out_dtype)
     is_int = x1.dtype == np.int8
     fp8 = _is_fp8(x1.dtype)
-    if fp8 and x1_scale is not None and x1_scale.ndim > 1 and x2_scale.ndim > 1:
+    # fp8 per-block (qbmmv3_kernel_golden.py:237-358) and int8 per-tile (qbmmv4_kernel_golden.py:258-325) share the formula:
+    # int8 products and their 128-term sums are exact in fp32, so the float path restates the int32 matmul bit for bit
+    if (fp8 or is_int) and x1_scale is not None and x1_scale.ndim > 1 and x2_scale.ndim > 1:
         return compute_perblock(x1, x2, x1_scale, x2_scale, unpack_groupsize(group_size), transpose_x1, transpose_x2,
                                 out_dtype, bias)
     a = x1.T if transpose_x1 else x1

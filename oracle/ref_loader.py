@@ -48,7 +48,7 @@ _cache = {}
 
 
 def goldens():
-    """Returns a dict of the reference golden modules: qbmmv3, qbmmv4_aclnn, wqbmmv2, mxquant, blockquant."""
+    """Returns a dict of the reference golden modules: qbmmv3, qbmmv4 (kernel goldens), wqbmmv2, mxquant."""
     if _cache:
         return _cache
     _install_shim()
@@ -62,10 +62,12 @@ def goldens():
     matmul_golden_util._DTYPE_TO_STR[np.dtype(ml_dtypes.float4_e2m1fn)] = "float4_e2m1"
     matmul_golden_util._DTYPE_TO_STR[np.dtype(ml_dtypes.float8_e8m0fnu)] = "float8_e8m0"
     import qbmmv3_kernel_golden  # noqa: E402
+    import qbmmv4_kernel_golden  # noqa: E402
     import wqbmmv2_kernel_golden  # noqa: E402
 
     _cache["util"] = matmul_golden_util
     _cache["qbmmv3"] = qbmmv3_kernel_golden
+    _cache["qbmmv4"] = qbmmv4_kernel_golden
     _cache["wqbmmv2"] = wqbmmv2_kernel_golden
     _cache["mxquant"] = _load(os.path.join(REF, "quant/dynamic_mx_quant/tests/assets/golden.py"), "ref_dynamic_mx_quant_golden")
     return _cache

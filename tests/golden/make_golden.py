@@ -86,8 +86,9 @@ def e8m0(rng, shape, lo=-3, hi=3):
 
 # ------------------------------------------------------------------------------------------------------------
 def qmm_case(G, name, seed, x1, x2, x1s, x2s, bias, t1, t2, group, out, note, x2s_u64=None, check_oracle=True,
-             api_group=None):
-    """x2s_u64: the packed uint64 tensor handed to the API when the scale is the fixpipe-packed form."""
+             api_group=None, per_tile=False):
+    """x2s_u64: the packed uint64 tensor handed to the API when the scale is the fixpipe-packed form.
+    per_tile: int8 per-block, computed by the V4 golden's compute_per_tile (2-D operands only)."""
     ref = G["qbmmv3"]
     kw = dict(dtype=ACL.get(out, 0), transpose_x1=t1, transpose_x2=t2, group_size=group, output_dtypes=[out])
     a = x1.T if t1 and x1.ndim == 2 else x1
@@ -95,7 +96,9 @@ def qmm_case(G, name, seed, x1, x2, x1s, x2s, bias, t1, t2, group, out, note, x2
     m = x1.shape[-1] if t1 else x1.shape[-2]
     n = x2.shape[-2] if t2 else x2.shape[-1]
     batched = x1.ndim > 2 or x2.ndim > 2
-    if batched:
+    if per_tile:
+        y = G["qbmmv4"].compute_per_tile(x1, x2, x1s, x2s, bias, t1, t2, group, out)
+    elif batched:
         nb = max(x1.shape[0] if x1.ndim > 2 else 1, x2.shape[0] if x2.ndim > 2 else 1)
         outs = []
         for i in range(nb):  # the reference golden cannot take 4-D mx scales: call it per batch
@@ -172,6 +175,20 @@ def gen_qmm(G):
     qmm_case(G, "bb_fp8_fp16_transA", 22, q_fp8(rng, (283, 300), E5M2), q_fp8(rng, (283, 261), E4M3),
              f32(rng, (3, 3), .5, 2), f32(rng, (3, 3), .5, 2), None, True, False, (128 << 32) | (128 << 16) | 128, "float16",
              "B-B with x1 stored (k,m): scales are stored (k/128, m/128)")
+    # int8 per-block (the V4 golden's PER_TILE mode)
+    gb = (1 << 32) | (128 << 16) | 128
+    rng = np.random.default_rng(40)
+    qmm_case(G, "pt_int8_bf16", 40, i8(rng, (200, 384)), i8(rng, (384, 300)), f32(rng, (200, 3), 1e-3, 1e-2),
+             f32(rng, (3, 3), 1e-2, 1e-1), None, False, False, gb, "bfloat16", "int8 G-B per-block, tails in m and n",
+             per_tile=True)
+    rng = np.random.default_rng(41)
+    qmm_case(G, "pt_int8_bf16_bias_transB", 41, i8(rng, (77, 300)), i8(rng, (261, 300)), f32(rng, (77, 3), 1e-3, 1e-2),
+             f32(rng, (3, 3), 1e-2, 1e-1), rng.standard_normal(261).astype(np.float32), False, True, gb, "bfloat16",
+             "int8 G-B per-block, x2 stored (n,k) with scales (n/128,k/128), k tail, fp32 bias", per_tile=True)
+    rng = np.random.default_rng(42)
+    qmm_case(G, "pt_int8_fp16_big", 42, i8(rng, (384, 1024)), i8(rng, (512, 1024)), f32(rng, (384, 8), 1e-3, 1e-2),
+             f32(rng, (4, 8), 1e-2, 1e-1), None, False, True, gb, "float16", "int8 G-B per-block, whole tiles",
+             per_tile=True)
     # fp8 double scale / per-tensor
     rng = np.random.default_rng(23)
     qmm_case(G, "tt_fp8_doublescale_fp16", 23, q_fp8(rng, (48, 96), E4M3), q_fp8(rng, (96, 80), E4M3), f32(rng, (1,), .5, 2),

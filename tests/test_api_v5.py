@@ -103,6 +103,22 @@ def test_group_size_inference_mx_and_perblock(aclnn):
             aclnn.destroy_executor(ex)
 
 
+def test_int8_perblock_is_accepted(aclnn):
+    """int8 x int8 with (m, k/128) and (k/128, n/128) fp32 scales: the PER_TILE mode of
+    matmul/quant_batch_matmul_v4/tests/assets/qbmmv4_kernel_golden.py:258-325; bias allowed, groupSizeN must be 128."""
+    x1 = aclnn.Tensor((256, 384), "int8")
+    x2 = aclnn.Tensor((384, 256), "int8")
+    s1 = aclnn.Tensor((256, 3), "float32")
+    s2 = aclnn.Tensor((3, 2), "float32")
+    bias = aclnn.Tensor((256,), "float32")
+    out = aclnn.Tensor((256, 256), "bfloat16")
+    for g, b, want in ((4303356032, None, 0), (4303356032, bias, 0), ((1 << 32) | (64 << 16) | 128, None, 161002)):
+        st, _, ex = aclnn.quant_matmul_v5_get_workspace_size(x1, x2, s1, s2, None, None, None, None, b, False, False, g, out)
+        assert st == want, (g, aclnn.last_error())
+        if st == 0:
+            aclnn.destroy_executor(ex)
+
+
 def test_phase1_is_thread_safe(aclnn):
     """The reference drives phase 1 from three threads at once
     (weight_quant_batch_matmul_v2/tests/ut/op_host/op_api/test_aclnn_weight_quant_batch_matmul_v2_api.cpp:2757-2802)."""

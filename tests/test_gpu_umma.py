@@ -110,6 +110,35 @@ def test_fp8_perblock(aclnn, case):
     got = _run(aclnn, x1, x2, s1, s2, None, t1, t2, group, out_name, "qmm_umma_perblock", bn)
     check_close(got, want, ref32, out_name)
 
+I8PB_CASES = [
+    # m, k, n, t1, t2, bn, bias, out
+    (256, 512, 512, False, False, 128, None, "bfloat16"),
+    (200, 400, 304, False, False, 256, "f32", "bfloat16"),   # tails everywhere
+    (200, 400, 304, False, True, 128, "bf16", "bfloat16"),   # k-major B, scales (n/128, k/128)
+    (208, 400, 304, True, False, 128, "i32", "bfloat16"),    # x1 stored (k,m), scales (k/128, m)
+    (144, 1040, 208, True, True, 256, "f32", "float16"),
+]
+
+
+@pytest.mark.parametrize("case", I8PB_CASES, ids=[str(c) for c in I8PB_CASES])
+def test_int8_perblock_bit_exact(aclnn, case):
+    """int8 with 1 x 128 / 128 x 128 fp32 scales: each 128-k partial is an exact int32, converted, multiplied by
+    s1 * s2 and added with separate roundings like the reference's golden, so the result is compared bit for bit."""
+    m, k, n, t1, t2, bn, bias_kind, out_name = case
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
+    kb, ng = -(-k // 128), -(-n // 128)
+    s1 = rng.uniform(1e-3, 1e-2, (kb, m) if t1 else (m, kb)).astype(np.float32)
+    s2 = rng.uniform(1e-2, 1e-1, (ng, kb) if t2 else (kb, ng)).astype(np.float32)
+    bias = {None: None, "f32": rng.standard_normal(n).astype(np.float32), "i32": rng.integers(-5, 6, n).astype(np.int32),
+            "bf16": rng.standard_normal(n).astype(ml_dtypes.bfloat16)}[bias_kind]
+    group = (1 << 32) | (128 << 16) | 128
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, group, out_name)
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, group, out_name, "qmm_umma_perblock", bn)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
 
 def test_fp8_dequant_doublescale(aclnn):
     from gpu_util import check_close
