@@ -34,6 +34,8 @@ typedef enum {
 #define OPSNN_DEQ_TRUNC_SCALE_B 1 /* x2Scale &= 0xFFFFE000 before use */
 #define OPSNN_DEQ_MERGE_TRUNC 2   /* (x2Scale * x1Scale) &= 0xFFFFE000, one multiply */
 #define OPSNN_DEQ_FBIAS_BEFORE_SCALE 4 /* a float bias is added to the fp32 accumulator before the scale multiply */
+#define OPSNN_DEQ_REQUANT 8        /* INT8 out (qbmmv3_kernel_golden.py:465-487): clip(rint(acc * scale), -256, 255), then clip to int8 */
+#define OPSNN_DEQ_REQUANT_OFFSET 16 /* with REQUANT: add the signed 9-bit offset held in bits 37..45 of the packed UINT64 scale */
 
 typedef enum {
     OPSNN_KERNEL_AUTO = 0,    /* host tile selection decides */
@@ -66,7 +68,19 @@ typedef struct OpsnnQmmParams {
     int64_t out_ld, out_bs;
     void* workspace;
     uint64_t workspace_size;
+    /* A8W4 (fp8 x fp4, aclnn_quant_matmul_v5.cpp:193-243): b is FLOAT4_E2M1 and is rewritten as fp8 into the head of
+       the workspace before the matmul runs on it.
+       OPSNN_B_PREPASS_WIDEN: every e2m1 value as the same value in e4m3 (exact); the mx scales apply unchanged.
+       OPSNN_B_PREPASS_GROUP_SCALE: T-CG of qbmmv4_kernel_golden.py:189-255: value * pre_scale[group] rounded to
+       pre_scale_dtype (BF16 | FLOAT16), then rounded to a_dtype; pre_scale is stored like b with one entry per
+       pre_group elements of k: (n, k/pre_group) for b (n,k), (k/pre_group, n) for b (k,n). */
+    int32_t b_prepass;
+    int32_t pre_scale_dtype;
+    const void* pre_scale;
+    int32_t pre_group;
 } OpsnnQmmParams;
+
+enum { OPSNN_B_PREPASS_NONE = 0, OPSNN_B_PREPASS_WIDEN = 1, OPSNN_B_PREPASS_GROUP_SCALE = 2 };
 
 /* Bytes of device workspace `opsnn_qmm_launch` needs for these parameters with this kernel choice. */
 OPSNN_API uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice);

@@ -240,10 +240,10 @@ def destroy_executor(ex):
 # ---- both phases on device tensors -------------------------------------------------------------------------------
 
 def quant_matmul_v5(x1, x2, x1_scale, x2_scale, out, bias=None, transpose_x1=False, transpose_x2=False, group_size=0,
-                    x2_offset=None, workspace=None):
+                    x2_offset=None, workspace=None, y_scale=None):
     """Runs aclnnQuantMatmulV5 on the current torch CUDA stream. Arguments are `Tensor` descriptors over device memory;
     `out` is written in place. Returns the workspace size used."""
-    st, ws_size, ex = quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, None, None, x2_offset, None, bias,
+    st, ws_size, ex = quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, y_scale, None, x2_offset, None, bias,
                                                          transpose_x1, transpose_x2, group_size, out)
     if st != ACLNN_SUCCESS:
         raise AclnnError("aclnnQuantMatmulV5GetWorkspaceSize", st)

@@ -80,8 +80,29 @@ __device__ __forceinline__ void store_out(void* base, int64_t idx, float v, int 
         case ACL_BF16: reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v); break;
         case ACL_FLOAT16: reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v); break;
         case ACL_FLOAT: reinterpret_cast<float*>(base)[idx] = v; break;
+        case ACL_INT8: reinterpret_cast<int8_t*>(base)[idx] = (int8_t)(int)v; break;  // v is integral and already clipped
         default: break;
     }
+}
+
+// Requantisation to int8 (qbmmv3_kernel_golden.py:465-487, matmul_quant_util.py:57-59, 137-143): the scaled accumulator is
+// rounded half-to-even and clipped to nine signed bits, the optional nine-bit offset (bits 37..45 of the packed scale) is
+// added, and the sum is clipped to int8. `f` is float(acc + int32 bias).
+__device__ __forceinline__ float requant_s9(float f, float sb, const void* scale_b, int64_t col, int flags)
+{
+    f = fminf(fmaxf(rintf(__fmul_rn(f, sb)), -256.f), 255.f);
+    if (flags & OPSNN_DEQ_REQUANT_OFFSET) {
+        const uint64_t w = __ldg(reinterpret_cast<const unsigned long long*>(scale_b) + col);
+        int off = (int)((w >> 37) & 0x1FFu);
+        if (off & 0x100) off -= 0x200;
+        f = __fadd_rn(f, (float)off);
+    }
+    return fminf(fmaxf(f, -128.f), 127.f);
+}
+
+__device__ __forceinline__ int out_elem_bytes(int dtype)
+{
+    return (dtype == ACL_FLOAT || dtype == ACL_INT32) ? 4 : (dtype == ACL_INT8 ? 1 : 2);
 }
 
 // The dequantisation epilogue of the per-tensor / per-channel / per-token modes, with the reference's rounding

@@ -23,6 +23,9 @@ int32_t qmm_generic_launch(const OpsnnQmmParams* p, cudaStream_t stream);
 bool qmm_umma_eligible(const OpsnnQmmParams* p);
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p);
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream);
+uint64_t qmm_a8w4_prepass_bytes(const OpsnnQmmParams* p);
+void qmm_a8w4_view(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst);
+int32_t qmm_a8w4_prepass_launch(const OpsnnQmmParams* p, void* dst, cudaStream_t stream);
 
 int32_t wqbmm_generic_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p);
@@ -40,9 +43,20 @@ using namespace opsnn;
 
 extern "C" {
 
+// A8W4: kernel selection and workspace are those of the fp8 problem the pre-pass leaves behind. For planning (no
+// workspace yet) the rewritten operand is given a stand-in address with the alignment every device allocation has.
+static const OpsnnQmmParams* after_prepass(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst)
+{
+    if (p->b_prepass == OPSNN_B_PREPASS_NONE) return p;
+    qmm_a8w4_view(p, q, dst);
+    return q;
+}
+
 int32_t opsnn_qmm_select_kernel(const OpsnnQmmParams* p)
 {
     if (p == nullptr) return OPSNN_KERNEL_GENERIC;
+    OpsnnQmmParams q;
+    p = after_prepass(p, &q, reinterpret_cast<void*>(uintptr_t(256)));
     return qmm_umma_eligible(p) ? OPSNN_KERNEL_UMMA : OPSNN_KERNEL_GENERIC;
 }
 
@@ -50,13 +64,24 @@ uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice
 {
     if (p == nullptr) return 0;
     if (kernel_choice == OPSNN_KERNEL_AUTO) kernel_choice = opsnn_qmm_select_kernel(p);
-    return kernel_choice == OPSNN_KERNEL_UMMA ? qmm_umma_workspace_size(p) : 0;
+    const uint64_t pre = qmm_a8w4_prepass_bytes(p);
+    OpsnnQmmParams q;
+    p = after_prepass(p, &q, reinterpret_cast<void*>(uintptr_t(256)));
+    return pre + (kernel_choice == OPSNN_KERNEL_UMMA ? qmm_umma_workspace_size(p) : 0);
 }
 
 int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* stream)
 {
     if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
     if (p->m <= 0 || p->n <= 0 || p->batch <= 0) return 0;
+    OpsnnQmmParams q;
+    if (p->b_prepass != OPSNN_B_PREPASS_NONE) {
+        if (p->workspace == nullptr || p->workspace_size < qmm_a8w4_prepass_bytes(p)) return (int32_t)cudaErrorInvalidValue;
+        const int32_t rc = qmm_a8w4_prepass_launch(p, p->workspace, static_cast<cudaStream_t>(stream));
+        if (rc != 0) return rc;
+        p = after_prepass(p, &q, p->workspace);
+        if (kernel_choice == OPSNN_KERNEL_UMMA && !qmm_umma_eligible(p)) kernel_choice = OPSNN_KERNEL_GENERIC;  // odd workspace address
+    }
     if (kernel_choice == OPSNN_KERNEL_AUTO) kernel_choice = opsnn_qmm_select_kernel(p);
     if (kernel_choice == OPSNN_KERNEL_UMMA) {
         if (!qmm_umma_eligible(p)) return (int32_t)cudaErrorInvalidValue;

@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(NT) qmm_generic_kernel(const OpsnnQmmParams p)
 
     // ---- epilogue ----
     uint8_t* out = reinterpret_cast<uint8_t*>(p.out);
-    const int out_bytes = p.out_dtype == ACL_FLOAT || p.out_dtype == ACL_INT32 ? 4 : 2;
+    const int out_bytes = out_elem_bytes(p.out_dtype);
     out += bz * p.out_bs * out_bytes;
     const uint8_t* bias = reinterpret_cast<const uint8_t*>(p.bias);
     if (bias != nullptr) bias += bz * p.bias_bs * (p.bias_dtype == ACL_FLOAT || p.bias_dtype == ACL_INT32 ? 4 : 2);
@@ -175,7 +175,8 @@ __global__ void __launch_bounds__(NT) qmm_generic_kernel(const OpsnnQmmParams p)
                 float sb = load_deq_scale(p.scale_b, p.scale_b_len == 1 ? 0 : gn, p.scale_b_dtype);
                 const bool has_sa = p.scale_a != nullptr;
                 float sa = has_sa ? saf[p.scale_a_len == 1 ? 0 : gm] : 1.f;
-                f = deq_epilogue(f, sb, sa, has_sa, fb, has_fbias, p.deq_flags);
+                if (p.deq_flags & OPSNN_DEQ_REQUANT) f = requant_s9(f, sb, p.scale_b, p.scale_b_len == 1 ? 0 : gn, p.deq_flags);
+                else f = deq_epilogue(f, sb, sa, has_sa, fb, has_fbias, p.deq_flags);
                 store_out(out, oidx, f, p.out_dtype);
             } else {
                 float f = p.mode == OPSNN_QMM_PERBLOCK ? tot[i][j] : (float)acc[i][j];

@@ -95,6 +95,24 @@ __device__ __forceinline__ void store_row32(const UmmaArgs& a, uint8_t* out, int
         }
         return;
     }
+    if (a.out_dtype == ACL_INT8) {  // requantised: f holds integers in [-128, 127]
+        uint32_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            q[i] = ((uint32_t)(int)f[4 * i] & 0xFFu) | (((uint32_t)(int)f[4 * i + 1] & 0xFFu) << 8) |
+                   (((uint32_t)(int)f[4 * i + 2] & 0xFFu) << 16) | (((uint32_t)(int)f[4 * i + 3] & 0xFFu) << 24);
+        }
+        uint8_t* o = out + row * a.out_ld + col;
+        if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            *reinterpret_cast<uint4*>(o) = make_uint4(q[0], q[1], q[2], q[3]);
+            *reinterpret_cast<uint4*>(o + 16) = make_uint4(q[4], q[5], q[6], q[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < valid) o[i] = (uint8_t)(q[i >> 2] >> (8 * (i & 3)));
+        }
+        return;
+    }
     uint32_t pk[16];
     if (a.out_dtype == ACL_BF16) {
 #pragma unroll
@@ -203,7 +221,9 @@ __device__ __forceinline__ void deq_store_cols(const UmmaArgs& a, uint32_t tmem_
                                             float x;
                                             if (a.is_int) x = (float)((int32_t)v[i] + (has_ibias ? (int32_t)s_bias[c + i] : 0));
                                             else x = __uint_as_float(v[i]);
-                                            f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
+                                            if (flags & OPSNN_DEQ_REQUANT)
+                                                f[i] = requant_s9(x, s_scale[c + i], a.scale_b, a.scale_b_len == 1 ? 0 : min(col + i, a.n - 1), flags);
+                                            else f[i] = deq_epilogue(x, s_scale[c + i], sav, has_sa, __uint_as_float(s_bias[c + i]), has_fbias, flags);
                                         }
                                         break;
                                 }
@@ -392,7 +412,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
-            const int out_bytes = (a.out_dtype == ACL_FLOAT || a.out_dtype == ACL_INT32) ? 4 : 2;
+            const int out_bytes = out_elem_bytes(a.out_dtype);
             uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + b * a.out_bs * out_bytes;
             const int64_t colbase = n0 + half * kCols;
             if (!kPerBlock) {
@@ -666,7 +686,8 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
         return false;
     }
     if (p->out_dtype != ACL_BF16 && p->out_dtype != ACL_FLOAT16 && p->out_dtype != ACL_FLOAT &&
-        !(p->out_dtype == ACL_INT32 && i8 && p->mode == OPSNN_QMM_DEQ))
+        !((p->out_dtype == ACL_INT32 || (p->out_dtype == ACL_INT8 && (p->deq_flags & OPSNN_DEQ_REQUANT))) && i8 &&
+          p->mode == OPSNN_QMM_DEQ))
         return false;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (p->a != nullptr && (!al16(p->a) || !al16(p->b))) return false;
@@ -682,7 +703,7 @@ uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p) { return p->mode == OP
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
-    const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32;
+    const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32 && p->out_dtype != ACL_INT8;
     const int bn = pair ? 256 : pick_bn(p);
     const int bm = pair ? 256 : BM;
     UmmaArgs a{};

@@ -535,9 +535,64 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
     if (a8w4f) {
         aclnnStatus st = check_a8w4_float(c, x1Scale, group);
         if (st != ACLNN_SUCCESS) return st;
-        exec->unsupported = true;
-        exec->unsupported_why = "fp8 x fp4 (A8W4) kernels are not built yet";
-        *workspaceSize = 0;
+        // Plan: the fp4 weight is rewritten as fp8 into the workspace, then the fp8 kernels run (mx: block-scaled matmul
+        // on the widened weight; T-CG: group scale folded into the rewrite, yScale is the per-channel dequant scale).
+        OpsnnQmmParams& p = exec->qmm;
+        const bool is_mx = c.has_x1s && c.x2s.dtype == ACL_FLOAT8_E8M0;
+        p.a_dtype = c.x1.dtype;
+        p.b_dtype = c.x2.dtype;
+        p.out_dtype = c.out.dtype;
+        p.bias_dtype = c.has_bias ? (int)c.bias.dtype : -1;
+        p.trans_a = 0;
+        p.trans_b = 1;
+        p.m = c.m; p.n = c.n; p.k = c.k1; p.batch = 1;
+        int64_t ld = 0, bs = 0;
+        auto why_unsupported = [&](const char* w) {
+            exec->unsupported = true;
+            exec->unsupported_why = w;
+        };
+        if (!row_strided_view(&c.x1, &ld, &bs)) why_unsupported("x1 is neither contiguous nor row-strided");
+        p.a_ld = ld;
+        if (!row_strided_view(&c.x2, &ld, &bs)) why_unsupported("x2 is neither contiguous nor row-strided");
+        p.b_ld = ld;
+        if (!row_strided_view(&c.out, &ld, &bs)) why_unsupported("out must be contiguous or row-strided");
+        p.out_ld = ld;
+        p.out_bs = c.m * ld;
+        p.a = data_ptr(&c.x1);
+        p.b = data_ptr(&c.x2);
+        p.out = const_cast<uint8_t*>(data_ptr(&c.out));
+        p.bias = c.has_bias ? data_ptr(&c.bias) : nullptr;
+        for (const aclTensor* t : {&c.x2s, c.has_x1s ? &c.x1s : nullptr, c.has_bias ? &c.bias : nullptr, c.has_ys ? &c.ys : nullptr}) {
+            if (t != nullptr && !is_contiguous(t)) why_unsupported("scale/bias tensors must be contiguous");
+        }
+        p.group_m = 1; p.group_n = 1; p.group_k = 32;
+        if (is_mx) {
+            p.mode = OPSNN_QMM_MX;
+            p.b_prepass = OPSNN_B_PREPASS_WIDEN;
+            p.scale_a = data_ptr(&c.x1s);
+            p.scale_b = data_ptr(&c.x2s);
+            p.scale_b_dtype = ACL_FLOAT8_E8M0;
+            p.pre_scale_dtype = -1;
+        } else {
+            p.mode = OPSNN_QMM_DEQ;
+            p.b_prepass = OPSNN_B_PREPASS_GROUP_SCALE;
+            p.pre_scale = data_ptr(&c.x2s);
+            p.pre_scale_dtype = c.x2s.dtype;
+            p.pre_group = 32;
+            p.scale_a = nullptr;
+            p.scale_b = data_ptr(&c.ys);
+            p.scale_b_dtype = ACL_UINT64;
+            p.scale_b_len = c.n;
+        }
+        exec->kernel_choice = OPSNN_KERNEL_AUTO;
+        if (const char* e = std::getenv("OPSNN_QMM_KERNEL")) exec->kernel_choice = std::atoi(e);
+        if (!exec->unsupported) {
+            if (exec->kernel_choice == OPSNN_KERNEL_AUTO) exec->kernel_choice = opsnn_qmm_select_kernel(&p);
+            exec->workspace_size = opsnn_qmm_workspace_size(&p, exec->kernel_choice);
+        }
+        *workspaceSize = exec->workspace_size;
+        log_info("aclnnQuantMatmulV5 plan: A8W4 %s m=%ld n=%ld k=%ld kernel=%d ws=%lu", is_mx ? "mx" : "T-CG", (long)p.m,
+                 (long)p.n, (long)p.k, exec->kernel_choice, (unsigned long)exec->workspace_size);
         *executor = exec.release();
         return ACLNN_SUCCESS;
     }
@@ -654,7 +709,12 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         p.scale_a_len = c.has_x1s ? c.x1s.shape[0] : 0;
         if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
         if (c.int4_in()) why_unsupported("INT4 x INT4 kernels are not built yet");
-        if (c.out.dtype == ACL_INT8) why_unsupported("INT8 (requant) output is not built yet");
+        if (c.out.dtype == ACL_INT8) {
+            // requantised output: the offset tensor only says that the packed scale carries one (QuantBatchMatmulV3TestSpec.golden,
+            // qbmmv3_kernel_golden.py:726-731)
+            p.deq_flags |= OPSNN_DEQ_REQUANT;
+            if (c.has_x2o) p.deq_flags |= OPSNN_DEQ_REQUANT_OFFSET;
+        }
         // Rounding-point rules of the reference golden (qbmmv3_kernel_golden.py:566-577, 641-692;
         // matmul_quant_util.py:62-72): which scales lose their low 13 bits, and where a float bias is added.
         const bool float_bias = c.has_bias && in(c.bias.dtype, {ACL_FLOAT, ACL_BF16, ACL_FLOAT16});

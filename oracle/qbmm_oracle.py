@@ -38,6 +38,18 @@ def u64_to_deq_scale(u64):
     return lo.view(np.float32).reshape(np.shape(u64))
 
 
+def u64_to_offset(u64):
+    """Signed 9-bit offset in bits 37..45 of the packed scale (matmul_quant_util.py:137-143)."""
+    raw = ((np.asarray(u64).astype(np.uint64) >> np.uint64(37)) & np.uint64(0x1FF)).astype(np.int64)
+    raw = np.where(raw & 0x100, raw - 0x200, raw)
+    return raw.astype(np.float32).reshape(np.shape(u64))
+
+
+def f32_2_s9(a):
+    """Round half to even, clip to nine signed bits (matmul_quant_util.py:57-59)."""
+    return np.clip(np.round(a), -256, 255)
+
+
 def unpack_groupsize(g):
     gm, gn, gk = (g >> 32) & 0xFFFF, (g >> 16) & 0xFFFF, g & 0xFFFF
     return gm or 1, gn or 1, gk or 1
@@ -96,6 +108,30 @@ def compute_mx(x1, x2, x1_scale, x2_scale, bias, transpose_x1, transpose_x2, out
     return cast_out(y, out_dtype)
 
 
+def compute_t_cg(x1, x2, x2_scale, y_scale, transpose_x1, transpose_x2, group_k, out_dtype, bias=None):
+    """A8W4 T-CG: fp8 x1, fp4 x2 with a bf16/fp16 scale per `group_k` elements of k, uint64 yScale per column.
+    qbmmv4_kernel_golden.py:189-255: the weight is widened to the scale's dtype, multiplied by the scale in that dtype,
+    rounded to x1's fp8 dtype, and only then multiplied; yScale (decoded as in matmul_quant_util.py:129-134) scales the
+    fp32 product."""
+    mid = x2_scale.dtype
+    b = x2.astype(np.float32)
+    s = x2_scale.astype(np.float32)
+    if transpose_x2:
+        b, s = b.T, s.T
+    k = b.shape[0]
+    s = np.repeat(s, group_k, axis=0)[:k]
+    w = (b.astype(mid) * s.astype(mid)).astype(np.float32).astype(x1.dtype).astype(np.float32)
+    a = x1.astype(np.float32)
+    if transpose_x1:
+        a = a.T
+    y = np.matmul(a, w)
+    if y_scale is not None:
+        y = y * u64_to_deq_scale(y_scale).reshape(1, -1)[:, : y.shape[-1]]
+    if bias is not None:
+        y = y + bias.astype(np.float32)
+    return cast_out(y, out_dtype)
+
+
 def compute_perblock(x1, x2, x1_scale, x2_scale, group, transpose_x1, transpose_x2, out_dtype, bias=None):
     """2-D operands. qbmmv3_kernel_golden.py:237-358"""
     gm, gn, gk = group
@@ -129,7 +165,7 @@ def int_matmul(a, b):
 
 
 def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, transpose_x2=False, group_size=0,
-                    out_dtype="bfloat16", x2_scale_is_u64=False):
+                    out_dtype="bfloat16", x2_scale_is_u64=False, y_scale=None, x2_offset=None):
     """aclnnQuantMatmulV5 for the modes this build implements; batch dims on x1/x2 are looped.
 
     Mode selection = qbmmv3_kernel_golden.py:62-145 (same tree as the reference's host tiling,
@@ -152,6 +188,9 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, t
                                         transpose_x1, transpose_x2, group_size, out_dtype, x2_scale_is_u64))
         return np.stack(outs)
 
+    if y_scale is not None and _is_fp8(x1.dtype) and x2.dtype == np.dtype(E2M1) and x1_scale is None:
+        return compute_t_cg(x1, x2, x2_scale, y_scale, transpose_x1, transpose_x2, (group_size & 0xFFFF) or 32, out_dtype,
+                            bias)
     if x2_scale.dtype == np.dtype(E8M0):
         return compute_mx(x1, x2, x1_scale, x2_scale, bias, transpose_x1, transpose_x2, out_dtype)
     is_int = x1.dtype == np.int8
@@ -170,6 +209,12 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, t
     if out_dtype == "int32":  # compute_int32 :490-506
         return (acc + bias).astype(np.int32) if bias is not None else acc.astype(np.int32)
     s2 = u64_to_deq_scale(x2_scale) if x2_scale_is_u64 else x2_scale.astype(np.float32)
+    if out_dtype == "int8":  # compute_requant :465-487; the offset rides in bits 37..45 of the packed scale (:726-731)
+        out = acc + bias if bias is not None and bias_dt == np.int32 else acc
+        out = f32_2_s9(out.astype(np.float32) * s2)
+        if x2_offset is not None:
+            out = out + f32_2_s9(u64_to_offset(x2_scale))
+        return np.clip(out, -128, 127).astype(np.int8)
     per_token = x1_scale is not None and x1_scale.ndim == 1 and x1_scale.shape[0] == m and not (
         fp8 and x1_scale.shape[0] == 1)
     double_scale = fp8 and x1_scale is not None and x1_scale.ndim == 1 and x1_scale.shape[0] == 1

@@ -86,7 +86,7 @@ def e8m0(rng, shape, lo=-3, hi=3):
 
 # ------------------------------------------------------------------------------------------------------------
 def qmm_case(G, name, seed, x1, x2, x1s, x2s, bias, t1, t2, group, out, note, x2s_u64=None, check_oracle=True,
-             api_group=None, per_tile=False):
+             api_group=None, per_tile=False, offset=None):
     """x2s_u64: the packed uint64 tensor handed to the API when the scale is the fixpipe-packed form.
     per_tile: int8 per-block, computed by the V4 golden's compute_per_tile (2-D operands only)."""
     ref = G["qbmmv3"]
@@ -112,17 +112,31 @@ def qmm_case(G, name, seed, x1, x2, x1s, x2s, bias, t1, t2, group, out, note, x2
         y = np.stack(outs)
     else:
         if x2s_u64 is not None:
-            y = ref.QuantBatchMatmulV3TestSpec.golden(x1, x2, x2s_u64, None, bias, x1s, output_shapes=[(m, n)],
+            y = ref.QuantBatchMatmulV3TestSpec.golden(x1, x2, x2s_u64, offset, bias, x1s, output_shapes=[(m, n)],
                                                       scale_dtype="uint64", **kw)[0]
         else:
             y = ref.qbmmv3_kernel_compute(x1, x2, x2s, None, bias, x1s, output_shapes=[(m, n)], **kw)[0]
     if check_oracle:
         yo = qbmm_oracle.quant_matmul_v5(x1, x2, x1s, x2s_u64 if x2s_u64 is not None else x2s, bias, t1, t2, group, out,
-                                         x2_scale_is_u64=x2s_u64 is not None)
+                                         x2_scale_is_u64=x2s_u64 is not None, x2_offset=offset)
         assert bits_equal(y, yo), "oracle != reference for " + name
-    save("qmm_" + name, dict(x1=x1, x2=x2, x1_scale=x1s, x2_scale=x2s_u64 if x2s_u64 is not None else x2s, bias=bias, out=y),
+    save("qmm_" + name, dict(x1=x1, x2=x2, x1_scale=x1s, x2_scale=x2s_u64 if x2s_u64 is not None else x2s, bias=bias, out=y,
+                             x2_offset=offset),
          dict(op="quant_matmul_v5", transpose_x1=t1, transpose_x2=t2, group_size=group if api_group is None else api_group,
               out_dtype=out, seed=seed, note=note))
+
+
+def a8w4_case(G, name, seed, x1, x2, x1s, x2s, ys, bias, out, note):
+    """fp8 x fp4 through the V4 golden's entry (mx when the scales are e8m0, T-CG when x2Scale is bf16/fp16 + yScale);
+    x2 is stored (n,k) (transposeX2 = true), groupSizeK 32, as the API demands for these modes."""
+    y = G["qbmmv4"].qbmmv4_kernel_compute(x1, x2, bias, x1s, x2s, ys, transpose_x1=False, transpose_x2=True, group_size=32,
+                                          output_dtypes=[out])
+    y = y[0] if isinstance(y, (list, tuple)) else y
+    yo = qbmm_oracle.quant_matmul_v5(x1, x2, x1s, x2s, None if bias is None else bias.reshape(-1), False, True, 32, out,
+                                     y_scale=ys)
+    assert bits_equal(y, yo), "oracle != reference for " + name
+    save("qmm_" + name, dict(x1=x1, x2=x2, x1_scale=x1s, x2_scale=x2s, y_scale=ys, bias=bias, out=y),
+         dict(op="quant_matmul_v5", transpose_x1=False, transpose_x2=True, group_size=32, out_dtype=out, seed=seed, note=note))
 
 
 def gen_qmm(G):
@@ -189,6 +203,39 @@ def gen_qmm(G):
     qmm_case(G, "pt_int8_fp16_big", 42, i8(rng, (384, 1024)), i8(rng, (512, 1024)), f32(rng, (384, 8), 1e-3, 1e-2),
              f32(rng, (4, 8), 1e-2, 1e-1), None, False, True, gb, "float16", "int8 G-B per-block, whole tiles",
              per_tile=True)
+    # int8 requantised output: uint64 scale = fp32 scale | 1 << 46 | s9 offset << 37 (matmul_quant_util.py:146-155)
+    import matmul_quant_util as mqu  # on sys.path once the goldens are loaded
+    rng = np.random.default_rng(60)
+    sc = rng.uniform(2e-5, 6e-4, 300).astype(np.float32) * rng.choice([-1, 1], 300).astype(np.float32)
+    qmm_case(G, "tc_int8_requant", 60, i8(rng, (77, 512)), i8(rng, (512, 300)), None, None,
+             rng.integers(-20000, 20001, 300).astype(np.int32), False, False, 0, "int8",
+             "int8 output, per-channel packed scale, int32 bias, no offset", x2s_u64=mqu.pack_u64_scale(sc))
+    rng = np.random.default_rng(61)
+    sc = rng.uniform(2e-5, 6e-5, 208).astype(np.float32)
+    off = rng.uniform(-60, 60, 208).astype(np.float32)
+    qmm_case(G, "tc_int8_requant_offset_transB", 61, i8(rng, (130, 1040)), i8(rng, (208, 1040)), None, None, None, False, True,
+             0, "int8", "int8 output with the 9-bit offset packed into the scale, x2 stored (n,k)",
+             x2s_u64=mqu.pack_u64_scale(sc, off), offset=off)
+    # A8W4: fp8 x fp4 (the V4 golden's MX and T_CG modes)
+    def u64_scale(rng, n, lo, hi):
+        sc = rng.uniform(lo, hi, (1, n)).astype(np.float32)
+        return (np.ascontiguousarray(sc).view(np.uint32) & np.uint32(0xFFFFE000)).astype(np.uint64)
+
+    rng = np.random.default_rng(50)
+    a8w4_case(G, "a8w4_mx_bf16", 50, q_fp8(rng, (96, 256), E4M3), q_fp4(rng, (200, 256)), e8m0(rng, (96, 4, 2)),
+              e8m0(rng, (200, 4, 2)), None, None, "bfloat16", "MxA8W4: e4m3 x e2m1, e8m0 scales per 32, tails in m and n")
+    rng = np.random.default_rng(51)
+    a8w4_case(G, "a8w4_mx_fp16_bias", 51, q_fp8(rng, (16, 128), E4M3), q_fp4(rng, (128, 128)), e8m0(rng, (16, 2, 2), -2, 2),
+              e8m0(rng, (128, 2, 2), -2, 2), None, rng.standard_normal((1, 128)).astype(np.float16), "float16",
+              "test_aclnn_quant_matmul_v5_api.csv MxA8W4_Bias_fp16: bias (1,n) in the output dtype")
+    rng = np.random.default_rng(52)
+    a8w4_case(G, "a8w4_tcg_fp16", 52, q_fp8(rng, (16, 64), E4M3), q_fp4(rng, (16, 64)), None,
+              rng.uniform(0.25, 4, (16, 2)).astype(BF16), u64_scale(rng, 16, 0.01, 0.1), None, "float16",
+              "test_aclnn_quant_matmul_v5_api.csv A8W4F_TCG_fp16_ok: bf16 group scale (n, k/32), uint64 yScale (1,n)")
+    rng = np.random.default_rng(53)
+    a8w4_case(G, "a8w4_tcg_bf16_f16scale", 53, q_fp8(rng, (150, 512), E4M3), q_fp4(rng, (272, 512)), None,
+              rng.uniform(0.05, 8, (272, 16)).astype(np.float16), u64_scale(rng, 272, 0.01, 0.1), None, "bfloat16",
+              "T-CG with an fp16 group scale, tails in m and n")
     # fp8 double scale / per-tensor
     rng = np.random.default_rng(23)
     qmm_case(G, "tt_fp8_doublescale_fp16", 23, q_fp8(rng, (48, 96), E4M3), q_fp8(rng, (96, 80), E4M3), f32(rng, (1,), .5, 2),

@@ -43,9 +43,10 @@ def desc(aclnn, a, strides=None, shape=None):
 
 
 def out_tensor(shape, name):
-    dt = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "int32": torch.int32}[name]
+    dt = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "int32": torch.int32, "int8": torch.int8}[name]
     # poison so that an element the kernel fails to write is caught
-    t = torch.full(shape, -7777.0 if dt != torch.int32 else -7777, dtype=dt, device=DEV)
+    poison = {torch.int32: -7777, torch.int8: -77}.get(dt, -7777.0)
+    t = torch.full(shape, poison, dtype=dt, device=DEV)
     return t
 
 
@@ -65,7 +66,8 @@ def run_qmm_fixture(aclnn, a, meta, kernel=None):
     try:
         aclnn.quant_matmul_v5(desc(aclnn, a["x1"]), desc(aclnn, a["x2"]), desc(aclnn, a.get("x1_scale")),
                               desc(aclnn, a["x2_scale"]), d_out, desc(aclnn, a.get("bias")), meta["transpose_x1"],
-                              meta["transpose_x2"], meta["group_size"])
+                              meta["transpose_x2"], meta["group_size"], y_scale=desc(aclnn, a.get("y_scale")),
+                              x2_offset=desc(aclnn, a.get("x2_offset")))
     finally:
         os.environ.pop("OPSNN_QMM_KERNEL", None)
     torch.cuda.synchronize()

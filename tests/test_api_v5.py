@@ -119,6 +119,24 @@ def test_int8_perblock_is_accepted(aclnn):
             aclnn.destroy_executor(ex)
 
 
+def test_a8w4_plans_reserve_the_rewritten_weight(aclnn):
+    """fp8 x fp4 (mx and T-CG): phase 1 succeeds and asks for at least n * k bytes, the fp8 copy of the weight."""
+    m, k, n = 16, 128, 128
+    x1 = aclnn.Tensor((m, k), "float8_e4m3fn")
+    x2 = aclnn.Tensor((n, k), "float4_e2m1")
+    out = aclnn.Tensor((m, n), "float16")
+    s1 = aclnn.Tensor((m, 2, 2), "float8_e8m0")
+    s2 = aclnn.Tensor((n, 2, 2), "float8_e8m0")
+    st, ws, ex = aclnn.quant_matmul_v5_get_workspace_size(x1, x2, s1, s2, None, None, None, None, None, False, True, 32, out)
+    assert st == 0 and ws >= n * k, (st, ws, aclnn.last_error())
+    aclnn.destroy_executor(ex)
+    s2g = aclnn.Tensor((n, 4), "bfloat16")
+    ys = aclnn.Tensor((1, n), "uint64")
+    st, ws, ex = aclnn.quant_matmul_v5_get_workspace_size(x1, x2, None, s2g, ys, None, None, None, None, False, True, 32, out)
+    assert st == 0 and ws >= n * k, (st, ws, aclnn.last_error())
+    aclnn.destroy_executor(ex)
+
+
 def test_phase1_is_thread_safe(aclnn):
     """The reference drives phase 1 from three threads at once
     (weight_quant_batch_matmul_v2/tests/ut/op_host/op_api/test_aclnn_weight_quant_batch_matmul_v2_api.cpp:2757-2802)."""

@@ -14,9 +14,13 @@ EXACT = {n for n in golden_names("qmm_") if "_int8_" in n}
 def _ref32(a, meta):
     u64 = meta["dtypes"].get("x2_scale") == "uint64"
     g = meta["group_size"]
-    out = "int32" if meta["out_dtype"] == "int32" else "float32"
-    return qbmm_oracle.quant_matmul_v5(a["x1"], a["x2"], a.get("x1_scale"), a["x2_scale"], a.get("bias"), meta["transpose_x1"],
-                                       meta["transpose_x2"], g, out, x2_scale_is_u64=u64)
+    out = meta["out_dtype"] if meta["out_dtype"] in ("int32", "int8") else "float32"
+    bias = a.get("bias")
+    if bias is not None and bias.ndim == 2:
+        bias = bias.reshape(-1)  # the A8W4 modes take bias as (1, n)
+    return qbmm_oracle.quant_matmul_v5(a["x1"], a["x2"], a.get("x1_scale"), a["x2_scale"], bias, meta["transpose_x1"],
+                                       meta["transpose_x2"], g, out, x2_scale_is_u64=u64, y_scale=a.get("y_scale"),
+                                       x2_offset=a.get("x2_offset"))
 
 
 @pytest.mark.parametrize("kernel", [1, 0], ids=["generic", "auto"])

@@ -193,3 +193,45 @@ def test_mxfp4_operands_stored_along_m_or_n(aclnn, case):
     s2 = _e8m0(rng, batch + ((n, kq, 2) if t2 else (kq, n, 2)))
     got = _run(aclnn, x1, x2, s1, s2, None, t1, t2, "bfloat16", "qmm_umma_mxfp4", 128)
     _check(got, _oracle(x1, x2, s1, s2, None, t1, t2, "bfloat16"), "bfloat16")
+
+
+A8W4_CASES = [
+    # m, k, n, mode, out
+    (256, 512, 448, "mx", "bfloat16"),
+    (130, 1024, 300, "mx", "float16"),      # tails in m and n
+    (256, 512, 448, "tcg-bf16", "bfloat16"),
+    (130, 1024, 304, "tcg-fp16", "float16"),
+]
+
+
+@pytest.mark.parametrize("case", A8W4_CASES, ids=[str(c) for c in A8W4_CASES])
+def test_a8w4_fp8_x_fp4(aclnn, case):
+    """fp8 x fp4 (qbmmv4_kernel_golden.py:119-255): the weight is rewritten as fp8 by a pre-pass, then the mx kernel
+    (e8m0 scales) or the fp8 dequant kernel (T-CG: group scale folded into the rewrite, uint64 yScale per column) runs."""
+    import torch
+
+    from gpu_util import desc, out_tensor, out_to_np
+
+    m, k, n, mode, out_name = case
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    x1, x2 = _q(rng, (m, k), E4M3), _q(rng, (n, k), E2M1)
+    out = out_tensor((m, n), out_name)
+    if mode == "mx":
+        s1, s2 = _e8m0(rng, (m, k // 64, 2)), _e8m0(rng, (n, k // 64, 2))
+        bias = rng.standard_normal((1, n)).astype(ml_dtypes.bfloat16 if out_name == "bfloat16" else np.float16)
+        ys, expect = None, "qmm_umma_mxfp8"
+        want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias.reshape(-1), False, True, 32, out_name)
+    else:
+        s1, bias = None, None
+        s2 = rng.uniform(0.25, 4, (n, k // 32)).astype(ml_dtypes.bfloat16 if mode == "tcg-bf16" else np.float16)
+        sc = rng.uniform(0.01, 0.1, (1, n)).astype(np.float32)
+        ys = (sc.view(np.uint32) & np.uint32(0xFFFFE000)).astype(np.uint64)
+        expect = "qmm_umma_deq"
+        want = qbmm_oracle.quant_matmul_v5(x1, x2, None, s2, None, False, True, 32, out_name, y_scale=ys)
+    ws = aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2),
+                               aclnn.Tensor(out.shape, out_name, out), desc(aclnn, bias), False, True, 32, y_scale=desc(aclnn, ys))
+    torch.cuda.synchronize()
+    assert ws >= n * k  # the rewritten weight lives in the caller's workspace
+    assert aclnn.last_kernel_name().startswith(expect), aclnn.last_kernel_name()
+    assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
+    _check(out_to_np(out), want, out_name)

@@ -11,7 +11,7 @@ def _close(got, want, dtype_name):
     one unit in the last place of the output dtype on a few elements. Integer outputs: exact."""
     g = np.asarray(got).astype(np.float64)
     w = np.asarray(want).astype(np.float64)
-    if dtype_name == "int32":
+    if dtype_name in ("int32", "int8"):
         return np.array_equal(g, w)
     ulp = {"bfloat16": 2.0 ** -7, "float16": 2.0 ** -10, "float32": 2.0 ** -18}[dtype_name]
     fin = np.isfinite(w)
@@ -23,9 +23,13 @@ def _close(got, want, dtype_name):
 def test_qmm_oracle_matches_reference_golden(name):
     a, meta = load_golden(name)
     u64 = meta["dtypes"].get("x2_scale") == "uint64"
-    got = qbmm_oracle.quant_matmul_v5(a["x1"], a["x2"], a.get("x1_scale"), a["x2_scale"], a.get("bias"),
+    bias = a.get("bias")
+    if bias is not None and "y_scale" in meta["dtypes"] or (bias is not None and bias.ndim == 2):
+        bias = bias.reshape(-1)  # the A8W4 modes take bias as (1, n)
+    got = qbmm_oracle.quant_matmul_v5(a["x1"], a["x2"], a.get("x1_scale"), a["x2_scale"], bias,
                                       meta["transpose_x1"], meta["transpose_x2"],
-                                      _full_group(meta, a), meta["out_dtype"], x2_scale_is_u64=u64)
+                                      _full_group(meta, a), meta["out_dtype"], x2_scale_is_u64=u64, y_scale=a.get("y_scale"),
+                                      x2_offset=a.get("x2_offset"))
     assert got.shape == a["out"].shape
     assert _close(got, a["out"], meta["out_dtype"])
 
