@@ -209,6 +209,8 @@ QMM_WORKLOADS = {
     "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
     "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
     "c5mmt": (32, 2048, 4096, 14336, "mxfp8_t"),    # same with the weight stored (n,k), transposeX2 = true
+    "c2p": (1, 2048, 8192, 28672, "w4a16_prefill"), # the headline weight at a prefill m: dequant pre-pass + bf16 tcgen05 matmul
+    "c2ps": (1, 256, 8192, 28672, "w4a16_prefill"),
 }
 
 
@@ -266,6 +268,22 @@ def run_qmm_workload(args):
             else:
                 call = lambda i: mm()  # noqa: E731
                 nbytes = b * (m * k + k * n + (m + n) * kq * 2 + 2 * m * n)
+    elif kind == "w4a16_prefill":
+        sets = 1  # the packed weight (117 MB) plus its dequantised copy (470 MB) exceed L2 by themselves
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        x = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        w = torch.randint(-8, 8, (k, n), generator=gen, device=dev, dtype=torch.int32)
+        words = torch.zeros((k, n // 8), dtype=torch.int32, device=dev)
+        for j in range(8):
+            words |= (w[:, j::8] & 0xF) << (4 * j)
+        del w
+        scale = (torch.rand((k // 128, n), generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
+        offset = (torch.rand((k // 128, n), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
+        d = [aclnn.from_torch(t) for t in (x, words, scale, offset, out)]
+        ws_bytes = aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128)
+        workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        call = lambda i: aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128, workspace=workspace)  # noqa: E731
+        nbytes = k * n // 2 + 2 * (k // 128) * n * 2 + 2 * m * k + 2 * m * n
     elif kind.startswith("int8_kc"):
         tb = kind.endswith("_t")
         x1 = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
@@ -311,7 +329,7 @@ def run_qmm_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 9000.0 if kind.startswith("mxfp4") else 4500.0
+    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind == "w4a16_prefill" else 4500.0)
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
                       "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,

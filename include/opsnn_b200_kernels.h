@@ -92,11 +92,13 @@ OPSNN_API int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choic
 
 typedef enum {
     OPSNN_WQ_KERNEL_AUTO = 0,
-    OPSNN_WQ_KERNEL_GENERIC = 1, /* dequantise the whole weight into workspace, then a bf16/fp16 tensor-core GEMM */
+    OPSNN_WQ_KERNEL_GENERIC = 1, /* coverage kernel: any layout and stride, dequantisation fused, CUDA-core fp32 products */
     OPSNN_WQ_KERNEL_DECODE = 2,  /* fused streaming kernel for small m: int4 (n-packed) per-group/-channel; reproduces
                                     the reference's two roundings per dequantised weight */
-    OPSNN_WQ_KERNEL_DECODE_FAST = 3 /* same regime, "high performance" precision mode (inner_precise = 1): scale and
+    OPSNN_WQ_KERNEL_DECODE_FAST = 3, /* same regime, "high performance" precision mode (inner_precise = 1): scale and
                                     offset applied per k-group after the MMA in fp32; not bit-identical to DECODE */
+    OPSNN_WQ_KERNEL_PREFILL = 4  /* m beyond the decode range: the weight is dequantised (the reference's two roundings)
+                                    into workspace as (n,k) in x's dtype, then a tcgen05 bf16/fp16 matmul */
 } OpsnnWqKernelChoice;
 
 typedef struct OpsnnWqbmmParams {

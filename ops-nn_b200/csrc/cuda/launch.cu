@@ -35,6 +35,10 @@ bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 int32_t wqbmm_decode_ring_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact);
 
+bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
+uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
+int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
 
 }  // namespace opsnn
@@ -94,13 +98,17 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
 {
     if (p == nullptr) return OPSNN_WQ_KERNEL_GENERIC;
     if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
-    return wqbmm_decode_eligible(p) ? OPSNN_WQ_KERNEL_DECODE : OPSNN_WQ_KERNEL_GENERIC;
+    if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
+    // m beyond the decode range: dequantise once, multiply on the tensor cores; tiny problems stay on the one-launch coverage kernel
+    if (p->m > 16 && wqbmm_prefill_eligible(p)) return OPSNN_WQ_KERNEL_PREFILL;
+    return OPSNN_WQ_KERNEL_GENERIC;
 }
 
 uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice)
 {
     if (p == nullptr) return 0;
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    if (kernel_choice == OPSNN_WQ_KERNEL_PREFILL) return wqbmm_prefill_workspace_size(p);
     return (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) ? wqbmm_decode_workspace_size(p) : 0;
 }
 
@@ -120,6 +128,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) {
         if (!wqbmm_decode_fast_eligible(p)) return (int32_t)cudaErrorInvalidValue;
         return wqbmm_decode_fast_launch(p, static_cast<cudaStream_t>(stream));
+    }
+    if (kernel_choice == OPSNN_WQ_KERNEL_PREFILL) {
+        if (!wqbmm_prefill_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return wqbmm_prefill_launch(p, static_cast<cudaStream_t>(stream));
     }
     return wqbmm_generic_launch(p, static_cast<cudaStream_t>(stream));
 }

@@ -678,8 +678,13 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_eligible(p);
     const bool i8 = p->a_dtype == ACL_INT8 && p->b_dtype == ACL_INT8;
     const bool f8 = is_fp8(p->a_dtype) && is_fp8(p->b_dtype);
+    // bf16 x bf16 / fp16 x fp16 (the weight-only quant prefill path hands over a dequantised weight): both operands
+    // k-contiguous; seen as bytes they are the 8-bit k-major case with twice the k extent
+    const bool f16 = p->a_dtype == p->b_dtype && (p->a_dtype == ACL_BF16 || p->a_dtype == ACL_FLOAT16);
+    const int es = f16 ? 2 : 1;
     if (p->mode == OPSNN_QMM_DEQ) {
-        if (!i8 && !f8) return false;
+        if (!i8 && !f8 && !f16) return false;
+        if (f16 && (p->trans_a || !p->trans_b)) return false;
     } else if (p->mode == OPSNN_QMM_PERBLOCK) {
         if ((!f8 && !i8) || p->group_k != 128 || p->group_n != 128 || (p->group_m != 1 && p->group_m != 128)) return false;
     } else {
@@ -691,7 +696,7 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
         return false;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (p->a != nullptr && (!al16(p->a) || !al16(p->b))) return false;
-    if (p->a_ld % 16 != 0 || p->b_ld % 16 != 0 || p->a_bs % 16 != 0 || p->b_bs % 16 != 0) return false;
+    if ((p->a_ld * es) % 16 != 0 || (p->b_ld * es) % 16 != 0 || (p->a_bs * es) % 16 != 0 || (p->b_bs * es) % 16 != 0) return false;
     if (p->m < 1 || p->n < 1 || p->k < 1 || p->batch < 1 || p->batch > 0x7FFFFFFF) return false;
     if (p->batch * ((p->m + 127) / 128) * ((p->n + 31) / 32) > 0x7FFFFFFF) return false;  // tile index is 32 bit
     if (p->m > 0x7FFFFF00 || p->n > 0x7FFFFF00 || p->k > 0x7FFFFF00) return false;
@@ -714,7 +719,9 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
     a.tiles_m = (int32_t)((p->m + bm - 1) / bm);
     a.tiles_n = (int32_t)((p->n + bn - 1) / bn);
-    a.kblocks = (int32_t)((p->k + BK - 1) / BK);
+    const bool f16 = p->a_dtype == ACL_BF16 || p->a_dtype == ACL_FLOAT16;
+    const uint64_t es = f16 ? 2 : 1;  // bytes per operand element: extents and pitches below are in bytes
+    a.kblocks = (int32_t)((p->k * (int64_t)es + BK - 1) / BK);
     a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
     a.a_batched = p->a_bs != 0;
     a.b_batched = p->b_bs != 0;
@@ -726,16 +733,22 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     const uint32_t fa = a.is_int ? 1u : (p->a_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     const uint32_t fb = a.is_int ? 1u : (p->b_dtype == ACL_FLOAT8_E5M2 ? 1u : 0u);
     a.idesc = make_idesc(a.is_int ? 2u : 1u, fa, fb, (uint32_t)a.a_mn_major, (uint32_t)a.b_mn_major, (uint32_t)bm, (uint32_t)bn);
+    if (f16) {  // kind::f16 operand formats: 0 = fp16, 1 = bf16; fp32 accumulate
+        const uint32_t ff = p->a_dtype == ACL_BF16 ? 1u : 0u;
+        a.idesc = make_idesc(1u, ff, ff, 0u, 0u, (uint32_t)bm, (uint32_t)bn);
+    }
 
     CUtensorMap ma, mb;
     const uint64_t nb_a = a.a_batched ? (uint64_t)p->batch : 1, nb_b = a.b_batched ? (uint64_t)p->batch : 1;
     bool ok;
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
-    else ok = make_map(&ma, p->a, (uint64_t)p->k, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
+    else ok = make_map(&ma, p->a, (uint64_t)p->k * es, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld * es, (uint64_t)p->a_bs * es, 128);
     if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
-    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, pair ? 128u : (uint32_t)bn);
+    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld * es, (uint64_t)p->b_bs * es, pair ? 128u : (uint32_t)bn);
     if (!ok) return (int32_t)cudaErrorInvalidValue;
+    if (pair && f16) return launch_pair<ptx::MmaKind::kF16>(ma, mb, a, stream);
     if (pair) return a.is_int ? launch_pair<ptx::MmaKind::kI8>(ma, mb, a, stream) : launch_pair<ptx::MmaKind::kF8F6F4>(ma, mb, a, stream);
+    if (f16) return launch_bn<false, ptx::MmaKind::kF16>(bn, ma, mb, a, stream);
 
     if (p->mode == OPSNN_QMM_PERBLOCK)
         return a.is_int ? launch_bn<true, ptx::MmaKind::kI8>(bn, ma, mb, a, stream)

@@ -188,6 +188,12 @@ __device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t adesc, uint6
             "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
             "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
             : "memory");
+    } else if (K == MmaKind::kF16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
+            : "memory");
     } else {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"

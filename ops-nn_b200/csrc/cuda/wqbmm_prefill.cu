@@ -1,0 +1,171 @@
+// Weight-only quant matmul for m beyond the decode range ("prefill"): the weight is dequantised once into the workspace as
+// a k-contiguous (n, k) matrix in x's dtype, then the tcgen05 kind::f16 matmul of qmm_umma.cu runs on x and that matrix.
+//
+// Reference: weight_quant_batch_matmul_v2/op_kernel/arch35/weight_quant_batch_matmul_v2_reg_base_common.h:164-286 (vector
+// cores dequantise the weight tile by tile into L1, the cube unit multiplies in bf16/fp16); arithmetic of the golden
+// weight_quant_batch_matmul_v2/tests/assets/wqbmmv2_kernel_golden.py:199-297:
+//   w' = cast_x( cast_x( float(w) + float(offset) ) * float(scale) )     two roundings in x's dtype, as the decode kernel
+//   y  = cast_x( sum_k x * w' (fp32) + bias )
+// The dequantised weight is what the reference's cube unit sees too, so the result differs from the golden only by fp32
+// summation order.
+//
+// HBM cost of the pre-pass: n*k/2 (int4) read + 2*n*k written, then 2*n*k read once by the matmul (x stays in L2):
+// worthwhile once the matmul's 2*m*n*k flops dominate; below m = 17 the fused streaming decode kernels are used.
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace opsnn {
+
+bool qmm_umma_eligible(const OpsnnQmmParams* p);
+int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream);
+
+namespace {
+
+constexpr int TK = 64, TN = 64, NT = 256;
+
+template <bool kBf16>
+__device__ __forceinline__ float round_x(float v)
+{
+    if (kBf16) return __bfloat162float(__float2bfloat16_rn(v));
+    return __half2float(__float2half_rn(v));
+}
+template <bool kBf16>
+__device__ __forceinline__ float load_x(const void* base, int64_t idx)
+{
+    if (kBf16) return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(base) + idx) << 16);
+    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t*>(base) + idx)));
+}
+template <bool kBf16>
+__device__ __forceinline__ uint16_t bits_x(float v)
+{
+    if (kBf16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    return __half_as_ushort(__float2half_rn(v));
+}
+
+// One CTA: a TK x TN tile of the weight -> dst[n][k] (row pitch kp elements). kFast: int4 stored (k,n), 8 columns per 32-bit
+// word, word-aligned rows; otherwise any storage, one element at a time.
+template <bool kBf16, bool kFast>
+__global__ void __launch_bounds__(NT) wq_dequant_nk_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
+                                                           float* __restrict__ one)
+{
+    __shared__ __align__(16) uint16_t tile[TN][TK + 8];  // row pitch 144 bytes: 16-byte aligned rows, skewed banks
+    const int tid = threadIdx.x;
+    const int64_t tiles_n = (p.n + TN - 1) / TN;
+    const int64_t k0 = ((int64_t)blockIdx.x / tiles_n) * TK, n0 = ((int64_t)blockIdx.x % tiles_n) * TN;
+    if (blockIdx.x == 0 && tid == 0) *one = 1.0f;  // the unit dequant scale the matmul's epilogue multiplies by
+
+    if (kFast) {
+        // 64 rows x 8 words; thread -> (row, word): consecutive threads read consecutive words of a row
+        for (int e = tid; e < TK * (TN / 8); e += NT) {
+            const int kk = e / (TN / 8), wj = e % (TN / 8);
+            const int64_t gk = k0 + kk, gn = n0 + wj * 8;
+            uint32_t word = 0u;
+            const bool live = gk < p.k && gn < p.n;  // n % 8 == 0 on this path: a word is inside or outside as a whole
+            if (live) word = __ldcs(reinterpret_cast<const uint32_t*>(p.w) + (gk * p.w_ld + gn) / 8);
+            const int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float w = (float)(((int32_t)(word << (28 - 4 * j))) >> 28);  // sign-extended nibble j
+                if (live) {
+                    const int64_t sidx = g * p.scale_sg + (gn + j) * p.scale_sn;
+                    if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
+                    w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
+                }
+                tile[wj * 8 + j][kk] = bits_x<kBf16>(w);
+            }
+        }
+    } else {
+        for (int e = tid; e < TK * TN; e += NT) {
+            int kk, nn;
+            if (p.trans_w) { nn = e / TK; kk = e % TK; } else { kk = e / TN; nn = e % TN; }
+            const int64_t gn = n0 + nn, gk = k0 + kk;
+            float w = 0.f;
+            if (gn < p.n && gk < p.k) {
+                const int64_t idx = p.trans_w ? gn * p.w_ld + gk : gk * p.w_ld + gn;
+                w = load_as_float(p.w, idx, p.w_dtype);
+                const int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
+                const int64_t sidx = g * p.scale_sg + gn * p.scale_sn;
+                if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
+                w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
+            }
+            tile[nn][kk] = bits_x<kBf16>(w);
+        }
+    }
+    __syncthreads();
+    // 64 rows (n) x 128 bytes (64 k): 16-byte pieces, 8 per row; kp % 8 == 0 and k0 % 64 == 0 keep them aligned
+    for (int e = tid; e < TN * (TK / 8); e += NT) {
+        const int nn = e / (TK / 8), c = e % (TK / 8);
+        const int64_t gn = n0 + nn, gk = k0 + c * 8;
+        if (gn < p.n && gk < kp)
+            *reinterpret_cast<uint4*>(dst + gn * kp + gk) = *reinterpret_cast<const uint4*>(&tile[nn][c * 8]);
+    }
+}
+
+int64_t padded_k(const OpsnnWqbmmParams* p) { return (p->k + 7) / 8 * 8; }
+
+// The matmul the pre-pass leaves behind, as parameters of the quantised-matmul launcher.
+void gemm_view(const OpsnnWqbmmParams* p, OpsnnQmmParams* q, void* wdeq, const void* one)
+{
+    *q = OpsnnQmmParams{};
+    q->mode = OPSNN_QMM_DEQ;
+    q->a_dtype = q->b_dtype = q->out_dtype = p->x_dtype;
+    q->bias_dtype = p->bias != nullptr ? p->bias_dtype : -1;
+    q->scale_b_dtype = ACL_FLOAT;
+    q->trans_a = 0;
+    q->trans_b = 1;
+    q->batch = 1; q->m = p->m; q->n = p->n; q->k = p->k;
+    q->a = p->x; q->a_ld = p->x_ld;
+    q->b = wdeq; q->b_ld = padded_k(p);
+    q->scale_b = one; q->scale_b_len = 1;
+    q->group_m = q->group_n = q->group_k = 1;
+    q->bias = p->bias;
+    q->out = p->y; q->out_ld = p->y_ld; q->out_bs = p->m * p->y_ld;
+}
+
+}  // namespace
+
+uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p)
+{
+    return (uint64_t)p->n * (uint64_t)padded_k(p) * 2u + 512u;  // dequantised weight, alignment slack, the unit scale
+}
+
+bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p)
+{
+    if (getenv("OPSNN_WQ_NO_PREFILL")) return false;
+    if (p->x_dtype != ACL_BF16 && p->x_dtype != ACL_FLOAT16) return false;
+    if (p->w_dtype != ACL_INT4 && p->w_dtype != ACL_INT8) return false;
+    if (p->m < 1 || p->n < 1 || p->k < 1) return false;
+    if (p->x_ld % 8 != 0 || (p->x != nullptr && (reinterpret_cast<uintptr_t>(p->x) & 15) != 0)) return false;
+    OpsnnQmmParams q;
+    gemm_view(p, &q, reinterpret_cast<void*>(uintptr_t(256)), reinterpret_cast<const void*>(uintptr_t(256)));
+    q.a = nullptr;  // alignment of x was checked above; the stand-in addresses only serve the shape rules
+    return qmm_umma_eligible(&q);
+}
+
+int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+{
+    if (p->workspace == nullptr || p->workspace_size < wqbmm_prefill_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+    const int64_t kp = padded_k(p);
+    uint16_t* wdeq = reinterpret_cast<uint16_t*>(ws);
+    float* one = reinterpret_cast<float*>(ws + (((uint64_t)p->n * kp * 2u + 15u) & ~(uint64_t)15u));
+    const int64_t tiles = ((p->n + TN - 1) / TN) * ((p->k + TK - 1) / TK);
+    if (tiles > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+    const bool fast = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
+                      (reinterpret_cast<uintptr_t>(p->w) & 3) == 0;
+    const bool bf = p->x_dtype == ACL_BF16;
+    if (bf && fast) wq_dequant_nk_kernel<true, true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else if (bf) wq_dequant_nk_kernel<true, false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else if (fast) wq_dequant_nk_kernel<false, true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else wq_dequant_nk_kernel<false, false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    note_launch("wq_dequant_nk");
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int32_t)e;
+    OpsnnQmmParams q;
+    gemm_view(p, &q, wdeq, one);
+    if (!qmm_umma_eligible(&q)) return (int32_t)cudaErrorInvalidValue;
+    return qmm_umma_launch(&q, stream);
+}
+
+}  // namespace opsnn

@@ -191,7 +191,7 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
         // (unit tests pass NULL), so size the workspace for the decode kernel whenever the shapes allow it.
         OpsnnWqbmmParams probe = p;
         if (probe.w == nullptr) {
-            static const uint64_t dummy[4] = {0, 0, 0, 0};
+            alignas(256) static const uint64_t dummy[4] = {0, 0, 0, 0};
             probe.w = probe.x = probe.scale = dummy;
             if (probe.offset == nullptr && antiquantOffset) probe.offset = dummy;
         }
@@ -239,8 +239,7 @@ aclnnStatus wq_run(const char* api, void* workspace, uint64_t workspaceSize, acl
     if (choice == OPSNN_WQ_KERNEL_AUTO) {
         choice = opsnn_wqbmm_select_kernel(&p);
         // the plan sized the workspace for the decode kernel only if the shapes allowed it
-        if ((choice == OPSNN_WQ_KERNEL_DECODE || choice == OPSNN_WQ_KERNEL_DECODE_FAST) &&
-            workspaceSize < opsnn_wqbmm_workspace_size(&p, choice))
+        if (choice != OPSNN_WQ_KERNEL_GENERIC && workspaceSize < opsnn_wqbmm_workspace_size(&p, choice))
             choice = OPSNN_WQ_KERNEL_GENERIC;
     }
     int32_t rc = opsnn_wqbmm_launch(&p, choice, stream);

@@ -120,3 +120,45 @@ def test_dynamic_mx_quant_fixture(aclnn, name):
         want_y = (want_y[..., 0::2] & 0xF) | ((want_y[..., 1::2] & 0xF) << 4)
     assert np.array_equal(s.cpu().numpy(), a["scale"].view(np.uint8)), "e8m0 scales differ"
     assert np.array_equal(y.cpu().numpy(), want_y), "quantised elements differ"
+
+
+PREFILL_CASES = [
+    # m, k, n, group, int4, transposed weight, packed int32 words, offset, bias, x dtype
+    (17, 512, 256, 128, True, False, True, True, None, "bfloat16"),
+    (300, 1024, 640, 128, True, False, True, True, "x", "bfloat16"),      # tails in m and n tiles
+    (256, 1000, 512, 0, True, False, False, True, "f32", "float16"),      # per-channel, k not a multiple of 64
+    (130, 768, 264, 64, True, True, False, False, None, "bfloat16"),      # weight stored (n,k)
+    (64, 512, 384, 64, False, False, False, True, "x", "float16"),        # int8 weight
+    (512, 2048, 2048, 128, True, False, True, True, None, "bfloat16"),    # CTA-pair tiles
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES, ids=[str(c) for c in PREFILL_CASES])
+def test_prefill_dequant_then_tensor_core_matmul(aclnn, case):
+    """m beyond the decode range: the weight is dequantised with the reference's two roundings into workspace and multiplied
+    by the tcgen05 bf16/fp16 kernel, so the output differs from the golden only by fp32 summation order."""
+    import ml_dtypes
+
+    from gpu_util import np_name, run_wq_fixture
+
+    m, k, n, group, int4, tw, words, has_off, bias_kind, xname = case
+    xdt = ml_dtypes.bfloat16 if xname == "bfloat16" else np.float16
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    x = rng.standard_normal((m, k)).astype(xdt)
+    w = rng.integers(-8, 8, (k, n)).astype(np.int8) if int4 else rng.integers(-127, 128, (k, n)).astype(np.int8)
+    sshape = (-(-k // group), n) if group else (n,)
+    scale = rng.uniform(0.005, 0.02, sshape).astype(xdt)
+    offset = rng.uniform(-1, 1, sshape).astype(xdt) if has_off else None
+    bias = {None: None, "x": rng.standard_normal(n).astype(xdt), "f32": rng.standard_normal(n).astype(np.float32)}[bias_kind]
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, scale, offset, bias, group)
+    a = dict(x=x, w=w.T.copy() if tw else w, scale=scale.T.copy() if (tw and scale.ndim == 2) else scale,
+             offset=None if offset is None else (offset.T.copy() if (tw and offset.ndim == 2) else offset), bias=bias, out=want)
+    meta = dict(transpose_weight=tw, w_is_int4=int4, packed_int32=words, group_size=group)
+    got = run_wq_fixture(aclnn, a, meta, kernel=0)
+    assert aclnn.last_kernel_name() in ("qmm_umma_deq", "qmm_umma_pair_deq"), aclnn.last_kernel_name()
+    assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
+    g, wv = got.astype(np.float64), want.astype(np.float64)
+    ulp = 2.0 ** -7 if np_name(want) == "bfloat16" else 2.0 ** -10
+    rms = np.sqrt(np.mean(wv ** 2))
+    assert np.all(np.abs(g - wv) <= 2 * ulp * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
+    assert np.mean(g != wv) < 0.1
