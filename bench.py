@@ -200,6 +200,8 @@ QMM_WORKLOADS = {
     "c3": (1, 4096, 7168, 18432, "fp8_perblock"),
     "c3i8": (1, 4096, 7168, 18432, "int8_kc"),
     "c3i8pb": (1, 4096, 7168, 18432, "int8_perblock"),  # int8 operands with the 1x128 / 128x128 fp32 scales of c3
+    "c3t": (1, 4096, 7168, 18432, "fp8_perblock_t"),    # c3 with x2 stored (n,k), transposeX2 = true
+    "c3i8pbt": (1, 4096, 7168, 18432, "int8_perblock_t"),
     "c1t": (1, 128, 4096, 4096, "int8_kc_t"),      # same with x2 stored (n,k) and transposeX2 = true
     "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
     "c4": (8, 8192, 8192, 8192, "mxfp4"),           # both operands e2m1 + e8m0/32, x2 stored (n,k) with transposeX2 = true
@@ -297,19 +299,21 @@ def run_qmm_workload(args):
         call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, d[3], False, tb)  # noqa: E731
         nbytes = m * k + k * n + 4 * (m + 2 * n) + 2 * m * n
     else:
-        if kind == "int8_perblock":
+        tb = kind.endswith("_t")
+        wshape = (n, k) if tb else (k, n)
+        if kind.startswith("int8_perblock"):
             x1 = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
-            x2s = [torch.randint(-127, 128, (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
+            x2s = [torch.randint(-127, 128, wshape, generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
         else:
             x1 = torch.randn((m, k), generator=gen, device=dev).to(torch.float8_e4m3fn)
-            x2s = [torch.randn((k, n), generator=gen, device=dev).to(torch.float8_e4m3fn) for _ in range(sets)]
+            x2s = [torch.randn(wshape, generator=gen, device=dev).to(torch.float8_e4m3fn) for _ in range(sets)]
         s1 = torch.rand((m, k // 128), generator=gen, device=dev) + 0.5
-        s2 = torch.rand((k // 128, n // 128), generator=gen, device=dev) + 0.5
+        s2 = torch.rand((n // 128, k // 128) if tb else (k // 128, n // 128), generator=gen, device=dev) + 0.5
         d = [aclnn.from_torch(t) for t in (x1, s1, s2)]
         dx2 = [aclnn.from_torch(t) for t in x2s]
         dout = aclnn.from_torch(out)
         group = (1 << 32) | (128 << 16) | 128
-        call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, None, False, False, group)  # noqa: E731
+        call = lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % sets], d[1], d[2], dout, None, False, tb, group)  # noqa: E731
         nbytes = m * k + k * n + 4 * (m * k // 128 + k * n // 16384) + 2 * m * n
     for i in range(max(args.warmup, 3)):
         call(i)

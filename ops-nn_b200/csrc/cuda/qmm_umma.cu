@@ -670,6 +670,7 @@ int32_t launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs
 
 #include "qmm_mx_umma.cuh"
 #include "qmm_umma_pair.cuh"
+#include "qmm_umma_pair_pb.cuh"
 #include "qmm_mx_umma_pair.cuh"
 
 bool qmm_umma_eligible(const OpsnnQmmParams* p)
@@ -703,19 +704,49 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
     return true;
 }
 
-uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p) { return p->mode == OPSNN_QMM_MX ? qmm_mx_umma_workspace_size(p) : 0; }
+uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p)
+{
+    return p->mode == OPSNN_QMM_MX ? qmm_mx_umma_workspace_size(p) : pair_pb_workspace(p);
+}
 
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
     const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32 && p->out_dtype != ACL_INT8;
-    const int bn = pair ? 256 : pick_bn(p);
-    const int bm = pair ? 256 : BM;
+    // per-block on CTA pairs: 256 x 128 tiles, B k-contiguous (an x2 stored (k,n) goes through the workspace transposed)
+    bool pair_pb = pair_pb_worthwhile(p);
+    const uint8_t* b_ptr = static_cast<const uint8_t*>(p->b);
+    int64_t b_ld = p->b_ld, b_bs = p->b_bs;
+    int b_trans = p->trans_b;
+    if (pair_pb && !p->trans_b) {
+        const uint64_t need = pair_pb_workspace(p);
+        uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+        if (p->workspace == nullptr || p->workspace_size < need) {
+            pair_pb = false;  // no room for the transposed copy: single-CTA kernel on the operand as stored
+        } else {
+            const int64_t kp = (p->k + 15) / 16 * 16, nb = p->b_bs != 0 ? p->batch : 1;
+            const int64_t tiles = ((p->k + 63) / 64) * ((p->n + 63) / 64);
+            if (tiles > 0x7FFFFFFF || nb > 65535) return (int32_t)cudaErrorInvalidConfiguration;
+            if (p->n % 4 == 0 && p->b_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(b_ptr) & 3) == 0 && p->b_bs % 4 == 0)
+                transpose_bytes_words_kernel<<<dim3((unsigned)tiles, (unsigned)nb), 256, 0, stream>>>(b_ptr, ws, p->k, p->n, p->b_ld, kp,
+                                                                                                      p->b_bs, p->n * kp);
+            else
+                transpose_bytes_kernel<<<dim3((unsigned)tiles, (unsigned)nb), 256, 0, stream>>>(b_ptr, ws, p->k, p->n, p->b_ld, kp,
+                                                                                                p->b_bs, p->n * kp);
+            note_launch("transpose_bytes");
+            b_ptr = ws;
+            b_ld = kp;
+            b_bs = p->b_bs != 0 ? p->n * kp : 0;
+            b_trans = 1;
+        }
+    }
+    const int bn = pair ? 256 : (pair_pb ? 128 : pick_bn(p));
+    const int bm = (pair || pair_pb) ? 256 : BM;
     UmmaArgs a{};
     a.mode = p->mode;
     a.is_int = p->a_dtype == ACL_INT8;
     a.a_mn_major = p->trans_a ? 1 : 0;   // stored (k,m): m contiguous
-    a.b_mn_major = p->trans_b ? 0 : 1;   // stored (k,n): n contiguous
+    a.b_mn_major = b_trans ? 0 : 1;      // stored (k,n): n contiguous
     a.batch = p->batch; a.m = p->m; a.n = p->n; a.k = p->k;
     a.tiles_m = (int32_t)((p->m + bm - 1) / bm);
     a.tiles_n = (int32_t)((p->n + bn - 1) / bn);
@@ -724,7 +755,7 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     a.kblocks = (int32_t)((p->k * (int64_t)es + BK - 1) / BK);
     a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
     a.a_batched = p->a_bs != 0;
-    a.b_batched = p->b_bs != 0;
+    a.b_batched = b_bs != 0;
     a.out_dtype = p->out_dtype; a.bias_dtype = p->bias_dtype; a.scale_b_dtype = p->scale_b_dtype; a.deq_flags = p->deq_flags;
     a.scale_a = p->scale_a; a.scale_b = p->scale_b; a.scale_a_len = p->scale_a_len; a.scale_b_len = p->scale_b_len;
     a.sa_bs = p->sa_bs; a.sb_bs = p->sb_bs; a.group_m = p->group_m > 0 ? p->group_m : 1;
@@ -743,9 +774,14 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     bool ok;
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k * es, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld * es, (uint64_t)p->a_bs * es, 128);
-    if (a.b_mn_major) ok = ok && make_map(&mb, p->b, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)p->b_ld, (uint64_t)p->b_bs, 128);
-    else ok = ok && make_map(&mb, p->b, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)p->b_ld * es, (uint64_t)p->b_bs * es, pair ? 128u : (uint32_t)bn);
+    if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128);
+    else ok = ok && make_map(&mb, b_ptr, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)b_ld * es, (uint64_t)b_bs * es,
+                             pair ? 128u : (pair_pb ? 64u : (uint32_t)bn));
     if (!ok) return (int32_t)cudaErrorInvalidValue;
+    if (pair_pb) {
+        if (a.is_int) return launch_pair_pb<ptx::MmaKind::kI8, 8>(ma, mb, a, stream);
+        return launch_pair_pb<ptx::MmaKind::kF8F6F4, 4>(ma, mb, a, stream);
+    }
     if (pair && f16) return launch_pair<ptx::MmaKind::kF16>(ma, mb, a, stream);
     if (pair) return a.is_int ? launch_pair<ptx::MmaKind::kI8>(ma, mb, a, stream) : launch_pair<ptx::MmaKind::kF8F6F4>(ma, mb, a, stream);
     if (f16) return launch_bn<false, ptx::MmaKind::kF16>(bn, ma, mb, a, stream);

@@ -1,0 +1,362 @@
+// Per-block (1x128 / 128x128 fp32 scales) fp8 and int8 matmul on CTA pairs (tcgen05 cta_group::2). Included by qmm_umma.cu.
+//
+// Why. The single-CTA per-block kernel uses 128 x 128 tiles (the promotion epilogue keeps 128 fp32 sums per thread), which
+// pull 32 KB of operands from L2 per 128-deep k-block; with the epilogue switched off the main loop still needs ~700 cycles
+// per k-block against 256 of tensor work: it is bound by the L2 -> SM operand feed. A CTA pair shares a 256 x 128 tile: each
+// CTA loads its own 128 rows of A and 64 of the 128 rows of B (24 KB per k-block), keeps a 128 x 128 accumulator in its own
+// TMEM and runs the same promotion on it.
+//
+// B must be k-contiguous here (64 rows of a k-major tile per CTA; half a 128-byte swizzle row of an n-major tile is not a
+// legal operand): an x2 stored (k,n) is transposed into workspace first by transpose_bytes_kernel.
+//
+// Choreography per k-block (= one accumulation group), four TMEM buffers of 128 columns:
+//   producers (both CTAs) : wait own empty[s]; even CTA arms full[s] for both CTAs' bytes; each loads A (128 rows) and B (64 rows)
+//   MMA warp (even CTA)   : wait tempty[buf] (all epilogue warps of the pair), wait full[s], 4 pair MMAs (first overwrites),
+//                           commit -> empty[s] and tfull[buf] of both CTAs
+//   epilogue (both CTAs)  : wait own tfull[buf]; TMEM -> registers; acc += part * (s1 * s2); arrive on the even CTA's tempty[buf]
+// All waits bounded, teardown through a cluster barrier, as in qmm_umma_pair.cuh.
+namespace {
+
+// (rows, cols) bytes -> (cols, rows); 64 x 64 tiles through shared memory. src row pitch src_ld, dst rows packed to dst_ld.
+__global__ void __launch_bounds__(256) transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
+                                                              int64_t cols, int64_t src_ld, int64_t dst_ld, int64_t src_bs, int64_t dst_bs)
+{
+    __shared__ uint8_t t[64][65];
+    const int64_t tiles_c = (cols + 63) / 64;
+    const int64_t r0 = ((int64_t)blockIdx.x / tiles_c) * 64, c0 = ((int64_t)blockIdx.x % tiles_c) * 64;
+    src += (int64_t)blockIdx.y * src_bs;
+    dst += (int64_t)blockIdx.y * dst_bs;
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int r = e >> 6, c = e & 63;
+        t[r][c] = (r0 + r < rows && c0 + c < cols) ? src[(r0 + r) * src_ld + c0 + c] : (uint8_t)0;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int c = e >> 6, r = e & 63;
+        if (c0 + c < cols && r0 + r < rows) dst[(c0 + c) * dst_ld + r0 + r] = t[r][c];
+    }
+}
+
+// The same for word-aligned operands (cols % 4 == 0, src_ld % 4 == 0, dst_ld % 4 == 0, 4-byte aligned bases): a thread
+// moves a 4 x 4 byte block - four 32-bit loads, a register transpose with byte permutes, four 32-bit stores into a
+// shared-memory tile that is then written out in rows of 64 bytes.
+__global__ void __launch_bounds__(256) transpose_bytes_words_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
+                                                                    int64_t cols, int64_t src_ld, int64_t dst_ld, int64_t src_bs,
+                                                                    int64_t dst_bs)
+{
+    __shared__ uint32_t t[64][17];  // [dst row (src column)][4-byte group of src rows]
+    const int64_t tiles_c = (cols + 63) / 64;
+    const int64_t r0 = ((int64_t)blockIdx.x / tiles_c) * 64, c0 = ((int64_t)blockIdx.x % tiles_c) * 64;
+    src += (int64_t)blockIdx.y * src_bs;
+    dst += (int64_t)blockIdx.y * dst_bs;
+    const int cq = threadIdx.x & 15, rq = threadIdx.x >> 4;  // 4-column group, 4-row group
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t rr = r0 + 4 * rq + i, cc = c0 + 4 * cq;
+        r[i] = (rr < rows && cc < cols) ? __ldcs(reinterpret_cast<const uint32_t*>(src + rr * src_ld + cc)) : 0u;
+    }
+    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
+    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
+    t[4 * cq + 0][rq] = __byte_perm(t0, t1, 0x5410);
+    t[4 * cq + 1][rq] = __byte_perm(t0, t1, 0x7632);
+    t[4 * cq + 2][rq] = __byte_perm(t2, t3, 0x5410);
+    t[4 * cq + 3][rq] = __byte_perm(t2, t3, 0x7632);
+    __syncthreads();
+#pragma unroll
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+        const int c = e >> 4, g = e & 15;  // dst row, 4-byte group
+        const int64_t oc = c0 + c, orow = r0 + 4 * g;
+        if (oc < cols && orow < dst_ld) *reinterpret_cast<uint32_t*>(dst + oc * dst_ld + orow) = t[c][g];
+    }
+}
+
+template <ptx::MmaKind kKind, int EW>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((EW + 2) * 32, 1)
+qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
+{
+    constexpr int BN = 128, NBUF = 4;
+    constexpr int kCols = BN * 4 / EW;          // accumulator columns per epilogue thread
+    constexpr uint32_t kBHalf = 64 * BK;        // this CTA's 64 rows of the k-major B tile
+    constexpr uint32_t kStage = kATile + kBHalf;
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)a.stages * kStage);
+    uint64_t* full = bars;                    // [stages]  used in the even CTA only
+    uint64_t* empty = bars + a.stages;        // [stages]
+    uint64_t* tfull = bars + 2 * a.stages;    // [NBUF]
+    uint64_t* tempty = tfull + NBUF;          // [NBUF]    used in the even CTA only
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tempty + NBUF);
+    volatile uint32_t* abort_flag = tmem_ptr + 1;
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < NBUF; ++b) {
+            ptx::mbar_init(&tfull[b], 1);
+            ptx::mbar_init(&tempty[b], 2 * EW);
+        }
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == EW + 1) ptx::tmem_alloc_pair(tmem_ptr, kTmemCols);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    const uint32_t tiles_per_batch = (uint32_t)a.tiles_m * (uint32_t)a.tiles_n;
+    const uint32_t ntiles = (uint32_t)a.num_tiles;
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const uint32_t smem0 = ptx::smem_u32(smem), full0 = ptx::smem_u32(full), empty0 = ptx::smem_u32(empty);
+    const uint32_t tfull0 = ptx::smem_u32(tfull), tempty0 = ptx::smem_u32(tempty);
+    const uint32_t stages = (uint32_t)a.stages;
+    const int kblocks = a.kblocks;
+
+    if (warp == EW) {
+        // ======================= TMA producer (both CTAs) =======================
+        if (lane == 0) {
+            ptx::tma_prefetch_desc(&map_a);
+            ptx::tma_prefetch_desc(&map_b);
+        }
+        __syncwarp();
+        uint32_t s = 0, par = 0;
+        bool ok = true;
+        const bool a_mn = a.a_mn_major != 0;
+        const uint32_t lead_full0 = full0 & ptx::kPeerBitMask;
+        for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * 256 + (int32_t)rank * 128;
+            const int32_t n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN + (int32_t)rank * 64;
+            const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
+            int32_t kk = 0;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
+                    report(abort_flag, (1u << 8) | 1u);
+                    ok = false;
+                    break;
+                }
+                if (ptx::elect_one()) {
+                    const uint32_t fb = lead_full0 + 8u * s, sa = smem0 + s * kStage, sb = sa + (uint32_t)kATile;
+                    if (leader) ptx::mbar_expect_tx_a(full0 + 8u * s, 2u * kStage);
+                    ptx::tma_load_3d_pair(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
+                    ptx::tma_load_3d_pair(sb, &map_b, fb, kk, n0, bb);
+                }
+                __syncwarp();
+                kk += BK;
+                if (++s == stages) {
+                    s = 0;
+                    par ^= 1u;
+                }
+            }
+        }
+    } else if (warp == EW + 1) {
+        // ======================= MMA issuer (even CTA only): every k-block is its own accumulation group =======================
+        if (leader) {
+            uint32_t s = 0, par = 0, buf = 0, bpar = 0;
+            bool ok = true;
+            const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
+            const uint64_t db0 = ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+            const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0;
+            const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull;
+            const uint32_t a_k1 = a.a_mn_major ? 256u : 2u;
+            const uint32_t idesc = a.idesc;
+            for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!ptx::mbar_wait_a(tempty0 + 8u * buf, bpar ^ 1u, abort_flag)) {
+                        report(abort_flag, (2u << 8) | 1u);
+                        ok = false;
+                        break;
+                    }
+                    if (!ptx::mbar_wait_a(full0 + 8u * s, par, abort_flag)) {
+                        report(abort_flag, (2u << 8) | 2u);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    if (ptx::elect_one()) {
+                        const uint32_t stage_off = (s * kStage) >> 4;
+                        const uint32_t d = tmem_base + buf * BN;
+                        const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            ptx::umma_pair<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * 2u), idesc, k == 0 ? 0u : 1u);
+                        ptx::umma_commit_pair(empty0 + 8u * s, (uint16_t)3);
+                        ptx::umma_commit_pair(tfull0 + 8u * buf, (uint16_t)3);
+                    }
+                    __syncwarp();
+                    if (++s == stages) {
+                        s = 0;
+                        par ^= 1u;
+                    }
+                    if (++buf == NBUF) {
+                        buf = 0;
+                        bpar ^= 1u;
+                    }
+                }
+            }
+        }
+    } else {
+        // ======================= epilogue warps (both CTAs): own 128 rows, kCols columns each =======================
+        const int quad = warp & 3, part = warp >> 2;
+        const uint32_t lane_addr = ((uint32_t)(quad * 32) << 16) + (uint32_t)(part * kCols);
+        const uint32_t lead_tempty0 = tempty0 & ptx::kPeerBitMask;
+        uint32_t buf = 0, bpar = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+            const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
+            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * 256 + (int64_t)rank * 128, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            const int64_t row = m0 + quad * 32 + lane;
+            const bool row_ok = row < a.m;
+            uint8_t* out = reinterpret_cast<uint8_t*>(a.out) + b * a.out_bs * out_elem_bytes(a.out_dtype);
+            const int64_t colbase = n0 + part * kCols;
+            float acc[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
+            const float* s1 = reinterpret_cast<const float*>(a.scale_a) + b * a.sa_bs;
+            const float* s2 = reinterpret_cast<const float*>(a.scale_b) + b * a.sb_bs;
+            const int64_t mg = (row_ok ? row : 0) / a.group_m;
+            const int64_t n_mg = (a.m + a.group_m - 1) / a.group_m, n_ng = (a.n + 127) / 128;
+            const int64_t ng = min(colbase / 128, n_ng - 1);
+            auto load_s1 = [&](int kb) {
+                kb = min(kb, a.kblocks - 1);
+                return a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
+            };
+            auto load_s2 = [&](int kb) {
+                kb = min(kb, a.kblocks - 1);
+                return a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
+            };
+            float s1_next[4], s2_next[4];  // raw scales of the next four k-blocks; multiplied when their turn comes
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                s1_next[j] = load_s1(j);
+                s2_next[j] = load_s2(j);
+            }
+            for (int kb0 = 0; kb0 < a.kblocks && ok; kb0 += 4) {
+                float sc_cur[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc_cur[j] = __fmul_rn(s1_next[j], s2_next[j]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s1_next[j] = load_s1(kb0 + 4 + j);
+                    s2_next[j] = load_s2(kb0 + 4 + j);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (kb0 + j >= a.kblocks) break;
+                    const float sc = sc_cur[j];
+                    if (!ptx::mbar_wait_a(tfull0 + 8u * buf, bpar, abort_flag)) {
+                        report(abort_flag, (3u << 8) | 2u);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    constexpr int W = 16;
+                    const uint32_t t0 = tmem_base + lane_addr + buf * BN;
+                    uint32_t va[W], vb[W];
+                    ptx::tmem_ld16(t0, va);
+#pragma unroll
+                    for (int c = 0; c < kCols; c += 2 * W) {
+                        ptx::tmem_ld_wait();
+                        ptx::tmem_ld16(t0 + c + W, vb);
+#pragma unroll
+                        for (int i = 0; i < W; ++i) acc[c + i] = promote<kKind>(va[i], sc, acc[c + i]);
+                        ptx::tmem_ld_wait();
+                        if (c + 2 * W < kCols) {
+                            ptx::tmem_ld16(t0 + c + 2 * W, va);
+                        } else {
+                            ptx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
+                        }
+#pragma unroll
+                        for (int i = 0; i < W; ++i) acc[c + W + i] = promote<kKind>(vb[i], sc, acc[c + W + i]);
+                    }
+                    if (++buf == NBUF) {
+                        buf = 0;
+                        bpar ^= 1u;
+                    }
+                }
+            }
+            if (ok && row_ok) {
+#pragma unroll
+                for (int c = 0; c < kCols; c += 32) {
+                    const int64_t col = colbase + c;
+                    const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
+                    if (valid > 0) {
+                        float f[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = acc[c + i];
+                        if (a.bias != nullptr) {
+                            const uint8_t* bias = reinterpret_cast<const uint8_t*>(a.bias) +
+                                                  b * a.bias_bs * ((a.bias_dtype == ACL_FLOAT || a.bias_dtype == ACL_INT32) ? 4 : 2);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < valid) f[i] = __fadd_rn(f[i], load_as_float(bias, col + i, a.bias_dtype));
+                        }
+                        store_row32(a, out, row, col, f, valid);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown ----
+    if (*abort_flag != 0u) __nanosleep(200000);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == EW + 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+template <ptx::MmaKind KIND, int EW>
+int32_t launch_pair_pb(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
+{
+    constexpr int kStage = kATile + 64 * BK;
+    int stages = (227 * 1024 - 2048) / kStage;
+    if (stages > 8) stages = 8;
+    if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * kStage + 1024 + 256;
+    auto kern = qmm_umma_pair_pb_kernel<KIND, EW>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return (int32_t)cudaGetLastError();
+        configured = true;
+    }
+    int64_t pairs = sm_count() / 2;
+    if (a.num_tiles < pairs) pairs = a.num_tiles;
+    kern<<<(unsigned)(2 * pairs), (EW + 2) * 32, smem, stream>>>(ma, mb, a);
+    note_launch("qmm_umma_pair_perblock");
+    return (int32_t)cudaGetLastError();
+}
+
+// Pair tiles for per-block problems: worthwhile once there are enough 256 x 128 tiles to fill the pairs.
+bool pair_pb_worthwhile(const OpsnnQmmParams* p)
+{
+    if (p->mode != OPSNN_QMM_PERBLOCK) return false;
+    if (const char* e = getenv("OPSNN_QMM_PAIR")) return atoi(e) != 0;
+    const int64_t tiles = p->batch * ((p->m + 255) / 256) * ((p->n + 127) / 128);
+    return p->m >= 256 && tiles >= 74;
+}
+
+uint64_t pair_pb_workspace(const OpsnnQmmParams* p)
+{
+    if (!pair_pb_worthwhile(p) || p->trans_b) return 0;
+    const uint64_t kp = ((uint64_t)p->k + 15u) & ~(uint64_t)15u;
+    return (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * kp + 256u;  // x2 rewritten (n,k)
+}
+
+}  // namespace

@@ -43,9 +43,8 @@ __device__ __forceinline__ uint16_t bits_x(float v)
     return __half_as_ushort(__float2half_rn(v));
 }
 
-// One CTA: a TK x TN tile of the weight -> dst[n][k] (row pitch kp elements). kFast: int4 stored (k,n), 8 columns per 32-bit
-// word, word-aligned rows; otherwise any storage, one element at a time.
-template <bool kBf16, bool kFast>
+// One CTA: a TK x TN tile of the weight -> dst[n][k] (row pitch kp elements). Any storage, one element at a time.
+template <bool kBf16>
 __global__ void __launch_bounds__(NT) wq_dequant_nk_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
                                                            float* __restrict__ one)
 {
@@ -54,43 +53,20 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_kernel(const OpsnnWqbmmParam
     const int64_t tiles_n = (p.n + TN - 1) / TN;
     const int64_t k0 = ((int64_t)blockIdx.x / tiles_n) * TK, n0 = ((int64_t)blockIdx.x % tiles_n) * TN;
     if (blockIdx.x == 0 && tid == 0) *one = 1.0f;  // the unit dequant scale the matmul's epilogue multiplies by
-
-    if (kFast) {
-        // 64 rows x 8 words; thread -> (row, word): consecutive threads read consecutive words of a row
-        for (int e = tid; e < TK * (TN / 8); e += NT) {
-            const int kk = e / (TN / 8), wj = e % (TN / 8);
-            const int64_t gk = k0 + kk, gn = n0 + wj * 8;
-            uint32_t word = 0u;
-            const bool live = gk < p.k && gn < p.n;  // n % 8 == 0 on this path: a word is inside or outside as a whole
-            if (live) word = __ldcs(reinterpret_cast<const uint32_t*>(p.w) + (gk * p.w_ld + gn) / 8);
+    for (int e = tid; e < TK * TN; e += NT) {
+        int kk, nn;
+        if (p.trans_w) { nn = e / TK; kk = e % TK; } else { kk = e / TN; nn = e % TN; }
+        const int64_t gn = n0 + nn, gk = k0 + kk;
+        float w = 0.f;
+        if (gn < p.n && gk < p.k) {
+            const int64_t idx = p.trans_w ? gn * p.w_ld + gk : gk * p.w_ld + gn;
+            w = load_as_float(p.w, idx, p.w_dtype);
             const int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float w = (float)(((int32_t)(word << (28 - 4 * j))) >> 28);  // sign-extended nibble j
-                if (live) {
-                    const int64_t sidx = g * p.scale_sg + (gn + j) * p.scale_sn;
-                    if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
-                    w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
-                }
-                tile[wj * 8 + j][kk] = bits_x<kBf16>(w);
-            }
+            const int64_t sidx = g * p.scale_sg + gn * p.scale_sn;
+            if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
+            w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
         }
-    } else {
-        for (int e = tid; e < TK * TN; e += NT) {
-            int kk, nn;
-            if (p.trans_w) { nn = e / TK; kk = e % TK; } else { kk = e / TN; nn = e % TN; }
-            const int64_t gn = n0 + nn, gk = k0 + kk;
-            float w = 0.f;
-            if (gn < p.n && gk < p.k) {
-                const int64_t idx = p.trans_w ? gn * p.w_ld + gk : gk * p.w_ld + gn;
-                w = load_as_float(p.w, idx, p.w_dtype);
-                const int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
-                const int64_t sidx = g * p.scale_sg + gn * p.scale_sn;
-                if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
-                w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
-            }
-            tile[nn][kk] = bits_x<kBf16>(w);
-        }
+        tile[nn][kk] = bits_x<kBf16>(w);
     }
     __syncthreads();
     // 64 rows (n) x 128 bytes (64 k): 16-byte pieces, 8 per row; kp % 8 == 0 and k0 % 64 == 0 keep them aligned
@@ -99,6 +75,78 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_kernel(const OpsnnWqbmmParam
         const int64_t gn = n0 + nn, gk = k0 + c * 8;
         if (gn < p.n && gk < kp)
             *reinterpret_cast<uint4*>(dst + gn * kp + gk) = *reinterpret_cast<const uint4*>(&tile[nn][c * 8]);
+    }
+}
+
+// two fp32 -> packed pair in x's dtype (lo in the low half), and back
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi)
+{
+    if (kBf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(uint32_t v)
+{
+    if (kBf16) return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
+// The common layout: int4 stored (k,n) as 32-bit words of 8 columns, n % 8 == 0, word-aligned rows, scale/offset
+// contiguous along n and constant over a 64-row tile (per-channel, or groups of a multiple of 64 rows).
+// Thread = one word column (8 n) x two adjacent k rows: the two rows of a column leave as one packed pair, so the tile
+// is written with 32-bit stores; 16-byte pieces of a tile row are XOR-swizzled by the word column (conflict-free both ways).
+template <bool kBf16>
+__global__ void __launch_bounds__(NT) wq_dequant_nk_words_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
+                                                                 float* __restrict__ one)
+{
+    __shared__ __align__(16) uint32_t tile[TN][TK / 2];  // [n][k pair], 128 bytes per row
+    const int tid = threadIdx.x;
+    const int64_t tiles_n = (p.n + TN - 1) / TN;
+    const int64_t k0 = ((int64_t)blockIdx.x / tiles_n) * TK, n0 = ((int64_t)blockIdx.x % tiles_n) * TN;
+    if (blockIdx.x == 0 && tid == 0) *one = 1.0f;
+    const int wj = tid & 7, kr = tid >> 3;  // word column 0..7, row pair 0..31
+    const int64_t gn = n0 + wj * 8, gk = k0 + 2 * kr;
+    const bool col_live = gn < p.n;
+    uint32_t w0 = 0u, w1 = 0u;
+    if (col_live && gk < p.k) w0 = __ldcs(reinterpret_cast<const uint32_t*>(p.w) + (gk * p.w_ld + gn) / 8);
+    if (col_live && gk + 1 < p.k) w1 = __ldcs(reinterpret_cast<const uint32_t*>(p.w) + ((gk + 1) * p.w_ld + gn) / 8);
+    float sc[8], of[8];
+    {
+        const int64_t g = p.group_size > 0 ? min(k0, p.k - 1) / p.group_size : 0;
+        const int64_t sidx = g * p.scale_sg + (col_live ? gn : 0) * p.scale_sn;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sc[j] = load_x<kBf16>(p.scale, sidx + j * p.scale_sn);
+            of[j] = p.offset != nullptr ? load_x<kBf16>(p.offset, sidx + j * p.scale_sn) : 0.f;
+        }
+    }
+    const bool has_off = p.offset != nullptr;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float a = (float)(((int32_t)(w0 << (28 - 4 * j))) >> 28);  // sign-extended nibble j of each row
+        float b = (float)(((int32_t)(w1 << (28 - 4 * j))) >> 28);
+        if (has_off) {
+            const float2 r = unpack2<kBf16>(pack2<kBf16>(__fadd_rn(a, of[j]), __fadd_rn(b, of[j])));  // first rounding
+            a = r.x;
+            b = r.y;
+        }
+        uint32_t v = pack2<kBf16>(__fmul_rn(a, sc[j]), __fmul_rn(b, sc[j]));  // second rounding
+        if (gk >= p.k) v = 0u;
+        else if (gk + 1 >= p.k) v &= 0xFFFFu;
+        tile[wj * 8 + j][(((kr >> 2) ^ wj) << 2) | (kr & 3)] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = tid; e < TN * 8; e += NT) {
+        const int nn = e >> 3, c = e & 7;  // row, 16-byte piece (8 k)
+        const int64_t on = n0 + nn, ok = k0 + c * 8;
+        if (on < p.n && ok < kp)
+            *reinterpret_cast<uint4*>(dst + on * kp + ok) = *reinterpret_cast<const uint4*>(&tile[nn][(c ^ (nn >> 3)) << 2]);
     }
 }
 
@@ -152,13 +200,14 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     float* one = reinterpret_cast<float*>(ws + (((uint64_t)p->n * kp * 2u + 15u) & ~(uint64_t)15u));
     const int64_t tiles = ((p->n + TN - 1) / TN) * ((p->k + TK - 1) / TK);
     if (tiles > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+    const bool tile_const_scale = p->group_size == 0 || p->group_size % TK == 0;
     const bool fast = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
-                      (reinterpret_cast<uintptr_t>(p->w) & 3) == 0;
+                      (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && tile_const_scale;
     const bool bf = p->x_dtype == ACL_BF16;
-    if (bf && fast) wq_dequant_nk_kernel<true, true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
-    else if (bf) wq_dequant_nk_kernel<true, false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
-    else if (fast) wq_dequant_nk_kernel<false, true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
-    else wq_dequant_nk_kernel<false, false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    if (bf && fast) wq_dequant_nk_words_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else if (bf) wq_dequant_nk_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else if (fast) wq_dequant_nk_words_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    else wq_dequant_nk_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     note_launch("wq_dequant_nk");
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int32_t)e;

@@ -230,3 +230,45 @@ def test_older_entry_points_v4_v3_match_v5(aclnn):
                           bias=desc(aclnn, bias), api="v3")
     torch.cuda.synchronize()
     assert np.array_equal(out_to_np(out3).view(np.uint16), want3.view(np.uint16))
+
+
+PAIR_PB_CASES = [
+    # m, k, n, t1, t2, group_m, int8, bias, out
+    (512, 512, 256, False, True, 1, False, None, "bfloat16"),       # k-major B as stored
+    (512, 512, 256, False, False, 1, False, None, "bfloat16"),      # x2 stored (k,n): transposed into workspace first
+    (300, 400, 304, False, False, 128, False, None, "float16"),     # tails in m, n, k; B-B
+    (272, 528, 400, True, True, 1, False, None, "float32"),         # x1 stored (k,m)
+    (512, 1024, 384, False, False, 1, True, "f32", "bfloat16"),     # int8: bit-exact
+    (304, 400, 304, True, True, 1, True, "i32", "bfloat16"),
+]
+
+
+@pytest.mark.parametrize("case", PAIR_PB_CASES, ids=[str(c) for c in PAIR_PB_CASES])
+def test_perblock_cta_pairs(aclnn, case, monkeypatch):
+    """The per-block kernels on CTA pairs (256 x 128 tiles, four TMEM buffers): same promotion arithmetic as the single-CTA
+    kernel; the int8 form stays bit-identical to the reference."""
+    from gpu_util import check_close
+
+    m, k, n, t1, t2, gm, is_int, bias_kind, out_name = case
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    kb, mg, ng = -(-k // 128), -(-m // gm), -(-n // 128)
+    if is_int:
+        x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
+        x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
+        s1 = rng.uniform(1e-3, 1e-2, (kb, mg) if t1 else (mg, kb)).astype(np.float32)
+        s2 = rng.uniform(1e-2, 1e-1, (ng, kb) if t2 else (kb, ng)).astype(np.float32)
+    else:
+        x1 = _fp8(rng, (k, m) if t1 else (m, k), E4M3)
+        x2 = _fp8(rng, (n, k) if t2 else (k, n), E4M3)
+        s1 = rng.uniform(0.5, 2, (kb, mg) if t1 else (mg, kb)).astype(np.float32)
+        s2 = rng.uniform(0.5, 2, (ng, kb) if t2 else (kb, ng)).astype(np.float32)
+    bias = {None: None, "f32": rng.standard_normal(n).astype(np.float32), "i32": rng.integers(-5, 6, n).astype(np.int32)}[bias_kind]
+    group = (gm << 32) | (128 << 16) | 128
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, group, out_name)
+    monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, group, out_name, "qmm_umma_pair_perblock")
+    if is_int:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    else:
+        ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, t1, t2, group, "float32")
+        check_close(got, want, ref32, out_name)

@@ -126,7 +126,7 @@ PREFILL_CASES = [
     # m, k, n, group, int4, transposed weight, packed int32 words, offset, bias, x dtype
     (17, 512, 256, 128, True, False, True, True, None, "bfloat16"),
     (300, 1024, 640, 128, True, False, True, True, "x", "bfloat16"),      # tails in m and n tiles
-    (256, 1000, 512, 0, True, False, False, True, "f32", "float16"),      # per-channel, k not a multiple of 64
+    (256, 1000, 512, 0, True, False, False, True, "x", "float16"),        # per-channel, k not a multiple of 64
     (130, 768, 264, 64, True, True, False, False, None, "bfloat16"),      # weight stored (n,k)
     (64, 512, 384, 64, False, False, False, True, "x", "float16"),        # int8 weight
     (512, 2048, 2048, 128, True, False, True, True, None, "bfloat16"),    # CTA-pair tiles
