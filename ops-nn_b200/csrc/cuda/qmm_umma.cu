@@ -26,6 +26,7 @@
 // status word (opsnn_qmm_umma_status) and the CTA tears down normally (TMEM freed).
 #include <cstdio>
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -60,6 +61,12 @@ struct UmmaArgs {
     const uint8_t* sfa;
     const uint8_t* sfb;
     int64_t sfa_bs, sfb_bs;  // bytes between batches; 0 broadcasts
+    // split-k (dequant kernel, few tiles): work item = (tile, split); every split writes its raw accumulator tile to
+    // ks_part, the split that arrives last at the tile's counter sums them in split order and runs the epilogue
+    int32_t ksplit;                    // 1: off
+    uint32_t* ks_part;                 // [tile][split][128][BN] raw 32-bit accumulators
+    unsigned long long* ks_count;      // [tile] (nonce << 8) | arrivals; any other nonce counts as zero arrivals
+    unsigned long long ks_nonce;
 };
 
 __device__ unsigned int g_umma_status = 0;
@@ -186,7 +193,8 @@ __device__ __forceinline__ void deq_stage_cols(const UmmaArgs& a, const uint8_t*
 template <int NCOLS>
 __device__ __forceinline__ void deq_store_cols(const UmmaArgs& a, uint32_t tmem_addr, uint8_t* out, int64_t row, bool row_ok,
                                                int64_t col0, const float* s_scale, const uint32_t* s_bias, float sav, bool has_sa,
-                                               bool has_fbias, bool has_ibias)
+                                               bool has_fbias, bool has_ibias, const uint32_t* ks_row = nullptr, int ks_n = 0,
+                                               int64_t ks_stride = 0)
 {
                     const int flags = a.deq_flags & ~OPSNN_DEQ_TRUNC_SCALE_B;  // already applied while staging
                     const bool simple = flags == 0 && a.out_dtype != ACL_INT32;
@@ -194,8 +202,29 @@ __device__ __forceinline__ void deq_store_cols(const UmmaArgs& a, uint32_t tmem_
     #pragma unroll 1
                     for (int c = 0; c < NCOLS; c += 32) {
                         uint32_t v[32];
-                        ptx::tmem_ld32(tmem_addr + c, v);
-                        ptx::tmem_ld_wait();
+                        if (ks_row == nullptr) {
+                            ptx::tmem_ld32(tmem_addr + c, v);
+                            ptx::tmem_ld_wait();
+                        } else {
+                            // split-k: the accumulator is the sum of the splits' partial tiles, in split order (deterministic)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0u;
+                            for (int sp = 0; sp < ks_n; ++sp) {
+                                const uint4* src = reinterpret_cast<const uint4*>(ks_row + sp * ks_stride + c);
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) {
+                                    const uint4 t = __ldcg(src + q);
+                                    if (a.is_int) {
+                                        v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+                                    } else {
+                                        v[4 * q] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * q]), __uint_as_float(t.x)));
+                                        v[4 * q + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * q + 1]), __uint_as_float(t.y)));
+                                        v[4 * q + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * q + 2]), __uint_as_float(t.z)));
+                                        v[4 * q + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[4 * q + 3]), __uint_as_float(t.w)));
+                                    }
+                                }
+                            }
+                        }
                         const int64_t col = col0 + c;
                         const int valid = (int)max((int64_t)0, min((int64_t)32, a.n - col));
                         if (row_ok && valid > 0) {
@@ -293,6 +322,8 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     const uint32_t tiles_per_batch = (uint32_t)a.tiles_m * (uint32_t)a.tiles_n;
     const uint32_t ntiles = (uint32_t)a.num_tiles;
+    const uint32_t ks = kPerBlock ? 1u : (uint32_t)a.ksplit;  // split-k factor; work item = tile * ks + split
+    const uint32_t nwork = ntiles * ks;
 
     if (warp == EW) {
         // ======================= TMA producer =======================
@@ -309,12 +340,14 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int kblocks = a.kblocks;
         const bool a_mn = a.a_mn_major != 0, b_mn = a.b_mn_major != 0;
         const uint32_t smem0 = ptx::smem_u32(smem), full0 = ptx::smem_u32(full), empty0 = ptx::smem_u32(empty);
-        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
+            const uint32_t tile = work / ks, split = work - tile * ks;
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
             const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
-            int32_t kk = 0;
-            for (int kb = 0; kb < kblocks; ++kb) {
+            const int kb_begin = (int)((int64_t)split * kblocks / (int)ks), kb_end = (int)((int64_t)(split + 1) * kblocks / (int)ks);
+            int32_t kk = kb_begin * BK;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
                 if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
                     report(abort_flag, (1u << 8) | 1u);
                     ok = false;
@@ -353,7 +386,9 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 256u : 2u;
         const uint32_t stages = (uint32_t)a.stages, idesc = a.idesc;
         const int kblocks = a.kblocks;
-        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
+            const uint32_t split = work % ks;
+            const int kb_begin = (int)((int64_t)split * kblocks / (int)ks), kb_end = (int)((int64_t)(split + 1) * kblocks / (int)ks);
             uint32_t acc = 0u;
             if (!kPerBlock) {
                 if (!ptx::mbar_wait_a(tempty0 + 8u * (grp & 1u), ((grp >> 1) & 1u) ^ 1u, abort_flag)) {
@@ -362,7 +397,7 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     break;
                 }
             }
-            for (int kb = 0; kb < kblocks; ++kb) {
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
                 if (kPerBlock) {
                     if (!ptx::mbar_wait_a(tempty0 + 8u * (grp & 1u), ((grp >> 1) & 1u) ^ 1u, abort_flag)) {
                         report(abort_flag, (2u << 8) | 1u);
@@ -407,7 +442,8 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         uint32_t grp = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
+            const uint32_t tile = work / ks, split = work - tile * ks;
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
             const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
             const int64_t row = m0 + quad * 32 + lane;
@@ -435,8 +471,44 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     break;
                 }
                 ptx::tc_fence_after();
-                deq_store_cols<kCols>(a, tmem_base + lane_addr + buf * BN, out, row, row_ok, colbase, s_scale, s_bias, sav, has_sa, has_fbias,
-                                      has_ibias);
+                if (ks == 1u) {
+                    deq_store_cols<kCols>(a, tmem_base + lane_addr + buf * BN, out, row, row_ok, colbase, s_scale, s_bias, sav, has_sa,
+                                          has_fbias, has_ibias);
+                } else {
+                    // split-k: park this split's raw accumulator rows in the workspace; whoever completes the tile's count reduces
+                    uint32_t* my_row = a.ks_part + (((int64_t)tile * ks + split) * BM + (quad * 32 + lane)) * BN;
+#pragma unroll 1
+                    for (int c = 0; c < kCols; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(tmem_base + lane_addr + buf * BN + c, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            __stcg(reinterpret_cast<uint4*>(my_row + c) + q, make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                    }
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps' rows are written and fenced
+                    if (threadIdx.x == 0) {
+                        unsigned long long* cnt = a.ks_count + tile;
+                        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(cnt), want = 0ull;
+                        bool done = false;
+                        for (int it = 0; it < 64 && !done; ++it) {  // at most ks - 1 other splits can get in between
+                            want = ((cur >> 8) == a.ks_nonce) ? cur + 1ull : ((a.ks_nonce << 8) | 1ull);
+                            const unsigned long long prev = atomicCAS(cnt, cur, want);
+                            done = prev == cur;
+                            cur = prev;
+                        }
+                        if (!done) report(abort_flag, (3u << 8) | 3u);
+                        tmem_ptr[2] = (done && (uint32_t)(want & 0xFFull) == ks) ? 1u : 0u;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (tmem_ptr[2] != 0u) {
+                        __threadfence();
+                        const uint32_t* tile_row = a.ks_part + ((int64_t)tile * ks * BM + (quad * 32 + lane)) * BN;
+                        deq_store_cols<kCols>(a, 0u, out, row, row_ok, colbase, s_scale, s_bias, sav, has_sa, has_fbias, has_ibias, tile_row,
+                                              (int)ks, (int64_t)BM * BN);
+                    }
+                }
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tempty[buf]);
@@ -617,6 +689,38 @@ int pick_bn(const OpsnnQmmParams* p)
     return lo;
 }
 
+// Split-k for problems with few output tiles (a decode-sized m against a square weight). Opt-in (OPSNN_QMM_KSPLIT=2..8):
+// on m128 k4096 n4096 the partial tiles' round trip through L2 and the reduction cost more than the shorter main loop
+// saves (44 us against 17 us), so the host never picks it by itself; 1 = off.
+int pick_ksplit(const OpsnnQmmParams* p, int bn, int kblocks)
+{
+    (void)bn;
+    if (p->mode != OPSNN_QMM_DEQ) return 1;
+    if (const char* e = getenv("OPSNN_QMM_KSPLIT")) {
+        const int v = atoi(e);
+        return (v >= 1 && v <= 8 && v * 2 <= kblocks) ? v : 1;
+    }
+    return 1;
+}
+
+uint64_t ksplit_workspace(const OpsnnQmmParams* p)
+{
+    if (p->mode != OPSNN_QMM_DEQ) return 0;
+    const bool f16 = p->a_dtype == ACL_BF16 || p->a_dtype == ACL_FLOAT16;
+    const int kblocks = (int)((p->k * (f16 ? 2 : 1) + BK - 1) / BK);
+    const int bn = pick_bn(p);
+    const int ks = pick_ksplit(p, bn, kblocks);
+    if (ks == 1) return 0;
+    const uint64_t tiles = (uint64_t)(p->batch * ((p->m + BM - 1) / BM) * ((p->n + bn - 1) / bn));
+    return tiles * (uint64_t)ks * BM * (uint64_t)bn * 4u + tiles * 8u + 512u;
+}
+
+unsigned long long next_ks_nonce()
+{
+    static std::atomic<unsigned long long> seq{0x5EED0000ull};
+    return seq.fetch_add(1, std::memory_order_relaxed) + 1;
+}
+
 template <int BN, bool PB, ptx::MmaKind KIND, int EW = 4>
 int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
 {
@@ -633,9 +737,10 @@ int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cu
             return (int32_t)cudaGetLastError();
         configured = true;
     }
-    int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
+    const int64_t work = a.num_tiles * (PB ? 1 : a.ksplit);
+    int64_t grid = work < sm_count() ? work : sm_count();
     kern<<<(unsigned)grid, (EW + 2) * 32, smem, stream>>>(ma, mb, a);
-    note_launch(PB ? "qmm_umma_perblock" : "qmm_umma_deq");
+    note_launch(PB ? "qmm_umma_perblock" : (a.ksplit > 1 ? "qmm_umma_deq_splitk" : "qmm_umma_deq"));
     return (int32_t)cudaGetLastError();
 }
 
@@ -706,7 +811,8 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
 
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p)
 {
-    return p->mode == OPSNN_QMM_MX ? qmm_mx_umma_workspace_size(p) : pair_pb_workspace(p);
+    if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_workspace_size(p);
+    return p->mode == OPSNN_QMM_PERBLOCK ? pair_pb_workspace(p) : ksplit_workspace(p);
 }
 
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
@@ -754,6 +860,18 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     const uint64_t es = f16 ? 2 : 1;  // bytes per operand element: extents and pitches below are in bytes
     a.kblocks = (int32_t)((p->k * (int64_t)es + BK - 1) / BK);
     a.num_tiles = p->batch * a.tiles_m * a.tiles_n;
+    a.ksplit = 1;
+    if (!pair && !pair_pb && p->mode == OPSNN_QMM_DEQ) {
+        const int ks = pick_ksplit(p, bn, a.kblocks);
+        const uint64_t need = ksplit_workspace(p);
+        if (ks > 1 && p->workspace != nullptr && p->workspace_size >= need && a.num_tiles * ks < 0x7FFFFFFF) {
+            uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+            a.ksplit = ks;
+            a.ks_count = reinterpret_cast<unsigned long long*>(ws);
+            a.ks_part = reinterpret_cast<uint32_t*>(ws + (((uint64_t)a.num_tiles * 8u + 255u) & ~(uint64_t)255u));
+            a.ks_nonce = next_ks_nonce();
+        }
+    }
     a.a_batched = p->a_bs != 0;
     a.b_batched = b_bs != 0;
     a.out_dtype = p->out_dtype; a.bias_dtype = p->bias_dtype; a.scale_b_dtype = p->scale_b_dtype; a.deq_flags = p->deq_flags;

@@ -272,3 +272,46 @@ def test_perblock_cta_pairs(aclnn, case, monkeypatch):
     else:
         ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, t1, t2, group, "float32")
         check_close(got, want, ref32, out_name)
+
+
+KSPLIT_CASES = [
+    # m, k, n, t1, t2, ksplit, per-token, bias, out
+    (128, 4096, 512, False, False, 4, True, "i32", "bfloat16"),
+    (100, 1040, 208, False, True, 2, True, "f32", "float16"),      # k tail: the last split is shorter
+    (130, 2048, 300, False, True, 3, False, None, "bfloat16"),     # two m tiles, uneven splits
+    (64, 4096, 1024, False, False, 8, False, "i32", "int32"),      # raw int32 accumulator out
+    (128, 2048, 256, True, False, 5, True, None, "bfloat16"),      # x1 stored (k,m)
+]
+
+
+@pytest.mark.parametrize("case", KSPLIT_CASES, ids=[str(c) for c in KSPLIT_CASES])
+def test_int8_split_k_bit_exact(aclnn, case, monkeypatch):
+    """Few output tiles: the k range is split over several CTAs, partial int32 tiles meet in the workspace and the CTA that
+    completes the tile's arrival count sums them and runs the epilogue. Integer partial sums: still bit-identical."""
+    m, k, n, t1, t2, ks, per_token, bias_kind, out_name = case
+    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32) if per_token else None
+    bias = {None: None, "i32": rng.integers(-1000, 1001, n).astype(np.int32), "f32": rng.standard_normal(n).astype(np.float32)}[bias_kind]
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, 0, out_name)
+    monkeypatch.setenv("OPSNN_QMM_KSPLIT", str(ks))
+    for _ in range(2):  # the second call finds the first call's counters in the workspace: the nonce tells them apart
+        got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, 0, out_name, "qmm_umma_deq_splitk")
+        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(want).view(np.uint8))
+
+
+def test_fp8_split_k(aclnn, monkeypatch):
+    from gpu_util import check_close
+
+    rng = np.random.default_rng(77)
+    m, k, n = 96, 3072, 384
+    x1, x2 = _fp8(rng, (m, k), E4M3), _fp8(rng, (n, k), E5M2)
+    s1 = rng.uniform(0.5, 2, m).astype(np.float32)
+    s2 = rng.uniform(0.5, 2, n).astype(np.float32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, False, True, 0, "bfloat16")
+    ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, False, True, 0, "float32")
+    monkeypatch.setenv("OPSNN_QMM_KSPLIT", "4")
+    got = _run(aclnn, x1, x2, s1, s2, None, False, True, 0, "bfloat16", "qmm_umma_deq_splitk")
+    check_close(got, want, ref32, "bfloat16")
