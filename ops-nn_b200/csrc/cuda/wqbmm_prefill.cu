@@ -14,6 +14,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "wqbmm_decode_common.cuh"
 
 namespace opsnn {
 
@@ -150,6 +151,86 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_words_kernel(const OpsnnWqbm
     }
 }
 
+// The streaming form of the same layout: a thread owns one word column (8 n) over 8 consecutive k rows and does the
+// arithmetic on packed pairs exactly as the decode kernels do (nibble -> 136 + w by one lop3, then sub / add / mul .rn on
+// bf16x2 or f16x2: the reference's two roundings). A lop3 pairs columns j and j + 4 of one row; two rows' results are
+// re-paired into (k, k + 1) words of one column with byte permutes and stored into a 64 x 256 tile whose word index is
+// XOR-swizzled by the word column (bank = column + index, 129-word rows: conflict-free writes and reads).
+// Needs group_size % 8 == 0 (a thread's 8 rows share their scales).
+constexpr int PK = 256, PN = 64, PP = PK / 2 + 1;
+
+template <bool kBf16>
+__global__ void __launch_bounds__(NT) wq_dequant_nk_pairs_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
+                                                                 float* __restrict__ one, int vec_scale)
+{
+    using N = Num<kBf16>;
+    extern __shared__ uint32_t ptile[];  // [PN][PP]
+    const int tid = threadIdx.x;
+    const int64_t tiles_n = (p.n + PN - 1) / PN;
+    const int64_t k0 = ((int64_t)blockIdx.x / tiles_n) * PK, n0 = ((int64_t)blockIdx.x % tiles_n) * PN;
+    if (blockIdx.x == 0 && tid == 0) *one = 1.0f;
+    const int wj = tid & 7, kr = tid >> 3;
+    const int64_t gn = n0 + wj * 8, gk = k0 + 8 * kr;
+    const bool col_live = gn < p.n;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        w[i] = (col_live && gk + i < p.k) ? __ldcs(reinterpret_cast<const uint32_t*>(p.w) + ((gk + i) * p.w_ld + gn) / 8) : 0u;
+    // scale / offset of columns (j, j + 4), j = 0..3, as packed pairs
+    uint32_t sp[4], op[4];
+    const bool has_off = p.offset != nullptr;
+    {
+        const int64_t g = p.group_size > 0 ? min(gk, p.k - 1) / p.group_size : 0;
+        const int64_t sidx = g * p.scale_sg + (col_live ? gn : 0) * p.scale_sn;
+        if (vec_scale) {
+            const uint4 sv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.scale) + sidx));
+            sp[0] = __byte_perm(sv.x, sv.z, 0x5410); sp[1] = __byte_perm(sv.x, sv.z, 0x7632);
+            sp[2] = __byte_perm(sv.y, sv.w, 0x5410); sp[3] = __byte_perm(sv.y, sv.w, 0x7632);
+            if (has_off) {
+                const uint4 ov = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.offset) + sidx));
+                op[0] = __byte_perm(ov.x, ov.z, 0x5410); op[1] = __byte_perm(ov.x, ov.z, 0x7632);
+                op[2] = __byte_perm(ov.y, ov.w, 0x5410); op[3] = __byte_perm(ov.y, ov.w, 0x7632);
+            }
+        } else {
+            const uint16_t* sc = reinterpret_cast<const uint16_t*>(p.scale);
+            const uint16_t* of = reinterpret_cast<const uint16_t*>(p.offset);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                sp[j] = (uint32_t)__ldg(sc + sidx + j * p.scale_sn) | ((uint32_t)__ldg(sc + sidx + (j + 4) * p.scale_sn) << 16);
+                if (has_off) op[j] = (uint32_t)__ldg(of + sidx + j * p.scale_sn) | ((uint32_t)__ldg(of + sidx + (j + 4) * p.scale_sn) << 16);
+            }
+        }
+    }
+    const int swz = (wj & 3) | ((wj >> 2) << 4);
+#pragma unroll
+    for (int rp = 0; rp < 4; ++rp) {
+        const int col = (4 * kr + rp) ^ swz;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t t0, t1;
+            asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(t0) : "r"(w[2 * rp] >> (4 * j)), "n"(0x000F000F), "r"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(t1) : "r"(w[2 * rp + 1] >> (4 * j)), "n"(0x000F000F), "r"(N::kMagic));
+            t0 = N::sub(t0, N::kBias);
+            t1 = N::sub(t1, N::kBias);
+            if (has_off) {
+                t0 = N::add(t0, op[j]);
+                t1 = N::add(t1, op[j]);
+            }
+            t0 = N::mul(t0, sp[j]);
+            t1 = N::mul(t1, sp[j]);
+            ptile[(wj * 8 + j) * PP + col] = __byte_perm(t0, t1, 0x5410);      // column j: rows (2rp, 2rp + 1)
+            ptile[(wj * 8 + j + 4) * PP + col] = __byte_perm(t0, t1, 0x7632);  // column j + 4
+        }
+    }
+    __syncthreads();
+    uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+    for (int e = tid; e < PN * (PK / 2); e += NT) {
+        const int nn = e >> 7, c = e & 127;
+        const int64_t on = n0 + nn, ok = k0 + 2 * c;
+        if (on < p.n && ok < kp) out[(on * kp + ok) >> 1] = ptile[nn * PP + (c ^ (((nn >> 3) & 3) | (((nn >> 5) & 1) << 4)))];
+    }
+}
+
 int64_t padded_k(const OpsnnWqbmmParams* p) { return (p->k + 7) / 8 * 8; }
 
 // The matmul the pre-pass leaves behind, as parameters of the quantised-matmul launcher.
@@ -204,7 +285,24 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     const bool fast = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
                       (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && tile_const_scale;
     const bool bf = p->x_dtype == ACL_BF16;
-    if (bf && fast) wq_dequant_nk_words_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+    const bool pairs = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
+                       (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && (p->group_size == 0 || p->group_size % 8 == 0) &&
+                       getenv("OPSNN_WQ_PREFILL_SIMPLE") == nullptr;
+    if (pairs) {
+        const int64_t ptiles = ((p->n + PN - 1) / PN) * ((p->k + PK - 1) / PK);
+        if (ptiles > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+        const int vec = p->scale_sn == 1 && p->scale_sg % 8 == 0 && (reinterpret_cast<uintptr_t>(p->scale) & 15) == 0 &&
+                        (p->offset == nullptr || (reinterpret_cast<uintptr_t>(p->offset) & 15) == 0);
+        const size_t sm = (size_t)PN * PP * 4;
+        static bool configured = false;
+        if (!configured) {
+            cudaFuncSetAttribute(wq_dequant_nk_pairs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            cudaFuncSetAttribute(wq_dequant_nk_pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            configured = true;
+        }
+        if (bf) wq_dequant_nk_pairs_kernel<true><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
+        else wq_dequant_nk_pairs_kernel<false><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
+    } else if (bf && fast) wq_dequant_nk_words_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else if (bf) wq_dequant_nk_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else if (fast) wq_dequant_nk_words_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else wq_dequant_nk_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
