@@ -78,9 +78,12 @@ typedef struct OpsnnQmmParams {
     int32_t pre_scale_dtype;
     const void* pre_scale;
     int32_t pre_group;
+    /* INT4 x INT4 (per-tensor / per-channel / per-token modes): OPSNN_PREPASS_WIDEN_INT4 in a_prepass and b_prepass
+       sign-extends the packed nibbles of that operand to INT8 in the workspace (exact), then the INT8 kernels run. */
+    int32_t a_prepass;
 } OpsnnQmmParams;
 
-enum { OPSNN_B_PREPASS_NONE = 0, OPSNN_B_PREPASS_WIDEN = 1, OPSNN_B_PREPASS_GROUP_SCALE = 2 };
+enum { OPSNN_B_PREPASS_NONE = 0, OPSNN_B_PREPASS_WIDEN = 1, OPSNN_B_PREPASS_GROUP_SCALE = 2, OPSNN_PREPASS_WIDEN_INT4 = 3 };
 
 /* Bytes of device workspace `opsnn_qmm_launch` needs for these parameters with this kernel choice. */
 OPSNN_API uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice);

@@ -26,6 +26,9 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream);
 uint64_t qmm_a8w4_prepass_bytes(const OpsnnQmmParams* p);
 void qmm_a8w4_view(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst);
 int32_t qmm_a8w4_prepass_launch(const OpsnnQmmParams* p, void* dst, cudaStream_t stream);
+uint64_t qmm_int4_prepass_bytes(const OpsnnQmmParams* p);
+void qmm_int4_view(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst);
+int32_t qmm_int4_prepass_launch(const OpsnnQmmParams* p, void* dst, cudaStream_t stream);
 
 int32_t wqbmm_generic_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p);
@@ -51,6 +54,10 @@ extern "C" {
 // workspace yet) the rewritten operand is given a stand-in address with the alignment every device allocation has.
 static const OpsnnQmmParams* after_prepass(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst)
 {
+    if (p->a_prepass == OPSNN_PREPASS_WIDEN_INT4 || p->b_prepass == OPSNN_PREPASS_WIDEN_INT4) {
+        qmm_int4_view(p, q, dst);
+        return q;
+    }
     if (p->b_prepass == OPSNN_B_PREPASS_NONE) return p;
     qmm_a8w4_view(p, q, dst);
     return q;
@@ -68,7 +75,7 @@ uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice
 {
     if (p == nullptr) return 0;
     if (kernel_choice == OPSNN_KERNEL_AUTO) kernel_choice = opsnn_qmm_select_kernel(p);
-    const uint64_t pre = qmm_a8w4_prepass_bytes(p);
+    const uint64_t pre = qmm_a8w4_prepass_bytes(p) + qmm_int4_prepass_bytes(p);
     OpsnnQmmParams q;
     p = after_prepass(p, &q, reinterpret_cast<void*>(uintptr_t(256)));
     return pre + (kernel_choice == OPSNN_KERNEL_UMMA ? qmm_umma_workspace_size(p) : 0);
@@ -79,9 +86,12 @@ int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* s
     if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
     if (p->m <= 0 || p->n <= 0 || p->batch <= 0) return 0;
     OpsnnQmmParams q;
-    if (p->b_prepass != OPSNN_B_PREPASS_NONE) {
-        if (p->workspace == nullptr || p->workspace_size < qmm_a8w4_prepass_bytes(p)) return (int32_t)cudaErrorInvalidValue;
-        const int32_t rc = qmm_a8w4_prepass_launch(p, p->workspace, static_cast<cudaStream_t>(stream));
+    if (p->a_prepass != OPSNN_B_PREPASS_NONE || p->b_prepass != OPSNN_B_PREPASS_NONE) {
+        const bool i4 = p->a_prepass == OPSNN_PREPASS_WIDEN_INT4 || p->b_prepass == OPSNN_PREPASS_WIDEN_INT4;
+        if (p->workspace == nullptr || p->workspace_size < qmm_a8w4_prepass_bytes(p) + qmm_int4_prepass_bytes(p))
+            return (int32_t)cudaErrorInvalidValue;
+        const int32_t rc = i4 ? qmm_int4_prepass_launch(p, p->workspace, static_cast<cudaStream_t>(stream))
+                              : qmm_a8w4_prepass_launch(p, p->workspace, static_cast<cudaStream_t>(stream));
         if (rc != 0) return rc;
         p = after_prepass(p, &q, p->workspace);
         if (kernel_choice == OPSNN_KERNEL_UMMA && !qmm_umma_eligible(p)) kernel_choice = OPSNN_KERNEL_GENERIC;  // odd workspace address

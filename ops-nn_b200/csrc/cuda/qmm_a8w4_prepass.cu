@@ -90,11 +90,92 @@ __global__ void __launch_bounds__(256) a8w4_group_scale_kernel(const uint8_t* __
     }
 }
 
+// INT4 -> INT8, sign extended: rows x inner nibbles (two per byte, low first), src rows src_ld nibbles apart, dst packed
+__global__ void __launch_bounds__(256) widen_int4_kernel(const uint8_t* __restrict__ src, int8_t* __restrict__ dst, int64_t rows,
+                                                         int64_t inner, int64_t src_ld)
+{
+    const int64_t per_row = inner / 2, total = rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row, c = i % per_row;
+        const int32_t byte = src[(r * src_ld) / 2 + c];
+        *reinterpret_cast<char2*>(dst + r * inner + 2 * c) = make_char2((signed char)((byte << 28) >> 28), (signed char)((byte << 24) >> 28));
+    }
+}
+
 }  // namespace
+
+// ---- INT4 x INT4: both operands widened to INT8 -------------------------------------------------------------------------
+static int64_t int4_rows(const OpsnnQmmParams* p, bool is_a) { return is_a ? (p->trans_a ? p->k : p->m) : (p->trans_b ? p->n : p->k); }
+static int64_t int4_inner(const OpsnnQmmParams* p, bool is_a) { return is_a ? (p->trans_a ? p->m : p->k) : (p->trans_b ? p->k : p->n); }
+static uint64_t int4_bytes_one(const OpsnnQmmParams* p, bool is_a)
+{
+    const int64_t nb = (is_a ? p->a_bs : p->b_bs) != 0 ? p->batch : 1;
+    return ((uint64_t)(nb * int4_rows(p, is_a) * int4_inner(p, is_a)) + 255u) & ~(uint64_t)255u;
+}
+
+uint64_t qmm_int4_prepass_bytes(const OpsnnQmmParams* p)
+{
+    uint64_t n = 0;
+    if (p->a_prepass == OPSNN_PREPASS_WIDEN_INT4) n += int4_bytes_one(p, true);
+    if (p->b_prepass == OPSNN_PREPASS_WIDEN_INT4) n += int4_bytes_one(p, false);
+    return n;
+}
+
+// Parameters of the INT8 problem the widening leaves behind (operands packed at `dst`).
+void qmm_int4_view(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst)
+{
+    *q = *p;
+    uint8_t* at = static_cast<uint8_t*>(dst);
+    uint64_t used = 0;
+    if (p->a_prepass == OPSNN_PREPASS_WIDEN_INT4) {
+        q->a = dst == nullptr ? nullptr : at;
+        q->a_dtype = ACL_INT8;
+        q->a_ld = int4_inner(p, true);
+        q->a_bs = p->a_bs != 0 ? int4_rows(p, true) * int4_inner(p, true) : 0;
+        used += int4_bytes_one(p, true);
+        q->a_prepass = OPSNN_B_PREPASS_NONE;
+    }
+    if (p->b_prepass == OPSNN_PREPASS_WIDEN_INT4) {
+        q->b = dst == nullptr ? nullptr : at + used;
+        q->b_dtype = ACL_INT8;
+        q->b_ld = int4_inner(p, false);
+        q->b_bs = p->b_bs != 0 ? int4_rows(p, false) * int4_inner(p, false) : 0;
+        used += int4_bytes_one(p, false);
+        q->b_prepass = OPSNN_B_PREPASS_NONE;
+    }
+    q->workspace = dst == nullptr ? nullptr : at + used;
+    q->workspace_size = p->workspace_size > used ? p->workspace_size - used : 0;
+}
+
+int32_t qmm_int4_prepass_launch(const OpsnnQmmParams* p, void* dst, cudaStream_t stream)
+{
+    uint8_t* at = static_cast<uint8_t*>(dst);
+    for (int side = 0; side < 2; ++side) {
+        const bool is_a = side == 0;
+        if ((is_a ? p->a_prepass : p->b_prepass) != OPSNN_PREPASS_WIDEN_INT4) continue;
+        const int64_t rows1 = int4_rows(p, is_a), inner = int4_inner(p, is_a);
+        const int64_t ld = is_a ? p->a_ld : p->b_ld, bs = is_a ? p->a_bs : p->b_bs;
+        const int64_t nb = bs != 0 ? p->batch : 1;
+        if (inner % 2 != 0 || ld % 2 != 0 || bs % 2 != 0) return (int32_t)cudaErrorInvalidValue;
+        const uint8_t* src = static_cast<const uint8_t*>(is_a ? p->a : p->b);
+        for (int64_t b = 0; b < nb; ++b) {
+            int64_t grid = (rows1 * inner / 2 + 255) / 256;
+            if (grid > 148 * 16) grid = 148 * 16;
+            if (grid < 1) grid = 1;
+            widen_int4_kernel<<<(unsigned)grid, 256, 0, stream>>>(src + (b * bs) / 2, reinterpret_cast<int8_t*>(at) + b * rows1 * inner, rows1,
+                                                                   inner, ld);
+            note_launch("widen_int4");
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return (int32_t)e;
+        }
+        at += int4_bytes_one(p, is_a);
+    }
+    return 0;
+}
 
 uint64_t qmm_a8w4_prepass_bytes(const OpsnnQmmParams* p)
 {
-    if (p->b_prepass == OPSNN_B_PREPASS_NONE) return 0;
+    if (p->b_prepass != OPSNN_B_PREPASS_WIDEN && p->b_prepass != OPSNN_B_PREPASS_GROUP_SCALE) return 0;
     const int64_t rows = p->trans_b ? p->n : p->k, inner = p->trans_b ? p->k : p->n;
     const int64_t nb = p->b_bs != 0 ? p->batch : 1;
     return ((uint64_t)(nb * rows * inner) + 255u) & ~(uint64_t)255u;

@@ -708,7 +708,14 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         p.scale_b_len = c.x2s.shape[0];
         p.scale_a_len = c.has_x1s ? c.x1s.shape[0] : 0;
         if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
-        if (c.int4_in()) why_unsupported("INT4 x INT4 kernels are not built yet");
+        if (c.int4_in()) {
+            if (c.has_x2o) {
+                why_unsupported("INT4 x INT4 per-group asymmetric (x2Offset) kernels are not built yet");
+            } else {  // sign-extend both operands to INT8 in the workspace, then the INT8 kernels (same integers, same result)
+                p.a_prepass = OPSNN_PREPASS_WIDEN_INT4;
+                p.b_prepass = OPSNN_PREPASS_WIDEN_INT4;
+            }
+        }
         if (c.out.dtype == ACL_INT8) {
             // requantised output: the offset tensor only says that the packed scale carries one (QuantBatchMatmulV3TestSpec.golden,
             // qbmmv3_kernel_golden.py:726-731)

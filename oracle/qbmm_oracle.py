@@ -16,6 +16,7 @@ E4M3 = ml_dtypes.float8_e4m3fn
 E5M2 = ml_dtypes.float8_e5m2
 E2M1 = ml_dtypes.float4_e2m1fn
 E8M0 = ml_dtypes.float8_e8m0fnu
+INT4 = ml_dtypes.int4
 
 _OUT = {"bfloat16": BF16, "float16": np.float16, "float32": np.float32, "int32": np.int32}
 
@@ -171,6 +172,8 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, t
     Mode selection = qbmmv3_kernel_golden.py:62-145 (same tree as the reference's host tiling,
     quant_batch_matmul_v3_tiling_base.cpp:458-557).
     """
+    if x1.dtype == np.dtype(INT4):  # int4 x int4: the golden widens both to int32 like int8 (qbmmv3_kernel_golden.py:612-615)
+        x1, x2 = x1.astype(np.int8), x2.astype(np.int8)
     if x1.ndim > 2 or x2.ndim > 2:
         nb = max(x1.shape[0] if x1.ndim > 2 else 1, x2.shape[0] if x2.ndim > 2 else 1)
         outs = []

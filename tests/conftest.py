@@ -59,5 +59,8 @@ def load_golden(name):
     out = {}
     for k, dt in meta["dtypes"].items():
         a = z[k]
-        out[k] = a.view(views[dt]) if dt in views else a
+        if dt == "int4" and name.startswith("qmm_"):
+            out[k] = a.astype(ml_dtypes.int4)  # stored one value per byte
+        else:
+            out[k] = a.view(views[dt]) if dt in views else a
     return out, meta

@@ -203,6 +203,15 @@ def gen_qmm(G):
     qmm_case(G, "pt_int8_fp16_big", 42, i8(rng, (384, 1024)), i8(rng, (512, 1024)), f32(rng, (384, 8), 1e-3, 1e-2),
              f32(rng, (4, 8), 1e-2, 1e-1), None, False, True, gb, "float16", "int8 G-B per-block, whole tiles",
              per_tile=True)
+    # int4 x int4 (per-token x per-channel and per-tensor with a packed scale): same integer arithmetic as int8
+    i4 = lambda rng, shape: rng.integers(-8, 8, shape).astype(np.int8).astype(INT4)
+    rng = np.random.default_rng(70)
+    qmm_case(G, "kc_int4_bf16_transB", 70, i4(rng, (77, 512)), i4(rng, (200, 512)), f32(rng, (77,)), f32(rng, (200,)),
+             rng.integers(-100, 101, 200).astype(np.int32), False, True, 0, "bfloat16",
+             "int4 x int4 per-token x per-channel, x2 stored (n,k), int32 bias")
+    rng = np.random.default_rng(71)
+    qmm_case(G, "kc_int4_fp16", 71, i4(rng, (130, 256)), i4(rng, (256, 320)), f32(rng, (130,)), f32(rng, (320,)), None, False, False,
+             0, "float16", "int4 x int4, x2 stored (k,n): packed along n")
     # int8 requantised output: uint64 scale = fp32 scale | 1 << 46 | s9 offset << 37 (matmul_quant_util.py:146-155)
     import matmul_quant_util as mqu  # on sys.path once the goldens are loaded
     rng = np.random.default_rng(60)

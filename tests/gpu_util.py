@@ -11,7 +11,7 @@ DEV = "cuda:0"
 def np_name(a):
     names = {np.dtype(ml_dtypes.bfloat16): "bfloat16", np.dtype(ml_dtypes.float8_e4m3fn): "float8_e4m3fn",
              np.dtype(ml_dtypes.float8_e5m2): "float8_e5m2", np.dtype(ml_dtypes.float4_e2m1fn): "float4_e2m1",
-             np.dtype(ml_dtypes.float8_e8m0fnu): "float8_e8m0"}
+             np.dtype(ml_dtypes.float8_e8m0fnu): "float8_e8m0", np.dtype(ml_dtypes.int4): "int4"}
     return names.get(a.dtype, a.dtype.name)
 
 
@@ -26,6 +26,10 @@ def to_dev_raw(a):
         t = torch.from_numpy(a.view(np.uint8).copy())
     elif name == "float4_e2m1":
         codes = a.view(np.uint8)
+        assert codes.shape[-1] % 2 == 0
+        t = torch.from_numpy((codes[..., 0::2] & 0xF) | ((codes[..., 1::2] & 0xF) << 4))
+    elif name == "int4":
+        codes = a.astype(np.int8).view(np.uint8)
         assert codes.shape[-1] % 2 == 0
         t = torch.from_numpy((codes[..., 0::2] & 0xF) | ((codes[..., 1::2] & 0xF) << 4))
     elif name == "uint64":

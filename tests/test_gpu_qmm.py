@@ -8,7 +8,7 @@ from oracle import qbmm_oracle
 pytestmark = pytest.mark.gpu
 
 # int8 dequant modes: the accumulator is exact and the epilogue's rounding points are fully specified -> bit-exact
-EXACT = {n for n in golden_names("qmm_") if "_int8_" in n}
+EXACT = {n for n in golden_names("qmm_") if "_int8_" in n or "_int4_" in n}
 
 
 def _ref32(a, meta):
