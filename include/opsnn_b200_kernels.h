@@ -26,7 +26,9 @@ extern "C" {
 typedef enum {
     OPSNN_QMM_DEQ = 0,      /* int8 (or fp8 with fp32 scales): out = f32(acc [+ibias]) * sB[n|0] [* sA[m|0]] [+ fbias] */
     OPSNN_QMM_PERBLOCK = 1, /* out = sum_kb part_kb * (sA[m/gm,kb] * sB[kb,n/gn]), fp32 */
-    OPSNN_QMM_MX = 2        /* e8m0 scale per 32 along k on both operands, + fp32 bias */
+    OPSNN_QMM_MX = 2,       /* e8m0 scale per 32 along k on both operands, + fp32 bias */
+    OPSNN_QMM_PERGROUP_ASYM = 3 /* INT4 x INT4 asymmetric per-group (qbmmv4_kernel_golden.py:328-395):
+                                  out = sA[m] * sum_g (part_g - rowsum_g(a)[m] * b_offset[g,n]) * sB[g,n], g = group_k rows of k */
 } OpsnnQmmMode;
 
 /* The reference's fixpipe keeps only the top 19 bits of some fp32 scales
@@ -81,6 +83,7 @@ typedef struct OpsnnQmmParams {
     /* INT4 x INT4 (per-tensor / per-channel / per-token modes): OPSNN_PREPASS_WIDEN_INT4 in a_prepass and b_prepass
        sign-extends the packed nibbles of that operand to INT8 in the workspace (exact), then the INT8 kernels run. */
     int32_t a_prepass;
+    const void* b_offset;   /* PERGROUP_ASYM: x2Offset (k/group_k, n), FLOAT16 */
 } OpsnnQmmParams;
 
 enum { OPSNN_B_PREPASS_NONE = 0, OPSNN_B_PREPASS_WIDEN = 1, OPSNN_B_PREPASS_GROUP_SCALE = 2, OPSNN_PREPASS_WIDEN_INT4 = 3 };

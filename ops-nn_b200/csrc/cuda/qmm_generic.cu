@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(NT) qmm_generic_kernel(const OpsnnQmmParams p)
 
     AccT acc[4][4];
     float tot[4][4];
+    float rs[4] = {0.f, 0.f, 0.f, 0.f};  // PERGROUP_ASYM: sums of this thread's rows of a over the current k-group
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -117,8 +118,30 @@ __global__ void __launch_bounds__(NT) qmm_generic_kernel(const OpsnnQmmParams p)
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+            if (!kInt && p.mode == OPSNN_QMM_PERGROUP_ASYM) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rs[i] += (float)av[i];
+            }
         }
         __syncthreads();
+        if (p.mode == OPSNN_QMM_PERGROUP_ASYM && (((k0 + TK) % p.group_k == 0) || k0 + TK >= p.k)) {
+            // close the k-group: tot += (part - rowsum * offset[g,n]) * scale[g,n], every step rounded like the golden
+            const int64_t g = k0 / p.group_k;
+            const __half* offp = reinterpret_cast<const __half*>(p.b_offset);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t gn = n0 + tx * 4 + j;
+                    if (gn < p.n) {
+                        const float off = __half2float(offp[g * p.n + gn]), sc = sbf[g * p.n + gn];
+                        tot[i][j] = __fadd_rn(tot[i][j], __fmul_rn(__fsub_rn((float)acc[i][j], __fmul_rn(rs[i], off)), sc));
+                    }
+                    acc[i][j] = 0;
+                }
+                rs[i] = 0.f;
+            }
+        }
         if (p.mode == OPSNN_QMM_PERBLOCK && (((k0 + TK) % 128 == 0) || k0 + TK >= p.k)) {
             // promote the finished 128-k block: tot += part * (s1 * s2), the two scales multiplied first
             int64_t kb = k0 / 128;
@@ -178,6 +201,8 @@ __global__ void __launch_bounds__(NT) qmm_generic_kernel(const OpsnnQmmParams p)
                 if (p.deq_flags & OPSNN_DEQ_REQUANT) f = requant_s9(f, sb, p.scale_b, p.scale_b_len == 1 ? 0 : gn, p.deq_flags);
                 else f = deq_epilogue(f, sb, sa, has_sa, fb, has_fbias, p.deq_flags);
                 store_out(out, oidx, f, p.out_dtype);
+            } else if (p.mode == OPSNN_QMM_PERGROUP_ASYM) {
+                store_out(out, oidx, __fmul_rn(tot[i][j], saf[gm]), p.out_dtype);
             } else {
                 float f = p.mode == OPSNN_QMM_PERBLOCK ? tot[i][j] : (float)acc[i][j];
                 if (p.bias != nullptr) f = __fadd_rn(f, load_as_float(bias, gn, p.bias_dtype));

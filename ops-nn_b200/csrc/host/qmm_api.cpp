@@ -698,6 +698,15 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         if (!ok1 || !ok2) why_unsupported("mx scale stored with a transposition different from its operand");
         if (!operand_batch(c.x1s, 3, ob, c.m * kq * 2, &p.sa_bs)) why_unsupported("x1Scale batch dims");
         if (!operand_batch(c.x2s, 3, ob, c.n * kq * 2, &p.sb_bs)) why_unsupported("x2Scale batch dims");
+    } else if (c.int4_in() && c.has_x2o) {
+        // INT4 x INT4 asymmetric per-group: operands widened to INT8 in the workspace, per-group epilogue in the coverage kernel
+        p.mode = OPSNN_QMM_PERGROUP_ASYM;
+        p.a_prepass = OPSNN_PREPASS_WIDEN_INT4;
+        p.b_prepass = OPSNN_PREPASS_WIDEN_INT4;
+        p.group_k = 256;
+        p.b_offset = data_ptr(&c.x2o);
+        if (!is_contiguous(&c.x2o)) why_unsupported("x2Offset must be contiguous");
+        if (p.batch != 1) why_unsupported("INT4 per-group asymmetric takes 2-D operands");
     } else if (c.perblock()) {
         p.mode = OPSNN_QMM_PERBLOCK;
         if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
@@ -709,9 +718,7 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         p.scale_a_len = c.has_x1s ? c.x1s.shape[0] : 0;
         if (c.hif8_in()) why_unsupported("HIFLOAT8 has no implementation here");
         if (c.int4_in()) {
-            if (c.has_x2o) {
-                why_unsupported("INT4 x INT4 per-group asymmetric (x2Offset) kernels are not built yet");
-            } else {  // sign-extend both operands to INT8 in the workspace, then the INT8 kernels (same integers, same result)
+            {  // sign-extend both operands to INT8 in the workspace, then the INT8 kernels (same integers, same result)
                 p.a_prepass = OPSNN_PREPASS_WIDEN_INT4;
                 p.b_prepass = OPSNN_PREPASS_WIDEN_INT4;
             }

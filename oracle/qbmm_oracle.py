@@ -133,6 +133,28 @@ def compute_t_cg(x1, x2, x2_scale, y_scale, transpose_x1, transpose_x2, group_k,
     return cast_out(y, out_dtype)
 
 
+def compute_int4_asym(x1, x2, x1_scale, x2_scale, x2_offset, transpose_x1, transpose_x2, out_dtype, group_k=256):
+    """INT4 x INT4 asymmetric per-group (qbmmv4_kernel_golden.py:328-395):
+    out = x1Scale[m] * sum_g (x1_g @ x2_g - rowsum(x1_g) * x2Offset[g, n]) * x2Scale[g, n], groups of 256 along k."""
+    a = x1.astype(np.int32)
+    b = x2.astype(np.int32)
+    if transpose_x1:
+        a = a.T
+    if transpose_x2:
+        b = b.T
+    m, k = a.shape
+    s2 = x2_scale.astype(np.float32)
+    of = x2_offset.astype(np.float32)
+    out = np.zeros((m, b.shape[1]), dtype=np.float32)
+    for g in range(-(-k // group_k)):
+        ag, bg = a[:, g * group_k:(g + 1) * group_k], b[g * group_k:(g + 1) * group_k]
+        mm = np.matmul(ag, bg).astype(np.float32)
+        rs = np.sum(ag.astype(np.float32), axis=-1, keepdims=True)
+        out += (mm - rs * of[g:g + 1, :]) * s2[g:g + 1, :]
+    out = out * x1_scale.astype(np.float32)[:, 0:1]
+    return cast_out(out, out_dtype)
+
+
 def compute_perblock(x1, x2, x1_scale, x2_scale, group, transpose_x1, transpose_x2, out_dtype, bias=None):
     """2-D operands. qbmmv3_kernel_golden.py:237-358"""
     gm, gn, gk = group
@@ -172,6 +194,8 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, bias=None, transpose_x1=False, t
     Mode selection = qbmmv3_kernel_golden.py:62-145 (same tree as the reference's host tiling,
     quant_batch_matmul_v3_tiling_base.cpp:458-557).
     """
+    if x1.dtype == np.dtype(INT4) and x2_offset is not None:
+        return compute_int4_asym(x1, x2, x1_scale, x2_scale, x2_offset, transpose_x1, transpose_x2, out_dtype)
     if x1.dtype == np.dtype(INT4):  # int4 x int4: the golden widens both to int32 like int8 (qbmmv3_kernel_golden.py:612-615)
         x1, x2 = x1.astype(np.int8), x2.astype(np.int8)
     if x1.ndim > 2 or x2.ndim > 2:

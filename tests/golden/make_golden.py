@@ -212,6 +212,19 @@ def gen_qmm(G):
     rng = np.random.default_rng(71)
     qmm_case(G, "kc_int4_fp16", 71, i4(rng, (130, 256)), i4(rng, (256, 320)), f32(rng, (130,)), f32(rng, (320,)), None, False, False,
              0, "float16", "int4 x int4, x2 stored (k,n): packed along n")
+    # int4 x int4 asymmetric per-group (the V4 golden's INT4_ASYMMETRICAL mode): k % 1024 == 0, n % 256 == 0, x2 stored (n,k)
+    rng = np.random.default_rng(72)
+    m, k, n = 50, 1024, 256
+    x1, x2 = i4(rng, (m, k)), i4(rng, (n, k))
+    x1s = f32(rng, (m, 1))
+    x2s = f32(rng, (k // 256, n), 1e-2, 1e-1)
+    x2o = rng.uniform(-4, 4, (k // 256, n)).astype(np.float16)
+    y = G["qbmmv4"].compute_int4_asymmetrical(x1, x2, x1s, x2s, x2o, False, True, "bfloat16")
+    yo = qbmm_oracle.quant_matmul_v5(x1, x2, x1s, x2s, None, False, True, 256, "bfloat16", x2_offset=x2o)
+    assert bits_equal(y, yo), "oracle != reference for kg_int4_asym"
+    save("qmm_kg_int4_asym_bf16", dict(x1=x1, x2=x2, x1_scale=x1s, x2_scale=x2s, x2_offset=x2o, out=y),
+         dict(op="quant_matmul_v5", transpose_x1=False, transpose_x2=True, group_size=256, out_dtype="bfloat16", seed=72,
+              note="INT4 x INT4 per-group asymmetric: x1Scale (m,1), x2Scale / x2Offset (k/256, n)"))
     # int8 requantised output: uint64 scale = fp32 scale | 1 << 46 | s9 offset << 37 (matmul_quant_util.py:146-155)
     import matmul_quant_util as mqu  # on sys.path once the goldens are loaded
     rng = np.random.default_rng(60)
