@@ -166,6 +166,17 @@ typedef struct OpsnnMxQuantParams {
 
 OPSNN_API int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream);
 
+/* ---- 4-bit weight packing (aclnnConvertWeightToINT4Pack path) --------------------------------------------------- */
+
+typedef struct OpsnnPackB4Params {
+    int32_t src_dtype;  /* ACL_INT32: one 4-bit integer per word (low nibble used) | ACL_FLOAT: one e2m1 value per float */
+    int64_t count;      /* elements; even */
+    const void* src;    /* contiguous */
+    void* dst;          /* count / 2 bytes: element 2i in the low nibble of byte i, element 2i+1 in the high nibble */
+} OpsnnPackB4Params;
+
+OPSNN_API int32_t opsnn_pack_b4_launch(const OpsnnPackB4Params* p, void* stream);
+
 /* ---- misc ---------------------------------------------------------------------------------------------------- */
 
 /* Number of kernel launches issued through this library since load (all streams, all threads). */

@@ -4,6 +4,7 @@ Mirrors the reference's operator interface (names, argument order and meaning, s
   aclnnQuantMatmulV5[GetWorkspaceSize]            matmul/quant_batch_matmul_v4/op_host/op_api/aclnn_quant_matmul_v5.h:43-60
   aclnnWeightQuantBatchMatmulV2/V3[GetWorkspaceSize]  matmul/weight_quant_batch_matmul_v2/op_host/op_api/*.h
   aclnnDynamicMxQuant[GetWorkspaceSize]           quant/dynamic_mx_quant/docs/aclnnDynamicMxQuant.md:76-95
+  aclnnConvertWeightToINT4Pack[GetWorkspaceSize]  matmul/convert_weight_to_int4_pack/op_host/op_api/aclnn_convert_weight_to_int4_pack.h:30-45
 
 There is no CPU or PyTorch fallback: if the shared library is missing, loading fails; if no CUDA device is present,
 phase 2 fails with ACLNN_ERR_RUNTIME_ERROR.
@@ -74,10 +75,11 @@ def lib():
                                                                  POINTER(c_void_p)]
     L.aclnnDynamicMxQuantGetWorkspaceSize.argtypes = [T, c_int64, c_char_p, c_int64, c_int64, c_int64, T, T,
                                                        POINTER(c_uint64), POINTER(c_void_p)]
+    L.aclnnConvertWeightToINT4PackGetWorkspaceSize.argtypes = [T, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV4GetWorkspaceSize.argtypes = [T, T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
     for name in ("aclnnQuantMatmulV5", "aclnnQuantMatmulV4", "aclnnQuantMatmulV3", "aclnnWeightQuantBatchMatmulV2",
-                 "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant"):
+                 "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant", "aclnnConvertWeightToINT4Pack"):
         getattr(L, name).argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
         getattr(L, name).restype = c_int32
         getattr(L, name + "GetWorkspaceSize").restype = c_int32
@@ -273,6 +275,23 @@ def weight_quant_batch_matmul(x, weight, antiquant_scale, y, antiquant_offset=No
     if st != ACLNN_SUCCESS:
         raise AclnnError(api, st)
     return ws_size
+
+
+def convert_weight_to_int4_pack_get_workspace_size(weight, weight_int4_pack):
+    ws, ex = c_uint64(0), c_void_p(0)
+    st = lib().aclnnConvertWeightToINT4PackGetWorkspaceSize(_h(weight), _h(weight_int4_pack), byref(ws), byref(ex))
+    return st, ws.value, ex
+
+
+def convert_weight_to_int4_pack(weight, weight_int4_pack):
+    """Runs aclnnConvertWeightToINT4Pack on the current torch CUDA stream: one 4-bit value per 32-bit element of `weight`
+    -> two per byte in `weight_int4_pack`."""
+    st, _, ex = convert_weight_to_int4_pack_get_workspace_size(weight, weight_int4_pack)
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnConvertWeightToINT4PackGetWorkspaceSize", st)
+    st = lib().aclnnConvertWeightToINT4Pack(c_void_p(0), c_uint64(0), ex, _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("aclnnConvertWeightToINT4Pack", st)
 
 
 def dynamic_mx_quant(x, y_out, mxscale_out, dst_type, axis=-1, round_mode=b"rint", blocksize=32, scale_alg=0):

@@ -43,6 +43,7 @@ uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
+int32_t pack_b4_launch(const OpsnnPackB4Params* p, cudaStream_t stream);
 
 }  // namespace opsnn
 
@@ -150,6 +151,12 @@ int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream)
 {
     if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
     return mx_quant_launch(p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t opsnn_pack_b4_launch(const OpsnnPackB4Params* p, void* stream)
+{
+    if (p == nullptr || p->src == nullptr || p->dst == nullptr) return (int32_t)cudaErrorInvalidValue;
+    return pack_b4_launch(p, static_cast<cudaStream_t>(stream));
 }
 
 uint64_t opsnn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

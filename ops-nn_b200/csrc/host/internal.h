@@ -31,7 +31,7 @@ struct aclTensor {
     bool empty() const { return numel() == 0; }
 };
 
-enum class ExecKind : int { kNone = 0, kQmm = 1, kWqbmm = 2, kMxQuant = 3 };
+enum class ExecKind : int { kNone = 0, kQmm = 1, kWqbmm = 2, kMxQuant = 3, kPackB4 = 4 };
 
 // Plan produced by phase 1 and consumed by phase 2.
 struct aclOpExecutor {
@@ -45,6 +45,7 @@ struct aclOpExecutor {
     OpsnnQmmParams qmm{};
     OpsnnWqbmmParams wq{};
     OpsnnMxQuantParams mxq{};
+    OpsnnPackB4Params pack{};
 };
 
 namespace opsnn {

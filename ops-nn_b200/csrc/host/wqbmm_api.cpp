@@ -8,6 +8,7 @@
 #include <cstring>
 #include <memory>
 
+#include "aclnnop/aclnn_convert_weight_to_int4_pack.h"
 #include "aclnnop/aclnn_dynamic_mx_quant.h"
 #include "aclnnop/aclnn_weight_quant_batch_matmul_v2.h"
 #include "aclnnop/aclnn_weight_quant_batch_matmul_v3.h"
@@ -389,6 +390,72 @@ aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspaceSize, aclOpEx
     int32_t rc = opsnn_mx_quant_launch(&exec->mxq, stream);
     if (rc != 0) {
         set_err("aclnnDynamicMxQuant: kernel launch failed with CUDA error %d", rc);
+        return ACLNN_ERR_RUNTIME_ERROR;
+    }
+    return ACLNN_SUCCESS;
+}
+
+// ---- aclnnConvertWeightToINT4Pack (matmul/convert_weight_to_int4_pack/op_host/op_api/aclnn_convert_weight_to_int4_pack.cpp) ----
+
+aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor* weight, aclTensor* weightInt4Pack,
+                                                         uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    const char* api = "aclnnConvertWeightToINT4PackGetWorkspaceSize";
+    clear_err();
+    if (weight == nullptr || weightInt4Pack == nullptr || workspaceSize == nullptr || executor == nullptr) {
+        set_err("%s: a required argument is nullptr", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    // ParamsCheck (:307-316): contiguous, dtype pairs, formats, 2..3 dims, shapes
+    if (!is_contiguous(weight) || !is_contiguous(weightInt4Pack)) WQ_INVALID("%s: weight and weightInt4Pack must be contiguous", api);
+    const int wd = weight->dtype, pd = weightInt4Pack->dtype;
+    if (wd != ACL_INT32 && wd != ACL_FLOAT) WQ_INVALID("%s: weight must be INT32 or FLOAT", api);
+    const bool ok_pair = (wd == ACL_INT32 && (pd == ACL_INT32 || pd == ACL_INT4)) || (wd == ACL_FLOAT && (pd == ACL_FLOAT || pd == ACL_FLOAT4_E2M1));
+    if (!ok_pair) WQ_INVALID("%s: weightInt4Pack must be INT32/INT4 for an INT32 weight, FLOAT/FLOAT4_E2M1 for a FLOAT weight", api);
+    if (weight->format != ACL_FORMAT_ND) WQ_INVALID("%s: weight's format must be ND", api);
+    if (weightInt4Pack->format != ACL_FORMAT_ND)
+        WQ_INVALID("%s: weightInt4Pack in FRACTAL_NZ is an Ascend cube-unit layout and is not accepted here; use ND", api);
+    if (weight->rank() < 2 || weight->rank() > 3 || weightInt4Pack->rank() < 2 || weightInt4Pack->rank() > 3)
+        WQ_INVALID("%s: weight and weightInt4Pack must have 2 or 3 dims", api);
+    if (weight->empty() || weightInt4Pack->empty()) WQ_INVALID("%s: empty tensors are not accepted", api);
+    const int64_t w_first = weight->dim(-2), w_last = weight->dim(-1), p_first = weightInt4Pack->dim(-2), p_last = weightInt4Pack->dim(-1);
+    if (pd == ACL_INT4 || pd == ACL_FLOAT4_E2M1) {
+        if (w_last % 2 != 0) WQ_INVALID("%s: the last dim of weight must be even, got %ld", api, (long)w_last);
+        if (w_first != p_first || w_last != p_last) WQ_INVALID("%s: weightInt4Pack must have weight's shape", api);
+    } else {
+        if (w_last % 8 != 0) WQ_INVALID("%s: the last dim of weight must be a multiple of 8, got %ld", api, (long)w_last);
+        if (w_first != p_first || w_last / 8 != p_last) WQ_INVALID("%s: weightInt4Pack's last dim must be weight's / 8", api);
+    }
+    if (weight->rank() != weightInt4Pack->rank() || (weight->rank() == 3 && weight->shape[0] != weightInt4Pack->shape[0]))
+        WQ_INVALID("%s: weight and weightInt4Pack must agree in their leading dim", api);
+    auto exec = std::make_unique<aclOpExecutor>();
+    exec->kind = ExecKind::kPackB4;
+    exec->pack.src_dtype = wd;
+    exec->pack.count = weight->numel();
+    exec->pack.src = data_ptr(weight);
+    exec->pack.dst = const_cast<uint8_t*>(data_ptr(weightInt4Pack));
+    *workspaceSize = 0;
+    *executor = exec.release();
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnConvertWeightToINT4Pack(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    (void)workspace;
+    (void)workspaceSize;
+    clear_err();
+    if (executor == nullptr) return ACLNN_ERR_PARAM_NULLPTR;
+    std::unique_ptr<aclOpExecutor> exec(executor);
+    if (exec->magic != 0x4F50534E || exec->kind != ExecKind::kPackB4) {
+        exec.release();
+        set_err("aclnnConvertWeightToINT4Pack: executor was not created by aclnnConvertWeightToINT4PackGetWorkspaceSize");
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    exec->magic = 0;
+    if (exec->pack.src == nullptr || exec->pack.dst == nullptr) return ACLNN_ERR_PARAM_NULLPTR;
+    int32_t rc = opsnn_pack_b4_launch(&exec->pack, stream);
+    if (rc != 0) {
+        set_err("aclnnConvertWeightToINT4Pack: kernel launch failed with CUDA error %d", rc);
         return ACLNN_ERR_RUNTIME_ERROR;
     }
     return ACLNN_SUCCESS;

@@ -74,3 +74,21 @@ def fp32_dequant_product(x, w, scale, offset=None, bias=None, group_size=0):
     if bias is not None:
         out = out + bias.astype(np.float64)
     return out
+
+
+def convert_weight_to_b4_pack(weight):
+    """aclnnConvertWeightToINT4Pack, ND output (aclnn_convert_weight_to_int4_pack.cpp:43-121 of the reference): `weight` holds one
+    4-bit value per element - int32 (low nibble used) or float32 (an e2m1 value; anything else packs as code 0). Returns the
+    packed bytes, element 2i in the low nibble of byte i, shaped (..., n / 2)."""
+    w = np.ascontiguousarray(weight)
+    if w.dtype == np.float32:
+        bits = w.view(np.uint32) & np.uint32(0xFFC00000)
+        table = {0x00000000: 0, 0x3F000000: 1, 0x3F800000: 2, 0x3FC00000: 3, 0x40000000: 4, 0x40400000: 5, 0x40800000: 6,
+                 0x40C00000: 7, 0x80000000: 8, 0xBF000000: 9, 0xBF800000: 10, 0xBFC00000: 11, 0xC0000000: 12, 0xC0400000: 13,
+                 0xC0800000: 14, 0xC0C00000: 15}
+        codes = np.zeros(bits.shape, dtype=np.uint8)
+        for k, v in table.items():
+            codes[bits == np.uint32(k)] = v
+    else:
+        codes = (w.astype(np.int64) & 0xF).astype(np.uint8)
+    return (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
