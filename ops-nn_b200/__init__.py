@@ -11,3 +11,4 @@ module name `ops_nn_b200`.
 """
 from . import aclnn  # noqa: F401
 from . import shard  # noqa: F401
+from . import torch_api  # noqa: F401
