@@ -641,18 +641,18 @@ EncodeFn get_encode()
 
 // 3-D byte tensor (inner bytes, rows, batch) with a (128, box_rows, 1) box and 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t row_pitch,
-              uint64_t batch_pitch, uint32_t box_rows)
+              uint64_t batch_pitch, uint32_t box_rows, uint32_t box_inner = 128)
 {
     EncodeFn enc = get_encode();
     if (enc == nullptr) return false;
     cuuint64_t dims[3] = {inner, rows, batch};
     cuuint64_t strides[2] = {row_pitch, batch_pitch ? batch_pitch : row_pitch * rows};
     if (strides[1] % 16 != 0) strides[1] = ((strides[1] + 15) / 16) * 16;  // only reached when batch == 1
-    cuuint32_t box[3] = {128, box_rows, 1};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};  // rows of 128 bytes in the 128-byte swizzle, or of 64 bytes in the 64-byte one
     cuuint32_t estr[3] = {1, 1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+               CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int g_sms = 0;
@@ -812,40 +812,18 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_workspace_size(p);
-    return p->mode == OPSNN_QMM_PERBLOCK ? pair_pb_workspace(p) : ksplit_workspace(p);
+    return p->mode == OPSNN_QMM_PERBLOCK ? 0 : ksplit_workspace(p);
 }
 
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
     const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32 && p->out_dtype != ACL_INT8;
-    // per-block on CTA pairs: 256 x 128 tiles, B k-contiguous (an x2 stored (k,n) goes through the workspace transposed)
-    bool pair_pb = pair_pb_worthwhile(p);
+    // per-block on CTA pairs: 256 x 128 tiles
+    const bool pair_pb = pair_pb_worthwhile(p);
     const uint8_t* b_ptr = static_cast<const uint8_t*>(p->b);
     int64_t b_ld = p->b_ld, b_bs = p->b_bs;
     int b_trans = p->trans_b;
-    if (pair_pb && !p->trans_b) {
-        const uint64_t need = pair_pb_workspace(p);
-        uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
-        if (p->workspace == nullptr || p->workspace_size < need) {
-            pair_pb = false;  // no room for the transposed copy: single-CTA kernel on the operand as stored
-        } else {
-            const int64_t kp = (p->k + 15) / 16 * 16, nb = p->b_bs != 0 ? p->batch : 1;
-            const int64_t tiles = ((p->k + 63) / 64) * ((p->n + 63) / 64);
-            if (tiles > 0x7FFFFFFF || nb > 65535) return (int32_t)cudaErrorInvalidConfiguration;
-            if (p->n % 4 == 0 && p->b_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(b_ptr) & 3) == 0 && p->b_bs % 4 == 0)
-                transpose_bytes_words_kernel<<<dim3((unsigned)tiles, (unsigned)nb), 256, 0, stream>>>(b_ptr, ws, p->k, p->n, p->b_ld, kp,
-                                                                                                      p->b_bs, p->n * kp);
-            else
-                transpose_bytes_kernel<<<dim3((unsigned)tiles, (unsigned)nb), 256, 0, stream>>>(b_ptr, ws, p->k, p->n, p->b_ld, kp,
-                                                                                                p->b_bs, p->n * kp);
-            note_launch("transpose_bytes");
-            b_ptr = ws;
-            b_ld = kp;
-            b_bs = p->b_bs != 0 ? p->n * kp : 0;
-            b_trans = 1;
-        }
-    }
     const int bn = pair ? 256 : (pair_pb ? 128 : pick_bn(p));
     const int bm = (pair || pair_pb) ? 256 : BM;
     UmmaArgs a{};
@@ -892,7 +870,8 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     bool ok;
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k * es, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld * es, (uint64_t)p->a_bs * es, 128);
-    if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128);
+    if (a.b_mn_major && pair_pb) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128, 64);
+    else if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128);
     else ok = ok && make_map(&mb, b_ptr, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)b_ld * es, (uint64_t)b_bs * es,
                              pair ? 128u : (pair_pb ? 64u : (uint32_t)bn));
     if (!ok) return (int32_t)cudaErrorInvalidValue;

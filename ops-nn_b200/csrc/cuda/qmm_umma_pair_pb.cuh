@@ -6,8 +6,9 @@
 // CTA loads its own 128 rows of A and 64 of the 128 rows of B (24 KB per k-block), keeps a 128 x 128 accumulator in its own
 // TMEM and runs the same promotion on it.
 //
-// B must be k-contiguous here (64 rows of a k-major tile per CTA; half a 128-byte swizzle row of an n-major tile is not a
-// legal operand): an x2 stored (k,n) is transposed into workspace first by transpose_bytes_kernel.
+// B per CTA is half of the tile's 128 columns. k-major (x2 stored (n,k)): 64 rows of 128 swizzled bytes. n-major (x2 stored
+// (k,n)): half a 128-byte swizzle row is not a legal operand, so the 64 columns x 128 k rows are loaded and described in the
+// 64-byte swizzle (TMA box 64 x 128, descriptor layout type 4, 512 bytes per 8 rows).
 //
 // Choreography per k-block (= one accumulation group), four TMEM buffers of 128 columns:
 //   producers (both CTAs) : wait own empty[s]; even CTA arms full[s] for both CTAs' bytes; each loads A (128 rows) and B (64 rows)
@@ -16,60 +17,6 @@
 //   epilogue (both CTAs)  : wait own tfull[buf]; TMEM -> registers; acc += part * (s1 * s2); arrive on the even CTA's tempty[buf]
 // All waits bounded, teardown through a cluster barrier, as in qmm_umma_pair.cuh.
 namespace {
-
-// (rows, cols) bytes -> (cols, rows); 64 x 64 tiles through shared memory. src row pitch src_ld, dst rows packed to dst_ld.
-__global__ void __launch_bounds__(256) transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
-                                                              int64_t cols, int64_t src_ld, int64_t dst_ld, int64_t src_bs, int64_t dst_bs)
-{
-    __shared__ uint8_t t[64][65];
-    const int64_t tiles_c = (cols + 63) / 64;
-    const int64_t r0 = ((int64_t)blockIdx.x / tiles_c) * 64, c0 = ((int64_t)blockIdx.x % tiles_c) * 64;
-    src += (int64_t)blockIdx.y * src_bs;
-    dst += (int64_t)blockIdx.y * dst_bs;
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-        const int r = e >> 6, c = e & 63;
-        t[r][c] = (r0 + r < rows && c0 + c < cols) ? src[(r0 + r) * src_ld + c0 + c] : (uint8_t)0;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-        const int c = e >> 6, r = e & 63;
-        if (c0 + c < cols && r0 + r < rows) dst[(c0 + c) * dst_ld + r0 + r] = t[r][c];
-    }
-}
-
-// The same for word-aligned operands (cols % 4 == 0, src_ld % 4 == 0, dst_ld % 4 == 0, 4-byte aligned bases): a thread
-// moves a 4 x 4 byte block - four 32-bit loads, a register transpose with byte permutes, four 32-bit stores into a
-// shared-memory tile that is then written out in rows of 64 bytes.
-__global__ void __launch_bounds__(256) transpose_bytes_words_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
-                                                                    int64_t cols, int64_t src_ld, int64_t dst_ld, int64_t src_bs,
-                                                                    int64_t dst_bs)
-{
-    __shared__ uint32_t t[64][17];  // [dst row (src column)][4-byte group of src rows]
-    const int64_t tiles_c = (cols + 63) / 64;
-    const int64_t r0 = ((int64_t)blockIdx.x / tiles_c) * 64, c0 = ((int64_t)blockIdx.x % tiles_c) * 64;
-    src += (int64_t)blockIdx.y * src_bs;
-    dst += (int64_t)blockIdx.y * dst_bs;
-    const int cq = threadIdx.x & 15, rq = threadIdx.x >> 4;  // 4-column group, 4-row group
-    uint32_t r[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int64_t rr = r0 + 4 * rq + i, cc = c0 + 4 * cq;
-        r[i] = (rr < rows && cc < cols) ? __ldcs(reinterpret_cast<const uint32_t*>(src + rr * src_ld + cc)) : 0u;
-    }
-    const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
-    const uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
-    t[4 * cq + 0][rq] = __byte_perm(t0, t1, 0x5410);
-    t[4 * cq + 1][rq] = __byte_perm(t0, t1, 0x7632);
-    t[4 * cq + 2][rq] = __byte_perm(t2, t3, 0x5410);
-    t[4 * cq + 3][rq] = __byte_perm(t2, t3, 0x7632);
-    __syncthreads();
-#pragma unroll
-    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
-        const int c = e >> 4, g = e & 15;  // dst row, 4-byte group
-        const int64_t oc = c0 + c, orow = r0 + 4 * g;
-        if (oc < cols && orow < dst_ld) *reinterpret_cast<uint32_t*>(dst + oc * dst_ld + orow) = t[c][g];
-    }
-}
 
 template <ptx::MmaKind kKind, int EW>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((EW + 2) * 32, 1)
@@ -132,7 +79,7 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         __syncwarp();
         uint32_t s = 0, par = 0;
         bool ok = true;
-        const bool a_mn = a.a_mn_major != 0;
+        const bool a_mn = a.a_mn_major != 0, b_mn = a.b_mn_major != 0;
         const uint32_t lead_full0 = full0 & ptx::kPeerBitMask;
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
@@ -150,7 +97,8 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     const uint32_t fb = lead_full0 + 8u * s, sa = smem0 + s * kStage, sb = sa + (uint32_t)kATile;
                     if (leader) ptx::mbar_expect_tx_a(full0 + 8u * s, 2u * kStage);
                     ptx::tma_load_3d_pair(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
-                    ptx::tma_load_3d_pair(sb, &map_b, fb, kk, n0, bb);
+                    if (b_mn) ptx::tma_load_3d_pair(sb, &map_b, fb, n0, kk, bb);  // 64 columns x 128 k rows, 64-byte swizzle
+                    else ptx::tma_load_3d_pair(sb, &map_b, fb, kk, n0, bb);
                 }
                 __syncwarp();
                 kk += BK;
@@ -166,10 +114,13 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t s = 0, par = 0, buf = 0, bpar = 0;
             bool ok = true;
             const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
-            const uint64_t db0 = ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+            // B k-major: 64 rows of 128 swizzled bytes. B n-major (x2 stored (k,n)): 128 k rows of this CTA's 64 columns in the
+            // 64-byte swizzle (layout type 4): 8 rows = 512 bytes (stride byte offset), one MMA = 32 rows = 2 KB
+            const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 64 * BK, 512, 4)
+                                              : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
             const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0;
             const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull;
-            const uint32_t a_k1 = a.a_mn_major ? 256u : 2u;
+            const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 128u : 2u;
             const uint32_t idesc = a.idesc;
             for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
                 for (int kb = 0; kb < kblocks; ++kb) {
@@ -190,7 +141,7 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off;
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            ptx::umma_pair<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * 2u), idesc, k == 0 ? 0u : 1u);
+                            ptx::umma_pair<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * b_k1), idesc, k == 0 ? 0u : 1u);
                         ptx::umma_commit_pair(empty0 + 8u * s, (uint16_t)3);
                         ptx::umma_commit_pair(tfull0 + 8u * buf, (uint16_t)3);
                     }
@@ -350,13 +301,6 @@ bool pair_pb_worthwhile(const OpsnnQmmParams* p)
     if (const char* e = getenv("OPSNN_QMM_PAIR")) return atoi(e) != 0;
     const int64_t tiles = p->batch * ((p->m + 255) / 256) * ((p->n + 127) / 128);
     return p->m >= 256 && tiles >= 74;
-}
-
-uint64_t pair_pb_workspace(const OpsnnQmmParams* p)
-{
-    if (!pair_pb_worthwhile(p) || p->trans_b) return 0;
-    const uint64_t kp = ((uint64_t)p->k + 15u) & ~(uint64_t)15u;
-    return (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * kp + 256u;  // x2 rewritten (n,k)
 }
 
 }  // namespace
