@@ -379,11 +379,14 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // descriptors: only the 14-bit start-address field (low word) changes: stage base, then the k step inside the
         // stage. K-major operand: a k step is 32 bytes along the swizzled row; MN-major: 32 k-rows = 4 KB (units of 16 B)
         const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
-        const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
-                                          : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+        // n-major B narrower than a 128-byte swizzle row (BN 64 / 32): rows of BN bytes in the 64- / 32-byte swizzle
+        // (layout type 4 / 6), 8 rows = 8 * BN bytes, one MMA = 32 rows
+        const uint64_t db0 = !a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2)
+                             : BN >= 128   ? ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2)
+                                           : ptx::make_smem_desc(smem0 + kATile, BN * BK, 8 * BN, BN == 64 ? 4 : 6);
         const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0;
         const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull;
-        const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 256u : 2u;
+        const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = !a.b_mn_major ? 2u : (BN >= 128 ? 256u : 2u * BN);
         const uint32_t stages = (uint32_t)a.stages, idesc = a.idesc;
         const int kblocks = a.kblocks;
         for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
@@ -651,7 +654,8 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
     cuuint32_t box[3] = {box_inner, box_rows, 1};  // rows of 128 bytes in the 128-byte swizzle, or of 64 bytes in the 64-byte one
     cuuint32_t estr[3] = {1, 1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_INTERLEAVE_NONE,
+               box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -669,7 +673,7 @@ int sm_count()
 
 bool is_fp8(int dt) { return dt == ACL_FLOAT8_E4M3FN || dt == ACL_FLOAT8_E5M2; }
 
-// Host tile selection: the widest N tile that still yields about one tile per SM; MN-major B needs whole 128-column boxes.
+// Host tile selection: the widest N tile that still yields about one tile per SM.
 int pick_bn(const OpsnnQmmParams* p)
 {
     if (const char* e = getenv("OPSNN_QMM_BN")) {
@@ -680,7 +684,7 @@ int pick_bn(const OpsnnQmmParams* p)
     if (p->mode == OPSNN_QMM_PERBLOCK) return 128;
     const int64_t tiles_m = (p->m + BM - 1) / BM;
     const int sms = 148;
-    const int lo = (p->mode == OPSNN_QMM_PERBLOCK || !p->trans_b) ? 128 : 32;
+    const int lo = p->mode == OPSNN_QMM_PERBLOCK ? 128 : 32;
     for (int bn = 256; bn > lo; bn /= 2) {
         if (bn / 2 >= p->n) continue;  // half the width still covers n
         const int64_t tiles = p->batch * tiles_m * ((p->n + bn - 1) / bn);
@@ -871,7 +875,8 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k * es, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld * es, (uint64_t)p->a_bs * es, 128);
     if (a.b_mn_major && pair_pb) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128, 64);
-    else if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128);
+    else if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128,
+                                               bn < 128 ? (uint32_t)bn : 128u);
     else ok = ok && make_map(&mb, b_ptr, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)b_ld * es, (uint64_t)b_bs * es,
                              pair ? 128u : (pair_pb ? 64u : (uint32_t)bn));
     if (!ok) return (int32_t)cudaErrorInvalidValue;

@@ -46,6 +46,10 @@ INT8_CASES = [
     (272, 528, 400, True, True, 64, True, "i32", "bfloat16"),        # mn-major A, k-major B
     (64, 4096, 1024, False, False, None, False, "i32", "int32"),     # int32 accumulator out
     (1, 128, 16, False, True, None, True, None, "bfloat16"),
+    (300, 400, 384, False, False, 64, True, "i32", "bfloat16"),      # n-major B in the 64-byte swizzle
+    (130, 528, 208, False, False, 32, True, "f32", "float16"),       # n-major B in the 32-byte swizzle, n tail
+    (272, 528, 400, True, False, 32, False, None, "bfloat16"),       # both operands stored along m / n
+    (128, 4096, 1024, False, False, None, True, "i32", "bfloat16"),  # few tiles: the host picks a narrow tile by itself
 ]
 
 
