@@ -1,7 +1,7 @@
 """Imports the reference's own numpy goldens from a checkout of hicann/ops-nn (never copied into this repository).
 
-Only `tests/golden/make_golden.py` uses this, on a machine that has the reference tree (default /root/reference, or
-$OPSNN_REFERENCE_ROOT). The goldens import `en_dtypes`, which is not installable here; a shim module maps the two dtypes
+Only `tests/golden/make_golden.py` uses this, on a machine that has the reference tree ($OPSNN_REFERENCE_ROOT, or a
+`reference` folder next to this repository). The goldens import `en_dtypes`, which is not installable here; a shim module maps the two dtypes
 the hot path needs onto ml_dtypes (float4_e2m1 -> float4_e2m1fn, float8_e8m0 -> float8_e8m0fnu).
 
 Test infrastructure only (see oracle/__init__.py).
@@ -14,7 +14,8 @@ import types
 import ml_dtypes
 import numpy as np
 
-REF = os.environ.get("OPSNN_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("OPSNN_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 
 
 def available():

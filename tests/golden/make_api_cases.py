@@ -12,7 +12,8 @@ import csv
 import json
 import os
 
-REF = os.environ.get("OPSNN_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("OPSNN_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference"))
 SRC = os.path.join(REF, "matmul/quant_batch_matmul_v4/tests/ut/op_host/test_aclnn_quant_matmul_v5_api.csv")
 HERE = os.path.dirname(os.path.abspath(__file__))
 

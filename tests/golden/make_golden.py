@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this folder by running the REFERENCE's own numpy goldens on seeded inputs.
 
-Run where a checkout of hicann/ops-nn is available (default /root/reference, or $OPSNN_REFERENCE_ROOT):
+Run where a checkout of hicann/ops-nn is available ($OPSNN_REFERENCE_ROOT, or a `reference` folder next to this repository):
 
     python tests/golden/make_golden.py
 
