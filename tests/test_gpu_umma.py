@@ -319,3 +319,20 @@ def test_fp8_split_k(aclnn, monkeypatch):
     monkeypatch.setenv("OPSNN_QMM_KSPLIT", "4")
     got = _run(aclnn, x1, x2, s1, s2, None, False, True, 0, "bfloat16", "qmm_umma_deq_splitk")
     check_close(got, want, ref32, "bfloat16")
+
+
+def test_perblock_cta_pairs_batched(aclnn, monkeypatch):
+    """Batched per-block operands on the CTA-pair kernel: per-batch scales, x2 stored (k,n)."""
+    from gpu_util import check_close
+
+    rng = np.random.default_rng(4242)
+    b, m, k, n = 3, 272, 384, 256
+    x1, x2 = _fp8(rng, (b, m, k), E4M3), _fp8(rng, (b, k, n), E4M3)
+    s1 = rng.uniform(0.5, 2, (b, m, k // 128)).astype(np.float32)
+    s2 = rng.uniform(0.5, 2, (b, k // 128, n // 128)).astype(np.float32)
+    group = (1 << 32) | (128 << 16) | 128
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, False, False, group, "bfloat16")
+    ref32 = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, False, False, group, "float32")
+    monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    got = _run(aclnn, x1, x2, s1, s2, None, False, False, group, "bfloat16", "qmm_umma_pair_perblock")
+    check_close(got, want, ref32, "bfloat16")
