@@ -213,6 +213,8 @@ QMM_WORKLOADS = {
     "c5mmt": (32, 2048, 4096, 14336, "mxfp8_t"),    # same with the weight stored (n,k), transposeX2 = true
     "c2p": (1, 2048, 8192, 28672, "w4a16_prefill"), # the headline weight at a prefill m: dequant pre-pass + bf16 tcgen05 matmul
     "c2ps": (1, 256, 8192, 28672, "w4a16_prefill"),
+    "c2m32": (1, 32, 8192, 28672, "w4a16_prefill"),  # 16 < m <= 48: the decode kernel once per 16 rows
+    "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
 }
 
 

@@ -105,11 +105,43 @@ int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* s
     return qmm_generic_launch(p, static_cast<cudaStream_t>(stream));
 }
 
+// 16 < m <= 48 against a large weight: the streaming decode kernel once per 16 rows of x (the weight is re-read from HBM
+// for every chunk, 62 us each on the m16 k8192 n28672 shape) still beats dequantising the whole weight into workspace
+// first (0.19 ms for that weight before the matmul starts).
+static bool decode_in_chunks(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* chunk)
+{
+    if (p->m <= 16 || p->m > 48 || p->k * p->n < ((int64_t)1 << 26)) return false;
+    *chunk = *p;
+    chunk->m = 16;
+    return wqbmm_decode_eligible(chunk);
+}
+
+// One decode launch per 16 rows; `fast` = the group-wise kernel of inner_precise = 1.
+static int32_t decode_chunk_launches(const OpsnnWqbmmParams* p, cudaStream_t stream, int which)
+{
+    const size_t esz = 2;  // bf16 / fp16
+    for (int64_t r0 = 0; r0 < p->m; r0 += 16) {
+        OpsnnWqbmmParams q = *p;
+        q.m = p->m - r0 < 16 ? p->m - r0 : 16;
+        q.x = static_cast<const uint8_t*>(p->x) + (size_t)r0 * (size_t)p->x_ld * esz;
+        q.y = static_cast<uint8_t*>(p->y) + (size_t)r0 * (size_t)p->y_ld * esz;
+        int32_t rc;
+        if (which == OPSNN_WQ_KERNEL_DECODE_FAST) rc = wqbmm_decode_fast_launch(&q, stream);
+        else if (wqbmm_decode_fast_eligible(&q) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr) rc = wqbmm_decode_ring_launch(&q, stream, true);
+        else rc = wqbmm_decode_launch(&q, stream);
+        if (rc != 0) return rc;
+    }
+    return 0;
+}
+
 int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
 {
     if (p == nullptr) return OPSNN_WQ_KERNEL_GENERIC;
     if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
+    OpsnnWqbmmParams chunk;
+    if (getenv("OPSNN_WQ_NO_CHUNKS") == nullptr && decode_in_chunks(p, &chunk))
+        return (p->inner_precise == 1 && wqbmm_decode_fast_eligible(&chunk)) ? OPSNN_WQ_KERNEL_DECODE_FAST : OPSNN_WQ_KERNEL_DECODE;
     // m beyond the decode range: dequantise once, multiply on the tensor cores; tiny problems stay on the one-launch coverage kernel
     if (p->m > 16 && wqbmm_prefill_eligible(p)) return OPSNN_WQ_KERNEL_PREFILL;
     return OPSNN_WQ_KERNEL_GENERIC;
@@ -128,6 +160,12 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
     if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
     if (p->m <= 0 || p->n <= 0) return 0;
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    OpsnnWqbmmParams chunk;
+    if (p->m > 16 && (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST)) {
+        if (!decode_in_chunks(p, &chunk)) return (int32_t)cudaErrorInvalidValue;
+        if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST && !wqbmm_decode_fast_eligible(&chunk)) return (int32_t)cudaErrorInvalidValue;
+        return decode_chunk_launches(p, static_cast<cudaStream_t>(stream), kernel_choice);
+    }
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE) {
         if (!wqbmm_decode_eligible(p)) return (int32_t)cudaErrorInvalidValue;
         // same arithmetic, two data paths: shared-memory ring + ldmatrix where the layout allows it (32-column pieces, 16-byte

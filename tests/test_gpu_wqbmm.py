@@ -162,3 +162,32 @@ def test_prefill_dequant_then_tensor_core_matmul(aclnn, case):
     rms = np.sqrt(np.mean(wv ** 2))
     assert np.all(np.abs(g - wv) <= 2 * ulp * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
     assert np.mean(g != wv) < 0.1
+
+
+@pytest.mark.parametrize("m,inner_precise", [(40, 0), (33, 1)])
+def test_decode_kernel_in_chunks_of_16_rows(aclnn, m, inner_precise):
+    """16 < m <= 48 against a large weight: one launch of the streaming decode kernel per 16 rows of x."""
+    import ml_dtypes
+
+    from gpu_util import run_wq_fixture
+
+    k, n, g = 4096, 16384, 128
+    rng = np.random.default_rng(100 + m)
+    x = rng.standard_normal((m, k)).astype(ml_dtypes.bfloat16)
+    w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+    scale = rng.uniform(0.005, 0.02, (k // g, n)).astype(ml_dtypes.bfloat16)
+    offset = rng.uniform(-1, 1, (k // g, n)).astype(ml_dtypes.bfloat16)
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, scale, offset, None, g)
+    a = dict(x=x, w=w, scale=scale, offset=offset, bias=None, out=want)
+    meta = dict(transpose_weight=False, w_is_int4=True, packed_int32=True, group_size=g)
+    got = run_wq_fixture(aclnn, a, meta, kernel=0, api="v3", inner_precise=inner_precise)
+    assert aclnn.last_kernel_name() in ("wqbmm_decode", "wqbmm_decode_fast"), aclnn.last_kernel_name()
+    gv = got.astype(np.float64)
+    if inner_precise == 0:  # the reference's two roundings per weight: one output ulp from the golden
+        wv = want.astype(np.float64)
+        tol = 2.0 ** -7
+    else:  # high-performance mode: measured against the unrounded fp32 product, as the API documents it
+        wv = np.asarray(wqbmm_oracle.fp32_dequant_product(x, w, scale, offset, None, g), dtype=np.float64)
+        tol = 2.0 ** -8 * 1.05
+    rms = np.sqrt(np.mean(wv ** 2))
+    assert np.all(np.abs(gv - wv) <= tol * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
