@@ -59,6 +59,74 @@ __global__ void mx_sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* 
     }
 }
 
+// The same relayout staged through shared memory: one CTA per (batch, tile, row atom) = 128 rows, k-blocks in chunks of 256.
+// Reads follow the source's contiguous axis (row-major scales: 32-bit words along k; scales stored (k/64, rows, 2): 16-bit
+// pairs along the rows), writes are whole 512-byte atoms. The per-word kernel above reads or writes 4 bytes per 32-byte
+// sector; this one moves whole sectors both ways. Needs an even k/64 count for the word loads, else falls back to bytes.
+constexpr int kSfChunk = 256;
+__global__ void __launch_bounds__(256) mx_sf_relayout_tiled_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows,
+                                                                   int64_t kblocks, int64_t kq, int transposed_layout, int64_t tiles,
+                                                                   int64_t stages, int atoms, int64_t src_bs, int tile_rows, int row_atoms)
+{
+    __shared__ __align__(16) uint8_t sm[128][kSfChunk + 4];
+    int64_t r = blockIdx.x;
+    const int ra = (int)(r % row_atoms); r /= row_atoms;
+    const int64_t tile = r % tiles;
+    const int64_t b = r / tiles;
+    const uint8_t* s = src + b * src_bs;
+    const int64_t row0 = tile * tile_rows + ra * 128;                       // first row of this atom column
+    const int live = (int)max((int64_t)0, min((int64_t)128, min((int64_t)tile_rows - ra * 128, rows - row0)));  // rows that exist
+    const int64_t kb_total = stages * atoms * 4;                            // k-blocks the atoms cover (>= kblocks)
+    const int tid = threadIdx.x;
+    for (int64_t kc0 = 0; kc0 < kb_total; kc0 += kSfChunk) {
+        const int kc = (int)min((int64_t)kSfChunk, kb_total - kc0);         // multiple of 4
+        __syncthreads();
+        if (!transposed_layout) {
+            const bool words = ((2 * kq) & 3) == 0 && (reinterpret_cast<uintptr_t>(s) & 3) == 0;
+            for (int e = tid; e < 128 * (kc / 4); e += 256) {
+                const int rr = e / (kc / 4), c4 = e % (kc / 4);
+                const int64_t kb = kc0 + 4 * c4;
+                uint32_t w = 0x7F7F7F7Fu;  // 2^0 where no row / k-block exists (the data there is zero-filled)
+                if (rr < live) {
+                    const uint8_t* q = s + (row0 + rr) * (2 * kq) + kb;
+                    if (words && kb + 3 < kblocks) {
+                        w = __ldg(reinterpret_cast<const uint32_t*>(q));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (kb + j < kblocks) w = (w & ~(0xFFu << (8 * j))) | ((uint32_t)q[j] << (8 * j));
+                    }
+                }
+                *reinterpret_cast<uint32_t*>(&sm[rr][4 * c4]) = w;
+            }
+        } else {
+            for (int e = tid; e < 128 * (kc / 2); e += 256) {
+                const int kbp = e >> 7, rr = e & 127;   // pair of k-blocks, row: consecutive threads read consecutive rows
+                const int64_t kb = kc0 + 2 * kbp;
+                uint32_t w = 0x7F7Fu;
+                if (rr < live && kb < kblocks) {
+                    const uint8_t* q = s + ((kb >> 1) * rows + row0 + rr) * 2;
+                    w = (reinterpret_cast<uintptr_t>(q) & 1) ? ((uint32_t)q[0] | ((uint32_t)q[1] << 8)) : (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(q));
+                    if (kb + 1 >= kblocks) w = (w & 0xFFu) | 0x7F00u;
+                }
+                *reinterpret_cast<uint16_t*>(&sm[rr][2 * kbp]) = (uint16_t)w;
+            }
+        }
+        __syncthreads();
+        // atoms of this chunk: atom (st, at) holds k-blocks 4 * (st * atoms + at) .. + 3; 128 words of 4 bytes each
+        const int natoms = kc / 4;
+        for (int e = tid; e < natoms * 128; e += 256) {
+            const int ai = e >> 7, wi = e & 127;
+            const int l = wi >> 2, m1 = wi & 3, rr = m1 * 32 + l;
+            const int64_t ka = kc0 / 4 + ai;              // = st * atoms + at
+            const int64_t st = ka / atoms;
+            const int at = (int)(ka % atoms);
+            const int64_t atom_idx = (((b * tiles + tile) * stages + st) * atoms + at) * row_atoms + ra;
+            *reinterpret_cast<uint32_t*>(dst + atom_idx * 512 + wi * 4) = *reinterpret_cast<const uint32_t*>(&sm[rr][4 * ai]);
+        }
+    }
+}
+
 // fp4 operands stored along m / n (x1 given as (k,m), x2 as (k,n)) cannot be fed to the tensor core (kind::mxf4 has no MN-major
 // form); a pre-pass rewrites them k-contiguous into workspace: (R, C) packed along C -> (C, R) packed along R, two e2m1 per
 // byte, low nibble first. 64 x 64 element tiles through shared memory; ~1.5 % of the matmul's time at the benchmark shape.
@@ -454,12 +522,21 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
         const int threads = 256;
         const auto blocks = [&](int64_t w) { return (unsigned)std::min<int64_t>((w + threads - 1) / threads, 148 * 16); };
         // x1Scale is (m, kq, 2), or (kq, m, 2) when x1 is stored (k,m); x2Scale is (kq, n, 2), or (n, kq, 2) when x2 is stored (n,k)
+        const int64_t ga = (int64_t)q.nb_a * q.tiles_m, gb = (int64_t)q.nb_b * q.tiles_n * q.row_atoms;
+        if (getenv("OPSNN_MX_SF_SIMPLE") == nullptr && ga < 0x7FFFFFFF && gb < 0x7FFFFFFF) {
+            mx_sf_relayout_tiled_kernel<<<(unsigned)ga, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32,
+                                                                          q.kq, p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, p->sa_bs, BM, 1);
+            mx_sf_relayout_tiled_kernel<<<(unsigned)gb, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32,
+                                                                          q.kq, p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, p->sb_bs, q.bn,
+                                                                          q.row_atoms);
+        } else {
         mx_sf_relayout_kernel<<<blocks(wa), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32, q.kq,
                                                                   p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs,
                                                                   BM, 1);
         mx_sf_relayout_kernel<<<blocks(wb), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32, q.kq,
                                                                   p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, (int64_t)q.nb_b, p->sb_bs,
                                                                   q.bn, q.row_atoms);
+        }
         note_launch("mx_sf_relayout", 2);
     }
     // ---- pre-pass: fp4 operands that are not k-contiguous ----
