@@ -128,6 +128,10 @@ typedef struct OpsnnWqbmmParams {
     void* workspace;
     uint64_t workspace_size;
     int32_t inner_precise;  /* innerPrecise of aclnnWeightQuantBatchMatmulV3: 0 high precision (default), 1 high performance */
+    /* aclnnWeightQuantBatchMatmulNz: the (k,n) weight is stored FRACTAL_NZ, [ceil(n/nz_n0)][ceil(k/nz_k0)][nz_k0][nz_n0] elements
+       (matmul/common/tests/st/arch35/matmul_golden_util.py:76-114 of the reference). 0, 0: plain row-major storage. It is
+       rewritten row-major into the head of the workspace before the matmul runs. */
+    int32_t nz_k0, nz_n0;
 } OpsnnWqbmmParams;
 
 OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice);

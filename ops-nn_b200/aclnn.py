@@ -46,7 +46,8 @@ class WqbmmParams(ctypes.Structure):
                 ("x", c_void_p), ("x_ld", c_int64), ("w", c_void_p), ("w_ld", c_int64),
                 ("scale", c_void_p), ("offset", c_void_p), ("group_size", c_int64), ("scale_sg", c_int64),
                 ("scale_sn", c_int64), ("bias", c_void_p), ("y", c_void_p), ("y_ld", c_int64),
-                ("workspace", c_void_p), ("workspace_size", c_uint64), ("inner_precise", c_int32)]
+                ("workspace", c_void_p), ("workspace_size", c_uint64), ("inner_precise", c_int32),
+                ("nz_k0", c_int32), ("nz_n0", c_int32)]
 
 
 _lib = None
@@ -73,13 +74,16 @@ def lib():
                                                                  POINTER(c_void_p)]
     L.aclnnWeightQuantBatchMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, c_int, T, POINTER(c_uint64),
                                                                  POINTER(c_void_p)]
+    L.aclnnWeightQuantBatchMatmulNzGetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, T, POINTER(c_uint64),
+                                                                 POINTER(c_void_p)]
     L.aclnnDynamicMxQuantGetWorkspaceSize.argtypes = [T, c_int64, c_char_p, c_int64, c_int64, c_int64, T, T,
                                                        POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnConvertWeightToINT4PackGetWorkspaceSize.argtypes = [T, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV4GetWorkspaceSize.argtypes = [T, T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
     for name in ("aclnnQuantMatmulV5", "aclnnQuantMatmulV4", "aclnnQuantMatmulV3", "aclnnWeightQuantBatchMatmulV2",
-                 "aclnnWeightQuantBatchMatmulV3", "aclnnDynamicMxQuant", "aclnnConvertWeightToINT4Pack"):
+                 "aclnnWeightQuantBatchMatmulV3", "aclnnWeightQuantBatchMatmulNz", "aclnnDynamicMxQuant",
+                 "aclnnConvertWeightToINT4Pack"):
         getattr(L, name).argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
         getattr(L, name).restype = c_int32
         getattr(L, name + "GetWorkspaceSize").restype = c_int32
@@ -222,7 +226,11 @@ def weight_quant_batch_matmul_get_workspace_size(x, weight, antiquant_scale, ant
                                                  bias, antiquant_group_size, y, inner_precise=None):
     ws, ex = c_uint64(0), c_void_p(0)
     L = lib()
-    if inner_precise is None:
+    if inner_precise == "nz":
+        st = L.aclnnWeightQuantBatchMatmulNzGetWorkspaceSize(_h(x), _h(weight), _h(antiquant_scale), _h(antiquant_offset),
+                                                             _h(quant_scale), _h(quant_offset), _h(bias),
+                                                             int(antiquant_group_size), _h(y), byref(ws), byref(ex))
+    elif inner_precise is None:
         st = L.aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(_h(x), _h(weight), _h(antiquant_scale), _h(antiquant_offset),
                                                              _h(quant_scale), _h(quant_offset), _h(bias),
                                                              int(antiquant_group_size), _h(y), byref(ws), byref(ex))
@@ -261,10 +269,12 @@ def quant_matmul_v5(x1, x2, x1_scale, x2_scale, out, bias=None, transpose_x1=Fal
 
 def weight_quant_batch_matmul(x, weight, antiquant_scale, y, antiquant_offset=None, bias=None, antiquant_group_size=0,
                               inner_precise=None, workspace=None):
-    """Runs aclnnWeightQuantBatchMatmulV2 (or V3 when `inner_precise` is given) on the current torch CUDA stream."""
+    """Runs aclnnWeightQuantBatchMatmulV2 (V3 when `inner_precise` is 0 / 1, the Nz entry point when it is "nz") on the current
+    torch CUDA stream."""
     st, ws_size, ex = weight_quant_batch_matmul_get_workspace_size(x, weight, antiquant_scale, antiquant_offset, None, None,
                                                                    bias, antiquant_group_size, y, inner_precise)
-    api = "aclnnWeightQuantBatchMatmulV2" if inner_precise is None else "aclnnWeightQuantBatchMatmulV3"
+    api = "aclnnWeightQuantBatchMatmulNz" if inner_precise == "nz" else (
+        "aclnnWeightQuantBatchMatmulV2" if inner_precise is None else "aclnnWeightQuantBatchMatmulV3")
     if st != ACLNN_SUCCESS:
         raise AclnnError(api + "GetWorkspaceSize", st)
     if workspace is not None and workspace.numel() >= ws_size:

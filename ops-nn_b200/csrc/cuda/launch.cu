@@ -42,6 +42,10 @@ bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
 uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 
+uint64_t wq_nz_bytes(const OpsnnWqbmmParams* p);
+void wq_nz_view(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* q, void* dst);
+int32_t wq_nz_launch(const OpsnnWqbmmParams* p, void* dst, cudaStream_t stream);
+
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream);
 int32_t pack_b4_launch(const OpsnnPackB4Params* p, cudaStream_t stream);
 
@@ -137,6 +141,11 @@ static int32_t decode_chunk_launches(const OpsnnWqbmmParams* p, cudaStream_t str
 int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
 {
     if (p == nullptr) return OPSNN_WQ_KERNEL_GENERIC;
+    OpsnnWqbmmParams nd;
+    if (p->nz_k0 != 0) {  // FRACTAL_NZ weight: selection is that of the row-major copy (stand-in address with allocation alignment)
+        wq_nz_view(p, &nd, reinterpret_cast<void*>(uintptr_t(256)));
+        p = &nd;
+    }
     if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
     OpsnnWqbmmParams chunk;
@@ -151,6 +160,12 @@ uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_ch
 {
     if (p == nullptr) return 0;
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    OpsnnWqbmmParams nd;
+    if (p->nz_k0 != 0) {
+        const uint64_t pre = wq_nz_bytes(p);
+        wq_nz_view(p, &nd, reinterpret_cast<void*>(uintptr_t(256)));
+        return pre + opsnn_wqbmm_workspace_size(&nd, kernel_choice);
+    }
     if (kernel_choice == OPSNN_WQ_KERNEL_PREFILL) return wqbmm_prefill_workspace_size(p);
     return (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) ? wqbmm_decode_workspace_size(p) : 0;
 }
@@ -159,6 +174,14 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
 {
     if (p == nullptr) return (int32_t)cudaErrorInvalidValue;
     if (p->m <= 0 || p->n <= 0) return 0;
+    OpsnnWqbmmParams nd;
+    if (p->nz_k0 != 0) {
+        if (p->workspace == nullptr || p->workspace_size < wq_nz_bytes(p)) return (int32_t)cudaErrorInvalidValue;
+        const int32_t rc = wq_nz_launch(p, p->workspace, static_cast<cudaStream_t>(stream));
+        if (rc != 0) return rc;
+        wq_nz_view(p, &nd, p->workspace);
+        return opsnn_wqbmm_launch(&nd, kernel_choice, stream);
+    }
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
     OpsnnWqbmmParams chunk;
     if (p->m > 16 && (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST)) {

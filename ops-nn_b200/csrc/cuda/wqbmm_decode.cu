@@ -342,6 +342,10 @@ void set_err(const char* fmt, ...);  // thread-local text behind aclGetRecentErr
 
 int32_t wqbmm_decode_static_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
 {
+    if (p->nz_k0 != 0) {
+        set_err("opsnn_wqbmm_decode_static_launch: a FRACTAL_NZ weight needs workspace for its row-major copy");
+        return (int32_t)cudaErrorInvalidValue;
+    }
     if (p->n > (int64_t)kStaticGrid * kStripCols) {
         set_err("opsnn_wqbmm_decode_static_launch: n=%lld exceeds the %lld columns the built-in scratch covers", (long long)p->n,
                 (long long)kStaticGrid * kStripCols);

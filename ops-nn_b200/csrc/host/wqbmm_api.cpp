@@ -11,6 +11,7 @@
 #include "aclnnop/aclnn_convert_weight_to_int4_pack.h"
 #include "aclnnop/aclnn_dynamic_mx_quant.h"
 #include "aclnnop/aclnn_weight_quant_batch_matmul_v2.h"
+#include "aclnnop/aclnn_weight_quant_batch_matmul_nz.h"
 #include "aclnnop/aclnn_weight_quant_batch_matmul_v3.h"
 #include "internal.h"
 
@@ -27,7 +28,7 @@ namespace {
 aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weight, const aclTensor* antiquantScale,
                       const aclTensor* antiquantOffset, const aclTensor* quantScale, const aclTensor* quantOffset,
                       const aclTensor* bias, int antiquantGroupSize, int innerPrecise, const aclTensor* y,
-                      uint64_t* workspaceSize, aclOpExecutor** executor)
+                      uint64_t* workspaceSize, aclOpExecutor** executor, int nz_k0 = 0, int nz_n0 = 0)
 {
     clear_err();
     if (workspaceSize == nullptr || executor == nullptr) {
@@ -38,7 +39,7 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
         set_err("%s: x, weight, antiquantScale and y are required", api);
         return ACLNN_ERR_PARAM_NULLPTR;
     }
-    if (weight->format != ACL_FORMAT_ND) WQ_INVALID("%s: only ACL_FORMAT_ND weights are accepted by this entry point", api);
+    if (weight->format != ACL_FORMAT_ND && nz_k0 == 0) WQ_INVALID("%s: only ACL_FORMAT_ND weights are accepted by this entry point", api);
 
     // TensorPreProcess (:1526-1576): INT32 words are 8 INT4 along the inner axis; FLOAT words are 8 FP4
     aclTensor w = *weight;
@@ -185,6 +186,9 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     // innerPrecise = 1 asks for the high-performance mode; it only changes anything where the reference says it does
     // (A16W4 per-group, small m: docs/aclnnWeightQuantBatchMatmulV3.md:389), i.e. where the fast decode kernel applies
     p.inner_precise = innerPrecise;
+    p.nz_k0 = nz_k0;
+    p.nz_n0 = nz_n0;
+    if (nz_k0 != 0 && trans_w) no_kernel("a FRACTAL_NZ weight must be the plain (k,n) view");
     exec->kernel_choice = OPSNN_WQ_KERNEL_AUTO;
     if (const char* e = std::getenv("OPSNN_WQ_KERNEL")) exec->kernel_choice = std::atoi(e);
     if (!exec->unsupported) {
@@ -297,6 +301,43 @@ aclnnStatus aclnnWeightQuantBatchMatmulV3(void* workspace, uint64_t workspaceSiz
                                           aclrtStream stream)
 {
     return wq_run("aclnnWeightQuantBatchMatmulV3", workspace, workspaceSize, executor, stream);
+}
+
+// ---- aclnnWeightQuantBatchMatmulNz (aclnn_weight_quant_batch_matmul_v2.cpp:1820-1890) ---------------------------------------
+
+aclnnStatus aclnnWeightQuantBatchMatmulNzGetWorkspaceSize(const aclTensor* x, const aclTensor* weight, const aclTensor* antiquantScale,
+                                                          const aclTensor* antiquantOffsetOptional, const aclTensor* quantScaleOptional,
+                                                          const aclTensor* quantOffsetOptional, const aclTensor* biasOptional,
+                                                          int antiquantGroupSize, const aclTensor* y, uint64_t* workspaceSize,
+                                                          aclOpExecutor** executor)
+{
+    const char* api = "aclnnWeightQuantBatchMatmulNzGetWorkspaceSize";
+    clear_err();
+    if (x == nullptr || weight == nullptr || antiquantScale == nullptr || y == nullptr || workspaceSize == nullptr || executor == nullptr) {
+        set_err("%s: x, weight, antiquantScale, y, workspaceSize and executor are required", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (weight->format != ACL_FORMAT_FRACTAL_NZ && weight->format != ACL_FORMAT_FRACTAL_NZ_C0_32)
+        WQ_INVALID("%s: weight's storage format must be FRACTAL_NZ", api);
+    // storage dims [.., ceil(n/n0), ceil(k/k0), k0, n0] in elements of weight's dtype (INT32 words hold eight INT4)
+    const auto& sd = weight->storage_shape;
+    if (weight->rank() != 2 || sd.size() != 4) WQ_INVALID("%s: a FRACTAL_NZ weight needs a 2-D view and 4 storage dims", api);
+    const int64_t kw = weight->shape[0], nw = weight->shape[1], n1 = sd[0], k1 = sd[1], k0 = sd[2], n0 = sd[3];
+    if (k0 <= 0 || n0 <= 0 || k0 > 4096 || n0 > 4096 || n1 != ceil_div(nw, n0) || k1 != ceil_div(kw, k0))
+        WQ_INVALID("%s: storage dims [%ld,%ld,%ld,%ld] do not tile the (%ld,%ld) view", api, (long)n1, (long)k1, (long)k0, (long)n0,
+                   (long)kw, (long)nw);
+    aclTensor nd = *weight;  // the plan sees the row-major (k,n) matrix the pre-pass leaves in the workspace
+    nd.format = ACL_FORMAT_ND;
+    nd.strides = {nw, 1};
+    nd.storage_shape = nd.shape;
+    const int words = weight->dtype == ACL_INT32 || weight->dtype == ACL_FLOAT ? 8 : 1;
+    return wq_common(api, x, &nd, antiquantScale, antiquantOffsetOptional, quantScaleOptional, quantOffsetOptional, biasOptional,
+                     antiquantGroupSize, 0, y, workspaceSize, executor, (int)k0, (int)(n0 * words));
+}
+
+aclnnStatus aclnnWeightQuantBatchMatmulNz(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return wq_run("aclnnWeightQuantBatchMatmulNz", workspace, workspaceSize, executor, stream);
 }
 
 // ---- aclnnDynamicMxQuant --------------------------------------------------------------------------------------

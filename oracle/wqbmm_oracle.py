@@ -92,3 +92,20 @@ def convert_weight_to_b4_pack(weight):
     else:
         codes = (w.astype(np.int64) & 0xF).astype(np.uint8)
     return (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
+
+
+def nd_to_nz(a, k0, n0):
+    """(k, n) -> FRACTAL_NZ storage [ceil(n/n0), ceil(k/k0), k0, n0], zero padded: element (i, j) sits at
+    [j // n0, i // k0, i % k0, j % n0] (inverse of nz_to_nd, matmul/common/tests/st/arch35/matmul_golden_util.py:76-114)."""
+    k, n = a.shape
+    k1, n1 = -(-k // k0), -(-n // n0)
+    pad = np.zeros((k1 * k0, n1 * n0), dtype=a.dtype)
+    pad[:k, :n] = a
+    return np.ascontiguousarray(pad.reshape(k1, k0, n1, n0).transpose(2, 0, 1, 3))
+
+
+def nz_to_nd(nz, shape):
+    """FRACTAL_NZ storage [n1, k1, k0, n0] -> (k, n) (matmul_golden_util.py:76-114 of the reference)."""
+    n1, k1, k0, n0 = nz.shape
+    k, n = shape
+    return np.ascontiguousarray(nz.transpose(1, 2, 0, 3).reshape(k1 * k0, n1 * n0)[:k, :n])

@@ -366,9 +366,24 @@ def gen_mxq(G):
              dict(op="dynamic_mx_quant", dst=dst, seed=seed, note="quant/dynamic_mx_quant golden, last axis, OCP scale"))
 
 
+def gen_nz(G):
+    """FRACTAL_NZ storage -> (k, n) by the reference's nz_to_nd (matmul_golden_util.py:76-114), on random storage contents
+    (padding included), for the layout helper the aclnnWeightQuantBatchMatmulNz tests build their inputs with."""
+    import matmul_golden_util as mgu  # on sys.path once the goldens are loaded
+
+    rng = np.random.default_rng(80)
+    for i, (k, n, k0, n0) in enumerate([(50, 70, 16, 32), (64, 128, 16, 64), (33, 40, 16, 8)]):
+        nz = rng.integers(-128, 128, (-(-n // n0), -(-k // k0), k0, n0)).astype(np.int8)
+        nd = mgu.nz_to_nd(nz, (k, n))
+        assert bits_equal(nd, wqbmm_oracle.nz_to_nd(nz, (k, n)))
+        assert bits_equal(mgu.nz_to_nd(wqbmm_oracle.nd_to_nz(nd, k0, n0), (k, n)), nd)
+        save("nz_layout_%d" % i, dict(nz=nz, nd=nd), dict(op="nz_to_nd", k=k, n=n, k0=k0, n0=n0, seed=80))
+
+
 if __name__ == "__main__":
     assert ref_loader.available(), "reference tree not found"
     G = ref_loader.goldens()
     gen_qmm(G)
     gen_wq(G)
     gen_mxq(G)
+    gen_nz(G)
