@@ -166,6 +166,9 @@ typedef struct OpsnnMxQuantParams {
     const void* x;
     void* y;           /* (rows,k) fp8, or (rows, k/2) bytes for fp4 */
     void* scale;       /* (rows, 2*ceil(ceil(k/32)/2)) e8m0 bytes */
+    int64_t inner;     /* 0 or 1: blocks along the last axis. > 1: x is (rows, k, inner) contiguous with the blocks along k (a
+                          non-last axis); y has x's shape (fp4 packed along inner, inner even), scale is
+                          (rows, ceil(ceil(k/32)/2), inner, 2) with block b of a pair at [.., b / 2, i, b % 2] */
 } OpsnnMxQuantParams;
 
 OPSNN_API int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream);

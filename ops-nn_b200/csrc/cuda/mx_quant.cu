@@ -177,10 +177,88 @@ __global__ void __launch_bounds__(256) mx_quant_stream_kernel(const OpsnnMxQuant
     }
 }
 
+// Blocks along a non-last axis: x is (rows, k, inner); a thread owns one column i (two adjacent columns for fp4, which packs
+// along inner) of one 32-row block, so consecutive threads read consecutive addresses in every one of the 32 rows.
+template <bool kBf16, int kCols>
+__global__ void __launch_bounds__(256) mx_quant_axis_kernel(const OpsnnMxQuantParams p, int64_t nblk, int64_t pairs)
+{
+    const int64_t icols = p.inner / kCols, total = p.rows * pairs * 2 * icols;
+    const int emax = p.y_dtype == ACL_FLOAT4_E2M1 ? 2 : (p.y_dtype == ACL_FLOAT8_E4M3FN ? 8 : 15);
+    const uint16_t* x = reinterpret_cast<const uint16_t*>(p.x);
+    uint8_t* sc = reinterpret_cast<uint8_t*>(p.scale);
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t ic = t % icols, rb = (t / icols) % (pairs * 2), o = t / (icols * pairs * 2);
+        const int64_t i0 = ic * kCols;
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) {
+            uint8_t* sp = sc + ((o * pairs + (rb >> 1)) * p.inner + i0 + c) * 2 + (rb & 1);
+            if (rb >= nblk) *sp = 0;  // the entry that pads the block count to an even number
+        }
+        if (rb >= nblk) continue;
+        const int cnt = (int)min((int64_t)32, p.k - rb * 32);
+        float v[kCols][32];
+        float amax[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) amax[c] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                float f = 0.f;
+                if (j < cnt) {
+                    const uint16_t raw = x[(o * p.k + rb * 32 + j) * p.inner + i0 + c];
+                    f = kBf16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+                }
+                v[c][j] = f;
+                amax[c] = fmaxf(amax[c], fabsf(f));
+            }
+        }
+        float s0[kCols], s1[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) {
+            const int e = mx_shared_exp(amax[c], emax);
+            sc[((o * pairs + (rb >> 1)) * p.inner + i0 + c) * 2 + (rb & 1)] = e > 127 ? 255 : (uint8_t)(e + 127);
+            // 2^-e as two exact factors (2^-127 is subnormal)
+            s0[c] = e > 127 ? __uint_as_float(0x7FC00000u) : (e == 127 ? __uint_as_float(1u << 23) : __uint_as_float((uint32_t)(127 - e) << 23));
+            s1[c] = e == 127 ? 0.5f : 1.f;
+        }
+        if (p.y_dtype == ACL_FLOAT4_E2M1) {
+            uint8_t* y = reinterpret_cast<uint8_t*>(p.y);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < cnt)
+                    y[((o * p.k + rb * 32 + j) * p.inner + i0) / 2] =
+                        quant_fp4_e2m1(v[0][j] * s0[0] * s1[0]) | (quant_fp4_e2m1(v[kCols - 1][j] * s0[kCols - 1] * s1[kCols - 1]) << 4);
+        } else {
+            uint8_t* y = reinterpret_cast<uint8_t*>(p.y);
+            const __nv_fp8_interpretation_t kind = p.y_dtype == ACL_FLOAT8_E4M3FN ? __NV_E4M3 : __NV_E5M2;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < cnt) y[(o * p.k + rb * 32 + j) * p.inner + i0] = (uint8_t)__nv_cvt_float_to_fp8(v[0][j] * s0[0] * s1[0], __NV_SATFINITE, kind);
+        }
+    }
+}
+
 }  // namespace
 
 int32_t mx_quant_launch(const OpsnnMxQuantParams* p, cudaStream_t stream)
 {
+    if (p->inner > 1) {
+        const int64_t nblk = (p->k + 31) / 32, pairs = (nblk + 1) / 2;
+        const bool f4 = p->y_dtype == ACL_FLOAT4_E2M1;
+        if (f4 && p->inner % 2 != 0) return (int32_t)cudaErrorInvalidValue;
+        const int64_t total = p->rows * pairs * 2 * (p->inner / (f4 ? 2 : 1));
+        if (total == 0) return 0;
+        int64_t grid = (total + 255) / 256;
+        if (grid > 148 * 32) grid = 148 * 32;
+        const bool bf = p->x_dtype == ACL_BF16;
+        if (bf && f4) mx_quant_axis_kernel<true, 2><<<(unsigned)grid, 256, 0, stream>>>(*p, nblk, pairs);
+        else if (bf) mx_quant_axis_kernel<true, 1><<<(unsigned)grid, 256, 0, stream>>>(*p, nblk, pairs);
+        else if (f4) mx_quant_axis_kernel<false, 2><<<(unsigned)grid, 256, 0, stream>>>(*p, nblk, pairs);
+        else mx_quant_axis_kernel<false, 1><<<(unsigned)grid, 256, 0, stream>>>(*p, nblk, pairs);
+        note_launch("mx_quant_axis");
+        return (int32_t)cudaGetLastError();
+    }
     const int64_t blocks_per_row = (p->k + 31) / 32;
     const int64_t scale_row = ((blocks_per_row + 1) / 2) * 2;
     const int64_t total = p->rows * scale_row;

@@ -384,10 +384,7 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
     auto exec = std::make_unique<aclOpExecutor>();
     exec->kind = ExecKind::kMxQuant;
     if (x->empty()) exec->nothing_to_do = true;
-    if (ax != r - 1) {
-        exec->unsupported = true;
-        exec->unsupported_why = "only the last axis is implemented";
-    }
+
     if (scaleAlg != 0 || dstType == ACL_FLOAT4_E1M2 || (roundModeOptional && std::strcmp(roundModeOptional, "rint") != 0)) {
         exec->unsupported = true;
         exec->unsupported_why = "only scaleAlg 0, roundMode rint and e4m3/e5m2/e2m1 outputs are implemented";
@@ -401,6 +398,13 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
     p.y_dtype = (int32_t)dstType;
     p.k = kdim;
     p.rows = kdim > 0 ? x->numel() / kdim : 0;
+    if (ax != r - 1) {  // blocks along a non-last axis: (outer, k, inner)
+        int64_t inner = 1;
+        for (int64_t i = ax + 1; i < r; ++i) inner *= x->shape[i];
+        p.inner = inner;
+        p.rows = (kdim > 0 && inner > 0) ? x->numel() / (kdim * inner) : 0;
+        if (inner == 1) p.inner = 0;  // trailing dims of extent 1: the last-axis kernels apply
+    }
     p.x = data_ptr(x);
     p.y = const_cast<uint8_t*>(data_ptr(yOut));
     p.scale = const_cast<uint8_t*>(data_ptr(mxscaleOut));

@@ -1,4 +1,4 @@
-"""numpy restatement of the reference's dynamic MX quantisation golden (aclnnDynamicMxQuant, last axis, OCP scale).
+"""numpy restatement of the reference's dynamic MX quantisation golden (aclnnDynamicMxQuant, OCP scale).
 
 Follows quant/dynamic_mx_quant/tests/assets/golden.py of the reference: shared exponent :141-154, element quantisation
 :197-217, _mx_quantize :272-336 (scale padded to an even count with 2^-127, shaped (.., ceil(k/64), 2)).
@@ -15,8 +15,14 @@ _FMT = {
 }
 
 
-def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32):
-    """x (.., k) bf16|fp16|fp32 -> (y in dst dtype (.., k), scale bytes uint8 (.., ceil(k/64), 2))."""
+def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32, axis=-1):
+    """x bf16|fp16|fp32, blocks of 32 along `axis` -> (y in dst dtype, x's shape; scale bytes uint8: x's shape with the axis
+    replaced by ceil(ceil(len/32)/2), plus a trailing 2 holding the even/odd block of each pair - golden.py:320-331)."""
+    ax = axis if axis >= 0 else x.ndim + axis
+    if ax != x.ndim - 1:
+        y, sc = dynamic_mx_quant(np.moveaxis(x, ax, -1), dst, block)
+        # sc: (rest.., pairs, 2) -> pairs back to the axis position, the 2 stays last
+        return np.ascontiguousarray(np.moveaxis(y, -1, ax)), np.ascontiguousarray(np.moveaxis(sc, -2, ax))
     np_dt, ebits, mbits, max_norm = _FMT[dst]
     xf = x.astype(np.float32)
     k = xf.shape[-1]

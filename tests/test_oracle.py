@@ -54,7 +54,7 @@ def test_wq_oracle_matches_reference_golden(name):
 @pytest.mark.parametrize("name", golden_names("mxq_"))
 def test_mx_quant_oracle_matches_reference_golden(name):
     a, meta = load_golden(name)
-    y, s = mx_quant_oracle.dynamic_mx_quant(a["x"], meta["dst"])
+    y, s = mx_quant_oracle.dynamic_mx_quant(a["x"], meta["dst"], axis=meta.get("axis", -1))
     assert np.array_equal(y.view(np.uint8), a["y"].view(np.uint8))
     assert np.array_equal(s, a["scale"].view(np.uint8))
 
