@@ -169,6 +169,9 @@ typedef struct OpsnnMxQuantParams {
     int64_t inner;     /* 0 or 1: blocks along the last axis. > 1: x is (rows, k, inner) contiguous with the blocks along k (a
                           non-last axis); y has x's shape (fp4 packed along inner, inner even), scale is
                           (rows, ceil(ceil(k/32)/2), inner, 2) with block b of a pair at [.., b / 2, i, b % 2] */
+    int32_t scale_alg;  /* 0: OCP shared exponent floor(log2 amax) - emax; 1 (fp8 outputs): exponent of amax / max_norm rounded up
+                           to a power of two (quant/dynamic_mx_quant/tests/assets/golden.py:157-177) */
+    int32_t round_mode; /* fp4 outputs: 0 rint (ties to even), 1 round (ties away from zero), 2 floor; fp8 outputs: 0 */
 } OpsnnMxQuantParams;
 
 OPSNN_API int32_t opsnn_mx_quant_launch(const OpsnnMxQuantParams* p, void* stream);

@@ -36,6 +36,58 @@ __device__ __forceinline__ uint8_t quant_fp4_e2m1(float r)
     return (r < 0.f || (r == 0.f && signbit(r))) ? (code | 8) : code;
 }
 
+// scale_alg 1: exponent of amax / max_norm, one more unless that quotient is a power of two (golden.py:157-177)
+__device__ __forceinline__ int mx_shared_exp_up(float amax, float max_norm)
+{
+    if (amax == 0.f || !(amax == amax)) return -127;
+    if (isinf(amax)) return 128;
+    const uint32_t bits = __float_as_uint(__fdiv_rn(amax, max_norm));
+    int ex = (int)((bits >> 23) & 0xFFu);
+    const uint32_t mant = bits & 0x7FFFFFu;
+    if ((ex > 0 && ex < 254 && mant > 0u) || (ex == 0 && mant > (1u << 22))) ++ex;
+    return max(-127, ex - 127);
+}
+
+__device__ __forceinline__ int mx_shared_exp(float amax, int emax)
+{
+    int e;
+    if (amax == 0.f || !(amax == amax)) {
+        e = -127;
+    } else {
+        const int field = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
+        if (field != 0) {
+            e = field - 127 - emax;  // floor(log2(amax)) of a normal float is its exponent
+        } else {
+            int ex;
+            frexpf(amax, &ex);
+            e = (ex - 1) - emax;
+        }
+    }
+    if (isinf(amax)) e = 128;
+    return max(-127, e);
+}
+
+__device__ __forceinline__ int mx_block_exp(float amax, const OpsnnMxQuantParams& p, int emax)
+{
+    if (p.scale_alg == 1 && p.y_dtype != ACL_FLOAT4_E2M1) return mx_shared_exp_up(amax, p.y_dtype == ACL_FLOAT8_E4M3FN ? 448.f : 57344.f);
+    return mx_shared_exp(amax, emax);
+}
+
+// e2m1 with the golden's other rounding modes (golden.py:180-217): the value is scaled to its mantissa grid (0.5 below 2, 1 below
+// 4, 2 above), rounded there (1: half away from zero, 2: floor of the signed value), clipped to +-6; the result is an e2m1 value.
+__device__ __forceinline__ uint8_t quant_fp4_e2m1_mode(float r, int mode)
+{
+    if (mode == 0) return quant_fp4_e2m1(r);
+    const float a = fabsf(r);
+    const float step = a < 2.f ? 0.5f : (a < 4.f ? 1.f : 2.f);
+    float t = r / step;
+    if (mode == 1) t = copysignf(floorf(fabsf(t) + 0.5f), t);
+    else t = floorf(t);
+    const float q = fminf(fmaxf(t * step, -6.f), 6.f);
+    const uint8_t code = quant_fp4_e2m1(q);  // exact
+    return (q == 0.f && signbit(r) && mode == 1) ? (uint8_t)(code | 8) : code;
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const OpsnnMxQuantParams p, int64_t blocks_per_row,
                                                        int64_t scale_row)
@@ -64,17 +116,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const OpsnnMxQuantParams 
             amax = fmaxf(amax, fabsf(f));
         }
         const int emax = p.y_dtype == ACL_FLOAT4_E2M1 ? 2 : (p.y_dtype == ACL_FLOAT8_E4M3FN ? 8 : 15);
-        int e;
-        if (amax == 0.f || !(amax == amax)) {
-            e = -127;
-        } else {
-            // floor(log2(amax)) from the exponent field (subnormal inputs handled through frexp)
-            int ex;
-            frexpf(amax, &ex);  // amax = f * 2^ex, f in [0.5, 1)
-            e = (ex - 1) - emax;
-        }
-        if (isinf(amax)) e = 128;
-        e = max(-127, e);
+        const int e = mx_block_exp(amax, p, emax);
         const uint8_t byte = e > 127 ? 255 : (uint8_t)(e + 127);
         *sc = byte;
         const float inv = e > 127 ? __uint_as_float(0x7FC00000u) : ldexpf(1.f, -e);  // exact power of two
@@ -83,8 +125,8 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const OpsnnMxQuantParams 
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
                 if (j < cnt) {
-                    uint8_t lo = quant_fp4_e2m1(v[j] * inv);
-                    uint8_t hi = (j + 1 < cnt) ? quant_fp4_e2m1(v[j + 1] * inv) : 0;
+                    uint8_t lo = quant_fp4_e2m1_mode(v[j] * inv, p.round_mode);
+                    uint8_t hi = (j + 1 < cnt) ? quant_fp4_e2m1_mode(v[j + 1] * inv, p.round_mode) : 0;
                     dst[j / 2] = lo | (hi << 4);
                 }
             }
@@ -96,25 +138,6 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const OpsnnMxQuantParams 
                 if (j < cnt) dst[j] = (uint8_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, kind);
         }
     }
-}
-
-__device__ __forceinline__ int mx_shared_exp(float amax, int emax)
-{
-    int e;
-    if (amax == 0.f || !(amax == amax)) {
-        e = -127;
-    } else {
-        const int field = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
-        if (field != 0) {
-            e = field - 127 - emax;  // floor(log2(amax)) of a normal float is its exponent
-        } else {
-            int ex;
-            frexpf(amax, &ex);
-            e = (ex - 1) - emax;
-        }
-    }
-    if (isinf(amax)) e = 128;
-    return max(-127, e);
 }
 
 // Streaming form: k % 32 == 0, x and y 16-byte aligned. One lane = 8 consecutive elements; lanes 4j..4j+3 = one block.
@@ -147,7 +170,7 @@ __global__ void __launch_bounds__(256) mx_quant_stream_kernel(const OpsnnMxQuant
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        const int e = mx_shared_exp(amax, emax);
+        const int e = mx_block_exp(amax, p, emax);
         if (!live) continue;
         const int64_t blk_lin = i >> 2;
         if ((i & 3) == 0) {
@@ -162,7 +185,7 @@ __global__ void __launch_bounds__(256) mx_quant_stream_kernel(const OpsnnMxQuant
         if (p.y_dtype == ACL_FLOAT4_E2M1) {
             uint32_t out = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) out |= (uint32_t)quant_fp4_e2m1(v[j] * s0 * inv2) << (4 * j);
+            for (int j = 0; j < 8; ++j) out |= (uint32_t)quant_fp4_e2m1_mode(v[j] * s0 * inv2, p.round_mode) << (4 * j);
             reinterpret_cast<uint32_t*>(p.y)[i] = out;
         } else {
             const __nv_fp8_interpretation_t kind = p.y_dtype == ACL_FLOAT8_E4M3FN ? __NV_E4M3 : __NV_E5M2;
@@ -216,7 +239,7 @@ __global__ void __launch_bounds__(256) mx_quant_axis_kernel(const OpsnnMxQuantPa
         float s0[kCols], s1[kCols];
 #pragma unroll
         for (int c = 0; c < kCols; ++c) {
-            const int e = mx_shared_exp(amax[c], emax);
+            const int e = mx_block_exp(amax[c], p, emax);
             sc[((o * pairs + (rb >> 1)) * p.inner + i0 + c) * 2 + (rb & 1)] = e > 127 ? 255 : (uint8_t)(e + 127);
             // 2^-e as two exact factors (2^-127 is subnormal)
             s0[c] = e > 127 ? __uint_as_float(0x7FC00000u) : (e == 127 ? __uint_as_float(1u << 23) : __uint_as_float((uint32_t)(127 - e) << 23));
@@ -228,7 +251,8 @@ __global__ void __launch_bounds__(256) mx_quant_axis_kernel(const OpsnnMxQuantPa
             for (int j = 0; j < 32; ++j)
                 if (j < cnt)
                     y[((o * p.k + rb * 32 + j) * p.inner + i0) / 2] =
-                        quant_fp4_e2m1(v[0][j] * s0[0] * s1[0]) | (quant_fp4_e2m1(v[kCols - 1][j] * s0[kCols - 1] * s1[kCols - 1]) << 4);
+                        quant_fp4_e2m1_mode(v[0][j] * s0[0] * s1[0], p.round_mode) |
+                        (quant_fp4_e2m1_mode(v[kCols - 1][j] * s0[kCols - 1] * s1[kCols - 1], p.round_mode) << 4);
         } else {
             uint8_t* y = reinterpret_cast<uint8_t*>(p.y);
             const __nv_fp8_interpretation_t kind = p.y_dtype == ACL_FLOAT8_E4M3FN ? __NV_E4M3 : __NV_E5M2;

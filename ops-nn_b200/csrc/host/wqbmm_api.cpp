@@ -385,9 +385,9 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
     exec->kind = ExecKind::kMxQuant;
     if (x->empty()) exec->nothing_to_do = true;
 
-    if (scaleAlg != 0 || dstType == ACL_FLOAT4_E1M2 || (roundModeOptional && std::strcmp(roundModeOptional, "rint") != 0)) {
+    if (dstType == ACL_FLOAT4_E1M2) {
         exec->unsupported = true;
-        exec->unsupported_why = "only scaleAlg 0, roundMode rint and e4m3/e5m2/e2m1 outputs are implemented";
+        exec->unsupported_why = "FLOAT4_E1M2 output is not implemented";
     }
     if (!is_contiguous(x) || !is_contiguous(yOut) || !is_contiguous(mxscaleOut)) {
         exec->unsupported = true;
@@ -398,6 +398,9 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
     p.y_dtype = (int32_t)dstType;
     p.k = kdim;
     p.rows = kdim > 0 ? x->numel() / kdim : 0;
+    p.scale_alg = (int32_t)scaleAlg;
+    p.round_mode = roundModeOptional == nullptr || std::strcmp(roundModeOptional, "rint") == 0 ? 0
+                   : (std::strcmp(roundModeOptional, "round") == 0 ? 1 : 2);
     if (ax != r - 1) {  // blocks along a non-last axis: (outer, k, inner)
         int64_t inner = 1;
         for (int64_t i = ax + 1; i < r; ++i) inner *= x->shape[i];

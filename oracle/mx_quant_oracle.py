@@ -15,12 +15,12 @@ _FMT = {
 }
 
 
-def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32, axis=-1):
+def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32, axis=-1, scale_alg=0, round_mode="rint"):
     """x bf16|fp16|fp32, blocks of 32 along `axis` -> (y in dst dtype, x's shape; scale bytes uint8: x's shape with the axis
     replaced by ceil(ceil(len/32)/2), plus a trailing 2 holding the even/odd block of each pair - golden.py:320-331)."""
     ax = axis if axis >= 0 else x.ndim + axis
     if ax != x.ndim - 1:
-        y, sc = dynamic_mx_quant(np.moveaxis(x, ax, -1), dst, block)
+        y, sc = dynamic_mx_quant(np.moveaxis(x, ax, -1), dst, block, -1, scale_alg, round_mode)
         # sc: (rest.., pairs, 2) -> pairs back to the axis position, the 2 stays last
         return np.ascontiguousarray(np.moveaxis(y, -1, ax)), np.ascontiguousarray(np.moveaxis(sc, -2, ax))
     np_dt, ebits, mbits, max_norm = _FMT[dst]
@@ -35,13 +35,26 @@ def dynamic_mx_quant(x, dst="float8_e4m3fn", block=32, axis=-1):
     emax = int(np.log2(max_norm))
     with np.errstate(divide="ignore"):
         e = np.floor(np.log2(np.where(amax == 0, np.float32(2.0 ** -126), amax))) - emax
+    if scale_alg == 1 and dst != "float4_e2m1":  # exponent of amax / max_norm, rounded up to a power of two (golden.py:157-177)
+        bits = (amax.astype(np.float32) / np.float32(max_norm)).view(np.uint32)
+        ex = ((bits & np.uint32(0x7F800000)) >> 23).astype(np.int16)
+        mant = bits & np.uint32(0x007FFFFF)
+        up = ((ex > 0) & (ex < 254) & (mant > 0)) | ((ex == 0) & (mant > 2 ** 22))
+        e = (np.where(up, ex + 1, ex) - 127).astype(np.float32)
     e[amax == 0] = -np.inf
     e = np.where(e < -127, -127.0, e)
     r = blk / np.exp2(e).astype(np.float32)
     with np.errstate(divide="ignore"):
         pe = np.floor(np.log2(np.abs(r) + (r == 0)))
     pe = np.maximum(pe, -(2 ** (ebits - 1)) + 2)
-    q = np.rint(r / np.exp2(pe) * (2 ** mbits)) / (2 ** mbits) * np.exp2(pe)
+    t = r / np.exp2(pe) * (2 ** mbits)
+    if round_mode == "rint":
+        t = np.rint(t)
+    elif round_mode == "round":  # ties away from zero (golden.py:183-186)
+        t = np.where(np.signbit(t), -np.floor(np.abs(t) + 0.5), np.floor(np.abs(t) + 0.5))
+    else:  # "floor"
+        t = np.floor(t)
+    q = t / (2 ** mbits) * np.exp2(pe)
     q = np.clip(q, -max_norm, max_norm).astype(np.float32)
     y = q.reshape(xf.shape)[..., :k].astype(np_dt)
     sbytes = (e[..., 0] + 127).astype(np.uint8)

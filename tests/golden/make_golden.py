@@ -351,8 +351,13 @@ def gen_mxq(G):
              ("bf16_e4m3_outliers_3d", 65, (2, 6, 160), BF16, "float8_e4m3fn", 36, -1),
              # blocks along the second-to-last axis: what a (k, n) weight needs; scales come out as (k/64, n, 2)
              ("bf16_e4m3_axis0", 66, (256, 48), BF16, "float8_e4m3fn", 36, 0), ("fp16_e5m2_axis1_tail_3d", 67, (3, 100, 20), np.float16, "float8_e5m2", 35, -2),
-             ("bf16_e2m1_axis0", 68, (96, 64), BF16, "float4_e2m1", 40, -2)]
+             ("bf16_e2m1_axis0", 68, (96, 64), BF16, "float4_e2m1", 40, -2),
+             # the other shared-exponent rule (scaleAlg 1, fp8) and the other fp4 rounding modes
+             ("bf16_e4m3_alg1", 69, (9, 160), BF16, "float8_e4m3fn", 36, -1), ("fp16_e5m2_alg1", 70, (6, 96), np.float16, "float8_e5m2", 35, -1),
+             ("bf16_e2m1_round", 71, (8, 128), BF16, "float4_e2m1", 40, -1), ("fp16_e2m1_floor", 72, (8, 128), np.float16, "float4_e2m1", 40, -1)]
     for name, seed, shape, dt, dst, code, axis in cases:
+        alg = 1 if name.endswith("alg1") else 0
+        rmode = "round" if name.endswith("round") else ("floor" if name.endswith("floor") else "rint")
         rng = np.random.default_rng(seed)
         x = rng.standard_normal(shape).astype(np.float32)
         if "outliers" in name:
@@ -360,13 +365,14 @@ def gen_mxq(G):
             x = np.where(mask, x * 50, x)
             x[0, 0, :32] = 0.0  # an all-zero block
         x = x.astype(dt)
-        y, scale = ref.dynamic_mx_quant_golden(x, axis=axis, round_mode="rint", dst_type=code, blocksize=32, scale_alg=0,
+        y, scale = ref.dynamic_mx_quant_golden(x, axis=axis, round_mode=rmode, dst_type=code, blocksize=32, scale_alg=alg,
                                                output_dtypes=[dst, "float8_e8m0"])
-        yo, so = mx_quant_oracle.dynamic_mx_quant(x, dst, axis=axis)
+        yo, so = mx_quant_oracle.dynamic_mx_quant(x, dst, axis=axis, scale_alg=alg, round_mode=rmode)
         assert bits_equal(np.asarray(y).view(np.uint8), yo.view(np.uint8)), "oracle != reference (y) for " + name
         assert bits_equal(np.asarray(scale).view(np.uint8), so), "oracle != reference (scale) for " + name
         save("mxq_" + name, dict(x=x, y=np.asarray(y), scale=np.asarray(scale)),
-             dict(op="dynamic_mx_quant", dst=dst, axis=axis, seed=seed, note="quant/dynamic_mx_quant golden, OCP scale"))
+             dict(op="dynamic_mx_quant", dst=dst, axis=axis, scale_alg=alg, round_mode=rmode, seed=seed,
+                  note="quant/dynamic_mx_quant golden"))
 
 
 def gen_nz(G):

@@ -114,7 +114,7 @@ def test_dynamic_mx_quant_fixture(aclnn, name):
     y = torch.full(ybytes, 0xAA, dtype=torch.uint8, device=DEV)
     s = torch.full(a["scale"].shape, 0xAA, dtype=torch.uint8, device=DEV)
     aclnn.dynamic_mx_quant(desc(aclnn, x), aclnn.Tensor(x.shape, dst, y), aclnn.Tensor(a["scale"].shape, "float8_e8m0", s), dst,
-                           axis=meta.get("axis", -1))
+                           axis=meta.get("axis", -1), round_mode=meta.get("round_mode", "rint").encode(), scale_alg=meta.get("scale_alg", 0))
     torch.cuda.synchronize()
     want_y = a["y"].view(np.uint8)
     if dst == "float4_e2m1":

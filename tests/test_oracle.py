@@ -54,7 +54,8 @@ def test_wq_oracle_matches_reference_golden(name):
 @pytest.mark.parametrize("name", golden_names("mxq_"))
 def test_mx_quant_oracle_matches_reference_golden(name):
     a, meta = load_golden(name)
-    y, s = mx_quant_oracle.dynamic_mx_quant(a["x"], meta["dst"], axis=meta.get("axis", -1))
+    y, s = mx_quant_oracle.dynamic_mx_quant(a["x"], meta["dst"], axis=meta.get("axis", -1), scale_alg=meta.get("scale_alg", 0),
+                                            round_mode=meta.get("round_mode", "rint"))
     assert np.array_equal(y.view(np.uint8), a["y"].view(np.uint8))
     assert np.array_equal(s, a["scale"].view(np.uint8))
 
