@@ -109,7 +109,8 @@ typedef enum {
 
 typedef struct OpsnnWqbmmParams {
     int32_t x_dtype;        /* ACL_BF16 | ACL_FLOAT16; y has the same dtype */
-    int32_t w_dtype;        /* ACL_INT4 (packed nibbles, low first, along the stored inner axis) | ACL_INT8 */
+    int32_t w_dtype;        /* ACL_INT4 / ACL_FLOAT4_E2M1 (packed nibbles, low first, along the stored inner axis) | ACL_INT8 |
+                               ACL_FLOAT8_E4M3FN | ACL_FLOAT8_E5M2 */
     int32_t bias_dtype;     /* -1 | x_dtype | ACL_FLOAT */
     int32_t trans_w;        /* 0: weight stored (k,n); 1: stored (n,k) */
     int64_t m, n, k;
@@ -132,6 +133,7 @@ typedef struct OpsnnWqbmmParams {
        (matmul/common/tests/st/arch35/matmul_golden_util.py:76-114 of the reference). 0, 0: plain row-major storage. It is
        rewritten row-major into the head of the workspace before the matmul runs. */
     int32_t nz_k0, nz_n0;
+    int32_t scale_dtype;    /* 0 or x_dtype: scale in x's dtype; ACL_FLOAT8_E8M0: mx antiquant (group_size 32, no offset) */
 } OpsnnWqbmmParams;
 
 OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice);

@@ -47,7 +47,7 @@ class WqbmmParams(ctypes.Structure):
                 ("scale", c_void_p), ("offset", c_void_p), ("group_size", c_int64), ("scale_sg", c_int64),
                 ("scale_sn", c_int64), ("bias", c_void_p), ("y", c_void_p), ("y_ld", c_int64),
                 ("workspace", c_void_p), ("workspace_size", c_uint64), ("inner_precise", c_int32),
-                ("nz_k0", c_int32), ("nz_n0", c_int32)]
+                ("nz_k0", c_int32), ("nz_n0", c_int32), ("scale_dtype", c_int32)]
 
 
 _lib = None

@@ -62,6 +62,19 @@ __device__ __forceinline__ float load_as_float(const void* base, int64_t idx, in
     }
 }
 
+// Antiquant scale of the weight-only matmul as a float: in x's dtype, or e8m0 (mx) widened and, for fp16 activations, passed
+// through fp16 as the golden does (wqbmmv2_kernel_golden.py:323-326 of the reference: 2^e outside fp16's range becomes 0 / inf).
+__device__ __forceinline__ float load_wq_scale(const void* base, int64_t idx, int scale_dtype, bool x_is_bf16)
+{
+    if (scale_dtype == ACL_FLOAT8_E8M0) {
+        const uint32_t b = reinterpret_cast<const uint8_t*>(base)[idx];
+        const float f = b == 255u ? __uint_as_float(0x7FC00000u) : (b == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(b << 23));
+        return x_is_bf16 ? f : __half2float(__float2half_rn(f));
+    }
+    const uint16_t raw = reinterpret_cast<const uint16_t*>(base)[idx];
+    return x_is_bf16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+}
+
 // Dequant scale element as the reference's golden decodes it: fp32 as is, bf16 widened, uint64 = low word with the low
 // 13 bits cleared (matmul/common/tests/st/arch35/matmul_quant_util.py:129-134 of the reference).
 __device__ __forceinline__ float load_deq_scale(const void* base, int64_t idx, int dtype)

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(NT) wqbmm_generic_kernel(const OpsnnWqbmmParam
                 int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
                 int64_t sidx = g * p.scale_sg + gn * p.scale_sn;
                 if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
-                w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
+                w = round_x<kBf16>(__fmul_rn(w, load_wq_scale(p.scale, sidx, p.scale_dtype, kBf16)));
             }
             Ws[kk][nn] = w;
         }

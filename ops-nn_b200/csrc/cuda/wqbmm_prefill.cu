@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_kernel(const OpsnnWqbmmParam
             const int64_t g = p.group_size > 0 ? gk / p.group_size : 0;
             const int64_t sidx = g * p.scale_sg + gn * p.scale_sn;
             if (p.offset != nullptr) w = round_x<kBf16>(__fadd_rn(w, load_x<kBf16>(p.offset, sidx)));
-            w = round_x<kBf16>(__fmul_rn(w, load_x<kBf16>(p.scale, sidx)));
+            w = round_x<kBf16>(__fmul_rn(w, load_wq_scale(p.scale, sidx, p.scale_dtype, kBf16)));
         }
         tile[nn][kk] = bits_x<kBf16>(w);
     }
@@ -263,7 +263,9 @@ bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p)
 {
     if (getenv("OPSNN_WQ_NO_PREFILL")) return false;
     if (p->x_dtype != ACL_BF16 && p->x_dtype != ACL_FLOAT16) return false;
-    if (p->w_dtype != ACL_INT4 && p->w_dtype != ACL_INT8) return false;
+    if (p->w_dtype != ACL_INT4 && p->w_dtype != ACL_INT8 && p->w_dtype != ACL_FLOAT8_E4M3FN && p->w_dtype != ACL_FLOAT8_E5M2 &&
+        p->w_dtype != ACL_FLOAT4_E2M1)
+        return false;
     if (p->m < 1 || p->n < 1 || p->k < 1) return false;
     if (p->x_ld % 8 != 0 || (p->x != nullptr && (reinterpret_cast<uintptr_t>(p->x) & 15) != 0)) return false;
     OpsnnQmmParams q;
@@ -283,10 +285,11 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     if (tiles > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
     const bool tile_const_scale = p->group_size == 0 || p->group_size % TK == 0;
     const bool fast = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
-                      (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && tile_const_scale;
+                      (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && tile_const_scale && p->scale_dtype != ACL_FLOAT8_E8M0;
     const bool bf = p->x_dtype == ACL_BF16;
     const bool pairs = p->w_dtype == ACL_INT4 && !p->trans_w && p->w_ld % 8 == 0 && p->n % 8 == 0 &&
                        (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && (p->group_size == 0 || p->group_size % 8 == 0) &&
+                       p->scale_dtype != ACL_FLOAT8_E8M0 &&
                        getenv("OPSNN_WQ_PREFILL_SIMPLE") == nullptr;
     if (pairs) {
         const int64_t ptiles = ((p->n + PN - 1) / PN) * ((p->k + PK - 1) / PK);

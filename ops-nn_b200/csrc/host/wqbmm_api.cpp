@@ -180,8 +180,9 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     int64_t yld = nw;
     if (!row_strided_view(y, &yld, &bs)) no_kernel("y must be contiguous or row-strided");
     p.y_ld = yld;
-    if (wd != ACL_INT4 && wd != ACL_INT8) no_kernel("fp8/fp4/hifloat8 weight kernels are not built yet");
-    if (sc.dtype == ACL_FLOAT8_E8M0) no_kernel("mx (e8m0) antiquant kernels are not built yet");
+    if (wd == ACL_HIFLOAT8) no_kernel("HIFLOAT8 weights have no implementation here");
+    p.scale_dtype = sc.dtype == ACL_FLOAT8_E8M0 ? (int32_t)ACL_FLOAT8_E8M0 : 0;
+    if (sc.dtype == ACL_FLOAT8_E8M0 && antiquantOffset) no_kernel("mx antiquant takes no offset");
 
     // innerPrecise = 1 asks for the high-performance mode; it only changes anything where the reference says it does
     // (A16W4 per-group, small m: docs/aclnnWeightQuantBatchMatmulV3.md:389), i.e. where the fast decode kernel applies

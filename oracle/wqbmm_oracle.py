@@ -33,8 +33,16 @@ def pack_int4_words(vals):
 
 def dequant_weight(w, scale, offset, group_size, inter):
     """w (k,n) integer values; scale/offset (1|groups, 1|n) or (n,) in `inter` dtype. Two roundings in `inter`."""
-    wf = w.astype(np.float32)
+    wf = w.astype(np.float32)  # int4/int8 values, or fp8 / fp4 (exact in either intermediate dtype)
     sf = np.atleast_2d(scale.astype(np.float32))
+    if scale.dtype.name.startswith("float8_e8m0"):
+        # mx antiquant (wqbmmv2_kernel_golden.py:298-352): e8m0 per 32 rows, row count padded to even; with fp16 activations
+        # the scale passes through fp16 first
+        if inter == np.float16:
+            with np.errstate(over="ignore"):
+                sf = sf.astype(np.float16).astype(np.float32)
+        group_size = 32
+        sf = sf[: -(-wf.shape[0] // 32)]
     of = None if offset is None else np.atleast_2d(offset.astype(np.float32))
     k = wf.shape[0]
     if group_size and group_size > 0:

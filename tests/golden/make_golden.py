@@ -293,7 +293,8 @@ def wq_case(G, name, seed, x, w, scale, offset, bias, group, trans_w, note, pack
     """w: integer values as stored ((k,n), or (n,k) when trans_w); scale/offset as stored (transposed with the weight)."""
     ref = G["wqbmmv2"]
     out_name = "bfloat16" if x.dtype == np.dtype(BF16) else "float16"
-    wt = w.astype(INT4) if np.abs(w).max() <= 8 and packed is not None and w.dtype == np.int8 and name.find("s8") < 0 else w
+    wfloat = w.dtype != np.int8
+    wt = w if wfloat else (w.astype(INT4) if np.abs(w).max() <= 8 and packed is not None and name.find("s8") < 0 else w)
     y = ref.wqbmm_kernel_compute(x, wt, scale, offset, None, None, bias, transpose_x=False, transpose_weight=trans_w,
                                  antiquant_group_size=group, output_dtypes=[out_name])[0]
     wk = w.T if trans_w else w
@@ -303,7 +304,7 @@ def wq_case(G, name, seed, x, w, scale, offset, bias, group, trans_w, note, pack
     assert bits_equal(y, yo), "oracle != reference for " + name
     save("wq_" + name, dict(x=x, w=w, scale=scale, offset=offset, bias=bias, out=y),
          dict(op="weight_quant_batch_matmul_v2", group_size=group, transpose_weight=trans_w, seed=seed, note=note,
-              w_is_int4=bool(name.find("s8") < 0), packed_int32=bool(packed)))
+              w_is_int4=bool(name.find("s8") < 0) and not wfloat, packed_int32=bool(packed), w_float=bool(wfloat)))
 
 
 def gen_wq(G):
@@ -341,6 +342,21 @@ def gen_wq(G):
     rng = np.random.default_rng(48)
     wq_case(G, "fp16_s4_group64_bias_m8", 48, xs(rng, (8, 768), np.float16), i4(rng, (768, 576)), sc(rng, (12, 576), np.float16),
             None, xs(rng, (576,), np.float16), 64, False, "st_v2_fp16_s4_pergroup_bias (m scaled down)", packed=True)
+
+
+    # fp8 / fp4 weights (A16F8, A16MXF4): same two roundings; mx = e8m0 scale per 32 rows, row count padded to even
+    rng = np.random.default_rng(49)
+    wq_case(G, "bf16_f8e4m3_channel_m20", 49, xs(rng, (20, 256), BF16), q_fp8(rng, (256, 320), E4M3), sc(rng, (320,), BF16),
+            None, None, 0, False, "A16F8 per-channel (the API takes no offset with fp8 weights)")
+    rng = np.random.default_rng(50)
+    wq_case(G, "fp16_f8e4m3_group64_m4", 50, xs(rng, (4, 192), np.float16), q_fp8(rng, (192, 136), E4M3), sc(rng, (3, 136), np.float16),
+            None, xs(rng, (136,), np.float16), 64, False, "A16F8 per-group, bias")
+    rng = np.random.default_rng(51)
+    wq_case(G, "bf16_mxfp4_m40", 51, xs(rng, (40, 192), BF16), q_fp4(rng, (192, 128)), e8m0(rng, (6, 128), -4, 1), None, None, 32, False,
+            "A16MXF4: e2m1 weight, e8m0 scale per 32 rows (the golden itself only takes k that is a multiple of 64)")
+    rng = np.random.default_rng(52)
+    wq_case(G, "fp16_mxfp4_m3", 52, xs(rng, (3, 128), np.float16), q_fp4(rng, (128, 72)), e8m0(rng, (4, 72), -4, 1), None, None, 32, False,
+            "A16MXF4 with fp16 activations")
 
 
 # ------------------------------------------------------------------------------------------------------------

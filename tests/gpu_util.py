@@ -89,7 +89,9 @@ def run_wq_fixture(aclnn, a, meta, kernel=None, api="v2", inner_precise=0):
     out_name = np_name(a["out"])
     out = out_tensor(a["out"].shape, out_name)
     d_y = aclnn.Tensor(a["out"].shape, out_name, out)
-    if meta["w_is_int4"]:
+    if meta.get("w_float"):
+        d_w = desc(aclnn, w)  # fp8 bytes, or fp4 packed two per byte along n
+    elif meta["w_is_int4"]:
         if meta.get("packed_int32"):
             words = wqbmm_oracle.pack_int4_words(w)  # packed along the stored inner axis
             wt = torch.from_numpy(words.copy()).to(DEV)
