@@ -181,6 +181,8 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     if (!row_strided_view(y, &yld, &bs)) no_kernel("y must be contiguous or row-strided");
     p.y_ld = yld;
     if (wd == ACL_HIFLOAT8) no_kernel("HIFLOAT8 weights have no implementation here");
+    if ((quantScale != nullptr && !quantScale->empty()) || (quantOffset != nullptr && !quantOffset->empty()))
+        no_kernel("quantScale / quantOffset (INT8 output) have no implementation here");
     p.scale_dtype = sc.dtype == ACL_FLOAT8_E8M0 ? (int32_t)ACL_FLOAT8_E8M0 : 0;
     if (sc.dtype == ACL_FLOAT8_E8M0 && antiquantOffset) no_kernel("mx antiquant takes no offset");
 
