@@ -231,6 +231,65 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_pairs_kernel(const OpsnnWqbm
     }
 }
 
+// 8-bit weights (int8 / fp8) stored (k,n): a thread owns one 32-bit word (4 columns) over 4 consecutive k rows, the two row
+// pairs of a column leave as packed words; 64 x 64 tile with 33-word rows. Needs n % 4 == 0, word-aligned rows,
+// group_size % 4 == 0 and scales in x's dtype.
+template <bool kBf16>
+__global__ void __launch_bounds__(NT) wq_dequant_nk_bytes_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
+                                                                 float* __restrict__ one)
+{
+    __shared__ uint32_t tile[TN][TK / 2 + 1];
+    const int tid = threadIdx.x;
+    const int64_t tiles_n = (p.n + TN - 1) / TN;
+    const int64_t k0 = ((int64_t)blockIdx.x / tiles_n) * TK, n0 = ((int64_t)blockIdx.x % tiles_n) * TN;
+    if (blockIdx.x == 0 && tid == 0) *one = 1.0f;
+    const int wj = tid & 15, kq = tid >> 4;
+    const int64_t gn = n0 + wj * 4, gk = k0 + 4 * kq;
+    const bool col_live = gn < p.n;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = (col_live && gk + i < p.k) ? __ldcs(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.w) + (gk + i) * p.w_ld + gn)) : 0u;
+    float sc[4], of[4];
+    const bool has_off = p.offset != nullptr;
+    {
+        const int64_t g = p.group_size > 0 ? min(gk, p.k - 1) / p.group_size : 0;
+        const int64_t sidx = g * p.scale_sg + (col_live ? gn : 0) * p.scale_sn;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sc[j] = load_x<kBf16>(p.scale, sidx + j * p.scale_sn);
+            of[j] = has_off ? load_x<kBf16>(p.offset, sidx + j * p.scale_sn) : 0.f;
+        }
+    }
+    const bool is_int = p.w_dtype == ACL_INT8;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t byte = (w[i] >> (8 * j)) & 0xFFu;
+            v[i] = is_int ? (float)(int8_t)byte : fp8_to_float((uint8_t)byte, p.w_dtype);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float a = v[2 * h], b = v[2 * h + 1];
+            if (has_off) {
+                const float2 r = unpack2<kBf16>(pack2<kBf16>(__fadd_rn(a, of[j]), __fadd_rn(b, of[j])));
+                a = r.x;
+                b = r.y;
+            }
+            tile[wj * 4 + j][2 * kq + h] = pack2<kBf16>(__fmul_rn(a, sc[j]), __fmul_rn(b, sc[j]));
+        }
+    }
+    __syncthreads();
+    uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+    for (int e = tid; e < TN * (TK / 2); e += NT) {
+        const int nn = e >> 5, c = e & 31;
+        const int64_t on = n0 + nn, ok = k0 + 2 * c;
+        if (on < p.n && ok < kp) out[(on * kp + ok) >> 1] = tile[nn][c];
+    }
+}
+
 int64_t padded_k(const OpsnnWqbmmParams* p) { return (p->k + 7) / 8 * 8; }
 
 // The matmul the pre-pass leaves behind, as parameters of the quantised-matmul launcher.
@@ -305,6 +364,12 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
         }
         if (bf) wq_dequant_nk_pairs_kernel<true><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
         else wq_dequant_nk_pairs_kernel<false><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
+    } else if ((p->w_dtype == ACL_INT8 || p->w_dtype == ACL_FLOAT8_E4M3FN || p->w_dtype == ACL_FLOAT8_E5M2) && !p->trans_w &&
+               p->n % 4 == 0 && p->w_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 &&
+               (p->group_size == 0 || p->group_size % 4 == 0) && p->scale_dtype != ACL_FLOAT8_E8M0 &&
+               getenv("OPSNN_WQ_PREFILL_SIMPLE") == nullptr) {
+        if (bf) wq_dequant_nk_bytes_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
+        else wq_dequant_nk_bytes_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     } else if (bf && fast) wq_dequant_nk_words_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else if (bf) wq_dequant_nk_kernel<true><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else if (fast) wq_dequant_nk_words_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
