@@ -290,6 +290,53 @@ __global__ void __launch_bounds__(NT) wq_dequant_nk_bytes_kernel(const OpsnnWqbm
     }
 }
 
+// Weight stored (n,k) (the transposed-view case, e.g. a torch Linear weight): the destination has the same orientation, so a
+// thread dequantises one 32-bit word - kPer consecutive k of one column (8 for 4-bit, 4 for 8-bit weights) - and stores it as
+// one 16- / 8-byte piece. One scale / offset per word (groups are multiples of kPer, or per-channel).
+template <bool kBf16, int kPer>
+__global__ void __launch_bounds__(NT) wq_dequant_nk_rows_kernel(const OpsnnWqbmmParams p, uint16_t* __restrict__ dst, int64_t kp,
+                                                                float* __restrict__ one)
+{
+    if (blockIdx.x == 0 && threadIdx.x == 0) *one = 1.0f;
+    const int64_t wpr = p.k / kPer, total = p.n * wpr;  // words per row
+    const bool has_off = p.offset != nullptr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t nn = i / wpr, kw = i % wpr, kk = kw * kPer;
+        const uint32_t word = __ldcs(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.w) + (nn * p.w_ld + kk) * (32 / kPer) / 8));
+        const int64_t g = p.group_size > 0 ? kk / p.group_size : 0;
+        const int64_t sidx = g * p.scale_sg + nn * p.scale_sn;
+        const float sc = load_x<kBf16>(p.scale, sidx), of = has_off ? load_x<kBf16>(p.offset, sidx) : 0.f;
+        uint32_t outw[kPer / 2];
+#pragma unroll
+        for (int h = 0; h < kPer / 2; ++h) {
+            float a, b;
+            if (kPer == 8) {
+                const uint32_t n0 = (word >> (8 * h)) & 0xFu, n1 = (word >> (8 * h + 4)) & 0xFu;
+                if (p.w_dtype == ACL_INT4) {
+                    a = (float)((int)(n0 ^ 8u) - 8);
+                    b = (float)((int)(n1 ^ 8u) - 8);
+                } else {
+                    a = fp4_e2m1_to_float((uint8_t)n0);
+                    b = fp4_e2m1_to_float((uint8_t)n1);
+                }
+            } else {
+                const uint32_t b0 = (word >> (16 * h)) & 0xFFu, b1 = (word >> (16 * h + 8)) & 0xFFu;
+                a = p.w_dtype == ACL_INT8 ? (float)(int8_t)b0 : fp8_to_float((uint8_t)b0, p.w_dtype);
+                b = p.w_dtype == ACL_INT8 ? (float)(int8_t)b1 : fp8_to_float((uint8_t)b1, p.w_dtype);
+            }
+            if (has_off) {
+                const float2 r = unpack2<kBf16>(pack2<kBf16>(__fadd_rn(a, of), __fadd_rn(b, of)));
+                a = r.x;
+                b = r.y;
+            }
+            outw[h] = pack2<kBf16>(__fmul_rn(a, sc), __fmul_rn(b, sc));
+        }
+        uint16_t* o = dst + nn * kp + kk;
+        if (kPer == 8) *reinterpret_cast<uint4*>(o) = make_uint4(outw[0], outw[1], outw[kPer / 2 - 2], outw[kPer / 2 - 1]);
+        else *reinterpret_cast<uint2*>(o) = make_uint2(outw[0], outw[1]);
+    }
+}
+
 int64_t padded_k(const OpsnnWqbmmParams* p) { return (p->k + 7) / 8 * 8; }
 
 // The matmul the pre-pass leaves behind, as parameters of the quantised-matmul launcher.
@@ -350,7 +397,21 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
                        (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 && (p->group_size == 0 || p->group_size % 8 == 0) &&
                        p->scale_dtype != ACL_FLOAT8_E8M0 &&
                        getenv("OPSNN_WQ_PREFILL_SIMPLE") == nullptr;
-    if (pairs) {
+    const bool four = p->w_dtype == ACL_INT4 || p->w_dtype == ACL_FLOAT4_E2M1;
+    const int per = four ? 8 : 4;
+    const bool rows_path = p->trans_w && p->k % per == 0 && p->w_ld % per == 0 && (p->group_size == 0 || p->group_size % per == 0) &&
+                           p->scale_dtype != ACL_FLOAT8_E8M0 && (reinterpret_cast<uintptr_t>(p->w) & 3) == 0 &&
+                           getenv("OPSNN_WQ_PREFILL_SIMPLE") == nullptr;
+    if (rows_path) {
+        const int64_t work = p->n * (p->k / per);
+        int64_t grid = (work + NT - 1) / NT;
+        if (grid > 148 * 32) grid = 148 * 32;
+        if (grid < 1) grid = 1;
+        if (bf && four) wq_dequant_nk_rows_kernel<true, 8><<<(unsigned)grid, NT, 0, stream>>>(*p, wdeq, kp, one);
+        else if (bf) wq_dequant_nk_rows_kernel<true, 4><<<(unsigned)grid, NT, 0, stream>>>(*p, wdeq, kp, one);
+        else if (four) wq_dequant_nk_rows_kernel<false, 8><<<(unsigned)grid, NT, 0, stream>>>(*p, wdeq, kp, one);
+        else wq_dequant_nk_rows_kernel<false, 4><<<(unsigned)grid, NT, 0, stream>>>(*p, wdeq, kp, one);
+    } else if (pairs) {
         const int64_t ptiles = ((p->n + PN - 1) / PN) * ((p->k + PK - 1) / PK);
         if (ptiles > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
         const int vec = p->scale_sn == 1 && p->scale_sg % 8 == 0 && (reinterpret_cast<uintptr_t>(p->scale) & 15) == 0 &&

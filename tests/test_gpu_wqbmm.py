@@ -131,6 +131,8 @@ PREFILL_CASES = [
     (130, 768, 264, 64, True, True, False, False, None, "bfloat16"),      # weight stored (n,k)
     (64, 512, 384, 64, False, False, False, True, "x", "float16"),        # int8 weight
     (512, 2048, 2048, 128, True, False, True, True, None, "bfloat16"),    # CTA-pair tiles
+    (64, 512, 384, 0, False, True, False, True, "x", "bfloat16"),          # int8 weight stored (n,k), per-channel
+    (40, 1024, 520, 128, True, True, True, True, None, "float16"),         # int4 words stored (n, k/8), groups
 ]
 
 
