@@ -185,6 +185,56 @@ __global__ void __launch_bounds__(256) fp4_transpose_kernel(const uint8_t* __res
     }
 }
 
+// 8-bit operand stored along n (x2 given as (k,n)) -> k-contiguous (n, kp) in workspace, kp = k rounded up to 16. The
+// tensor core accepts the n-contiguous form, but the matmul kernel runs ~20 % slower on it; when one weight copy serves
+// thousands of output rows, moving it once (2 bytes of traffic per element) costs a few percent of that.
+// Tile = 64 k x 256 n bytes; 4 x 4 byte blocks are transposed in registers with byte permutes, 16-byte loads and stores.
+__global__ void __launch_bounds__(256) byte_transpose_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t R, int64_t C,
+                                                             int64_t src_pitch, int64_t dst_pitch, int64_t src_bs, int64_t dst_bs)
+{
+    __shared__ uint32_t tile[64][65];
+    const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 256;
+    const uint8_t* s = src + (int64_t)blockIdx.z * src_bs;
+    uint8_t* d = dst + (int64_t)blockIdx.z * dst_bs;
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = i * 16 + (t >> 4), c16 = t & 15;
+        const int64_t r = r0 + row, c = c0 + c16 * 16;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < R) {
+            if (c + 16 <= C) {
+                v = *reinterpret_cast<const uint4*>(s + r * src_pitch + c);
+            } else if (c < C) {
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                for (int j = 0; j < 16 && c + j < C; ++j) w[j >> 2] |= (uint32_t)s[r * src_pitch + c + j] << (8 * (j & 3));
+                v = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        tile[row][c16 * 4 + 0] = v.x; tile[row][c16 * 4 + 1] = v.y; tile[row][c16 * 4 + 2] = v.z; tile[row][c16 * 4 + 3] = v.w;
+    }
+    __syncthreads();
+    const int k16 = t & 3, c4 = t >> 2;  // 16 source rows x 4 source columns -> 4 destination rows x 16 bytes
+    uint32_t o[4][4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint32_t a0 = tile[k16 * 16 + 4 * g + 0][c4], a1 = tile[k16 * 16 + 4 * g + 1][c4];
+        const uint32_t a2 = tile[k16 * 16 + 4 * g + 2][c4], a3 = tile[k16 * 16 + 4 * g + 3][c4];
+        const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a2, a3, 0x5140);
+        const uint32_t t2 = __byte_perm(a0, a1, 0x7362), t3 = __byte_perm(a2, a3, 0x7362);
+        o[0][g] = __byte_perm(t0, t1, 0x5410); o[1][g] = __byte_perm(t0, t1, 0x7632);
+        o[2][g] = __byte_perm(t2, t3, 0x5410); o[3][g] = __byte_perm(t2, t3, 0x7632);
+    }
+    const int64_t kk = r0 + k16 * 16;
+    if (kk < dst_pitch) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t c = c0 + c4 * 4 + j;
+            if (c < C) *reinterpret_cast<uint4*>(d + c * dst_pitch + kk) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        }
+    }
+}
+
 template <int BN, bool kF4>
 __global__ void __launch_bounds__(192, 1)
 qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
@@ -249,7 +299,8 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const bool b_mn = a.b_mn_major != 0, a_mn = a.a_mn_major != 0;
         for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const uint32_t tm = r % (uint32_t)a.tiles_m, tn = r / (uint32_t)a.tiles_m;
+            uint32_t tm, tn;
+            tile_of<16>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
             const int32_t m0 = (int32_t)tm * BM, n0 = (int32_t)tn * BN;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
             const uint8_t* sfa = a.sfa + (int64_t)ba * a.sfa_bs + ((int64_t)tm * kstages) * kSfaBytes;
@@ -352,7 +403,9 @@ qmm_mx_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_of<16>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
             const int out_bytes = a.out_dtype == ACL_FLOAT ? 4 : 2;
@@ -415,7 +468,8 @@ struct MxPlan {
     int bn, atoms, row_atoms;
     int64_t tiles_m, tiles_n, kstages, kblocks32, kq;
     uint64_t sfa_bytes_per_batch, sfb_bytes_per_batch, nb_a, nb_b;
-    bool tr_a, tr_b;               // fp4 operand stored along m / n: rewritten k-contiguous into workspace first
+    bool tr_a, tr_b;               // operand stored along m / n rewritten k-contiguous into workspace first: always for fp4,
+                                   // for an 8-bit x2 when one copy of it serves enough output rows to pay for the move
     uint64_t tr_a_bytes, tr_b_bytes;  // whole operand, all batches
 };
 
@@ -451,8 +505,10 @@ MxPlan mx_plan(const OpsnnQmmParams* p)
     q.nb_b = p->sb_bs != 0 ? (uint64_t)p->batch : 1;
     q.tr_a = q.f4 && p->trans_a != 0;
     q.tr_b = q.f4 && p->trans_b == 0;
+    if (!q.f4 && p->trans_b == 0 && getenv("OPSNN_MX_NO_TRANSPOSE") == nullptr)
+        q.tr_b = p->m * (p->b_bs == 0 ? p->batch : 1) >= 8192 && (p->b_bs == 0 || p->batch <= 65535) && p->k / 64 < 65535;
     q.tr_a_bytes = q.tr_a ? (uint64_t)(p->a_bs != 0 ? p->batch : 1) * (uint64_t)p->m * (uint64_t)(p->k / 2) : 0;
-    q.tr_b_bytes = q.tr_b ? (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * (uint64_t)(p->k / 2) : 0;
+    q.tr_b_bytes = q.tr_b ? (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * (uint64_t)(q.f4 ? p->k / 2 : p->k) : 0;
     q.sfa_bytes_per_batch = (uint64_t)q.tiles_m * q.kstages * q.atoms * 512;
     q.sfb_bytes_per_batch = (uint64_t)q.tiles_n * q.kstages * q.atoms * q.row_atoms * 512;
     return q;
@@ -552,7 +608,13 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
             next = up(next + q.tr_a_bytes);
             note_launch("fp4_transpose");
         }
-        if (q.tr_b) {  // stored (k, n) -> (n, k)
+        if (q.tr_b && !q.f4) {  // 8-bit, stored (k, n) -> (n, k); k is a multiple of 32 here
+            const int64_t nb = p->b_bs != 0 ? p->batch : 1;
+            byte_transpose_kernel<<<dim3((unsigned)((p->n + 255) / 256), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
+                reinterpret_cast<const uint8_t*>(p->b), next, p->k, p->n, p->b_ld, p->k, p->b_bs, p->n * p->k);
+            pk.b = next; pk.b_ld = p->k; pk.b_bs = p->b_bs != 0 ? p->n * p->k : 0; pk.trans_b = 1;
+            note_launch("byte_transpose");
+        } else if (q.tr_b) {  // stored (k, n) -> (n, k)
             const int64_t nb = p->b_bs != 0 ? p->batch : 1;
             fp4_transpose_kernel<<<dim3((unsigned)((p->n + 63) / 64), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
                 reinterpret_cast<const uint8_t*>(p->b), next, p->k, p->n, p->b_ld / 2, p->k / 2, p->b_bs / 2, p->n * (p->k / 2));

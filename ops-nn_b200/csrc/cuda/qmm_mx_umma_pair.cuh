@@ -84,7 +84,8 @@ qmm_mx_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const uint32_t tx = (uint32_t)kATile + (b_mn ? kBHalf : (uint32_t)(HALF * BK)) + kSfaBytes + kSfbBytes;
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const uint32_t tmp = r % (uint32_t)a.tiles_m, tn = r / (uint32_t)a.tiles_m;
+            uint32_t tmp, tn;
+            tile_of<8>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tmp, tn);
             const int64_t tm128 = (int64_t)tmp * 2 + rank;
             const int32_t m0 = (int32_t)tm128 * 128, n0 = (int32_t)tn * BN + (int32_t)rank * HALF;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
@@ -191,7 +192,9 @@ qmm_mx_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         bool ok = true;
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * 256 + (int64_t)rank * 128, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_of<8>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int64_t m0 = (int64_t)tm * 256 + (int64_t)rank * 128, n0 = (int64_t)tn * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
             const int out_bytes = a.out_dtype == ACL_FLOAT ? 4 : 2;

@@ -69,6 +69,20 @@ struct UmmaArgs {
     unsigned long long ks_nonce;
 };
 
+// Order of the tiles of one batch. m runs fastest inside bands of kBand tile rows; a band is finished over all of n before
+// the next one starts. The tiles in flight at one time then span about as many rows as columns, so both operands are
+// fetched from L2; with m simply fastest, a matrix of tens of thousands of rows would stream the whole of A from DRAM once
+// per tile column. Up to kBand tile rows the order is plain m-fastest.
+template <uint32_t kBand>
+__device__ __forceinline__ void tile_of(uint32_t r, uint32_t tiles_m, uint32_t tiles_n, uint32_t& tm, uint32_t& tn)
+{
+    const uint32_t band_tiles = kBand * tiles_n;
+    const uint32_t band = r / band_tiles, rr = r - band * band_tiles;
+    const uint32_t rows = min(kBand, tiles_m - band * kBand);
+    tn = rr / rows;
+    tm = band * kBand + (rr - tn * rows);
+}
+
 __device__ unsigned int g_umma_status = 0;
   // 0 ok; otherwise (role << 8) | reason of the first failed wait
 
@@ -343,7 +357,9 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
             const uint32_t tile = work / ks, split = work - tile * ks;
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_of<16>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int32_t m0 = (int32_t)tm * BM, n0 = (int32_t)tn * BN;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
             const int kb_begin = (int)((int64_t)split * kblocks / (int)ks), kb_end = (int)((int64_t)(split + 1) * kblocks / (int)ks);
             int32_t kk = kb_begin * BK;
@@ -448,7 +464,9 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (uint32_t work = blockIdx.x; work < nwork && ok; work += gridDim.x) {
             const uint32_t tile = work / ks, split = work - tile * ks;
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * BM, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_of<16>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int64_t m0 = (int64_t)tm * BM, n0 = (int64_t)tn * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
             const int out_bytes = out_elem_bytes(a.out_dtype);

@@ -82,8 +82,10 @@ qmm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint32_t lead_full0 = full0 & ptx::kPeerBitMask;  // the even CTA's full barriers, from either CTA
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int32_t m0 = (int32_t)(r % (uint32_t)a.tiles_m) * 256 + (int32_t)rank * 128;
-            const int32_t n0 = (int32_t)(r / (uint32_t)a.tiles_m) * BN + (int32_t)rank * 128;
+            uint32_t tm, tn;
+            tile_of<8>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int32_t m0 = (int32_t)tm * 256 + (int32_t)rank * 128;
+            const int32_t n0 = (int32_t)tn * BN + (int32_t)rank * 128;
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
             int32_t kk = 0;
             for (int kb = 0; kb < kblocks; ++kb) {
@@ -165,7 +167,9 @@ qmm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         bool ok = true;
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
-            const int64_t m0 = (int64_t)(r % (uint32_t)a.tiles_m) * 256 + (int64_t)rank * 128, n0 = (int64_t)(r / (uint32_t)a.tiles_m) * BN;
+            uint32_t tm, tn;
+            tile_of<8>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
+            const int64_t m0 = (int64_t)tm * 256 + (int64_t)rank * 128, n0 = (int64_t)tn * BN;
             const int64_t row = m0 + quad * 32 + lane;
             const bool row_ok = row < a.m;
             const int out_bytes = (a.out_dtype == ACL_FLOAT || a.out_dtype == ACL_INT32) ? 4 : 2;
