@@ -50,6 +50,7 @@ INT8_CASES = [
     (130, 528, 208, False, False, 32, True, "f32", "float16"),       # n-major B in the 32-byte swizzle, n tail
     (272, 528, 400, True, False, 32, False, None, "bfloat16"),       # both operands stored along m / n
     (128, 4096, 1024, False, False, None, True, "i32", "bfloat16"),  # few tiles: the host picks a narrow tile by itself
+    (2200, 256, 304, False, False, 128, True, "i32", "bfloat16"),    # 18 tile rows: a band of 16 and a ragged band of 2
 ]
 
 
@@ -165,6 +166,7 @@ PAIR_CASES = [
     (300, 400, 400, False, False, True, "f32", "float16"),         # tails in m (odd CTA partly / wholly past m), k and n
     (640, 528, 336, True, True, True, "i32", "bfloat16"),          # x1 stored (k,m)
     (257, 2048, 272, False, True, False, "bf16", "bfloat16"),      # one row in the second CTA's half
+    (2500, 256, 528, False, True, True, "i32", "bfloat16"),        # 10 pair-tile rows: a band of 8 and a ragged band of 2
 ]
 
 
@@ -244,6 +246,7 @@ PAIR_PB_CASES = [
     (272, 528, 400, True, True, 1, False, None, "float32"),         # x1 stored (k,m)
     (512, 1024, 384, False, False, 1, True, "f32", "bfloat16"),     # int8: bit-exact
     (304, 400, 304, True, True, 1, True, "i32", "bfloat16"),
+    (2500, 256, 272, False, False, 1, True, None, "bfloat16"),      # 10 pair-tile rows: a band of 8 and a ragged band of 2
 ]
 
 

@@ -84,6 +84,7 @@ MX8_CASES = [
     ((), 1024, 2048, 1536, False, False, E4M3, E4M3, "f32", "bfloat16"),     # many tiles per CTA, deep k
     ((), 256, 512, 1344, False, True, E4M3, E4M3, "f32", "bfloat16"),        # n = 6 x 224
     ((), 256, 512, 1008, False, False, E4M3, E4M3, None, "float32"),         # n-major B, ragged last 224-tile
+    ((), 2500, 256, 464, False, True, E4M3, E4M3, "f32", "bfloat16"),        # 20 tile rows / 10 pair-tile rows: ragged last band
 ]
 
 
