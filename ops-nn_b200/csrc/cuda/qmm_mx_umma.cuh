@@ -185,6 +185,68 @@ __global__ void __launch_bounds__(256) fp4_transpose_kernel(const uint8_t* __res
     }
 }
 
+// The same rewrite for operands made of whole 64 x 128 tiles (R a multiple of 64, C of 128, 16-byte aligned source rows):
+// 16-byte loads, nibbles widened to bytes into shared memory (pitch 33 words: conflict-free stores), then every thread
+// takes an 8-row x 4-column block as eight words, transposes its bytes with byte permutes, packs each column's eight
+// rows into one word and stores it; eight neighbouring lanes fill one 32-byte sector of a destination row.
+__global__ void __launch_bounds__(256) fp4_transpose_tiles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t src_pitch,
+                                                                  int64_t dst_pitch, int64_t src_bs, int64_t dst_bs)
+{
+    __shared__ uint32_t tile[64][33];  // [source row][4 source columns per word, one element per byte]
+    const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 128;
+    const uint8_t* s = src + (int64_t)blockIdx.z * src_bs;
+    uint8_t* d = dst + (int64_t)blockIdx.z * dst_bs;
+    const int t = threadIdx.x;
+    {
+        const int row = t >> 2, seg = t & 3;  // 16 source bytes = 32 elements of one row
+        const uint4 v = *reinterpret_cast<const uint4*>(s + (r0 + row) * src_pitch + c0 / 2 + seg * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const uint32_t lo = w[h] & 0x0F0F0F0Fu, hi = (w[h] >> 4) & 0x0F0F0F0Fu;
+            tile[row][seg * 8 + 2 * h] = __byte_perm(lo, hi, 0x5140);      // e0 e1 e2 e3
+            tile[row][seg * 8 + 2 * h + 1] = __byte_perm(lo, hi, 0x7362);  // e4 e5 e6 e7
+        }
+    }
+    __syncthreads();
+    const int r8 = t & 7, c4 = t >> 3;
+    uint32_t a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = tile[r8 * 8 + i][c4];
+    uint32_t o[4];
+    {
+        const uint32_t p0 = __byte_perm(a[0], a[1], 0x5140), p1 = __byte_perm(a[2], a[3], 0x5140);
+        const uint32_t p2 = __byte_perm(a[0], a[1], 0x7362), p3 = __byte_perm(a[2], a[3], 0x7362);
+        const uint32_t q0 = __byte_perm(a[4], a[5], 0x5140), q1 = __byte_perm(a[6], a[7], 0x5140);
+        const uint32_t q2 = __byte_perm(a[4], a[5], 0x7362), q3 = __byte_perm(a[6], a[7], 0x7362);
+        const uint32_t lo[4] = {__byte_perm(p0, p1, 0x5410), __byte_perm(p0, p1, 0x7632), __byte_perm(p2, p3, 0x5410), __byte_perm(p2, p3, 0x7632)};
+        const uint32_t hi[4] = {__byte_perm(q0, q1, 0x5410), __byte_perm(q0, q1, 0x7632), __byte_perm(q2, q3, 0x5410), __byte_perm(q2, q3, 0x7632)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // bytes (rows 0..3), (rows 4..7) of column j -> eight nibbles, row 0 lowest
+            const uint32_t y0 = lo[j] | (lo[j] >> 4), y1 = hi[j] | (hi[j] >> 4);
+            o[j] = __byte_perm(y0, y1, 0x6420);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint32_t*>(d + (c0 + c4 * 4 + j) * dst_pitch + r0 / 2 + r8 * 4) = o[j];
+}
+
+// (R, C) fp4 packed along C -> (C, R) packed along R, for nb matrices; whole-tile operands take the word-wise kernel.
+inline void fp4_transpose(const uint8_t* src, uint8_t* dst, int64_t R, int64_t C, int64_t src_pitch, int64_t dst_pitch, int64_t src_bs,
+                          int64_t dst_bs, int64_t nb, cudaStream_t stream)
+{
+    const bool whole = R % 64 == 0 && C % 128 == 0 && src_pitch % 16 == 0 && src_bs % 16 == 0 && dst_pitch % 4 == 0 && dst_bs % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0 &&
+                       getenv("OPSNN_FP4_TRANSPOSE_SIMPLE") == nullptr;
+    if (whole)
+        fp4_transpose_tiles_kernel<<<dim3((unsigned)(C / 128), (unsigned)(R / 64), (unsigned)nb), 256, 0, stream>>>(src, dst, src_pitch, dst_pitch,
+                                                                                                                   src_bs, dst_bs);
+    else
+        fp4_transpose_kernel<<<dim3((unsigned)((C + 63) / 64), (unsigned)((R + 63) / 64), (unsigned)nb), 256, 0, stream>>>(src, dst, R, C, src_pitch,
+                                                                                                                         dst_pitch, src_bs, dst_bs);
+}
+
 // 8-bit operand stored along n (x2 given as (k,n)) -> k-contiguous (n, kp) in workspace, kp = k rounded up to 16. The
 // tensor core accepts the n-contiguous form, but the matmul kernel runs ~20 % slower on it; when one weight copy serves
 // thousands of output rows, moving it once (2 bytes of traffic per element) costs a few percent of that.
@@ -602,8 +664,7 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
         uint8_t* next = up(sfb + q.nb_b * q.sfb_bytes_per_batch);
         if (q.tr_a) {  // stored (k, m) -> (m, k)
             const int64_t nb = p->a_bs != 0 ? p->batch : 1;
-            fp4_transpose_kernel<<<dim3((unsigned)((p->m + 63) / 64), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
-                reinterpret_cast<const uint8_t*>(p->a), next, p->k, p->m, p->a_ld / 2, p->k / 2, p->a_bs / 2, p->m * (p->k / 2));
+            fp4_transpose(reinterpret_cast<const uint8_t*>(p->a), next, p->k, p->m, p->a_ld / 2, p->k / 2, p->a_bs / 2, p->m * (p->k / 2), nb, stream);
             pk.a = next; pk.a_ld = p->k; pk.a_bs = p->a_bs != 0 ? p->m * p->k : 0; pk.trans_a = 0;
             next = up(next + q.tr_a_bytes);
             note_launch("fp4_transpose");
@@ -616,8 +677,7 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
             note_launch("byte_transpose");
         } else if (q.tr_b) {  // stored (k, n) -> (n, k)
             const int64_t nb = p->b_bs != 0 ? p->batch : 1;
-            fp4_transpose_kernel<<<dim3((unsigned)((p->n + 63) / 64), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
-                reinterpret_cast<const uint8_t*>(p->b), next, p->k, p->n, p->b_ld / 2, p->k / 2, p->b_bs / 2, p->n * (p->k / 2));
+            fp4_transpose(reinterpret_cast<const uint8_t*>(p->b), next, p->k, p->n, p->b_ld / 2, p->k / 2, p->b_bs / 2, p->n * (p->k / 2), nb, stream);
             pk.b = next; pk.b_ld = p->k; pk.b_bs = p->b_bs != 0 ? p->n * p->k : 0; pk.trans_b = 1;
             note_launch("fp4_transpose");
         }

@@ -178,6 +178,8 @@ MX4_LAYOUT_CASES = [
     ((), 128, 256, 160, False, False),     # x2 given as (k,n): rewritten k-contiguous by the pre-pass
     ((), 192, 512, 352, True, True),       # x1 given as (k,m)
     ((2,), 160, 384, 224, True, False),    # both, batched
+    ((), 256, 320, 384, True, False),      # whole 64 x 128 tiles: the word-wise form of the pre-pass, both operands
+    ((3,), 128, 192, 256, False, False),   # the same, batched
 ]
 
 
