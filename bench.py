@@ -211,6 +211,7 @@ QMM_WORKLOADS = {
     "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
     "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
     "c5w": (1, 65536, 4096, 14336, "mxfp8"),        # c5mm's rows against ONE weight stored (k,n): the weight is moved k-contiguous first
+    "c5h": (1, 4096, 4096, 14336, "mxfp8"),         # the smallest row count at which that move is made
     "c5mmt": (32, 2048, 4096, 14336, "mxfp8_t"),    # same with the weight stored (n,k), transposeX2 = true
     "c2p": (1, 2048, 8192, 28672, "w4a16_prefill"), # the headline weight at a prefill m: dequant pre-pass + bf16 tcgen05 matmul
     "c2ps": (1, 256, 8192, 28672, "w4a16_prefill"),

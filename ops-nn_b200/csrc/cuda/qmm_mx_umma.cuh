@@ -248,8 +248,9 @@ inline void fp4_transpose(const uint8_t* src, uint8_t* dst, int64_t R, int64_t C
 }
 
 // 8-bit operand stored along n (x2 given as (k,n)) -> k-contiguous (n, kp) in workspace, kp = k rounded up to 16. The
-// tensor core accepts the n-contiguous form, but the matmul kernel runs ~20 % slower on it; when one weight copy serves
-// thousands of output rows, moving it once (2 bytes of traffic per element) costs a few percent of that.
+// tensor core accepts the n-contiguous form, but with 224-column tiles the matmul kernel runs ~20 % slower on it (a CTA's
+// 112-column share starts off the 32-byte sector grid); when one weight copy serves thousands of output rows, moving it
+// once (2 bytes of traffic per element) costs a fraction of that.
 // Tile = 64 k x 256 n bytes; 4 x 4 byte blocks are transposed in registers with byte permutes, 16-byte loads and stores.
 __global__ void __launch_bounds__(256) byte_transpose_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t R, int64_t C,
                                                              int64_t src_pitch, int64_t dst_pitch, int64_t src_bs, int64_t dst_bs)
@@ -568,7 +569,7 @@ MxPlan mx_plan(const OpsnnQmmParams* p)
     q.tr_a = q.f4 && p->trans_a != 0;
     q.tr_b = q.f4 && p->trans_b == 0;
     if (!q.f4 && p->trans_b == 0 && getenv("OPSNN_MX_NO_TRANSPOSE") == nullptr)
-        q.tr_b = p->m * (p->b_bs == 0 ? p->batch : 1) >= 8192 && (p->b_bs == 0 || p->batch <= 65535) && p->k / 64 < 65535;
+        q.tr_b = q.bn == 224 && p->m * (p->b_bs == 0 ? p->batch : 1) >= 4096 && (p->b_bs == 0 || p->batch <= 65535) && p->k / 64 < 65535;
     q.tr_a_bytes = q.tr_a ? (uint64_t)(p->a_bs != 0 ? p->batch : 1) * (uint64_t)p->m * (uint64_t)(p->k / 2) : 0;
     q.tr_b_bytes = q.tr_b ? (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * (uint64_t)(q.f4 ? p->k / 2 : p->k) : 0;
     q.sfa_bytes_per_batch = (uint64_t)q.tiles_m * q.kstages * q.atoms * 512;

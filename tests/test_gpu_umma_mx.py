@@ -199,7 +199,7 @@ def test_mxfp4_operands_stored_along_m_or_n(aclnn, case):
 
 
 MX8_MOVED_WEIGHT_CASES = [
-    # batch, m, k, n: x2 stored (k,n), one copy of it serving >= 8192 output rows
+    # batch, m, k, n: x2 stored (k,n), one copy of it serving >= 4096 output rows, 224-column tiles
     ((), 8200, 160, 208),     # ragged m; k = 2.5 tiles of 64; n below one 256-column tile of the pre-pass
     ((), 8192, 96, 528),      # n = 2 tiles + 16
     ((2,), 8192, 64, 272),    # per-batch weights
@@ -218,11 +218,11 @@ def test_mxfp8_weight_stored_along_n_is_moved_k_contiguous(aclnn, case, monkeypa
     s1, s2 = _e8m0(rng, batch + (m, kq, 2)), _e8m0(rng, batch + (kq, n, 2))
     bias = rng.uniform(-2, 2, n).astype(np.float32)
     before = aclnn.launch_count()
-    got = _run(aclnn, x1, x2, s1, s2, bias, False, False, "bfloat16", "qmm_umma_mxfp8", 128)
+    got = _run(aclnn, x1, x2, s1, s2, bias, False, False, "bfloat16", "qmm_umma_mxfp8", 224)
     moved = aclnn.launch_count() - before
     monkeypatch.setenv("OPSNN_MX_NO_TRANSPOSE", "1")
     before = aclnn.launch_count()
-    plain = _run(aclnn, x1, x2, s1, s2, bias, False, False, "bfloat16", "qmm_umma_mxfp8", 128)
+    plain = _run(aclnn, x1, x2, s1, s2, bias, False, False, "bfloat16", "qmm_umma_mxfp8", 224)
     assert moved == aclnn.launch_count() - before + 1
     assert np.array_equal(got.view(np.uint16), plain.view(np.uint16))
     _check(got, _oracle(x1, x2, s1, s2, bias, False, False, "bfloat16"), "bfloat16")
