@@ -64,3 +64,11 @@ def load_golden(name):
         else:
             out[k] = a.view(views[dt]) if dt in views else a
     return out, meta
+
+
+def case_seed(case):
+    """Seed for a parametrised case's random inputs: the same in every process (the built-in hash of a string is salted
+    per interpreter run, which would make a failure unrepeatable)."""
+    import zlib
+
+    return zlib.crc32(repr(case).encode()) & 0x7FFFFFFF

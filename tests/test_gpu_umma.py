@@ -4,6 +4,7 @@ import ml_dtypes
 import numpy as np
 import pytest
 
+from conftest import case_seed
 from oracle import qbmm_oracle
 
 pytestmark = pytest.mark.gpu
@@ -57,7 +58,7 @@ INT8_CASES = [
 @pytest.mark.parametrize("case", INT8_CASES, ids=[str(c) for c in INT8_CASES])
 def test_int8_dequant_bit_exact(aclnn, case):
     m, k, n, t1, t2, bn, pertoken, bias_kind, out_name = case
-    rng = np.random.default_rng(hash(case) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
     x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
     s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
@@ -103,7 +104,7 @@ def test_fp8_perblock(aclnn, case):
     from gpu_util import check_close
 
     m, k, n, t1, t2, gm, bn, da, db, out_name = case
-    rng = np.random.default_rng(abs(hash(case[:7])) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case[:7]))
     x1 = _fp8(rng, (k, m) if t1 else (m, k), da)
     x2 = _fp8(rng, (n, k) if t2 else (k, n), db)
     kb, mg, ng = -(-k // 128), -(-m // gm), -(-n // 128)
@@ -130,7 +131,7 @@ def test_int8_perblock_bit_exact(aclnn, case):
     """int8 with 1 x 128 / 128 x 128 fp32 scales: each 128-k partial is an exact int32, converted, multiplied by
     s1 * s2 and added with separate roundings like the reference's golden, so the result is compared bit for bit."""
     m, k, n, t1, t2, bn, bias_kind, out_name = case
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
     x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
     kb, ng = -(-k // 128), -(-n // 128)
@@ -176,7 +177,7 @@ def test_int8_dequant_cta_pairs_bit_exact(aclnn, case, monkeypatch):
     would give to the single-CTA kernel, against the oracle: bit for bit."""
     m, k, n, t1, t2, pertoken, bias_kind, out_name = case
     monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
     x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
     s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
@@ -257,7 +258,7 @@ def test_perblock_cta_pairs(aclnn, case, monkeypatch):
     from gpu_util import check_close
 
     m, k, n, t1, t2, gm, is_int, bias_kind, out_name = case
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     kb, mg, ng = -(-k // 128), -(-m // gm), -(-n // 128)
     if is_int:
         x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
@@ -296,7 +297,7 @@ def test_int8_split_k_bit_exact(aclnn, case, monkeypatch):
     """Few output tiles: the k range is split over several CTAs, partial int32 tiles meet in the workspace and the CTA that
     completes the tile's arrival count sums them and runs the epilogue. Integer partial sums: still bit-identical."""
     m, k, n, t1, t2, ks, per_token, bias_kind, out_name = case
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x1 = rng.integers(-127, 128, (k, m) if t1 else (m, k), dtype=np.int8)
     x2 = rng.integers(-127, 128, (n, k) if t2 else (k, n), dtype=np.int8)
     s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import golden_names, load_golden
+from conftest import case_seed, golden_names, load_golden
 from oracle import mx_quant_oracle, wqbmm_oracle
 
 pytestmark = pytest.mark.gpu
@@ -146,7 +146,7 @@ def test_prefill_dequant_then_tensor_core_matmul(aclnn, case):
 
     m, k, n, group, int4, tw, words, has_off, bias_kind, xname = case
     xdt = ml_dtypes.bfloat16 if xname == "bfloat16" else np.float16
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x = rng.standard_normal((m, k)).astype(xdt)
     w = rng.integers(-8, 8, (k, n)).astype(np.int8) if int4 else rng.integers(-127, 128, (k, n)).astype(np.int8)
     sshape = (-(-k // group), n) if group else (n,)

@@ -3,7 +3,7 @@ argument rules on CPU, and on the GPU the same result as the row-major call."""
 import numpy as np
 import pytest
 
-from conftest import golden_names, load_golden
+from conftest import case_seed, golden_names, load_golden
 from oracle import wqbmm_oracle
 
 ACL_FORMAT_FRACTAL_NZ = 29
@@ -47,7 +47,7 @@ def test_nz_weight_gives_the_row_major_result(aclnn, case):
     from gpu_util import desc, out_tensor, out_to_np
 
     m, k, n, g, int4, k0, n0 = case
-    rng = np.random.default_rng(abs(hash(case)) % (2 ** 31))
+    rng = np.random.default_rng(case_seed(case))
     x = rng.standard_normal((m, k)).astype(ml_dtypes.bfloat16)
     w = (rng.integers(-8, 8, (k, n)) if int4 else rng.integers(-127, 128, (k, n))).astype(np.int8)
     sshape = (k // g, n) if g else (n,)
