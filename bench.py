@@ -1,20 +1,26 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-matmul hot path. Contract: `python bench.py --gpus N --steps K --warmup W` prints ONE JSON line.
 
-Headline workload (`--workload c2`, the default): weight_quant_batch_matmul_v2 W4A16 decode, x bf16 [16, 8192],
-weight int4 [8192, 28672] packed 8 per int32 along n, per-group (128) bf16 scale + offset, y bf16 [16, 28672];
-HBM-bound, metric = achieved HBM GB/s on the algorithmic bytes (125.96 MB per call). One "step" is one call.
+The line's top level is the headline workload c2 (weight_quant_batch_matmul_v2 W4A16 decode: x bf16 [16, 8192], weight int4
+[8192, 28672] packed 8 per int32 along n, per-group (128) bf16 scale + offset, y bf16 [16, 28672]; HBM bound; metric = HBM
+GB/s on the algorithmic bytes, 125.96 MB per call; one "step" is one call). `workloads` carries the four other named
+configurations (c1 int8 K-C, c3 fp8 per-block, c4 MXFP4, c5 dynamic MX quant + MXFP8), each with its time, T(FL)OP/s, a
+roofline fraction against the measured and the datasheet peak, the kernels that ran, a parity verdict from sampled
+output tiles against the CPU oracle computed in the same run, and the oracle timed on the host cores on a bounded sample.
 
-  value   device-timed throughput with every operand resident in HBM. The weight (117 MB) would fit the 126 MB L2, so
+  value   device-timed throughput with every operand resident in HBM. The c2 weight (117 MB) would fit the 126 MB L2, so
           the steps rotate over 4 distinct weight/scale/offset sets (504 MB) and every step streams from DRAM.
   e2e     the same call through the aclnn C ABI starting from HOST buffers: per step the activation x is copied from
-          pinned host memory to the device and y is copied back; the quantised weight, being a static model parameter,
-          is uploaded once before the timed region (its upload time is reported separately as `weight_upload_ms`).
-  N > 1   one process per GPU (torchrun); the weight is sharded along n with a fixed [8192, 28672] shard per rank (weak
-          scaling: the global n grows with N), x replicated, no collective on the data path. Timing = max over ranks.
+          pinned host memory to the device and y is copied back; the quantised weight, a static model parameter, is
+          uploaded once before the timed region (its upload time is reported as `weight_upload_ms`).
+  N > 1   one process per GPU (torchrun). Every named shape is sharded as a whole across the ranks ("strong" scaling): c2
+          and c3 along n (weight columns, x replicated), c4 and c5 along the batch; no collective on the data path. value =
+          the global algorithmic work / the slowest rank's time. `with_gather` adds the optional all-gather of the y shards
+          (NCCL) inside the timed region; `weak` is the former figure (every rank a full-size shard).
 
-`--impl reference` times the CPU restatement of the reference's golden (oracle/, numpy on all host cores) on the same
-workload and prints the same line with "impl": "reference".
+`--impl reference` times the CPU restatement of the reference's golden (oracle/, all host cores) on the same seeded inputs,
+one bounded sample of the workload per step, and prints the same line with "impl": "reference".
+`--workload NAME` prints a single secondary line for one shape (development aid; NAME from QMM_WORKLOADS).
 """
 import argparse
 import importlib.util
@@ -29,7 +35,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 M, K, N, G = 16, 8192, 28672, 128
-ALGO_BYTES = K * N // 2 + 2 * (K // G) * N * 2 + M * K * 2 + M * N * 2  # 125,960,192
+MX_GROUP = (1 << 32) | (1 << 16) | 32
+PB_GROUP = (1 << 32) | (128 << 16) | 128
+
+
+def c2_bytes(n):
+    return K * n // 2 + 2 * (K // G) * n * 2 + M * K * 2 + M * n * 2
+
+
+ALGO_BYTES = c2_bytes(N)  # 125,960,192
+WORKLOAD_C2 = "c2: W4A16 decode m16 k8192 n28672 group128 bf16 scale+offset, int4 packed 8/int32 along n"
+METRIC = "W4A16 decode HBM GB/s (weight_quant_batch_matmul_v2, algorithmic bytes / time)"
 
 
 def load_package():
@@ -44,16 +60,18 @@ def load_package():
     return mod
 
 
-def measured_peak():
+def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, source text)."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as fh:
-            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, 1590.0, "fallback (earlier measurement on this pool)"
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reading only)."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run (reading only)."""
 
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
@@ -64,7 +82,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -75,16 +93,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:  # noqa: BLE001
-            pass
+    def mark(self):
+        return len(self.rows)
+
+    def summary(self, first=0, last=None):
         mhz, mx, reasons = [], None, set()
-        for r in self.rows:
+        for r in self.rows[first:last]:
             try:
                 mhz.append(float(r[0]))
                 mx = float(r[1])
@@ -94,120 +108,589 @@ class ClockSampler:
             except Exception:  # noqa: BLE001
                 continue
         mhz.sort()
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            pass
 
 
-WORKLOAD_C2 = "c2: W4A16 decode m16 k8192 n28672 group128 bf16 scale+offset, int4 packed 8/int32 along n"
+# ------------------------------------------------------------------------------------------------------------------
+# inputs of c2: numpy, seeded, the same in the GPU arm (set 0, the one parity and the CPU baseline use) and the CPU arm
+# ------------------------------------------------------------------------------------------------------------------
 
-
-def make_inputs(torch, dev, seed, sets):
-    gen = torch.Generator(device=dev).manual_seed(seed)
-    x = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    data = []
-    for _ in range(sets):
-        w = torch.randint(-8, 8, (K, N), generator=gen, device=dev, dtype=torch.int32)
-        words = torch.zeros((K, N // 8), dtype=torch.int32, device=dev)
-        for j in range(8):
-            words |= (w[:, j::8] & 0xF) << (4 * j)
-        del w
-        scale = (torch.rand((K // G, N), generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
-        offset = (torch.rand((K // G, N), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
-        data.append((words, scale, offset))
-    return x, data
-
-
-def cpu_oracle_once(x_np, words_np, scale_np, offset_np):
-    from oracle import wqbmm_oracle
-
-    t0 = time.perf_counter()
-    w = wqbmm_oracle.unpack_int4_words(words_np)
-    y = wqbmm_oracle.weight_quant_batch_matmul(x_np, w, scale_np, offset_np, None, G)
-    return time.perf_counter() - t0, y
-
-
-def cpu_c_oracle_once(x_np, words_np, scale_np, offset_np, cols):
-    """The plain-C restatement (oracle/c) on all host cores over the first `cols` columns; returns seconds scaled to the
-    full width, or None when the C oracle is not built and cannot be built here."""
+def c2_host_inputs(cols=N):
+    """x bf16 [16, 8192] ~ N(0,1); int4 weight U{-8..7} packed 8 per int32 along n; bf16 scale U[0.005, 0.02] and offset
+    U[-1, 1] per (128-row group, column). `cols` < N generates the leading columns of the same streams."""
+    import ml_dtypes
     import numpy as np
 
-    try:
-        from oracle import c_oracle
-
-        c_oracle.lib()
-    except Exception:
-        return None
-    threads = os.cpu_count() or 1
-    u16 = lambda a: a.view(np.uint16)
-    t0 = time.perf_counter()
-    c_oracle.wq_w4a16_group(u16(x_np), words_np, u16(scale_np), u16(offset_np), G, 0, cols, threads=threads)
-    return (time.perf_counter() - t0) * (N / cols)
+    rng = np.random.default_rng(1002)
+    x = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    words = rng.integers(-2 ** 31, 2 ** 31, (K, N // 8), dtype=np.int64).astype(np.int32)  # uniform words = uniform nibbles
+    scale = rng.uniform(0.005, 0.02, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    offset = rng.uniform(-1, 1, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    if cols < N:
+        words, scale, offset = (np.ascontiguousarray(words[:, :cols // 8]), np.ascontiguousarray(scale[:, :cols]),
+                                np.ascontiguousarray(offset[:, :cols]))
+    return x, words, scale, offset
 
 
-def cpu_baseline_c2(x_np, words_np, scale_np, offset_np):
-    """CPU baseline of the c2 workload: the faster of the numpy restatement of the reference golden (one full call, BLAS
-    threads) and the C restatement (all cores, a 2048-column panel scaled to the full width)."""
-    sec_np, _ = cpu_oracle_once(x_np, words_np, scale_np, offset_np)
-    sec_c = cpu_c_oracle_once(x_np, words_np, scale_np, offset_np, 2048)
-    use_c = sec_c is not None and sec_c < sec_np
-    sec = sec_c if use_c else sec_np
-    sample = ("C restatement of the reference golden, %d threads, 2048-column panel scaled x%d (numpy restatement, full call: %.2f s)"
-              % (os.cpu_count() or 1, N // 2048, sec_np)) if use_c else (
-        "one full call of the numpy restatement of the reference golden (%.2f s%s)"
-        % (sec_np, "" if sec_c is None else "; C restatement on all cores: %.2f s" % sec_c))
-    return sec, {"value": ALGO_BYTES / sec / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample}
+def bf16_to_torch(torch, a):
+    import numpy as np
+
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16).copy()).view(torch.bfloat16)
 
 
 def to_np_bf16(t):
     import ml_dtypes
     import torch
 
-    return t.view(torch.int16).cpu().numpy().view(ml_dtypes.bfloat16)
+    return t.contiguous().view(torch.int16).cpu().numpy().view(ml_dtypes.bfloat16)
+
+
+def c2_device_sets(torch, dev, host, sets, col_begin, col_end, seed):
+    """Set 0 = the seeded host inputs (columns [col_begin, col_end)); sets 1.. = device-generated tensors of the same
+    distribution, only there to keep the rotation larger than L2."""
+    import numpy as np
+
+    hx, hw, hs, ho = host
+    x = bf16_to_torch(torch, hx).to(dev)
+    data = [(torch.from_numpy(np.ascontiguousarray(hw[:, col_begin // 8:col_end // 8])).to(dev),
+             bf16_to_torch(torch, hs[:, col_begin:col_end]).to(dev), bf16_to_torch(torch, ho[:, col_begin:col_end]).to(dev))]
+    n = col_end - col_begin
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    for _ in range(sets - 1):
+        words = torch.randint(-2 ** 31, 2 ** 31, (K, n // 8), generator=gen, device=dev, dtype=torch.int64).to(torch.int32)
+        scale = (torch.rand((K // G, n), generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
+        offset = (torch.rand((K // G, n), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
+        data.append((words, scale, offset))
+    return x, data
+
+
+def c2_cpu_once(host, cols, threads):
+    """One bounded sample of c2 on the host cores: the leading `cols` columns through the C restatement of the reference golden
+    (all `threads`), or through the numpy restatement when the C library is not there. Returns (seconds, y bf16 [16, cols], how)."""
+    import numpy as np
+
+    x, words, scale, offset = host
+    u16 = lambda a: np.ascontiguousarray(a).view(np.uint16)  # noqa: E731
+    try:
+        from oracle import c_oracle
+
+        c_oracle.lib()
+        t0 = time.perf_counter()
+        y = c_oracle.wq_w4a16_group(u16(x), words[:, :cols // 8], u16(scale[:, :cols]), u16(offset[:, :cols]), G, 0, cols, threads=threads)
+        return time.perf_counter() - t0, y.view(x.dtype), "C restatement of the reference golden, %d threads" % threads
+    except Exception:  # noqa: BLE001
+        from oracle import wqbmm_oracle
+
+        t0 = time.perf_counter()
+        w = wqbmm_oracle.unpack_int4_words(words[:, :cols // 8])
+        y = wqbmm_oracle.weight_quant_batch_matmul(x, w, scale[:, :cols], offset[:, :cols], None, G)
+        return time.perf_counter() - t0, y, "numpy restatement of the reference golden (BLAS threads)"
+
+
+C2_PANEL = 2048  # columns of the bounded CPU sample
+
+
+def c2_cpu_baseline(host, repeats=2):
+    threads = os.cpu_count() or 1
+    best, how = None, ""
+    for _ in range(repeats):
+        sec, _, how = c2_cpu_once(host, C2_PANEL, threads)
+        best = sec if best is None else min(best, sec)
+    full = best * (N / C2_PANEL)
+    return {"value": ALGO_BYTES / full / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "%s; columns [0, %d) of the seeded c2 inputs, time scaled x%d to the full width" % (how, C2_PANEL, N // C2_PANEL),
+            "seconds_per_full_call_extrapolated": full}
 
 
 def run_reference(args):
-    """CPU arm: the oracle port of the reference golden, all host cores numpy can use, on the same workload."""
+    """CPU arm: the oracle port of the reference golden on the host cores, same seeded inputs as the GPU arm's set 0; every step is
+    one bounded sample (a 2048-column panel); --steps / --warmup are honoured."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import ml_dtypes
-    import numpy as np
-
-    rng = np.random.default_rng(1002)
-    x = rng.standard_normal((M, K)).astype(np.float32).astype(ml_dtypes.bfloat16)
-    words = rng.integers(-2 ** 31, 2 ** 31, (K, N // 8), dtype=np.int64).astype(np.int32)
-    scale = rng.uniform(0.005, 0.02, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
-    offset = rng.uniform(-1, 1, (K // G, N)).astype(np.float32).astype(ml_dtypes.bfloat16)
-    for _ in range(min(args.warmup, 1)):
-        cpu_baseline_c2(x, words, scale, offset)
-    steps = max(1, min(args.steps, 3))
-    runs = [cpu_baseline_c2(x, words, scale, offset) for _ in range(steps)]
-    sec = sum(r[0] for r in runs) / len(runs)
-    gbs = ALGO_BYTES / sec / 1e9
-    base = dict(runs[-1][1], value=gbs)
-    line = {"impl": "reference", "metric": "W4A16 decode HBM GB/s (weight_quant_batch_matmul_v2, algorithmic bytes / time)",
-            "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
-            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": WORKLOAD_C2},
-            "cpu_baseline": base,
+    host = c2_host_inputs()
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        c2_cpu_once(host, C2_PANEL, threads)
+    secs, how = [], ""
+    for _ in range(args.steps):
+        s, _, how = c2_cpu_once(host, C2_PANEL, threads)
+        secs.append(s)
+    sec = sum(secs) / len(secs)
+    full = sec * (N / C2_PANEL)
+    gbs = ALGO_BYTES / full / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded numpy streams; shapes and value ranges of BASELINE config 2)",
+            "config": {"workload": WORKLOAD_C2},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                             "sample": "%s; each step = columns [0, %d) of the seeded c2 inputs (%.1f ms), ms_per_step and value scaled x%d "
+                                       "to the full width" % (how, C2_PANEL, sec * 1e3, N // C2_PANEL)},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line))
 
 
-QMM_WORKLOADS = {
+# ------------------------------------------------------------------------------------------------------------------
+# device timing helpers
+# ------------------------------------------------------------------------------------------------------------------
+
+def time_calls(torch, call, steps, warmup, barrier=None):
+    """Warm-up, then `steps` calls queued behind a ~15 ms spin kernel so that they run back to back; per-call CUDA events on the
+    launching stream plus one pair around the whole region. Returns dict(ms list sorted, avg, min, median, total_ms)."""
+    for i in range(max(warmup, 3)):
+        call(i)
+    (barrier or torch.cuda.synchronize)()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(30_000_000)
+    t0.record()
+    for i in range(steps):
+        evs[i][0].record()
+        call(i)
+        evs[i][1].record()
+    t1.record()
+    (barrier or torch.cuda.synchronize)()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return {"ms": ts, "avg": sum(ts) / len(ts), "min": ts[0], "median": ts[len(ts) // 2], "total_ms": t0.elapsed_time(t1)}
+
+
+def rel_err(got, ref, floor=0.05):
+    """max |got - ref| / max(|ref|, floor * rms(ref)) and the fraction of elements with isclose(rtol 1e-3, atol 1e-3)."""
+    import numpy as np
+
+    g, r = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(r ** 2))) if r.size else 0.0
+    den = np.maximum(np.abs(r), floor * rms + 1e-30)
+    return float(np.max(np.abs(g - r) / den)) if r.size else 0.0, float(np.mean(np.isclose(g, r, rtol=1e-3, atol=1e-3))) if r.size else 1.0
+
+
+def tensor_roofline(tflops, kind, bf16_peak, src):
+    """Tensor-bound roofline entry. The measured denominator is the cuBLAS bf16 burst figure scaled by the operand width (8-bit
+    operands issue at twice, 4-bit at four times the bf16 rate); the datasheet dense peak is quoted beside it."""
+    mult, sheet = {"int8": (2, 4500.0), "fp8": (2, 4500.0), "fp4": (4, 9000.0), "bf16": (1, 2250.0)}[kind]
+    peak = mult * bf16_peak
+    return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TOP/s" if kind == "int8" else "TFLOP/s",
+            "frac": tflops / peak, "frac_of_measured": tflops / peak, "frac_of_datasheet": tflops / sheet,
+            "peak_source": "%d x bf16_tflops burst, %s" % (mult, src), "datasheet_dense_peak": sheet, "traffic": None}
+
+
+def sample_idx(rng, total, count, block=1):
+    """`count` distinct indices of [0, total) as whole blocks of `block`, always including the first and the last block."""
+    import numpy as np
+
+    nb = total // block
+    want = max(2, count // block)
+    picks = {0, nb - 1}
+    picks.update(int(v) for v in rng.choice(nb, size=min(nb, want), replace=False)[:max(0, want - 2)])
+    blocks = np.array(sorted(picks), dtype=np.int64)
+    return (blocks[:, None] * block + np.arange(block)[None, :]).reshape(-1)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# the four other named configurations
+# ------------------------------------------------------------------------------------------------------------------
+
+def fp4_codes_to_np(packed_bytes):
+    """uint8 (.., c) two e2m1 codes per byte, low nibble first -> ml_dtypes float4_e2m1fn (.., 2c)."""
+    import ml_dtypes
+    import numpy as np
+
+    p = np.ascontiguousarray(packed_bytes)
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.uint8)
+    out[..., 0::2] = p & 0xF
+    out[..., 1::2] = p >> 4
+    return out.view(ml_dtypes.float4_e2m1fn)
+
+
+def run_c1(torch, dev, aclnn, args, peaks):
+    """int8 K-C, m128 k4096 n4096, per-token x per-channel fp32 scales, int32 bias, bf16 out: the correctness configuration
+    (latency bound, 18.4 MB per call). Inputs from numpy (seed 1001); 10 weight copies are rotated (168 MB > L2)."""
+    import numpy as np
+
+    from oracle import qbmm_oracle
+
+    m, k, n = 128, 4096, 4096
+    rng = np.random.default_rng(1001)
+    x1 = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+    tx1, ts1, ts2, tb = t(x1), t(s1), t(s2), t(bias)
+    gen = torch.Generator(device=dev).manual_seed(11001)
+    x2s = [t(x2)] + [torch.randint(-127, 128, (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(9)]
+    out = torch.full((m, n), -7777.0, dtype=torch.bfloat16, device=dev)
+    o32 = torch.full((m, n), -7777, dtype=torch.int32, device=dev)
+    d = [aclnn.from_torch(v) for v in (tx1, ts1, ts2, tb, out, o32)]
+    dx2 = [aclnn.from_torch(v) for v in x2s]
+    # parity: int32 accumulator (+ bias) and the bf16 output, whole tensors, bit for bit
+    aclnn.quant_matmul_v5(d[0], dx2[0], None, d[2], d[5], d[3])
+    aclnn.quant_matmul_v5(d[0], dx2[0], d[1], d[2], d[4], d[3])
+    torch.cuda.synchronize()
+    kernel = aclnn.last_kernel_name()
+    acc = qbmm_oracle.quant_matmul_v5(x1, x2, None, s2, bias, out_dtype="int32")
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, out_dtype="bfloat16")
+    acc_ok = bool(np.array_equal(o32.cpu().numpy(), acc))
+    out_ok = bool(np.array_equal(to_np_bf16(out).view(np.uint16), want.view(np.uint16)))
+    tm = time_calls(torch, lambda i: aclnn.quant_matmul_v5(d[0], dx2[i % 10], d[1], d[2], d[4], d[3]), args.steps, args.warmup)
+    nbytes = m * k + k * n + 4 * n + 4 * m + 4 * n + 2 * m * n
+    ops = 2.0 * m * k * n
+    sec = tm["avg"] * 1e-3
+    # CPU: the same call through the numpy restatement (int32 matmul through float64 BLAS, exact), whole problem
+    t0 = time.perf_counter()
+    qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, out_dtype="bfloat16")
+    cpu = time.perf_counter() - t0
+    hbm = peaks[0]
+    return {"workload": "c1: int8 K-C m128 k4096 n4096, fp32 per-token x per-channel scales, int32 bias, bf16 out",
+            "ms_per_step": tm["avg"], "ms_median": tm["median"], "ms_min": tm["min"], "value": ops / sec / 1e12, "unit": "TOP/s",
+            "kernels": [kernel],
+            "roofline": {"bound": "hbm", "achieved": nbytes / sec / 1e9, "peak": hbm, "unit": "GB/s", "frac": nbytes / sec / 1e9 / hbm,
+                         "frac_of_measured": nbytes / sec / 1e9 / hbm, "frac_of_datasheet": nbytes / sec / 1e9 / 8000.0,
+                         "algorithmic_bytes_per_launch": nbytes, "peak_source": "hbm_gbs, " + peaks[2], "traffic": None,
+                         "note": "latency bound: 32 serial k-blocks on 128 CTAs; reported for completeness"},
+            "parity": {"checked_elems": 2 * m * n, "int32_accumulator_bit_exact": acc_ok, "bf16_output_bit_exact": out_ok,
+                       "max_rel_err": 0.0 if out_ok else None, "ok": acc_ok and out_ok},
+            "cpu_baseline": {"value": ops / cpu / 1e12, "unit": "TOP/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": "one full call of the numpy restatement of the reference golden (%.2f s)" % cpu},
+            "l2": "10 weight copies rotated (168 MB > 126 MB L2)"}
+
+
+def quant_perblock_torch(torch, xf, row_block):
+    """scale = amax / 448 per (row_block x 128) block, q = e4m3(x / scale) (the recipe of quant/dynamic_block_quant's golden)."""
+    r, c = xf.shape
+    v = xf.view(r // row_block, row_block, c // 128, 128)
+    amax = v.abs().amax(dim=(1, 3))
+    scale = (amax / 448.0).clamp_min(1e-30)
+    q = (v / scale[:, None, :, None]).clamp(-448.0, 448.0).view(r, c).to(torch.float8_e4m3fn)
+    return q, scale.contiguous()
+
+
+def run_c3(torch, dev, aclnn, args, peaks, rank, world, dist):
+    """fp8 e4m3 per-block (G-B): x [4096, 7168] scales per 1x128, weight [7168, 18432] scales per 128x128, bf16 out, no bias.
+    N-sharded: rank r owns n/world columns of the weight and of its scales; x and its scales are replicated."""
+    import ml_dtypes
+    import numpy as np
+
+    from oracle import qbmm_oracle
+
+    shard = load_package().shard
+    m, k, n = 4096, 7168, 18432
+    cb, ce = shard.split_range(n, world, rank, 128)
+    nl = ce - cb
+    gen = torch.Generator(device=dev).manual_seed(1003)
+    x1, s1 = quant_perblock_torch(torch, torch.randn((m, k), generator=gen, device=dev), 1)
+    wsets = []
+    for i in range(2):  # the two weight sets are generated whole so that every world size sees the same global problem
+        wq, sw = quant_perblock_torch(torch, torch.randn((k, n), generator=gen, device=dev), 128)
+        wsets.append((wq[:, cb:ce].contiguous(), sw[:, cb // 128:ce // 128].contiguous()))
+        del wq, sw
+    out = torch.full((m, nl), -7777.0, dtype=torch.bfloat16, device=dev)
+    d1, ds1, dout = aclnn.from_torch(x1), aclnn.from_torch(s1), aclnn.from_torch(out)
+    dw = [(aclnn.from_torch(a), aclnn.from_torch(b)) for a, b in wsets]
+    call = lambda i: aclnn.quant_matmul_v5(d1, dw[i % 2][0], ds1, dw[i % 2][1], dout, None, False, False, PB_GROUP)  # noqa: E731
+    call(0)
+    torch.cuda.synchronize()
+    kernel = aclnn.last_kernel_name()
+    # parity on sampled rows x whole 128-column blocks of this rank's shard
+    rng = np.random.default_rng(3003 + rank)
+    rows, cols = sample_idx(rng, m, 128), sample_idx(rng, nl, 1024, 128)
+    rt, ct = torch.from_numpy(rows).to(dev), torch.from_numpy(cols).to(dev)
+    f8 = lambda tt: tt.contiguous().view(torch.uint8).cpu().numpy().view(ml_dtypes.float8_e4m3fn)  # noqa: E731
+    a_s, b_s = f8(x1[rt]), f8(wsets[0][0][:, ct])
+    s1_s = s1[rt].cpu().numpy()
+    s2_s = wsets[0][1][:, torch.from_numpy(cols // 128).to(dev)].cpu().numpy()  # one scale column per sampled weight column
+    ref = qbmm_oracle.compute_perblock(a_s, b_s, s1_s, s2_s, (1, 1, 128), False, False, "float32")
+    got = to_np_bf16(out[rt][:, ct]).astype(np.float32)
+    err, close = rel_err(got, ref)
+    unwritten = bool((out == -7777.0).any().item())
+    tm = time_calls(torch, call, args.steps, args.warmup, barrier=dist_barrier(torch, dist))
+    res = {"tm": tm, "kernel": kernel, "flops_global": 2.0 * m * k * n, "shard": [cb, ce],
+           "parity": {"checked_elems": int(ref.size), "max_rel_err": err, "tol": 1e-2, "frac_isclose_rtol1e-3": close,
+                      "unwritten_elems": unwritten, "ok": bool(err <= 1e-2 and not unwritten)}}
+    if rank == 0 and not args.no_cpu_baseline:
+        # CPU: a 512-row panel against this rank's whole weight shard (world 1: the whole weight)
+        pr = 512
+        a_p, s1_p = f8(x1[:pr]), s1[:pr].cpu().numpy()
+        b_p, s2_p = f8(wsets[0][0]), wsets[0][1].cpu().numpy()
+        t0 = time.perf_counter()
+        qbmm_oracle.compute_perblock(a_p, b_p, s1_p, s2_p, (1, 128, 128), False, False, "bfloat16")
+        cpu = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": 2.0 * pr * k * nl / cpu / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": "numpy restatement of the reference golden on rows [0, 512) x %d columns (%.2f s); rate, not "
+                                         "extrapolated time" % (nl, cpu)}
+    res["gather"] = (lambda: shard.gather_columns(out, n, world, rank, 128)) if world > 1 else None
+    res["keep"] = (x1, s1, wsets, out)
+    return res
+
+
+def mx_quant_dev(torch, aclnn, src_bf16, dst, axis=-1):
+    """Quantises a bf16 device tensor with the library's dynamic MX quantiser (bit-identical to the reference golden on the committed
+    fixtures): returns (payload uint8, e8m0 scale bytes uint8) in the layouts aclnnQuantMatmulV5 takes."""
+    shp = list(src_bf16.shape)
+    ax = axis if axis >= 0 else len(shp) + axis
+    groups = -(-shp[ax] // 64)
+    sshape = shp[:ax] + [groups] + shp[ax + 1:] + [2]
+    pshape = list(shp)
+    if dst == "float4_e2m1":
+        pshape[-1] //= 2
+    y = torch.empty(pshape, dtype=torch.uint8, device=src_bf16.device)
+    sc = torch.empty(sshape, dtype=torch.uint8, device=src_bf16.device)
+    aclnn.dynamic_mx_quant(aclnn.from_torch(src_bf16), aclnn.from_torch(y, dst, tuple(shp), None) if dst == "float4_e2m1"
+                           else aclnn.from_torch(y, dst), aclnn.from_torch(sc, "float8_e8m0"), dst, axis=axis)
+    return y, sc
+
+
+def dist_barrier(torch, dist):
+    def f():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+    return f
+
+
+def run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, which):
+    """c4: MXFP4 both operands, batch 8, m = k = n = 8192, weight stored (k, n) as the configuration states (and, second figure,
+    stored (n, k) with transposeX2). c5: bf16 activations [32, 2048, 4096] with 0.1 % outliers x50 quantised on the fly to MXFP8
+    (aclnnDynamicMxQuant) + MXFP8 matmul against pre-quantised weights [32, 4096, 14336] + bias. Batch-sharded across ranks."""
+    import ml_dtypes
+    import numpy as np
+
+    from oracle import mx_quant_oracle, qbmm_oracle
+
+    shard = load_package().shard
+    f4 = which == "c4"
+    B, m, k, n = (8, 8192, 8192, 8192) if f4 else (32, 2048, 4096, 14336)
+    if args.batch > 0 and args.workload == which:
+        B = args.batch
+    bb, be = shard.split_range(B, world, rank)
+    b = be - bb
+    dst = "float4_e2m1" if f4 else "float8_e4m3fn"
+    gen = torch.Generator(device=dev).manual_seed((1004 if f4 else 1005) * 1000 + rank)
+    act = torch.randn((b, m, k), generator=gen, device=dev, dtype=torch.bfloat16)
+    if not f4:
+        idx = torch.randint(0, act.numel(), (act.numel() // 1000,), generator=gen, device=dev)
+        act.view(-1)[idx] *= 50  # 0.1 % outliers x50
+    wsrc = torch.randn((b, k, n), generator=gen, device=dev, dtype=torch.bfloat16)
+    if not f4:
+        wsrc.mul_(0.02)
+    x2, s2 = mx_quant_dev(torch, aclnn, wsrc, dst, axis=-2)       # stored (k, n): scale (b, k/64, n, 2)
+    wt = wsrc.transpose(1, 2).contiguous()
+    del wsrc
+    x2t, s2t = mx_quant_dev(torch, aclnn, wt, dst, axis=-1)        # the same weight stored (n, k): scale (b, n, k/64, 2)
+    del wt
+    x1, s1 = mx_quant_dev(torch, aclnn, act, dst, axis=-1)
+    bias = None if f4 else torch.randn((n,), generator=torch.Generator(device=dev).manual_seed(5005), device=dev, dtype=torch.float32)
+    out = torch.full((b, m, n), -7777.0, dtype=torch.bfloat16, device=dev)
+    lg = lambda t_, last: aclnn.from_torch(t_, dst, tuple(t_.shape[:-1]) + (last,), None) if f4 else aclnn.from_torch(t_, dst)  # noqa: E731
+    d_x1, d_s1, d_out = lg(x1, k), aclnn.from_torch(s1, "float8_e8m0"), aclnn.from_torch(out)
+    d_x2, d_s2 = lg(x2, n), aclnn.from_torch(s2, "float8_e8m0")
+    d_x2t, d_s2t = lg(x2t, k), aclnn.from_torch(s2t, "float8_e8m0")
+    d_bias = None if bias is None else aclnn.from_torch(bias)
+    d_act = aclnn.from_torch(act)
+    kernels = []
+
+    def quant():
+        aclnn.dynamic_mx_quant(d_act, d_x1, d_s1, dst)
+
+    def mm(transposed, bias_desc=d_bias):
+        if transposed:
+            aclnn.quant_matmul_v5(d_x1, d_x2t, d_s1, d_s2t, d_out, bias_desc, False, True, MX_GROUP)
+        else:
+            aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, d_out, bias_desc, False, False, MX_GROUP)
+
+    def step(i, transposed=False):
+        if not f4:
+            quant()  # c5: the activations are quantised on the fly, every step
+        mm(transposed)
+
+    # ---- parity (weight stored (k, n), the layout the configuration names), first and last batch of the shard ----
+    if not f4:
+        quant()
+        kernels.append(aclnn.last_kernel_name())
+    mm(False)
+    torch.cuda.synchronize()
+    kernels.append(aclnn.last_kernel_name())
+    rng = np.random.default_rng((4004 if f4 else 5005) + rank)
+    np_dt = ml_dtypes.float4_e2m1fn if f4 else ml_dtypes.float8_e4m3fn
+    e8 = lambda tt: tt.contiguous().cpu().numpy().view(ml_dtypes.float8_e8m0fnu)  # noqa: E731
+
+    def payload(tt):
+        a = tt.contiguous().cpu().numpy()
+        return fp4_codes_to_np(a) if f4 else a.view(np_dt)
+
+    def check(bias_t, tag):
+        worst, checked, closes, quant_ok = 0.0, 0, [], True
+        for bi in sorted({0, b - 1}):
+            rows, cols = sample_idx(rng, m, 64), sample_idx(rng, n, 256, 2)
+            rt, ct = torch.from_numpy(rows).to(dev), torch.from_numpy(cols).to(dev)
+            a_s, sa = payload(x1[bi][rt]), e8(s1[bi][rt])
+            if f4:
+                pc = torch.from_numpy(np.unique(cols // 2)).to(dev)  # packed along n: the bytes that hold the sampled column pairs
+                b_s = payload(x2[bi][:, pc])
+            else:
+                b_s = payload(x2[bi][:, ct])
+            sb = e8(s2[bi][:, ct])
+            bias_np = None if bias_t is None else bias_t.float().cpu().numpy()[cols]
+            ref = qbmm_oracle.compute_mx(a_s, b_s, sa, sb, bias_np, False, False, "float32")
+            got = to_np_bf16(out[bi][rt][:, ct]).astype(np.float32)
+            err, close = rel_err(got, ref)
+            worst, checked = max(worst, err), checked + int(ref.size)
+            closes.append(close)
+            if not f4:  # the on-the-fly quantiser against its oracle, bit for bit, on the sampled rows
+                yq, sq = mx_quant_oracle.dynamic_mx_quant(to_np_bf16(act[bi][rt]), "float8_e4m3fn")
+                quant_ok = quant_ok and bool(np.array_equal(yq.view(np.uint8), a_s.view(np.uint8))) and bool(
+                    np.array_equal(sq.reshape(sa.shape).view(np.uint8), sa.view(np.uint8)))
+        return {"bias": tag, "checked_elems": checked, "max_rel_err": worst, "frac_isclose_rtol1e-3": min(closes), "quantiser_bit_exact": quant_ok}
+
+    unwritten = bool((out == -7777.0).any().item())
+    checks = [check(bias, "none" if f4 else "float32")]
+    if not f4:  # the configuration names a bf16 bias: accepted as an extension, checked here, not timed separately
+        bias16 = bias.to(torch.bfloat16)
+        mm(False, aclnn.from_torch(bias16))
+        torch.cuda.synchronize()
+        checks.append(check(bias16, "bfloat16"))
+    worst = max(c_["max_rel_err"] for c_ in checks)
+    parity = {"checked_elems": sum(c_["checked_elems"] for c_ in checks), "max_rel_err": worst, "tol": 1e-2,
+              "frac_isclose_rtol1e-3": min(c_["frac_isclose_rtol1e-3"] for c_ in checks), "unwritten_elems": unwritten, "cases": checks,
+              "ok": bool(worst <= 1e-2 and not unwritten and all(c_["quantiser_bit_exact"] for c_ in checks))}
+    barrier = dist_barrier(torch, dist)
+    tm = time_calls(torch, lambda i: step(i, False), args.steps, args.warmup, barrier=barrier)
+    tm_t = time_calls(torch, lambda i: step(i, True), args.steps, args.warmup, barrier=barrier)
+    res = {"tm": tm, "tm_weight_nk": tm_t, "kernel": kernels, "flops_global": 2.0 * B * m * k * n, "shard": [bb, be], "parity": parity}
+    if rank == 0 and not args.no_cpu_baseline:
+        # CPU: batch 0, a 512-row panel against the whole weight of that batch (c5: the quantiser oracle on the panel first)
+        pr = 512
+        rows_np = to_np_bf16(act[0][:pr])
+        b_p, sb_p = payload(x2[0]), e8(s2[0])
+        a_p, sa_p = payload(x1[0][:pr]), e8(s1[0][:pr])
+        bias_np = None if bias is None else bias.cpu().numpy()
+        t0 = time.perf_counter()
+        if not f4:
+            mx_quant_oracle.dynamic_mx_quant(rows_np, "float8_e4m3fn")
+        qbmm_oracle.compute_mx(a_p, b_p, sa_p, sb_p, bias_np, False, False, "bfloat16")
+        cpu = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": 2.0 * pr * k * n / cpu / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": "numpy restatement of the reference golden%s on batch 0, rows [0, 512) x all %d columns (%.2f s); "
+                                         "rate, not extrapolated time" % ("" if f4 else " (quantiser + matmul)", n, cpu)}
+    res["gather"] = (lambda: shard.gather_batch(out, B, world, rank)) if world > 1 else None
+    res["keep"] = (act, x1, s1, x2, s2, x2t, s2t, bias, out)
+    return res
+
+
+def finish_tensor_workload(torch, dist, dev, res, kind, desc, peaks, world, args, extra_note=None):
+    """Max over ranks of the timings, global T(FL)OP/s, roofline, optional gather timing; returns the JSON entry (rank 0)."""
+    keys = ["tm"] + (["tm_weight_nk"] if "tm_weight_nk" in res else [])
+    vals = []
+    for kname in keys:
+        vals += [res[kname]["avg"], res[kname]["median"], res[kname]["min"]]
+    gather_ms = None
+    if res.get("gather") is not None:
+        barrier = dist_barrier(torch, dist)
+        for _ in range(2):
+            res["gather"]()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            res["gather"]()
+        e1.record()
+        barrier()
+        gather_ms = e0.elapsed_time(e1) / reps
+        vals.append(gather_ms)
+    ok = 1.0 if res["parity"]["ok"] else 0.0
+    if dist is not None:
+        t = torch.tensor(vals, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        vals = [float(v) for v in t.tolist()]
+        o = torch.tensor([ok], device=dev, dtype=torch.float64)
+        dist.all_reduce(o, op=dist.ReduceOp.MIN)
+        ok = float(o.item())
+    avg, med, mn = vals[0], vals[1], vals[2]
+    tf = res["flops_global"] / (avg * 1e-3) / 1e12
+    entry = {"workload": desc, "ms_per_step": avg, "ms_median": med, "ms_min": mn, "value": tf,
+             "unit": "TOP/s" if kind == "int8" else "TFLOP/s", "kernels": res["kernel"] if isinstance(res["kernel"], list) else [res["kernel"]],
+             "roofline": tensor_roofline(tf, kind, peaks[1], peaks[2]), "parity": dict(res["parity"], ok=bool(ok >= 1.0), ranks_checked=world),
+             "cpu_baseline": res.get("cpu_baseline"), "sharding": "rank 0 of %d holds [%d, %d)" % (world, res["shard"][0], res["shard"][1])}
+    if "tm_weight_nk" in res:
+        tft = res["flops_global"] / (vals[3] * 1e-3) / 1e12
+        entry["weight_stored_nk"] = {"ms_per_step": vals[3], "ms_min": vals[5], "value": tft, "frac_of_measured": tft / entry["roofline"]["peak"],
+                                     "frac_of_datasheet": tft / entry["roofline"]["datasheet_dense_peak"],
+                                     "note": "same problem with x2 stored (n, k) and transposeX2 = true (no per-call re-layout of the weight)"}
+    if gather_ms is not None:
+        g = vals[-1]
+        entry["with_gather"] = {"gather_ms": g, "ms_per_step": avg + g, "value": res["flops_global"] / ((avg + g) * 1e-3) / 1e12,
+                                "note": "all ranks receive the whole output (torch.distributed all_gather_into_tensor over NCCL + re-assembly), timed "
+                                        "separately after the matmul"}
+    if extra_note:
+        entry["note"] = extra_note
+    return entry
+
+
+QMM_WORKLOADS = ("c1", "c3", "c4", "c5")
+
+
+def run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names):
+    out = {}
+    for name in names:
+        try:
+            if name == "c1":
+                if rank == 0:
+                    out["c1"] = run_c1(torch, dev, aclnn, args, peaks)
+                if dist is not None:
+                    dist.barrier()
+                continue
+            if name == "c3":
+                res = run_c3(torch, dev, aclnn, args, peaks, rank, world, dist)
+                entry = finish_tensor_workload(torch, dist, dev, res, "fp8",
+                                               "c3: fp8 e4m3 per-block m4096 k7168 n18432 (scales 1x128 / 128x128, amax/448), bf16 out, weight stored (k,n)",
+                                               peaks, world, args)
+            else:
+                res = run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, name)
+                if name == "c4":
+                    entry = finish_tensor_workload(torch, dist, dev, res, "fp4",
+                                                   "c4: MXFP4 x MXFP4 batch 8, m = k = n = 8192, e8m0 per 32 along k, bf16 out, weight stored (k,n): "
+                                                   "transposed k-contiguous into workspace by a pre-pass inside the timed call", peaks, world, args)
+                else:
+                    entry = finish_tensor_workload(torch, dist, dev, res, "fp8",
+                                                   "c5: bf16 activations [32, 2048, 4096] (0.1 % outliers x50) quantised on the fly to MXFP8 "
+                                                   "(aclnnDynamicMxQuant, inside the timed step) + MXFP8 matmul, weight [32, 4096, 14336] stored "
+                                                   "(k,n), fp32 bias, bf16 out", peaks, world, args,
+                                                   "flops count the matmul only; the quantiser's bytes (537 MB read, 277 MB written) are inside the time")
+            res.clear()
+            torch.cuda.empty_cache()
+            if rank == 0:
+                out[name] = entry
+        except Exception as exc:  # noqa: BLE001 - a secondary workload must never take the contract line down
+            if rank == 0:
+                out[name] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+            try:
+                torch.cuda.empty_cache()
+            except Exception:  # noqa: BLE001
+                pass
+    return out
+
+
+DEV_WORKLOADS = {
     # name: (batch, m, k, n, kind)
-    "c1": (1, 128, 4096, 4096, "int8_kc"),
-    "c3": (1, 4096, 7168, 18432, "fp8_perblock"),
     "c3i8": (1, 4096, 7168, 18432, "int8_kc"),
     "c3i8pb": (1, 4096, 7168, 18432, "int8_perblock"),  # int8 operands with the 1x128 / 128x128 fp32 scales of c3
     "c3t": (1, 4096, 7168, 18432, "fp8_perblock_t"),    # c3 with x2 stored (n,k), transposeX2 = true
     "c3i8pbt": (1, 4096, 7168, 18432, "int8_perblock_t"),
     "c1t": (1, 128, 4096, 4096, "int8_kc_t"),      # same with x2 stored (n,k) and transposeX2 = true
     "c3i8t": (1, 4096, 7168, 18432, "int8_kc_t"),
-    "c4": (8, 8192, 8192, 8192, "mxfp4"),           # both operands e2m1 + e8m0/32, x2 stored (n,k) with transposeX2 = true
     "c4s": (2, 4096, 4096, 4096, "mxfp4"),          # small form of c4 (profiling)
     "c4n": (8, 8192, 8192, 8192, "mxfp4_n"),        # c4 with the weight stored (k,n): transposed into workspace by a pre-pass
-    "c5": (32, 2048, 4096, 14336, "mxfp8_dq"),      # bf16 activations -> dynamic mx quant -> mxfp8 matmul + fp32 bias
     "c5s": (4, 2048, 4096, 4096, "mxfp8_dq"),
     "c5mm": (32, 2048, 4096, 14336, "mxfp8"),       # the matmul of c5 alone (activations pre-quantised)
     "c5w": (1, 65536, 4096, 14336, "mxfp8"),        # c5mm's rows against ONE weight stored (k,n): the weight is moved k-contiguous first
@@ -220,14 +703,14 @@ QMM_WORKLOADS = {
 }
 
 
-def run_qmm_workload(args):
-    """Secondary workloads (`--workload c1|c3|c3i8`): aclnnQuantMatmulV5 timed on device, TFLOPS against the measured bf16
-    GEMM ceiling x2 (8-bit operands) and the datasheet dense peak. Same timing discipline as the headline workload."""
+def run_dev_workload(args):
+    """Development shapes (`--workload NAME` with NAME from DEV_WORKLOADS): variants of the named configurations (other layouts, small forms
+    for profiler captures, pre-pass experiments) with random operand bytes and random scale bytes; timing only, no parity, one GPU."""
     import torch
 
     aclnn = load_package().aclnn
     dev = torch.device("cuda", 0)
-    b, m, k, n, kind = QMM_WORKLOADS[args.workload]
+    b, m, k, n, kind = DEV_WORKLOADS[args.workload]
     gen = torch.Generator(device=dev).manual_seed(1001)
     sets = max(2, min(8, int(300e6 // (k * n)) + 1))  # rotate weights so they do not sit in L2
     out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
@@ -332,7 +815,8 @@ def run_qmm_workload(args):
         call(i)
         evs[i][1].record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    sampler.stop()
+    clocks = sampler.summary()
     ts = sorted(a.elapsed_time(b_) for a, b_ in evs)
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
@@ -344,20 +828,26 @@ def run_qmm_workload(args):
                       "hbm_gbs_on_algorithmic_bytes": nbytes / (ms * 1e-3) / 1e9, "clocks": clocks, "weight_sets": sets}))
 
 
+
+# ------------------------------------------------------------------------------------------------------------------
+# the contract line
+# ------------------------------------------------------------------------------------------------------------------
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--workload", default="all", help="all (contract line), c2 (contract line without the other shapes), or one of c1 c3 c4 c5")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sets", type=int, default=4, help="distinct weight sets rotated through (L2 defeat)")
+    ap.add_argument("--sets", type=int, default=4, help="distinct c2 weight sets rotated through (L2 defeat)")
+    ap.add_argument("--batch", type=int, default=0, help="c4 / c5 as a single workload: batch count override (small forms for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    if args.workload in QMM_WORKLOADS:
-        return run_qmm_workload(args)
+    if args.workload in DEV_WORKLOADS:
+        return run_dev_workload(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -365,103 +855,132 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this library has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    aclnn = load_package().aclnn
-    aclnn.lib()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
 
-    x, data = make_inputs(torch, dev, 1002 + rank, args.sets)
-    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+    pkg = load_package()
+    aclnn, shard = pkg.aclnn, pkg.shard
+    aclnn.lib()
+    peaks = measured_peaks()
+    barrier = dist_barrier(torch, dist)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    if args.workload in QMM_WORKLOADS:  # single secondary line
+        entry = run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, [args.workload])
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps(dict(entry[args.workload], metric="QBMM TFLOPS", n_gpus=world, steps=args.steps, clocks=sampler.summary())))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- c2, sharded along n: rank r owns columns [cb, ce) of the seeded global problem ----
+    host = c2_host_inputs()
+    cb, ce = shard.split_range(N, world, rank, 512)
+    nl = ce - cb
+    x, data = c2_device_sets(torch, dev, host, args.sets, cb, ce, 2002 + rank)
+    y = torch.full((M, nl), -7777.0, dtype=torch.bfloat16, device=dev)
     d_x, d_y = aclnn.from_torch(x), aclnn.from_torch(y)
     descs = [(aclnn.from_torch(w), aclnn.from_torch(s), aclnn.from_torch(o)) for (w, s, o) in data]
     ws_bytes = aclnn.weight_quant_batch_matmul(d_x, descs[0][0], descs[0][1], d_y, descs[0][2], None, G)
     workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
     kernel_name = aclnn.last_kernel_name()
+    torch.cuda.synchronize()
+    y_default = y.clone()
 
-    def step(i):
+    def step(i, ip=None, yd=d_y, xd=d_x):
         w, s, o = descs[i % len(descs)]
-        aclnn.weight_quant_batch_matmul(d_x, w, s, d_y, o, None, G, workspace=workspace)
+        aclnn.weight_quant_batch_matmul(xd, w, s, yd, o, None, G, inner_precise=ip, workspace=workspace)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    # ---- parity of this rank's shard against the oracle: 512 sampled columns of set 0, default mode and innerPrecise = 1 ----
+    import numpy as np
 
-    # ---- device-resident timing ----
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    launches0 = aclnn.launch_count()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    # park the GPU on a ~30 ms spin so that every launch of the timed region is already queued when it starts:
-    # the 20 us kernels are then timed back to back, not the Python loop that enqueues them
-    torch.cuda._sleep(60_000_000)
-    t_begin.record()
-    for i in range(args.steps):
-        evs[i][0].record()
-        step(i)
-        evs[i][1].record()
-    t_end.record()
-    barrier()
-    launches = aclnn.launch_count() - launches0
-    total_ms = t_begin.elapsed_time(t_end)
-    per_launch_ms = sorted(a.elapsed_time(b) for a, b in evs)
-    kernel_ms = sum(per_launch_ms) / len(per_launch_ms)
+    from oracle import wqbmm_oracle
 
-    # ---- the same workload in the API's high-performance precision mode (innerPrecise = 1), device resident ----
-    def step_hp(i):
-        w, s, o = descs[i % len(descs)]
-        aclnn.weight_quant_batch_matmul(d_x, w, s, d_y, o, None, G, inner_precise=1, workspace=workspace)
-
-    for i in range(args.warmup):
-        step_hp(i)
+    rng = np.random.default_rng(77 + rank)
+    cols = np.sort(rng.choice(nl, min(512, nl), replace=False))
+    hx, hw, hs, ho = host
+    gcols = cb + cols  # global column numbers; nibble j of a word is column 8 c + j
+    w_cols = (((hw[:, gcols // 8].view(np.uint32) >> (4 * (gcols % 8)).astype(np.uint32)[None, :]) & 0xF).astype(np.int8) ^ 8) - 8
+    want = wqbmm_oracle.weight_quant_batch_matmul(hx, w_cols, hs[:, cb:ce][:, cols], ho[:, cb:ce][:, cols], None, G).astype(np.float64)
+    ref64 = wqbmm_oracle.fp32_dequant_product(hx, w_cols, hs[:, cb:ce][:, cols], ho[:, cb:ce][:, cols], None, G)
+    ct = torch.from_numpy(cols).to(dev)
+    got = to_np_bf16(y_default[:, ct]).astype(np.float64)
+    rms = float(np.sqrt(np.mean(want ** 2)))
+    ulp_ok = bool(np.all(np.abs(got - want) <= 2.0 ** -7 * np.maximum(np.abs(want), 0.05 * rms) * 1.01))
+    err_default, _ = rel_err(got, ref64)
+    step(0, ip=1)
+    torch.cuda.synchronize()
     hp_kernel = aclnn.last_kernel_name()
-    barrier()
-    hp_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    torch.cuda._sleep(60_000_000)
-    for i in range(args.steps):
-        hp_evs[i][0].record()
-        step_hp(i)
-        hp_evs[i][1].record()
-    barrier()
-    hp_ms = sorted(a.elapsed_time(b) for a, b in hp_evs)
-    hp_kernel_ms = sum(hp_ms) / len(hp_ms)
+    err_hp, _ = rel_err(to_np_bf16(y[:, ct]).astype(np.float64), ref64)
+    unwritten = bool((y_default == -7777.0).any().item())
+    parity = {"checked_elems": int(2 * want.size), "default_mode_within_1ulp_of_golden": ulp_ok, "max_rel_err": err_default,
+              "max_rel_err_inner_precise_1": err_hp, "tol": 1e-2, "unwritten_elems": unwritten,
+              "ok": bool(ulp_ok and err_default <= 1e-2 and err_hp <= 1e-2 and not unwritten),
+              "note": "512 sampled columns of weight set 0 on every rank; max_rel_err against the fp32 dequantised product (float64 accumulate)"}
+
+    # ---- device-resident timing, default precision mode (the contract value) ----
+    launches0 = aclnn.launch_count()
+    mark0 = sampler.mark()
+    tm = time_calls(torch, step, args.steps, args.warmup, barrier=barrier)
+    launches = aclnn.launch_count() - launches0 - max(args.warmup, 3)
+    tm_hp = time_calls(torch, lambda i: step(i, ip=1), args.steps, args.warmup, barrier=barrier)
+    # optional gather of the y shards (strong scaling, N > 1)
+    gather_ms = None
+    if world > 1:
+        for _ in range(3):
+            shard.gather_columns(y, N, world, rank, 512)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+            shard.gather_columns(y, N, world, rank, 512)
+        e1.record()
+        barrier()
+        gather_ms = e0.elapsed_time(e1) / args.steps
+    # a sustained stretch of the same kernel (untimed) so that the clock sampler sees the GPU under this load
+    mark_load = sampler.mark()
+    t_end = time.perf_counter() + 0.6
+    while time.perf_counter() < t_end:
+        for i in range(50):
+            step(i)
+        torch.cuda.synchronize()
+    mark_load_end = sampler.mark()
 
     # ---- end to end from host buffers (x H2D + call + y D2H per step) ----
-    hx = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
-    hx.copy_(x.cpu())
-    hy = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
-    hw = [t.cpu().pin_memory() for t in data[0]]
+    hx_p = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
+    hx_p.copy_(x.cpu())
+    hy_p = torch.empty((M, nl), dtype=torch.bfloat16).pin_memory()
+    hw_p = [t.cpu().pin_memory() for t in data[0]]
     barrier()
     tu0 = time.perf_counter()
-    for dst, src in zip(data[0], hw):
+    for dst, src in zip(data[0], hw_p):
         dst.copy_(src, non_blocking=True)
     torch.cuda.synchronize()
     weight_upload_ms = (time.perf_counter() - tu0) * 1e3
-    e2e_steps = max(10, args.steps // 4)
+    e2e_steps = max(10, args.steps)
     for i in range(3):
-        x.copy_(hx, non_blocking=True)
+        x.copy_(hx_p, non_blocking=True)
         step(i)
-        hy.copy_(y, non_blocking=True)
+        hy_p.copy_(y, non_blocking=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(e2e_steps):
-        x.copy_(hx, non_blocking=True)
+        x.copy_(hx_p, non_blocking=True)
         step(i)
-        hy.copy_(y, non_blocking=True)
+        hy_p.copy_(y, non_blocking=True)
     e1.record()
     barrier()
     e2e_serial_ms = e0.elapsed_time(e1) / e2e_steps
@@ -470,27 +989,22 @@ def main():
     # computes; two buffers of each, ordered by events). Every step still copies its x from pinned host memory and its y
     # back, inside the timed region; the host enqueues in real time, nothing is parked.
     s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    xb = [x, torch.empty_like(x)]
-    yb = [y, torch.empty_like(y)]
-    hyb = [hy, torch.empty_like(hy).pin_memory()]
-    dxb = [aclnn.from_torch(t) for t in xb]
-    dyb = [aclnn.from_torch(t) for t in yb]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_cmp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    xb, yb = [x, torch.empty_like(x)], [y, torch.empty_like(y)]
+    hyb = [hy_p, torch.empty_like(hy_p).pin_memory()]
+    dxb, dyb = [aclnn.from_torch(t) for t in xb], [aclnn.from_torch(t) for t in yb]
+    ev_in, ev_cmp, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
 
     def pipelined(nsteps):
         for i in range(nsteps):
             b = i & 1
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_cmp[b])  # the step that last read this x buffer
-                xb[b].copy_(hx, non_blocking=True)
+                xb[b].copy_(hx_p, non_blocking=True)
                 ev_in[b].record(s_in)
             with torch.cuda.stream(s_cmp):
                 s_cmp.wait_event(ev_in[b])
                 s_cmp.wait_event(ev_out[b])  # the copy that last read this y buffer
-                w, sc, of = descs[i % len(descs)]
-                aclnn.weight_quant_batch_matmul(dxb[b], w, sc, dyb[b], of, None, G, workspace=workspace)
+                step(i, yd=dyb[b], xd=dxb[b])
                 ev_cmp[b].record(s_cmp)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_cmp[b])
@@ -507,54 +1021,97 @@ def main():
     p1.record(s_out)
     barrier()
     e2e_pipe_ms = p0.elapsed_time(p1) / e2e_steps
-    e2e_ms = min(e2e_serial_ms, e2e_pipe_ms)
-    clocks = sampler.stop() if rank == 0 else None  # sampled from before the first timed launch to after the last timed copy
+    mark1 = sampler.mark()
 
+    vals = [tm["total_ms"], tm["avg"], tm["min"], tm["median"], tm_hp["avg"], tm_hp["min"], e2e_serial_ms, e2e_pipe_ms,
+            gather_ms if gather_ms is not None else 0.0]
+    par_ok = 1.0 if parity["ok"] else 0.0
     if dist is not None:
-        t = torch.tensor([total_ms, kernel_ms, e2e_ms, hp_kernel_ms, e2e_serial_ms, e2e_pipe_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor(vals, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, kernel_ms, e2e_ms, hp_kernel_ms, e2e_serial_ms, e2e_pipe_ms = [float(v) for v in t.tolist()]
+        vals = [float(v) for v in t.tolist()]
         lt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(lt)
         launches = int(lt.item())
+        o = torch.tensor([par_ok], device=dev, dtype=torch.float64)
+        dist.all_reduce(o, op=dist.ReduceOp.MIN)
+        par_ok = float(o.item())
+    total_ms, kernel_ms, kernel_min, kernel_med, hp_ms, hp_min, e2e_serial_ms, e2e_pipe_ms, gather_all_ms = vals
+
+    # ---- N > 1: the former weak-scaling figure (every rank a full-width shard) as a secondary key ----
+    weak = None
+    if world > 1:
+        xw, dataw = c2_device_sets(torch, dev, host, 2, 0, N, 3003 + rank)
+        yw = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        dw = [(aclnn.from_torch(a), aclnn.from_torch(b_), aclnn.from_torch(c_)) for a, b_, c_ in dataw] * 2
+        dxw, dyw = aclnn.from_torch(xw), aclnn.from_torch(yw)
+        tmw = time_calls(torch, lambda i: aclnn.weight_quant_batch_matmul(dxw, dw[i % 4][0], dw[i % 4][1], dyw, dw[i % 4][2], None, G,
+                                                                          workspace=workspace), args.steps, args.warmup, barrier=barrier)
+        t = torch.tensor([tmw["total_ms"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wms = float(t.item()) / args.steps
+        weak = {"value": world * ALGO_BYTES / (wms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": wms,
+                "note": "every rank a full [8192, 28672] shard (global n = 28672 x %d), 2 weight sets per rank" % world}
+
+    names = [] if args.workload == "c2" else list(QMM_WORKLOADS)
+    workloads = run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names)
 
     if rank == 0:
+        sampler.stop()
         ms_per_step = total_ms / args.steps
-        value = world * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
-        peak, peak_src = measured_peak()
-        achieved = ALGO_BYTES / (kernel_ms * 1e-3) / 1e9
+        value = ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+        hbm, _, peak_src = peaks
+        local_bytes = c2_bytes(nl)
+        achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
+        e2e_ms = min(e2e_serial_ms, e2e_pipe_ms)
+        clocks = sampler.summary(mark_load, mark_load_end)
+        clocks["timed_regions"] = sampler.summary(mark0, mark1)
+        clocks["note"] = "sm_mhz: median over a 0.6 s stretch of the same kernel right after the timed region; timed_regions: samples taken " \
+                         "while the timed regions themselves ran (they last milliseconds)"
         line = {
-            "metric": "W4A16 decode HBM GB/s (weight_quant_batch_matmul_v2, algorithmic bytes / time)",
-            "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (seeded; shapes and value ranges of BASELINE config 2)",
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded; shapes, value ranges and quantisation recipes of the BASELINE configurations)",
             "config": {"workload": WORKLOAD_C2,
-                       "sharding": "n-sharded, one [8192,28672] weight shard per GPU, x replicated, no collective",
-                       "l2": "rotating %d weight sets (%d MB) > 126 MB L2" % (args.sets, args.sets * ALGO_BYTES // 1000000),
-                       "kernel": kernel_name, "workspace_bytes": int(ws_bytes)},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": ALGO_BYTES,
-                         "kernel_ms_avg": kernel_ms, "kernel_ms_min": per_launch_ms[0],
-                         "frac_of_8TBps_datasheet": achieved / 8000.0},
-            "e2e": {"value": world * ALGO_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
-                    "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_ms, "ms_per_step_one_stream": e2e_serial_ms,
-                    "ms_per_step_copy_streams": e2e_pipe_ms, "weight_upload_ms": weight_upload_ms,
-                    "note": "x copied from pinned host memory and y copied back every step (the faster of: everything on one stream; copies on their own streams, double buffered); the quantised weight is a static parameter uploaded once"},
+                       "sharding": "the [8192, 28672] weight cut along n into %d shard(s) of %d columns, x replicated, no collective" % (world, nl),
+                       "l2": "rotating %d weight sets (%d MB per rank) > 126 MB L2" % (args.sets, args.sets * local_bytes // 1000000)
+                             if args.sets * local_bytes > 126e6 else
+                             "rotating %d weight sets (%d MB per rank): BELOW the 126 MB L2 at this shard size, launches may hit L2" % (
+                                 args.sets, args.sets * local_bytes // 1000000),
+                       "kernel": kernel_name, "precision_mode": "default (innerPrecise 0): every dequantised weight rounded twice in bf16 like the "
+                       "reference golden", "workspace_bytes": int(ws_bytes)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "traffic": None, "peak_source": "hbm_gbs, " + peak_src, "algorithmic_bytes_per_launch": local_bytes,
+                         "kernel_ms_avg": kernel_ms, "kernel_ms_median": kernel_med, "kernel_ms_min": kernel_min,
+                         "frac_of_8TBps_datasheet": achieved / 8000.0,
+                         "note": "per rank: this rank's algorithmic bytes / its average launch duration (per-launch CUDA events, max over ranks)"},
+            "parity": dict(parity, ok=bool(par_ok >= 1.0), ranks_checked=world),
+            "e2e": {"value": ALGO_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
+                    "d2h_bytes_per_step": M * nl * 2, "ms_per_step": e2e_ms, "ms_per_step_one_stream": e2e_serial_ms,
+                    "ms_per_step_copy_streams": e2e_pipe_ms, "scheme": "copy_streams" if e2e_pipe_ms <= e2e_serial_ms else "one_stream",
+                    "weight_upload_ms": weight_upload_ms,
+                    "note": "per rank x copied from pinned host memory and its y shard copied back every step; value is the faster of two schemes "
+                            "(`scheme`): everything on one stream, or copies on their own streams, double buffered; the quantised weight is a "
+                            "static parameter uploaded once"},
             "gpu_launches": launches, "clocks": clocks,
-            # not the contract line's mode: aclnnWeightQuantBatchMatmulV3 with innerPrecise = 1 (the reference's documented
-            # high-performance mode for A16W4 per-group, m <= 16); per-launch CUDA events, same inputs and rotation
-            "inner_precise_1": {"kernel": hp_kernel, "achieved": ALGO_BYTES / (hp_kernel_ms * 1e-3) / 1e9, "unit": "GB/s",
-                                "frac": ALGO_BYTES / (hp_kernel_ms * 1e-3) / 1e9 / peak, "kernel_ms_avg": hp_kernel_ms,
-                                "kernel_ms_min": hp_ms[0]},
+            # aclnnWeightQuantBatchMatmulV3 with innerPrecise = 1 (the reference's documented high-performance mode for A16W4
+            # per-group, m <= 16): same inputs and rotation, per-launch CUDA events
+            "inner_precise_1": {"kernel": hp_kernel, "achieved": local_bytes / (hp_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                "frac": local_bytes / (hp_ms * 1e-3) / 1e9 / hbm, "kernel_ms_avg": hp_ms, "kernel_ms_min": hp_min},
+            "workloads": workloads,
         }
         traffic_file = os.path.join(ROOT, "profiles", "wqbmm_decode_c2_traffic.json")
-        if os.path.exists(traffic_file):
+        if world == 1 and os.path.exists(traffic_file):
             with open(traffic_file) as fh:
-                line["roofline"]["traffic"] = json.load(fh).get("dram_bytes_per_launch")
+                tj = json.load(fh)
+            line["roofline"]["traffic"] = tj.get("dram_bytes_per_launch")
+            line["roofline"]["traffic_source"] = tj.get("source")
+        if world > 1:
+            line["with_gather"] = {"ms_per_step": gather_all_ms, "value": ALGO_BYTES / (gather_all_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                   "note": "every step followed by the all-gather of the y shards (%d KB per rank, NCCL) + re-assembly" % (M * nl * 2 // 1024)}
+            line["weak"] = weak
         if not args.no_cpu_baseline and world == 1:
-            xs = to_np_bf16(x)
-            w0, s0, o0 = data[0]
-            _, line["cpu_baseline"] = cpu_baseline_c2(xs, w0.cpu().numpy(), to_np_bf16(s0), to_np_bf16(o0))
+            line["cpu_baseline"] = c2_cpu_baseline(host)
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))

@@ -5,9 +5,13 @@
  * Replaces the reference's
  *   matmul/weight_quant_batch_matmul_v2/op_host/op_api/aclnn_weight_quant_batch_matmul_v3.h:24-34
  * (implementation: aclnn_weight_quant_batch_matmul_v2.cpp:1772-1889; innerPrecise check :283-291).
- * On the reference's current NPU generation the flag is documented to have no effect
- * (docs/aclnnWeightQuantBatchMatmulV3.md:414); here it is accepted and the same bit-faithful kernel runs
- * for both values.
+ * The reference documents innerPrecise = 1 as the faster, slightly less faithful mode for A16W4 per-group with
+ * m <= 16 (docs/aclnnWeightQuantBatchMatmulV3.md:28, :389) and as having no effect elsewhere (:414). Here:
+ *   innerPrecise = 0  every dequantised weight is rounded twice in x's dtype, exactly as the reference's golden does;
+ *   innerPrecise = 1  where the streaming decode kernel applies (INT4 weight stored (k,n), m <= 16, 32-column pieces)
+ *                     scale and offset are applied per k-group to the fp32 accumulators instead: no weight is rounded,
+ *                     the result is closer to the fp32 dequantised product but not bit-identical to innerPrecise = 0;
+ *                     on every other shape the flag changes nothing.
  */
 #ifndef OPSNN_B200_ACLNN_WEIGHT_QUANT_BATCH_MATMUL_V3_H_
 #define OPSNN_B200_ACLNN_WEIGHT_QUANT_BATCH_MATMUL_V3_H_

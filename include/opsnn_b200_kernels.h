@@ -197,8 +197,15 @@ OPSNN_API uint64_t opsnn_launch_count(void);
 OPSNN_API const char* opsnn_last_kernel_name(void);
 /* Error word of the tensor-core (tcgen05) quant matmul kernels on the current device: 0 when every bounded wait
  * inside them completed; otherwise the code of the first wait that gave up (the kernel then returned early and its
- * output is undefined). Synchronises the device. reset != 0 clears the word after reading it. */
+ * output is undefined). Synchronises the device. reset != 0 clears the word after reading it.
+ * The same condition also reaches the caller without polling: the word is mirrored into pinned host memory, and every later
+ * tensor-core launch of the process (opsnn_qmm_launch, and through it aclnnQuantMatmulV3/V4/V5 and the prefill path of
+ * aclnnWeightQuantBatchMatmul*) first looks at the mirror and, while it is non-zero, refuses with cudaErrorLaunchFailure
+ * (ACLNN_ERR_RUNTIME_ERROR at the aclnn level, reason in aclGetRecentErrMsg) until this function is called with reset != 0. */
 OPSNN_API uint32_t opsnn_qmm_umma_status(int32_t reset);
+/* The same for the streaming W4A16 decode kernel that feeds shared memory with bulk tensor copies: 0, or 1 (a stage of
+ * operands never arrived) / 2 (a stage buffer was never released). Synchronises the device. */
+OPSNN_API uint32_t opsnn_wqbmm_decode_status(int32_t reset);
 
 #ifdef __cplusplus
 }

@@ -90,6 +90,8 @@ def lib():
     L.opsnn_launch_count.restype = c_uint64
     L.opsnn_qmm_umma_status.restype = ctypes.c_uint32
     L.opsnn_qmm_umma_status.argtypes = [c_int32]
+    L.opsnn_wqbmm_decode_status.restype = ctypes.c_uint32
+    L.opsnn_wqbmm_decode_status.argtypes = [c_int32]
     L.opsnn_last_kernel_name.restype = c_char_p
     for name in ("opsnn_wqbmm_launch", "opsnn_wqbmm_decode_static_launch"):
         getattr(L, name).restype = c_int32

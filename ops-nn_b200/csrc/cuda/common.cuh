@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "aclnn_compat/acl_base.h"
 #include "opsnn_b200_kernels.h"
 
@@ -15,6 +17,36 @@ namespace opsnn {
 // Host: count a launch and remember which kernel family ran (read back through opsnn_launch_count /
 // opsnn_last_kernel_name).
 void note_launch(const char* name, uint64_t n = 1);
+
+// Host: set-up that is a property of the (function, device) pair - the dynamic shared-memory limit of a kernel, occupancy - done the
+// first time a launcher runs with each device current. `done` holds one bit per device ordinal. Two threads racing on the same first
+// call both run `f`, which is idempotent.
+template <typename F>
+inline cudaError_t once_per_device(std::atomic<uint64_t>& done, F&& f)
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    const cudaError_t rc = f();
+    if (rc == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return rc;
+}
+
+// Host: SM count of the current device (cached per device ordinal).
+inline int current_sm_count()
+{
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int v = cache[dev & 63].load(std::memory_order_relaxed);
+    if (v <= 0) {
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        if (v <= 0) v = 148;
+        cache[dev & 63].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
 
 __device__ __forceinline__ float e8m0_to_float(uint8_t b)
 {

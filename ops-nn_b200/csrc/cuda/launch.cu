@@ -37,6 +37,18 @@ int32_t wqbmm_decode_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode_fast_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 int32_t wqbmm_decode_ring_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact);
+bool wqbmm_decode_tma_eligible(const OpsnnWqbmmParams* p);
+int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact);
+
+// The streaming decode kernels that share one data layout condition, newest data path first: bulk tensor copies (TMA) into
+// swizzled stages, else the per-warp cp.async ring. OPSNN_WQ_DECODE_PATH=ring forces the second.
+static int32_t decode_stream_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact)
+{
+    const char* e = getenv("OPSNN_WQ_DECODE_PATH");
+    const bool ring_only = e != nullptr && e[0] == 'r';
+    if (!ring_only && wqbmm_decode_tma_eligible(p)) return wqbmm_decode_tma_launch(p, stream, exact);
+    return wqbmm_decode_ring_launch(p, stream, exact);
+}
 
 bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
 uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
@@ -130,8 +142,8 @@ static int32_t decode_chunk_launches(const OpsnnWqbmmParams* p, cudaStream_t str
         q.x = static_cast<const uint8_t*>(p->x) + (size_t)r0 * (size_t)p->x_ld * esz;
         q.y = static_cast<uint8_t*>(p->y) + (size_t)r0 * (size_t)p->y_ld * esz;
         int32_t rc;
-        if (which == OPSNN_WQ_KERNEL_DECODE_FAST) rc = wqbmm_decode_fast_launch(&q, stream);
-        else if (wqbmm_decode_fast_eligible(&q) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr) rc = wqbmm_decode_ring_launch(&q, stream, true);
+        if (which == OPSNN_WQ_KERNEL_DECODE_FAST) rc = decode_stream_launch(&q, stream, false);
+        else if (wqbmm_decode_fast_eligible(&q) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr) rc = decode_stream_launch(&q, stream, true);
         else rc = wqbmm_decode_launch(&q, stream);
         if (rc != 0) return rc;
     }
@@ -196,12 +208,12 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
         // same arithmetic, two data paths: shared-memory ring + ldmatrix where the layout allows it (32-column pieces, 16-byte
         // aligned rows, groups of whole step pairs), register prefetch otherwise
         if (wqbmm_decode_fast_eligible(p) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr)
-            return wqbmm_decode_ring_launch(p, static_cast<cudaStream_t>(stream), true);
+            return decode_stream_launch(p, static_cast<cudaStream_t>(stream), true);
         return wqbmm_decode_launch(p, static_cast<cudaStream_t>(stream));
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) {
         if (!wqbmm_decode_fast_eligible(p)) return (int32_t)cudaErrorInvalidValue;
-        return wqbmm_decode_fast_launch(p, static_cast<cudaStream_t>(stream));
+        return decode_stream_launch(p, static_cast<cudaStream_t>(stream), false);
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_PREFILL) {
         if (!wqbmm_prefill_eligible(p)) return (int32_t)cudaErrorInvalidValue;

@@ -587,11 +587,11 @@ int32_t mx_launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a,
     a.stages = stages;
     const size_t smem = (size_t)stages * stage + 1024 + 256 + 256 * 4;
     const int64_t grid = a.num_tiles < sm_count() ? a.num_tiles : sm_count();
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t rc = cudaFuncSetAttribute(qmm_mx_umma_kernel<BN, kF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    static std::atomic<uint64_t> configured{0};
+    {
+        const cudaError_t rc = once_per_device(
+            configured, [&] { return cudaFuncSetAttribute(qmm_mx_umma_kernel<BN, kF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (rc != cudaSuccess) return (int32_t)rc;
-        configured = true;
     }
     qmm_mx_umma_kernel<BN, kF4><<<(unsigned)grid, 192, smem, stream>>>(ma, mb, a);
     note_launch(kF4 ? "qmm_umma_mxfp4" : "qmm_umma_mxfp8");

@@ -277,11 +277,11 @@ int32_t mx_launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a
     if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * stage + 1024 + 256 + 256 * 4;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t rc = cudaFuncSetAttribute(qmm_mx_umma_pair_kernel<kF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    static std::atomic<uint64_t> configured{0};
+    {
+        const cudaError_t rc = once_per_device(
+            configured, [&] { return cudaFuncSetAttribute(qmm_mx_umma_pair_kernel<kF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (rc != cudaSuccess) return (int32_t)rc;
-        configured = true;
     }
     int64_t pairs = sm_count() / 2;
     if (a.num_tiles < pairs) pairs = a.num_tiles;

@@ -83,8 +83,10 @@ __device__ __forceinline__ void tile_of(uint32_t r, uint32_t tiles_m, uint32_t t
     tm = band * kBand + (rr - tn * rows);
 }
 
-__device__ unsigned int g_umma_status = 0;
-  // 0 ok; otherwise (role << 8) | reason of the first failed wait
+__device__ unsigned int g_umma_status = 0;  // 0 ok; otherwise (role << 8) | reason of the first failed wait
+// The same word in pinned host memory (set once per device by arm_status_mirror): the host reads it before the next launch
+// without synchronising anything, which is how a give-up turns into an error code of the following call.
+__device__ volatile unsigned int* g_umma_status_host = nullptr;
 
 template <int BN>
 struct Smem {
@@ -95,7 +97,10 @@ struct Smem {
 __device__ __forceinline__ void report(volatile uint32_t* abort_flag, unsigned int code)
 {
     *abort_flag = 1u;
-    atomicCAS(&g_umma_status, 0u, code);
+    if (atomicCAS(&g_umma_status, 0u, code) == 0u && g_umma_status_host != nullptr) {
+        *g_umma_status_host = code;
+        __threadfence_system();
+    }
 }
 
 // Converts 32 accumulator columns of one output row and stores them. `col` is the first column (global), valid = number
@@ -677,17 +682,7 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_sms = 0;
-int sm_count()
-{
-    if (g_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sms <= 0) g_sms = 148;
-    }
-    return g_sms;
-}
+int sm_count() { return current_sm_count(); }
 
 bool is_fp8(int dt) { return dt == ACL_FLOAT8_E4M3FN || dt == ACL_FLOAT8_E5M2; }
 
@@ -752,13 +747,10 @@ int32_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cu
     if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * kStage + 1024 + 256 + 2 * BN * 4;
-    static bool configured = false;
+    static std::atomic<uint64_t> configured{0};
     auto kern = qmm_umma_kernel<BN, PB, KIND, EW>;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
-            return (int32_t)cudaGetLastError();
-        configured = true;
-    }
+    if (once_per_device(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess)
+        return (int32_t)cudaGetLastError();
     const int64_t work = a.num_tiles * (PB ? 1 : a.ksplit);
     int64_t grid = work < sm_count() ? work : sm_count();
     kern<<<(unsigned)grid, (EW + 2) * 32, smem, stream>>>(ma, mb, a);
@@ -837,8 +829,55 @@ uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p)
     return p->mode == OPSNN_QMM_PERBLOCK ? 0 : ksplit_workspace(p);
 }
 
+namespace {
+
+std::atomic<unsigned int*> g_status_host_word{nullptr};
+std::atomic<uint64_t> g_status_armed{0};
+
+// Once per process: one pinned, device-visible word. Once per device: its address into g_umma_status_host.
+cudaError_t arm_status_mirror()
+{
+    return once_per_device(g_status_armed, [] {
+        unsigned int* w = g_status_host_word.load(std::memory_order_acquire);
+        if (w == nullptr) {
+            unsigned int* fresh = nullptr;
+            cudaError_t rc = cudaHostAlloc(reinterpret_cast<void**>(&fresh), 64, cudaHostAllocPortable | cudaHostAllocMapped);
+            if (rc != cudaSuccess) return rc;
+            *fresh = 0u;
+            if (g_status_host_word.compare_exchange_strong(w, fresh)) w = fresh;
+            else cudaFreeHost(fresh);
+        }
+        unsigned int* dptr = nullptr;
+        cudaError_t rc = cudaHostGetDevicePointer(reinterpret_cast<void**>(&dptr), w, 0);
+        if (rc != cudaSuccess) return rc;
+        return cudaMemcpyToSymbol(g_umma_status_host, &dptr, sizeof(dptr));
+    });
+}
+
+}  // namespace
+
+void set_err(const char* fmt, ...);  // thread-local text behind aclGetRecentErrMsg (host library)
+
+// Called by every tensor-core launcher before it enqueues anything: non-zero when an earlier tensor-core kernel of this process
+// gave up a bounded wait (its output is undefined). The condition is sticky until opsnn_qmm_umma_status(1) clears it.
+int32_t umma_prelaunch_check()
+{
+    if (arm_status_mirror() != cudaSuccess) {
+        cudaGetLastError();
+        return 0;  // no mirror (host allocation refused): the device word is still there for opsnn_qmm_umma_status
+    }
+    const unsigned int* w = g_status_host_word.load(std::memory_order_acquire);
+    const unsigned int code = w ? *reinterpret_cast<const volatile unsigned int*>(w) : 0u;
+    if (code == 0u) return 0;
+    set_err("an earlier tensor-core kernel gave up a bounded wait (role %u, reason %u): its output is undefined; "
+            "opsnn_qmm_umma_status(1) clears the condition",
+            code >> 8, code & 0xFFu);
+    return (int32_t)cudaErrorLaunchFailure;
+}
+
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
 {
+    if (const int32_t bad = umma_prelaunch_check()) return bad;
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
     const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32 && p->out_dtype != ACL_INT8;
     // per-block on CTA pairs: 256 x 128 tiles
@@ -922,6 +961,7 @@ extern "C" __attribute__((visibility("default"))) uint32_t opsnn_qmm_umma_status
     if (reset) {
         unsigned int z = 0;
         cudaMemcpyToSymbol(opsnn::g_umma_status, &z, sizeof(z));
+        if (unsigned int* w = opsnn::g_status_host_word.load(std::memory_order_acquire)) *reinterpret_cast<volatile unsigned int*>(w) = 0u;
     }
     return v;
 }

@@ -218,11 +218,9 @@ int32_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, c
     a.stages = stages;
     const size_t smem = (size_t)stages * kStage + 1024 + 256 + 2 * 256 * 4;
     auto kern = qmm_umma_pair_kernel<KIND>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return (int32_t)cudaGetLastError();
-        configured = true;
-    }
+    static std::atomic<uint64_t> configured{0};
+    if (once_per_device(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess)
+        return (int32_t)cudaGetLastError();
     int64_t pairs = sm_count() / 2;
     if (a.num_tiles < pairs) pairs = a.num_tiles;
     kern<<<(unsigned)(2 * pairs), 192, smem, stream>>>(ma, mb, a);

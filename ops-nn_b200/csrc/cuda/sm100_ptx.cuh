@@ -77,7 +77,7 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t pari
                  : "memory");
     return ok != 0;
 }
-__device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
+static __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
 {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait_a(bar_addr, parity)) return true;

@@ -208,23 +208,17 @@ __global__ void __launch_bounds__(kThreads, OPSNN_DECODE_MINB) wqbmm_decode_kern
     }
 }
 
-int g_decode_ctas_per_sm[4] = {0, 0, 0, 0};
-int g_sm_count = 0;
+int g_decode_ctas_per_sm[4] = {0, 0, 0, 0};  // a property of the kernel image and the architecture: the same on every device of a box
 
 template <bool kBf16, bool kHasOffset>
 int decode_grid(int variant)
 {
-    if (g_sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-    }
     if (g_decode_ctas_per_sm[variant] == 0) {
         int nb = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, wqbmm_decode_kernel<kBf16, kHasOffset>, kThreads, 0);
         g_decode_ctas_per_sm[variant] = nb > 0 ? nb : 1;
     }
-    return g_sm_count * g_decode_ctas_per_sm[variant];
+    return current_sm_count() * g_decode_ctas_per_sm[variant];
 }
 
 constexpr int kMaxGrid = 148 * 4 * 2;  // workspace is sized for at most this many CTAs
@@ -244,7 +238,9 @@ uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p)
 bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p)
 {
     if (p->w_dtype != ACL_INT4 || p->trans_w != 0) return false;
+    if (p->scale_dtype == ACL_FLOAT8_E8M0) return false;  // the decode kernels read scale as 16-bit elements of x's dtype
     if (p->m < 1 || p->m > 16) return false;
+    if (p->k < 16) return false;                            // at least one k-step: the prefetch reads 16 weight rows unconditionally
     if (p->k % 16 != 0 || p->n % 8 != 0 || p->w_ld % 8 != 0 || p->x_ld % 8 != 0) return false;
     if (p->group_size != 0 && p->group_size % 16 != 0) return false;
     if (p->scale_sn != 0 && p->scale_sn != 1) return false;

@@ -366,23 +366,20 @@ __global__ void __launch_bounds__(kThreads, 2) wqbmm_decode_fast_kernel(const De
 }
 
 int g_fast_ctas_per_sm[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-int g_fast_sm_count = 0;
+std::atomic<uint64_t> g_fast_configured[8];
 
 template <bool kBf16, bool kHasOffset, bool kExact>
 int fast_grid(int variant)
 {
-    if (g_fast_sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_fast_sm_count, cudaDevAttrMultiProcessorCount, dev);
-    }
+    once_per_device(g_fast_configured[variant], [&] {
+        return cudaFuncSetAttribute(wqbmm_decode_fast_kernel<kBf16, kHasOffset, kExact>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFastSmem);
+    });
     if (g_fast_ctas_per_sm[variant] == 0) {
-        cudaFuncSetAttribute(wqbmm_decode_fast_kernel<kBf16, kHasOffset, kExact>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFastSmem);
         int nb = 0;
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, wqbmm_decode_fast_kernel<kBf16, kHasOffset, kExact>, kThreads, kFastSmem);
         g_fast_ctas_per_sm[variant] = nb > 0 ? nb : 1;
     }
-    return g_fast_sm_count * g_fast_ctas_per_sm[variant];
+    return current_sm_count() * g_fast_ctas_per_sm[variant];
 }
 
 constexpr int kFastMaxGrid = 148 * 4 * 2;  // same workspace layout and bound as the default decode kernel

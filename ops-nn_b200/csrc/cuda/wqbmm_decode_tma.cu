@@ -1,0 +1,538 @@
+// Weight-only quant matmul, streaming decode kernel (m <= 16, INT4 weight stored (k,n)), bulk-tensor-copy data path.
+//
+// Same arithmetic as the two ring kernels of wqbmm_decode_fast.cu - kExact: the reference's two roundings per weight
+// (weight_quant_batch_matmul_v2/op_kernel/arch35/weight_quant_batch_matmul_v2_reg_base_common_vf.h:345-442, golden
+// wqbmmv2_kernel_golden.py:242-297); group-wise: scale and offset applied per k-group to fp32 partial sums
+// (innerPrecise = 1, docs/aclnnWeightQuantBatchMatmulV3.md:28, :389) - but the operands reach shared memory differently:
+//
+//   * A CTA (8 warps) owns a strip of 512 weight columns and a k range made of whole stages of 64 k rows. One stage is
+//     three TMA boxes: two of 128 bytes x 64 rows of packed weights (columns 0-255 and 256-511 of the strip) and one
+//     of 128 bytes x 16 rows of x (the same 64 k), all in the 128-byte swizzle, 18 KB together. Columns past n, rows of
+//     x past m and k rows past the end arrive as zeros, so ragged strips and k tails need no special code.
+//   * Six stages per CTA, two CTAs per SM: up to 192 KB of weights in flight per SM with one instruction per box. The
+//     warp whose turn it is (stage index mod 8) refills the buffer it left one stage ago once all eight warps have
+//     released it (an mbarrier with one arrival per warp); nobody else ever waits for another warp.
+//   * Per k-step (16 k rows) a warp issues one ldmatrix.x4.trans on its 64 columns (four nibbles of two k rows per
+//     register, already paired the way the MMA B fragment wants them) and one ldmatrix.x4 for the x fragment, with
+//     immediate offsets inside the stage; there is no per-step address arithmetic, no copy instruction and no barrier.
+//
+// The integer pipe (logic and shifts: 28 instructions per k-step), the 16-bit-pair arithmetic (kExact: 48 per k-step) and
+// mma.sync (8 or 9 per k-step) each run at one warp instruction per two clocks per SM sub-partition on this part, so the
+// main loop is written to add as little as possible to any of them.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "wqbmm_decode_common.cuh"
+
+namespace opsnn {
+
+namespace {
+
+constexpr int kStageSteps = 4;                      // k-steps (16 rows each) per stage
+constexpr int kStageRows = kStageSteps * 16;        // 64 k rows
+constexpr int kWBoxBytes = 128 * kStageRows;        // one weight box: 256 columns x 64 rows
+constexpr int kXBoxBytes = 128 * 16;                // x: 64 k x 16 rows
+constexpr int kStageBytes = 2 * kWBoxBytes + kXBoxBytes;  // 18432
+constexpr int kNumStages = 6;
+constexpr int kTmaSmem = kNumStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr uint32_t kWaitPolls = 4u * 1000u * 1000u;  // polls before a wait is declared dead
+
+template <bool kBf16>
+struct GwNum;
+template <>
+struct GwNum<true> {
+    static constexpr uint32_t kOnes = 0x3F803F80u;  // bf16x2 {1, 1}
+    static constexpr float kB = 136.f;
+    __device__ __forceinline__ static float lo(uint32_t r) { return __uint_as_float(r << 16); }
+    __device__ __forceinline__ static float hi(uint32_t r) { return __uint_as_float(r & 0xFFFF0000u); }
+};
+template <>
+struct GwNum<false> {
+    static constexpr uint32_t kOnes = 0x3C003C00u;  // half2 {1, 1}
+    static constexpr float kB = 1032.f;
+    __device__ __forceinline__ static float lo(uint32_t r) { return __half2float(__ushort_as_half((unsigned short)(r & 0xFFFFu))); }
+    __device__ __forceinline__ static float hi(uint32_t r) { return __half2float(__ushort_as_half((unsigned short)(r >> 16))); }
+};
+
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+template <int kOff>
+__device__ __forceinline__ void ldsm4_trans(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr), "n"(kOff));
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_addr, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_a(uint32_t bar_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+
+// 0 when every wait of every launch completed; otherwise 1 (a stage never arrived) or 2 (a stage was never released).
+__device__ unsigned int g_wq_tma_status = 0;
+
+__device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int code)
+{
+    for (uint32_t i = 0; i < kWaitPolls; ++i) {
+        if (ptx::mbar_try_wait_a(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    atomicCAS(&g_wq_tma_status, 0u, code);
+    return false;
+}
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int code)
+{
+    if (ptx::mbar_try_wait_a(bar, parity)) return true;
+    return wait_slow(bar, parity, abort_flag, code);
+}
+
+struct TmaArgs {
+    DecodeArgs d;
+    int32_t total_stages;      // ceil(k / 64)
+    int32_t stages_per_group;  // kAligned kernels: steps_per_group / 4
+};
+
+// kAligned: every k-group is a whole number of stages (or there is a single group), so group changes happen at stage
+// boundaries only. Otherwise groups are whole step pairs and the change is looked for before steps 0 and 2 of a stage.
+template <bool kBf16, bool kExact, bool kAligned>
+__global__ void __launch_bounds__(kThreads, 2)
+wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TmaArgs ta)
+{
+    using N = Num<kBf16>;
+    using F = GwNum<kBf16>;
+    const DecodeArgs& a = ta.d;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    __shared__ int s_reduce;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ int s_issued[kNumStages];
+    extern __shared__ uint8_t dyn_raw[];
+    const uint32_t smem0 = (ptx::smem_u32(dyn_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem0 + kNumStages * kStageBytes;  // full[i] at bar0 + 8 i, empty[i] at bar0 + 64 + 8 i
+
+    const int64_t c = blockIdx.x;
+    const int64_t strip = c % a.strips;
+    const int64_t chunk = c / a.strips;
+    // this CTA's k range in stages
+    const int st_a = (int)((chunk * ta.total_stages) / a.splits);
+    const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
+    const int nst = st_b - st_a;
+    const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
+    const int32_t wcol_bytes = (int32_t)(strip * (kStripCols / 2));
+
+    if (tid == 0) {
+        s_abort = 0u;
+        for (int i = 0; i < kNumStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8u * i), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 64u + 8u * i), "r"((uint32_t)kWarps) : "memory");
+            s_issued[i] = -1;
+        }
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+    }
+    __syncthreads();
+    volatile uint32_t* abort_flag = &s_abort;
+
+    auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
+        const uint32_t fb = bar0 + 8u * buf;
+        const uint32_t dst = smem0 + (uint32_t)buf * kStageBytes;
+        const int32_t krow = (st_a + t) * kStageRows;
+        s_issued[buf] = t;
+        ptx::mbar_expect_tx_a(fb, (uint32_t)kStageBytes);
+        tma_load_2d(dst, &map_w, fb, wcol_bytes, krow);
+        tma_load_2d(dst + kWBoxBytes, &map_w, fb, wcol_bytes + 128, krow);
+        tma_load_2d(dst + 2 * kWBoxBytes, &map_x, fb, krow * 2, 0);
+    };
+    if (tid == 0) {
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_x);
+        const int pro = nst < kNumStages ? nst : kNumStages;
+        for (int t = 0; t < pro; ++t) issue_stage(t, t);
+    }
+
+    float total[kTiles][4], part[kExact ? 1 : kTiles][4], xsum[4];
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) total[t][0] = total[t][1] = total[t][2] = total[t][3] = 0.f;
+#pragma unroll
+    for (int t = 0; t < (kExact ? 1 : kTiles); ++t) part[t][0] = part[t][1] = part[t][2] = part[t][3] = 0.f;
+    xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
+
+    // ---- scale / offset of the current k-group ----
+    const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+    const int64_t n_groups = (a.ksteps + spg - 1) / spg;
+    // exact mode: the lane's B-fragment columns (tile t < 4: column 4g + t, else 32 + 4g + t - 4), each value in both halves
+    const int64_t ecol0 = (warp_col + 4 * g < a.n) ? warp_col + 4 * g : 0;
+    const int64_t ecol1 = (warp_col + 32 + 4 * g < a.n) ? warp_col + 32 + 4 * g : 0;
+    // group-wise mode: the lane's 16 output columns, 8q..8q+7 of each 32-column half
+    const int64_t scol0 = (warp_col + 8 * q < a.n) ? warp_col + 8 * q : 0;
+    const int64_t scol1 = (warp_col + 32 + 8 * q < a.n) ? warp_col + 32 + 8 * q : 0;
+    const bool has_off = a.offset != nullptr;
+    uint32_t sc[kExact ? kTiles : 1], of[kExact ? kTiles : 1], rs_next[4], ro_next[4] = {0u, 0u, 0u, 0u};
+    uint32_t raw_s[kExact ? 1 : 8], raw_o[kExact ? 1 : 8];
+
+    auto fetch_exact = [&](int64_t group) {
+        if (a.scale_sn != 0) {
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+            const uint2 s0 = __ldg(reinterpret_cast<const uint2*>(sp + ecol0)), s1 = __ldg(reinterpret_cast<const uint2*>(sp + ecol1));
+            rs_next[0] = s0.x; rs_next[1] = s0.y; rs_next[2] = s1.x; rs_next[3] = s1.y;
+            if (has_off) {
+                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+                const uint2 o0 = __ldg(reinterpret_cast<const uint2*>(op + ecol0)), o1 = __ldg(reinterpret_cast<const uint2*>(op + ecol1));
+                ro_next[0] = o0.x; ro_next[1] = o0.y; ro_next[2] = o1.x; ro_next[3] = o1.y;
+            }
+        } else {
+            const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+            const uint32_t ov = has_off ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                rs_next[i] = sv | (sv << 16);
+                ro_next[i] = ov | (ov << 16);
+            }
+        }
+    };
+    auto load_group = [&](int64_t group) {
+        if (group >= n_groups) group = n_groups - 1;  // zero-filled stages past the end of k: any finite scale will do
+        if (kExact) {
+            // the values requested one group ago become this group's registers; the next group's are requested now
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) {
+                const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
+                sc[t] = prmt(rs_next[t >> 1], rs_next[t >> 1], sel);
+                of[t] = prmt(ro_next[t >> 1], ro_next[t >> 1], sel);
+            }
+            fetch_exact(min(group + 1, n_groups - 1));
+            return;
+        }
+        if (a.scale_sn != 0) {
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+            const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(sp + scol0)), s1 = __ldg(reinterpret_cast<const uint4*>(sp + scol1));
+            raw_s[0] = s0.x; raw_s[1] = s0.y; raw_s[2] = s0.z; raw_s[3] = s0.w;
+            raw_s[4] = s1.x; raw_s[5] = s1.y; raw_s[6] = s1.z; raw_s[7] = s1.w;
+            if (has_off) {
+                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+                const uint4 o0 = __ldg(reinterpret_cast<const uint4*>(op + scol0)), o1 = __ldg(reinterpret_cast<const uint4*>(op + scol1));
+                raw_o[0] = o0.x; raw_o[1] = o0.y; raw_o[2] = o0.z; raw_o[3] = o0.w;
+                raw_o[4] = o1.x; raw_o[5] = o1.y; raw_o[6] = o1.z; raw_o[7] = o1.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) raw_o[i] = 0u;
+            }
+        } else {
+            const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+            const uint32_t ov = has_off ? reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg] : 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                raw_s[i] = sv | (sv << 16);
+                raw_o[i] = ov | (ov << 16);
+            }
+        }
+    };
+    // group-wise mode: fold the finished group into the totals, total += scale * (part + (offset - B) * rowsum(x))
+    auto finish_group = [&]() {
+        if (kExact) return;
+#pragma unroll
+        for (int idx = 0; idx < 16; ++idx) {  // idx = 8*half + 4*(e&1) + (t&3): position among the lane's 16 columns
+            const uint32_t rs = raw_s[idx >> 1], ro = raw_o[idx >> 1];
+            const float sf = (idx & 1) ? F::hi(rs) : F::lo(rs);
+            const float ofs = ((idx & 1) ? F::hi(ro) : F::lo(ro)) - F::kB;
+            const int t = (idx >> 3) * 4 + (idx & 3), e0 = (idx >> 2) & 1;  // fragment entries e0 (row g) and e0 + 2 (row g + 8)
+            total[t][e0] = fmaf(sf, fmaf(ofs, xsum[0], part[t][e0]), total[t][e0]);
+            total[t][e0 + 2] = fmaf(sf, fmaf(ofs, xsum[2], part[t][e0 + 2]), total[t][e0 + 2]);
+        }
+#pragma unroll
+        for (int t = 0; t < (kExact ? 1 : kTiles); ++t) part[t][0] = part[t][1] = part[t][2] = part[t][3] = 0.f;
+        xsum[0] = xsum[1] = xsum[2] = xsum[3] = 0.f;
+    };
+    // one k-step: 4 registers of paired nibbles -> 16 B-fragment registers -> 8 MMAs (+ the row-sum MMA)
+    auto compute = [&](const uint32_t(&w4)[4], const uint32_t(&af)[4]) {
+        uint32_t b0[kTiles], b1[kTiles];
+        if (kExact) {
+            // (nibble ^ 8) | magic == B + w exactly; then the reference's rounding points: w' = mul(add(sub(v, B), offset), scale)
+            auto deq = [&](uint32_t tw, int t) {
+                uint32_t v;
+                asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(tw), "n"(0x000F000F), "n"(N::kMagic));
+                v = N::sub(v, a.c_bias);
+                v = N::add(v, of[kExact ? t : 0]);
+                return N::mul(v, sc[kExact ? t : 0]);
+            };
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                b0[t] = deq(w4[0] >> (4 * t), t);
+                b1[t] = deq(w4[1] >> (4 * t), t);
+                b0[4 + t] = deq(w4[2] >> (4 * t), 4 + t);
+                b1[4 + t] = deq(w4[3] >> (4 * t), 4 + t);
+            }
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) N::mma_free(total[t], af, b0[t], b1[t]);
+            return;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[t]) : "r"(w4[0] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[t]) : "r"(w4[1] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b0[4 + t]) : "r"(w4[2] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(b1[4 + t]) : "r"(w4[3] >> (4 * t)), "n"(0x000F000F), "n"(N::kMagic));
+        }
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) N::mma_free(part[kExact ? 0 : t], af, b0[t], b1[t]);
+        N::mma_free(xsum, af, F::kOnes, F::kOnes);
+    };
+
+    // ---- per-lane ldmatrix addresses inside a stage (128-byte swizzle: 16-byte chunk index ^ (row & 7)) ----
+    // weights: matrix j = lane / 8 is (rows 0-7 | 8-15)[j & 1] x (columns 0-31 | 32-63)[j >> 1] of the warp's 64 columns, lane % 8
+    // its row; a k-step further down is + 2048 bytes (16 rows), which leaves row & 7 alone.
+    const int li = lane & 7, lj = lane >> 3;
+    const uint32_t wlane = (uint32_t)(warp >> 2) * kWBoxBytes + (uint32_t)(li + 8 * (lj & 1)) * 128u +
+                           (uint32_t)(((2 * (warp & 3) + (lj >> 1)) ^ li) << 4);
+    // x: rows (l % 8) + 8 ((l / 8) & 1), k half l / 16 of step s: chunk 2 s + (l / 16), i.e. the lane's address ^ (s << 5)
+    const uint32_t xrow = (uint32_t)(li + 8 * (lj & 1));
+    const uint32_t xlane = 2u * kWBoxBytes + xrow * 128u + ((((uint32_t)lj >> 1) ^ (uint32_t)li) << 4);
+
+    // first group
+    const int first_step = st_a * kStageSteps;
+    int64_t group = first_step / spg;
+    if (kExact) fetch_exact(min(group, n_groups - 1));
+    load_group(group);
+    int until_change;  // kAligned: stages left in the current group (counting the next one); else steps left
+    if (kAligned) until_change = ta.stages_per_group - (st_a % ta.stages_per_group);
+    else until_change = (int)((group + 1) * (int64_t)spg - first_step);
+
+    uint32_t w0[4], a0[4], w1[4], a1[4];
+    int buf = 0;
+    uint32_t par = 0;
+    bool ok = nst > 0;
+    if (ok) {
+        ok = wait_bar(bar0, 0u, abort_flag, 1u);
+        ldsm4_trans<0>(smem0 + wlane, w0);
+        ldsm4(smem0 + xlane, a0);
+    }
+    int duty = (warp + 8 * 8 - (kNumStages - 1)) & 7;  // this warp refills when (stage index & 7) == duty
+    for (int j = 0; j < nst && ok; ++j) {
+        const uint32_t sbase = smem0 + (uint32_t)buf * kStageBytes;
+        const uint32_t wb = sbase + wlane, xb = sbase + xlane;
+        // refill duty: stage j + kNumStages - 1 goes into the buffer this warp finished one stage ago
+        if (j >= 1 && (j & 7) == duty && j + kNumStages - 1 < nst) {
+            if (lane == 0) {
+                const int pbuf = buf == 0 ? kNumStages - 1 : buf - 1;
+                const uint32_t ppar = buf == 0 ? par ^ 1u : par;
+                if (wait_bar(bar0 + 64u + 8u * pbuf, ppar, abort_flag, 2u)) issue_stage(j + kNumStages - 1, pbuf);
+            }
+            __syncwarp();
+        }
+        if (!kAligned) {
+            if (until_change == 0) { finish_group(); load_group(++group); until_change = spg; }
+        } else if (j > 0 && until_change == 0) {
+            finish_group();
+            load_group(++group);
+            until_change = ta.stages_per_group;
+        }
+        // step 0
+        ldsm4_trans<2048>(wb, w1);
+        ldsm4(xb ^ 32u, a1);
+        compute(w0, a0);
+        // step 1
+        ldsm4_trans<4096>(wb, w0);
+        ldsm4(xb ^ 64u, a0);
+        compute(w1, a1);
+        if (!kAligned) {
+            until_change -= 2;
+            if (until_change == 0) { finish_group(); load_group(++group); until_change = spg; }
+        }
+        // step 2
+        ldsm4_trans<6144>(wb, w1);
+        ldsm4(xb ^ 96u, a1);
+        compute(w0, a0);
+        // step 3, after the first fragments of the next stage have been requested
+        int nbuf = buf + 1;
+        uint32_t npar = par;
+        if (nbuf == kNumStages) { nbuf = 0; npar ^= 1u; }
+        if (j + 1 < nst) {
+            ok = wait_bar(bar0 + 8u * nbuf, npar, abort_flag, 1u);
+            const uint32_t nb = smem0 + (uint32_t)nbuf * kStageBytes;
+            ldsm4_trans<0>(nb + wlane, w0);
+            ldsm4(nb + xlane, a0);
+        }
+        compute(w1, a1);
+        if (!kAligned) until_change -= 2;
+        else --until_change;
+        // every lane has read the stage: release the buffer
+        __syncwarp();
+        if (lane == 0) mbar_arrive_a(bar0 + 64u + 8u * buf);
+        buf = nbuf;
+        par = npar;
+    }
+    finish_group();
+
+    if (__syncthreads_or(s_abort != 0u)) {
+        // A wait gave up. Nothing is written; before the CTA leaves, the copies already issued get a bounded time to land
+        // (shared memory must not be handed to another CTA while a bulk copy still targets it).
+        if (tid == 0) {
+            for (int i = 0; i < kNumStages; ++i) {
+                const int t = s_issued[i];
+                if (t < 0) continue;
+                const uint32_t p = (uint32_t)(t / kNumStages) & 1u;
+                for (uint32_t it = 0; it < kWaitPolls; ++it)
+                    if (ptx::mbar_try_wait_a(bar0 + 8u * i, p)) break;
+            }
+        }
+        __syncthreads();
+        return;
+    }
+    combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn tma_encoder()
+{
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D byte tensor (inner bytes, rows) with a (128, box_rows) box in the 128-byte swizzle; out-of-range bytes read as zero.
+bool make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows)
+{
+    EncodeFn enc = tma_encoder();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {inner_bytes, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+std::atomic<uint64_t> g_tma_configured[8];
+
+template <bool kBf16, bool kExact, bool kAligned>
+cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
+{
+    auto kern = wqbmm_decode_tma_kernel<kBf16, kExact, kAligned>;
+    cudaError_t rc = once_per_device(g_tma_configured[variant],
+                                     [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmaSmem); });
+    if (rc != cudaSuccess) return rc;
+    kern<<<grid, kThreads, kTmaSmem, stream>>>(mw, mx, ta);
+    return cudaGetLastError();
+}
+
+constexpr int kTmaMaxGrid = 148 * 4 * 2;  // same workspace layout and bound as the other decode kernels
+
+}  // namespace
+
+bool wqbmm_decode_eligible(const OpsnnWqbmmParams* p);
+uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
+bool wqbmm_decode_fast_eligible(const OpsnnWqbmmParams* p);
+
+// What the bulk-copy data path needs beyond the ring kernels' conditions: 16-byte aligned x rows (tensor-map pitches) and a
+// device that can encode tensor maps.
+bool wqbmm_decode_tma_eligible(const OpsnnWqbmmParams* p)
+{
+    if (!wqbmm_decode_fast_eligible(p)) return false;
+    if (p->x_ld % 8 != 0 || (reinterpret_cast<uintptr_t>(p->x) % 16) != 0) return false;
+    if (p->n >= ((int64_t)1 << 31) || p->k >= ((int64_t)1 << 30)) return false;  // 32-bit tensor coordinates
+    return true;
+}
+
+// exact = true: the reference's default arithmetic; false: the group-wise form of innerPrecise = 1.
+int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact)
+{
+    TmaArgs ta{};
+    DecodeArgs& a = ta.d;
+    a.w = reinterpret_cast<const uint32_t*>(p->w);
+    a.w_ld32 = p->w_ld / 8;
+    a.x = p->x;
+    a.x_ld = p->x_ld;
+    a.scale = p->scale;
+    a.offset = p->offset;
+    a.scale_sg = p->group_size > 0 ? p->scale_sg : 0;
+    a.scale_sn = (int32_t)p->scale_sn;
+    a.bias = p->bias;
+    a.bias_dtype = p->bias_dtype;
+    a.y = p->y;
+    a.y_ld = p->y_ld;
+    a.m = (int32_t)p->m;
+    a.n = p->n;
+    a.k = p->k;
+    a.strips = (p->n + kStripCols - 1) / kStripCols;
+    a.ksteps = p->k / 16;
+    a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
+    ta.total_stages = (int32_t)((a.ksteps + kStageSteps - 1) / kStageSteps);
+    const bool single_group = a.steps_per_group >= a.ksteps;
+    const bool aligned = single_group || a.steps_per_group % kStageSteps == 0;
+    ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / kStageSteps);
+    const bool bf16 = p->x_dtype == ACL_BF16;
+    const int variant = (exact ? 4 : 0) + (bf16 ? 2 : 0) + (aligned ? 1 : 0);
+
+    const int resident = 2 * current_sm_count();
+    int64_t splits = resident / a.strips;
+    if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
+        int v = atoi(e);
+        if (v > 0) splits = v;
+    }
+    if (splits > ta.total_stages) splits = ta.total_stages;
+    if (splits * a.strips > kTmaMaxGrid) splits = kTmaMaxGrid / a.strips;
+    if (splits < 1) splits = 1;
+    a.splits = splits;
+    const int64_t grid64 = a.strips * splits;
+    if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+    const uint64_t tag_bytes = (((uint64_t)kTmaMaxGrid * 8 + 255) / 256) * 256;
+    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
+    a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
+    a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
+    a.nonce = next_nonce();
+    a.c_mask = 0x000F000Fu;
+    a.c_magic = bf16 ? Num<true>::kMagic : Num<false>::kMagic;
+    a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
+
+    CUtensorMap mw, mx;
+    if (!make_map_2d(&mw, p->w, (uint64_t)p->n / 2, (uint64_t)p->k, (uint64_t)p->w_ld / 2, kStageRows) ||
+        !make_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
+        return (int32_t)cudaErrorInvalidValue;
+
+    const int grid = (int)grid64;
+    cudaError_t rc;
+    switch (variant) {
+        case 0: rc = launch_variant<false, false, false>(0, grid, mw, mx, ta, stream); break;
+        case 1: rc = launch_variant<false, false, true>(1, grid, mw, mx, ta, stream); break;
+        case 2: rc = launch_variant<true, false, false>(2, grid, mw, mx, ta, stream); break;
+        case 3: rc = launch_variant<true, false, true>(3, grid, mw, mx, ta, stream); break;
+        case 4: rc = launch_variant<false, true, false>(4, grid, mw, mx, ta, stream); break;
+        case 5: rc = launch_variant<false, true, true>(5, grid, mw, mx, ta, stream); break;
+        case 6: rc = launch_variant<true, true, false>(6, grid, mw, mx, ta, stream); break;
+        default: rc = launch_variant<true, true, true>(7, grid, mw, mx, ta, stream); break;
+    }
+    note_launch(exact ? "wqbmm_decode" : "wqbmm_decode_fast");
+    return (int32_t)rc;
+}
+
+}  // namespace opsnn
+
+// Error word of the bulk-copy decode kernel on the current device: 0 when every bounded wait inside it completed. Synchronises the
+// device; reset != 0 clears the word after reading it.
+extern "C" __attribute__((visibility("default"))) uint32_t opsnn_wqbmm_decode_status(int32_t reset)
+{
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, opsnn::g_wq_tma_status, sizeof(v));
+    if (reset) {
+        unsigned int z = 0;
+        cudaMemcpyToSymbol(opsnn::g_wq_tma_status, &z, sizeof(z));
+    }
+    return v;
+}

@@ -417,12 +417,11 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
         const int vec = p->scale_sn == 1 && p->scale_sg % 8 == 0 && (reinterpret_cast<uintptr_t>(p->scale) & 15) == 0 &&
                         (p->offset == nullptr || (reinterpret_cast<uintptr_t>(p->offset) & 15) == 0);
         const size_t sm = (size_t)PN * PP * 4;
-        static bool configured = false;
-        if (!configured) {
+        static std::atomic<uint64_t> configured{0};
+        once_per_device(configured, [&] {
             cudaFuncSetAttribute(wq_dequant_nk_pairs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            cudaFuncSetAttribute(wq_dequant_nk_pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            configured = true;
-        }
+            return cudaFuncSetAttribute(wq_dequant_nk_pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        });
         if (bf) wq_dequant_nk_pairs_kernel<true><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
         else wq_dequant_nk_pairs_kernel<false><<<(unsigned)ptiles, NT, sm, stream>>>(*p, wdeq, kp, one, vec);
     } else if ((p->w_dtype == ACL_INT8 || p->w_dtype == ACL_FLOAT8_E4M3FN || p->w_dtype == ACL_FLOAT8_E5M2) && !p->trans_w &&

@@ -187,7 +187,9 @@ bool check_dtype(const Ctx& c)
         }
     } else if (c.mx()) {
         if (!c.fp4_in() && !c.fp8_in()) FAIL("mx needs fp8 x fp8 or fp4 x fp4 inputs");
-        if (c.has_bias && bias != ACL_FLOAT) FAIL("mx bias must be FLOAT");
+        // the reference takes a FLOAT bias only in this mode (quant_matmul_checker.cpp:1685-1687); a BF16 bias is accepted here as
+        // an extension (widened to fp32 exactly before the add), because serving stacks keep the bias in the activation dtype
+        if (c.has_bias && bias != ACL_FLOAT && bias != ACL_BF16) FAIL("mx bias must be FLOAT (or BF16, an extension of this library)");
         if (!in(out, {ACL_FLOAT16, ACL_BF16, ACL_FLOAT})) FAIL("out dtype %s not supported", dtype_name(out));
         if (c.has_x2o) FAIL("x2Offset not supported");
     } else if (c.int4_in() && c.has_x2o) {  // per-token per-group asymmetric int4

@@ -74,11 +74,17 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     if (sc.dtype != ACL_FLOAT16 && sc.dtype != ACL_BF16 && sc.dtype != ACL_FLOAT8_E8M0)
         WQ_INVALID("%s: antiquantScale dtype %s not supported", api, dtype_name(sc.dtype));
     if (sc.dtype != ACL_FLOAT8_E8M0 && sc.dtype != xd) WQ_INVALID("%s: antiquantScale dtype must equal x dtype", api);
+    // an e8m0 scale is the micro-scaling form and only goes with FLOAT4_E2M1 weights (:766 refuses it for fp8 weights;
+    // the integer weights have no mx golden at all)
+    if (sc.dtype == ACL_FLOAT8_E8M0 && wd != ACL_FLOAT4_E2M1)
+        WQ_INVALID("%s: a FLOAT8_E8M0 antiquantScale needs FLOAT4_E2M1 weights, got %s", api, dtype_name(wd));
     if (antiquantOffset) {
         if (wd == ACL_FLOAT8_E4M3FN || wd == ACL_HIFLOAT8 || wd == ACL_FLOAT4_E2M1) WQ_INVALID("%s: antiquantOffset must be null for fp8/fp4 weights", api);
         if (antiquantOffset->dtype != xd) WQ_INVALID("%s: antiquantOffset dtype must equal x dtype", api);
     }
-    if (quantScale != nullptr || quantOffset != nullptr) WQ_INVALID("%s: quantScale/quantOffset must be null on this target", api);
+    // INT8 output (quantScale / quantOffset) does not exist on this target: empty tensors count as absent, anything else is refused
+    if ((quantScale != nullptr && !quantScale->empty()) || (quantOffset != nullptr && !quantOffset->empty()))
+        WQ_INVALID("%s: quantScale/quantOffset must be null on this target", api);
     if (y->dtype != xd) WQ_INVALID("%s: y dtype must equal x dtype", api);
     if (bias) {
         if (!(bias->dtype == xd || (xd == ACL_BF16 && bias->dtype == ACL_FLOAT))) WQ_INVALID("%s: bias dtype %s not supported", api, dtype_name(bias->dtype));
@@ -146,6 +152,7 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     };
     p.x_dtype = xd;
     p.w_dtype = wd;
+    if (bias && bias->empty()) bias = nullptr;  // a 0-element bias is "no bias": nothing may be read through its pointer
     p.bias_dtype = bias ? (int)bias->dtype : -1;
     p.trans_w = trans_w ? 1 : 0;
     p.m = mx;
@@ -181,8 +188,6 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     if (!row_strided_view(y, &yld, &bs)) no_kernel("y must be contiguous or row-strided");
     p.y_ld = yld;
     if (wd == ACL_HIFLOAT8) no_kernel("HIFLOAT8 weights have no implementation here");
-    if ((quantScale != nullptr && !quantScale->empty()) || (quantOffset != nullptr && !quantOffset->empty()))
-        no_kernel("quantScale / quantOffset (INT8 output) have no implementation here");
     p.scale_dtype = sc.dtype == ACL_FLOAT8_E8M0 ? (int32_t)ACL_FLOAT8_E8M0 : 0;
     if (sc.dtype == ACL_FLOAT8_E8M0 && antiquantOffset) no_kernel("mx antiquant takes no offset");
 

@@ -44,6 +44,20 @@ def aclnn(pkg):
     return pkg.aclnn
 
 
+@pytest.fixture(autouse=True)
+def _device_status_words(request):
+    """After every GPU test: no kernel of the library may have given up a bounded wait. A give-up leaves the output
+    undefined, so without this check it could pass as (or hide behind) a parity mismatch."""
+    yield
+    if request.node.get_closest_marker("gpu") is None or "ops_nn_b200" not in sys.modules:
+        return
+    L = sys.modules["ops_nn_b200"].aclnn.lib()
+    umma = L.opsnn_qmm_umma_status(1)
+    decode = L.opsnn_wqbmm_decode_status(1)
+    assert umma == 0, "a tensor-core kernel gave up a bounded wait: status 0x%x" % umma
+    assert decode == 0, "the streaming decode kernel gave up a bounded wait: status %d" % decode
+
+
 def golden_names(prefix):
     return sorted(f[:-4] for f in os.listdir(GOLDEN) if f.startswith(prefix) and f.endswith(".npz"))
 

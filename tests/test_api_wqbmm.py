@@ -43,6 +43,11 @@ EXTRA = [
     ("transposed_weight_view", (4, 64), (64, 2176), (2176,), None, 0, (4, 2176), "float16", "int4", "float16", None, ND, True, OK),
     ("per_tensor_1d", (9, 96), (96, 40), (1,), None, 0, (9, 40), "bfloat16", "int8", "bfloat16", None, ND, False, OK),
     ("x_dtype_fp32", (9, 96), (96, 40), (1,), None, 0, (9, 40), "float32", "int8", "float32", None, ND, False, INVALID),
+    # an e8m0 (micro-scaling) antiquantScale goes with FLOAT4_E2M1 weights only (aclnn_weight_quant_batch_matmul_v2.cpp:766 refuses it
+    # for fp8 weights; integer weights have no mx form): without this rule an INT4 weight would reach kernels that read 16-bit scales
+    ("e8m0_scale_with_int4_weight", (16, 512), (512, 256), (16, 256), None, 32, (16, 256), "bfloat16", "int4", "float8_e8m0", None, ND, False, INVALID),
+    ("e8m0_scale_with_int8_weight", (16, 512), (512, 256), (16, 256), None, 32, (16, 256), "bfloat16", "int8", "float8_e8m0", None, ND, False, INVALID),
+    ("e8m0_scale_with_fp8_weight", (16, 512), (512, 256), (16, 256), None, 32, (16, 256), "bfloat16", "float8_e4m3fn", "float8_e8m0", None, ND, False, INVALID),
 ]
 
 

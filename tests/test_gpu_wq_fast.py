@@ -32,8 +32,9 @@ def test_fast_mode_fixture(aclnn, name):
     den = np.maximum(np.abs(ref), 0.05 * rms)
     rel = np.max(np.abs(got - ref) / den)
     assert rel <= (1e-2 if bf16 else 5e-3), (name, rel)
-    # one rounding of the output (bf16: 2^-9 of the value) plus, for fp16, the fp32 cancellation of the 1032 * sum(x) term
-    assert rel <= (2.0 ** -8 if bf16 else 2.0 ** -10) * 1.05, (name, rel)
+    # one rounding of the output (bf16: 2^-9 of the value, fp16: 2^-12) plus the fp32 cancellation of the B * sum(x) term (B = 136 /
+    # 1032), whose size depends on where the k ranges of the CTAs fall: within two output ulps for fp16
+    assert rel <= (2.0 ** -8 if bf16 else 2.0 ** -9) * 1.05, (name, rel)
     # and it is at least as close to the unrounded product as the default mode's golden is
     gold = a["out"].astype(np.float64)
     assert np.max(np.abs(got - ref) / den) <= np.max(np.abs(gold - ref) / den) + 1e-12

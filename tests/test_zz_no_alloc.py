@@ -104,3 +104,7 @@ def test_static_scratch_rejects_sizes_beyond_its_limit(aclnn):
     assert L.opsnn_wqbmm_decode_static_launch(ctypes.byref(p2), None) != 0
     assert "range" in aclnn.last_error()
     assert aclnn.launch_count() == before
+    p3 = _params(aclnn, t, y)
+    p3.k = 0  # no k-step at all: the kernel's prefetch would read weight rows that do not exist
+    assert L.opsnn_wqbmm_decode_static_launch(ctypes.byref(p3), None) != 0
+    assert aclnn.launch_count() == before
