@@ -422,7 +422,7 @@ def run_c3(torch, dev, aclnn, args, peaks, rank, world, dist):
     res = {"tm": tm, "kernel": kernel, "flops_global": 2.0 * m * k * n, "shard": [cb, ce],
            "parity": {"checked_elems": int(ref.size), "max_rel_err": err, "tol": 1e-2, "frac_isclose_rtol1e-3": close,
                       "unwritten_elems": unwritten, "ok": bool(err <= 1e-2 and not unwritten)}}
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         # CPU: a 512-row panel against this rank's whole weight shard (world 1: the whole weight)
         pr = 512
         a_p, s1_p = f8(x1[:pr]), s1[:pr].cpu().numpy()
@@ -433,7 +433,11 @@ def run_c3(torch, dev, aclnn, args, peaks, rank, world, dist):
         res["cpu_baseline"] = {"value": 2.0 * pr * k * nl / cpu / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                                "sample": "numpy restatement of the reference golden on rows [0, 512) x %d columns (%.2f s); rate, not "
                                          "extrapolated time" % (nl, cpu)}
-    res["gather"] = (lambda: shard.gather_columns(out, n, world, rank, 128)) if world > 1 else None
+    if world > 1:
+        full = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        res["gather"] = lambda: args.comm.gather_columns(out, n, 128, out=full)
+    else:
+        res["gather"] = None
     res["keep"] = (x1, s1, wsets, out)
     return res
 
@@ -572,7 +576,7 @@ def run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, which):
     tm = time_calls(torch, lambda i: step(i, False), args.steps, args.warmup, barrier=barrier)
     tm_t = time_calls(torch, lambda i: step(i, True), args.steps, args.warmup, barrier=barrier)
     res = {"tm": tm, "tm_weight_nk": tm_t, "kernel": kernels, "flops_global": 2.0 * B * m * k * n, "shard": [bb, be], "parity": parity}
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         # CPU: batch 0, a 512-row panel against the whole weight of that batch (c5: the quantiser oracle on the panel first)
         pr = 512
         rows_np = to_np_bf16(act[0][:pr])
@@ -587,7 +591,11 @@ def run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, which):
         res["cpu_baseline"] = {"value": 2.0 * pr * k * n / cpu / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                                "sample": "numpy restatement of the reference golden%s on batch 0, rows [0, 512) x all %d columns (%.2f s); "
                                          "rate, not extrapolated time" % ("" if f4 else " (quantiser + matmul)", n, cpu)}
-    res["gather"] = (lambda: shard.gather_batch(out, B, world, rank)) if world > 1 else None
+    if world > 1 and B % world == 0:
+        full = torch.empty((B, m, n), dtype=torch.bfloat16, device=dev)
+        res["gather"] = lambda: args.comm.gather_batch(out, B, out=full)
+    else:
+        res["gather"] = None
     res["keep"] = (act, x1, s1, x2, s2, x2t, s2t, bias, out)
     return res
 
@@ -625,18 +633,19 @@ def finish_tensor_workload(torch, dist, dev, res, kind, desc, peaks, world, args
     tf = res["flops_global"] / (avg * 1e-3) / 1e12
     entry = {"workload": desc, "ms_per_step": avg, "ms_median": med, "ms_min": mn, "value": tf,
              "unit": "TOP/s" if kind == "int8" else "TFLOP/s", "kernels": res["kernel"] if isinstance(res["kernel"], list) else [res["kernel"]],
-             "roofline": tensor_roofline(tf, kind, peaks[1], peaks[2]), "parity": dict(res["parity"], ok=bool(ok >= 1.0), ranks_checked=world),
+             "roofline": dict(tensor_roofline(tf / world, kind, peaks[1], peaks[2]),
+                              note="per GPU: the global rate / %d ranks against one GPU's peak" % world), "parity": dict(res["parity"], ok=bool(ok >= 1.0), ranks_checked=world),
              "cpu_baseline": res.get("cpu_baseline"), "sharding": "rank 0 of %d holds [%d, %d)" % (world, res["shard"][0], res["shard"][1])}
     if "tm_weight_nk" in res:
         tft = res["flops_global"] / (vals[3] * 1e-3) / 1e12
-        entry["weight_stored_nk"] = {"ms_per_step": vals[3], "ms_min": vals[5], "value": tft, "frac_of_measured": tft / entry["roofline"]["peak"],
-                                     "frac_of_datasheet": tft / entry["roofline"]["datasheet_dense_peak"],
+        entry["weight_stored_nk"] = {"ms_per_step": vals[3], "ms_min": vals[5], "value": tft, "frac_of_measured": tft / world / entry["roofline"]["peak"],
+                                     "frac_of_datasheet": tft / world / entry["roofline"]["datasheet_dense_peak"],
                                      "note": "same problem with x2 stored (n, k) and transposeX2 = true (no per-call re-layout of the weight)"}
     if gather_ms is not None:
         g = vals[-1]
         entry["with_gather"] = {"gather_ms": g, "ms_per_step": avg + g, "value": res["flops_global"] / ((avg + g) * 1e-3) / 1e12,
-                                "note": "all ranks receive the whole output (torch.distributed all_gather_into_tensor over NCCL + re-assembly), timed "
-                                        "separately after the matmul"}
+                                "note": "all ranks receive the whole output (opsnn_gather_columns / opsnn_gather_batch: one ncclAllGather, column shards "
+                                        "interleaved by one kernel), timed separately after the matmul"}
     if extra_note:
         entry["note"] = extra_note
     return entry
@@ -875,6 +884,7 @@ def main():
     aclnn, shard = pkg.aclnn, pkg.shard
     aclnn.lib()
     peaks = measured_peaks()
+    args.comm = aclnn.Comm(world, rank, dev) if world > 1 else None
     barrier = dist_barrier(torch, dist)
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -948,14 +958,15 @@ def main():
     # optional gather of the y shards (strong scaling, N > 1)
     gather_ms = None
     if world > 1:
+        y_full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         for _ in range(3):
-            shard.gather_columns(y, N, world, rank, 512)
+            args.comm.gather_columns(y, N, 512, out=y_full)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(args.steps):
             step(i)
-            shard.gather_columns(y, N, world, rank, 512)
+            args.comm.gather_columns(y, N, 512, out=y_full)
         e1.record()
         barrier()
         gather_ms = e0.elapsed_time(e1) / args.steps
@@ -1118,13 +1129,16 @@ def main():
             line["roofline"]["traffic_source"] = tj.get("source")
         if world > 1:
             line["with_gather"] = {"ms_per_step": gather_all_ms, "value": ALGO_BYTES / (gather_all_ms * 1e-3) / 1e9, "unit": "GB/s",
-                                   "note": "every step followed by the all-gather of the y shards (%d KB per rank, NCCL) + re-assembly" % (M * nl * 2 // 1024)}
+                                   "note": "every step followed by opsnn_gather_columns of the y shards (%d KB per rank: one strided copy, one ncclAllGather, one "
+                                           "interleave kernel)" % (M * nl * 2 // 1024)}
             line["weak"] = weak
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = c2_cpu_baseline(host)
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line))
+    if args.comm is not None:
+        args.comm.close()
     if dist is not None:
         dist.destroy_process_group()
 

@@ -159,6 +159,12 @@ OPSNN_API int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_c
  */
 OPSNN_API int32_t opsnn_wqbmm_decode_static_launch(const OpsnnWqbmmParams* p, void* stream);
 
+/* A 2-D byte matrix stored FRACTAL_NZ, [ceil(row_bytes / c0_bytes)][ceil(rows / r0)][r0][c0_bytes] (nz_to_nd of
+ * matmul/common/tests/st/arch35/matmul_golden_util.py:76-114 in the reference), rewritten row-major (rows, row_bytes) into dst.
+ * What aclnnWeightQuantBatchMatmulNz and aclnnQuantMatmulWeightNz run before their matmul. */
+OPSNN_API int32_t opsnn_nz_to_nd_launch(const void* src, void* dst, int64_t rows, int64_t row_bytes, int64_t r0, int64_t c0_bytes,
+                                        void* stream);
+
 /* ---- dynamic MX quant (aclnnDynamicMxQuant path)---------------------------------------------------------- */
 
 typedef struct OpsnnMxQuantParams {

@@ -70,6 +70,7 @@ def lib():
     T = c_void_p
     L.aclnnQuantMatmulV5GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, T, T, c_bool, c_bool, c_int64, T,
                                                       POINTER(c_uint64), POINTER(c_void_p)]
+    L.aclnnQuantMatmulWeightNzGetWorkspaceSize.argtypes = L.aclnnQuantMatmulV5GetWorkspaceSize.argtypes
     L.aclnnWeightQuantBatchMatmulV2GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, T, POINTER(c_uint64),
                                                                  POINTER(c_void_p)]
     L.aclnnWeightQuantBatchMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, T, T, c_int, c_int, T, POINTER(c_uint64),
@@ -81,7 +82,7 @@ def lib():
     L.aclnnConvertWeightToINT4PackGetWorkspaceSize.argtypes = [T, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV4GetWorkspaceSize.argtypes = [T, T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
     L.aclnnQuantMatmulV3GetWorkspaceSize.argtypes = [T, T, T, T, T, c_bool, c_bool, T, POINTER(c_uint64), POINTER(c_void_p)]
-    for name in ("aclnnQuantMatmulV5", "aclnnQuantMatmulV4", "aclnnQuantMatmulV3", "aclnnWeightQuantBatchMatmulV2",
+    for name in ("aclnnQuantMatmulV5", "aclnnQuantMatmulWeightNz", "aclnnQuantMatmulV4", "aclnnQuantMatmulV3", "aclnnWeightQuantBatchMatmulV2",
                  "aclnnWeightQuantBatchMatmulV3", "aclnnWeightQuantBatchMatmulNz", "aclnnDynamicMxQuant",
                  "aclnnConvertWeightToINT4Pack"):
         getattr(L, name).argtypes = [c_void_p, c_uint64, c_void_p, c_void_p]
@@ -101,6 +102,18 @@ def lib():
     L.opsnn_wqbmm_workspace_size.argtypes = [POINTER(WqbmmParams), c_int32]
     L.opsnn_wqbmm_select_kernel.restype = c_int32
     L.opsnn_wqbmm_select_kernel.argtypes = [POINTER(WqbmmParams)]
+    I64, I32, U64, VP = c_int64, c_int32, c_uint64, c_void_p
+    L.opsnn_shard_range.restype = None
+    L.opsnn_shard_range.argtypes = [I64, I32, I32, I64, POINTER(I64), POINTER(I64)]
+    L.opsnn_comm_unique_id.argtypes = [VP]
+    L.opsnn_comm_init.argtypes = [VP, I32, I32, POINTER(VP)]
+    L.opsnn_comm_destroy.argtypes = [VP]
+    L.opsnn_gather_columns_workspace.restype = U64
+    L.opsnn_gather_columns_workspace.argtypes = [I32, I64, I64, I64, I32]
+    L.opsnn_gather_columns.argtypes = [VP, VP, I64, I64, I64, I64, I32, VP, VP, U64, VP]
+    L.opsnn_gather_batch.argtypes = [VP, VP, I64, U64, VP, VP]
+    for name in ("opsnn_comm_unique_id", "opsnn_comm_init", "opsnn_comm_destroy", "opsnn_gather_columns", "opsnn_gather_batch"):
+        getattr(L, name).restype = c_int32
     _lib = L
     return L
 
@@ -193,9 +206,10 @@ def _workspace(nbytes, like):
 # ---- phase-1-only helpers (return the raw status; used by the argument-validation tests) -----------------------
 
 def quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, y_scale, x1_offset, x2_offset, y_offset, bias,
-                                       transpose_x1, transpose_x2, group_size, out):
+                                       transpose_x1, transpose_x2, group_size, out, weight_nz=False):
     ws, ex = c_uint64(0), c_void_p(0)
-    st = lib().aclnnQuantMatmulV5GetWorkspaceSize(_h(x1), _h(x2), _h(x1_scale), _h(x2_scale), _h(y_scale), _h(x1_offset),
+    fn = lib().aclnnQuantMatmulWeightNzGetWorkspaceSize if weight_nz else lib().aclnnQuantMatmulV5GetWorkspaceSize
+    st = fn(_h(x1), _h(x2), _h(x1_scale), _h(x2_scale), _h(y_scale), _h(x1_offset),
                                                   _h(x2_offset), _h(y_offset), _h(bias), bool(transpose_x1),
                                                   bool(transpose_x2), int(group_size), _h(out), byref(ws), byref(ex))
     return st, ws.value, ex
@@ -252,20 +266,21 @@ def destroy_executor(ex):
 # ---- both phases on device tensors -------------------------------------------------------------------------------
 
 def quant_matmul_v5(x1, x2, x1_scale, x2_scale, out, bias=None, transpose_x1=False, transpose_x2=False, group_size=0,
-                    x2_offset=None, workspace=None, y_scale=None):
-    """Runs aclnnQuantMatmulV5 on the current torch CUDA stream. Arguments are `Tensor` descriptors over device memory;
-    `out` is written in place. Returns the workspace size used."""
+                    x2_offset=None, workspace=None, y_scale=None, weight_nz=False):
+    """Runs aclnnQuantMatmulV5 (aclnnQuantMatmulWeightNz with weight_nz: x2 described as FRACTAL_NZ) on the current torch CUDA
+    stream. Arguments are `Tensor` descriptors over device memory; `out` is written in place. Returns the workspace size used."""
     st, ws_size, ex = quant_matmul_v5_get_workspace_size(x1, x2, x1_scale, x2_scale, y_scale, None, x2_offset, None, bias,
-                                                         transpose_x1, transpose_x2, group_size, out)
+                                                         transpose_x1, transpose_x2, group_size, out, weight_nz)
     if st != ACLNN_SUCCESS:
-        raise AclnnError("aclnnQuantMatmulV5GetWorkspaceSize", st)
+        raise AclnnError("aclnnQuantMatmul%sGetWorkspaceSize" % ("WeightNz" if weight_nz else "V5"), st)
     if workspace is not None and workspace.numel() >= ws_size:
         keep, wp = workspace, c_void_p(workspace.data_ptr())
     else:
         keep, wp = _workspace(ws_size, out._keep)
-    st = lib().aclnnQuantMatmulV5(wp, c_uint64(ws_size if keep is None else keep.numel()), ex, _stream())
+    run = lib().aclnnQuantMatmulWeightNz if weight_nz else lib().aclnnQuantMatmulV5
+    st = run(wp, c_uint64(ws_size if keep is None else keep.numel()), ex, _stream())
     if st != ACLNN_SUCCESS:
-        raise AclnnError("aclnnQuantMatmulV5", st)
+        raise AclnnError("aclnnQuantMatmul%s" % ("WeightNz" if weight_nz else "V5"), st)
     return ws_size
 
 
@@ -316,3 +331,79 @@ def dynamic_mx_quant(x, y_out, mxscale_out, dst_type, axis=-1, round_mode=b"rint
     st = lib().aclnnDynamicMxQuant(c_void_p(0), c_uint64(0), ex, _stream())
     if st != ACLNN_SUCCESS:
         raise AclnnError("aclnnDynamicMxQuant", st)
+
+
+# ---- multi-GPU helpers (include/opsnn_b200_shard.h) --------------------------------------------------------------
+
+def shard_range(total, world, rank, multiple=1):
+    """opsnn_shard_range: [begin, end) of `rank`'s share (the C mirror of shard.split_range)."""
+    b, e = c_int64(0), c_int64(0)
+    lib().opsnn_shard_range(int(total), int(world), int(rank), int(multiple), byref(b), byref(e))
+    return b.value, e.value
+
+
+class Comm:
+    """The library's own NCCL communicator (opsnn_comm_*): created once per process from an initialised torch.distributed group,
+    which is only used to hand rank 0's 128-byte NCCL id to the other ranks."""
+
+    def __init__(self, world, rank, device, broadcast=None):
+        import torch
+
+        self.world, self.rank, self.device = int(world), int(rank), device
+        idbuf = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            raw = (ctypes.c_ubyte * 128)()
+            rc = lib().opsnn_comm_unique_id(raw)
+            if rc != 0:
+                raise RuntimeError("opsnn_comm_unique_id failed (%d): %s" % (rc, last_error()))
+            idbuf = torch.tensor(list(raw), dtype=torch.uint8)
+        if world > 1:
+            if broadcast is None:
+                import torch.distributed as dist
+
+                t = idbuf.to(device) if dist.get_backend() == "nccl" else idbuf
+                dist.broadcast(t, src=0)
+                idbuf = t.cpu()
+            else:
+                idbuf = broadcast(idbuf)
+        raw = (ctypes.c_ubyte * 128)(*[int(v) for v in idbuf.tolist()])
+        h = c_void_p(0)
+        rc = lib().opsnn_comm_init(raw, self.world, self.rank, byref(h))
+        if rc != 0:
+            raise RuntimeError("opsnn_comm_init failed (%d): %s" % (rc, last_error()))
+        self.handle = h
+        self._ws = None
+
+    def gather_columns(self, y_local, n_total, multiple=8, out=None):
+        """Every rank receives the (m, n_total) output from the ranks' (m, width) column shards; enqueued on the current stream."""
+        import torch
+
+        m = y_local.shape[0]
+        eb = y_local.element_size()
+        need = lib().opsnn_gather_columns_workspace(self.world, m, int(n_total), int(multiple), eb)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(int(need), dtype=torch.uint8, device=y_local.device)
+        if out is None:
+            out = torch.empty((m, int(n_total)), dtype=y_local.dtype, device=y_local.device)
+        rc = lib().opsnn_gather_columns(self.handle, c_void_p(y_local.data_ptr()), int(y_local.stride(0)), m, int(n_total), int(multiple), eb,
+                                        c_void_p(out.data_ptr()), c_void_p(self._ws.data_ptr()), c_uint64(self._ws.numel()), _stream())
+        if rc != 0:
+            raise RuntimeError("opsnn_gather_columns failed (%d): %s" % (rc, last_error()))
+        return out
+
+    def gather_batch(self, y_local, batch_total, out=None):
+        """Every rank receives the (batch_total, ...) output from equal contiguous batch shards; enqueued on the current stream."""
+        import torch
+
+        per = y_local[0].numel() * y_local.element_size()
+        if out is None:
+            out = torch.empty((int(batch_total),) + tuple(y_local.shape[1:]), dtype=y_local.dtype, device=y_local.device)
+        rc = lib().opsnn_gather_batch(self.handle, c_void_p(y_local.data_ptr()), int(batch_total), c_uint64(per), c_void_p(out.data_ptr()), _stream())
+        if rc != 0:
+            raise RuntimeError("opsnn_gather_batch failed (%d): %s" % (rc, last_error()))
+        return out
+
+    def close(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            lib().opsnn_comm_destroy(self.handle)
+            self.handle = c_void_p(0)

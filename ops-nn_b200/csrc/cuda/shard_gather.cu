@@ -1,0 +1,225 @@
+// Multi-GPU side of the path: partition arithmetic and the optional gather of the output shards, behind the C ABI.
+//
+// The quantised matmuls shard with no data-path collective (weight columns for the decode and per-block shapes, the batch
+// axis for the batched MX shapes); the reference has no multi-device code for these operators. What a caller may still want
+// is the whole output on every rank: one ncclAllGather of the shards over NVLink. Batch shards land in place (they are
+// contiguous in the full output); column shards land rank-major in workspace and one small kernel interleaves them into
+// rows. NCCL is not linked: its five entry points are resolved at run time from the libnccl.so.2 the process already
+// carries (the one a PyTorch host loaded, or the system one), so the library loads on machines without it.
+#include <dlfcn.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "opsnn_b200_shard.h"
+
+namespace opsnn {
+
+void set_err(const char* fmt, ...);
+
+namespace {
+
+struct NcclUniqueId {
+    char internal[128];
+};
+using ncclComm_t = void*;
+struct NcclApi {
+    int (*GetUniqueId)(NcclUniqueId*) = nullptr;
+    int (*CommInitRank)(ncclComm_t*, int, NcclUniqueId, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int /*ncclDataType_t*/, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+
+const NcclApi& nccl()
+{
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+        if (h == nullptr) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) return;
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.GetErrorString;
+    });
+    return api;
+}
+
+struct Comm {
+    ncclComm_t nccl = nullptr;
+    int world = 1, rank = 0;
+};
+
+int32_t nccl_fail(const char* what, int rc)
+{
+    set_err("%s: NCCL error %d (%s)", what, rc, nccl().GetErrorString ? nccl().GetErrorString(rc) : "?");
+    return (int32_t)cudaErrorUnknown;
+}
+
+// recv is [world][m][wmax] elements of `eb` bytes; rank r's block holds its columns [begin_r, end_r) in its first end_r - begin_r
+// columns. 16-byte pieces when every width and the row pitch allow it, else bytes.
+template <typename T>
+__global__ void interleave_columns_kernel(const T* __restrict__ recv, T* __restrict__ full, int64_t m, int64_t n_total_t, int64_t wmax_t,
+                                          int32_t world, int64_t units, int64_t mult_t)
+{
+    const int64_t base = units / world, extra = units % world;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < m * n_total_t; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / n_total_t, col = i - row * n_total_t;
+        // owner of column `col`: the first `extra` ranks hold base + 1 units of `mult_t` columns, the others base; a ragged tail
+        // shorter than one unit belongs to the last rank that owns anything
+        int64_t u = col / mult_t;
+        if (u >= units) u = units - 1;
+        int64_t r = (u < extra * (base + 1)) ? u / (base + 1) : extra + (base > 0 ? (u - extra * (base + 1)) / base : 0);
+        const int64_t begin = (r * base + (r < extra ? r : extra)) * mult_t;
+        full[i] = recv[(r * m + row) * wmax_t + (col - begin)];
+    }
+}
+
+}  // namespace
+}  // namespace opsnn
+
+using namespace opsnn;
+
+extern "C" {
+
+void opsnn_shard_range(int64_t total, int32_t world, int32_t rank, int64_t multiple, int64_t* begin, int64_t* end)
+{
+    int64_t b = 0, e = 0;
+    if (world >= 1 && rank >= 0 && rank < world && total >= 0 && multiple >= 1) {
+        const int64_t units = total / multiple, base = units / world, extra = units % world;
+        const int64_t bu = rank * base + (rank < extra ? rank : extra);
+        const int64_t eu = bu + base + (rank < extra ? 1 : 0);
+        b = bu * multiple;
+        e = eu * multiple;
+        const int64_t tail = total - units * multiple;
+        if (tail != 0) {
+            const int64_t last_owner = units ? (world < units ? world : units) - 1 : 0;
+            if (rank == last_owner) e += tail;
+            if (units == 0 && rank != 0) b = e = total;
+        }
+    }
+    if (begin) *begin = b;
+    if (end) *end = e;
+}
+
+int32_t opsnn_comm_unique_id(void* id128)
+{
+    if (id128 == nullptr) return (int32_t)cudaErrorInvalidValue;
+    if (!nccl().ok) {
+        set_err("opsnn_comm_unique_id: libnccl.so.2 could not be loaded");
+        return (int32_t)cudaErrorNotSupported;
+    }
+    const int rc = nccl().GetUniqueId(reinterpret_cast<NcclUniqueId*>(id128));
+    return rc == 0 ? 0 : nccl_fail("ncclGetUniqueId", rc);
+}
+
+int32_t opsnn_comm_init(const void* id128, int32_t world, int32_t rank, void** comm)
+{
+    if (id128 == nullptr || comm == nullptr || world < 1 || rank < 0 || rank >= world) return (int32_t)cudaErrorInvalidValue;
+    if (!nccl().ok) {
+        set_err("opsnn_comm_init: libnccl.so.2 could not be loaded");
+        return (int32_t)cudaErrorNotSupported;
+    }
+    Comm* c = new Comm();
+    c->world = world;
+    c->rank = rank;
+    NcclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    const int rc = nccl().CommInitRank(&c->nccl, world, id, rank);
+    if (rc != 0) {
+        delete c;
+        return nccl_fail("ncclCommInitRank", rc);
+    }
+    *comm = c;
+    return 0;
+}
+
+int32_t opsnn_comm_destroy(void* comm)
+{
+    if (comm == nullptr) return 0;
+    Comm* c = static_cast<Comm*>(comm);
+    const int rc = c->nccl ? nccl().CommDestroy(c->nccl) : 0;
+    delete c;
+    return rc == 0 ? 0 : nccl_fail("ncclCommDestroy", rc);
+}
+
+uint64_t opsnn_gather_columns_workspace(int32_t world, int64_t m, int64_t n_total, int64_t multiple, int32_t elem_bytes)
+{
+    int64_t wmax = 0;
+    for (int32_t r = 0; r < world; ++r) {
+        int64_t b, e;
+        opsnn_shard_range(n_total, world, r, multiple, &b, &e);
+        if (e - b > wmax) wmax = e - b;
+    }
+    // the padded send block of this rank + the rank-major receive area
+    return (uint64_t)(world + 1) * (uint64_t)m * (uint64_t)wmax * (uint64_t)elem_bytes + 512;
+}
+
+int32_t opsnn_gather_columns(void* comm, const void* y_local, int64_t y_local_ld, int64_t m, int64_t n_total, int64_t multiple,
+                             int32_t elem_bytes, void* y_full, void* workspace, uint64_t workspace_size, void* stream)
+{
+    if (comm == nullptr || y_local == nullptr || y_full == nullptr || m < 0 || n_total < 0 || multiple < 1 ||
+        (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4))
+        return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (m == 0 || n_total == 0) return 0;
+    int64_t wmax = 0, mine_b = 0, mine_e = 0;
+    for (int32_t r = 0; r < c->world; ++r) {
+        int64_t b, e;
+        opsnn_shard_range(n_total, c->world, r, multiple, &b, &e);
+        if (e - b > wmax) wmax = e - b;
+        if (r == c->rank) mine_b = b, mine_e = e;
+    }
+    if (workspace == nullptr || workspace_size < opsnn_gather_columns_workspace(c->world, m, n_total, multiple, elem_bytes)) {
+        set_err("opsnn_gather_columns: workspace of %llu bytes needed", (unsigned long long)opsnn_gather_columns_workspace(c->world, m, n_total, multiple, elem_bytes));
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255);
+    const size_t block = (size_t)m * (size_t)wmax * (size_t)elem_bytes;
+    uint8_t* send = ws;
+    uint8_t* recv = ws + block;
+    // this rank's (m, width) shard into the head of a (m, wmax) block: one strided copy on the stream
+    cudaError_t rc = cudaMemcpy2DAsync(send, (size_t)wmax * elem_bytes, y_local, (size_t)y_local_ld * elem_bytes, (size_t)(mine_e - mine_b) * elem_bytes,
+                                       (size_t)m, cudaMemcpyDeviceToDevice, s);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    const int nrc = nccl().AllGather(send, recv, block, 0 /* ncclInt8: the payload is moved as bytes */, c->nccl, s);
+    if (nrc != 0) return nccl_fail("ncclAllGather", nrc);
+    const int64_t units = n_total / multiple;
+    const int64_t total = m * n_total;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 1184 ? (total + threads - 1) / threads : 1184);
+    if (elem_bytes == 2)
+        interleave_columns_kernel<uint16_t><<<blocks, threads, 0, s>>>(reinterpret_cast<const uint16_t*>(recv), static_cast<uint16_t*>(y_full), m, n_total,
+                                                                     wmax, c->world, units, multiple);
+    else if (elem_bytes == 4)
+        interleave_columns_kernel<uint32_t><<<blocks, threads, 0, s>>>(reinterpret_cast<const uint32_t*>(recv), static_cast<uint32_t*>(y_full), m, n_total,
+                                                                     wmax, c->world, units, multiple);
+    else
+        interleave_columns_kernel<uint8_t><<<blocks, threads, 0, s>>>(recv, static_cast<uint8_t*>(y_full), m, n_total, wmax, c->world, units, multiple);
+    note_launch("gather_interleave");
+    return (int32_t)cudaGetLastError();
+}
+
+int32_t opsnn_gather_batch(void* comm, const void* y_local, int64_t batch_total, uint64_t bytes_per_batch, void* y_full, void* stream)
+{
+    if (comm == nullptr || y_local == nullptr || y_full == nullptr || batch_total < 0) return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    if (batch_total % c->world != 0) {
+        set_err("opsnn_gather_batch: %lld batches do not divide over %d ranks (ncclAllGather moves equal shares)", (long long)batch_total, c->world);
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    if (batch_total == 0 || bytes_per_batch == 0) return 0;
+    const size_t share = (size_t)(batch_total / c->world) * (size_t)bytes_per_batch;
+    // in place when the caller's shard already sits at its slot of y_full (NCCL's in-place rule), else from y_local
+    const int nrc = nccl().AllGather(y_local, y_full, share, 0, c->nccl, static_cast<cudaStream_t>(stream));
+    return nrc == 0 ? 0 : nccl_fail("ncclAllGather", nrc);
+}
+
+}  // extern "C"

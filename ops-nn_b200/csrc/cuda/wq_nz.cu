@@ -63,3 +63,22 @@ int32_t wq_nz_launch(const OpsnnWqbmmParams* p, void* dst, cudaStream_t stream)
 }
 
 }  // namespace opsnn
+
+// Any 2-D byte matrix stored FRACTAL_NZ, [ceil(row_bytes / c0_bytes)][ceil(rows / r0)][r0][c0_bytes], -> row-major (rows, row_bytes).
+extern "C" __attribute__((visibility("default"))) int32_t opsnn_nz_to_nd_launch(const void* src, void* dst, int64_t rows, int64_t row_bytes,
+                                                                                int64_t r0, int64_t c0_bytes, void* stream)
+{
+    using namespace opsnn;
+    if (src == nullptr || dst == nullptr || rows < 0 || row_bytes < 0 || r0 <= 0 || c0_bytes <= 0) return (int32_t)cudaErrorInvalidValue;
+    const int64_t r1 = (rows + r0 - 1) / r0;
+    const bool wide = row_bytes % 16 == 0 && c0_bytes % 16 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+    const int64_t work = rows * (wide ? row_bytes / 16 : row_bytes);
+    if (work == 0) return 0;
+    int64_t grid = (work + 255) / 256;
+    if (grid > 148 * 32) grid = 148 * 32;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (wide) nz_to_nd_kernel<uint4><<<(unsigned)grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, row_bytes, r0, c0_bytes, r1);
+    else nz_to_nd_kernel<uint8_t><<<(unsigned)grid, 256, 0, s>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, row_bytes, r0, c0_bytes, r1);
+    note_launch("nz_to_nd");
+    return (int32_t)cudaGetLastError();
+}

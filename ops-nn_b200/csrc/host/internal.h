@@ -46,6 +46,10 @@ struct aclOpExecutor {
     OpsnnWqbmmParams wq{};
     OpsnnMxQuantParams mxq{};
     OpsnnPackB4Params pack{};
+    // aclnnQuantMatmulWeightNz: x2 arrives FRACTAL_NZ and is rewritten row-major into the head of the workspace before the matmul
+    const void* nz_src = nullptr;
+    int64_t nz_rows = 0, nz_row_bytes = 0, nz_r0 = 0, nz_c0_bytes = 0;
+    uint64_t nz_bytes = 0;
 };
 
 namespace opsnn {

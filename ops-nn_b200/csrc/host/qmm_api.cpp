@@ -11,6 +11,7 @@
 
 #include "aclnnop/aclnn_quant_matmul_v4.h"
 #include "aclnnop/aclnn_quant_matmul_v5.h"
+#include "aclnnop/aclnn_quant_matmul_weight_nz.h"
 #include "internal.h"
 
 using namespace opsnn;
@@ -755,42 +756,123 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
     return ACLNN_SUCCESS;
 }
 
-aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+static aclnnStatus qmm_run(const char* api, void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
     clear_err();
     if (executor == nullptr) {
-        set_err("aclnnQuantMatmulV5: executor is nullptr");
+        set_err("%s: executor is nullptr", api);
         return ACLNN_ERR_PARAM_NULLPTR;
     }
     std::unique_ptr<aclOpExecutor> exec(executor);  // phase 2 consumes the executor
     if (exec->magic != 0x4F50534E || exec->kind != ExecKind::kQmm) {
         exec.release();
-        set_err("aclnnQuantMatmulV5: executor was not created by aclnnQuantMatmulV5GetWorkspaceSize");
+        set_err("%s: executor was not created by the matching GetWorkspaceSize call", api);
         return ACLNN_ERR_PARAM_INVALID;
     }
     exec->magic = 0;
     if (exec->nothing_to_do) return ACLNN_SUCCESS;
     if (exec->unsupported) {
-        set_err("aclnnQuantMatmulV5: %s", exec->unsupported_why.c_str());
+        set_err("%s: %s", api, exec->unsupported_why.c_str());
         return ACLNN_ERR_INNER_FIND_KERNEL_ERROR;
     }
     if (workspaceSize < exec->workspace_size || (exec->workspace_size > 0 && workspace == nullptr)) {
-        set_err("aclnnQuantMatmulV5: workspace too small (%lu < %lu)", (unsigned long)workspaceSize,
-                (unsigned long)exec->workspace_size);
+        set_err("%s: workspace too small (%lu < %lu)", api, (unsigned long)workspaceSize, (unsigned long)exec->workspace_size);
         return ACLNN_ERR_PARAM_INVALID;
     }
+    if (exec->nz_bytes != 0) {  // FRACTAL_NZ x2: row-major copy into the head of the workspace, the matmul gets the rest
+        if (exec->nz_src == nullptr) {
+            set_err("%s: a tensor was created without a device address", api);
+            return ACLNN_ERR_PARAM_NULLPTR;
+        }
+        const int32_t rc = opsnn_nz_to_nd_launch(exec->nz_src, workspace, exec->nz_rows, exec->nz_row_bytes, exec->nz_r0, exec->nz_c0_bytes, stream);
+        if (rc != 0) {
+            set_err("%s: the FRACTAL_NZ -> row-major copy failed with CUDA error %d", api, rc);
+            return ACLNN_ERR_RUNTIME_ERROR;
+        }
+        exec->qmm.b = workspace;
+        workspace = static_cast<uint8_t*>(workspace) + exec->nz_bytes;
+        workspaceSize -= exec->nz_bytes;
+    }
     if (exec->qmm.a == nullptr || exec->qmm.b == nullptr || exec->qmm.out == nullptr || exec->qmm.scale_b == nullptr) {
-        set_err("aclnnQuantMatmulV5: a tensor was created without a device address");
+        set_err("%s: a tensor was created without a device address", api);
         return ACLNN_ERR_PARAM_NULLPTR;
     }
     exec->qmm.workspace = workspace;
     exec->qmm.workspace_size = workspaceSize;
     int32_t rc = opsnn_qmm_launch(&exec->qmm, exec->kernel_choice, stream);
     if (rc != 0) {
-        set_err("aclnnQuantMatmulV5: kernel launch failed with CUDA error %d", rc);
+        const std::string why = aclGetRecentErrMsg() ? aclGetRecentErrMsg() : "";
+        set_err("%s: kernel launch failed with CUDA error %d%s%s", api, rc, why.empty() ? "" : ": ", why.c_str());
         return ACLNN_ERR_RUNTIME_ERROR;
     }
     return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return qmm_run("aclnnQuantMatmulV5", workspace, workspaceSize, executor, stream);
+}
+
+// ---- aclnnQuantMatmulWeightNz (matmul/quant_batch_matmul_v3/op_api/aclnn_quant_matmul_weight_nz.h:41-55): aclnnQuantMatmulV5's
+// arguments with x2 stored FRACTAL_NZ. The fractal layout feeds the Ascend cube unit and has no use on this hardware, so phase 2
+// first rewrites x2 row-major into the head of the workspace (one copy kernel) and the ND plan runs on that. ----
+
+aclnnStatus aclnnQuantMatmulWeightNzGetWorkspaceSize(const aclTensor* x1, const aclTensor* x2, const aclTensor* x1Scale,
+                                                     const aclTensor* x2Scale, const aclTensor* yScale, const aclTensor* x1Offset,
+                                                     const aclTensor* x2Offset, const aclTensor* yOffset, const aclTensor* bias,
+                                                     bool transposeX1, bool transposeX2, int64_t groupSize, aclTensor* out,
+                                                     uint64_t* workspaceSize, aclOpExecutor** executor)
+{
+    const char* api = "aclnnQuantMatmulWeightNzGetWorkspaceSize";
+    clear_err();
+    if (workspaceSize == nullptr || executor == nullptr || x2 == nullptr) {
+        set_err("%s: x2, workspaceSize and executor are required", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (x2->format != ACL_FORMAT_FRACTAL_NZ && x2->format != ACL_FORMAT_FRACTAL_NZ_C0_32) {  // aclnn_quant_matmul_v4.cpp:855
+        set_err("%s: x2's storage format must be FRACTAL_NZ", api);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    // storage dims [ceil(cols / c0), ceil(rows / r0), r0, c0] over the 2-D matrix the view describes
+    const auto& sd = x2->storage_shape;
+    const int bits = dtype_bits(x2->dtype);
+    if (x2->rank() != 2 || sd.size() != 4 || bits == 0) {
+        set_err("%s: a FRACTAL_NZ x2 needs a 2-D view and 4 storage dims", api);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    const int64_t rows = x2->shape[0], cols = x2->shape[1], c1 = sd[0], r1 = sd[1], r0 = sd[2], c0 = sd[3];
+    if (r0 <= 0 || c0 <= 0 || r0 > 4096 || c0 > 4096 || c1 != (cols + c0 - 1) / c0 || r1 != (rows + r0 - 1) / r0 || (cols * bits) % 8 != 0 ||
+        (c0 * bits) % 8 != 0) {
+        set_err("%s: storage dims [%ld,%ld,%ld,%ld] do not tile the (%ld,%ld) view", api, (long)c1, (long)r1, (long)r0, (long)c0, (long)rows,
+                (long)cols);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    aclTensor nd = *x2;  // the plan sees the row-major matrix the pre-pass leaves in the workspace
+    nd.format = ACL_FORMAT_ND;
+    nd.strides = {cols, 1};
+    nd.storage_shape = nd.shape;
+    nd.offset = 0;
+    nd.data = reinterpret_cast<void*>(uintptr_t(256));  // stand-in with allocation alignment: kernel selection looks at alignment only
+    const aclnnStatus st = aclnnQuantMatmulV5GetWorkspaceSize(x1, &nd, x1Scale, x2Scale, yScale, x1Offset, x2Offset, yOffset, bias, transposeX1,
+                                                              transposeX2, groupSize, out, workspaceSize, executor);
+    if (st != ACLNN_SUCCESS) return st;
+    aclOpExecutor* exec = *executor;
+    exec->qmm.b = nullptr;
+    exec->nz_src = x2->data == nullptr ? nullptr : data_ptr(x2);
+    exec->nz_rows = rows;
+    exec->nz_row_bytes = cols * bits / 8;
+    exec->nz_r0 = r0;
+    exec->nz_c0_bytes = c0 * bits / 8;
+    exec->nz_bytes = (((uint64_t)rows * (uint64_t)exec->nz_row_bytes) + 255u) & ~(uint64_t)255u;
+    if (exec->nothing_to_do) exec->nz_bytes = 0;
+    exec->workspace_size += exec->nz_bytes;
+    *workspaceSize = exec->workspace_size;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus aclnnQuantMatmulWeightNz(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
+{
+    return qmm_run("aclnnQuantMatmulWeightNz", workspace, workspaceSize, executor, stream);
 }
 
 // ---- older entry points of the same operator (matmul/quant_batch_matmul_v3/op_api/aclnn_quant_matmul_v4.h:41-60,

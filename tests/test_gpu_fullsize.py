@@ -27,7 +27,7 @@ def bench():
 
 
 def _args(workload):
-    return argparse.Namespace(steps=3, warmup=3, no_cpu_baseline=True, workload=workload, batch=0)
+    return argparse.Namespace(steps=3, warmup=3, no_cpu_baseline=True, workload=workload, batch=0, comm=None)
 
 
 def test_c3_fp8_perblock_full_size(aclnn, bench):

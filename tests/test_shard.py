@@ -122,3 +122,15 @@ def test_two_rank_gloo_shard_compute_gather():
         for p in procs:
             assert p.exitcode == 0
         assert dict(ret) == {0: (True, True), 1: (True, True)}
+
+
+def test_c_abi_shard_range_equals_the_python_mirror(aclnn, pkg):
+    """opsnn_shard_range (the C-ABI planner a non-Python host binds) and shard.split_range are the same function."""
+    sh = pkg.shard
+    for total in (0, 1, 7, 8, 100, 127, 128, 1000, 3584, 18432, 28672):
+        for world in (1, 2, 3, 4, 8):
+            for multiple in (1, 8, 128, 512):
+                got = [aclnn.shard_range(total, world, r, multiple) for r in range(world)]
+                want = [sh.split_range(total, world, r, multiple) for r in range(world)]
+                assert got == want, (total, world, multiple, got, want)
+                assert got[0][0] == 0 and got[-1][1] <= total and sum(e - b for b, e in got) == total

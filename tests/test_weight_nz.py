@@ -69,3 +69,55 @@ def test_nz_weight_gives_the_row_major_result(aclnn, case):
     got = out_to_np(y).astype(np.float64)
     rms = np.sqrt(np.mean(want ** 2))
     assert np.all(np.abs(got - want) <= 2 * 2.0 ** -7 * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
+
+
+def test_quant_matmul_weight_nz_argument_rules(aclnn):
+    """aclnnQuantMatmulWeightNz (aclnn_quant_matmul_weight_nz.h:41-55 of the reference): x2 must be FRACTAL_NZ with storage dims that
+    tile its view; the reported workspace includes the row-major copy."""
+    T = aclnn.Tensor
+    x1, out = T((32, 64), "int8"), T((32, 128), "bfloat16")
+    s2 = T((128,), "float32")
+    x2_nz = T((64, 128), "int8", fmt=ACL_FORMAT_FRACTAL_NZ, storage_shape=(4, 4, 16, 32))
+    st, ws, ex = aclnn.quant_matmul_v5_get_workspace_size(x1, x2_nz, None, s2, None, None, None, None, None, False, False, 0, out,
+                                                          weight_nz=True)
+    assert st == 0 and ws >= 64 * 128, (st, ws, aclnn.last_error())
+    aclnn.destroy_executor(ex)
+    st, _, _ = aclnn.quant_matmul_v5_get_workspace_size(x1, T((64, 128), "int8"), None, s2, None, None, None, None, None, False, False, 0,
+                                                        out, weight_nz=True)
+    assert st == 161002  # row-major x2 is refused by this entry point ...
+    st, _, _ = aclnn.quant_matmul_v5_get_workspace_size(x1, x2_nz, None, s2, None, None, None, None, None, False, False, 0, out)
+    assert st == 161002  # ... and a fractal one by aclnnQuantMatmulV5
+    bad = T((64, 128), "int8", fmt=ACL_FORMAT_FRACTAL_NZ, storage_shape=(4, 3, 16, 32))
+    st, _, _ = aclnn.quant_matmul_v5_get_workspace_size(x1, bad, None, s2, None, None, None, None, None, False, False, 0, out, weight_nz=True)
+    assert st == 161002
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [(128, 512, 256, False, 16, 32), (96, 200, 176, False, 16, 32), (64, 256, 320, True, 16, 32)],
+                         ids=["aligned", "ragged", "x2_stored_nk"])
+def test_quant_matmul_weight_nz_gives_the_nd_result(aclnn, case):
+    """int8 per-token x per-channel: the FRACTAL_NZ call equals the ND call bit for bit (and the oracle)."""
+    import torch
+
+    from gpu_util import DEV, out_to_np
+    from oracle import qbmm_oracle
+
+    m, k, n, tb, r0, c0 = case
+    rng = np.random.default_rng(case_seed(case))
+    x1 = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (n, k) if tb else (k, n), dtype=np.int8)  # the stored 2-D matrix
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, transpose_x2=tb, out_dtype="bfloat16")
+    nz = wqbmm_oracle.nd_to_nz(x2, r0, c0)
+    t = lambda a: aclnn.from_torch(torch.from_numpy(np.ascontiguousarray(a)).to(DEV))  # noqa: E731
+    d_nz = aclnn.Tensor(x2.shape, "int8", torch.from_numpy(nz.copy()).to(DEV), fmt=ACL_FORMAT_FRACTAL_NZ, storage_shape=nz.shape)
+    outs = []
+    for nzcall in (False, True):
+        out = torch.full((m, n), -7777.0, dtype=torch.bfloat16, device=DEV)
+        aclnn.quant_matmul_v5(t(x1), d_nz if nzcall else t(x2), t(s1), t(s2), aclnn.from_torch(out), t(bias), False, tb, 0, weight_nz=nzcall)
+        torch.cuda.synchronize()
+        outs.append(out_to_np(out).view(np.uint16))
+    assert np.array_equal(outs[0], want.view(np.uint16))
+    assert np.array_equal(outs[1], outs[0])
