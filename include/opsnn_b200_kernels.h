@@ -84,6 +84,14 @@ typedef struct OpsnnQmmParams {
        sign-extends the packed nibbles of that operand to INT8 in the workspace (exact), then the INT8 kernels run. */
     int32_t a_prepass;
     const void* b_offset;   /* PERGROUP_ASYM: x2Offset (k/group_k, n), FLOAT16 */
+    /* MX mode, x2 prepared once by opsnn_qmm_prepare_b_launch (all three zero: nothing prepared, every call does its own layout work):
+       prep_b   x2 rewritten k-contiguous (n,k) for all batches (used instead of b, which stays the caller's tensor), or NULL when x2
+                is already stored (n,k);
+       prep_sfb x2Scale in the tensor core's scale-atom order, laid out for tiles of prep_bn columns; ignored (the call relays the
+                scales itself) when host tile selection picks another width for this call's m. */
+    const void* prep_b;
+    const void* prep_sfb;
+    int32_t prep_bn;
 } OpsnnQmmParams;
 
 enum { OPSNN_B_PREPASS_NONE = 0, OPSNN_B_PREPASS_WIDEN = 1, OPSNN_B_PREPASS_GROUP_SCALE = 2, OPSNN_PREPASS_WIDEN_INT4 = 3 };
@@ -93,6 +101,17 @@ OPSNN_API uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t ker
 /* Returns the OpsnnKernelChoice the host tile selection resolves AUTO to (never AUTO). */
 OPSNN_API int32_t opsnn_qmm_select_kernel(const OpsnnQmmParams* p);
 OPSNN_API int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* stream);
+
+/* Prepare-once form of a static x2 (a weight) for the MX modes. The layout work that does not depend on x1 - x2Scale into scale-atom
+ * order, and x2 stored (k,n) rewritten k-contiguous (fp4 must be, fp8 runs faster so) - is done one time into caller memory
+ * `storage` (opsnn_qmm_prepare_b_size bytes; the library allocates nothing) and described by three values to put into prep_b /
+ * prep_sfb / prep_bn of later calls on the same x2. p describes a representative call: its m and batch select the tile width the
+ * scale atoms are laid out for; x1, x1Scale and out are not touched. Returns 0 and leaves *prep_bn = 0 when p's mode or layout has
+ * nothing to prepare. The reference's precedent for offline weight re-layout is aclnnConvertWeightToINT4Pack
+ * (matmul/convert_weight_to_int4_pack/op_host/op_api/aclnn_convert_weight_to_int4_pack.cpp:318-358, ND -> NZ). */
+OPSNN_API uint64_t opsnn_qmm_prepare_b_size(const OpsnnQmmParams* p);
+OPSNN_API int32_t opsnn_qmm_prepare_b_launch(const OpsnnQmmParams* p, void* storage, uint64_t storage_size, const void** prep_b,
+                                             const void** prep_sfb, int32_t* prep_bn, void* stream);
 
 /* ---- weight-only quant matmul (aclnnWeightQuantBatchMatmulV2/V3 path) ------------------------------------ */
 

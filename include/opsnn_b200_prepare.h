@@ -1,0 +1,42 @@
+/*
+ * Prepare-once weights for aclnnQuantMatmulV5 (the MX modes).
+ *
+ * A weight (x2) and its scale are static, yet part of every call's time goes into layout work on them that does not depend on
+ * the activations: x2Scale is rewritten into the order the tensor core's scale copies want, an MXFP4 x2 stored (k,n) must be
+ * rewritten k-contiguous before the tensor core can read it, and an MXFP8 x2 stored (k,n) runs ~20 % slower than one stored
+ * (n,k). opsnnQuantMatmulPrepareX2 does that work one time, into memory the caller provides and keeps alive, and registers the
+ * result under x2's device address. Every later aclnnQuantMatmulV5 / V4 / V3 call whose x2 and x2Scale are those same tensors
+ * (address, shape, strides, dtype, transposeX2, groupSize) then skips it; any other call, and every call after
+ * opsnnQuantMatmulReleaseX2, runs exactly as before. Results are bit-identical either way.
+ *
+ * No counterpart in the reference's aclnn API. Its precedent for offline weight re-layout is aclnnConvertWeightToINT4Pack
+ * (matmul/convert_weight_to_int4_pack/op_host/op_api/aclnn_convert_weight_to_int4_pack.cpp:318-358: ND -> FRACTAL_NZ, once,
+ * ahead of the matmuls), whose target layout is specific to the Ascend cube unit; this is the same idea for this hardware.
+ *
+ *   mHint         activation rows per batch of the calls to come: selects the tile width the scale atoms are laid out for. A
+ *                 later call whose own m selects another width relays the scales itself and still uses the moved x2.
+ *   storage       device memory of at least the size the first function reports; owned by the caller, must outlive the
+ *                 registration; the library allocates nothing.
+ *   The contents of x2 / x2Scale must not change while registered (the prepared copy would go stale).
+ *   Modes with nothing to prepare (everything but MXFP8 x MXFP8 and MXFP4 x MXFP4 on the tensor-core path) report size 0 and
+ *   register nothing.
+ */
+#ifndef OPSNN_B200_PREPARE_H_
+#define OPSNN_B200_PREPARE_H_
+
+#include "aclnn_compat/acl_base.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+ACLNN_API aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2,
+                                                              int64_t groupSize, int64_t mHint, uint64_t* storageSize);
+ACLNN_API aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize,
+                                                int64_t mHint, void* storage, uint64_t storageSize, aclrtStream stream);
+ACLNN_API aclnnStatus opsnnQuantMatmulReleaseX2(const aclTensor* x2);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPSNN_B200_PREPARE_H_ */

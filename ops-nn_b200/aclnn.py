@@ -102,6 +102,11 @@ def lib():
     L.opsnn_wqbmm_workspace_size.argtypes = [POINTER(WqbmmParams), c_int32]
     L.opsnn_wqbmm_select_kernel.restype = c_int32
     L.opsnn_wqbmm_select_kernel.argtypes = [POINTER(WqbmmParams)]
+    L.opsnnQuantMatmulPrepareX2GetStorageSize.argtypes = [T, T, c_bool, c_int64, c_int64, POINTER(c_uint64)]
+    L.opsnnQuantMatmulPrepareX2.argtypes = [T, T, c_bool, c_int64, c_int64, c_void_p, c_uint64, c_void_p]
+    L.opsnnQuantMatmulReleaseX2.argtypes = [T]
+    for name in ("opsnnQuantMatmulPrepareX2GetStorageSize", "opsnnQuantMatmulPrepareX2", "opsnnQuantMatmulReleaseX2"):
+        getattr(L, name).restype = c_int32
     I64, I32, U64, VP = c_int64, c_int32, c_uint64, c_void_p
     L.opsnn_shard_range.restype = None
     L.opsnn_shard_range.argtypes = [I64, I32, I32, I64, POINTER(I64), POINTER(I64)]
@@ -331,6 +336,33 @@ def dynamic_mx_quant(x, y_out, mxscale_out, dst_type, axis=-1, round_mode=b"rint
     st = lib().aclnnDynamicMxQuant(c_void_p(0), c_uint64(0), ex, _stream())
     if st != ACLNN_SUCCESS:
         raise AclnnError("aclnnDynamicMxQuant", st)
+
+
+# ---- prepare-once weights (include/opsnn_b200_prepare.h) ----------------------------------------------------------
+
+def prepare_x2(x2, x2_scale, transpose_x2=False, group_size=0, m_hint=128):
+    """opsnnQuantMatmulPrepareX2 on the current torch CUDA stream. Returns the storage tensor (uint8, device) that now backs the
+    registration and must be kept alive by the caller, or None when the mode has nothing to prepare."""
+    import torch
+
+    need = c_uint64(0)
+    st = lib().opsnnQuantMatmulPrepareX2GetStorageSize(_h(x2), _h(x2_scale), bool(transpose_x2), int(group_size), int(m_hint), byref(need))
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnQuantMatmulPrepareX2GetStorageSize", st)
+    if need.value == 0:
+        return None
+    storage = torch.empty(int(need.value), dtype=torch.uint8, device=x2._keep.device)
+    st = lib().opsnnQuantMatmulPrepareX2(_h(x2), _h(x2_scale), bool(transpose_x2), int(group_size), int(m_hint),
+                                         c_void_p(storage.data_ptr()), c_uint64(need.value), _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnQuantMatmulPrepareX2", st)
+    return storage
+
+
+def release_x2(x2):
+    st = lib().opsnnQuantMatmulReleaseX2(_h(x2))
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnQuantMatmulReleaseX2", st)
 
 
 # ---- multi-GPU helpers (include/opsnn_b200_shard.h) --------------------------------------------------------------

@@ -23,6 +23,9 @@ int32_t qmm_generic_launch(const OpsnnQmmParams* p, cudaStream_t stream);
 bool qmm_umma_eligible(const OpsnnQmmParams* p);
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p);
 int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream);
+uint64_t qmm_mx_prepare_b_size(const OpsnnQmmParams* p);
+int32_t qmm_mx_prepare_b_launch(const OpsnnQmmParams* p, void* storage, uint64_t storage_size, const void** prep_b, const void** prep_sfb,
+                                int32_t* prep_bn, cudaStream_t stream);
 uint64_t qmm_a8w4_prepass_bytes(const OpsnnQmmParams* p);
 void qmm_a8w4_view(const OpsnnQmmParams* p, OpsnnQmmParams* q, void* dst);
 int32_t qmm_a8w4_prepass_launch(const OpsnnQmmParams* p, void* dst, cudaStream_t stream);
@@ -96,6 +99,26 @@ uint64_t opsnn_qmm_workspace_size(const OpsnnQmmParams* p, int32_t kernel_choice
     OpsnnQmmParams q;
     p = after_prepass(p, &q, reinterpret_cast<void*>(uintptr_t(256)));
     return pre + (kernel_choice == OPSNN_KERNEL_UMMA ? qmm_umma_workspace_size(p) : 0);
+}
+
+// Only the plain MX modes have x1-independent layout work worth keeping: the A8W4 and INT4 forms rewrite x2 through their own
+// pre-passes, the dequant and per-block modes feed x2 to the tensor core as stored.
+static bool preparable(const OpsnnQmmParams* p)
+{
+    return p != nullptr && p->mode == OPSNN_QMM_MX && p->a_prepass == OPSNN_B_PREPASS_NONE && p->b_prepass == OPSNN_B_PREPASS_NONE &&
+           p->b != nullptr && p->scale_b != nullptr && p->m > 0 && p->n > 0 && p->batch > 0;
+}
+
+uint64_t opsnn_qmm_prepare_b_size(const OpsnnQmmParams* p) { return preparable(p) ? qmm_mx_prepare_b_size(p) : 0; }
+
+int32_t opsnn_qmm_prepare_b_launch(const OpsnnQmmParams* p, void* storage, uint64_t storage_size, const void** prep_b, const void** prep_sfb,
+                                   int32_t* prep_bn, void* stream)
+{
+    if (prep_b == nullptr || prep_sfb == nullptr || prep_bn == nullptr) return (int32_t)cudaErrorInvalidValue;
+    *prep_b = *prep_sfb = nullptr;
+    *prep_bn = 0;
+    if (!preparable(p)) return 0;
+    return qmm_mx_prepare_b_launch(p, storage, storage_size, prep_b, prep_sfb, prep_bn, static_cast<cudaStream_t>(stream));
 }
 
 int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* stream)

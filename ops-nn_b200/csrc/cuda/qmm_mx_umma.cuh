@@ -548,6 +548,19 @@ int mx_pick_bn(const OpsnnQmmParams* p)
     return tiles >= 148 ? 224 : 128;
 }
 
+// The x2 the matmul kernel will see when the caller handed over a prepared k-contiguous copy.
+OpsnnQmmParams mx_effective(const OpsnnQmmParams* p)
+{
+    OpsnnQmmParams e = *p;
+    if (p->prep_b != nullptr) {
+        e.b = p->prep_b;
+        e.b_ld = p->k;
+        e.b_bs = p->b_bs != 0 ? p->n * p->k : 0;
+        e.trans_b = 1;
+    }
+    return e;
+}
+
 MxPlan mx_plan(const OpsnnQmmParams* p)
 {
     MxPlan q{};
@@ -621,19 +634,87 @@ bool qmm_mx_umma_eligible(const OpsnnQmmParams* p)
     return true;
 }
 
-uint64_t qmm_mx_umma_workspace_size(const OpsnnQmmParams* p)
+uint64_t qmm_mx_umma_workspace_size(const OpsnnQmmParams* p0)
 {
+    const OpsnnQmmParams pe = mx_effective(p0);
+    const OpsnnQmmParams* p = &pe;
     const MxPlan q = mx_plan(p);
     return q.nb_a * q.sfa_bytes_per_batch + q.nb_b * q.sfb_bytes_per_batch + q.tr_a_bytes + q.tr_b_bytes + 3 * 256;
 }
 
-int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
+// x2Scale of p (all batches) into scale-atom order at dst, for the tile width of plan q.
+static void mx_relayout_sfb(const OpsnnQmmParams* p, const MxPlan& q, int scale_b_k_major, uint8_t* dst, cudaStream_t stream)
 {
+    const int64_t gb = (int64_t)q.nb_b * q.tiles_n * q.row_atoms;
+    if (getenv("OPSNN_MX_SF_SIMPLE") == nullptr && gb < 0x7FFFFFFF) {
+        mx_sf_relayout_tiled_kernel<<<(unsigned)gb, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), dst, p->n, q.kblocks32, q.kq,
+                                                                      scale_b_k_major, q.tiles_n, q.kstages, q.atoms, p->sb_bs, q.bn, q.row_atoms);
+    } else {
+        const int64_t wb = (int64_t)q.nb_b * q.tiles_n * q.kstages * q.atoms * q.row_atoms * 128;
+        mx_sf_relayout_kernel<<<(unsigned)std::min<int64_t>((wb + 255) / 256, 148 * 16), 256, 0, stream>>>(
+            reinterpret_cast<const uint8_t*>(p->scale_b), dst, p->n, q.kblocks32, q.kq, scale_b_k_major, q.tiles_n, q.kstages, q.atoms,
+            (int64_t)q.nb_b, p->sb_bs, q.bn, q.row_atoms);
+    }
+}
+
+// x2 stored (k, n) (all batches) rewritten (n, k) at dst.
+static void mx_transpose_b(const OpsnnQmmParams* p, bool f4, uint8_t* dst, cudaStream_t stream)
+{
+    const int64_t nb = p->b_bs != 0 ? p->batch : 1;
+    if (f4) {
+        fp4_transpose(reinterpret_cast<const uint8_t*>(p->b), dst, p->k, p->n, p->b_ld / 2, p->k / 2, p->b_bs / 2, p->n * (p->k / 2), nb, stream);
+        note_launch("fp4_transpose");
+    } else {
+        byte_transpose_kernel<<<dim3((unsigned)((p->n + 255) / 256), (unsigned)((p->k + 63) / 64), (unsigned)nb), 256, 0, stream>>>(
+            reinterpret_cast<const uint8_t*>(p->b), dst, p->k, p->n, p->b_ld, p->k, p->b_bs, p->n * p->k);
+        note_launch("byte_transpose");
+    }
+}
+
+uint64_t qmm_mx_prepare_b_size(const OpsnnQmmParams* p)
+{
+    if (!qmm_mx_umma_eligible(p)) return 0;
     const MxPlan q = mx_plan(p);
-    if (p->workspace == nullptr || p->workspace_size < qmm_mx_umma_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+    const bool move = p->trans_b == 0 && (q.f4 || (p->k % 32 == 0 && p->k / 64 < 65535 && (p->b_bs == 0 || p->batch <= 65535)));
+    const uint64_t copy = move ? (uint64_t)(p->b_bs != 0 ? p->batch : 1) * (uint64_t)p->n * (uint64_t)(q.f4 ? p->k / 2 : p->k) : 0;
+    return ((q.nb_b * q.sfb_bytes_per_batch + 255) & ~(uint64_t)255) + copy + 256;
+}
+
+int32_t qmm_mx_prepare_b_launch(const OpsnnQmmParams* p, void* storage, uint64_t storage_size, const void** prep_b, const void** prep_sfb,
+                                int32_t* prep_bn, cudaStream_t stream)
+{
+    *prep_b = *prep_sfb = nullptr;
+    *prep_bn = 0;
+    if (!qmm_mx_umma_eligible(p) || p->prep_b != nullptr || p->prep_sfb != nullptr) return 0;
+    const uint64_t need = qmm_mx_prepare_b_size(p);
+    if (storage == nullptr || storage_size < need) return (int32_t)cudaErrorInvalidValue;
+    const MxPlan q = mx_plan(p);
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(storage) + 255) & ~(uintptr_t)255);
+    mx_relayout_sfb(p, q, p->trans_b ? 0 : 1, base, stream);
+    note_launch("mx_sf_relayout", 1);
+    *prep_sfb = base;
+    *prep_bn = q.bn;
+    const bool move = p->trans_b == 0 && (q.f4 || (p->k % 32 == 0 && p->k / 64 < 65535 && (p->b_bs == 0 || p->batch <= 65535)));
+    if (move) {
+        uint8_t* copy = base + ((q.nb_b * q.sfb_bytes_per_batch + 255) & ~(uint64_t)255);
+        mx_transpose_b(p, q.f4, copy, stream);
+        *prep_b = copy;
+    }
+    return (int32_t)cudaGetLastError();
+}
+
+int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p0, cudaStream_t stream)
+{
+    const OpsnnQmmParams pe = mx_effective(p0);  // a prepared k-contiguous copy of x2 replaces the caller's (k,n) one
+    const OpsnnQmmParams* p = &pe;
+    const MxPlan q = mx_plan(p);
+    if (p->workspace == nullptr || p->workspace_size < qmm_mx_umma_workspace_size(p0)) return (int32_t)cudaErrorInvalidValue;
     uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
     uint8_t* sfa = ws;
     uint8_t* sfb = ws + q.nb_a * q.sfa_bytes_per_batch;
+    // x2Scale keeps the caller's storage order even when x2 itself was moved: (kq, n, 2) for x2 given as (k,n), (n, kq, 2) for (n,k)
+    const int scale_b_k_major = p0->trans_b ? 0 : 1;
+    const bool sfb_ready = p0->prep_sfb != nullptr && p0->prep_bn == q.bn;
     // ---- pre-pass: both operands' scales into atom order ----
     {
         const int64_t wa = (int64_t)q.nb_a * q.tiles_m * q.kstages * q.atoms * 128;
@@ -642,27 +723,25 @@ int32_t qmm_mx_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
         const auto blocks = [&](int64_t w) { return (unsigned)std::min<int64_t>((w + threads - 1) / threads, 148 * 16); };
         // x1Scale is (m, kq, 2), or (kq, m, 2) when x1 is stored (k,m); x2Scale is (kq, n, 2), or (n, kq, 2) when x2 is stored (n,k)
         const int64_t ga = (int64_t)q.nb_a * q.tiles_m, gb = (int64_t)q.nb_b * q.tiles_n * q.row_atoms;
-        if (getenv("OPSNN_MX_SF_SIMPLE") == nullptr && ga < 0x7FFFFFFF && gb < 0x7FFFFFFF) {
+        (void)wb;
+        (void)gb;
+        if (getenv("OPSNN_MX_SF_SIMPLE") == nullptr && ga < 0x7FFFFFFF) {
             mx_sf_relayout_tiled_kernel<<<(unsigned)ga, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32,
                                                                           q.kq, p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, p->sa_bs, BM, 1);
-            mx_sf_relayout_tiled_kernel<<<(unsigned)gb, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32,
-                                                                          q.kq, p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, p->sb_bs, q.bn,
-                                                                          q.row_atoms);
         } else {
-        mx_sf_relayout_kernel<<<blocks(wa), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32, q.kq,
-                                                                  p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs,
-                                                                  BM, 1);
-        mx_sf_relayout_kernel<<<blocks(wb), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_b), sfb, p->n, q.kblocks32, q.kq,
-                                                                  p->trans_b ? 0 : 1, q.tiles_n, q.kstages, q.atoms, (int64_t)q.nb_b, p->sb_bs,
-                                                                  q.bn, q.row_atoms);
+            mx_sf_relayout_kernel<<<blocks(wa), threads, 0, stream>>>(reinterpret_cast<const uint8_t*>(p->scale_a), sfa, p->m, q.kblocks32, q.kq,
+                                                                      p->trans_a ? 1 : 0, q.tiles_m, q.kstages, q.atoms, (int64_t)q.nb_a, p->sa_bs,
+                                                                      BM, 1);
         }
-        note_launch("mx_sf_relayout", 2);
+        if (sfb_ready) sfb = const_cast<uint8_t*>(static_cast<const uint8_t*>(p0->prep_sfb));
+        else mx_relayout_sfb(p, q, scale_b_k_major, sfb, stream);
+        note_launch("mx_sf_relayout", sfb_ready ? 1 : 2);
     }
     // ---- pre-pass: fp4 operands that are not k-contiguous ----
     OpsnnQmmParams pk = *p;  // the operand views the matmul kernel sees
     {
         auto up = [](uint8_t* x) { return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(x) + 255) & ~(uintptr_t)255); };
-        uint8_t* next = up(sfb + q.nb_b * q.sfb_bytes_per_batch);
+        uint8_t* next = up(ws + q.nb_a * q.sfa_bytes_per_batch + q.nb_b * q.sfb_bytes_per_batch);
         if (q.tr_a) {  // stored (k, m) -> (m, k)
             const int64_t nb = p->a_bs != 0 ? p->batch : 1;
             fp4_transpose(reinterpret_cast<const uint8_t*>(p->a), next, p->k, p->m, p->a_ld / 2, p->k / 2, p->a_bs / 2, p->m * (p->k / 2), nb, stream);

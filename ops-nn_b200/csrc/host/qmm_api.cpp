@@ -7,11 +7,15 @@
 //   :1137-1195 (groupSize / CheckShape), :1574-1916 (dtype tables, CheckParams order).
 // The rule order is kept (dtype -> shape -> format -> empty tensor) so the first failure yields the same status.
 #include <algorithm>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <shared_mutex>
 
 #include "aclnnop/aclnn_quant_matmul_v4.h"
 #include "aclnnop/aclnn_quant_matmul_v5.h"
 #include "aclnnop/aclnn_quant_matmul_weight_nz.h"
+#include "opsnn_b200_prepare.h"
 #include "internal.h"
 
 using namespace opsnn;
@@ -441,6 +445,64 @@ bool operand_batch(const aclTensor& t, size_t core_rank, const std::vector<int64
     return true;
 }
 
+// ---- prepared x2 registry (opsnnQuantMatmulPrepareX2) --------------------------------------------------------------------
+// Keyed by x2's device address. An entry is used only by calls whose x2 and x2Scale describe the very tensors that were
+// prepared (same addresses, extents, strides, orientation); anything else runs unprepared.
+struct PreparedX2 {
+    OpsnnQmmParams key{};  // the plan fields of the prepared call that must match
+    const void* prep_b = nullptr;
+    const void* prep_sfb = nullptr;
+    int32_t prep_bn = 0;
+};
+std::shared_mutex g_prepared_mu;
+std::map<const void*, PreparedX2> g_prepared;
+
+bool same_x2(const OpsnnQmmParams& a, const OpsnnQmmParams& b)
+{
+    return a.mode == b.mode && a.b == b.b && a.scale_b == b.scale_b && a.b_dtype == b.b_dtype && a.a_dtype == b.a_dtype &&
+           a.trans_b == b.trans_b && a.n == b.n && a.k == b.k && a.b_ld == b.b_ld && a.b_bs == b.b_bs && a.sb_bs == b.sb_bs &&
+           (a.b_bs == 0 || a.batch == b.batch) && a.group_k == b.group_k && a.b_prepass == b.b_prepass;
+}
+
+void attach_prepared(OpsnnQmmParams* p)
+{
+    if (p->mode != OPSNN_QMM_MX || p->b == nullptr) return;
+    std::shared_lock<std::shared_mutex> lk(g_prepared_mu);
+    auto it = g_prepared.find(p->b);
+    if (it == g_prepared.end() || !same_x2(it->second.key, *p)) return;
+    p->prep_b = it->second.prep_b;
+    p->prep_sfb = it->second.prep_sfb;
+    p->prep_bn = it->second.prep_bn;
+}
+
+// A stand-in x1 / x1Scale / out of mHint rows for planning a call on x2 alone (no device addresses: nothing of them is read).
+struct HintTensors {
+    aclTensor x1, x1s, out;
+};
+void make_hint(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t m_hint, HintTensors* h)
+{
+    const size_t r = x2->rank();
+    const int64_t k = transposeX2 ? x2->dim(-1) : x2->dim(-2), n = transposeX2 ? x2->dim(-2) : x2->dim(-1);
+    std::vector<int64_t> batch(x2->shape.begin(), x2->shape.begin() + (r >= 2 ? r - 2 : 0));
+    auto contiguous = [](aclTensor* t) {
+        t->strides.assign(t->shape.size(), 1);
+        for (int i = (int)t->shape.size() - 2; i >= 0; --i) t->strides[i] = t->strides[i + 1] * t->shape[i + 1];
+        t->storage_shape = t->shape;
+        t->offset = 0;
+        t->format = ACL_FORMAT_ND;
+        t->data = nullptr;
+    };
+    h->x1.shape = batch; h->x1.shape.push_back(m_hint); h->x1.shape.push_back(k);
+    h->x1.dtype = x2->dtype;
+    contiguous(&h->x1);
+    h->x1s.shape = batch; h->x1s.shape.push_back(m_hint); h->x1s.shape.push_back((k + 63) / 64); h->x1s.shape.push_back(2);
+    h->x1s.dtype = x2Scale->dtype;
+    contiguous(&h->x1s);
+    h->out.shape = batch; h->out.shape.push_back(m_hint); h->out.shape.push_back(n);
+    h->out.dtype = ACL_BF16;
+    contiguous(&h->out);
+}
+
 }  // namespace
 
 extern "C" {
@@ -746,6 +808,7 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
     if (const char* e = std::getenv("OPSNN_QMM_KERNEL")) exec->kernel_choice = std::atoi(e);
     if (!exec->unsupported) {
         if (exec->kernel_choice == OPSNN_KERNEL_AUTO) exec->kernel_choice = opsnn_qmm_select_kernel(&p);
+        if (exec->kernel_choice == OPSNN_KERNEL_UMMA) attach_prepared(&p);  // an x2 registered by opsnnQuantMatmulPrepareX2
         exec->workspace_size = opsnn_qmm_workspace_size(&p, exec->kernel_choice);
     }
     *workspaceSize = exec->workspace_size;
@@ -903,6 +966,89 @@ aclnnStatus aclnnQuantMatmulV3GetWorkspaceSize(const aclTensor* x1, const aclTen
 aclnnStatus aclnnQuantMatmulV3(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
     return aclnnQuantMatmulV5(workspace, workspaceSize, executor, stream);
+}
+
+// ---- prepare-once x2 (include/opsnn_b200_prepare.h) ----------------------------------------------------------------------------
+
+static aclnnStatus plan_on_x2(const char* api, const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize,
+                              int64_t mHint, std::unique_ptr<aclOpExecutor>* exec_out)
+{
+    if (x2 == nullptr || x2Scale == nullptr) {
+        set_err("%s: x2 and x2Scale are required", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (mHint < 1 || x2->rank() < 2) {
+        set_err("%s: mHint must be >= 1 and x2 at least 2-D", api);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    HintTensors h;
+    make_hint(x2, x2Scale, transposeX2, mHint, &h);
+    uint64_t ws = 0;
+    aclOpExecutor* ex = nullptr;
+    const aclnnStatus st = aclnnQuantMatmulV5GetWorkspaceSize(&h.x1, x2, &h.x1s, x2Scale, nullptr, nullptr, nullptr, nullptr, nullptr, false,
+                                                              transposeX2, groupSize, &h.out, &ws, &ex);
+    if (st != ACLNN_SUCCESS) return st;
+    exec_out->reset(ex);
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize,
+                                                    int64_t mHint, uint64_t* storageSize)
+{
+    const char* api = "opsnnQuantMatmulPrepareX2GetStorageSize";
+    clear_err();
+    if (storageSize == nullptr) {
+        set_err("%s: storageSize is nullptr", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    *storageSize = 0;
+    std::unique_ptr<aclOpExecutor> exec;
+    const aclnnStatus st = plan_on_x2(api, x2, x2Scale, transposeX2, groupSize, mHint, &exec);
+    if (st != ACLNN_SUCCESS) return st;
+    if (!exec->unsupported && !exec->nothing_to_do && exec->kernel_choice == OPSNN_KERNEL_UMMA) {
+        exec->qmm.prep_b = exec->qmm.prep_sfb = nullptr;  // size of a fresh preparation, also when one is registered already
+        exec->qmm.prep_bn = 0;
+        *storageSize = opsnn_qmm_prepare_b_size(&exec->qmm);
+    }
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize, int64_t mHint,
+                                      void* storage, uint64_t storageSize, aclrtStream stream)
+{
+    const char* api = "opsnnQuantMatmulPrepareX2";
+    clear_err();
+    std::unique_ptr<aclOpExecutor> exec;
+    const aclnnStatus st = plan_on_x2(api, x2, x2Scale, transposeX2, groupSize, mHint, &exec);
+    if (st != ACLNN_SUCCESS) return st;
+    if (exec->unsupported || exec->nothing_to_do || exec->kernel_choice != OPSNN_KERNEL_UMMA) return ACLNN_SUCCESS;  // nothing to prepare
+    OpsnnQmmParams& p = exec->qmm;
+    if (p.b == nullptr || p.scale_b == nullptr) {
+        set_err("%s: x2 / x2Scale were created without a device address", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    p.prep_b = p.prep_sfb = nullptr;
+    p.prep_bn = 0;
+    PreparedX2 e;
+    const int32_t rc = opsnn_qmm_prepare_b_launch(&p, storage, storageSize, &e.prep_b, &e.prep_sfb, &e.prep_bn, stream);
+    if (rc != 0) {
+        set_err("%s: preparation failed with CUDA error %d (storage of %lu bytes needed)", api, rc, (unsigned long)opsnn_qmm_prepare_b_size(&p));
+        return rc == 1 /* cudaErrorInvalidValue */ ? ACLNN_ERR_PARAM_INVALID : ACLNN_ERR_RUNTIME_ERROR;
+    }
+    if (e.prep_bn == 0) return ACLNN_SUCCESS;
+    e.key = p;
+    std::unique_lock<std::shared_mutex> lk(g_prepared_mu);
+    g_prepared[p.b] = e;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnQuantMatmulReleaseX2(const aclTensor* x2)
+{
+    clear_err();
+    if (x2 == nullptr) return ACLNN_ERR_PARAM_NULLPTR;
+    std::unique_lock<std::shared_mutex> lk(g_prepared_mu);
+    g_prepared.erase(data_ptr(x2));
+    return ACLNN_SUCCESS;
 }
 
 }  // extern "C"

@@ -36,7 +36,7 @@ def test_headers_are_plain_c():
     inc = os.path.join(ROOT, "include")
     hdrs = ["aclnn_compat/acl_base.h", "aclnnop/aclnn_quant_matmul_v5.h", "aclnnop/aclnn_weight_quant_batch_matmul_v2.h",
             "aclnnop/aclnn_weight_quant_batch_matmul_v3.h", "aclnnop/aclnn_dynamic_mx_quant.h", "aclnnop/aclnn_quant_matmul_v4.h",
-            "aclnnop/aclnn_convert_weight_to_int4_pack.h", "aclnnop/aclnn_quant_matmul_weight_nz.h", "opsnn_b200_kernels.h", "opsnn_b200_shard.h"]
+            "aclnnop/aclnn_convert_weight_to_int4_pack.h", "aclnnop/aclnn_quant_matmul_weight_nz.h", "opsnn_b200_kernels.h", "opsnn_b200_shard.h", "opsnn_b200_prepare.h"]
     with tempfile.TemporaryDirectory() as td:
         src = os.path.join(td, "t.c")
         with open(src, "w") as fh:
