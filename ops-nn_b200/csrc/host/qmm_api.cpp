@@ -475,7 +475,7 @@ void attach_prepared(OpsnnQmmParams* p)
     p->prep_bn = it->second.prep_bn;
 }
 
-// A stand-in x1 / x1Scale / out of mHint rows for planning a call on x2 alone (no device addresses: nothing of them is read).
+// A stand-in x1 / x1Scale / out of mHint rows for planning a call on x2 alone (stand-in addresses: nothing of them is read).
 struct HintTensors {
     aclTensor x1, x1s, out;
 };
@@ -490,7 +490,7 @@ void make_hint(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, 
         t->storage_shape = t->shape;
         t->offset = 0;
         t->format = ACL_FORMAT_ND;
-        t->data = nullptr;
+        t->data = reinterpret_cast<void*>(uintptr_t(256));  // stand-in with allocation alignment: kernel selection looks at it, nothing reads it
     };
     h->x1.shape = batch; h->x1.shape.push_back(m_hint); h->x1.shape.push_back(k);
     h->x1.dtype = x2->dtype;
@@ -1002,6 +1002,7 @@ aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x2, const a
         return ACLNN_ERR_PARAM_NULLPTR;
     }
     *storageSize = 0;
+    if (x2 != nullptr && x2Scale != nullptr && x2Scale->dtype != ACL_FLOAT8_E8M0) return ACLNN_SUCCESS;  // not an MX mode: nothing to prepare
     std::unique_ptr<aclOpExecutor> exec;
     const aclnnStatus st = plan_on_x2(api, x2, x2Scale, transposeX2, groupSize, mHint, &exec);
     if (st != ACLNN_SUCCESS) return st;
@@ -1018,6 +1019,7 @@ aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Sc
 {
     const char* api = "opsnnQuantMatmulPrepareX2";
     clear_err();
+    if (x2 != nullptr && x2Scale != nullptr && x2Scale->dtype != ACL_FLOAT8_E8M0) return ACLNN_SUCCESS;  // not an MX mode: nothing to prepare
     std::unique_ptr<aclOpExecutor> exec;
     const aclnnStatus st = plan_on_x2(api, x2, x2Scale, transposeX2, groupSize, mHint, &exec);
     if (st != ACLNN_SUCCESS) return st;
