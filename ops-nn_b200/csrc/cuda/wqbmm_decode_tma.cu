@@ -120,6 +120,11 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     const uint32_t smem0 = (ptx::smem_u32(dyn_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = smem0 + kNumStages * kStageBytes;  // full[i] at bar0 + 8 i, empty[i] at bar0 + 64 + 8 i
 
+    // Programmatic dependent launch: the next kernel of the stream may be placed as soon as every CTA of this one has got here
+    // (its CTAs take the SM slots this kernel's early finishers leave), and this kernel reads nothing another kernel may have
+    // written before griddepcontrol.wait below has returned. Both are no-ops for an ordinary launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     const int64_t c = blockIdx.x;
     const int64_t strip = c % a.strips;
     const int64_t chunk = c / a.strips;
@@ -141,6 +146,7 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         ptx::fence_proxy_async();
     }
     __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     volatile uint32_t* abort_flag = &s_abort;
 
     auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
@@ -425,11 +431,24 @@ template <bool kBf16, bool kExact, bool kAligned>
 cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
 {
     auto kern = wqbmm_decode_tma_kernel<kBf16, kExact, kAligned>;
-    cudaError_t rc = once_per_device(g_tma_configured[variant],
-                                     [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmaSmem); });
+    cudaError_t rc = once_per_device(g_tma_configured[variant], [&] {
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmaSmem);
+    });
     if (rc != cudaSuccess) return rc;
-    kern<<<grid, kThreads, kTmaSmem, stream>>>(mw, mx, ta);
-    return cudaGetLastError();
+    // launched as a programmatic dependent of whatever precedes it in the stream (OPSNN_WQ_PDL=0: an ordinary launch)
+    const char* pe = getenv("OPSNN_WQ_PDL");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kTmaSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (pe == nullptr || pe[0] != '0') ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, mw, mx, ta);
 }
 
 constexpr int kTmaMaxGrid = 148 * 4 * 2;  // same workspace layout and bound as the other decode kernels
@@ -524,7 +543,7 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
 
 }  // namespace opsnn
 
-// Error word of the bulk-copy decode kernel on the current device: 0 when every bounded wait inside it completed. Synchronises the
+// Error word of the bulk-copy decode kernels on the current device: 0 when every bounded wait inside them completed. Synchronises the
 // device; reset != 0 clears the word after reading it.
 extern "C" __attribute__((visibility("default"))) uint32_t opsnn_wqbmm_decode_status(int32_t reset)
 {
