@@ -687,6 +687,35 @@ def finish_tensor_workload(torch, dist, dev, res, kind, desc, peaks, world, args
 QMM_WORKLOADS = ("c1", "c3", "c4", "c5")
 
 
+def run_ceilings(aclnn, sm_mhz=1965.0, sms=148):
+    """Measured instruction-issue ceilings (opsnn_probe_umma / opsnn_probe_mix): what a kernel of each kind could reach with operands
+    already in shared memory and nothing but MMAs (tensor-core kinds), or with nothing but the dequantisation instruction mix (decode)."""
+    import ctypes
+
+    L = aclnn.lib()
+    out = {"sm_mhz_assumed": sm_mhz, "sms": sms, "umma": {}, "decode_mix": {}}
+    for name, kind, bn, kelems in (("i8", 0, 256, 32), ("f8f6f4", 1, 256, 32), ("mxf8f6f4", 2, 224, 32), ("mxf4", 3, 224, 64),
+                                   ("mxf8f6f4_bn256", 2, 256, 32), ("mxf4_bn256", 3, 256, 64)):
+        clk = ctypes.c_double(0.0)
+        rc = L.opsnn_probe_umma(kind, bn, ctypes.byref(clk))
+        if rc != 0 or clk.value <= 0:
+            out["umma"][name] = {"error": rc}
+            continue
+        ops = 2.0 * 128 * bn * kelems
+        out["umma"][name] = {"bn": bn, "clocks_per_mma": clk.value, "ops_per_clk_per_sm": ops / clk.value,
+                             "ceiling_tops": ops / clk.value * sms * sm_mhz * 1e6 / 1e12}
+    for name, mix in (("integer_only", 0), ("pair16_only", 1), ("mma_sync_only", 2), ("default_arithmetic", 3), ("group_wise_arithmetic", 4)):
+        clk = ctypes.c_double(0.0)
+        rc = L.opsnn_probe_mix(mix, ctypes.byref(clk))
+        out["decode_mix"][name] = {"error": rc} if rc != 0 else {"clocks_per_kstep_per_scheduler": clk.value}
+    # one k-step = 1024 int4 weights = 512 bytes per warp; 4 schedulers per SM
+    for name in ("default_arithmetic", "group_wise_arithmetic"):
+        e = out["decode_mix"].get(name, {})
+        if "clocks_per_kstep_per_scheduler" in e:
+            e["weight_stream_ceiling_gbs"] = 512.0 * 4 / e["clocks_per_kstep_per_scheduler"] * sms * sm_mhz * 1e6 / 1e9
+    return out
+
+
 def run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names):
     out = {}
     for name in names:
@@ -923,6 +952,13 @@ def main():
     if rank == 0:
         sampler.start()
 
+    if args.workload == "ceilings":
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps(dict(run_ceilings(aclnn), metric="measured ceilings")))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     if args.workload in QMM_WORKLOADS:  # single secondary line
         entry = run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, [args.workload])
         if rank == 0:
@@ -1109,6 +1145,13 @@ def main():
 
     names = [] if args.workload == "c2" else list(QMM_WORKLOADS)
     workloads = run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names)
+    ceilings = None
+    if rank == 0:
+        try:
+            ceilings = run_ceilings(aclnn)
+        except Exception as exc:  # noqa: BLE001
+            ceilings = {"error": "%s: %s" % (type(exc).__name__, exc)}
+    barrier()
 
     if rank == 0:
         sampler.stop()
@@ -1157,7 +1200,20 @@ def main():
             "inner_precise_1": {"kernel": hp_kernel, "achieved": local_bytes / (hp_ms * 1e-3) / 1e9, "unit": "GB/s",
                                 "frac": local_bytes / (hp_ms * 1e-3) / 1e9 / hbm, "kernel_ms_avg": hp_ms, "kernel_ms_min": hp_min},
             "workloads": workloads,
+            "ceilings": ceilings,
         }
+        if isinstance(ceilings, dict) and "umma" in ceilings:
+            if clocks.get("sm_mhz"):
+                ceilings["note"] = "ceiling_tops / weight_stream_ceiling_gbs assume %.0f MHz; the clocks sampled under load are in `clocks`" % ceilings["sm_mhz_assumed"]
+            kind_of = {"c3": "f8f6f4", "c4": "mxf4", "c5": "mxf8f6f4"}
+            for wname, kname in kind_of.items():
+                w, cdict = workloads.get(wname), ceilings["umma"].get(kname, {})
+                if isinstance(w, dict) and "roofline" in w and "ceiling_tops" in cdict:
+                    w["roofline"]["frac_of_mma_issue_ceiling"] = w["value"] / world / cdict["ceiling_tops"]
+            dm = ceilings["decode_mix"].get("default_arithmetic", {})
+            if "weight_stream_ceiling_gbs" in dm:
+                line["roofline"]["instruction_mix_ceiling_gbs"] = dm["weight_stream_ceiling_gbs"] * (local_bytes / (K * nl / 2.0))
+                line["roofline"]["frac_of_instruction_mix_ceiling"] = achieved / line["roofline"]["instruction_mix_ceiling_gbs"]
         traffic_file = os.path.join(ROOT, "profiles", "wqbmm_decode_c2_traffic.json")
         if world == 1 and os.path.exists(traffic_file):
             with open(traffic_file) as fh:

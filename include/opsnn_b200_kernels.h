@@ -232,6 +232,15 @@ OPSNN_API uint32_t opsnn_qmm_umma_status(int32_t reset);
  * operands never arrived) / 2 (a stage buffer was never released). Synchronises the device. */
 OPSNN_API uint32_t opsnn_wqbmm_decode_status(int32_t reset);
 
+/* ---- measured ceilings (diagnostics; not on any product path) --------------------------------------------------------------
+ * opsnn_probe_umma: clocks per tcgen05.mma (128 x bn x 32 bytes of k) when one CTA per SM issues them back to back on operands
+ * resident in shared memory; kind 0 i8, 1 f8f6f4, 2 mxf8f6f4, 3 mxf4; bn 128, 224 or 256. opsnn_probe_mix: clocks per k-step per
+ * scheduler of the decode kernels' instruction mixes (0 integer only, 1 16-bit-pair arithmetic only, 2 mma.sync only, 3 default
+ * arithmetic, 4 group-wise arithmetic). Both synchronise the device and use a few KB of their own device memory for the duration of
+ * the call. No counterpart in the reference. */
+OPSNN_API int32_t opsnn_probe_umma(int32_t kind, int32_t bn, double* clocks_per_mma);
+OPSNN_API int32_t opsnn_probe_mix(int32_t mix, double* clocks_per_kstep);
+
 #ifdef __cplusplus
 }
 #endif

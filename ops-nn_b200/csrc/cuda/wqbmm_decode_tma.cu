@@ -80,9 +80,13 @@ __device__ __forceinline__ void mbar_arrive_a(uint32_t bar_addr)
 // 0 when every wait of every launch completed; otherwise 1 (a stage never arrived) or 2 (a stage was never released).
 __device__ unsigned int g_wq_tma_status = 0;
 
+// Poll limit of the waits: kWaitPolls, or what a test set to make a wait run out quickly (see TmaArgs::test_*).
+__device__ uint32_t g_wq_tma_poll_limit = kWaitPolls;
+
 __device__ __noinline__ bool wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int code)
 {
-    for (uint32_t i = 0; i < kWaitPolls; ++i) {
+    const uint32_t limit = g_wq_tma_poll_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
         if (ptx::mbar_try_wait_a(bar, parity)) return true;
         if ((i & 255u) == 255u && *abort_flag != 0u) return false;
     }
@@ -100,6 +104,8 @@ struct TmaArgs {
     DecodeArgs d;
     int32_t total_stages;      // ceil(k / 64)
     int32_t stages_per_group;  // kAligned kernels: steps_per_group / 4
+    int32_t test_stall_stage;  // tests only: >= 0 makes every CTA stop issuing copies from this stage of its range on, so that the
+                               // consumers' wait for it runs out (nothing is in flight then) and the give-up path executes; -1 otherwise
 };
 
 // kAligned: every k-group is a whole number of stages (or there is a single group), so group changes happen at stage
@@ -150,6 +156,7 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     volatile uint32_t* abort_flag = &s_abort;
 
     auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
+        if (ta.test_stall_stage >= 0 && t >= ta.test_stall_stage) return;
         const uint32_t fb = bar0 + 8u * buf;
         const uint32_t dst = smem0 + (uint32_t)buf * kStageBytes;
         const int32_t krow = (st_a + t) * kStageRows;
@@ -493,6 +500,13 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.ksteps = p->k / 16;
     a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
     ta.total_stages = (int32_t)((a.ksteps + kStageSteps - 1) / kStageSteps);
+    ta.test_stall_stage = -1;
+    if (const char* e = getenv("OPSNN_TEST_DECODE_STALL_STAGE")) {  // tests of the give-up path only
+        ta.test_stall_stage = atoi(e);
+        const char* pl = getenv("OPSNN_TEST_DECODE_POLL_LIMIT");
+        const uint32_t limit = pl != nullptr ? (uint32_t)atoi(pl) : 4096u;
+        cudaMemcpyToSymbolAsync(g_wq_tma_poll_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, stream);
+    }
     const bool single_group = a.steps_per_group >= a.ksteps;
     const bool aligned = single_group || a.steps_per_group % kStageSteps == 0;
     ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / kStageSteps);
@@ -552,6 +566,8 @@ extern "C" __attribute__((visibility("default"))) uint32_t opsnn_wqbmm_decode_st
     if (reset) {
         unsigned int z = 0;
         cudaMemcpyToSymbol(opsnn::g_wq_tma_status, &z, sizeof(z));
+        const uint32_t limit = opsnn::kWaitPolls;  // a test may have shortened the waits: back to the normal limit
+        cudaMemcpyToSymbol(opsnn::g_wq_tma_poll_limit, &limit, sizeof(limit));
     }
     return v;
 }

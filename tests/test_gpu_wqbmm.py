@@ -194,3 +194,48 @@ def test_decode_kernel_in_chunks_of_16_rows(aclnn, m, inner_precise):
         tol = 2.0 ** -8 * 1.05
     rms = np.sqrt(np.mean(wv ** 2))
     assert np.all(np.abs(gv - wv) <= tol * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
+
+
+def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, monkeypatch):
+    """Every wait in the bulk-copy decode kernel is bounded. Here the producer is told (test-only switch) to stop issuing copies
+    after the eighth stage of each CTA's range, with a poll limit of a few thousand, so the consumers' wait for the ninth stage
+    runs out while nothing is in flight: the kernel must come back by itself, leave its error word at 1 (a stage never
+    arrived), and the next, ordinary call must work. Nothing faults, traps or hangs: the wait simply gives up."""
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    m, k, n, g = 16, 8192, 4096, 128
+    rng = np.random.default_rng(5)
+    import ml_dtypes
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+    sc = rng.uniform(0.005, 0.02, (k // g, n)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    of = rng.uniform(-1, 1, (k // g, n)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    bf = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV)  # noqa: E731
+    tx, tw, ts, to = bf(x), torch.from_numpy(wqbmm_oracle.pack_int4_words(w).copy()).to(DEV), bf(sc), bf(of)
+    L = aclnn.lib()
+    assert L.opsnn_wqbmm_decode_status(1) == 0
+
+    def run():
+        y = torch.full((m, n), -7777.0, dtype=torch.bfloat16, device=DEV)
+        aclnn.weight_quant_batch_matmul(aclnn.from_torch(tx), aclnn.from_torch(tw), aclnn.from_torch(ts), aclnn.from_torch(y),
+                                        aclnn.from_torch(to), None, g)
+        torch.cuda.synchronize()
+        return y
+
+    monkeypatch.setenv("OPSNN_WQ_DECODE_SPLITS", "2")           # 64 stages per CTA
+    monkeypatch.setenv("OPSNN_TEST_DECODE_STALL_STAGE", "8")
+    monkeypatch.setenv("OPSNN_TEST_DECODE_POLL_LIMIT", "3000")
+    y_bad = run()
+    assert aclnn.last_kernel_name() == "wqbmm_decode"
+    assert L.opsnn_wqbmm_decode_status(1) == 1                   # reported, and cleared (which also restores the poll limit)
+    assert bool((y_bad == -7777.0).all())                        # a kernel that gave up writes nothing
+    monkeypatch.delenv("OPSNN_TEST_DECODE_STALL_STAGE")
+    monkeypatch.delenv("OPSNN_TEST_DECODE_POLL_LIMIT")
+    y = run()
+    assert L.opsnn_wqbmm_decode_status(1) == 0
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, None, g).astype(np.float64)
+    got = out_to_np(y).astype(np.float64)
+    rms = np.sqrt(np.mean(want ** 2))
+    assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
