@@ -67,6 +67,8 @@ struct UmmaArgs {
     uint32_t* ks_part;                 // [tile][split][128][BN] raw 32-bit accumulators
     unsigned long long* ks_count;      // [tile] (nonce << 8) | arrivals; any other nonce counts as zero arrivals
     unsigned long long ks_nonce;
+    int32_t test_stall_kblock;  // tests of the give-up path only: >= 0 makes the producer stop issuing copies from this k-block of each
+                                // work item on (nothing is in flight then), so the MMA warp's wait for it runs out; 0 / negative: off
 };
 
 // Order of the tiles of one batch. m runs fastest inside bands of kBand tile rows; a band is finished over all of n before
@@ -369,6 +371,10 @@ qmm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int kb_begin = (int)((int64_t)split * kblocks / (int)ks), kb_end = (int)((int64_t)(split + 1) * kblocks / (int)ks);
             int32_t kk = kb_begin * BK;
             for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (a.test_stall_kblock > 0 && kb >= a.test_stall_kblock) {  // test switch: the producer simply stops
+                    ok = false;
+                    break;
+                }
                 if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
                     report(abort_flag, (1u << 8) | 1u);
                     ok = false;
@@ -911,6 +917,12 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
             a.ks_nonce = next_ks_nonce();
         }
     }
+    if (const char* e = getenv("OPSNN_TEST_UMMA_STALL_KBLOCK")) {  // tests of the give-up path only (single-CTA kernels)
+        a.test_stall_kblock = atoi(e);
+        const char* pl = getenv("OPSNN_TEST_UMMA_POLL_LIMIT");
+        const uint32_t limit = pl != nullptr ? (uint32_t)atoi(pl) : 20000u;
+        cudaMemcpyToSymbolAsync(ptx::g_spin_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, stream);
+    }
     a.a_batched = p->a_bs != 0;
     a.b_batched = b_bs != 0;
     a.out_dtype = p->out_dtype; a.bias_dtype = p->bias_dtype; a.scale_b_dtype = p->scale_b_dtype; a.deq_flags = p->deq_flags;
@@ -961,6 +973,8 @@ extern "C" __attribute__((visibility("default"))) uint32_t opsnn_qmm_umma_status
     if (reset) {
         unsigned int z = 0;
         cudaMemcpyToSymbol(opsnn::g_umma_status, &z, sizeof(z));
+        const uint32_t limit = opsnn::ptx::kSpinLimit;  // a test may have shortened the waits: back to the normal limit
+        cudaMemcpyToSymbol(opsnn::ptx::g_spin_limit, &limit, sizeof(limit));
         if (unsigned int* w = opsnn::g_status_host_word.load(std::memory_order_acquire)) *reinterpret_cast<volatile unsigned int*>(w) = 0u;
     }
     return v;

@@ -11,6 +11,9 @@ namespace opsnn {
 namespace ptx {
 
 constexpr uint32_t kSpinLimit = 20u * 1000u * 1000u;  // polls before a wait is declared dead (order of a second)
+// The limit the waits actually use (one copy per translation unit that includes this header): kSpinLimit, unless a test of the
+// give-up path shortened it through that translation unit's setter.
+static __device__ uint32_t g_spin_limit = kSpinLimit;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -43,7 +46,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 // Bounded wait. `abort_flag` (shared memory) is polled too, so that one role giving up releases the others.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    const uint32_t limit = g_spin_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
     }
@@ -55,7 +59,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // that the polling warps do not take issue slots from the single thread that feeds the tensor core.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
-    for (uint32_t i = 0; i < kSpinLimit / 16; ++i) {
+    const uint32_t limit = g_spin_limit / 16u + 1u;
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(200);
         if ((i & 63u) == 63u && *abort_flag != 0u) return false;
@@ -79,7 +84,8 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t pari
 }
 static __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
 {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    const uint32_t limit = g_spin_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait_a(bar_addr, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
     }

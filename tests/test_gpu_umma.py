@@ -340,3 +340,48 @@ def test_perblock_cta_pairs_batched(aclnn, monkeypatch):
     monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
     got = _run(aclnn, x1, x2, s1, s2, None, False, False, group, "bfloat16", "qmm_umma_pair_perblock")
     check_close(got, want, ref32, "bfloat16")
+
+
+def test_tensor_core_wait_that_runs_out_reaches_the_caller(aclnn, monkeypatch):
+    """Every wait in the tcgen05 kernels is bounded. A test-only switch makes the copy producer stop after the eighth k-block of
+    each tile with the poll limit cut to thousands, so the MMA warp's wait for the ninth runs out while nothing is in flight.
+    The kernel must come back by itself (all roles leave, TMEM is freed), the error word must be set, the NEXT aclnn call must
+    be refused with ACLNN_ERR_RUNTIME_ERROR (the word is mirrored to the host), and after opsnn_qmm_umma_status(1) everything
+    works again. Nothing faults, traps or hangs: the wait simply gives up."""
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    rng = np.random.default_rng(11)
+    m, k, n = 256, 4096, 512
+    x1 = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    x2 = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    s1 = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    s2 = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    t = lambda a: aclnn.from_torch(torch.from_numpy(a).to(DEV))  # noqa: E731
+    d = [t(x1), t(x2), t(s1), t(s2)]
+    L = aclnn.lib()
+    assert L.opsnn_qmm_umma_status(1) == 0
+
+    def run():
+        out = torch.full((m, n), -7777.0, dtype=torch.bfloat16, device=DEV)
+        aclnn.quant_matmul_v5(d[0], d[1], d[2], d[3], aclnn.from_torch(out))
+        torch.cuda.synchronize()
+        return out
+
+    monkeypatch.setenv("OPSNN_QMM_PAIR", "0")  # the single-CTA kernel carries the test switch
+    monkeypatch.setenv("OPSNN_TEST_UMMA_STALL_KBLOCK", "8")
+    monkeypatch.setenv("OPSNN_TEST_UMMA_POLL_LIMIT", "20000")
+    run()
+    assert aclnn.last_kernel_name() == "qmm_umma_deq"
+    monkeypatch.delenv("OPSNN_TEST_UMMA_STALL_KBLOCK")
+    monkeypatch.delenv("OPSNN_TEST_UMMA_POLL_LIMIT")
+    with pytest.raises(aclnn.AclnnError) as err:  # refused before anything is enqueued
+        run()
+    assert err.value.status == aclnn.ACLNN_ERR_RUNTIME_ERROR and "bounded wait" in str(err.value)
+    code = L.opsnn_qmm_umma_status(1)  # read and clear; also restores the poll limit
+    assert code != 0 and (code >> 8) in (2, 3), hex(code)  # the MMA issuer or an epilogue warp gave up first
+    out = run()
+    assert L.opsnn_qmm_umma_status(1) == 0
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, out_dtype="bfloat16")
+    assert np.array_equal(out_to_np(out).view(np.uint16), want.view(np.uint16))
