@@ -525,10 +525,21 @@ def run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, which):
         else:
             aclnn.quant_matmul_v5(d_x1, d_x2, d_s1, d_s2, d_out, bias_desc, False, False, MX_GROUP)
 
+    fused_ws = {}
+
     def step(i, transposed=False):
-        if not f4:
-            quant()  # c5: the activations are quantised on the fly, every step
-        mm(transposed)
+        if f4:
+            return mm(transposed)
+        # c5: ONE aclnnQuantMatmulV5 call pair per step on the bf16 activations (no x1Scale): the library quantises them on the fly
+        # (aclnnDynamicMxQuant's kernel, into the workspace) and runs the MXFP8 matmul - bit-identical to the two-call chain
+        key = bool(transposed)
+        if key not in fused_ws:
+            need = aclnn.quant_matmul_v5(d_act, d_x2t if transposed else d_x2, None, d_s2t if transposed else d_s2, d_out, d_bias, False,
+                                         transposed, MX_GROUP)
+            fused_ws[key] = torch.empty(max(int(need), 1), dtype=torch.uint8, device=dev)
+            return
+        aclnn.quant_matmul_v5(d_act, d_x2t if transposed else d_x2, None, d_s2t if transposed else d_s2, d_out, d_bias, False, transposed,
+                              MX_GROUP, workspace=fused_ws[key])
 
     # ---- parity (weight stored (k, n), the layout the configuration names), first and last batch of the shard ----
     if not f4:
@@ -586,6 +597,8 @@ def run_mx(torch, dev, aclnn, args, peaks, rank, world, dist, which):
     # the weight is a static parameter: its x1-independent layout work (scale atoms, k-contiguous copy) done once, outside the timed
     # region, the way the reference converts weights ahead of time with aclnnConvertWeightToINT4Pack; same entry points afterwards
     storage = aclnn.prepare_x2(d_x2, d_s2, False, MX_GROUP, m_hint=m)
+    fused_ws.clear()  # the prepared plan needs less workspace; size it again
+    step(0, False)
     torch.cuda.synchronize()
     out.fill_(-7777.0)
     launches0 = aclnn.launch_count()

@@ -50,6 +50,10 @@ struct aclOpExecutor {
     const void* nz_src = nullptr;
     int64_t nz_rows = 0, nz_row_bytes = 0, nz_r0 = 0, nz_c0_bytes = 0;
     uint64_t nz_bytes = 0;
+    // aclnnQuantMatmulV5 with a BF16 / FLOAT16 x1 and no x1Scale in the MX modes: x1 is quantised first (aclnnDynamicMxQuant's
+    // arithmetic, `mxq`) into the head of the workspace: dq_q_bytes of payload, then dq_s_bytes of e8m0 scales
+    bool dyn_quant = false;
+    uint64_t dq_q_bytes = 0, dq_s_bytes = 0;
 };
 
 namespace opsnn {

@@ -519,6 +519,59 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
         set_err("aclnnQuantMatmulV5GetWorkspaceSize: workspaceSize/executor is nullptr");
         return ACLNN_ERR_PARAM_NULLPTR;
     }
+    // Extension (no counterpart in the reference, whose checker refuses 16-bit x1 here): BF16 / FLOAT16 x1 with no x1Scale against an
+    // MX weight = "dynamic activation quantisation fused ahead". x1 is quantised with aclnnDynamicMxQuant's arithmetic (OCP shared
+    // exponent per 32 along k, round to nearest even; quant/dynamic_mx_quant/tests/assets/golden.py:141-217) to x2's element type
+    // into the workspace, then the MX matmul runs: one call pair, results bit-identical to the two-call chain.
+    if (x1 != nullptr && x2 != nullptr && x2Scale != nullptr && x1Scale == nullptr && out != nullptr &&
+        (x1->dtype == ACL_BF16 || x1->dtype == ACL_FLOAT16) && x2Scale->dtype == ACL_FLOAT8_E8M0 &&
+        (x2->dtype == ACL_FLOAT8_E4M3FN || x2->dtype == ACL_FLOAT8_E5M2 || x2->dtype == ACL_FLOAT4_E2M1)) {
+        const char* api = "aclnnQuantMatmulV5GetWorkspaceSize";
+        if (transposeX1 || x1->rank() < 2 || !is_contiguous(x1)) {
+            set_err("%s: a 16-bit x1 (quantised on the fly) must be contiguous, at least 2-D and not transposed", api);
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+        const int64_t k = x1->dim(-1);
+        if (x2->dtype == ACL_FLOAT4_E2M1 && (k & 1)) {
+            set_err("%s: fp4 quantisation needs an even k", api);
+            return ACLNN_ERR_PARAM_INVALID;
+        }
+        aclTensor q = *x1, sc = *x1;
+        q.dtype = x2->dtype;
+        q.data = reinterpret_cast<void*>(uintptr_t(256));  // stand-ins with allocation alignment; replaced by workspace addresses in phase 2
+        q.offset = 0;
+        sc.shape.back() = (k + 63) / 64;
+        sc.shape.push_back(2);
+        sc.dtype = ACL_FLOAT8_E8M0;
+        sc.strides.assign(sc.shape.size(), 1);
+        for (int i = (int)sc.shape.size() - 2; i >= 0; --i) sc.strides[i] = sc.strides[i + 1] * sc.shape[i + 1];
+        sc.storage_shape = sc.shape;
+        sc.data = reinterpret_cast<void*>(uintptr_t(256));
+        sc.offset = 0;
+        const aclnnStatus st = aclnnQuantMatmulV5GetWorkspaceSize(&q, x2, &sc, x2Scale, yScale, x1Offset, x2Offset, yOffset, bias, false,
+                                                                  transposeX2, groupSize, out, workspaceSize, executor);
+        if (st != ACLNN_SUCCESS) return st;
+        aclOpExecutor* exec = *executor;
+        if (exec->nothing_to_do) return ACLNN_SUCCESS;
+        exec->dyn_quant = true;
+        OpsnnMxQuantParams& mq = exec->mxq;
+        mq.x_dtype = x1->dtype;
+        mq.y_dtype = x2->dtype;
+        mq.k = k;
+        mq.rows = k > 0 ? x1->numel() / k : 0;
+        mq.x = x1->data == nullptr ? nullptr : data_ptr(x1);
+        mq.inner = 0;
+        mq.scale_alg = 0;
+        mq.round_mode = 0;
+        const uint64_t bits = (uint64_t)dtype_bits(x2->dtype);
+        exec->dq_q_bytes = (((uint64_t)x1->numel() * bits / 8) + 255u) & ~(uint64_t)255u;
+        exec->dq_s_bytes = (((uint64_t)mq.rows * 2u * (uint64_t)((k + 63) / 64)) + 255u) & ~(uint64_t)255u;
+        exec->qmm.a = nullptr;
+        exec->qmm.scale_a = nullptr;
+        exec->workspace_size += exec->dq_q_bytes + exec->dq_s_bytes;
+        *workspaceSize = exec->workspace_size;
+        return ACLNN_SUCCESS;
+    }
     if (x2 == nullptr) {
         set_err("aclnnQuantMatmulV5GetWorkspaceSize: x2 is nullptr");
         return ACLNN_ERR_PARAM_NULLPTR;
@@ -841,6 +894,24 @@ static aclnnStatus qmm_run(const char* api, void* workspace, uint64_t workspaceS
     if (workspaceSize < exec->workspace_size || (exec->workspace_size > 0 && workspace == nullptr)) {
         set_err("%s: workspace too small (%lu < %lu)", api, (unsigned long)workspaceSize, (unsigned long)exec->workspace_size);
         return ACLNN_ERR_PARAM_INVALID;
+    }
+    if (exec->dyn_quant) {  // 16-bit x1: quantised into the head of the workspace first, the matmul reads it from there
+        if (exec->mxq.x == nullptr) {
+            set_err("%s: a tensor was created without a device address", api);
+            return ACLNN_ERR_PARAM_NULLPTR;
+        }
+        uint8_t* ws = static_cast<uint8_t*>(workspace);
+        exec->mxq.y = ws;
+        exec->mxq.scale = ws + exec->dq_q_bytes;
+        const int32_t rc = opsnn_mx_quant_launch(&exec->mxq, stream);
+        if (rc != 0) {
+            set_err("%s: the activation quantiser failed with CUDA error %d", api, rc);
+            return ACLNN_ERR_RUNTIME_ERROR;
+        }
+        exec->qmm.a = ws;
+        exec->qmm.scale_a = ws + exec->dq_q_bytes;
+        workspace = ws + exec->dq_q_bytes + exec->dq_s_bytes;
+        workspaceSize -= exec->dq_q_bytes + exec->dq_s_bytes;
     }
     if (exec->nz_bytes != 0) {  // FRACTAL_NZ x2: row-major copy into the head of the workspace, the matmul gets the rest
         if (exec->nz_src == nullptr) {

@@ -268,3 +268,36 @@ def test_a8w4_fp8_x_fp4(aclnn, case):
     assert aclnn.last_kernel_name().startswith(expect), aclnn.last_kernel_name()
     assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
     _check(out_to_np(out), want, out_name)
+
+
+@pytest.mark.parametrize("dst", [E4M3, E2M1], ids=["mxfp8", "mxfp4"])
+def test_16bit_x1_is_quantised_on_the_fly_like_the_two_call_chain(aclnn, dst):
+    """aclnnQuantMatmulV5 with a BF16 x1 and no x1Scale against an MX weight (an extension: "dynamic activation quantisation fused
+    ahead"): one call pair must give exactly what aclnnDynamicMxQuant followed by the MX matmul gives, and the quantised operand
+    must be the quantiser oracle's bit for bit (checked through the two-call chain's buffers)."""
+    import torch
+
+    from gpu_util import DEV, desc, out_tensor, out_to_np
+    from oracle import mx_quant_oracle
+
+    rng = np.random.default_rng(case_seed("dynq" + str(dst)))
+    b, m, k, n = 2, 192, 512, 448
+    act = (rng.standard_normal((b, m, k)).astype(np.float32) * np.where(rng.random((b, m, k)) < 1e-3, 50.0, 1.0)).astype(ml_dtypes.bfloat16)
+    x2 = _q(rng, (b, n, k), dst)
+    s2 = _e8m0(rng, (b, n, k // 64, 2))
+    bias = rng.uniform(-2, 2, n).astype(np.float32)
+    name = "float4_e2m1" if dst == E2M1 else "float8_e4m3fn"
+    yq, sq = mx_quant_oracle.dynamic_mx_quant(act, name)
+    d_act, d_x2, d_s2, d_bias = desc(aclnn, act), desc(aclnn, x2), desc(aclnn, s2), desc(aclnn, bias)
+    # two calls
+    two = out_tensor((b, m, n), "bfloat16")
+    aclnn.quant_matmul_v5(desc(aclnn, yq), d_x2, desc(aclnn, sq.view(E8M0)), d_s2, aclnn.Tensor(two.shape, "bfloat16", two), d_bias, False, True,
+                          GROUP_MX)
+    # one call
+    one = out_tensor((b, m, n), "bfloat16")
+    before = aclnn.launch_count()
+    aclnn.quant_matmul_v5(d_act, d_x2, None, d_s2, aclnn.Tensor(one.shape, "bfloat16", one), d_bias, False, True, GROUP_MX)
+    torch.cuda.synchronize()
+    assert aclnn.launch_count() - before >= 2 and aclnn.last_kernel_name().startswith("qmm_umma")
+    assert np.array_equal(out_to_np(one).view(np.uint16), out_to_np(two).view(np.uint16))
+    _check(out_to_np(one), _oracle(yq, x2, sq.view(E8M0), s2, bias, False, True, "bfloat16"), "bfloat16")
