@@ -53,6 +53,8 @@ static int32_t decode_stream_launch(const OpsnnWqbmmParams* p, cudaStream_t stre
     return wqbmm_decode_ring_launch(p, stream, exact);
 }
 
+bool wqbmm_decode8_eligible(const OpsnnWqbmmParams* p);
+int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
 uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
@@ -183,6 +185,8 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
     }
     if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
+    // 8-bit integer weights at small m: their own streaming kernel once the weight is large enough to be worth a k-split grid
+    if (wqbmm_decode8_eligible(p) && p->k * p->n >= ((int64_t)1 << 20) && getenv("OPSNN_WQ_NO_DECODE8") == nullptr) return OPSNN_WQ_KERNEL_DECODE;
     OpsnnWqbmmParams chunk;
     if (getenv("OPSNN_WQ_NO_CHUNKS") == nullptr && decode_in_chunks(p, &chunk))
         return (p->inner_precise == 1 && wqbmm_decode_fast_eligible(&chunk)) ? OPSNN_WQ_KERNEL_DECODE_FAST : OPSNN_WQ_KERNEL_DECODE;
@@ -225,6 +229,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
         if (!decode_in_chunks(p, &chunk)) return (int32_t)cudaErrorInvalidValue;
         if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST && !wqbmm_decode_fast_eligible(&chunk)) return (int32_t)cudaErrorInvalidValue;
         return decode_chunk_launches(p, static_cast<cudaStream_t>(stream), kernel_choice);
+    }
+    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE && p->w_dtype == ACL_INT8) {
+        if (!wqbmm_decode8_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return wqbmm_decode8_launch(p, static_cast<cudaStream_t>(stream));
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE) {
         if (!wqbmm_decode_eligible(p)) return (int32_t)cudaErrorInvalidValue;

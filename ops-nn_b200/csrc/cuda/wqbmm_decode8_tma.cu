@@ -1,0 +1,450 @@
+// Weight-only quant matmul, streaming decode kernel for 8-bit integer weights (W8A16, m <= 16, INT8 weight stored (k,n)).
+//
+// The reference runs this regime on its n-first kernels (weight_quant_batch_matmul_v2/op_kernel/arch35/n_first/*); the arithmetic
+// is the golden's: w' = rn(rn(w + offset) * scale) in x's dtype, y = x @ w' in fp32 (wqbmmv2_kernel_golden.py:199-297).
+// Same structure as the int4 kernel of wqbmm_decode_tma.cu: a CTA of 8 warps owns 512 columns and a k range of whole 64-row stages,
+// a stage is four TMA boxes of 128 bytes x 64 rows of weights + one of x in the 128-byte swizzle, the warp whose turn it is
+// refills the buffer it left one stage ago, k-splits are combined through workspace by the last arriver in CTA order.
+//
+// Fragments. A warp's 64 columns are four 16-byte chunks of every k row. ldmatrix.trans works on 16-bit elements, i.e. on PAIRS of
+// adjacent byte columns: lane (g, q) receives, per 8 x 16-byte matrix, the bytes of columns 2g and 2g+1 of rows 2q and 2q+1. The
+// even column feeds one MMA tile, the odd one another (the column permutation is undone when y is written). A byte b = w mod 256
+// becomes bf16(w) exactly with two logic ops and one subtraction: (b & 0x7f) | 0x4300 is 128 + (b & 0x7f), (b & 0x80) | 0x4300 is
+// 128 or 256, their difference is w (fp16: 0x6400, 1024 + ..., same idea with ten mantissa bits).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "wqbmm_decode_common.cuh"
+
+namespace opsnn {
+
+namespace {
+
+constexpr int k8StageSteps = 4;
+constexpr int k8StageRows = k8StageSteps * 16;          // 64 k rows
+constexpr int k8WBox = 128 * k8StageRows;               // 8192: 128 columns x 64 rows
+constexpr int k8XBox = 128 * 16;                        // x: 64 k x 16 rows
+constexpr int k8Stage = 4 * k8WBox + k8XBox;            // 34816
+constexpr int k8Stages = 3;
+constexpr int k8Smem = k8Stages * k8Stage + 1024 + 256;
+constexpr uint32_t k8Polls = 4u * 1000u * 1000u;
+
+template <bool kBf16>
+struct Num8;
+template <>
+struct Num8<true> {
+    static constexpr uint32_t kLowMask = 0x007F007Fu, kHighMask = 0x00800080u, kMagic = 0x43004300u;  // bf16 128.0
+};
+template <>
+struct Num8<false> {
+    // fp16 has ten mantissa bits: the whole byte fits under 0x6400 (1024.0): (b ^ 0x80) | 0x6400 = 1024 + 128 + w
+    static constexpr uint32_t kLowMask = 0x00FF00FFu, kHighMask = 0x00800080u, kMagic = 0x64006400u;
+};
+
+__device__ __forceinline__ void d8_ldsm4(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <int kOff>
+__device__ __forceinline__ void d8_ldsm4_trans(uint32_t addr, uint32_t (&r)[4])
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr), "n"(kOff));
+}
+__device__ __forceinline__ void d8_tma_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_addr, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void d8_arrive(uint32_t bar_addr) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory"); }
+
+__device__ unsigned int g_wq8_status = 0;  // 0, or 1 (a stage never arrived) / 2 (a stage buffer was never released)
+
+static __device__ __noinline__ bool d8_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int code)
+{
+    for (uint32_t i = 0; i < k8Polls; ++i) {
+        if (ptx::mbar_try_wait_a(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    atomicCAS(&g_wq8_status, 0u, code);
+    return false;
+}
+__device__ __forceinline__ bool d8_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int code)
+{
+    if (ptx::mbar_try_wait_a(bar, parity)) return true;
+    return d8_wait_slow(bar, parity, abort_flag, code);
+}
+
+struct D8Args {
+    DecodeArgs d;
+    int32_t total_stages;      // ceil(k / 64)
+    int32_t stages_per_group;  // group_size / 64, or "never" for a single group
+};
+
+template <bool kBf16, bool kHasOffset>
+__global__ void __launch_bounds__(kThreads, 2)
+wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const D8Args ta)
+{
+    using N = Num<kBf16>;
+    using N8 = Num8<kBf16>;
+    const DecodeArgs& a = ta.d;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    __shared__ int s_reduce;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ int s_issued[k8Stages];
+    extern __shared__ uint8_t dyn_raw[];
+    const uint32_t smem0 = (ptx::smem_u32(dyn_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem0 + k8Stages * k8Stage;  // full[i] at bar0 + 8 i, empty[i] at bar0 + 64 + 8 i
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int64_t c = blockIdx.x;
+    const int64_t strip = c % a.strips;
+    const int64_t chunk = c / a.strips;
+    const int st_a = (int)((chunk * ta.total_stages) / a.splits);
+    const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
+    const int nst = st_b - st_a;
+    const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
+    const int32_t wcol_bytes = (int32_t)(strip * kStripCols);
+
+    if (tid == 0) {
+        s_abort = 0u;
+        for (int i = 0; i < k8Stages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8u * i), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 64u + 8u * i), "r"((uint32_t)kWarps) : "memory");
+            s_issued[i] = -1;
+        }
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_x);
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    volatile uint32_t* abort_flag = &s_abort;
+
+    auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
+        const uint32_t fb = bar0 + 8u * buf;
+        const uint32_t dst = smem0 + (uint32_t)buf * k8Stage;
+        const int32_t krow = (st_a + t) * k8StageRows;
+        s_issued[buf] = t;
+        ptx::mbar_expect_tx_a(fb, (uint32_t)k8Stage);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) d8_tma_2d(dst + b * k8WBox, &map_w, fb, wcol_bytes + 128 * b, krow);
+        d8_tma_2d(dst + 4 * k8WBox, &map_x, fb, krow * 2, 0);
+    };
+    if (tid == 0) {
+        const int pro = nst < k8Stages ? nst : k8Stages;
+        for (int t = 0; t < pro; ++t) issue_stage(t, t);
+    }
+
+    float total[kTiles][4];
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) total[t][0] = total[t][1] = total[t][2] = total[t][3] = 0.f;
+
+    // ---- scale / offset of the current k-group: tile t = (chunk t / 2, column parity t & 1) is column 16 (t / 2) + 2 g + (t & 1)
+    // for this lane, so one 32-bit load per chunk holds the two columns of its two tiles ----
+    const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+    const int64_t n_groups = (a.ksteps + spg - 1) / spg;
+    int64_t ecol[4];
+#pragma unroll
+    for (int cidx = 0; cidx < 4; ++cidx) ecol[cidx] = (warp_col + 16 * cidx + 2 * g < a.n) ? warp_col + 16 * cidx + 2 * g : 0;
+    uint32_t sc[kTiles], of[kHasOffset ? kTiles : 1], rs_next[4], ro_next[kHasOffset ? 4 : 1];
+    auto fetch = [&](int64_t group) {
+        if (a.scale_sn != 0) {
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx) rs_next[cidx] = __ldg(reinterpret_cast<const uint32_t*>(sp + ecol[cidx]));
+            if (kHasOffset) {
+                const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+#pragma unroll
+                for (int cidx = 0; cidx < 4; ++cidx) ro_next[kHasOffset ? cidx : 0] = __ldg(reinterpret_cast<const uint32_t*>(op + ecol[cidx]));
+            }
+        } else {
+            const uint32_t sv = reinterpret_cast<const uint16_t*>(a.scale)[group * a.scale_sg];
+#pragma unroll
+            for (int cidx = 0; cidx < 4; ++cidx) rs_next[cidx] = sv | (sv << 16);
+            if (kHasOffset) {
+                const uint32_t ov = reinterpret_cast<const uint16_t*>(a.offset)[group * a.scale_sg];
+#pragma unroll
+                for (int cidx = 0; cidx < 4; ++cidx) ro_next[kHasOffset ? cidx : 0] = ov | (ov << 16);
+            }
+        }
+    };
+    auto load_group = [&](int64_t group) {
+        if (group >= n_groups) group = n_groups - 1;
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {  // each value in both halves of a register: the halves are two k rows of one column
+            const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
+            sc[t] = prmt(rs_next[t >> 1], rs_next[t >> 1], sel);
+            if (kHasOffset) of[kHasOffset ? t : 0] = prmt(ro_next[kHasOffset ? t >> 1 : 0], ro_next[kHasOffset ? t >> 1 : 0], sel);
+        }
+        fetch(min(group + 1, n_groups - 1));
+    };
+    // two bytes (rows 2q, 2q+1 of one column, in the low byte of each half) -> two dequantised weights
+    auto deq = [&](uint32_t x, int t) {
+        uint32_t lo, v;
+        if (kBf16) {
+            uint32_t hi;
+            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(lo) : "r"(x), "n"(N8::kLowMask), "n"(N8::kMagic));   // (x & mask) | magic
+            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(hi) : "r"(x), "n"(N8::kHighMask), "n"(N8::kMagic));
+            v = N::sub(lo, hi);  // (128 + (b & 0x7f)) - (128 or 256) = w, exact
+        } else {
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(lo) : "r"(x), "n"(N8::kLowMask), "n"(0x64806480));  // ((x & 0xff) ^ 0x80) | 0x6400
+            v = N::sub(lo, 0x64806480u);  // (1024 + 128 + w) - 1152 = w, exact
+        }
+        if (kHasOffset) v = N::add(v, of[kHasOffset ? t : 0]);
+        return N::mul(v, sc[t]);
+    };
+    // one k-step: 8 registers (two ldmatrix.x4.trans) -> 16 B-fragment registers -> 8 MMAs
+    auto compute = [&](const uint32_t(&wa)[4], const uint32_t(&wb)[4], const uint32_t(&af)[4]) {
+        // wa: chunks 0, 1 as (rows 0-7, rows 8-15) pairs; wb: chunks 2, 3
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+            const uint32_t e0 = deq(wa[2 * cc], 2 * cc), e1 = deq(wa[2 * cc + 1], 2 * cc);
+            const uint32_t o0 = deq(wa[2 * cc] >> 8, 2 * cc + 1), o1 = deq(wa[2 * cc + 1] >> 8, 2 * cc + 1);
+            N::mma_free(total[2 * cc], af, e0, e1);
+            N::mma_free(total[2 * cc + 1], af, o0, o1);
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+            const uint32_t e0 = deq(wb[2 * cc], 4 + 2 * cc), e1 = deq(wb[2 * cc + 1], 4 + 2 * cc);
+            const uint32_t o0 = deq(wb[2 * cc] >> 8, 5 + 2 * cc), o1 = deq(wb[2 * cc + 1] >> 8, 5 + 2 * cc);
+            N::mma_free(total[4 + 2 * cc], af, e0, e1);
+            N::mma_free(total[5 + 2 * cc], af, o0, o1);
+        }
+    };
+
+    // ---- per-lane ldmatrix addresses inside a stage (128-byte swizzle: 16-byte chunk index ^ (row & 7)) ----
+    // weights: the warp's 64 columns are chunks 4 (warp & 1) .. + 3 of box warp / 2; matrix j = lane / 8 is
+    // (rows 0-7 | 8-15)[j & 1] x (chunk pair's first | second chunk)[j >> 1]; the second ldmatrix takes the next two chunks
+    const int li = lane & 7, lj = lane >> 3;
+    const uint32_t row_off = (uint32_t)(li + 8 * (lj & 1)) * 128u;
+    const uint32_t cbase = 4u * (uint32_t)(warp & 1);
+    const uint32_t wlane_a = (uint32_t)(warp >> 1) * k8WBox + row_off + (((cbase + (uint32_t)(lj >> 1)) ^ (uint32_t)li) << 4);
+    const uint32_t wlane_b = (uint32_t)(warp >> 1) * k8WBox + row_off + (((cbase + 2u + (uint32_t)(lj >> 1)) ^ (uint32_t)li) << 4);
+    const uint32_t xlane = 4u * k8WBox + row_off + ((((uint32_t)lj >> 1) ^ (uint32_t)li) << 4);
+
+    int64_t group = ((int64_t)st_a * k8StageSteps) / spg;
+    fetch(min(group, n_groups - 1));
+    load_group(group);
+    int until_change = ta.stages_per_group - (st_a % ta.stages_per_group);
+
+    uint32_t wa0[4], wb0[4], a0[4], wa1[4], wb1[4], a1[4];
+    int buf = 0;
+    uint32_t par = 0;
+    bool ok = nst > 0;
+    if (ok) {
+        ok = d8_wait(bar0, 0u, abort_flag, 1u);
+        d8_ldsm4_trans<0>(smem0 + wlane_a, wa0);
+        d8_ldsm4_trans<0>(smem0 + wlane_b, wb0);
+        d8_ldsm4(smem0 + xlane, a0);
+    }
+    const int duty = (warp + 8 * 8 - (k8Stages - 1)) & 7;  // this warp refills when (stage index & 7) == duty
+    for (int j = 0; j < nst && ok; ++j) {
+        const uint32_t sbase = smem0 + (uint32_t)buf * k8Stage;
+        const uint32_t wba = sbase + wlane_a, wbb = sbase + wlane_b, xb = sbase + xlane;
+        if (j >= 1 && (j & 7) == duty && j + k8Stages - 1 < nst) {
+            if (lane == 0) {
+                const int pbuf = buf == 0 ? k8Stages - 1 : buf - 1;
+                const uint32_t ppar = buf == 0 ? par ^ 1u : par;
+                if (d8_wait(bar0 + 64u + 8u * pbuf, ppar, abort_flag, 2u)) issue_stage(j + k8Stages - 1, pbuf);
+            }
+            __syncwarp();
+        }
+        if (j > 0 && until_change == 0) {
+            load_group(++group);
+            until_change = ta.stages_per_group;
+        }
+        // step 0
+        d8_ldsm4_trans<2048>(wba, wa1);
+        d8_ldsm4_trans<2048>(wbb, wb1);
+        d8_ldsm4(xb ^ 32u, a1);
+        compute(wa0, wb0, a0);
+        // step 1
+        d8_ldsm4_trans<4096>(wba, wa0);
+        d8_ldsm4_trans<4096>(wbb, wb0);
+        d8_ldsm4(xb ^ 64u, a0);
+        compute(wa1, wb1, a1);
+        // step 2
+        d8_ldsm4_trans<6144>(wba, wa1);
+        d8_ldsm4_trans<6144>(wbb, wb1);
+        d8_ldsm4(xb ^ 96u, a1);
+        compute(wa0, wb0, a0);
+        // step 3, after the first fragments of the next stage have been requested
+        int nbuf = buf + 1;
+        uint32_t npar = par;
+        if (nbuf == k8Stages) { nbuf = 0; npar ^= 1u; }
+        if (j + 1 < nst) {
+            ok = d8_wait(bar0 + 8u * nbuf, npar, abort_flag, 1u);
+            const uint32_t nb = smem0 + (uint32_t)nbuf * k8Stage;
+            d8_ldsm4_trans<0>(nb + wlane_a, wa0);
+            d8_ldsm4_trans<0>(nb + wlane_b, wb0);
+            d8_ldsm4(nb + xlane, a0);
+        }
+        compute(wa1, wb1, a1);
+        --until_change;
+        __syncwarp();
+        if (lane == 0) d8_arrive(bar0 + 64u + 8u * buf);
+        buf = nbuf;
+        par = npar;
+    }
+
+    if (__syncthreads_or(s_abort != 0u)) {
+        // A wait gave up. Nothing is written; the copies already issued get a bounded time to land before the CTA leaves.
+        if (tid == 0) {
+            for (int i = 0; i < k8Stages; ++i) {
+                const int t = s_issued[i];
+                if (t < 0) continue;
+                const uint32_t p = (uint32_t)(t / k8Stages) & 1u;
+                for (uint32_t it = 0; it < k8Polls; ++it)
+                    if (ptx::mbar_try_wait_a(bar0 + 8u * i, p)) break;
+            }
+        }
+        __syncthreads();
+        return;
+    }
+    combine_and_store<kBf16, 2>(a, total, c, strip, warp, lane, tid, &s_reduce);
+}
+
+using D8EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+D8EncodeFn d8_encoder()
+{
+    static D8EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<D8EncodeFn>(p);
+    }();
+    return fn;
+}
+
+bool d8_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows)
+{
+    D8EncodeFn enc = d8_encoder();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {inner_bytes, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+std::atomic<uint64_t> g_d8_configured[4];
+
+template <bool kBf16, bool kHasOffset>
+cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const D8Args& ta, cudaStream_t stream)
+{
+    auto kern = wqbmm_decode8_tma_kernel<kBf16, kHasOffset>;
+    cudaError_t rc = once_per_device(g_d8_configured[variant], [&] {
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, k8Smem);
+    });
+    if (rc != cudaSuccess) return rc;
+    const char* pe = getenv("OPSNN_WQ_PDL");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = k8Smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (pe == nullptr || pe[0] != '0') ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, mw, mx, ta);
+}
+
+constexpr int k8MaxGrid = 148 * 4 * 2;
+
+}  // namespace
+
+uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
+
+// INT8 weight stored (k,n), m <= 16, scale (and offset) in x's dtype per channel / per tensor / per k-group of whole 64-row stages.
+bool wqbmm_decode8_eligible(const OpsnnWqbmmParams* p)
+{
+    if (p->w_dtype != ACL_INT8 || p->trans_w != 0 || p->nz_k0 != 0) return false;
+    if (p->scale_dtype == ACL_FLOAT8_E8M0) return false;
+    if (p->m < 1 || p->m > 16 || p->k < 16 || p->k % 16 != 0) return false;
+    if (p->n % 16 != 0 || p->w_ld % 16 != 0 || p->x_ld % 8 != 0) return false;  // 16-byte tensor-map pitches; column pairs for the scale loads
+    if (p->group_size != 0 && p->group_size % 64 != 0) return false;           // group changes at stage boundaries only
+    if (p->scale_sn != 0 && p->scale_sn != 1) return false;
+    if (p->scale_sn == 1 && p->group_size != 0 && p->scale_sg % 2 != 0) return false;
+    auto aligned = [](const void* q, uintptr_t al) { return (reinterpret_cast<uintptr_t>(q) % al) == 0; };
+    if (!aligned(p->w, 16) || !aligned(p->x, 16)) return false;
+    if (p->scale_sn == 1 && (!aligned(p->scale, 4) || (p->offset && !aligned(p->offset, 4)))) return false;
+    if (p->n >= ((int64_t)1 << 31) || p->k >= ((int64_t)1 << 30)) return false;
+    return true;
+}
+
+int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+{
+    D8Args ta{};
+    DecodeArgs& a = ta.d;
+    a.scale = p->scale;
+    a.offset = p->offset;
+    a.scale_sg = p->group_size > 0 ? p->scale_sg : 0;
+    a.scale_sn = (int32_t)p->scale_sn;
+    a.bias = p->bias;
+    a.bias_dtype = p->bias_dtype;
+    a.y = p->y;
+    a.y_ld = p->y_ld;
+    a.m = (int32_t)p->m;
+    a.n = p->n;
+    a.k = p->k;
+    a.strips = (p->n + kStripCols - 1) / kStripCols;
+    a.ksteps = p->k / 16;
+    a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
+    ta.total_stages = (int32_t)((a.ksteps + k8StageSteps - 1) / k8StageSteps);
+    const bool single_group = a.steps_per_group >= a.ksteps;
+    ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / k8StageSteps);
+    const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
+
+    int64_t splits = (2 * (int64_t)current_sm_count()) / a.strips;
+    if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
+        const int v = atoi(e);
+        if (v > 0) splits = v;
+    }
+    if (splits > ta.total_stages) splits = ta.total_stages;
+    if (splits * a.strips > k8MaxGrid) splits = k8MaxGrid / a.strips;
+    if (splits < 1) splits = 1;
+    a.splits = splits;
+    const int64_t grid64 = a.strips * splits;
+    if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
+    const uint64_t tag_bytes = (((uint64_t)k8MaxGrid * 8 + 255) / 256) * 256;
+    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
+    a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
+    a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
+    a.nonce = next_nonce();
+
+    CUtensorMap mw, mx;
+    if (!d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows) ||
+        !d8_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
+        return (int32_t)cudaErrorInvalidValue;
+    const int grid = (int)grid64;
+    cudaError_t rc;
+    if (bf16) rc = has_off ? d8_launch_variant<true, true>(3, grid, mw, mx, ta, stream) : d8_launch_variant<true, false>(2, grid, mw, mx, ta, stream);
+    else rc = has_off ? d8_launch_variant<false, true>(1, grid, mw, mx, ta, stream) : d8_launch_variant<false, false>(0, grid, mw, mx, ta, stream);
+    note_launch("wqbmm_decode8");
+    return (int32_t)rc;
+}
+
+uint32_t wqbmm_decode8_status(int reset)
+{
+    unsigned int v = 0;
+    cudaMemcpyFromSymbol(&v, g_wq8_status, sizeof(v));
+    if (reset) {
+        unsigned int z = 0;
+        cudaMemcpyToSymbol(g_wq8_status, &z, sizeof(z));
+    }
+    return v;
+}
+
+}  // namespace opsnn

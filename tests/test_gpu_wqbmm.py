@@ -239,3 +239,52 @@ def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, 
     got = out_to_np(y).astype(np.float64)
     rms = np.sqrt(np.mean(want ** 2))
     assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
+
+
+W8_CASES = [
+    # x dtype, m, k, n, group, offset, bias
+    ("bfloat16", 16, 2048, 1024, 0, False, False),     # per-channel, symmetric: the common W8A16 form
+    ("bfloat16", 5, 4096, 1040, 0, True, True),        # ragged last strip, fewer than 16 rows, offset + bias
+    ("float16", 16, 2048, 768, 128, True, False),      # per-group (two stages per group), fp16
+    ("bfloat16", 1, 8192, 512, 64, False, True),       # one group per stage, m = 1
+]
+
+
+@pytest.mark.parametrize("case", W8_CASES, ids=[str(c) for c in W8_CASES])
+def test_w8a16_small_m_streaming_kernel(aclnn, case):
+    """INT8 weights at m <= 16 run on their own streaming kernel (the reference's n-first regime,
+    weight_quant_batch_matmul_v2/op_kernel/arch35/n_first/*); it reproduces the golden's two roundings per weight, so only the
+    fp32 summation order differs: <= 1 ulp of the output dtype."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    xdt, m, k, n, group, has_off, has_bias = case
+    rng = np.random.default_rng(case_seed(case))
+    np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(np_dt)
+    w = rng.integers(-128, 128, (k, n)).astype(np.int8)
+    groups = k // group if group else 1
+    sc = rng.uniform(0.002, 0.01, (groups, n)).astype(np.float32).astype(np_dt)
+    of = rng.uniform(-3, 3, (groups, n)).astype(np.float32).astype(np_dt) if has_off else None
+    bias = rng.uniform(-1, 1, n).astype(np.float32).astype(np_dt) if has_bias else None
+
+    def dev(a):
+        if a is None:
+            return None
+        if a.dtype == np.dtype(ml_dtypes.bfloat16):
+            return aclnn.from_torch(torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV))
+        return aclnn.from_torch(torch.from_numpy(a.copy()).to(DEV))
+
+    y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
+    aclnn.weight_quant_batch_matmul(dev(x), dev(w), dev(sc if group else sc[0]), aclnn.from_torch(y), dev(of if (group or of is None) else of[0]),
+                                    dev(bias), group)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, bias, group).astype(np.float64)
+    got = out_to_np(y).astype(np.float64)
+    assert not np.any(got == -7777.0)
+    ulp = 2.0 ** -7 if xdt == "bfloat16" else 2.0 ** -10
+    rms = np.sqrt(np.mean(want ** 2))
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
