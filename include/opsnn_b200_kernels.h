@@ -231,6 +231,10 @@ OPSNN_API uint32_t opsnn_qmm_umma_status(int32_t reset);
 /* The same for the streaming W4A16 decode kernel that feeds shared memory with bulk tensor copies: 0, or 1 (a stage of
  * operands never arrived) / 2 (a stage buffer was never released). Synchronises the device. */
 OPSNN_API uint32_t opsnn_wqbmm_decode_status(int32_t reset);
+/* How the calling thread's last streaming decode launch (W4A16 / W8A16, bulk-copy kernels) cut the problem: strips of 512
+ * columns, k-ranges per strip, and whether the k-ranges of a strip ran as one thread-block cluster (summed over distributed
+ * shared memory) or were summed through the workspace. Any pointer may be null. */
+OPSNN_API void opsnn_wqbmm_decode_last_plan(int32_t* strips, int32_t* splits, int32_t* cluster);
 
 /* ---- measured ceilings (diagnostics; not on any product path) --------------------------------------------------------------
  * opsnn_probe_umma: clocks per tcgen05.mma (128 x bn x 32 bytes of k) when one CTA per SM issues them back to back on operands

@@ -93,6 +93,8 @@ def lib():
     L.opsnn_qmm_umma_status.argtypes = [c_int32]
     L.opsnn_wqbmm_decode_status.restype = ctypes.c_uint32
     L.opsnn_wqbmm_decode_status.argtypes = [c_int32]
+    L.opsnn_wqbmm_decode_last_plan.restype = None
+    L.opsnn_wqbmm_decode_last_plan.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     L.opsnn_last_kernel_name.restype = c_char_p
     for name in ("opsnn_wqbmm_launch", "opsnn_wqbmm_decode_static_launch"):
         getattr(L, name).restype = c_int32
@@ -136,6 +138,14 @@ def launch_count():
 
 def last_kernel_name():
     return lib().opsnn_last_kernel_name().decode()
+
+
+def last_decode_plan():
+    """(strips, k-ranges per strip, 1 if the k-ranges ran as one thread-block cluster) of this thread's last streaming decode launch."""
+    v = (c_int32 * 3)()
+    base = ctypes.addressof(v)
+    lib().opsnn_wqbmm_decode_last_plan(base, base + 4, base + 8)
+    return int(v[0]), int(v[1]), int(v[2])
 
 
 class AclnnError(RuntimeError):

@@ -17,6 +17,7 @@ namespace opsnn {
 // Host: count a launch and remember which kernel family ran (read back through opsnn_launch_count /
 // opsnn_last_kernel_name).
 void note_launch(const char* name, uint64_t n = 1);
+void note_decode_plan(int64_t strips, int64_t splits, int32_t cluster);  // what the last streaming decode launch of this thread used
 
 // Host: set-up that is a property of the (function, device) pair - the dynamic shared-memory limit of a kernel, occupancy - done the
 // first time a launcher runs with each device current. `done` holds one bit per device ordinal. Two threads racing on the same first

@@ -19,6 +19,14 @@ void note_launch(const char* name, uint64_t n)
     g_last_kernel = name;
 }
 
+static thread_local int32_t g_decode_plan[3] = {0, 0, 0};
+void note_decode_plan(int64_t strips, int64_t splits, int32_t cluster)
+{
+    g_decode_plan[0] = (int32_t)strips;
+    g_decode_plan[1] = (int32_t)splits;
+    g_decode_plan[2] = cluster;
+}
+
 int32_t qmm_generic_launch(const OpsnnQmmParams* p, cudaStream_t stream);
 bool qmm_umma_eligible(const OpsnnQmmParams* p);
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p);
@@ -269,3 +277,10 @@ uint64_t opsnn_launch_count(void) { return g_launches.load(std::memory_order_rel
 const char* opsnn_last_kernel_name(void) { return g_last_kernel; }
 
 }  // extern "C"
+
+extern "C" OPSNN_API void opsnn_wqbmm_decode_last_plan(int32_t* strips, int32_t* splits, int32_t* cluster)
+{
+    if (strips != nullptr) *strips = opsnn::g_decode_plan[0];
+    if (splits != nullptr) *splits = opsnn::g_decode_plan[1];
+    if (cluster != nullptr) *cluster = opsnn::g_decode_plan[2];
+}

@@ -102,8 +102,8 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int64_t c = blockIdx.x;
-    const int64_t strip = c % a.strips;
-    const int64_t chunk = c / a.strips;
+    const int64_t strip = a.cluster ? c / a.splits : c % a.strips;
+    const int64_t chunk = a.cluster ? c % a.splits : c / a.strips;
     const int st_a = (int)((chunk * ta.total_stages) / a.splits);
     const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
     const int nst = st_b - st_a;
@@ -293,7 +293,8 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         par = npar;
     }
 
-    if (__syncthreads_or(s_abort != 0u)) {
+    const bool aborted = __syncthreads_or(s_abort != 0u) != 0;
+    if (aborted) {
         // A wait gave up. Nothing is written; the copies already issued get a bounded time to land before the CTA leaves.
         if (tid == 0) {
             for (int i = 0; i < k8Stages; ++i) {
@@ -305,9 +306,11 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             }
         }
         __syncthreads();
-        return;
+        if (!a.cluster) return;
     }
-    combine_and_store<kBf16, 2>(a, total, c, strip, warp, lane, tid, &s_reduce);
+    // every warp is past its last stage (barrier above): the stage buffers are free to hold the fragments
+    if (a.cluster) cluster_combine_and_store<kBf16, 2>(a, total, strip, warp, lane, tid, smem0, !aborted);
+    else combine_and_store<kBf16, 2>(a, total, c, strip, warp, lane, tid, &s_reduce);
 }
 
 using D8EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -338,29 +341,56 @@ bool d8_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_
 
 std::atomic<uint64_t> g_d8_configured[4];
 
-template <bool kBf16, bool kHasOffset>
-cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const D8Args& ta, cudaStream_t stream)
+// variant = 2 bf16 + has_offset
+const void* d8_kernel(int variant)
 {
-    auto kern = wqbmm_decode8_tma_kernel<kBf16, kHasOffset>;
-    cudaError_t rc = once_per_device(g_d8_configured[variant], [&] {
+    switch (variant) {
+        case 0: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false>);
+        case 1: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, true>);
+        case 2: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false>);
+        default: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, true>);
+    }
+}
+
+cudaError_t d8_configure_variant(int variant)
+{
+    const void* kern = d8_kernel(variant);
+    return once_per_device(g_d8_configured[variant], [&] {
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);  // clusters of up to 16 k-splits
         return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, k8Smem);
     });
-    if (rc != cudaSuccess) return rc;
+}
+
+cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const D8Args& ta, cudaStream_t stream)
+{
     const char* pe = getenv("OPSNN_WQ_PDL");
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = k8Smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = (pe == nullptr || pe[0] != '0') ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, mw, mx, ta);
+    cudaLaunchAttribute attr[2]{};
+    unsigned na = 0;
+    if (pe == nullptr || pe[0] != '0') {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (ta.d.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)ta.d.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    void* args[3] = {const_cast<CUtensorMap*>(&mw), const_cast<CUtensorMap*>(&mx), const_cast<D8Args*>(&ta)};
+    return cudaLaunchKernelExC(&cfg, d8_kernel(variant), args);
 }
 
+constexpr int k8ClusterMaxStrips = 28;
 constexpr int k8MaxGrid = 148 * 4 * 2;
 
 }  // namespace
@@ -407,19 +437,35 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / k8StageSteps);
     const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
 
+    const int variant = (bf16 ? 2 : 0) + (has_off ? 1 : 0);
+    cudaError_t crc = d8_configure_variant(variant);
+    if (crc != cudaSuccess) return (int32_t)crc;
     int64_t splits = (2 * (int64_t)current_sm_count()) / a.strips;
-    if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
-        const int v = atoi(e);
-        if (v > 0) splits = v;
-    }
+    const char* se = getenv("OPSNN_WQ_DECODE_SPLITS");
+    const char* ce = getenv("OPSNN_WQ_DECODE_CLUSTER");
+    if (se != nullptr && atoi(se) > 0) splits = atoi(se);
     if (splits > ta.total_stages) splits = ta.total_stages;
     if (splits * a.strips > k8MaxGrid) splits = k8MaxGrid / a.strips;
     if (splits < 1) splits = 1;
+    // narrow outputs: the k-splits of a strip as one cluster, summed over distributed shared memory; same rules as the int4 kernel
+    a.cluster = 0;
+    if (ce == nullptr || ce[0] != '0') {
+        if (se != nullptr || (ce != nullptr && splits <= 16)) {
+            a.cluster = (splits >= 2 && splits <= 16 && (ce != nullptr || a.strips <= k8ClusterMaxStrips)) ? 1 : 0;
+        } else if (a.strips <= k8ClusterMaxStrips && splits >= 2) {
+            const int s_pick = pick_cluster_size(d8_kernel(variant), kThreads, k8Smem, a.strips, (int)(splits < 16 ? splits : 16));
+            if (s_pick >= 2) {
+                splits = s_pick;
+                a.cluster = 1;
+            }
+        }
+    }
+    if (!a.cluster && se == nullptr && splits > 16) splits = 16;
     a.splits = splits;
     const int64_t grid64 = a.strips * splits;
     if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
     const uint64_t tag_bytes = (((uint64_t)k8MaxGrid * 8 + 255) / 256) * 256;
-    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
+    if (splits > 1 && !a.cluster && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
     a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
     a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
     a.nonce = next_nonce();
@@ -428,11 +474,9 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     if (!d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows) ||
         !d8_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
-    const int grid = (int)grid64;
-    cudaError_t rc;
-    if (bf16) rc = has_off ? d8_launch_variant<true, true>(3, grid, mw, mx, ta, stream) : d8_launch_variant<true, false>(2, grid, mw, mx, ta, stream);
-    else rc = has_off ? d8_launch_variant<false, true>(1, grid, mw, mx, ta, stream) : d8_launch_variant<false, false>(0, grid, mw, mx, ta, stream);
+    const cudaError_t rc = d8_launch_variant(variant, (int)grid64, mw, mx, ta, stream);
     note_launch("wqbmm_decode8");
+    note_decode_plan(a.strips, a.splits, a.cluster);
     return (int32_t)rc;
 }
 

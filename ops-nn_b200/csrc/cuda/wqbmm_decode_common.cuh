@@ -3,6 +3,9 @@
 #pragma once
 #include <atomic>
 #include <chrono>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 
@@ -41,7 +44,7 @@ struct DecodeArgs {
     int32_t m;
     int64_t n, k;
     int64_t strips, ksteps, splits, steps_per_group;
-    int32_t cluster;       // ring kernels: the k-splits of a strip form a thread-block cluster (CTA index = strip * splits + split)
+    int32_t cluster;       // != 0: the k-splits of a strip form a thread-block cluster (CTA index = strip * splits + split)
     int64_t k_align;       // group-wise kernel only: k ranges start and end on multiples of this many k-steps (even)
     unsigned long long* tags;  // [gridDim]
     float4* partials;          // [gridDim][kWarps][kTiles][32]
@@ -236,7 +239,137 @@ __device__ __forceinline__ void combine_and_store(const DecodeArgs& a, float (&a
             if (do_write) store_tile_y<kBf16, kLayout>(a, acc, strip, warp, lane);
 }
 
+// The same combination for k-splits launched as one thread-block cluster (CTA index = strip * splits + split): every CTA leaves
+// its fp32 fragments in its own shared memory at `frag` ([warp][tile][lane] float4, 32 KB, + one word "fragments valid"), and
+// after a cluster barrier CTA r sums the r-th slice of the strip's 2048 float4 over all CTAs, in CTA order (the same order,
+// hence the same bits, as combine_and_store), and writes those elements of y. No global scratch, no tags, and the summing is
+// spread over the cluster instead of falling on one CTA. `valid` is false for a CTA whose main loop gave up a wait: it still
+// joins both barriers (nobody waits for a CTA that left), and nobody writes that strip.
+template <bool kBf16, int kLayout>
+__device__ __forceinline__ void cluster_combine_and_store(const DecodeArgs& a, float (&acc)[kTiles][4], int64_t strip, int warp, int lane,
+                                                          int tid, uint32_t frag, bool valid)
+{
+    constexpr uint32_t kFragVec = (uint32_t)kWarps * kTiles * 32;  // float4 per CTA
+    const uint32_t mine = frag + (uint32_t)((warp * kTiles) * 32 + lane) * 16u;
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine + t * 512), "f"(acc[t][0]), "f"(acc[t][1]), "f"(acc[t][2]),
+                     "f"(acc[t][3])
+                     : "memory");
+    if (tid == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(frag + kFragVec * 16u), "r"(valid ? 1u : 0u) : "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const uint32_t S = (uint32_t)a.splits;
+    // thread j looks at CTA j's "valid" word: one round trip for all of them
+    uint32_t flag = 1u;
+    if ((uint32_t)tid < S) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(frag + kFragVec * 16u), "r"((uint32_t)tid));
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(flag) : "r"(remote) : "memory");
+    }
+    const uint32_t all_valid = __syncthreads_and(flag != 0u) ? 1u : 0u;
+    // the slice of this CTA: at most two float4 per thread (2048 / S <= 1024 only for S = 2, 3: the loop covers that)
+    const uint32_t per = (kFragVec + S - 1) / S;
+    const uint32_t lo = rank * per, hi = min(kFragVec, lo + per);
+    constexpr int kMaxSplits = 16;
+    bool arrived = false;
+    for (uint32_t i0 = lo; i0 < hi && all_valid != 0u; i0 += (uint32_t)kThreads) {
+        const uint32_t i = i0 + (uint32_t)tid;
+        const bool active = i < hi;
+        float4 v[kMaxSplits];
+        // all loads first (they do not depend on one another), then the sum in CTA order
+#pragma unroll
+        for (uint32_t j = 0; j < (uint32_t)kMaxSplits; ++j) {
+            if (active && j < S) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(frag + i * 16u), "r"(j));
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(v[j].x), "=f"(v[j].y), "=f"(v[j].z), "=f"(v[j].w)
+                             : "r"(remote)
+                             : "memory");
+            } else {
+                v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (uint32_t j = 0; j < (uint32_t)kMaxSplits; ++j) {
+            if (j < S) { s.x += v[j].x; s.y += v[j].y; s.z += v[j].z; s.w += v[j].w; }
+        }
+        if (i0 + (uint32_t)kThreads >= hi) {
+            // the last of this CTA's reads of the other CTAs' shared memory are in registers: tell the cluster before writing y
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            arrived = true;
+        }
+        if (active) {
+            // float4 i is tile t of lane l of warp w: rows g, g + 8, columns as in store_tile_y
+            const int w = (int)(i >> 8), t = (int)((i >> 5) & 7u), l = (int)(i & 31u);
+            const int g = l >> 2, q = l & 3;
+            const int64_t colw = strip * kStripCols + w * kWarpCols;
+            const float f4[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = g + (e >> 1) * 8;
+                const int64_t col = colw + (kLayout == 0   ? 8 * (2 * q + (e & 1)) + t
+                                            : kLayout == 1 ? 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3)
+                                                           : 16 * (t >> 1) + 2 * (2 * q + (e & 1)) + (t & 1));
+                if (row < a.m && col < a.n) {
+                    float f = f4[e];
+                    if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
+                    store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
+                }
+            }
+        }
+    }
+    // nobody leaves (and frees its shared memory) before every CTA has read what it needs
+    if (!arrived) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 }  // namespace
+
+// Largest cluster size S in [2, max_s] for which `clusters` clusters of S CTAs of `kernel` are all resident at once on the
+// current device, 0 when there is none. Answers are cached per (kernel, device, S).
+inline int pick_cluster_size(const void* kernel, int threads, int smem_bytes, int64_t clusters, int max_s)
+{
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, int>, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    for (int s = max_s; s >= 2; --s) {
+        int active = -1;
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            auto it = cache.find(std::make_tuple(kernel, dev, s));
+            if (it != cache.end()) active = it->second;
+        }
+        if (active < 0) {
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)(s * 64), 1, 1);
+            cfg.blockDim = dim3((unsigned)threads, 1, 1);
+            cfg.dynamicSmemBytes = (size_t)smem_bytes;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = (unsigned)s;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+                cudaGetLastError();
+                n = 0;
+            }
+            active = n;
+            std::lock_guard<std::mutex> lock(mu);
+            cache[std::make_tuple(kernel, dev, s)] = active;
+        }
+        if ((int64_t)active >= clusters) return s;
+    }
+    return 0;
+}
 
 // One sequence for the whole library (inline with external linkage: a single counter across translation units).
 inline unsigned long long next_nonce()

@@ -100,6 +100,20 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     return wait_slow(bar, parity, abort_flag, code);
 }
 
+#ifdef OPSNN_DECODE_TIMELINE
+// Diagnostic builds only: per CTA {entry, dependency wait over, first stage landed, main loop over, exit, SM id} in globaltimer ns.
+__device__ unsigned long long g_wq_tma_timeline[148 * 4 * 2 * 6];
+__device__ __forceinline__ unsigned long long gtimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define OPSNN_TL(slot) do { if (tid == 0) g_wq_tma_timeline[blockIdx.x * 6 + (slot)] = gtimer(); } while (0)
+#else
+#define OPSNN_TL(slot) do { } while (0)
+#endif
+
 struct TmaArgs {
     DecodeArgs d;
     int32_t total_stages;      // ceil(k / 64)
@@ -130,10 +144,11 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     // (its CTAs take the SM slots this kernel's early finishers leave), and this kernel reads nothing another kernel may have
     // written before griddepcontrol.wait below has returned. Both are no-ops for an ordinary launch.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    OPSNN_TL(0);
 
     const int64_t c = blockIdx.x;
-    const int64_t strip = c % a.strips;
-    const int64_t chunk = c / a.strips;
+    const int64_t strip = a.cluster ? c / a.splits : c % a.strips;
+    const int64_t chunk = a.cluster ? c % a.splits : c / a.strips;
     // this CTA's k range in stages
     const int st_a = (int)((chunk * ta.total_stages) / a.splits);
     const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
@@ -153,6 +168,7 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     }
     __syncthreads();
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    OPSNN_TL(1);
     volatile uint32_t* abort_flag = &s_abort;
 
     auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
@@ -326,6 +342,7 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     bool ok = nst > 0;
     if (ok) {
         ok = wait_bar(bar0, 0u, abort_flag, 1u);
+        OPSNN_TL(2);
         ldsm4_trans<0>(smem0 + wlane, w0);
         ldsm4(smem0 + xlane, a0);
     }
@@ -386,7 +403,9 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     }
     finish_group();
 
-    if (__syncthreads_or(s_abort != 0u)) {
+    const bool aborted = __syncthreads_or(s_abort != 0u) != 0;
+    OPSNN_TL(3);
+    if (aborted) {
         // A wait gave up. Nothing is written; before the CTA leaves, the copies already issued get a bounded time to land
         // (shared memory must not be handed to another CTA while a bulk copy still targets it).
         if (tid == 0) {
@@ -399,9 +418,19 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
             }
         }
         __syncthreads();
-        return;
+        if (!a.cluster) return;
     }
-    combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
+    // every warp is past its last stage (barrier above): the stage buffers are free to hold the fragments
+    if (a.cluster) cluster_combine_and_store<kBf16, 1>(a, total, strip, warp, lane, tid, smem0, !aborted);
+    else combine_and_store<kBf16, 1>(a, total, c, strip, warp, lane, tid, &s_reduce);
+#ifdef OPSNN_DECODE_TIMELINE
+    if (tid == 0) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_wq_tma_timeline[blockIdx.x * 6 + 4] = gtimer();
+        g_wq_tma_timeline[blockIdx.x * 6 + 5] = smid;
+    }
+#endif
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -434,15 +463,33 @@ bool make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint6
 
 std::atomic<uint64_t> g_tma_configured[8];
 
-template <bool kBf16, bool kExact, bool kAligned>
-cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
+// variant = 4 exact + 2 bf16 + aligned
+const void* tma_kernel(int variant)
 {
-    auto kern = wqbmm_decode_tma_kernel<kBf16, kExact, kAligned>;
-    cudaError_t rc = once_per_device(g_tma_configured[variant], [&] {
+    switch (variant) {
+        case 0: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, false, false>);
+        case 1: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, false, true>);
+        case 2: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<true, false, false>);
+        case 3: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<true, false, true>);
+        case 4: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, true, false>);
+        case 5: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, true, true>);
+        case 6: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<true, true, false>);
+        default: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<true, true, true>);
+    }
+}
+
+cudaError_t configure_variant(int variant)
+{
+    const void* kern = tma_kernel(variant);
+    return once_per_device(g_tma_configured[variant], [&] {
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);  // clusters of up to 16 k-splits
         return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmaSmem);
     });
-    if (rc != cudaSuccess) return rc;
+}
+
+cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
+{
     // launched as a programmatic dependent of whatever precedes it in the stream (OPSNN_WQ_PDL=0: an ordinary launch)
     const char* pe = getenv("OPSNN_WQ_PDL");
     cudaLaunchConfig_t cfg{};
@@ -450,14 +497,27 @@ cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const C
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = kTmaSmem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = (pe == nullptr || pe[0] != '0') ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, mw, mx, ta);
+    cudaLaunchAttribute attr[2]{};
+    unsigned na = 0;
+    if (pe == nullptr || pe[0] != '0') {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (ta.d.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)ta.d.splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    void* args[3] = {const_cast<CUtensorMap*>(&mw), const_cast<CUtensorMap*>(&mx), const_cast<TmaArgs*>(&ta)};
+    return cudaLaunchKernelExC(&cfg, tma_kernel(variant), args);
 }
 
+constexpr int kClusterMaxStrips = 28;  // wider outputs keep the workspace combination (measured equal or better there)
 constexpr int kTmaMaxGrid = 148 * 4 * 2;  // same workspace layout and bound as the other decode kernels
 
 }  // namespace
@@ -513,20 +573,42 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     const bool bf16 = p->x_dtype == ACL_BF16;
     const int variant = (exact ? 4 : 0) + (bf16 ? 2 : 0) + (aligned ? 1 : 0);
 
+    cudaError_t crc = configure_variant(variant);
+    if (crc != cudaSuccess) return (int32_t)crc;
     const int resident = 2 * current_sm_count();
     int64_t splits = resident / a.strips;
-    if (const char* e = getenv("OPSNN_WQ_DECODE_SPLITS")) {
-        int v = atoi(e);
-        if (v > 0) splits = v;
-    }
+    const char* se = getenv("OPSNN_WQ_DECODE_SPLITS");
+    const char* ce = getenv("OPSNN_WQ_DECODE_CLUSTER");
+    if (se != nullptr && atoi(se) > 0) splits = atoi(se);
     if (splits > ta.total_stages) splits = ta.total_stages;
     if (splits * a.strips > kTmaMaxGrid) splits = kTmaMaxGrid / a.strips;
     if (splits < 1) splits = 1;
+    // Narrow outputs (a column shard of a wider problem, a small layer): the k-splits of a strip are launched as one thread-block
+    // cluster and summed over distributed shared memory, every CTA of the cluster a slice of the strip - with many splits per
+    // strip, one CTA summing all fragments out of global memory is a visible part of the launch (3584 columns of k = 8192:
+    // 40.6 us with 42 splits through the workspace, 26.4 us with 16, 14.7 us with a cluster of 16). The split count is the largest
+    // that lets every strip's cluster be resident at once (the occupancy query knows how clusters pack into the device's GPCs).
+    // Wide outputs keep the workspace combination (measured equal or better there). OPSNN_WQ_DECODE_CLUSTER=0 / 1 forbids /
+    // forces the cluster form; OPSNN_WQ_DECODE_SPLITS fixes the split count.
+    a.cluster = 0;
+    if (ce == nullptr || ce[0] != '0') {
+        if (se != nullptr || (ce != nullptr && splits <= 16)) {
+            a.cluster = (splits >= 2 && splits <= 16 && (ce != nullptr || a.strips <= kClusterMaxStrips)) ? 1 : 0;
+        } else if (a.strips <= kClusterMaxStrips && splits >= 2) {
+            // (asking for one CTA per SM on top was measured: equal up to 7 strips, slower beyond)
+            const int s_pick = pick_cluster_size(tma_kernel(variant), kThreads, kTmaSmem, a.strips, (int)(splits < 16 ? splits : 16));
+            if (s_pick >= 2) {
+                splits = s_pick;
+                a.cluster = 1;
+            }
+        }
+    }
+    if (!a.cluster && se == nullptr && splits > 16) splits = 16;  // workspace combination: beyond 16 fragments per strip the summing CTA costs more than the parallelism gives
     a.splits = splits;
     const int64_t grid64 = a.strips * splits;
     if (grid64 > 0x7FFFFFFF) return (int32_t)cudaErrorInvalidConfiguration;
     const uint64_t tag_bytes = (((uint64_t)kTmaMaxGrid * 8 + 255) / 256) * 256;
-    if (splits > 1 && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
+    if (splits > 1 && !a.cluster && (p->workspace == nullptr || p->workspace_size < wqbmm_decode_workspace_size(p))) return (int32_t)cudaErrorInvalidValue;
     a.tags = reinterpret_cast<unsigned long long*>(p->workspace);
     a.partials = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p->workspace) + tag_bytes);
     a.nonce = next_nonce();
@@ -539,23 +621,20 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
         !make_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
 
-    const int grid = (int)grid64;
-    cudaError_t rc;
-    switch (variant) {
-        case 0: rc = launch_variant<false, false, false>(0, grid, mw, mx, ta, stream); break;
-        case 1: rc = launch_variant<false, false, true>(1, grid, mw, mx, ta, stream); break;
-        case 2: rc = launch_variant<true, false, false>(2, grid, mw, mx, ta, stream); break;
-        case 3: rc = launch_variant<true, false, true>(3, grid, mw, mx, ta, stream); break;
-        case 4: rc = launch_variant<false, true, false>(4, grid, mw, mx, ta, stream); break;
-        case 5: rc = launch_variant<false, true, true>(5, grid, mw, mx, ta, stream); break;
-        case 6: rc = launch_variant<true, true, false>(6, grid, mw, mx, ta, stream); break;
-        default: rc = launch_variant<true, true, true>(7, grid, mw, mx, ta, stream); break;
-    }
+    const cudaError_t rc = launch_variant(variant, (int)grid64, mw, mx, ta, stream);
     note_launch(exact ? "wqbmm_decode" : "wqbmm_decode_fast");
+    note_decode_plan(a.strips, a.splits, a.cluster);
     return (int32_t)rc;
 }
 
 }  // namespace opsnn
+
+#ifdef OPSNN_DECODE_TIMELINE
+extern "C" __attribute__((visibility("default"))) int32_t opsnn_wqbmm_decode_timeline(unsigned long long* host_out, int32_t ctas)
+{
+    return (int32_t)cudaMemcpyFromSymbol(host_out, opsnn::g_wq_tma_timeline, (size_t)ctas * 6 * sizeof(unsigned long long));
+}
+#endif
 
 // Error word of the bulk-copy decode kernels on the current device: 0 when every bounded wait inside them completed. Synchronises the
 // device; reset != 0 clears the word after reading it.

@@ -196,11 +196,14 @@ def test_decode_kernel_in_chunks_of_16_rows(aclnn, m, inner_precise):
     assert np.all(np.abs(gv - wv) <= tol * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
 
 
-def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, monkeypatch):
+@pytest.mark.parametrize("cluster", ["0", "1"], ids=["workspace combine", "cluster combine"])
+def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, monkeypatch, cluster):
     """Every wait in the bulk-copy decode kernel is bounded. Here the producer is told (test-only switch) to stop issuing copies
     after the eighth stage of each CTA's range, with a poll limit of a few thousand, so the consumers' wait for the ninth stage
     runs out while nothing is in flight: the kernel must come back by itself, leave its error word at 1 (a stage never
-    arrived), and the next, ordinary call must work. Nothing faults, traps or hangs: the wait simply gives up."""
+    arrived), and the next, ordinary call must work. Nothing faults, traps or hangs: the wait simply gives up. Both ways of
+    combining the k-splits are covered: with the splits launched as a cluster, the CTAs that gave up still join the cluster's
+    barriers and mark their fragments invalid, so nobody waits for them and nobody writes."""
     import torch
 
     from gpu_util import DEV, out_to_np
@@ -225,6 +228,7 @@ def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, 
         return y
 
     monkeypatch.setenv("OPSNN_WQ_DECODE_SPLITS", "2")           # 64 stages per CTA
+    monkeypatch.setenv("OPSNN_WQ_DECODE_CLUSTER", cluster)
     monkeypatch.setenv("OPSNN_TEST_DECODE_STALL_STAGE", "8")
     monkeypatch.setenv("OPSNN_TEST_DECODE_POLL_LIMIT", "3000")
     y_bad = run()
@@ -239,6 +243,95 @@ def test_decode_wait_that_runs_out_is_reported_and_the_next_call_is_fine(aclnn, 
     got = out_to_np(y).astype(np.float64)
     rms = np.sqrt(np.mean(want ** 2))
     assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
+
+
+COMBINE_CASES = [
+    # weight bits, x dtype, m, k, n, group, bias, inner_precise, k-splits
+    (4, "bfloat16", 16, 8192, 3584, 128, False, None, 16),   # a 1/8 column shard of the benchmark's decode shape
+    (4, "bfloat16", 16, 8192, 3584, 128, False, 1, 16),
+    (4, "float16", 7, 4096, 1296, 128, True, None, 5),       # ragged last strip, m < 16, bias, a split count that does not divide the fragments
+    (4, "bfloat16", 16, 2048, 512, 64, False, None, 3),
+    (8, "bfloat16", 16, 8192, 2048, 0, True, None, 16),
+    (8, "float16", 3, 4096, 1040, 128, False, None, 7),
+]
+
+
+@pytest.mark.parametrize("case", COMBINE_CASES, ids=[str(c) for c in COMBINE_CASES])
+def test_cluster_combine_equals_workspace_combine(aclnn, monkeypatch, case):
+    """The k-splits of a strip are summed either by the last CTA to arrive, from fragments in the workspace, or - launched as one
+    thread-block cluster - over distributed shared memory, each CTA a slice of the strip. Both add the fragments in CTA order,
+    so for the same split count the outputs must be identical bit for bit; the oracle bounds them as in the other tests."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    bits, xdt, m, k, n, g, with_bias, ip, splits = case
+    rng = np.random.default_rng(m * 131 + n)
+    nd = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
+    td = torch.bfloat16 if xdt == "bfloat16" else torch.float16
+    dev16 = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16).copy()).view(td).to(DEV)  # noqa: E731
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(nd)
+    groups = k // g if g else 1
+    sc = rng.uniform(0.005, 0.02, (groups, n)).astype(np.float32).astype(nd)
+    of = rng.uniform(-1, 1, (groups, n)).astype(np.float32).astype(nd)
+    bias = rng.standard_normal(n).astype(np.float32).astype(nd) if with_bias else None
+    if bits == 4:
+        w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+        tw = torch.from_numpy(wqbmm_oracle.pack_int4_words(w).copy()).to(DEV)
+    else:
+        w = rng.integers(-128, 128, (k, n)).astype(np.int8)
+        tw = torch.from_numpy(w.copy()).to(DEV)
+    tx, ts, to = dev16(x), dev16(sc if g else sc[0]), dev16(of if g else of[0])
+    tb = dev16(bias) if with_bias else None
+    monkeypatch.setenv("OPSNN_WQ_DECODE_SPLITS", str(splits))
+    outs = []
+    for cluster in ("0", "1"):
+        monkeypatch.setenv("OPSNN_WQ_DECODE_CLUSTER", cluster)
+        y = torch.full((m, n), -7777.0, dtype=td, device=DEV)
+        aclnn.weight_quant_batch_matmul(aclnn.from_torch(tx), aclnn.from_torch(tw), aclnn.from_torch(ts), aclnn.from_torch(y),
+                                        aclnn.from_torch(to), aclnn.from_torch(tb) if tb is not None else None, g, inner_precise=ip)
+        torch.cuda.synchronize()
+        assert aclnn.last_kernel_name() in ("wqbmm_decode", "wqbmm_decode_fast", "wqbmm_decode8")
+        outs.append(y.view(torch.int16).cpu().numpy().copy())
+        last = y
+    assert aclnn.lib().opsnn_wqbmm_decode_status(1) == 0
+    assert np.array_equal(outs[0], outs[1])
+    if ip:  # the high-performance mode is measured against the unrounded product, as the API documents it
+        want = np.asarray(wqbmm_oracle.fp32_dequant_product(x, w, sc, of, bias, g), dtype=np.float64)
+        tol = 2.0 ** -8 * 1.05
+    else:
+        want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, bias, g).astype(np.float64)
+        tol = 2.0 ** -7 if xdt == "bfloat16" else 2.0 ** -9
+    got = out_to_np(last).astype(np.float64)
+    rms = np.sqrt(np.mean(want ** 2))
+    assert np.all(np.abs(got - want) <= tol * np.maximum(np.abs(want), 0.05 * rms) * 1.01)
+
+
+def test_narrow_output_is_planned_as_clusters(aclnn):
+    """A 1/8 column shard of the benchmark's decode shape (what one of eight GPUs gets): the k-ranges of a strip run as one
+    thread-block cluster of as many CTAs as the device keeps resident for all seven strips at once, and the full width keeps
+    the workspace combination."""
+    import torch
+
+    from gpu_util import DEV
+
+    def plan(n):
+        m, k, g = 16, 8192, 128
+        gen = torch.Generator(device=DEV).manual_seed(n)
+        x = torch.randn((m, k), generator=gen, device=DEV).to(torch.bfloat16)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (k, n // 8), generator=gen, device=DEV, dtype=torch.int32)
+        sc = (torch.rand((k // g, n), generator=gen, device=DEV) * 0.01 + 0.005).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+        aclnn.weight_quant_batch_matmul(aclnn.from_torch(x), aclnn.from_torch(w), aclnn.from_torch(sc), aclnn.from_torch(y), None, None, g)
+        torch.cuda.synchronize()
+        assert aclnn.last_kernel_name() == "wqbmm_decode"
+        return aclnn.last_decode_plan()
+
+    strips, splits, cluster = plan(3584)
+    assert strips == 7 and (cluster & 1) == 1 and 2 <= splits <= 16
+    strips, splits, cluster = plan(28672)
+    assert strips == 56 and cluster == 0 and splits == 5
 
 
 W8_CASES = [
