@@ -81,6 +81,26 @@ __global__ void interleave_columns_kernel(const T* __restrict__ recv, T* __restr
     }
 }
 
+// The same move in 16-byte pieces, one rank's run per blockIdx.y: in a row, rank r's columns are contiguous both in its receive
+// block and in the full row. Needs every run to start and end on a 16-byte boundary in both places (checked on the host).
+constexpr int kMaxRunRanks = 64;
+struct ColumnRuns {
+    int64_t begin_b[kMaxRunRanks];  // byte offset of the rank's first column in a full row
+    int64_t width_b[kMaxRunRanks];  // bytes of a row the rank owns
+};
+
+__global__ void interleave_runs_kernel(const uint8_t* __restrict__ recv, uint8_t* __restrict__ full, int64_t m, int64_t full_row_b,
+                                       int64_t block_row_b, const __grid_constant__ ColumnRuns runs)
+{
+    const int r = blockIdx.y;
+    const int64_t pieces = runs.width_b[r] / 16, begin = runs.begin_b[r];
+    const uint8_t* src = recv + (int64_t)r * m * block_row_b;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < m * pieces; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / pieces, p = i - row * pieces;
+        *reinterpret_cast<uint4*>(full + row * full_row_b + begin + p * 16) = *reinterpret_cast<const uint4*>(src + row * block_row_b + p * 16);
+    }
+}
+
 }  // namespace
 }  // namespace opsnn
 
@@ -183,17 +203,40 @@ int32_t opsnn_gather_columns(void* comm, const void* y_local, int64_t y_local_ld
     }
     uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255);
     const size_t block = (size_t)m * (size_t)wmax * (size_t)elem_bytes;
-    uint8_t* send = ws;
+    const uint8_t* send = ws;
     uint8_t* recv = ws + block;
-    // this rank's (m, width) shard into the head of a (m, wmax) block: one strided copy on the stream
-    cudaError_t rc = cudaMemcpy2DAsync(send, (size_t)wmax * elem_bytes, y_local, (size_t)y_local_ld * elem_bytes, (size_t)(mine_e - mine_b) * elem_bytes,
-                                       (size_t)m, cudaMemcpyDeviceToDevice, s);
-    if (rc != cudaSuccess) return (int32_t)rc;
+    if (mine_e - mine_b == wmax && y_local_ld == wmax) {
+        send = static_cast<const uint8_t*>(y_local);  // the shard already is a dense (m, wmax) block: sent from where it lies
+    } else {
+        // this rank's (m, width) shard into the head of a (m, wmax) block: one strided copy on the stream
+        cudaError_t rc = cudaMemcpy2DAsync(ws, (size_t)wmax * elem_bytes, y_local, (size_t)y_local_ld * elem_bytes,
+                                           (size_t)(mine_e - mine_b) * elem_bytes, (size_t)m, cudaMemcpyDeviceToDevice, s);
+        if (rc != cudaSuccess) return (int32_t)rc;
+    }
     const int nrc = nccl().AllGather(send, recv, block, 0 /* ncclInt8: the payload is moved as bytes */, c->nccl, s);
     if (nrc != 0) return nccl_fail("ncclAllGather", nrc);
     const int64_t units = n_total / multiple;
     const int64_t total = m * n_total;
     const int threads = 256;
+    // 16-byte pieces when every rank's run starts and ends on a 16-byte boundary of the full row and of its receive block
+    ColumnRuns runs{};
+    bool vec = c->world <= kMaxRunRanks && (reinterpret_cast<uintptr_t>(y_full) % 16) == 0 && ((size_t)n_total * elem_bytes) % 16 == 0 &&
+               ((size_t)wmax * elem_bytes) % 16 == 0;
+    for (int32_t r = 0; vec && r < c->world; ++r) {
+        int64_t b, e;
+        opsnn_shard_range(n_total, c->world, r, multiple, &b, &e);
+        runs.begin_b[r] = b * elem_bytes;
+        runs.width_b[r] = (e - b) * elem_bytes;
+        vec = runs.begin_b[r] % 16 == 0 && runs.width_b[r] % 16 == 0;
+    }
+    if (vec) {
+        const int64_t per_rank = m * ((int64_t)wmax * elem_bytes / 16);
+        const int bx = (int)((per_rank + threads - 1) / threads < 296 ? (per_rank + threads - 1) / threads : 296);
+        interleave_runs_kernel<<<dim3((unsigned)(bx < 1 ? 1 : bx), (unsigned)c->world, 1), threads, 0, s>>>(
+            recv, static_cast<uint8_t*>(y_full), m, n_total * elem_bytes, wmax * elem_bytes, runs);
+        note_launch("gather_interleave");
+        return (int32_t)cudaGetLastError();
+    }
     const int blocks = (int)((total + threads - 1) / threads < 1184 ? (total + threads - 1) / threads : 1184);
     if (elem_bytes == 2)
         interleave_columns_kernel<uint16_t><<<blocks, threads, 0, s>>>(reinterpret_cast<const uint16_t*>(recv), static_cast<uint16_t*>(y_full), m, n_total,

@@ -23,6 +23,10 @@ def test_single_rank_gather_columns_and_batch(aclnn):
         full = comm.gather_columns(view, 512, 8)
         torch.cuda.synchronize()
         assert torch.equal(full, view.contiguous())
+        dense = view.contiguous()  # a dense shard is sent from where it lies
+        assert torch.equal(comm.gather_columns(dense, 512, 8), dense)
+        odd = y[:, :500].contiguous()  # 1000-byte rows: the element-wise interleave instead of 16-byte pieces
+        assert torch.equal(comm.gather_columns(odd, 500, 4), odd)
         b = torch.randn((4, 8, 32), device=dev)
         out = comm.gather_batch(b, 4)
         torch.cuda.synchronize()
@@ -54,15 +58,20 @@ def _rank_main(rank, world, port, ret):
         pkg = load_package()
         aclnn = pkg.aclnn
         comm = aclnn.Comm(world, rank, dev)
-        m, n = 16, 1544  # 193 units of 8 columns: uneven shares (97 / 96 units)
-        full = (torch.arange(m * n, dtype=torch.float32).reshape(m, n) % 251).to(torch.bfloat16)
-        b, e = aclnn.shard_range(n, world, rank, 8)
-        got = comm.gather_columns(full[:, b:e].to(dev), n, 8)
+        ok_cols = True
+        # 193 units of 8 columns: uneven shares (97 / 96 units), runs of whole 16-byte pieces; 385 units of 4 columns: shares of
+        # 1544 and 1536 bytes per row, moved element by element
+        for m, n, mult in ((16, 1544, 8), (16, 1540, 4)):
+            full = (torch.arange(m * n, dtype=torch.float32).reshape(m, n) % 251).to(torch.bfloat16)
+            b, e = aclnn.shard_range(n, world, rank, mult)
+            got = comm.gather_columns(full[:, b:e].to(dev), n, mult)
+            torch.cuda.synchronize()
+            ok_cols = ok_cols and bool(torch.equal(got.cpu(), full))
         bat = torch.arange(4 * 6 * 10, dtype=torch.float32).reshape(4, 6, 10)
         bb, be = aclnn.shard_range(4, world, rank, 1)
         gotb = comm.gather_batch(bat[bb:be].to(dev), 4)
         torch.cuda.synchronize()
-        ret[rank] = (bool(torch.equal(got.cpu(), full)), bool(torch.equal(gotb.cpu(), bat)))
+        ret[rank] = (ok_cols, bool(torch.equal(gotb.cpu(), bat)))
         comm.close()
     finally:
         dist.destroy_process_group()
