@@ -706,7 +706,7 @@ def run_ceilings(aclnn, sm_mhz=1965.0, sms=148):
     import ctypes
 
     L = aclnn.lib()
-    out = {"sm_mhz_assumed": sm_mhz, "sms": sms, "umma": {}, "decode_mix": {}}
+    out = {"sm_mhz_assumed": sm_mhz, "sms": sms, "umma": {}, "decode_mix": {}, "tmem_read": {}}
     for name, kind, bn, kelems in (("i8", 0, 256, 32), ("f8f6f4", 1, 256, 32), ("mxf8f6f4", 2, 224, 32), ("mxf4", 3, 224, 64),
                                    ("mxf8f6f4_bn256", 2, 256, 32), ("mxf4_bn256", 3, 256, 64)):
         clk = ctypes.c_double(0.0)
@@ -721,6 +721,11 @@ def run_ceilings(aclnn, sm_mhz=1965.0, sms=148):
         clk = ctypes.c_double(0.0)
         rc = L.opsnn_probe_mix(mix, ctypes.byref(clk))
         out["decode_mix"][name] = {"error": rc} if rc != 0 else {"clocks_per_kstep_per_scheduler": clk.value}
+    # tensor memory -> registers with nothing else running (what the per-block promotion reads once per 128-deep k-block)
+    for name, form, warps in (("32x32b_x16_4warps", 0, 4), ("32x32b_x16_8warps", 0, 8), ("32x32b_x64_8warps", 2, 8), ("16x256b_x8_8warps", 4, 8)):
+        v = ctypes.c_double(0.0)
+        rc = L.opsnn_probe_tmem_read(form, warps, ctypes.byref(v))
+        out["tmem_read"][name] = {"error": rc} if rc != 0 else {"bytes_per_clk_per_sm": v.value}
     # one k-step = 1024 int4 weights = 512 bytes per warp; 4 schedulers per SM
     for name in ("default_arithmetic", "group_wise_arithmetic"):
         e = out["decode_mix"].get(name, {})

@@ -241,9 +241,12 @@ OPSNN_API void opsnn_wqbmm_decode_last_plan(int32_t* strips, int32_t* splits, in
  * resident in shared memory; kind 0 i8, 1 f8f6f4, 2 mxf8f6f4, 3 mxf4; bn 128, 224 or 256. opsnn_probe_mix: clocks per k-step per
  * scheduler of the decode kernels' instruction mixes (0 integer only, 1 16-bit-pair arithmetic only, 2 mma.sync only, 3 default
  * arithmetic, 4 group-wise arithmetic). Both synchronise the device and use a few KB of their own device memory for the duration of
- * the call. No counterpart in the reference. */
+ * the call. opsnn_probe_tmem_read: bytes per clock a whole SM moves from tensor memory to registers with tcgen05.ld (form 0:
+ * 32x32b.x16, 1: .x32, 2: .x64, each waited for; 3: two .x16 per wait; 4: 16x256b.x8, two per wait; 5: four 32x32b.x32 per wait;
+ * warps 4 or 8) - the rate that bounds the per-block promotion. No counterpart in the reference. */
 OPSNN_API int32_t opsnn_probe_umma(int32_t kind, int32_t bn, double* clocks_per_mma);
 OPSNN_API int32_t opsnn_probe_mix(int32_t mix, double* clocks_per_kstep);
+OPSNN_API int32_t opsnn_probe_tmem_read(int32_t form, int32_t warps, double* bytes_per_clock);
 
 #ifdef __cplusplus
 }

@@ -111,7 +111,8 @@ def lib():
         getattr(L, name).restype = c_int32
     L.opsnn_probe_umma.argtypes = [c_int32, c_int32, POINTER(ctypes.c_double)]
     L.opsnn_probe_mix.argtypes = [c_int32, POINTER(ctypes.c_double)]
-    L.opsnn_probe_umma.restype = L.opsnn_probe_mix.restype = c_int32
+    L.opsnn_probe_tmem_read.argtypes = [c_int32, c_int32, POINTER(ctypes.c_double)]
+    L.opsnn_probe_umma.restype = L.opsnn_probe_mix.restype = L.opsnn_probe_tmem_read.restype = c_int32
     I64, I32, U64, VP = c_int64, c_int32, c_uint64, c_void_p
     L.opsnn_shard_range.restype = None
     L.opsnn_shard_range.argtypes = [I64, I32, I32, I64, POINTER(I64), POINTER(I64)]

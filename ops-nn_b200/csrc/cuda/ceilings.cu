@@ -116,6 +116,113 @@ long long max_of(const long long* dev, int n)
     return m;
 }
 
+
+// TMEM -> register read rate. `warps` warps (4 or 8; warp w reads lane quarter w % 4, column half w / 4 when there are 8) each read
+// 128 columns of their 32 lanes per iteration, 2000 times, in one of these forms:
+//   0: 32x32b.x16, wait after every load        1: 32x32b.x32, wait after every load      2: 32x32b.x64, wait after every load
+//   3: two 32x32b.x16 in flight per wait        4: 16x256b.x8 (16 lanes x 64 columns), two per wait (both lane halves)
+//   5: four 32x32b.x32 in flight per wait (all 128 columns)
+// Contents of TMEM are whatever the allocation holds; the values only feed an xor that keeps the loads alive.
+template <int FORM>
+__global__ void __launch_bounds__(256) tmem_read_kernel(int iters, long long* out, uint32_t* sink)
+{
+    __shared__ uint32_t tmem_ptr;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    if (warp == 0) ptx::tmem_alloc(&tmem_ptr, 512);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t base = tmem_ptr + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * 128);
+    uint32_t x = 0;
+    __syncthreads();
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+        const uint32_t b = base + (uint32_t)((it & 1) * 256);
+        if (FORM == 0) {
+#pragma unroll
+            for (int c = 0; c < 128; c += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld16(b + c, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x ^= v[i];
+            }
+        } else if (FORM == 1 || FORM == 5) {
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                ptx::tmem_ld32(b + c * 32, v[c]);
+                if (FORM == 1) ptx::tmem_ld_wait();
+            }
+            if (FORM == 5) ptx::tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x ^= v[c][i];
+        } else if (FORM == 2) {
+#pragma unroll
+            for (int c = 0; c < 128; c += 64) {
+                uint32_t v[64];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, "
+                    "%27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, "
+                    "%52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                      "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                      "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                      "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]),
+                      "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]),
+                      "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]),
+                      "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+                    : "r"(b + c)
+                    : "memory");
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 64; ++i) x ^= v[i];
+            }
+        } else if (FORM == 3) {
+#pragma unroll
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t v[16], w[16];
+                ptx::tmem_ld16(b + c, v);
+                ptx::tmem_ld16(b + c + 16, w);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x ^= v[i] ^ w[i];
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 128; c += 64) {
+                uint32_t v[2][32];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, "
+                        "%26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[h][0]), "=r"(v[h][1]), "=r"(v[h][2]), "=r"(v[h][3]), "=r"(v[h][4]), "=r"(v[h][5]), "=r"(v[h][6]), "=r"(v[h][7]),
+                          "=r"(v[h][8]), "=r"(v[h][9]), "=r"(v[h][10]), "=r"(v[h][11]), "=r"(v[h][12]), "=r"(v[h][13]), "=r"(v[h][14]),
+                          "=r"(v[h][15]), "=r"(v[h][16]), "=r"(v[h][17]), "=r"(v[h][18]), "=r"(v[h][19]), "=r"(v[h][20]), "=r"(v[h][21]),
+                          "=r"(v[h][22]), "=r"(v[h][23]), "=r"(v[h][24]), "=r"(v[h][25]), "=r"(v[h][26]), "=r"(v[h][27]), "=r"(v[h][28]),
+                          "=r"(v[h][29]), "=r"(v[h][30]), "=r"(v[h][31])
+                        : "r"(b + c + ((uint32_t)(h * 16) << 16))
+                        : "memory");
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x ^= v[0][i] ^ v[1][i];
+            }
+        }
+    }
+    const long long t1 = clock64();
+    if (lane == 0) atomicMax(reinterpret_cast<unsigned long long*>(out + blockIdx.x), (unsigned long long)(t1 - t0));
+    if (x == 0x12345678u) sink[0] = x;
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) ptx::tmem_dealloc(tmem_ptr, 512);
+    (void)nwarps;
+}
+
 template <int KIND>
 cudaError_t run_umma(int iters, uint32_t bn, int grid, long long* out, unsigned int* status)
 {
@@ -187,6 +294,34 @@ extern "C" __attribute__((visibility("default"))) int32_t opsnn_probe_mix(int32_
     }
     if (rc == cudaSuccess) *clocks_per_kstep = (double)max_of(cyc, grid) / iters / 4.0;  // 16 warps per SM = 4 per scheduler
     cudaFree(cyc);
+    cudaFree(sink);
+    return (int32_t)rc;
+}
+
+// form: see tmem_read_kernel; warps 4 or 8. One CTA per SM, all SMs at once. Writes the bytes a whole SM reads from TMEM per clock.
+extern "C" __attribute__((visibility("default"))) int32_t opsnn_probe_tmem_read(int32_t form, int32_t warps, double* bytes_per_clock)
+{
+    if (bytes_per_clock == nullptr || form < 0 || form > 5 || (warps != 4 && warps != 8)) return (int32_t)cudaErrorInvalidValue;
+    const int grid = current_sm_count() < 1024 ? current_sm_count() : 1024, iters = 2000;
+    long long* out = nullptr;
+    uint32_t* sink = nullptr;
+    cudaError_t rc = cudaMalloc(&out, 1024 * sizeof(long long));
+    if (rc == cudaSuccess) rc = cudaMalloc(&sink, 64);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    for (int rep = 0; rep < 2 && rc == cudaSuccess; ++rep) {
+        cudaMemset(out, 0, 1024 * sizeof(long long));
+        switch (form) {
+            case 0: tmem_read_kernel<0><<<grid, warps * 32>>>(iters, out, sink); break;
+            case 1: tmem_read_kernel<1><<<grid, warps * 32>>>(iters, out, sink); break;
+            case 2: tmem_read_kernel<2><<<grid, warps * 32>>>(iters, out, sink); break;
+            case 3: tmem_read_kernel<3><<<grid, warps * 32>>>(iters, out, sink); break;
+            case 4: tmem_read_kernel<4><<<grid, warps * 32>>>(iters, out, sink); break;
+            default: tmem_read_kernel<5><<<grid, warps * 32>>>(iters, out, sink); break;
+        }
+        rc = cudaDeviceSynchronize();
+    }
+    if (rc == cudaSuccess) *bytes_per_clock = (double)warps * 32.0 * 128.0 * 4.0 * iters / (double)max_of(out, grid);
+    cudaFree(out);
     cudaFree(sink);
     return (int32_t)rc;
 }

@@ -891,7 +891,8 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     const uint8_t* b_ptr = static_cast<const uint8_t*>(p->b);
     int64_t b_ld = p->b_ld, b_bs = p->b_bs;
     int b_trans = p->trans_b;
-    const int bn = pair ? 256 : (pair_pb ? 128 : pick_bn(p));
+    const int pb_bn = pair_pb ? pair_pb_bn(p) : 0;
+    const int bn = pair ? 256 : (pair_pb ? pb_bn : pick_bn(p));
     const int bm = (pair || pair_pb) ? 256 : BM;
     UmmaArgs a{};
     a.mode = p->mode;
@@ -943,13 +944,16 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     bool ok;
     if (a.a_mn_major) ok = make_map(&ma, p->a, (uint64_t)p->m, (uint64_t)p->k, nb_a, (uint64_t)p->a_ld, (uint64_t)p->a_bs, 128);
     else ok = make_map(&ma, p->a, (uint64_t)p->k * es, (uint64_t)p->m, nb_a, (uint64_t)p->a_ld * es, (uint64_t)p->a_bs * es, 128);
-    if (a.b_mn_major && pair_pb) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128, 64);
+    if (a.b_mn_major && pair_pb && pb_bn == 128) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128, 64);
     else if (a.b_mn_major) ok = ok && make_map(&mb, b_ptr, (uint64_t)p->n, (uint64_t)p->k, nb_b, (uint64_t)b_ld, (uint64_t)b_bs, 128,
                                                bn < 128 ? (uint32_t)bn : 128u);
     else ok = ok && make_map(&mb, b_ptr, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)b_ld * es, (uint64_t)b_bs * es,
-                             pair ? 128u : (pair_pb ? 64u : (uint32_t)bn));
+                             pair ? 128u : (pair_pb ? (uint32_t)(pb_bn / 2) : (uint32_t)bn));
     if (!ok) return (int32_t)cudaErrorInvalidValue;
     if (pair_pb) {
+        if (pb_bn == 256)
+            return a.is_int ? launch_pair_pb<ptx::MmaKind::kI8, 8, 256>(ma, mb, a, stream)
+                            : launch_pair_pb<ptx::MmaKind::kF8F6F4, 8, 256>(ma, mb, a, stream);
         if (a.is_int) return launch_pair_pb<ptx::MmaKind::kI8, 8>(ma, mb, a, stream);
         return launch_pair_pb<ptx::MmaKind::kF8F6F4, 4>(ma, mb, a, stream);
     }
@@ -979,3 +983,10 @@ extern "C" __attribute__((visibility("default"))) uint32_t opsnn_qmm_umma_status
     }
     return v;
 }
+
+#ifdef OPSNN_PB_DIAG
+extern "C" __attribute__((visibility("default"))) int32_t opsnn_pb_diag(unsigned long long* host_out, int32_t ctas)
+{
+    return (int32_t)cudaMemcpyFromSymbol(host_out, opsnn::g_pb_diag, (size_t)ctas * 5 * sizeof(unsigned long long));
+}
+#endif

@@ -18,13 +18,47 @@
 // All waits bounded, teardown through a cluster barrier, as in qmm_umma_pair.cuh.
 namespace {
 
-template <ptx::MmaKind kKind, int EW>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((EW + 2) * 32, 1)
+// 256-column tiles: 128 sums per epilogue thread need more registers than an even split of the register file over the CTA's
+// warps gives (168 with ten warps), so the block is three whole warpgroups - epilogue warps 0..7, then {producer, MMA issuer, two
+// idle warps} - and setmaxnreg moves registers from the third group (40 each) to the first two (232 each): per scheduler
+// 2 x 232 + 40 = 504 of the 512 registers per lane.
+#ifdef OPSNN_PB_DIAG
+// Diagnostic builds only: clocks the MMA issuer spent waiting for a free accumulator buffer / for operands, and its total; clocks
+// epilogue warp 0 spent waiting for a full buffer, and its total. [CTA][5]
+__device__ unsigned long long g_pb_diag[1024 * 5];
+#define OPSNN_PB_T(var) const long long var = clock64()
+#define OPSNN_PB_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define OPSNN_PB_T(var) do { } while (0)
+#define OPSNN_PB_ADD(acc, t0) do { } while (0)
+#endif
+
+// (Code that runs under setmaxnreg cannot call an out-of-line function: the bounded spin is inlined for those instances.)
+template <bool kInline>
+__device__ __forceinline__ bool pb_wait(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    if (!kInline) return ptx::mbar_wait_a(bar_addr, parity, abort_flag);
+    if (ptx::mbar_try_wait_a(bar_addr, parity)) return true;
+    const uint32_t limit = ptx::g_spin_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (ptx::mbar_try_wait_a(bar_addr, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag != 0u) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+
+template <int EW, int BN>
+constexpr int pair_pb_threads() { return (EW + (BN == 256 ? 4 : 2)) * 32; }
+
+template <ptx::MmaKind kKind, int EW, int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_pb_threads<EW, BN>(), 1)
 qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
 {
-    constexpr int BN = 128, NBUF = 4;
+    static_assert(BN == 128 || (BN == 256 && EW == 8), "256-column tiles keep 128 sums per thread: eight epilogue warps");
+    constexpr int NBUF = 512 / BN;              // accumulator buffers in the 512 TMEM columns
     constexpr int kCols = BN * 4 / EW;          // accumulator columns per epilogue thread
-    constexpr uint32_t kBHalf = 64 * BK;        // this CTA's 64 rows of the k-major B tile
+    constexpr uint32_t kBHalf = (BN / 2) * BK;  // this CTA's half of the B tile
     constexpr uint32_t kStage = kATile + kBHalf;
     constexpr uint32_t kTmemCols = 512;
 
@@ -72,6 +106,7 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (warp == EW) {
         // ======================= TMA producer (both CTAs) =======================
+        if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (lane == 0) {
             ptx::tma_prefetch_desc(&map_a);
             ptx::tma_prefetch_desc(&map_b);
@@ -86,11 +121,11 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t tm, tn;
             tile_of<8>(r, (uint32_t)a.tiles_m, (uint32_t)a.tiles_n, tm, tn);
             const int32_t m0 = (int32_t)tm * 256 + (int32_t)rank * 128;
-            const int32_t n0 = (int32_t)tn * BN + (int32_t)rank * 64;
+            const int32_t n0 = (int32_t)tn * BN + (int32_t)rank * (BN / 2);
             const int32_t ba = a.a_batched ? (int32_t)b : 0, bb = a.b_batched ? (int32_t)b : 0;
             int32_t kk = 0;
             for (int kb = 0; kb < kblocks; ++kb) {
-                if (!ptx::mbar_wait_a(empty0 + 8u * s, par ^ 1u, abort_flag)) {
+                if (!pb_wait<BN == 256>(empty0 + 8u * s, par ^ 1u, abort_flag)) {
                     report(abort_flag, (1u << 8) | 1u);
                     ok = false;
                     break;
@@ -99,7 +134,7 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     const uint32_t fb = lead_full0 + 8u * s, sa = smem0 + s * kStage, sb = sa + (uint32_t)kATile;
                     if (leader) ptx::mbar_expect_tx_a(full0 + 8u * s, 2u * kStage);
                     ptx::tma_load_3d_pair(sa, &map_a, fb, a_mn ? m0 : kk, a_mn ? kk : m0, ba);
-                    if (b_mn) ptx::tma_load_3d_pair(sb, &map_b, fb, n0, kk, bb);  // 64 columns x 128 k rows, 64-byte swizzle
+                    if (b_mn) ptx::tma_load_3d_pair(sb, &map_b, fb, n0, kk, bb);  // BN / 2 columns x 128 k rows (64 columns: 64-byte swizzle)
                     else ptx::tma_load_3d_pair(sb, &map_b, fb, kk, n0, bb);
                 }
                 __syncwarp();
@@ -112,30 +147,39 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
     } else if (warp == EW + 1) {
         // ======================= MMA issuer (even CTA only): every k-block is its own accumulation group =======================
+        if (BN == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (leader) {
             uint32_t s = 0, par = 0, buf = 0, bpar = 0;
             bool ok = true;
             const uint64_t da0 = a.a_mn_major ? ptx::make_smem_desc(smem0, 128 * BK, 1024, 2) : ptx::make_smem_desc(smem0, 0, 1024, 2);
             // B k-major: 64 rows of 128 swizzled bytes. B n-major (x2 stored (k,n)): 128 k rows of this CTA's 64 columns in the
             // 64-byte swizzle (layout type 4): 8 rows = 512 bytes (stride byte offset), one MMA = 32 rows = 2 KB
-            const uint64_t db0 = a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 64 * BK, 512, 4)
-                                              : ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2);
+            // 128 columns (BN = 256) are whole 128-byte swizzle rows, described like an m-major A
+            const uint64_t db0 = !a.b_mn_major ? ptx::make_smem_desc(smem0 + kATile, 0, 1024, 2)
+                                 : (BN == 128 ? ptx::make_smem_desc(smem0 + kATile, 64 * BK, 512, 4)
+                                              : ptx::make_smem_desc(smem0 + kATile, 128 * BK, 1024, 2));
             const uint32_t a_lo = (uint32_t)da0, b_lo = (uint32_t)db0;
             const uint64_t a_hi = da0 & 0xFFFFFFFF00000000ull, b_hi = db0 & 0xFFFFFFFF00000000ull;
-            const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? 128u : 2u;
+            const uint32_t a_k1 = a.a_mn_major ? 256u : 2u, b_k1 = a.b_mn_major ? (BN == 128 ? 128u : 256u) : 2u;
             const uint32_t idesc = a.idesc;
+            long long d_tempty = 0, d_full = 0;
+            OPSNN_PB_T(d_start);
             for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!ptx::mbar_wait_a(tempty0 + 8u * buf, bpar ^ 1u, abort_flag)) {
+                    OPSNN_PB_T(d_t0);
+                    if (!pb_wait<BN == 256>(tempty0 + 8u * buf, bpar ^ 1u, abort_flag)) {
                         report(abort_flag, (2u << 8) | 1u);
                         ok = false;
                         break;
                     }
-                    if (!ptx::mbar_wait_a(full0 + 8u * s, par, abort_flag)) {
+                    OPSNN_PB_ADD(d_tempty, d_t0);
+                    OPSNN_PB_T(d_t1);
+                    if (!pb_wait<BN == 256>(full0 + 8u * s, par, abort_flag)) {
                         report(abort_flag, (2u << 8) | 2u);
                         ok = false;
                         break;
                     }
+                    OPSNN_PB_ADD(d_full, d_t1);
                     ptx::tc_fence_after();
                     if (ptx::elect_one()) {
                         const uint32_t stage_off = (s * kStage) >> 4;
@@ -158,14 +202,26 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                 }
             }
+#ifdef OPSNN_PB_DIAG
+            if (lane == 0) {
+                g_pb_diag[blockIdx.x * 5 + 0] = (unsigned long long)d_tempty;
+                g_pb_diag[blockIdx.x * 5 + 1] = (unsigned long long)d_full;
+                g_pb_diag[blockIdx.x * 5 + 2] = (unsigned long long)(clock64() - d_start);
+            }
+#endif
+            (void)d_tempty;
+            (void)d_full;
         }
-    } else {
+    } else if (warp < EW) {
         // ======================= epilogue warps (both CTAs): own 128 rows, kCols columns each =======================
+        if (BN == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         const int quad = warp & 3, part = warp >> 2;
         const uint32_t lane_addr = ((uint32_t)(quad * 32) << 16) + (uint32_t)(part * kCols);
         const uint32_t lead_tempty0 = tempty0 & ptx::kPeerBitMask;
         uint32_t buf = 0, bpar = 0;
         bool ok = true;
+        long long d_tfull = 0;
+        OPSNN_PB_T(d_estart);
         for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
             const uint32_t b = tile / tiles_per_batch, r = tile % tiles_per_batch;
             uint32_t tm, tn;
@@ -210,25 +266,42 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 for (int j = 0; j < 4; ++j) {
                     if (kb0 + j >= a.kblocks) break;
                     const float sc = sc_cur[j];
-                    if (!ptx::mbar_wait_a(tfull0 + 8u * buf, bpar, abort_flag)) {
+                    OPSNN_PB_T(d_t2);
+                    if (!pb_wait<BN == 256>(tfull0 + 8u * buf, bpar, abort_flag)) {
                         report(abort_flag, (3u << 8) | 2u);
                         ok = false;
                         break;
                     }
+                    OPSNN_PB_ADD(d_tfull, d_t2);
                     ptx::tc_fence_after();
-                    constexpr int W = 16;
+#if defined(OPSNN_PB_EXPERIMENT) && OPSNN_PB_EXPERIMENT == 1
+                    // diagnostic build: the buffer is released unread (main loop alone)
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
+                    if (++buf == NBUF) {
+                        buf = 0;
+                        bpar ^= 1u;
+                    }
+                    acc[0] += sc;
+                    continue;
+#endif
+#ifndef OPSNN_PB256_W
+#define OPSNN_PB256_W 16
+#endif
+                    constexpr int W = BN == 256 ? OPSNN_PB256_W : 16;  // staging registers per TMEM load (two sets in flight)
                     const uint32_t t0 = tmem_base + lane_addr + buf * BN;
                     uint32_t va[W], vb[W];
-                    ptx::tmem_ld16(t0, va);
+                    ptx::tmem_ld_n(t0, va);
 #pragma unroll
                     for (int c = 0; c < kCols; c += 2 * W) {
                         ptx::tmem_ld_wait();
-                        ptx::tmem_ld16(t0 + c + W, vb);
+                        ptx::tmem_ld_n(t0 + c + W, vb);
 #pragma unroll
                         for (int i = 0; i < W; ++i) acc[c + i] = promote<kKind>(va[i], sc, acc[c + i]);
                         ptx::tmem_ld_wait();
                         if (c + 2 * W < kCols) {
-                            ptx::tmem_ld16(t0 + c + 2 * W, va);
+                            ptx::tmem_ld_n(t0 + c + 2 * W, va);
                         } else {
                             ptx::tc_fence_before();
                             __syncwarp();
@@ -264,7 +337,20 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 }
             }
         }
+#ifdef OPSNN_PB_DIAG
+        if (warp == 0 && lane == 0) {
+            g_pb_diag[blockIdx.x * 5 + 3] = (unsigned long long)d_tfull;
+            g_pb_diag[blockIdx.x * 5 + 4] = (unsigned long long)(clock64() - d_estart);
+        }
+#endif
+        (void)d_tfull;
     }
+    else if (BN == 256) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");  // the two idle warps of the third warpgroup
+    }
+#ifdef OPSNN_PB_DIAG
+    // (epilogue warp 0's counters are written from inside its branch)
+#endif
     // ---- teardown ----
     if (*abort_flag != 0u) __nanosleep(200000);
     ptx::tc_fence_before();
@@ -276,22 +362,22 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
-template <ptx::MmaKind KIND, int EW>
+template <ptx::MmaKind KIND, int EW, int BN = 128>
 int32_t launch_pair_pb(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
 {
-    constexpr int kStage = kATile + 64 * BK;
+    constexpr int kStage = kATile + (BN / 2) * BK;
     int stages = (227 * 1024 - 2048) / kStage;
     if (stages > 8) stages = 8;
     if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * kStage + 1024 + 256;
-    auto kern = qmm_umma_pair_pb_kernel<KIND, EW>;
+    auto kern = qmm_umma_pair_pb_kernel<KIND, EW, BN>;
     static std::atomic<uint64_t> configured{0};
     if (once_per_device(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess)
         return (int32_t)cudaGetLastError();
     int64_t pairs = sm_count() / 2;
     if (a.num_tiles < pairs) pairs = a.num_tiles;
-    kern<<<(unsigned)(2 * pairs), (EW + 2) * 32, smem, stream>>>(ma, mb, a);
+    kern<<<(unsigned)(2 * pairs), pair_pb_threads<EW, BN>(), smem, stream>>>(ma, mb, a);
     note_launch("qmm_umma_pair_perblock");
     return (int32_t)cudaGetLastError();
 }
@@ -303,6 +389,16 @@ bool pair_pb_worthwhile(const OpsnnQmmParams* p)
     if (const char* e = getenv("OPSNN_QMM_PAIR")) return atoi(e) != 0;
     const int64_t tiles = p->batch * ((p->m + 255) / 256) * ((p->n + 127) / 128);
     return p->m >= 256 && tiles >= 74;
+}
+
+// Tile width of the per-block pair kernel: 256 columns (32 KB of operands per CTA and k-block for twice the tensor work of the
+// 128-column tile's 24 KB: the L2 -> SM feed is what bounds the main loop) once there are enough such tiles for every pair.
+// OPSNN_QMM_PB_BN=128|256 fixes it.
+int pair_pb_bn(const OpsnnQmmParams* p)
+{
+    if (const char* e = getenv("OPSNN_QMM_PB_BN")) return atoi(e) == 256 ? 256 : 128;
+    const int64_t tiles = p->batch * ((p->m + 255) / 256) * ((p->n + 255) / 256);
+    return tiles >= sm_count() / 2 ? 256 : 128;
 }
 
 }  // namespace

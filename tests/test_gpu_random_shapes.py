@@ -37,14 +37,16 @@ def _perblock_case(rng):
     return m, k, n, t1, t2, is_int, gm, x1, x2, s1, s2
 
 
+@pytest.mark.parametrize("tile_n", ["128", "256"])
 @pytest.mark.parametrize("seed", [1, 2, 4])
-def test_perblock_pair_random_shapes(aclnn, seed, monkeypatch):
+def test_perblock_pair_random_shapes(aclnn, seed, tile_n, monkeypatch):
     """int8 per-block results are bit-exact (integer partial sums promoted exactly, fp32 operations in the reference's
     order); fp8 per-block within the stated bf16 tolerance of the fp32 result."""
     from gpu_util import check_close, desc, out_tensor, out_to_np
     import torch
 
     monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    monkeypatch.setenv("OPSNN_QMM_PB_BN", tile_n)
     rng = np.random.default_rng(seed)
     for _ in range(10):
         m, k, n, t1, t2, is_int, gm, x1, x2, s1, s2 = _perblock_case(rng)

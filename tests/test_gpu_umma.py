@@ -251,10 +251,12 @@ PAIR_PB_CASES = [
 ]
 
 
+@pytest.mark.parametrize("tile_n", ["128", "256"])
 @pytest.mark.parametrize("case", PAIR_PB_CASES, ids=[str(c) for c in PAIR_PB_CASES])
-def test_perblock_cta_pairs(aclnn, case, monkeypatch):
-    """The per-block kernels on CTA pairs (256 x 128 tiles, four TMEM buffers): same promotion arithmetic as the single-CTA
-    kernel; the int8 form stays bit-identical to the reference."""
+def test_perblock_cta_pairs(aclnn, case, tile_n, monkeypatch):
+    """The per-block kernels on CTA pairs (256 x 128 tiles with four TMEM buffers, or 256 x 256 tiles with two and the register
+    file re-divided between the warp roles): same promotion arithmetic as the single-CTA kernel; the int8 form stays
+    bit-identical to the reference."""
     from gpu_util import check_close
 
     m, k, n, t1, t2, gm, is_int, bias_kind, out_name = case
@@ -274,6 +276,7 @@ def test_perblock_cta_pairs(aclnn, case, monkeypatch):
     group = (gm << 32) | (128 << 16) | 128
     want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, bias, t1, t2, group, out_name)
     monkeypatch.setenv("OPSNN_QMM_PAIR", "1")
+    monkeypatch.setenv("OPSNN_QMM_PB_BN", tile_n)
     got = _run(aclnn, x1, x2, s1, s2, bias, t1, t2, group, out_name, "qmm_umma_pair_perblock")
     if is_int:
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
