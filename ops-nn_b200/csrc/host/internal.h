@@ -6,8 +6,23 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "aclnn_compat/acl_base.h"
 #include "opsnn_b200_kernels.h"
+
+// An NVTX range around each phase of every entry point (the reference brackets its entry points with L2_DFX_PHASE_1 / _2,
+// aclnn_quant_matmul_v5.cpp:1196, :1225): shows up in a timeline tool when one is attached, costs a null check otherwise.
+namespace opsnn {
+struct DfxRange {
+    explicit DfxRange(const char* name) { nvtxRangePushA(name); }
+    ~DfxRange() { nvtxRangePop(); }
+    DfxRange(const DfxRange&) = delete;
+    DfxRange& operator=(const DfxRange&) = delete;
+};
+}  // namespace opsnn
+#define OPSNN_DFX_RANGE(name) ::opsnn::DfxRange opsnn_dfx_range_(name)
+
 
 // Tensor descriptor. Mirrors what the reference's aclTensor carries (docs/zh/context/non_contiguous_tensor.md of
 // the reference): view shape, strides and offset in elements, storage shape, format, dtype, device address.

@@ -514,6 +514,7 @@ aclnnStatus aclnnQuantMatmulV5GetWorkspaceSize(const aclTensor* x1, const aclTen
                                                bool transposeX2, int64_t groupSize, aclTensor* out,
                                                uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV5GetWorkspaceSize");
     clear_err();
     if (workspaceSize == nullptr || executor == nullptr) {
         set_err("aclnnQuantMatmulV5GetWorkspaceSize: workspaceSize/executor is nullptr");
@@ -944,6 +945,7 @@ static aclnnStatus qmm_run(const char* api, void* workspace, uint64_t workspaceS
 
 aclnnStatus aclnnQuantMatmulV5(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV5");
     return qmm_run("aclnnQuantMatmulV5", workspace, workspaceSize, executor, stream);
 }
 
@@ -957,6 +959,7 @@ aclnnStatus aclnnQuantMatmulWeightNzGetWorkspaceSize(const aclTensor* x1, const 
                                                      bool transposeX1, bool transposeX2, int64_t groupSize, aclTensor* out,
                                                      uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulWeightNzGetWorkspaceSize");
     const char* api = "aclnnQuantMatmulWeightNzGetWorkspaceSize";
     clear_err();
     if (workspaceSize == nullptr || executor == nullptr || x2 == nullptr) {
@@ -1006,6 +1009,7 @@ aclnnStatus aclnnQuantMatmulWeightNzGetWorkspaceSize(const aclTensor* x1, const 
 
 aclnnStatus aclnnQuantMatmulWeightNz(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulWeightNz");
     return qmm_run("aclnnQuantMatmulWeightNz", workspace, workspaceSize, executor, stream);
 }
 
@@ -1017,12 +1021,14 @@ aclnnStatus aclnnQuantMatmulV4GetWorkspaceSize(const aclTensor* x1, const aclTen
                                                const aclTensor* bias, bool transposeX1, bool transposeX2, const aclTensor* out,
                                                uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV4GetWorkspaceSize");
     return aclnnQuantMatmulV5GetWorkspaceSize(x1, x2, pertokenScaleOptional, scale, nullptr, nullptr, offset, nullptr, bias, transposeX1,
                                               transposeX2, 0, const_cast<aclTensor*>(out), workspaceSize, executor);
 }
 
 aclnnStatus aclnnQuantMatmulV4(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV4");
     return aclnnQuantMatmulV5(workspace, workspaceSize, executor, stream);
 }
 
@@ -1030,12 +1036,14 @@ aclnnStatus aclnnQuantMatmulV3GetWorkspaceSize(const aclTensor* x1, const aclTen
                                                const aclTensor* offset, const aclTensor* bias, bool transposeX1, bool transposeX2,
                                                const aclTensor* out, uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV3GetWorkspaceSize");
     return aclnnQuantMatmulV5GetWorkspaceSize(x1, x2, nullptr, scale, nullptr, nullptr, offset, nullptr, bias, transposeX1, transposeX2, 0,
                                               const_cast<aclTensor*>(out), workspaceSize, executor);
 }
 
 aclnnStatus aclnnQuantMatmulV3(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnQuantMatmulV3");
     return aclnnQuantMatmulV5(workspace, workspaceSize, executor, stream);
 }
 
@@ -1066,6 +1074,7 @@ static aclnnStatus plan_on_x2(const char* api, const aclTensor* x2, const aclTen
 aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize,
                                                     int64_t mHint, uint64_t* storageSize)
 {
+    OPSNN_DFX_RANGE("opsnnQuantMatmulPrepareX2GetStorageSize");
     const char* api = "opsnnQuantMatmulPrepareX2GetStorageSize";
     clear_err();
     if (storageSize == nullptr) {
@@ -1088,6 +1097,7 @@ aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x2, const a
 aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize, int64_t mHint,
                                       void* storage, uint64_t storageSize, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("opsnnQuantMatmulPrepareX2");
     const char* api = "opsnnQuantMatmulPrepareX2";
     clear_err();
     if (x2 != nullptr && x2Scale != nullptr && x2Scale->dtype != ACL_FLOAT8_E8M0) return ACLNN_SUCCESS;  // not an MX mode: nothing to prepare
@@ -1117,6 +1127,7 @@ aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Sc
 
 aclnnStatus opsnnQuantMatmulReleaseX2(const aclTensor* x2)
 {
+    OPSNN_DFX_RANGE("opsnnQuantMatmulReleaseX2");
     clear_err();
     if (x2 == nullptr) return ACLNN_ERR_PARAM_NULLPTR;
     std::unique_lock<std::shared_mutex> lk(g_prepared_mu);

@@ -276,6 +276,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(const aclTensor* x, co
                                                           const aclTensor* y, uint64_t* workspaceSize,
                                                           aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulV2GetWorkspaceSize");
     return wq_common("aclnnWeightQuantBatchMatmulV2GetWorkspaceSize", x, weight, antiquantScale, antiquantOffsetOptional,
                      quantScaleOptional, quantOffsetOptional, biasOptional, antiquantGroupSize, 0, y, workspaceSize, executor);
 }
@@ -283,6 +284,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulV2GetWorkspaceSize(const aclTensor* x, co
 aclnnStatus aclnnWeightQuantBatchMatmulV2(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                           aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulV2");
     return wq_run("aclnnWeightQuantBatchMatmulV2", workspace, workspaceSize, executor, stream);
 }
 
@@ -295,6 +297,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulV3GetWorkspaceSize(const aclTensor* x, co
                                                           int innerPrecise, const aclTensor* y, uint64_t* workspaceSize,
                                                           aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulV3GetWorkspaceSize");
     if (innerPrecise != 0 && innerPrecise != 1) {
         clear_err();
         set_err("aclnnWeightQuantBatchMatmulV3GetWorkspaceSize: innerPrecise must be 0 or 1, got %d", innerPrecise);
@@ -308,6 +311,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulV3GetWorkspaceSize(const aclTensor* x, co
 aclnnStatus aclnnWeightQuantBatchMatmulV3(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor,
                                           aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulV3");
     return wq_run("aclnnWeightQuantBatchMatmulV3", workspace, workspaceSize, executor, stream);
 }
 
@@ -319,6 +323,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulNzGetWorkspaceSize(const aclTensor* x, co
                                                           int antiquantGroupSize, const aclTensor* y, uint64_t* workspaceSize,
                                                           aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulNzGetWorkspaceSize");
     const char* api = "aclnnWeightQuantBatchMatmulNzGetWorkspaceSize";
     clear_err();
     if (x == nullptr || weight == nullptr || antiquantScale == nullptr || y == nullptr || workspaceSize == nullptr || executor == nullptr) {
@@ -345,6 +350,7 @@ aclnnStatus aclnnWeightQuantBatchMatmulNzGetWorkspaceSize(const aclTensor* x, co
 
 aclnnStatus aclnnWeightQuantBatchMatmulNz(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnWeightQuantBatchMatmulNz");
     return wq_run("aclnnWeightQuantBatchMatmulNz", workspace, workspaceSize, executor, stream);
 }
 
@@ -355,6 +361,7 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
                                                 const aclTensor* yOut, const aclTensor* mxscaleOut,
                                                 uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnDynamicMxQuantGetWorkspaceSize");
     const char* api = "aclnnDynamicMxQuantGetWorkspaceSize";
     clear_err();
     if (workspaceSize == nullptr || executor == nullptr || x == nullptr || yOut == nullptr || mxscaleOut == nullptr) {
@@ -426,6 +433,7 @@ aclnnStatus aclnnDynamicMxQuantGetWorkspaceSize(const aclTensor* x, int64_t axis
 
 aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnDynamicMxQuant");
     (void)workspace;
     (void)workspaceSize;
     clear_err();
@@ -456,6 +464,7 @@ aclnnStatus aclnnDynamicMxQuant(void* workspace, uint64_t workspaceSize, aclOpEx
 aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor* weight, aclTensor* weightInt4Pack,
                                                          uint64_t* workspaceSize, aclOpExecutor** executor)
 {
+    OPSNN_DFX_RANGE("aclnnConvertWeightToINT4PackGetWorkspaceSize");
     const char* api = "aclnnConvertWeightToINT4PackGetWorkspaceSize";
     clear_err();
     if (weight == nullptr || weightInt4Pack == nullptr || workspaceSize == nullptr || executor == nullptr) {
@@ -497,6 +506,7 @@ aclnnStatus aclnnConvertWeightToINT4PackGetWorkspaceSize(const aclTensor* weight
 
 aclnnStatus aclnnConvertWeightToINT4Pack(void* workspace, uint64_t workspaceSize, aclOpExecutor* executor, aclrtStream stream)
 {
+    OPSNN_DFX_RANGE("aclnnConvertWeightToINT4Pack");
     (void)workspace;
     (void)workspaceSize;
     clear_err();
