@@ -792,6 +792,8 @@ DEV_WORKLOADS = {
     "c5mmt": (32, 2048, 4096, 14336, "mxfp8_t"),    # same with the weight stored (n,k), transposeX2 = true
     "c2p": (1, 2048, 8192, 28672, "w4a16_prefill"), # the headline weight at a prefill m: dequant pre-pass + bf16 tcgen05 matmul
     "c2ps": (1, 256, 8192, 28672, "w4a16_prefill"),
+    "c2pp": (1, 2048, 8192, 28672, "w4a16_prefill_prepared"),  # c2p with the weight dequantised once (opsnnWeightQuantPrepare)
+    "c2pps": (1, 256, 8192, 28672, "w4a16_prefill_prepared"),
     "c2m32": (1, 32, 8192, 28672, "w4a16_prefill"),  # 16 < m <= 48: the decode kernel once per 16 rows
     "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
     "w8m16": (1, 16, 8192, 28672, "w8a16"),            # the headline shape with INT8 weights (per-channel bf16 scale): streaming kernel, 235 MB
@@ -852,7 +854,7 @@ def run_dev_workload(args):
             else:
                 call = lambda i: mm()  # noqa: E731
                 nbytes = b * (m * k + k * n + (m + n) * kq * 2 + 2 * m * n)
-    elif kind == "w4a16_prefill":
+    elif kind in ("w4a16_prefill", "w4a16_prefill_prepared"):
         sets = 1  # the packed weight (117 MB) plus its dequantised copy (470 MB) exceed L2 by themselves
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         x = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
@@ -864,6 +866,7 @@ def run_dev_workload(args):
         scale = (torch.rand((k // 128, n), generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
         offset = (torch.rand((k // 128, n), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
         d = [aclnn.from_torch(t) for t in (x, words, scale, offset, out)]
+        prepared_storage = aclnn.prepare_weight(d[1], d[2], d[3], 128, "bfloat16") if kind.endswith("prepared") else None  # noqa: F841 (kept alive)
         ws_bytes = aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128)
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
         call = lambda i: aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128, workspace=workspace)  # noqa: E731
@@ -928,7 +931,7 @@ def run_dev_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w8a16") else 4500.0)
+    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w4a16_prefill_prepared", "w8a16") else 4500.0)
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
                       "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,

@@ -153,9 +153,18 @@ typedef struct OpsnnWqbmmParams {
        rewritten row-major into the head of the workspace before the matmul runs. */
     int32_t nz_k0, nz_n0;
     int32_t scale_dtype;    /* 0 or x_dtype: scale in x's dtype; ACL_FLOAT8_E8M0: mx antiquant (group_size 32, no offset) */
+    /* Optional: the weight as the prefill path would dequantise it (opsnn_wqbmm_prepare_launch wrote it, once, into caller
+       memory). With it set, calls on the prefill path (m > 16) skip the dequantisation pre-pass and need no workspace; results
+       are identical. Ignored by the decode kernels, which stream the packed weight. */
+    const void* prep_w;
 } OpsnnWqbmmParams;
 
 OPSNN_API uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_choice);
+/* Prepare-once form of the prefill path's weight: bytes of caller storage (0: this weight / layout has no prefill path), and the
+ * pre-pass alone, writing the dequantised 16-bit weight of p (x_dtype says bf16 or fp16) into `storage` (256-byte aligned). p->x, p->y
+ * and p->m are not read. Afterwards set p->prep_w = storage in calls on the same weight, scale, offset and x dtype. */
+OPSNN_API uint64_t opsnn_wqbmm_prepare_size(const OpsnnWqbmmParams* p);
+OPSNN_API int32_t opsnn_wqbmm_prepare_launch(const OpsnnWqbmmParams* p, void* storage, uint64_t storage_size, void* stream);
 OPSNN_API int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p);
 OPSNN_API int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream);
 

@@ -1,5 +1,5 @@
 /*
- * Prepare-once weights for aclnnQuantMatmulV5 (the MX modes).
+ * Prepare-once weights for aclnnQuantMatmulV5 (the MX modes) and for the prefill path of aclnnWeightQuantBatchMatmulV2 / V3.
  *
  * A weight (x2) and its scale are static, yet part of every call's time goes into layout work on them that does not depend on
  * the activations: x2Scale is rewritten into the order the tensor core's scale copies want, an MXFP4 x2 stored (k,n) must be
@@ -35,6 +35,26 @@ ACLNN_API aclnnStatus opsnnQuantMatmulPrepareX2GetStorageSize(const aclTensor* x
 ACLNN_API aclnnStatus opsnnQuantMatmulPrepareX2(const aclTensor* x2, const aclTensor* x2Scale, bool transposeX2, int64_t groupSize,
                                                 int64_t mHint, void* storage, uint64_t storageSize, aclrtStream stream);
 ACLNN_API aclnnStatus opsnnQuantMatmulReleaseX2(const aclTensor* x2);
+
+/*
+ * The same for aclnnWeightQuantBatchMatmulV2 / V3 beyond the decode range (m > 16). There a call first dequantises the whole
+ * weight into 16-bit workspace (k x n x 2 bytes: 470 MB for the benchmark's decode weight) and then runs the tensor-core
+ * matmul; the first step does not depend on the activations. opsnnWeightQuantPrepare runs it once into caller memory and
+ * registers the image under the weight's device address; later calls with the same weight, antiquantScale, antiquantOffset,
+ * antiquantGroupSize and x dtype and m > 16 skip the pre-pass and ask for no workspace (bit-identical results). Calls with
+ * m <= 16 keep streaming the packed weight. The price is memory: the image is four (int4) or two (int8 / fp8) times the packed
+ * weight, which is why this is the caller's choice. Weights with no prefill path report size 0 and register nothing.
+ *
+ *   xDtype   ACL_BF16 or ACL_FLOAT16: the dtype of the activations of the calls to come (the reference rounds the dequantised
+ *            weight to it, so the image depends on it).
+ */
+ACLNN_API aclnnStatus opsnnWeightQuantPrepareGetStorageSize(const aclTensor* weight, const aclTensor* antiquantScale,
+                                                            const aclTensor* antiquantOffset, int antiquantGroupSize, aclDataType xDtype,
+                                                            uint64_t* storageSize);
+ACLNN_API aclnnStatus opsnnWeightQuantPrepare(const aclTensor* weight, const aclTensor* antiquantScale, const aclTensor* antiquantOffset,
+                                              int antiquantGroupSize, aclDataType xDtype, void* storage, uint64_t storageSize,
+                                              aclrtStream stream);
+ACLNN_API aclnnStatus opsnnWeightQuantRelease(const aclTensor* weight);
 
 #ifdef __cplusplus
 }

@@ -47,7 +47,7 @@ class WqbmmParams(ctypes.Structure):
                 ("scale", c_void_p), ("offset", c_void_p), ("group_size", c_int64), ("scale_sg", c_int64),
                 ("scale_sn", c_int64), ("bias", c_void_p), ("y", c_void_p), ("y_ld", c_int64),
                 ("workspace", c_void_p), ("workspace_size", c_uint64), ("inner_precise", c_int32),
-                ("nz_k0", c_int32), ("nz_n0", c_int32), ("scale_dtype", c_int32)]
+                ("nz_k0", c_int32), ("nz_n0", c_int32), ("scale_dtype", c_int32), ("prep_w", c_void_p)]
 
 
 _lib = None
@@ -107,7 +107,11 @@ def lib():
     L.opsnnQuantMatmulPrepareX2GetStorageSize.argtypes = [T, T, c_bool, c_int64, c_int64, POINTER(c_uint64)]
     L.opsnnQuantMatmulPrepareX2.argtypes = [T, T, c_bool, c_int64, c_int64, c_void_p, c_uint64, c_void_p]
     L.opsnnQuantMatmulReleaseX2.argtypes = [T]
-    for name in ("opsnnQuantMatmulPrepareX2GetStorageSize", "opsnnQuantMatmulPrepareX2", "opsnnQuantMatmulReleaseX2"):
+    L.opsnnWeightQuantPrepareGetStorageSize.argtypes = [T, T, T, c_int32, c_int32, POINTER(c_uint64)]
+    L.opsnnWeightQuantPrepare.argtypes = [T, T, T, c_int32, c_int32, c_void_p, c_uint64, c_void_p]
+    L.opsnnWeightQuantRelease.argtypes = [T]
+    for name in ("opsnnQuantMatmulPrepareX2GetStorageSize", "opsnnQuantMatmulPrepareX2", "opsnnQuantMatmulReleaseX2",
+                 "opsnnWeightQuantPrepareGetStorageSize", "opsnnWeightQuantPrepare", "opsnnWeightQuantRelease"):
         getattr(L, name).restype = c_int32
     L.opsnn_probe_umma.argtypes = [c_int32, c_int32, POINTER(ctypes.c_double)]
     L.opsnn_probe_mix.argtypes = [c_int32, POINTER(ctypes.c_double)]
@@ -377,6 +381,33 @@ def release_x2(x2):
     st = lib().opsnnQuantMatmulReleaseX2(_h(x2))
     if st != ACLNN_SUCCESS:
         raise AclnnError("opsnnQuantMatmulReleaseX2", st)
+
+
+def prepare_weight(weight, antiquant_scale, antiquant_offset=None, antiquant_group_size=0, x_dtype="bfloat16"):
+    """opsnnWeightQuantPrepare on the current torch CUDA stream: the weight dequantised once for the prefill path (m > 16). Returns
+    the storage tensor the caller must keep alive, or None when this weight has no prefill path."""
+    import torch
+
+    code = DTYPE_BY_NAME[x_dtype] if isinstance(x_dtype, str) else x_dtype
+    need = c_uint64(0)
+    st = lib().opsnnWeightQuantPrepareGetStorageSize(_h(weight), _h(antiquant_scale), _h(antiquant_offset), int(antiquant_group_size),
+                                                     int(code), byref(need))
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnWeightQuantPrepareGetStorageSize", st)
+    if need.value == 0:
+        return None
+    storage = torch.empty(int(need.value), dtype=torch.uint8, device=weight._keep.device)
+    st = lib().opsnnWeightQuantPrepare(_h(weight), _h(antiquant_scale), _h(antiquant_offset), int(antiquant_group_size), int(code),
+                                       c_void_p(storage.data_ptr()), c_uint64(need.value), _stream())
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnWeightQuantPrepare", st)
+    return storage
+
+
+def release_weight(weight):
+    st = lib().opsnnWeightQuantRelease(_h(weight))
+    if st != ACLNN_SUCCESS:
+        raise AclnnError("opsnnWeightQuantRelease", st)
 
 
 # ---- multi-GPU helpers (include/opsnn_b200_shard.h) --------------------------------------------------------------

@@ -66,6 +66,8 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
 uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p);
 int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
+uint64_t wqbmm_prefill_image_size(const OpsnnWqbmmParams* p);
+int32_t wqbmm_prefill_prepass(const OpsnnWqbmmParams* p, uint8_t* ws, cudaStream_t stream);
 
 uint64_t wq_nz_bytes(const OpsnnWqbmmParams* p);
 void wq_nz_view(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* q, void* dst);
@@ -195,6 +197,9 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
     // 8-bit integer weights at small m: their own streaming kernel once the weight is large enough to be worth a k-split grid
     if (wqbmm_decode8_eligible(p) && p->k * p->n >= ((int64_t)1 << 20) && getenv("OPSNN_WQ_NO_DECODE8") == nullptr) return OPSNN_WQ_KERNEL_DECODE;
+    // a weight prepared for the prefill path (dequantised once, kept by the caller): beyond the decode range the tensor-core matmul
+    // alone beats streaming the packed weight once per 16 rows
+    if (p->prep_w != nullptr && p->m > 16 && wqbmm_prefill_eligible(p)) return OPSNN_WQ_KERNEL_PREFILL;
     OpsnnWqbmmParams chunk;
     if (getenv("OPSNN_WQ_NO_CHUNKS") == nullptr && decode_in_chunks(p, &chunk))
         return (p->inner_precise == 1 && wqbmm_decode_fast_eligible(&chunk)) ? OPSNN_WQ_KERNEL_DECODE_FAST : OPSNN_WQ_KERNEL_DECODE;
@@ -217,6 +222,38 @@ uint64_t opsnn_wqbmm_workspace_size(const OpsnnWqbmmParams* p, int32_t kernel_ch
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_PREFILL) return wqbmm_prefill_workspace_size(p);
     return (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) ? wqbmm_decode_workspace_size(p) : 0;
+}
+
+// A stand-in view for the questions that do not depend on the activations (is there a prefill path for this weight, how large is
+// its dequantised image): one aligned row of x.
+static void prepare_view(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* v)
+{
+    *v = *p;
+    v->m = 32;
+    v->x = reinterpret_cast<const void*>(uintptr_t(256));
+    v->x_ld = (p->k + 7) / 8 * 8;
+    v->y = reinterpret_cast<void*>(uintptr_t(256));
+    v->y_ld = p->n;
+    v->prep_w = nullptr;
+}
+
+uint64_t opsnn_wqbmm_prepare_size(const OpsnnWqbmmParams* p)
+{
+    if (p == nullptr || p->nz_k0 != 0 || p->n <= 0 || p->k <= 0) return 0;
+    OpsnnWqbmmParams v;
+    prepare_view(p, &v);
+    return wqbmm_prefill_eligible(&v) ? wqbmm_prefill_image_size(&v) : 0;
+}
+
+int32_t opsnn_wqbmm_prepare_launch(const OpsnnWqbmmParams* p, void* storage, uint64_t storage_size, void* stream)
+{
+    const uint64_t need = opsnn_wqbmm_prepare_size(p);
+    if (need == 0 || storage == nullptr || storage_size < need || (reinterpret_cast<uintptr_t>(storage) & 255) != 0 || p->w == nullptr ||
+        p->scale == nullptr)
+        return (int32_t)cudaErrorInvalidValue;
+    OpsnnWqbmmParams v;
+    prepare_view(p, &v);
+    return wqbmm_prefill_prepass(&v, static_cast<uint8_t*>(storage), static_cast<cudaStream_t>(stream));
 }
 
 int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, void* stream)

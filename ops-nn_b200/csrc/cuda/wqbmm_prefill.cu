@@ -360,10 +360,12 @@ void gemm_view(const OpsnnWqbmmParams* p, OpsnnQmmParams* q, void* wdeq, const v
 
 }  // namespace
 
-uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p)
+uint64_t wqbmm_prefill_image_size(const OpsnnWqbmmParams* p)
 {
     return (uint64_t)p->n * (uint64_t)padded_k(p) * 2u + 512u;  // dequantised weight, alignment slack, the unit scale
 }
+
+uint64_t wqbmm_prefill_workspace_size(const OpsnnWqbmmParams* p) { return p->prep_w != nullptr ? 0 : wqbmm_prefill_image_size(p); }
 
 bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p)
 {
@@ -380,10 +382,9 @@ bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p)
     return qmm_umma_eligible(&q);
 }
 
-int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+// The dequantisation pre-pass alone: the (n, padded k) 16-bit weight and the unit scale behind it, at `ws` (256-byte aligned).
+int32_t wqbmm_prefill_prepass(const OpsnnWqbmmParams* p, uint8_t* ws, cudaStream_t stream)
 {
-    if (p->workspace == nullptr || p->workspace_size < wqbmm_prefill_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
-    uint8_t* ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
     const int64_t kp = padded_k(p);
     uint16_t* wdeq = reinterpret_cast<uint16_t*>(ws);
     float* one = reinterpret_cast<float*>(ws + (((uint64_t)p->n * kp * 2u + 15u) & ~(uint64_t)15u));
@@ -435,8 +436,24 @@ int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     else if (fast) wq_dequant_nk_words_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     else wq_dequant_nk_kernel<false><<<(unsigned)tiles, NT, 0, stream>>>(*p, wdeq, kp, one);
     note_launch("wq_dequant_nk");
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return (int32_t)e;
+    return (int32_t)cudaGetLastError();
+}
+
+int32_t wqbmm_prefill_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
+{
+    uint8_t* ws;
+    if (p->prep_w != nullptr) {
+        if ((reinterpret_cast<uintptr_t>(p->prep_w) & 255) != 0) return (int32_t)cudaErrorInvalidValue;
+        ws = const_cast<uint8_t*>(static_cast<const uint8_t*>(p->prep_w));  // prepared once: nothing to do per call
+    } else {
+        if (p->workspace == nullptr || p->workspace_size < wqbmm_prefill_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+        ws = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+        const int32_t rc = wqbmm_prefill_prepass(p, ws, stream);
+        if (rc != 0) return rc;
+    }
+    const int64_t kp = padded_k(p);
+    uint16_t* wdeq = reinterpret_cast<uint16_t*>(ws);
+    float* one = reinterpret_cast<float*>(ws + (((uint64_t)p->n * kp * 2u + 15u) & ~(uint64_t)15u));
     OpsnnQmmParams q;
     gemm_view(p, &q, wdeq, one);
     if (!qmm_umma_eligible(&q)) return (int32_t)cudaErrorInvalidValue;

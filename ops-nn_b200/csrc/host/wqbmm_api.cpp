@@ -6,7 +6,10 @@
 //     :402-455 quant/bias shapes, :439-576 x/weight/y dims, :1482-1576 int32 -> int4 view, :1584-1590 x contiguity,
 //     :1671-1767 common process, :1719-1889 entry points.
 #include <cstring>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <shared_mutex>
 
 #include "aclnnop/aclnn_convert_weight_to_int4_pack.h"
 #include "aclnnop/aclnn_dynamic_mx_quant.h"
@@ -14,10 +17,36 @@
 #include "aclnnop/aclnn_weight_quant_batch_matmul_nz.h"
 #include "aclnnop/aclnn_weight_quant_batch_matmul_v3.h"
 #include "internal.h"
+#include "opsnn_b200_prepare.h"
 
 using namespace opsnn;
 
 namespace {
+
+// Weights prepared for the prefill path (opsnnWeightQuantPrepare): the dequantised image in caller memory, registered under the
+// weight's device address together with everything the image depends on.
+struct PreparedW {
+    OpsnnWqbmmParams key;
+    const void* image = nullptr;
+};
+std::shared_mutex g_prepared_w_mu;
+std::map<const void*, PreparedW> g_prepared_w;
+
+bool same_weight(const OpsnnWqbmmParams& a, const OpsnnWqbmmParams& b)
+{
+    return a.w == b.w && a.scale == b.scale && a.offset == b.offset && a.n == b.n && a.k == b.k && a.w_ld == b.w_ld &&
+           a.trans_w == b.trans_w && a.w_dtype == b.w_dtype && a.x_dtype == b.x_dtype && a.group_size == b.group_size &&
+           a.scale_sg == b.scale_sg && a.scale_sn == b.scale_sn && a.scale_dtype == b.scale_dtype && a.nz_k0 == b.nz_k0;
+}
+
+void attach_prepared_w(OpsnnWqbmmParams* p)
+{
+    p->prep_w = nullptr;
+    if (p->w == nullptr) return;
+    std::shared_lock<std::shared_mutex> lk(g_prepared_w_mu);
+    auto it = g_prepared_w.find(p->w);
+    if (it != g_prepared_w.end() && same_weight(it->second.key, *p)) p->prep_w = it->second.image;
+}
 
 #define WQ_INVALID(...)                 \
     do {                                \
@@ -197,6 +226,7 @@ aclnnStatus wq_common(const char* api, const aclTensor* x, const aclTensor* weig
     p.nz_k0 = nz_k0;
     p.nz_n0 = nz_n0;
     if (nz_k0 != 0 && trans_w) no_kernel("a FRACTAL_NZ weight must be the plain (k,n) view");
+    attach_prepared_w(&p);
     exec->kernel_choice = OPSNN_WQ_KERNEL_AUTO;
     if (const char* e = std::getenv("OPSNN_WQ_KERNEL")) exec->kernel_choice = std::atoi(e);
     if (!exec->unsupported) {
@@ -524,6 +554,112 @@ aclnnStatus aclnnConvertWeightToINT4Pack(void* workspace, uint64_t workspaceSize
         set_err("aclnnConvertWeightToINT4Pack: kernel launch failed with CUDA error %d", rc);
         return ACLNN_ERR_RUNTIME_ERROR;
     }
+    return ACLNN_SUCCESS;
+}
+
+
+// ---- prepare-once weight for the prefill path (include/opsnn_b200_prepare.h) ----
+static aclnnStatus plan_on_weight(const char* api, const aclTensor* weight, const aclTensor* antiquantScale, const aclTensor* antiquantOffset,
+                                  int antiquantGroupSize, aclDataType xDtype, std::unique_ptr<aclOpExecutor>* exec_out)
+{
+    if (weight == nullptr || antiquantScale == nullptr) {
+        set_err("%s: weight and antiquantScale are required", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    if (weight->rank() != 2) {
+        set_err("%s: weight must be 2-D", api);
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    // stand-ins for the activations: 32 rows (beyond the decode range), an aligned address that is never read
+    int64_t k = weight->dim(-2), n = weight->dim(-1);
+    if (weight->dtype == ACL_INT32 || weight->dtype == ACL_FLOAT) {  // 8 four-bit values per word along the axis with stride 1
+        const bool k_inner = weight->strides[0] == 1 && weight->strides[1] != 1;
+        (k_inner ? k : n) *= 8;
+    }
+    aclTensor x, y;
+    x.shape = {32, k};
+    x.strides = {k, 1};
+    x.storage_shape = x.shape;
+    x.dtype = xDtype;
+    x.data = reinterpret_cast<void*>(uintptr_t(256));
+    y.shape = {32, n};
+    y.strides = {n, 1};
+    y.storage_shape = y.shape;
+    y.dtype = xDtype;
+    y.data = reinterpret_cast<void*>(uintptr_t(256));
+    uint64_t ws = 0;
+    aclOpExecutor* ex = nullptr;
+    const aclnnStatus st = wq_common(api, &x, weight, antiquantScale, antiquantOffset, nullptr, nullptr, nullptr, antiquantGroupSize, 0, &y, &ws, &ex);
+    if (st != ACLNN_SUCCESS) return st;
+    exec_out->reset(ex);
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnWeightQuantPrepareGetStorageSize(const aclTensor* weight, const aclTensor* antiquantScale, const aclTensor* antiquantOffset,
+                                                  int antiquantGroupSize, aclDataType xDtype, uint64_t* storageSize)
+{
+    OPSNN_DFX_RANGE("opsnnWeightQuantPrepareGetStorageSize");
+    const char* api = "opsnnWeightQuantPrepareGetStorageSize";
+    clear_err();
+    if (storageSize == nullptr) {
+        set_err("%s: storageSize is nullptr", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    *storageSize = 0;
+    std::unique_ptr<aclOpExecutor> exec;
+    const aclnnStatus st = plan_on_weight(api, weight, antiquantScale, antiquantOffset, antiquantGroupSize, xDtype, &exec);
+    if (st != ACLNN_SUCCESS) return st;
+    if (!exec->unsupported) {
+        exec->wq.prep_w = nullptr;
+        *storageSize = opsnn_wqbmm_prepare_size(&exec->wq);
+        if (*storageSize != 0) *storageSize += 256;  // room to align the image inside storage of any alignment
+    }
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnWeightQuantPrepare(const aclTensor* weight, const aclTensor* antiquantScale, const aclTensor* antiquantOffset,
+                                    int antiquantGroupSize, aclDataType xDtype, void* storage, uint64_t storageSize, aclrtStream stream)
+{
+    OPSNN_DFX_RANGE("opsnnWeightQuantPrepare");
+    const char* api = "opsnnWeightQuantPrepare";
+    clear_err();
+    std::unique_ptr<aclOpExecutor> exec;
+    const aclnnStatus st = plan_on_weight(api, weight, antiquantScale, antiquantOffset, antiquantGroupSize, xDtype, &exec);
+    if (st != ACLNN_SUCCESS) return st;
+    if (exec->unsupported) return ACLNN_SUCCESS;  // nothing to prepare
+    OpsnnWqbmmParams& p = exec->wq;
+    p.prep_w = nullptr;
+    const uint64_t need = opsnn_wqbmm_prepare_size(&p);
+    if (need == 0) return ACLNN_SUCCESS;
+    if (p.w == nullptr || p.scale == nullptr) {
+        set_err("%s: weight / antiquantScale were created without a device address", api);
+        return ACLNN_ERR_PARAM_NULLPTR;
+    }
+    uint8_t* image = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(storage) + 255) & ~uintptr_t(255));
+    if (storage == nullptr || storageSize < need + (uint64_t)(image - static_cast<uint8_t*>(storage))) {
+        set_err("%s: storage of %lu bytes needed", api, (unsigned long)(need + 256));
+        return ACLNN_ERR_PARAM_INVALID;
+    }
+    const int32_t rc = opsnn_wqbmm_prepare_launch(&p, image, need, stream);
+    if (rc != 0) {
+        set_err("%s: preparation failed with CUDA error %d", api, rc);
+        return ACLNN_ERR_RUNTIME_ERROR;
+    }
+    PreparedW e;
+    e.key = p;
+    e.image = image;
+    std::unique_lock<std::shared_mutex> lk(g_prepared_w_mu);
+    g_prepared_w[p.w] = e;
+    return ACLNN_SUCCESS;
+}
+
+aclnnStatus opsnnWeightQuantRelease(const aclTensor* weight)
+{
+    OPSNN_DFX_RANGE("opsnnWeightQuantRelease");
+    clear_err();
+    if (weight == nullptr) return ACLNN_ERR_PARAM_NULLPTR;
+    std::unique_lock<std::shared_mutex> lk(g_prepared_w_mu);
+    g_prepared_w.erase(data_ptr(weight));
     return ACLNN_SUCCESS;
 }
 
