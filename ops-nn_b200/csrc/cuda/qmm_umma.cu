@@ -67,6 +67,10 @@ struct UmmaArgs {
     uint32_t* ks_part;                 // [tile][split][128][BN] raw 32-bit accumulators
     unsigned long long* ks_count;      // [tile] (nonce << 8) | arrivals; any other nonce counts as zero arrivals
     unsigned long long ks_nonce;
+    // INT4 x INT4 asymmetric per-group on the pair kernel: two 128-deep k-blocks form one accumulation group of 256
+    const float* row_sums;      // [m][groups]: sum of x1's row over each k-group (row_sums_kernel)
+    const void* b_offset;       // x2Offset [groups][n], FLOAT16
+    int32_t groups;
     int32_t test_stall_kblock;  // tests of the give-up path only: >= 0 makes the producer stop issuing copies from this k-block of each
                                 // work item on (nothing is in flight then), so the MMA warp's wait for it runs out; 0 / negative: off
 };
@@ -813,6 +817,10 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
         if (f16 && (p->trans_a || !p->trans_b)) return false;
     } else if (p->mode == OPSNN_QMM_PERBLOCK) {
         if ((!f8 && !i8) || p->group_k != 128 || p->group_n != 128 || (p->group_m != 1 && p->group_m != 128)) return false;
+    } else if (p->mode == OPSNN_QMM_PERGROUP_ASYM) {
+        // INT4 x INT4 asymmetric per-group, operands already widened to INT8: groups of two 128-deep k-blocks on the pair kernel
+        if (!i8 || p->group_k != 256 || p->batch != 1 || p->b_offset == nullptr || p->scale_a == nullptr || p->bias != nullptr) return false;
+        if (getenv("OPSNN_QMM_ASYM_GENERIC")) return false;
     } else {
         return false;
     }
@@ -832,6 +840,7 @@ bool qmm_umma_eligible(const OpsnnQmmParams* p)
 uint64_t qmm_umma_workspace_size(const OpsnnQmmParams* p)
 {
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_workspace_size(p);
+    if (p->mode == OPSNN_QMM_PERGROUP_ASYM) return (uint64_t)p->m * (uint64_t)((p->k + 255) / 256) * 4u + 256u;  // row sums per k-group
     return p->mode == OPSNN_QMM_PERBLOCK ? 0 : ksplit_workspace(p);
 }
 
@@ -887,11 +896,12 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     if (p->mode == OPSNN_QMM_MX) return qmm_mx_umma_launch(p, stream);
     const bool pair = pair_worthwhile(p) && p->mode == OPSNN_QMM_DEQ && p->out_dtype != ACL_INT32 && p->out_dtype != ACL_INT8;
     // per-block on CTA pairs: 256 x 128 tiles
-    const bool pair_pb = pair_pb_worthwhile(p);
+    const bool asym = p->mode == OPSNN_QMM_PERGROUP_ASYM;
+    const bool pair_pb = asym || pair_pb_worthwhile(p);
     const uint8_t* b_ptr = static_cast<const uint8_t*>(p->b);
     int64_t b_ld = p->b_ld, b_bs = p->b_bs;
     int b_trans = p->trans_b;
-    const int pb_bn = pair_pb ? pair_pb_bn(p) : 0;
+    const int pb_bn = asym ? 128 : (pair_pb ? pair_pb_bn(p) : 0);
     const int bn = pair ? 256 : (pair_pb ? pb_bn : pick_bn(p));
     const int bm = (pair || pair_pb) ? 256 : BM;
     UmmaArgs a{};
@@ -950,6 +960,22 @@ int32_t qmm_umma_launch(const OpsnnQmmParams* p, cudaStream_t stream)
     else ok = ok && make_map(&mb, b_ptr, (uint64_t)p->k * es, (uint64_t)p->n, nb_b, (uint64_t)b_ld * es, (uint64_t)b_bs * es,
                              pair ? 128u : (pair_pb ? (uint32_t)(pb_bn / 2) : (uint32_t)bn));
     if (!ok) return (int32_t)cudaErrorInvalidValue;
+    if (asym) {
+        if (p->workspace == nullptr || p->workspace_size < qmm_umma_workspace_size(p)) return (int32_t)cudaErrorInvalidValue;
+        float* rs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(p->workspace) + 255) & ~(uintptr_t)255);
+        a.groups = (int32_t)((p->k + 255) / 256);
+        a.row_sums = rs;
+        a.b_offset = p->b_offset;
+        const int64_t total = p->m * a.groups;
+        int64_t grid = (total + 255) / 256;
+        if (grid > 148 * 8) grid = 148 * 8;
+        row_sums_kernel<<<(unsigned)(grid < 1 ? 1 : grid), 256, 0, stream>>>(static_cast<const int8_t*>(p->a), p->a_ld, p->trans_a ? 1 : 0, p->m, p->k,
+                                                                           a.groups, 256, rs);
+        note_launch("row_sums");
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int32_t)e;
+        return launch_pair_pb<ptx::MmaKind::kI8, 4, 128, true>(ma, mb, a, stream);
+    }
     if (pair_pb) {
         if (pb_bn == 256)
             return a.is_int ? launch_pair_pb<ptx::MmaKind::kI8, 8, 256>(ma, mb, a, stream)

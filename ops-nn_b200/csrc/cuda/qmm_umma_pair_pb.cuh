@@ -51,11 +51,19 @@ __device__ __forceinline__ bool pb_wait(uint32_t bar_addr, uint32_t parity, vola
 template <int EW, int BN>
 constexpr int pair_pb_threads() { return (EW + (BN == 256 ? 4 : 2)) * 32; }
 
-template <ptx::MmaKind kKind, int EW, int BN>
+// kAsym: INT4 x INT4 asymmetric per-group (quant_batch_matmul_v4_pertoken_pergroup.h; golden qbmmv4_kernel_golden.py:328-395), both
+// operands widened to INT8 beforehand. An accumulation group is two k-blocks (256 of k); per group and element
+// tot += (part - rowsum(x1 over the group)[m] * x2Offset[g, n]) * x2Scale[g, n], four separately rounded fp32 operations as in
+// the golden, and at the end out = tot * x1Scale[m]. x2Offset / x2Scale of the tile's columns are staged in shared memory one
+// group ahead (three buffers, one named barrier per group whose reduced predicate also carries the abort flag, so that the
+// epilogue warps can only leave together).
+template <ptx::MmaKind kKind, int EW, int BN, bool kAsym = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_pb_threads<EW, BN>(), 1)
 qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaArgs a)
 {
     static_assert(BN == 128 || (BN == 256 && EW == 8), "256-column tiles keep 128 sums per thread: eight epilogue warps");
+    static_assert(!kAsym || (BN == 128 && EW == 4 && kKind == ptx::MmaKind::kI8), "the asymmetric per-group epilogue: int8, 128 columns, four warps");
+    __shared__ float s_cols[kAsym ? 3 * 2 * BN : 1];  // kAsym: [buffer][offset | scale][column]
     constexpr int NBUF = 512 / BN;              // accumulator buffers in the 512 TMEM columns
     constexpr int kCols = BN * 4 / EW;          // accumulator columns per epilogue thread
     constexpr uint32_t kBHalf = (BN / 2) * BK;  // this CTA's half of the B tile
@@ -166,8 +174,10 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             OPSNN_PB_T(d_start);
             for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
                 for (int kb = 0; kb < kblocks; ++kb) {
+                    // kAsym: k-blocks 2g and 2g + 1 accumulate into one buffer; otherwise every k-block is its own group
+                    const bool first = !kAsym || (kb & 1) == 0, last = !kAsym || (kb & 1) == 1 || kb == kblocks - 1;
                     OPSNN_PB_T(d_t0);
-                    if (!pb_wait<BN == 256>(tempty0 + 8u * buf, bpar ^ 1u, abort_flag)) {
+                    if (first && !pb_wait<BN == 256>(tempty0 + 8u * buf, bpar ^ 1u, abort_flag)) {
                         report(abort_flag, (2u << 8) | 1u);
                         ok = false;
                         break;
@@ -187,16 +197,17 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                         const uint32_t al = a_lo + stage_off, bl = b_lo + stage_off;
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            ptx::umma_pair<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * b_k1), idesc, k == 0 ? 0u : 1u);
+                            ptx::umma_pair<kKind>(d, a_hi | (uint64_t)(al + k * a_k1), b_hi | (uint64_t)(bl + k * b_k1), idesc,
+                                                  (k == 0 && first) ? 0u : 1u);
                         ptx::umma_commit_pair(empty0 + 8u * s, (uint16_t)3);
-                        ptx::umma_commit_pair(tfull0 + 8u * buf, (uint16_t)3);
+                        if (last) ptx::umma_commit_pair(tfull0 + 8u * buf, (uint16_t)3);
                     }
                     __syncwarp();
                     if (++s == stages) {
                         s = 0;
                         par ^= 1u;
                     }
-                    if (++buf == NBUF) {
+                    if (last && ++buf == NBUF) {
                         buf = 0;
                         bpar ^= 1u;
                     }
@@ -234,85 +245,170 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             float acc[kCols];
 #pragma unroll
             for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
-            const float* s1 = reinterpret_cast<const float*>(a.scale_a) + b * a.sa_bs;
-            const float* s2 = reinterpret_cast<const float*>(a.scale_b) + b * a.sb_bs;
-            const int64_t mg = (row_ok ? row : 0) / a.group_m;
-            const int64_t n_mg = (a.m + a.group_m - 1) / a.group_m, n_ng = (a.n + 127) / 128;
-            const int64_t ng = min(colbase / 128, n_ng - 1);
-            auto load_s1 = [&](int kb) {
-                kb = min(kb, a.kblocks - 1);
-                return a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
-            };
-            auto load_s2 = [&](int kb) {
-                kb = min(kb, a.kblocks - 1);
-                return a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
-            };
-            float s1_next[4], s2_next[4];  // raw scales of the next four k-blocks; multiplied when their turn comes
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                s1_next[j] = load_s1(j);
-                s2_next[j] = load_s2(j);
-            }
-            for (int kb0 = 0; kb0 < a.kblocks && ok; kb0 += 4) {
-                float sc_cur[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) sc_cur[j] = __fmul_rn(s1_next[j], s2_next[j]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    s1_next[j] = load_s1(kb0 + 4 + j);
-                    s2_next[j] = load_s2(kb0 + 4 + j);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (kb0 + j >= a.kblocks) break;
-                    const float sc = sc_cur[j];
-                    OPSNN_PB_T(d_t2);
-                    if (!pb_wait<BN == 256>(tfull0 + 8u * buf, bpar, abort_flag)) {
-                        report(abort_flag, (3u << 8) | 2u);
+            if constexpr (kAsym) {
+                const int groups = a.groups;
+                const float* rsp = a.row_sums + (row_ok ? row : 0) * (int64_t)groups;
+                const __half* offp = reinterpret_cast<const __half*>(a.b_offset);
+                const float* scp = reinterpret_cast<const float*>(a.scale_b);
+                const int tcol = quad * 32 + lane;  // the column of the tile whose offset and scale this thread stages
+                const int64_t gcol = n0 + tcol;
+                auto stage_cols = [&](int g) {
+                    float o = 0.f, sc = 0.f;
+                    if (g < groups && gcol < a.n) {
+                        o = __half2float(offp[(int64_t)g * a.n + gcol]);
+                        sc = __ldg(scp + (int64_t)g * a.n + gcol);
+                    }
+                    float* dst = s_cols + (g % 3) * 2 * BN;
+                    dst[tcol] = o;
+                    dst[BN + tcol] = sc;
+                };
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's readers of the column buffers are done
+                stage_cols(0);
+                float rs_next = __ldg(rsp);
+                for (int g = 0; g < groups; ++g) {
+                    const float rsg = rs_next;
+                    if (g + 1 < groups) rs_next = __ldg(rsp + g + 1);
+                    stage_cols(g + 1);  // buffer (g + 1) % 3: last read in group g - 2, which every warp has left (barrier of g - 1)
+                    const bool arrived = pb_wait<false>(tfull0 + 8u * buf, bpar, abort_flag);
+                    if (!arrived) report(abort_flag, (3u << 8) | 2u);
+                    // One barrier per group: group g's columns are visible to all four warps, and its reduced predicate tells every
+                    // warp the same thing about a give-up anywhere in the CTA - they can only leave together.
+                    const int bad = (!arrived || *abort_flag != 0u) ? 1 : 0;
+                    int any_bad;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.s32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(any_bad)
+                                 : "r"(bad)
+                                 : "memory");
+                    if (any_bad != 0) {
                         ok = false;
                         break;
                     }
-                    OPSNN_PB_ADD(d_tfull, d_t2);
                     ptx::tc_fence_after();
-#if defined(OPSNN_PB_EXPERIMENT) && OPSNN_PB_EXPERIMENT == 1
-                    // diagnostic build: the buffer is released unread (main loop alone)
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
-                    if (++buf == NBUF) {
-                        buf = 0;
-                        bpar ^= 1u;
-                    }
-                    acc[0] += sc;
-                    continue;
-#endif
-#ifndef OPSNN_PB256_W
-#define OPSNN_PB256_W 16
-#endif
-                    constexpr int W = BN == 256 ? OPSNN_PB256_W : 16;  // staging registers per TMEM load (two sets in flight)
+                    const float* cur = s_cols + (g % 3) * 2 * BN;
                     const uint32_t t0 = tmem_base + lane_addr + buf * BN;
-                    uint32_t va[W], vb[W];
-                    ptx::tmem_ld_n(t0, va);
+                    // (part - rowsum * offset) * scale, then the running sum: four roundings, none fused, as in the golden
+                    auto fold = [&](const uint32_t(&v)[16], int c) {
 #pragma unroll
-                    for (int c = 0; c < kCols; c += 2 * W) {
-                        ptx::tmem_ld_wait();
-                        ptx::tmem_ld_n(t0 + c + W, vb);
+                        for (int i = 0; i < 16; i += 4) {
+                            const float4 o4 = *reinterpret_cast<const float4*>(cur + c + i);
+                            const float4 s4 = *reinterpret_cast<const float4*>(cur + BN + c + i);
+                            const float oo[4] = {o4.x, o4.y, o4.z, o4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-                        for (int i = 0; i < W; ++i) acc[c + i] = promote<kKind>(va[i], sc, acc[c + i]);
+                            for (int j = 0; j < 4; ++j) {
+                                const float f = __fsub_rn(__uint_as_float(v[i + j] + 0x4B400000u), 12582912.f);  // exact int -> float, |part| < 2^22
+                                const float w = __fmul_rn(__fsub_rn(f, __fmul_rn(rsg, oo[j])), ss[j]);
+                                acc[c + i + j] = __fadd_rn(acc[c + i + j], w);
+                            }
+                        }
+                    };
+                    uint32_t va[16], vb[16];
+                    ptx::tmem_ld16(t0, va);
+#pragma unroll
+                    for (int c = 0; c < kCols; c += 32) {
                         ptx::tmem_ld_wait();
-                        if (c + 2 * W < kCols) {
-                            ptx::tmem_ld_n(t0 + c + 2 * W, va);
+                        ptx::tmem_ld16(t0 + c + 16, vb);
+                        fold(va, c);
+                        ptx::tmem_ld_wait();
+                        if (c + 32 < kCols) {
+                            ptx::tmem_ld16(t0 + c + 32, va);
                         } else {
                             ptx::tc_fence_before();
                             __syncwarp();
                             if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
                         }
-#pragma unroll
-                        for (int i = 0; i < W; ++i) acc[c + W + i] = promote<kKind>(vb[i], sc, acc[c + W + i]);
+                        fold(vb, c + 16);
                     }
                     if (++buf == NBUF) {
                         buf = 0;
                         bpar ^= 1u;
+                    }
+                }
+                if (row_ok) {  // out = tot * x1Scale[m]
+                    const float sa = __ldg(reinterpret_cast<const float*>(a.scale_a) + row);
+#pragma unroll
+                    for (int i = 0; i < kCols; ++i) acc[i] = __fmul_rn(acc[i], sa);
+                }
+            } else {
+                const float* s1 = reinterpret_cast<const float*>(a.scale_a) + b * a.sa_bs;
+                const float* s2 = reinterpret_cast<const float*>(a.scale_b) + b * a.sb_bs;
+                const int64_t mg = (row_ok ? row : 0) / a.group_m;
+                const int64_t n_mg = (a.m + a.group_m - 1) / a.group_m, n_ng = (a.n + 127) / 128;
+                const int64_t ng = min(colbase / 128, n_ng - 1);
+                auto load_s1 = [&](int kb) {
+                    kb = min(kb, a.kblocks - 1);
+                    return a.trans_a ? __ldg(s1 + kb * n_mg + mg) : __ldg(s1 + mg * a.kblocks + kb);
+                };
+                auto load_s2 = [&](int kb) {
+                    kb = min(kb, a.kblocks - 1);
+                    return a.trans_b ? __ldg(s2 + ng * a.kblocks + kb) : __ldg(s2 + kb * n_ng + ng);
+                };
+                float s1_next[4], s2_next[4];  // raw scales of the next four k-blocks; multiplied when their turn comes
+    #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s1_next[j] = load_s1(j);
+                    s2_next[j] = load_s2(j);
+                }
+                for (int kb0 = 0; kb0 < a.kblocks && ok; kb0 += 4) {
+                    float sc_cur[4];
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) sc_cur[j] = __fmul_rn(s1_next[j], s2_next[j]);
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        s1_next[j] = load_s1(kb0 + 4 + j);
+                        s2_next[j] = load_s2(kb0 + 4 + j);
+                    }
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (kb0 + j >= a.kblocks) break;
+                        const float sc = sc_cur[j];
+                        OPSNN_PB_T(d_t2);
+                        if (!pb_wait<BN == 256>(tfull0 + 8u * buf, bpar, abort_flag)) {
+                            report(abort_flag, (3u << 8) | 2u);
+                            ok = false;
+                            break;
+                        }
+                        OPSNN_PB_ADD(d_tfull, d_t2);
+                        ptx::tc_fence_after();
+    #if defined(OPSNN_PB_EXPERIMENT) && OPSNN_PB_EXPERIMENT == 1
+                        // diagnostic build: the buffer is released unread (main loop alone)
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
+                        if (++buf == NBUF) {
+                            buf = 0;
+                            bpar ^= 1u;
+                        }
+                        acc[0] += sc;
+                        continue;
+    #endif
+    #ifndef OPSNN_PB256_W
+    #define OPSNN_PB256_W 16
+    #endif
+                        constexpr int W = BN == 256 ? OPSNN_PB256_W : 16;  // staging registers per TMEM load (two sets in flight)
+                        const uint32_t t0 = tmem_base + lane_addr + buf * BN;
+                        uint32_t va[W], vb[W];
+                        ptx::tmem_ld_n(t0, va);
+    #pragma unroll
+                        for (int c = 0; c < kCols; c += 2 * W) {
+                            ptx::tmem_ld_wait();
+                            ptx::tmem_ld_n(t0 + c + W, vb);
+    #pragma unroll
+                            for (int i = 0; i < W; ++i) acc[c + i] = promote<kKind>(va[i], sc, acc[c + i]);
+                            ptx::tmem_ld_wait();
+                            if (c + 2 * W < kCols) {
+                                ptx::tmem_ld_n(t0 + c + 2 * W, va);
+                            } else {
+                                ptx::tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive_cluster(lead_tempty0 + 8u * buf);
+                            }
+    #pragma unroll
+                            for (int i = 0; i < W; ++i) acc[c + W + i] = promote<kKind>(vb[i], sc, acc[c + W + i]);
+                        }
+                        if (++buf == NBUF) {
+                            buf = 0;
+                            bpar ^= 1u;
+                        }
                     }
                 }
             }
@@ -362,24 +458,46 @@ qmm_umma_pair_pb_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
-template <ptx::MmaKind KIND, int EW, int BN = 128>
+template <ptx::MmaKind KIND, int EW, int BN = 128, bool ASYM = false>
 int32_t launch_pair_pb(const CUtensorMap& ma, const CUtensorMap& mb, UmmaArgs& a, cudaStream_t stream)
 {
     constexpr int kStage = kATile + (BN / 2) * BK;
-    int stages = (227 * 1024 - 2048) / kStage;
+    constexpr int kDynMax = 227 * 1024 - (ASYM ? 4096 : 0);  // the asymmetric epilogue keeps 3 KB of static shared memory for its column buffers
+    int stages = (kDynMax - 2048) / kStage;
     if (stages > 8) stages = 8;
     if (stages > a.kblocks + 1) stages = a.kblocks + 1 > 2 ? a.kblocks + 1 : 2;
     a.stages = stages;
     const size_t smem = (size_t)stages * kStage + 1024 + 256;
-    auto kern = qmm_umma_pair_pb_kernel<KIND, EW, BN>;
+    auto kern = qmm_umma_pair_pb_kernel<KIND, EW, BN, ASYM>;
     static std::atomic<uint64_t> configured{0};
-    if (once_per_device(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess)
+    if (once_per_device(configured, [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynMax); }) != cudaSuccess)
         return (int32_t)cudaGetLastError();
     int64_t pairs = sm_count() / 2;
     if (a.num_tiles < pairs) pairs = a.num_tiles;
     kern<<<(unsigned)(2 * pairs), pair_pb_threads<EW, BN>(), smem, stream>>>(ma, mb, a);
-    note_launch("qmm_umma_pair_perblock");
+    note_launch(ASYM ? "qmm_umma_pair_pergroup_asym" : "qmm_umma_pair_perblock");
     return (int32_t)cudaGetLastError();
+}
+
+// Sums of x1's rows over each k-group, as floats (exact: at most 256 values of magnitude <= 128), for the asymmetric per-group
+// epilogue. One thread per (row, group); x1 is the widened INT8 operand, stored (m,k) or, transposed, (k,m).
+__global__ void row_sums_kernel(const int8_t* __restrict__ x1, int64_t ld, int trans, int64_t m, int64_t k, int32_t groups, int32_t group_k,
+                                float* __restrict__ out)
+{
+    const int64_t total = m * groups;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        // transposed storage: consecutive threads take consecutive rows (contiguous in memory); else consecutive groups of one row
+        const int64_t row = trans ? i % m : i / groups;
+        const int g = (int)(trans ? i / m : i % groups);
+        const int64_t k0 = (int64_t)g * group_k, k1 = min(k, k0 + group_k);
+        int sum = 0;
+        if (trans) {
+            for (int64_t kk = k0; kk < k1; ++kk) sum += x1[kk * ld + row];
+        } else {
+            for (int64_t kk = k0; kk < k1; ++kk) sum += x1[row * ld + kk];
+        }
+        out[row * groups + g] = (float)sum;
+    }
 }
 
 // Pair tiles for per-block problems: worthwhile once there are enough 256 x 128 tiles to fill the pairs.

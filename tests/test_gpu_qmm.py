@@ -103,3 +103,51 @@ def test_phase2_rejects_small_workspace_and_reused_executor(aclnn):
     assert L.aclnnQuantMatmulV5(None, 0, None, None) == aclnn.ACLNN_ERR_PARAM_NULLPTR
     assert L.aclnnQuantMatmulV5(None, ctypes.c_uint64(ws), ex, None) == 0
     torch.cuda.synchronize()
+
+
+ASYM_CASES = [
+    # m, k, n, transpose_x1, transpose_x2, out dtype
+    # (the reference takes this mode with x1 (m,k), x2 stored (n,k), k a multiple of 1024 and n of 256 only: quant_matmul_checker.cpp:354-395)
+    (512, 1024, 768, False, True, "bfloat16"),
+    (300, 2048, 512, False, True, "float16"),     # ragged m
+    (64, 1024, 256, False, True, "bfloat16"),     # less than one tile of rows
+    (1000, 2048, 1280, False, True, "bfloat16"),  # several tiles per CTA pair
+]
+
+
+@pytest.mark.parametrize("case", ASYM_CASES, ids=[str(c) for c in ASYM_CASES])
+def test_int4_asymmetric_per_group_on_the_tensor_core(aclnn, case, monkeypatch):
+    """INT4 x INT4 with a per-group (256 of k) x2Scale and x2Offset and a per-token x1Scale (qbmmv4_kernel_golden.py:328-395):
+    operands widened to INT8, then the CTA-pair tensor-core kernel with two k-blocks per accumulation group and the golden's four
+    roundings per group in the epilogue. Bit-identical to the oracle and to the coverage kernel."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import desc, out_tensor, out_to_np
+
+    m, k, n, t1, t2, out_name = case
+    rng = np.random.default_rng(m * 7 + n)
+    groups = -(-k // 256)
+    x1 = rng.integers(-8, 8, (k, m) if t1 else (m, k)).astype(ml_dtypes.int4)
+    x2 = rng.integers(-8, 8, (n, k) if t2 else (k, n)).astype(ml_dtypes.int4)
+    s1 = rng.uniform(0.01, 0.1, (m, 1)).astype(np.float32)
+    s2 = rng.uniform(0.01, 0.1, (groups, n)).astype(np.float32)
+    off = rng.uniform(-4, 4, (groups, n)).astype(np.float16)
+    group = 256
+    want = qbmm_oracle.quant_matmul_v5(x1, x2, s1, s2, None, t1, t2, group, out_name, x2_offset=off)
+
+    def run():
+        out = out_tensor((m, n), out_name)
+        aclnn.quant_matmul_v5(desc(aclnn, x1), desc(aclnn, x2), desc(aclnn, s1), desc(aclnn, s2), aclnn.Tensor(out.shape, out_name, out), None,
+                              t1, t2, group, x2_offset=desc(aclnn, off))
+        torch.cuda.synchronize()
+        assert aclnn.lib().opsnn_qmm_umma_status(1) == 0
+        return out_to_np(out), aclnn.last_kernel_name()
+
+    got, name = run()
+    assert name == "qmm_umma_pair_pergroup_asym", name
+    bits = lambda a: a.view(np.uint16) if a.dtype.itemsize == 2 else a.view(np.uint32)  # noqa: E731
+    assert np.array_equal(bits(got), bits(want))
+    monkeypatch.setenv("OPSNN_QMM_ASYM_GENERIC", "1")
+    ref, ref_name = run()
+    assert ref_name != name and np.array_equal(bits(ref), bits(got))
