@@ -362,7 +362,7 @@ cudaError_t d8_configure_variant(int variant)
     });
 }
 
-cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const D8Args& ta, cudaStream_t stream)
+cudaError_t d8_launch_variant(int variant, int grid, int cluster_policy, const CUtensorMap& mw, const CUtensorMap& mx, const D8Args& ta, cudaStream_t stream)
 {
     const char* pe = getenv("OPSNN_WQ_PDL");
     cudaLaunchConfig_t cfg{};
@@ -370,7 +370,7 @@ cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, cons
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = k8Smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2]{};
+    cudaLaunchAttribute attr[3]{};
     unsigned na = 0;
     if (pe == nullptr || pe[0] != '0') {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -383,6 +383,11 @@ cudaError_t d8_launch_variant(int variant, int grid, const CUtensorMap& mw, cons
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
+        if (cluster_policy == 1 || cluster_policy == 2) {
+            attr[na].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+            attr[na].val.clusterSchedulingPolicyPreference = static_cast<cudaClusterSchedulingPolicy>(cluster_policy);
+            ++na;
+        }
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
@@ -449,6 +454,7 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     if (splits < 1) splits = 1;
     // narrow outputs: the k-splits of a strip as one cluster, summed over distributed shared memory; same rules as the int4 kernel
     a.cluster = 0;
+    int cluster_policy = 0;
     if (ce == nullptr || ce[0] != '0') {
         if (se != nullptr || (ce != nullptr && splits <= 16)) {
             a.cluster = (splits >= 2 && splits <= 16 && (ce != nullptr || a.strips <= k8ClusterMaxStrips)) ? 1 : 0;
@@ -457,6 +463,13 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
             if (s_pick >= 2) {
                 splits = s_pick;
                 a.cluster = 1;
+            }
+        } else if (a.strips > k8ClusterMaxStrips && splits >= 2 && splits <= 16) {
+            // wide outputs: clusters under the load-balancing policy when every strip's cluster is resident at once (see the int4 kernel)
+            if ((int64_t)max_active_clusters(d8_kernel(variant), kThreads, k8Smem, (int)splits, (int)cudaClusterSchedulingPolicyLoadBalancing) >=
+                a.strips) {
+                a.cluster = 1;
+                cluster_policy = (int)cudaClusterSchedulingPolicyLoadBalancing;
             }
         }
     }
@@ -474,7 +487,7 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     if (!d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows) ||
         !d8_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
-    const cudaError_t rc = d8_launch_variant(variant, (int)grid64, mw, mx, ta, stream);
+    const cudaError_t rc = d8_launch_variant(variant, (int)grid64, cluster_policy, mw, mx, ta, stream);
     note_launch("wqbmm_decode8");
     note_decode_plan(a.strips, a.splits, a.cluster);
     return (int32_t)rc;

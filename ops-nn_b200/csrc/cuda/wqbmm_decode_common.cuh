@@ -330,44 +330,49 @@ __device__ __forceinline__ void cluster_combine_and_store(const DecodeArgs& a, f
 
 }  // namespace
 
-// Largest cluster size S in [2, max_s] for which `clusters` clusters of S CTAs of `kernel` are all resident at once on the
-// current device, 0 when there is none. Answers are cached per (kernel, device, S).
-inline int pick_cluster_size(const void* kernel, int threads, int smem_bytes, int64_t clusters, int max_s)
+// How many clusters of s CTAs of `kernel` the current device keeps resident at once under a cluster scheduling policy
+// (cudaClusterSchedulingPolicy*: 0 default / 1 spread / 2 load balancing). Answers are cached per (kernel, device, s, policy).
+inline int max_active_clusters(const void* kernel, int threads, int smem_bytes, int s, int policy)
 {
     static std::mutex mu;
-    static std::map<std::tuple<const void*, int, int>, int> cache;
+    static std::map<std::tuple<const void*, int, int, int>, int> cache;
     int dev = 0;
     cudaGetDevice(&dev);
-    for (int s = max_s; s >= 2; --s) {
-        int active = -1;
-        {
-            std::lock_guard<std::mutex> lock(mu);
-            auto it = cache.find(std::make_tuple(kernel, dev, s));
-            if (it != cache.end()) active = it->second;
-        }
-        if (active < 0) {
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = dim3((unsigned)(s * 64), 1, 1);
-            cfg.blockDim = dim3((unsigned)threads, 1, 1);
-            cfg.dynamicSmemBytes = (size_t)smem_bytes;
-            cudaLaunchAttribute attr{};
-            attr.id = cudaLaunchAttributeClusterDimension;
-            attr.val.clusterDim.x = (unsigned)s;
-            attr.val.clusterDim.y = 1;
-            attr.val.clusterDim.z = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
-                cudaGetLastError();
-                n = 0;
-            }
-            active = n;
-            std::lock_guard<std::mutex> lock(mu);
-            cache[std::make_tuple(kernel, dev, s)] = active;
-        }
-        if ((int64_t)active >= clusters) return s;
+    const auto key = std::make_tuple(kernel, dev, s, policy);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) return it->second;
     }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(s * 64), 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute attr[2]{};
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)s;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attr[1].val.clusterSchedulingPolicyPreference = static_cast<cudaClusterSchedulingPolicy>(policy);
+    cfg.attrs = attr;
+    cfg.numAttrs = policy != 0 ? 2 : 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    cache[key] = n;
+    return n;
+}
+
+// Largest cluster size S in [2, max_s] for which `clusters` clusters of S CTAs of `kernel` are all resident at once on the
+// current device (default scheduling policy), 0 when there is none.
+inline int pick_cluster_size(const void* kernel, int threads, int smem_bytes, int64_t clusters, int max_s)
+{
+    for (int s = max_s; s >= 2; --s)
+        if ((int64_t)max_active_clusters(kernel, threads, smem_bytes, s, 0) >= clusters) return s;
     return 0;
 }
 

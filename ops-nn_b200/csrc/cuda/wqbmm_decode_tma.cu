@@ -19,6 +19,7 @@
 // The integer pipe (logic and shifts: 28 instructions per k-step), the 16-bit-pair arithmetic (kExact: 48 per k-step) and
 // mma.sync (8 or 9 per k-step) each run at one warp instruction per two clocks per SM sub-partition on this part, so the
 // main loop is written to add as little as possible to any of them.
+#include <cstdio>
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "wqbmm_decode_common.cuh"
@@ -497,7 +498,7 @@ cudaError_t configure_variant(int variant)
     });
 }
 
-cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
+cudaError_t launch_variant(int variant, int grid, int cluster_policy, const CUtensorMap& mw, const CUtensorMap& mx, const TmaArgs& ta, cudaStream_t stream)
 {
     // launched as a programmatic dependent of whatever precedes it in the stream (OPSNN_WQ_PDL=0: an ordinary launch)
     const char* pe = getenv("OPSNN_WQ_PDL");
@@ -506,7 +507,7 @@ cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const C
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = kTmaSmem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2]{};
+    cudaLaunchAttribute attr[3]{};
     unsigned na = 0;
     if (pe == nullptr || pe[0] != '0') {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -519,6 +520,12 @@ cudaError_t launch_variant(int variant, int grid, const CUtensorMap& mw, const C
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
+        if (const char* pol = getenv("OPSNN_WQ_CLUSTER_POLICY")) cluster_policy = atoi(pol);  // experiments: 1 spread, 2 load balancing
+        if (cluster_policy == 1 || cluster_policy == 2) {
+            attr[na].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+            attr[na].val.clusterSchedulingPolicyPreference = static_cast<cudaClusterSchedulingPolicy>(cluster_policy);
+            ++na;
+        }
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
@@ -600,6 +607,7 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     // Wide outputs keep the workspace combination (measured equal or better there). OPSNN_WQ_DECODE_CLUSTER=0 / 1 forbids /
     // forces the cluster form; OPSNN_WQ_DECODE_SPLITS fixes the split count.
     a.cluster = 0;
+    int cluster_policy = 0;
     if (ce == nullptr || ce[0] != '0') {
         if (se != nullptr || (ce != nullptr && splits <= 16)) {
             a.cluster = (splits >= 2 && splits <= 16 && (ce != nullptr || a.strips <= kClusterMaxStrips)) ? 1 : 0;
@@ -609,6 +617,17 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
             if (s_pick >= 2) {
                 splits = s_pick;
                 a.cluster = 1;
+            }
+        } else if (a.strips > kClusterMaxStrips && splits >= 2 && splits <= 16 && getenv("OPSNN_WQ_CLUSTER_POLICY") == nullptr) {
+            // Wide outputs, two CTAs per SM: a cluster per strip pays when the hardware may pack the clusters' CTAs two to an SM
+            // (the load-balancing scheduling policy; with the default, spreading one, a second wave forms: 74 us on the
+            // benchmark shape) and every strip's cluster is resident at once. 56 strips x 5: 53.5 -> 49.8 us; 64 x 4: 61.7 -> 58.9;
+            // cluster sizes that do not pack (6, 7, 9 CTAs: 47.6 -> 67 us) are what the occupancy question filters out.
+            const int act = max_active_clusters(tma_kernel(variant), kThreads, kTmaSmem, (int)splits, (int)cudaClusterSchedulingPolicyLoadBalancing);
+            if (getenv("OPSNN_DEBUG_PLAN")) fprintf(stderr, "[opsnn] decode plan: strips %lld splits %lld active clusters (load balancing) %d\n", (long long)a.strips, (long long)splits, act);
+            if ((int64_t)act >= a.strips) {
+                a.cluster = 1;
+                cluster_policy = (int)cudaClusterSchedulingPolicyLoadBalancing;
             }
         }
     }
@@ -630,7 +649,7 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
         !make_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
 
-    const cudaError_t rc = launch_variant(variant, (int)grid64, mw, mx, ta, stream);
+    const cudaError_t rc = launch_variant(variant, (int)grid64, cluster_policy, mw, mx, ta, stream);
     note_launch(exact ? "wqbmm_decode" : "wqbmm_decode_fast");
     note_decode_plan(a.strips, a.splits, a.cluster);
     return (int32_t)rc;

@@ -310,8 +310,9 @@ def test_cluster_combine_equals_workspace_combine(aclnn, monkeypatch, case):
 
 def test_narrow_output_is_planned_as_clusters(aclnn):
     """A 1/8 column shard of the benchmark's decode shape (what one of eight GPUs gets): the k-ranges of a strip run as one
-    thread-block cluster of as many CTAs as the device keeps resident for all seven strips at once, and the full width keeps
-    the workspace combination."""
+    thread-block cluster of as many CTAs as the device keeps resident for all seven strips at once. The full width (56 strips
+    of 5 k-ranges, two CTAs per SM) runs as clusters too when the device keeps all 56 resident under the load-balancing
+    policy, which a B200 does; a width whose cluster size does not pack (48 strips of 6) keeps the workspace combination."""
     import torch
 
     from gpu_util import DEV
@@ -331,7 +332,9 @@ def test_narrow_output_is_planned_as_clusters(aclnn):
     strips, splits, cluster = plan(3584)
     assert strips == 7 and (cluster & 1) == 1 and 2 <= splits <= 16
     strips, splits, cluster = plan(28672)
-    assert strips == 56 and cluster == 0 and splits == 5
+    assert strips == 56 and splits == 5 and cluster == 1
+    strips, splits, cluster = plan(24576)
+    assert strips == 48 and splits == 6 and cluster == 0
 
 
 W8_CASES = [
