@@ -46,6 +46,31 @@ OPSNN_SHARD_API int32_t opsnn_gather_columns(void* comm, const void* y_local, in
  * when y_local already is this rank's slot of y_full. */
 OPSNN_SHARD_API int32_t opsnn_gather_batch(void* comm, const void* y_local, int64_t batch_total, uint64_t bytes_per_batch, void* y_full, void* stream);
 
+/* ---- the gather folded into the decode kernels' epilogue (column shards, at most 8 ranks of one node) ----------------------
+ * For the small outputs of the decode regime (m <= 16) a separate all-gather costs more than the matmul (tens of microseconds of
+ * launch and NCCL latency for ~100 KB per rank). Instead every rank holds the full (m, n_total) output in memory that all ranks
+ * have mapped (CUDA IPC), and the streaming decode kernels store every element of their shard straight into every rank's copy -
+ * plain stores over NVLink from the epilogue, no TMA from or multicast into peer memory. opsnn_comm_arrive_and_wait then
+ * tells the other ranks that this rank's stores are done and waits until theirs are: one single-warp kernel, a release store per
+ * peer and a bounded poll per peer (about a second; a wait that runs out sets the word opsnn_comm_status reads, the kernel
+ * returns, nothing hangs).
+ *
+ *   opsnn_comm_symmetric_alloc   collective; `bytes` of zeroed device memory on every rank; peers (optional, [world]) receives
+ *                                every rank's block as mapped into this process, peers[rank] == *local.
+ *   opsnn_comm_bind_columns      registers y_local (this rank's (m, width) shard, the y of the calls to come) as a column shard of
+ *                                y_full_local (a symmetric allocation, (m, n_total) row-major, same element type). From then on
+ *                                aclnnWeightQuantBatchMatmulV2 / V3 / opsnn_wqbmm_launch calls whose y is y_local and that run on a
+ *                                streaming decode kernel write y_local and every rank's full output; a bound call that would run
+ *                                on another kernel is refused (cudaErrorNotSupported) rather than silently left ungathered.
+ *   opsnn_comm_arrive_and_wait   collective on `stream`, after the bound call: afterwards every rank's full output is complete.
+ * No counterpart in the reference (it has no multi-device code for these operators). */
+OPSNN_SHARD_API int32_t opsnn_comm_symmetric_alloc(void* comm, uint64_t bytes, void** local, void** peers);
+OPSNN_SHARD_API int32_t opsnn_comm_symmetric_free(void* comm, void* local);
+OPSNN_SHARD_API int32_t opsnn_comm_bind_columns(void* comm, const void* y_local, const void* y_full_local, int64_t n_total, int64_t multiple);
+OPSNN_SHARD_API int32_t opsnn_comm_unbind(const void* y_local);
+OPSNN_SHARD_API int32_t opsnn_comm_arrive_and_wait(void* comm, void* stream);
+OPSNN_SHARD_API uint32_t opsnn_comm_status(void* comm, int32_t reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -127,6 +127,16 @@ def lib():
     L.opsnn_gather_columns_workspace.argtypes = [I32, I64, I64, I64, I32]
     L.opsnn_gather_columns.argtypes = [VP, VP, I64, I64, I64, I64, I32, VP, VP, U64, VP]
     L.opsnn_gather_batch.argtypes = [VP, VP, I64, U64, VP, VP]
+    L.opsnn_comm_symmetric_alloc.argtypes = [VP, U64, POINTER(VP), POINTER(VP)]
+    L.opsnn_comm_symmetric_free.argtypes = [VP, VP]
+    L.opsnn_comm_bind_columns.argtypes = [VP, VP, VP, I64, I64]
+    L.opsnn_comm_unbind.argtypes = [VP]
+    L.opsnn_comm_arrive_and_wait.argtypes = [VP, VP]
+    L.opsnn_comm_status.argtypes = [VP, I32]
+    L.opsnn_comm_status.restype = ctypes.c_uint32
+    for name in ("opsnn_comm_symmetric_alloc", "opsnn_comm_symmetric_free", "opsnn_comm_bind_columns", "opsnn_comm_unbind",
+                 "opsnn_comm_arrive_and_wait"):
+        getattr(L, name).restype = c_int32
     for name in ("opsnn_comm_unique_id", "opsnn_comm_init", "opsnn_comm_destroy", "opsnn_gather_columns", "opsnn_gather_batch"):
         getattr(L, name).restype = c_int32
     _lib = L
@@ -479,6 +489,48 @@ class Comm:
         if rc != 0:
             raise RuntimeError("opsnn_gather_batch failed (%d): %s" % (rc, last_error()))
         return out
+
+    # ---- the gather folded into the decode kernels' epilogue (opsnn_comm_symmetric_alloc / bind_columns / arrive_and_wait) ----
+
+    def symmetric_empty(self, shape, dtype):
+        """Collective. A zeroed tensor of `shape` on every rank, in memory every rank has mapped: a torch view of this rank's block."""
+        import torch
+
+        class _Raw:  # zero-copy view of library-owned device memory
+            def __init__(self, ptr, nbytes):
+                self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        local = c_void_p(0)
+        rc = lib().opsnn_comm_symmetric_alloc(self.handle, c_uint64(max(nbytes, 16)), byref(local), None)
+        if rc != 0:
+            raise RuntimeError("opsnn_comm_symmetric_alloc failed (%d): %s" % (rc, last_error()))
+        with torch.cuda.device(self.device):
+            flat = torch.as_tensor(_Raw(local.value, nbytes), device=self.device)
+        return flat.view(dtype).view(*[int(d) for d in shape])
+
+    def bind_columns(self, y_local, y_full, multiple=8):
+        """From now on decode calls whose output is `y_local` (this rank's column shard) also store it into every rank's `y_full`
+        (from symmetric_empty); follow each such call with arrive_and_wait()."""
+        rc = lib().opsnn_comm_bind_columns(self.handle, c_void_p(y_local.data_ptr()), c_void_p(y_full.data_ptr()), int(y_full.shape[-1]), int(multiple))
+        if rc != 0:
+            raise RuntimeError("opsnn_comm_bind_columns failed (%d): %s" % (rc, last_error()))
+
+    def unbind(self, y_local):
+        lib().opsnn_comm_unbind(c_void_p(y_local.data_ptr()))
+
+    def arrive_and_wait(self):
+        """Collective, on the current stream: afterwards every rank's stores into the bound outputs are complete."""
+        rc = lib().opsnn_comm_arrive_and_wait(self.handle, _stream())
+        if rc != 0:
+            raise RuntimeError("opsnn_comm_arrive_and_wait failed (%d): %s" % (rc, last_error()))
+
+    def status(self, reset=True):
+        """0, or 1 when a wait for the other ranks ran out (synchronises the device)."""
+        return int(lib().opsnn_comm_status(self.handle, 1 if reset else 0))
 
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:

@@ -17,7 +17,19 @@ namespace opsnn {
 // Host: count a launch and remember which kernel family ran (read back through opsnn_launch_count /
 // opsnn_last_kernel_name).
 void note_launch(const char* name, uint64_t n = 1);
-void note_decode_plan(int64_t strips, int64_t splits, int32_t cluster);  // what the last streaming decode launch of this thread used
+void note_decode_plan(int64_t strips, int64_t splits, int32_t cluster);
+
+// A column shard of an output that every rank of a communicator holds in full, in memory the ranks mapped into one another
+// (opsnn_comm_bind_columns): the decode kernels then also store the shard's elements straight into every rank's full output -
+// plain peer stores over NVLink, the all-gather folded into the epilogue.
+constexpr int kMaxPeers = 8;
+struct PeerBinding {
+    void* full[kMaxPeers];  // every rank's full output (this rank's own included), as mapped into this process
+    int32_t count;          // ranks; 0: not bound
+    int64_t ld;             // elements per row of the full output
+    int64_t col0;           // first column of this rank's shard in it
+};
+bool lookup_peer_binding(const void* y_local, PeerBinding* out);  // what the last streaming decode launch of this thread used
 
 // Host: set-up that is a property of the (function, device) pair - the dynamic shared-memory limit of a kernel, occupancy - done the
 // first time a launcher runs with each device current. `done` holds one bit per device ordinal. Two threads racing on the same first

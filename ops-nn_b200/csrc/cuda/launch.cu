@@ -10,6 +10,8 @@
 
 namespace opsnn {
 
+void set_err(const char* fmt, ...);
+
 static std::atomic<uint64_t> g_launches{0};
 static thread_local const char* g_last_kernel = "";
 
@@ -269,6 +271,24 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
         return opsnn_wqbmm_launch(&nd, kernel_choice, stream);
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_AUTO) kernel_choice = opsnn_wqbmm_select_kernel(p);
+    {
+        // An output bound to a communicator (opsnn_comm_bind_columns) is written into every rank's full copy by the bulk-copy
+        // decode kernels only; a call that would run elsewhere must not silently skip that.
+        PeerBinding pb;
+        if (lookup_peer_binding(p->y, &pb)) {
+            const char* e = getenv("OPSNN_WQ_DECODE_PATH");
+            const bool ring_only = e != nullptr && e[0] == 'r';
+            const bool tma4 = (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) && p->w_dtype != ACL_INT8 &&
+                              p->m <= 16 && !ring_only && wqbmm_decode_fast_eligible(p) && wqbmm_decode_tma_eligible(p) &&
+                              getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr;
+            const bool tma8 = kernel_choice == OPSNN_WQ_KERNEL_DECODE && p->w_dtype == ACL_INT8 && wqbmm_decode8_eligible(p);
+            if (!tma4 && !tma8) {
+                set_err("opsnn_wqbmm_launch: y is bound to a communicator, but this call does not run on a streaming decode kernel that "
+                        "stores into the peers' outputs (m <= 16, int4 or int8 weight stored (k,n), aligned rows)");
+                return (int32_t)cudaErrorNotSupported;
+            }
+        }
+    }
     OpsnnWqbmmParams chunk;
     if (p->m > 16 && (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST)) {
         if (!decode_in_chunks(p, &chunk)) return (int32_t)cudaErrorInvalidValue;

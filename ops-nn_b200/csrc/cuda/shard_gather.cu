@@ -8,7 +8,9 @@
 // carries (the one a PyTorch host loaded, or the system one), so the library loads on machines without it.
 #include <dlfcn.h>
 
+#include <map>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "opsnn_b200_shard.h"
@@ -51,10 +53,25 @@ const NcclApi& nccl()
     return api;
 }
 
+// One symmetric allocation: this rank's memory and the other ranks' memory of the same size, mapped here through CUDA IPC.
+struct Symmetric {
+    void* local = nullptr;
+    uint64_t bytes = 0;
+    std::vector<void*> peers;  // [world]; peers[rank] == local
+};
+
 struct Comm {
     ncclComm_t nccl = nullptr;
     int world = 1, rank = 0;
+    std::vector<Symmetric> regions;
+    // cross-rank arrival flags (a symmetric region of its own, made on first use): flags[r] = the last epoch rank r announced here
+    Symmetric flags;
+    unsigned long long* epoch = nullptr;  // device counter of this rank's arrivals: advanced by the kernel itself, so a captured launch replays correctly
+    unsigned int* status = nullptr;       // device word: 0, or 1 when a wait for the other ranks ran out
 };
+
+std::mutex g_bind_mu;
+std::map<const void*, PeerBinding> g_bindings;
 
 int32_t nccl_fail(const char* what, int rc)
 {
@@ -101,10 +118,108 @@ __global__ void interleave_runs_kernel(const uint8_t* __restrict__ recv, uint8_t
     }
 }
 
+// Every rank writes its epoch into slot `rank` of every rank's flag array (release at system scope: the stores of the kernels
+// before it in the stream are performed by then), then waits, bounded, until every slot of its own array holds the epoch.
+struct FlagPeers {
+    unsigned long long* flags[kMaxPeers];
+};
+__global__ void arrive_and_wait_kernel(const __grid_constant__ FlagPeers peers, int world, int rank, unsigned long long* epoch_counter,
+                                       unsigned int limit, unsigned int* status)
+{
+    // Launched as a programmatic dependent of the kernel before it and a programmatic prerequisite of the one after: the next
+    // kernel may be placed at once, and this one reads and writes nothing before the previous kernel has completed (its stores,
+    // the peer stores included, are performed by then).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ unsigned long long s_epoch;
+    if (threadIdx.x == 0) s_epoch = ++(*epoch_counter);  // every rank makes the same number of calls: the counters agree
+    __syncthreads();
+    const unsigned long long epoch = s_epoch;
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(peers.flags[r] + rank), "l"(epoch) : "memory");
+    const unsigned long long* mine = peers.flags[rank] + r;
+    bool seen = false;
+    for (unsigned int i = 0; i < limit && !seen; ++i) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+        seen = v >= epoch;
+        if (!seen) __nanosleep(100);
+    }
+    if (!seen) atomicExch(status, 1u);
+}
+
 }  // namespace
+
+bool lookup_peer_binding(const void* y_local, PeerBinding* out)
+{
+    if (y_local == nullptr) return false;
+    std::lock_guard<std::mutex> lk(g_bind_mu);
+    if (g_bindings.empty()) return false;
+    auto it = g_bindings.find(y_local);
+    if (it == g_bindings.end()) return false;
+    *out = it->second;
+    return true;
+}
+
 }  // namespace opsnn
 
 using namespace opsnn;
+
+namespace {
+
+// Allocates `bytes` on every rank and maps every rank's block into this process (CUDA IPC; the handles travel through one
+// ncclAllGather). Collective: every rank of the communicator calls it with the same size.
+int32_t symmetric_alloc(Comm* c, uint64_t bytes, Symmetric* out)
+{
+    out->bytes = bytes;
+    out->peers.assign((size_t)c->world, nullptr);
+    cudaError_t rc = cudaMalloc(&out->local, bytes);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    cudaMemset(out->local, 0, bytes);
+    out->peers[(size_t)c->rank] = out->local;
+    if (c->world == 1) return 0;
+    cudaIpcMemHandle_t mine;
+    rc = cudaIpcGetMemHandle(&mine, out->local);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    uint8_t* dev = nullptr;
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    rc = cudaMalloc(&dev, hb * (size_t)(c->world + 1));
+    if (rc != cudaSuccess) return (int32_t)rc;
+    cudaMemcpy(dev, &mine, hb, cudaMemcpyHostToDevice);
+    const int nrc = nccl().AllGather(dev, dev + hb, hb, 0, c->nccl, (cudaStream_t)0);
+    if (nrc != 0) {
+        cudaFree(dev);
+        return nccl_fail("ncclAllGather", nrc);
+    }
+    rc = cudaStreamSynchronize((cudaStream_t)0);
+    std::vector<cudaIpcMemHandle_t> all((size_t)c->world);
+    if (rc == cudaSuccess) rc = cudaMemcpy(all.data(), dev + hb, hb * (size_t)c->world, cudaMemcpyDeviceToHost);
+    cudaFree(dev);
+    if (rc != cudaSuccess) return (int32_t)rc;
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) continue;
+        rc = cudaIpcOpenMemHandle(&out->peers[(size_t)r], all[(size_t)r], cudaIpcMemLazyEnablePeerAccess);
+        if (rc != cudaSuccess) {
+            set_err("opsnn_comm_symmetric_alloc: rank %d could not map rank %d's memory (CUDA error %d): the ranks must be processes of one node with peer access",
+                    c->rank, r, (int)rc);
+            return (int32_t)rc;
+        }
+    }
+    return 0;
+}
+
+void symmetric_release(Comm* c, Symmetric* sy)
+{
+    for (int r = 0; r < (int)sy->peers.size(); ++r)
+        if (r != c->rank && sy->peers[(size_t)r] != nullptr) cudaIpcCloseMemHandle(sy->peers[(size_t)r]);
+    if (sy->local != nullptr) cudaFree(sy->local);
+    sy->local = nullptr;
+    sy->peers.clear();
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -164,6 +279,21 @@ int32_t opsnn_comm_destroy(void* comm)
 {
     if (comm == nullptr) return 0;
     Comm* c = static_cast<Comm*>(comm);
+    cudaDeviceSynchronize();
+    {   // bindings into this communicator's symmetric memory go with it
+        std::lock_guard<std::mutex> lk(g_bind_mu);
+        for (auto it = g_bindings.begin(); it != g_bindings.end();) {
+            bool ours = false;
+            for (const Symmetric& sy : c->regions)
+                for (void* q : sy.peers) ours = ours || q == it->second.full[0];
+            it = ours ? g_bindings.erase(it) : std::next(it);
+        }
+    }
+    for (Symmetric& sy : c->regions) symmetric_release(c, &sy);
+    c->regions.clear();
+    if (c->flags.local != nullptr) symmetric_release(c, &c->flags);
+    if (c->status != nullptr) cudaFree(c->status);
+    if (c->epoch != nullptr) cudaFree(c->epoch);
     const int rc = c->nccl ? nccl().CommDestroy(c->nccl) : 0;
     delete c;
     return rc == 0 ? 0 : nccl_fail("ncclCommDestroy", rc);
@@ -263,6 +393,115 @@ int32_t opsnn_gather_batch(void* comm, const void* y_local, int64_t batch_total,
     // in place when the caller's shard already sits at its slot of y_full (NCCL's in-place rule), else from y_local
     const int nrc = nccl().AllGather(y_local, y_full, share, 0, c->nccl, static_cast<cudaStream_t>(stream));
     return nrc == 0 ? 0 : nccl_fail("ncclAllGather", nrc);
+}
+
+
+int32_t opsnn_comm_symmetric_alloc(void* comm, uint64_t bytes, void** local, void** peers)
+{
+    if (comm == nullptr || local == nullptr || bytes == 0) return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    if (c->world > kMaxPeers) {
+        set_err("opsnn_comm_symmetric_alloc: at most %d ranks", kMaxPeers);
+        return (int32_t)cudaErrorNotSupported;
+    }
+    Symmetric sy;
+    const int32_t rc = symmetric_alloc(c, bytes, &sy);
+    if (rc != 0) {
+        symmetric_release(c, &sy);
+        return rc;
+    }
+    *local = sy.local;
+    if (peers != nullptr)
+        for (int r = 0; r < c->world; ++r) peers[r] = sy.peers[(size_t)r];
+    c->regions.push_back(sy);
+    return 0;
+}
+
+int32_t opsnn_comm_symmetric_free(void* comm, void* local)
+{
+    if (comm == nullptr || local == nullptr) return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    for (size_t i = 0; i < c->regions.size(); ++i) {
+        if (c->regions[i].local != local) continue;
+        cudaDeviceSynchronize();
+        symmetric_release(c, &c->regions[i]);
+        c->regions.erase(c->regions.begin() + (long)i);
+        return 0;
+    }
+    return (int32_t)cudaErrorInvalidValue;
+}
+
+int32_t opsnn_comm_bind_columns(void* comm, const void* y_local, const void* y_full_local, int64_t n_total, int64_t multiple)
+{
+    if (comm == nullptr || y_local == nullptr || y_full_local == nullptr || n_total < 1 || multiple < 1) return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    const Symmetric* sy = nullptr;
+    for (const Symmetric& s : c->regions)
+        if (s.local == y_full_local) sy = &s;
+    if (sy == nullptr) {
+        set_err("opsnn_comm_bind_columns: y_full was not allocated by opsnn_comm_symmetric_alloc on this communicator");
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    PeerBinding b{};
+    b.count = c->world;
+    for (int r = 0; r < c->world; ++r) b.full[r] = sy->peers[(size_t)r];
+    b.ld = n_total;
+    int64_t begin = 0, end = 0;
+    opsnn_shard_range(n_total, c->world, c->rank, multiple, &begin, &end);
+    b.col0 = begin;
+    std::lock_guard<std::mutex> lk(g_bind_mu);
+    g_bindings[y_local] = b;
+    return 0;
+}
+
+int32_t opsnn_comm_unbind(const void* y_local)
+{
+    std::lock_guard<std::mutex> lk(g_bind_mu);
+    g_bindings.erase(y_local);
+    return 0;
+}
+
+int32_t opsnn_comm_arrive_and_wait(void* comm, void* stream)
+{
+    if (comm == nullptr) return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    if (c->world > kMaxPeers) return (int32_t)cudaErrorNotSupported;
+    if (c->flags.local == nullptr) {  // first use (collective, like every call of this function)
+        const int32_t rc = symmetric_alloc(c, 256 * sizeof(unsigned long long), &c->flags);
+        if (rc != 0) return rc;
+        cudaError_t e = cudaMalloc(&c->status, sizeof(unsigned int));
+        if (e == cudaSuccess) e = cudaMalloc(&c->epoch, sizeof(unsigned long long));
+        if (e != cudaSuccess) return (int32_t)e;
+        cudaMemset(c->status, 0, sizeof(unsigned int));
+        cudaMemset(c->epoch, 0, sizeof(unsigned long long));
+        cudaDeviceSynchronize();
+    }
+    FlagPeers fp{};
+    for (int r = 0; r < c->world; ++r) fp.flags[r] = static_cast<unsigned long long*>(c->flags.peers[(size_t)r]);
+    // about a second of polling at 100 ns per poll before the wait is declared dead
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(32, 1, 1);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, arrive_and_wait_kernel, fp, c->world, c->rank, c->epoch, 4u * 1000u * 1000u, c->status);
+    note_launch("comm_arrive_and_wait");
+    return (int32_t)rc;
+}
+
+uint32_t opsnn_comm_status(void* comm, int32_t reset)
+{
+    if (comm == nullptr) return 0;
+    Comm* c = static_cast<Comm*>(comm);
+    if (c->status == nullptr) return 0;
+    unsigned int v = 0;
+    cudaMemcpy(&v, c->status, sizeof(v), cudaMemcpyDeviceToHost);
+    if (reset) cudaMemset(c->status, 0, sizeof(unsigned int));
+    return v;
 }
 
 }  // extern "C"

@@ -50,6 +50,7 @@ struct DecodeArgs {
     float4* partials;          // [gridDim][kWarps][kTiles][32]
     unsigned long long nonce;
     uint32_t c_mask, c_magic, c_bias;  // 0x000F000F, Num::kMagic, Num::kBias
+    PeerBinding peers;         // bulk-copy kernels: count > 0 stores every element into each rank's full output as well
 };
 
 __device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p)
@@ -143,6 +144,14 @@ struct Num<false> {
     }
 };
 
+// The element (row, col of the shard) into every bound rank's full output.
+template <bool kBf16>
+__device__ __forceinline__ void store_to_peers(const DecodeArgs& a, int row, int64_t col, float f)
+{
+    const int64_t idx = (int64_t)row * a.peers.ld + a.peers.col0 + col;
+    for (int r = 0; r < a.peers.count; ++r) store_out(a.peers.full[r], idx, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
+}
+
 // Writes one warp's 16 x 64 block of y from its accumulator fragments (+ bias), undoing the column permutation of the MMA tiles.
 template <bool kBf16, int kLayout>
 __device__ __forceinline__ void store_tile_y(const DecodeArgs& a, float (&acc)[kTiles][4], int64_t strip, int warp, int lane)
@@ -165,6 +174,7 @@ __device__ __forceinline__ void store_tile_y(const DecodeArgs& a, float (&acc)[k
                             float f = acc[t][e];
                             if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
                             store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
+                            if (a.peers.count > 0) store_to_peers<kBf16>(a, row, col, f);
                         }
                     }
                 }
@@ -319,6 +329,7 @@ __device__ __forceinline__ void cluster_combine_and_store(const DecodeArgs& a, f
                     float f = f4[e];
                     if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
                     store_out(a.y, (int64_t)row * a.y_ld + col, f, kBf16 ? ACL_BF16 : ACL_FLOAT16);
+                    if (a.peers.count > 0) store_to_peers<kBf16>(a, row, col, f);
                 }
             }
         }

@@ -569,6 +569,7 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.bias_dtype = p->bias_dtype;
     a.y = p->y;
     a.y_ld = p->y_ld;
+    if (!lookup_peer_binding(p->y, &a.peers)) a.peers.count = 0;
     a.m = (int32_t)p->m;
     a.n = p->n;
     a.k = p->k;

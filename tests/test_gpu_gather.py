@@ -31,8 +31,58 @@ def test_single_rank_gather_columns_and_batch(aclnn):
         out = comm.gather_batch(b, 4)
         torch.cuda.synchronize()
         assert torch.equal(out, b)
+        assert _fused_gather_check(aclnn, comm, dev, 1, 0)
     finally:
         comm.close()
+
+
+def _fused_gather_check(aclnn, comm, dev, world, rank):
+    """Column shards of a W4A16 decode call stored by the kernel itself into every rank's full output (symmetric memory, peer
+    stores), then arrive_and_wait: must equal the NCCL gather of the same shards bit for bit; a bound call that cannot run on
+    a streaming decode kernel is refused."""
+    import torch
+
+    m, k, n, g = 16, 2048, 4096, 128
+    gen = torch.Generator(device=dev).manual_seed(99)  # the same tensors on every rank
+    x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+    w = torch.randint(-2 ** 31, 2 ** 31 - 1, (k, n // 8), generator=gen, device=dev, dtype=torch.int32)
+    sc = (torch.rand((k // g, n), generator=gen, device=dev) * 0.01 + 0.005).to(torch.bfloat16)
+    of = (torch.rand((k // g, n), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
+    b, e = aclnn.shard_range(n, world, rank, 512)
+    ws, ss, os_ = w[:, b // 8:e // 8].contiguous(), sc[:, b:e].contiguous(), of[:, b:e].contiguous()
+    y_local = torch.empty((m, e - b), dtype=torch.bfloat16, device=dev)
+    y_full = comm.symmetric_empty((m, n), torch.bfloat16)
+    comm.bind_columns(y_local, y_full, 512)
+    ok = True
+    try:
+        for rep in range(3):  # repeated steps: the arrival epochs advance
+            xr = (x.float() * (rep + 1)).to(torch.bfloat16)
+            aclnn.weight_quant_batch_matmul(aclnn.from_torch(xr), aclnn.from_torch(ws), aclnn.from_torch(ss), aclnn.from_torch(y_local),
+                                            aclnn.from_torch(os_), None, g)
+            assert aclnn.last_kernel_name() == "wqbmm_decode"
+            comm.arrive_and_wait()
+            torch.cuda.synchronize()
+            fused = y_full.clone()
+            comm.arrive_and_wait()  # nobody overwrites a full output another rank is still reading
+            torch.cuda.synchronize()
+            ref = comm.gather_columns(y_local, n, 512)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(fused, ref)) and not bool((fused == 0).all())
+        refused = False
+        try:  # m = 32 runs as two decode launches on row chunks: not a path that stores into the peers
+            x32 = torch.randn((32, k), generator=gen, device=dev).to(torch.bfloat16)
+            y32 = torch.empty((32, e - b), dtype=torch.bfloat16, device=dev)
+            comm.bind_columns(y32, y_full, 512)
+            aclnn.weight_quant_batch_matmul(aclnn.from_torch(x32), aclnn.from_torch(ws), aclnn.from_torch(ss), aclnn.from_torch(y32),
+                                            aclnn.from_torch(os_), None, g)
+        except aclnn.AclnnError:
+            refused = True
+        finally:
+            comm.unbind(y32)
+        ok = ok and refused and comm.status() == 0
+    finally:
+        comm.unbind(y_local)
+    return ok
 
 
 def _free_port():
@@ -71,7 +121,8 @@ def _rank_main(rank, world, port, ret):
         bb, be = aclnn.shard_range(4, world, rank, 1)
         gotb = comm.gather_batch(bat[bb:be].to(dev), 4)
         torch.cuda.synchronize()
-        ret[rank] = (ok_cols, bool(torch.equal(gotb.cpu(), bat)))
+        ok_fused = _fused_gather_check(aclnn, comm, dev, world, rank)
+        ret[rank] = (ok_cols, bool(torch.equal(gotb.cpu(), bat)), ok_fused)
         comm.close()
     finally:
         dist.destroy_process_group()
@@ -95,4 +146,4 @@ def test_two_rank_gather_over_nccl(aclnn):
             p.join(240)
         for p in procs:
             assert p.exitcode == 0
-        assert dict(ret) == {0: (True, True), 1: (True, True)}
+        assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}
