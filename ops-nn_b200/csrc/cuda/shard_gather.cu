@@ -8,6 +8,8 @@
 // carries (the one a PyTorch host loaded, or the system one), so the library loads on machines without it.
 #include <dlfcn.h>
 
+#include <cstdlib>
+
 #include <map>
 #include <mutex>
 #include <vector>
@@ -488,7 +490,12 @@ int32_t opsnn_comm_arrive_and_wait(void* comm, void* stream)
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t rc = cudaLaunchKernelEx(&cfg, arrive_and_wait_kernel, fp, c->world, c->rank, c->epoch, 4u * 1000u * 1000u, c->status);
+    unsigned int limit = 4u * 1000u * 1000u;
+    if (const char* e = getenv("OPSNN_COMM_POLL_LIMIT")) {  // tests of the give-up path: a shorter wait
+        const long v = atol(e);
+        if (v > 0 && v < (long)limit) limit = (unsigned int)v;
+    }
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, arrive_and_wait_kernel, fp, c->world, c->rank, c->epoch, limit, c->status);
     note_launch("comm_arrive_and_wait");
     return (int32_t)rc;
 }

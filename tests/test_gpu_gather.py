@@ -80,6 +80,27 @@ def _fused_gather_check(aclnn, comm, dev, world, rank):
         finally:
             comm.unbind(y32)
         ok = ok and refused and comm.status() == 0
+        if world > 1:
+            # A rank that does not show up: rank 0 announces its arrival and waits; nobody else does. Its wait is bounded (shortened
+            # here), the kernel returns by itself and the status word says so. The ranks talk on the host (gloo) in between, and
+            # when the others then make the same call they find rank 0's flag already there: the arrival counters agree again.
+            import torch.distributed as dist
+
+            os.environ["OPSNN_COMM_POLL_LIMIT"] = "200000"
+            if rank == 0:
+                comm.arrive_and_wait()
+                torch.cuda.synchronize()
+                ok = ok and comm.status() == 1
+            dist.barrier()
+            if rank != 0:
+                comm.arrive_and_wait()
+                torch.cuda.synchronize()
+                ok = ok and comm.status() == 0
+            dist.barrier()
+            os.environ.pop("OPSNN_COMM_POLL_LIMIT")
+            comm.arrive_and_wait()  # and an ordinary one afterwards
+            torch.cuda.synchronize()
+            ok = ok and comm.status() == 0
     finally:
         comm.unbind(y_local)
     return ok
