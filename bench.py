@@ -1066,6 +1066,8 @@ def main():
     fused_gather_ms = None
     fused_gather_err = None
     fused_scheme = "eager"
+    peer_gather_ms = None
+    peer_scheme = "eager"
     if world > 1:
         y_full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         for _ in range(3):
@@ -1136,6 +1138,55 @@ def main():
                     fused_gather_ms = None
             finally:
                 args.comm.unbind(y)
+            # Third form: one kernel after the call pushes the shard into every rank's full output with 16-byte peer stores and
+            # handles the arrival (opsnn_comm_allgather_columns); eager and from a CUDA graph.
+            try:
+                for i in range(3):
+                    step(i)
+                    args.comm.allgather_columns_peer(y, y_sym, 512)
+                barrier()
+                h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                h0.record()
+                for i in range(args.steps):
+                    step(i)
+                    args.comm.allgather_columns_peer(y, y_sym, 512)
+                h1.record()
+                barrier()
+                peer_gather_ms = h0.elapsed_time(h1) / args.steps
+                cap_p = torch.cuda.Stream(dev)
+                pg = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize()
+                barrier()
+                with torch.cuda.graph(pg, stream=cap_p):
+                    for i in range(10):
+                        step(i)
+                        args.comm.allgather_columns_peer(y, y_sym, 512)
+                reps = max(2, (args.steps + 9) // 10)
+                pg.replay()
+                barrier()
+                k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                k0.record()
+                for _ in range(reps):
+                    pg.replay()
+                k1.record()
+                barrier()
+                peer_graph_ms = k0.elapsed_time(k1) / (reps * 10)
+                if peer_graph_ms < peer_gather_ms:
+                    peer_gather_ms, peer_scheme = peer_graph_ms, "cuda_graph"
+                step(0)
+                args.comm.allgather_columns_peer(y, y_sym, 512)
+                torch.cuda.synchronize()
+                barrier()
+                pushed = y_sym.clone()
+                args.comm.arrive_and_wait()
+                args.comm.gather_columns(y, N, 512, out=y_full)
+                torch.cuda.synchronize()
+                if not torch.equal(pushed, y_full) or args.comm.status() != 0:
+                    peer_gather_ms = None
+            except Exception as exc:  # noqa: BLE001
+                peer_gather_ms = None
+                fused_gather_err = "%s: %s" % (type(exc).__name__, exc)
+                torch.cuda.synchronize()
         except Exception as exc:  # noqa: BLE001 - the separate gather above stands
             fused_gather_ms = None
             fused_gather_err = "%s: %s" % (type(exc).__name__, exc)
@@ -1269,7 +1320,7 @@ def main():
 
     vals = [tm["total_ms"], tm["avg"], tm["min"], tm["median"], tm_hp["avg"], tm_hp["min"], e2e_serial_ms, e2e_pipe_ms,
             gather_ms if gather_ms is not None else 0.0, e2e_graph_ms if e2e_graph_ms != float("inf") else 1e9,
-            fused_gather_ms if fused_gather_ms is not None else 1e9]
+            fused_gather_ms if fused_gather_ms is not None else 1e9, peer_gather_ms if peer_gather_ms is not None else 1e9]
     par_ok = 1.0 if parity["ok"] else 0.0
     if dist is not None:
         t = torch.tensor(vals, device=dev, dtype=torch.float64)
@@ -1281,7 +1332,7 @@ def main():
         o = torch.tensor([par_ok], device=dev, dtype=torch.float64)
         dist.all_reduce(o, op=dist.ReduceOp.MIN)
         par_ok = float(o.item())
-    total_ms, kernel_ms, kernel_min, kernel_med, hp_ms, hp_min, e2e_serial_ms, e2e_pipe_ms, gather_all_ms, e2e_graph_ms, fused_all_ms = vals
+    total_ms, kernel_ms, kernel_min, kernel_med, hp_ms, hp_min, e2e_serial_ms, e2e_pipe_ms, gather_all_ms, e2e_graph_ms, fused_all_ms, peer_all_ms = vals
 
     # ---- N > 1: the former weak-scaling figure (every rank a full-width shard) as a secondary key ----
     weak = None
@@ -1389,6 +1440,11 @@ def main():
                                                      "bit-identical to the NCCL gather in the same run"}
             elif fused_gather_err:
                 line["with_fused_gather"] = {"error": fused_gather_err}
+            if peer_all_ms < 1e8:
+                line["with_peer_gather"] = {"ms_per_step": peer_all_ms, "value": ALGO_BYTES / (peer_all_ms * 1e-3) / 1e9, "unit": "GB/s", "scheme": peer_scheme,
+                                            "note": "every step followed by opsnn_comm_allgather_columns: one kernel pushes the y shard into every rank's "
+                                                    "full output (symmetric memory, 16-byte peer stores) and handles the arrival; checked bit-identical "
+                                                    "to the NCCL gather in the same run"}
             line["weak"] = weak
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = c2_cpu_baseline(host)

@@ -63,12 +63,19 @@ OPSNN_SHARD_API int32_t opsnn_gather_batch(void* comm, const void* y_local, int6
  *                                streaming decode kernel write y_local and every rank's full output; a bound call that would run
  *                                on another kernel is refused (cudaErrorNotSupported) rather than silently left ungathered.
  *   opsnn_comm_arrive_and_wait   collective on `stream`, after the bound call: afterwards every rank's full output is complete.
+ *   opsnn_comm_allgather_columns the other way round, for any producer of y_local: ONE kernel of `world` CTAs after it copies the
+ *                                rank's (m, width) shard into every rank's full output with 16-byte peer stores (rows are
+ *                                contiguous on both sides), announces and awaits arrival like opsnn_comm_arrive_and_wait. With
+ *                                many ranks this beats the epilogue form (whose peer stores are 2-byte and scattered by the MMA
+ *                                fragment layout): 8 GPUs, 16 x 3584 shards. No binding is involved.
  * No counterpart in the reference (it has no multi-device code for these operators). */
 OPSNN_SHARD_API int32_t opsnn_comm_symmetric_alloc(void* comm, uint64_t bytes, void** local, void** peers);
 OPSNN_SHARD_API int32_t opsnn_comm_symmetric_free(void* comm, void* local);
 OPSNN_SHARD_API int32_t opsnn_comm_bind_columns(void* comm, const void* y_local, const void* y_full_local, int64_t n_total, int64_t multiple);
 OPSNN_SHARD_API int32_t opsnn_comm_unbind(const void* y_local);
 OPSNN_SHARD_API int32_t opsnn_comm_arrive_and_wait(void* comm, void* stream);
+OPSNN_SHARD_API int32_t opsnn_comm_allgather_columns(void* comm, const void* y_local, int64_t y_local_ld, int64_t m, const void* y_full_local,
+                                                     int64_t n_total, int64_t multiple, int32_t elem_bytes, void* stream);
 OPSNN_SHARD_API uint32_t opsnn_comm_status(void* comm, int32_t reset);
 
 #ifdef __cplusplus

@@ -132,6 +132,8 @@ def lib():
     L.opsnn_comm_bind_columns.argtypes = [VP, VP, VP, I64, I64]
     L.opsnn_comm_unbind.argtypes = [VP]
     L.opsnn_comm_arrive_and_wait.argtypes = [VP, VP]
+    L.opsnn_comm_allgather_columns.argtypes = [VP, VP, I64, I64, VP, I64, I64, I32, VP]
+    L.opsnn_comm_allgather_columns.restype = c_int32
     L.opsnn_comm_status.argtypes = [VP, I32]
     L.opsnn_comm_status.restype = ctypes.c_uint32
     for name in ("opsnn_comm_symmetric_alloc", "opsnn_comm_symmetric_free", "opsnn_comm_bind_columns", "opsnn_comm_unbind",
@@ -527,6 +529,14 @@ class Comm:
         rc = lib().opsnn_comm_arrive_and_wait(self.handle, _stream())
         if rc != 0:
             raise RuntimeError("opsnn_comm_arrive_and_wait failed (%d): %s" % (rc, last_error()))
+
+    def allgather_columns_peer(self, y_local, y_full, multiple=8):
+        """Collective, on the current stream: one kernel copies this rank's column shard into every rank's `y_full` (from
+        symmetric_empty) with peer stores and waits for the other ranks' shards to have arrived."""
+        rc = lib().opsnn_comm_allgather_columns(self.handle, c_void_p(y_local.data_ptr()), int(y_local.stride(0)), int(y_local.shape[0]),
+                                                c_void_p(y_full.data_ptr()), int(y_full.shape[-1]), int(multiple), y_local.element_size(), _stream())
+        if rc != 0:
+            raise RuntimeError("opsnn_comm_allgather_columns failed (%d): %s" % (rc, last_error()))
 
     def status(self, reset=True):
         """0, or 1 when a wait for the other ranks ran out (synchronises the device)."""

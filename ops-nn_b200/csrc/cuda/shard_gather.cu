@@ -68,6 +68,7 @@ struct Comm {
     std::vector<Symmetric> regions;
     // cross-rank arrival flags (a symmetric region of its own, made on first use): flags[r] = the last epoch rank r announced here
     Symmetric flags;
+    unsigned int* done = nullptr;         // device ticket of the push kernel's CTAs (the last one to finish advances the epoch)
     unsigned long long* epoch = nullptr;  // device counter of this rank's arrivals: advanced by the kernel itself, so a captured launch replays correctly
     unsigned int* status = nullptr;       // device word: 0, or 1 when a wait for the other ranks ran out
 };
@@ -152,6 +153,58 @@ __global__ void arrive_and_wait_kernel(const __grid_constant__ FlagPeers peers, 
     if (!seen) atomicExch(status, 1u);
 }
 
+
+// The all-gather of small column shards as one kernel over peer memory: the CTAs (blockIdx.x, r) copy this rank's (m, width)
+// shard into rank r's full output (16-byte stores over NVLink, rows are contiguous on both sides); the last of them to finish
+// (a ticket per peer) releases this rank's flag there and waits, bounded, for rank r's flag here. The epoch all CTAs use is the
+// device counter + 1; the last of the `world` flag-handling CTAs to finish advances it.
+struct PeerFull {
+    uint8_t* full[kMaxPeers];
+};
+template <int VB>
+__global__ void __launch_bounds__(256) allgather_columns_kernel(const __grid_constant__ FlagPeers flags, const __grid_constant__ PeerFull dst,
+                                                                const uint8_t* __restrict__ y_local, int64_t local_row_b, int64_t width_b,
+                                                                int64_t m, int64_t full_row_b, int64_t col0_b, int world, int rank,
+                                                                unsigned long long* epoch_counter, unsigned int* done, unsigned int limit,
+                                                                unsigned int* status)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the kernel that wrote y_local has completed
+    const int r = blockIdx.y;
+    const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(epoch_counter) + 1ull;
+    uint8_t* out = dst.full[r] + col0_b;
+    const int64_t pieces = width_b / VB;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < m * pieces; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / pieces, p = i - row * pieces;
+        if (VB == 16)
+            *reinterpret_cast<uint4*>(out + row * full_row_b + p * 16) = *reinterpret_cast<const uint4*>(y_local + row * local_row_b + p * 16);
+        else
+            *reinterpret_cast<uint16_t*>(out + row * full_row_b + p * 2) = *reinterpret_cast<const uint16_t*>(y_local + row * local_row_b + p * 2);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    // done[1 + r]: CTAs of peer r that have finished their part; done[0]: flag-handling CTAs that have finished
+    if (atomicAdd(done + 1 + r, 1u) != gridDim.x - 1u) return;
+    done[1 + r] = 0u;
+    __threadfence_system();  // the other CTAs' stores (ordered before their tickets) before the flag
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flags.flags[r] + rank), "l"(epoch) : "memory");
+    const unsigned long long* mine = flags.flags[rank] + r;
+    bool seen = false;
+    for (unsigned int i = 0; i < limit && !seen; ++i) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+        seen = v >= epoch;
+        if (!seen) __nanosleep(100);
+    }
+    if (!seen) atomicExch(status, 1u);
+    __threadfence();
+    if (atomicAdd(done, 1u) == (unsigned int)world - 1u) {  // every CTA has read the counter long ago
+        *done = 0u;
+        *epoch_counter = epoch;
+    }
+}
+
 }  // namespace
 
 bool lookup_peer_binding(const void* y_local, PeerBinding* out)
@@ -209,6 +262,23 @@ int32_t symmetric_alloc(Comm* c, uint64_t bytes, Symmetric* out)
             return (int32_t)rc;
         }
     }
+    return 0;
+}
+
+// The cross-rank flags and the device words beside them, made on first use (collective).
+int32_t ensure_flags(Comm* c)
+{
+    if (c->flags.local != nullptr) return 0;
+    const int32_t rc = symmetric_alloc(c, 256 * sizeof(unsigned long long), &c->flags);
+    if (rc != 0) return rc;
+    cudaError_t e = cudaMalloc(&c->status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->epoch, sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&c->done, 16 * sizeof(unsigned int));
+    if (e != cudaSuccess) return (int32_t)e;
+    cudaMemset(c->status, 0, sizeof(unsigned int));
+    cudaMemset(c->epoch, 0, sizeof(unsigned long long));
+    cudaMemset(c->done, 0, 16 * sizeof(unsigned int));
+    cudaDeviceSynchronize();
     return 0;
 }
 
@@ -296,6 +366,7 @@ int32_t opsnn_comm_destroy(void* comm)
     if (c->flags.local != nullptr) symmetric_release(c, &c->flags);
     if (c->status != nullptr) cudaFree(c->status);
     if (c->epoch != nullptr) cudaFree(c->epoch);
+    if (c->done != nullptr) cudaFree(c->done);
     const int rc = c->nccl ? nccl().CommDestroy(c->nccl) : 0;
     delete c;
     return rc == 0 ? 0 : nccl_fail("ncclCommDestroy", rc);
@@ -468,16 +539,7 @@ int32_t opsnn_comm_arrive_and_wait(void* comm, void* stream)
     if (comm == nullptr) return (int32_t)cudaErrorInvalidValue;
     Comm* c = static_cast<Comm*>(comm);
     if (c->world > kMaxPeers) return (int32_t)cudaErrorNotSupported;
-    if (c->flags.local == nullptr) {  // first use (collective, like every call of this function)
-        const int32_t rc = symmetric_alloc(c, 256 * sizeof(unsigned long long), &c->flags);
-        if (rc != 0) return rc;
-        cudaError_t e = cudaMalloc(&c->status, sizeof(unsigned int));
-        if (e == cudaSuccess) e = cudaMalloc(&c->epoch, sizeof(unsigned long long));
-        if (e != cudaSuccess) return (int32_t)e;
-        cudaMemset(c->status, 0, sizeof(unsigned int));
-        cudaMemset(c->epoch, 0, sizeof(unsigned long long));
-        cudaDeviceSynchronize();
-    }
+    if (const int32_t rc = ensure_flags(c)) return rc;
     FlagPeers fp{};
     for (int r = 0; r < c->world; ++r) fp.flags[r] = static_cast<unsigned long long*>(c->flags.peers[(size_t)r]);
     // about a second of polling at 100 ns per poll before the wait is declared dead
@@ -509,6 +571,69 @@ uint32_t opsnn_comm_status(void* comm, int32_t reset)
     cudaMemcpy(&v, c->status, sizeof(v), cudaMemcpyDeviceToHost);
     if (reset) cudaMemset(c->status, 0, sizeof(unsigned int));
     return v;
+}
+
+
+int32_t opsnn_comm_allgather_columns(void* comm, const void* y_local, int64_t y_local_ld, int64_t m, const void* y_full_local, int64_t n_total,
+                                     int64_t multiple, int32_t elem_bytes, void* stream)
+{
+    if (comm == nullptr || y_local == nullptr || y_full_local == nullptr || m < 0 || n_total < 1 || multiple < 1 ||
+        (elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 1))
+        return (int32_t)cudaErrorInvalidValue;
+    Comm* c = static_cast<Comm*>(comm);
+    if (c->world > kMaxPeers) return (int32_t)cudaErrorNotSupported;
+    const Symmetric* sy = nullptr;
+    for (const Symmetric& s : c->regions)
+        if (s.local == y_full_local) sy = &s;
+    if (sy == nullptr) {
+        set_err("opsnn_comm_allgather_columns: y_full was not allocated by opsnn_comm_symmetric_alloc on this communicator");
+        return (int32_t)cudaErrorInvalidValue;
+    }
+    if (const int32_t rc = ensure_flags(c)) return rc;
+    int64_t begin = 0, end = 0;
+    opsnn_shard_range(n_total, c->world, c->rank, multiple, &begin, &end);
+    FlagPeers fp{};
+    PeerFull pf{};
+    for (int r = 0; r < c->world; ++r) {
+        fp.flags[r] = static_cast<unsigned long long*>(c->flags.peers[(size_t)r]);
+        pf.full[r] = static_cast<uint8_t*>(sy->peers[(size_t)r]);
+    }
+    const int64_t width_b = (end - begin) * elem_bytes, col0_b = begin * elem_bytes, full_row_b = n_total * elem_bytes, local_row_b = y_local_ld * elem_bytes;
+    const bool vec = width_b % 16 == 0 && col0_b % 16 == 0 && full_row_b % 16 == 0 && local_row_b % 16 == 0 &&
+                     (reinterpret_cast<uintptr_t>(y_local) & 15) == 0;
+    if (!vec && (elem_bytes != 2 || width_b % 2 != 0)) {
+        set_err("opsnn_comm_allgather_columns: shards that are not whole 16-byte pieces are moved as 2-byte elements only");
+        return (int32_t)cudaErrorNotSupported;
+    }
+    unsigned int limit = 4u * 1000u * 1000u;
+    if (const char* e = getenv("OPSNN_COMM_POLL_LIMIT")) {
+        const long v = atol(e);
+        if (v > 0 && v < (long)limit) limit = (unsigned int)v;
+    }
+    cudaLaunchConfig_t cfg{};
+    // enough CTAs per peer that a copy is a handful of independent 16-byte round trips per thread, about 128 CTAs in all
+    int64_t parts = 128 / c->world;
+    const int64_t work = (m * (width_b / (vec ? 16 : 2)) + 255) / 256;
+    if (parts > work) parts = work;
+    if (parts < 1) parts = 1;
+    cfg.gridDim = dim3((unsigned)parts, (unsigned)c->world, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const uint8_t* src = static_cast<const uint8_t*>(y_local);
+    cudaError_t rc;
+    if (vec)
+        rc = cudaLaunchKernelEx(&cfg, allgather_columns_kernel<16>, fp, pf, src, local_row_b, width_b, m, full_row_b, col0_b, c->world, c->rank, c->epoch,
+                                c->done, limit, c->status);
+    else
+        rc = cudaLaunchKernelEx(&cfg, allgather_columns_kernel<2>, fp, pf, src, local_row_b, width_b, m, full_row_b, col0_b, c->world, c->rank, c->epoch,
+                                c->done, limit, c->status);
+    note_launch("comm_allgather_columns");
+    return (int32_t)rc;
 }
 
 }  // extern "C"

@@ -52,6 +52,7 @@ def _fused_gather_check(aclnn, comm, dev, world, rank):
     ws, ss, os_ = w[:, b // 8:e // 8].contiguous(), sc[:, b:e].contiguous(), of[:, b:e].contiguous()
     y_local = torch.empty((m, e - b), dtype=torch.bfloat16, device=dev)
     y_full = comm.symmetric_empty((m, n), torch.bfloat16)
+    y_push = comm.symmetric_empty((m, n), torch.bfloat16)
     comm.bind_columns(y_local, y_full, 512)
     ok = True
     try:
@@ -68,6 +69,13 @@ def _fused_gather_check(aclnn, comm, dev, world, rank):
             ref = comm.gather_columns(y_local, n, 512)
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(fused, ref)) and not bool((fused == 0).all())
+            # the one-kernel peer all-gather of the same shard (no binding involved) into a second full output
+            comm.allgather_columns_peer(y_local, y_push, 512)
+            torch.cuda.synchronize()
+            pushed = y_push.clone()
+            comm.arrive_and_wait()
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(pushed, ref))
         refused = False
         try:  # m = 32 runs as two decode launches on row chunks: not a path that stores into the peers
             x32 = torch.randn((32, k), generator=gen, device=dev).to(torch.bfloat16)
