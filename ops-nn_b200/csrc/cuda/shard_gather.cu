@@ -8,6 +8,7 @@
 // carries (the one a PyTorch host loaded, or the system one), so the library loads on machines without it.
 #include <dlfcn.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include <map>
@@ -75,6 +76,7 @@ struct Comm {
 
 std::mutex g_bind_mu;
 std::map<const void*, PeerBinding> g_bindings;
+std::atomic<int> g_binding_count{0};  // lets every decode launch skip the lock while nothing is bound
 
 int32_t nccl_fail(const char* what, int rc)
 {
@@ -209,9 +211,8 @@ __global__ void __launch_bounds__(256) allgather_columns_kernel(const __grid_con
 
 bool lookup_peer_binding(const void* y_local, PeerBinding* out)
 {
-    if (y_local == nullptr) return false;
+    if (y_local == nullptr || g_binding_count.load(std::memory_order_acquire) == 0) return false;
     std::lock_guard<std::mutex> lk(g_bind_mu);
-    if (g_bindings.empty()) return false;
     auto it = g_bindings.find(y_local);
     if (it == g_bindings.end()) return false;
     *out = it->second;
@@ -360,6 +361,7 @@ int32_t opsnn_comm_destroy(void* comm)
                 for (void* q : sy.peers) ours = ours || q == it->second.full[0];
             it = ours ? g_bindings.erase(it) : std::next(it);
         }
+        g_binding_count.store((int)g_bindings.size(), std::memory_order_release);
     }
     for (Symmetric& sy : c->regions) symmetric_release(c, &sy);
     c->regions.clear();
@@ -524,6 +526,7 @@ int32_t opsnn_comm_bind_columns(void* comm, const void* y_local, const void* y_f
     b.col0 = begin;
     std::lock_guard<std::mutex> lk(g_bind_mu);
     g_bindings[y_local] = b;
+    g_binding_count.store((int)g_bindings.size(), std::memory_order_release);
     return 0;
 }
 
@@ -531,6 +534,7 @@ int32_t opsnn_comm_unbind(const void* y_local)
 {
     std::lock_guard<std::mutex> lk(g_bind_mu);
     g_bindings.erase(y_local);
+    g_binding_count.store((int)g_bindings.size(), std::memory_order_release);
     return 0;
 }
 
