@@ -83,8 +83,6 @@ __global__ void __launch_bounds__(256) mx_sf_relayout_tiled_kernel(const uint8_t
         __syncthreads();
         if (!transposed_layout) {
             const bool words = ((2 * kq) & 3) == 0 && (reinterpret_cast<uintptr_t>(s) & 3) == 0;
-            // several independent loads in flight per thread: one at a time, the L2 round trips of a thread's 32 words add up
-#pragma unroll 8
             for (int e = tid; e < 128 * (kc / 4); e += 256) {
                 const int rr = e / (kc / 4), c4 = e % (kc / 4);
                 const int64_t kb = kc0 + 4 * c4;
@@ -102,7 +100,6 @@ __global__ void __launch_bounds__(256) mx_sf_relayout_tiled_kernel(const uint8_t
                 *reinterpret_cast<uint32_t*>(&sm[rr][4 * c4]) = w;
             }
         } else {
-#pragma unroll 8
             for (int e = tid; e < 128 * (kc / 2); e += 256) {
                 const int kbp = e >> 7, rr = e & 127;   // pair of k-blocks, row: consecutive threads read consecutive rows
                 const int64_t kb = kc0 + 2 * kbp;
@@ -118,7 +115,6 @@ __global__ void __launch_bounds__(256) mx_sf_relayout_tiled_kernel(const uint8_t
         __syncthreads();
         // atoms of this chunk: atom (st, at) holds k-blocks 4 * (st * atoms + at) .. + 3; 128 words of 4 bytes each
         const int natoms = kc / 4;
-#pragma unroll 4
         for (int e = tid; e < natoms * 128; e += 256) {
             const int ai = e >> 7, wi = e & 127;
             const int l = wi >> 2, m1 = wi & 3, rr = m1 * 32 + l;
