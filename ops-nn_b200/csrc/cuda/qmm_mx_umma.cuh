@@ -81,7 +81,33 @@ __global__ void __launch_bounds__(256) mx_sf_relayout_tiled_kernel(const uint8_t
     for (int64_t kc0 = 0; kc0 < kb_total; kc0 += kSfChunk) {
         const int kc = (int)min((int64_t)kSfChunk, kb_total - kc0);         // multiple of 4
         __syncthreads();
-        if (!transposed_layout) {
+        const bool vec16 = !transposed_layout && ((2 * kq) & 15) == 0 && (reinterpret_cast<uintptr_t>(s) & 15) == 0 && (kc & 15) == 0 &&
+                           kc0 + kc <= kblocks;
+        if (vec16) {
+            // whole chunk present and 16-byte aligned rows: 16 k-blocks per load, four independent loads in flight per thread
+            const int vecs = kc / 16;
+            for (int e0 = tid; e0 < 128 * vecs; e0 += 4 * 256) {
+                uint4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int e = e0 + j * 256;
+                    v[j] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+                    if (e < 128 * vecs) {
+                        const int rr = e / vecs, c = e - rr * vecs;
+                        if (rr < live) v[j] = __ldg(reinterpret_cast<const uint4*>(s + (row0 + rr) * (2 * kq) + kc0 + 16 * c));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int e = e0 + j * 256;
+                    if (e < 128 * vecs) {
+                        const int rr = e / vecs, c = e - rr * vecs;
+                        uint32_t* d32 = reinterpret_cast<uint32_t*>(&sm[rr][16 * c]);
+                        d32[0] = v[j].x; d32[1] = v[j].y; d32[2] = v[j].z; d32[3] = v[j].w;
+                    }
+                }
+            }
+        } else if (!transposed_layout) {
             const bool words = ((2 * kq) & 3) == 0 && (reinterpret_cast<uintptr_t>(s) & 3) == 0;
             for (int e = tid; e < 128 * (kc / 4); e += 256) {
                 const int rr = e / (kc / 4), c4 = e % (kc / 4);
