@@ -98,18 +98,21 @@ class ClockSampler:
         return len(self.rows)
 
     def summary(self, first=0, last=None):
-        mhz, mx, reasons = [], None, set()
+        mhz, mx, reasons, watts = [], None, set(), []
         for r in self.rows[first:last]:
             try:
                 mhz.append(float(r[0]))
                 mx = float(r[1])
+                watts.append(float(r[2]))
                 for name, col in (("hw_slowdown", 4), ("hw_thermal_slowdown", 5), ("sw_thermal_slowdown", 6), ("sw_power_cap", 7)):
                     if r[col].lower().startswith("active"):
                         reasons.add(name)
             except Exception:  # noqa: BLE001
                 continue
         mhz.sort()
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+        watts.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_min_mhz": mhz[0] if mhz else None, "sm_max_mhz": mx,
+                "power_w_max": watts[-1] if watts else None, "reasons": sorted(reasons), "samples": len(mhz)}
 
     def stop(self):
         if self.proc is None:
@@ -737,11 +740,15 @@ def run_ceilings(aclnn, sm_mhz=1965.0, sms=148):
 
 def run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names):
     out = {}
+    sampler = getattr(args, "sampler", None)  # rank 0's clock sampler: every workload's entry gets the clocks seen while it ran
     for name in names:
+        mark_a = sampler.mark() if sampler is not None else None
         try:
             if name == "c1":
                 if rank == 0:
                     out["c1"] = run_c1(torch, dev, aclnn, args, peaks)
+                    if sampler is not None:
+                        out["c1"]["clocks"] = sampler.summary(mark_a, sampler.mark())
                 if dist is not None:
                     dist.barrier()
                 continue
@@ -765,6 +772,9 @@ def run_secondary(torch, dev, aclnn, args, peaks, rank, world, dist, names):
             res.clear()
             torch.cuda.empty_cache()
             if rank == 0:
+                if sampler is not None:
+                    # whole workload (input generation, parity, all timed variants): long tensor-core runs meet the power cap
+                    entry["clocks"] = sampler.summary(mark_a, sampler.mark())
                 out[name] = entry
         except Exception as exc:  # noqa: BLE001 - a secondary workload must never take the contract line down
             if rank == 0:
@@ -984,6 +994,7 @@ def main():
     args.comm = aclnn.Comm(world, rank, dev) if world > 1 else None
     barrier = dist_barrier(torch, dist)
     sampler = ClockSampler(local_rank)
+    args.sampler = sampler if rank == 0 else None
     if rank == 0:
         sampler.start()
 
