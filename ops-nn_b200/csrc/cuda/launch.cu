@@ -197,7 +197,7 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
     }
     if (p->inner_precise == 1 && wqbmm_decode_fast_eligible(p)) return OPSNN_WQ_KERNEL_DECODE_FAST;
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
-    // 8-bit integer weights at small m: their own streaming kernel once the weight is large enough to be worth a k-split grid
+    // 8-bit weights (int8, e4m3) at small m: their own streaming kernel once the weight is large enough to be worth a k-split grid
     if (wqbmm_decode8_eligible(p) && p->k * p->n >= ((int64_t)1 << 20) && getenv("OPSNN_WQ_NO_DECODE8") == nullptr) return OPSNN_WQ_KERNEL_DECODE;
     // a weight prepared for the prefill path (dequantised once, kept by the caller): beyond the decode range the tensor-core matmul
     // alone beats streaming the packed weight once per 16 rows
@@ -281,10 +281,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
             const bool tma4 = (kernel_choice == OPSNN_WQ_KERNEL_DECODE || kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST) && p->w_dtype != ACL_INT8 &&
                               p->m <= 16 && !ring_only && wqbmm_decode_fast_eligible(p) && wqbmm_decode_tma_eligible(p) &&
                               getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr;
-            const bool tma8 = kernel_choice == OPSNN_WQ_KERNEL_DECODE && p->w_dtype == ACL_INT8 && wqbmm_decode8_eligible(p);
+            const bool tma8 = kernel_choice == OPSNN_WQ_KERNEL_DECODE && wqbmm_decode8_eligible(p);
             if (!tma4 && !tma8) {
                 set_err("opsnn_wqbmm_launch: y is bound to a communicator, but this call does not run on a streaming decode kernel that "
-                        "stores into the peers' outputs (m <= 16, int4 or int8 weight stored (k,n), aligned rows)");
+                        "stores into the peers' outputs (m <= 16, int4, int8 or e4m3 weight stored (k,n), aligned rows)");
                 return (int32_t)cudaErrorNotSupported;
             }
         }
@@ -295,7 +295,7 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
         if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST && !wqbmm_decode_fast_eligible(&chunk)) return (int32_t)cudaErrorInvalidValue;
         return decode_chunk_launches(p, static_cast<cudaStream_t>(stream), kernel_choice);
     }
-    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE && p->w_dtype == ACL_INT8) {
+    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE && (p->w_dtype == ACL_INT8 || p->w_dtype == ACL_FLOAT8_E4M3FN)) {
         if (!wqbmm_decode8_eligible(p)) return (int32_t)cudaErrorInvalidValue;
         return wqbmm_decode8_launch(p, static_cast<cudaStream_t>(stream));
     }

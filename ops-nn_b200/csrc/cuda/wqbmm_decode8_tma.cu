@@ -1,4 +1,5 @@
-// Weight-only quant matmul, streaming decode kernel for 8-bit integer weights (W8A16, m <= 16, INT8 weight stored (k,n)).
+// Weight-only quant matmul, streaming decode kernel for 8-bit weights (W8A16 / A16F8, m <= 16, INT8 or FLOAT8_E4M3FN weight stored
+// (k,n)).
 //
 // The reference runs this regime on its n-first kernels (weight_quant_batch_matmul_v2/op_kernel/arch35/n_first/*); the arithmetic
 // is the golden's: w' = rn(rn(w + offset) * scale) in x's dtype, y = x @ w' in fp32 (wqbmmv2_kernel_golden.py:199-297).
@@ -11,6 +12,13 @@
 // even column feeds one MMA tile, the odd one another (the column permutation is undone when y is written). A byte b = w mod 256
 // becomes bf16(w) exactly with two logic ops and one subtraction: (b & 0x7f) | 0x4300 is 128 + (b & 0x7f), (b & 0x80) | 0x4300 is
 // 128 or 256, their difference is w (fp16: 0x6400, 1024 + ..., same idea with ten mantissa bits).
+//
+// FLOAT8_E4M3FN weights (no offset: the API refuses one for fp8 weights, so w' = rn(w * scale), wqbmmv2_kernel_golden.py:199-297):
+// the seven magnitude bits are moved under the 16-bit type's sign so that the e4m3 exponent sits in the low four bits of the wider
+// exponent field and the three mantissa bits at the top of the wider mantissa; that reads as w * 2^-120 (bf16) / w * 2^-8 (fp16),
+// subnormals and zero included, and one exact multiplication by 2^120 / 2^8 gives w. The two NaN encodings (magnitude 0x7f) would
+// read as +-480: every weight register is also tested for a byte with all seven magnitude bits set, the hits are ORed per column,
+// and a column that met one is written as NaN, as the golden's x @ w' does.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "wqbmm_decode_common.cuh"
@@ -33,11 +41,17 @@ struct Num8;
 template <>
 struct Num8<true> {
     static constexpr uint32_t kLowMask = 0x007F007Fu, kHighMask = 0x00800080u, kMagic = 0x43004300u;  // bf16 128.0
+    // e4m3: magnitude to bits 10..4 of each half (shift left 4 from the low byte, right 4 from the high byte), then * 2^120
+    static constexpr int kF8Up = 4, kF8Down = 4;
+    static constexpr uint32_t kF8Mag = 0x07F007F0u, kF8Rebias = 0x7B807B80u;
 };
 template <>
 struct Num8<false> {
     // fp16 has ten mantissa bits: the whole byte fits under 0x6400 (1024.0): (b ^ 0x80) | 0x6400 = 1024 + 128 + w
     static constexpr uint32_t kLowMask = 0x00FF00FFu, kHighMask = 0x00800080u, kMagic = 0x64006400u;
+    // e4m3: magnitude to bits 13..7 of each half, then * 2^8
+    static constexpr int kF8Up = 7, kF8Down = 1;
+    static constexpr uint32_t kF8Mag = 0x3F803F80u, kF8Rebias = 0x5C005C00u;
 };
 
 __device__ __forceinline__ void d8_ldsm4(uint32_t addr, uint32_t (&r)[4])
@@ -83,7 +97,7 @@ struct D8Args {
     int32_t stages_per_group;  // group_size / 64, or "never" for a single group
 };
 
-template <bool kBf16, bool kHasOffset>
+template <bool kBf16, bool kHasOffset, bool kFp8>
 __global__ void __launch_bounds__(kThreads, 2)
 wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const D8Args ta)
 {
@@ -199,23 +213,47 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         if (kHasOffset) v = N::add(v, of[kHasOffset ? t : 0]);
         return N::mul(v, sc[t]);
     };
+    // the same for two e4m3 bytes: `mag` holds them shifted so that the magnitude bits lie under kF8Mag, `sgn` so that the sign bits
+    // are bits 15 and 31
+    auto deq_f8 = [&](uint32_t mag, uint32_t sgn, int t) {
+        uint32_t v;
+        mag &= N8::kF8Mag;
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(sgn), "n"(0x80008000), "r"(mag));  // (sgn & 0x8000) | mag
+        return N::mul(N::mul(v, N8::kF8Rebias), sc[t]);
+    };
+    // bit 7 of a byte of nan_seen[chunk]: that byte position (even column: bytes 0 and 2, odd column: bytes 1 and 3) held 0x7f / 0xff
+    uint32_t nan_seen[kFp8 ? 4 : 1];
+    if (kFp8) nan_seen[0] = nan_seen[kFp8 ? 1 : 0] = nan_seen[kFp8 ? 2 : 0] = nan_seen[kFp8 ? 3 : 0] = 0u;
+    auto note_nan = [&](uint32_t x, int chunk) {
+        const uint32_t carry = (x & 0x7F7F7F7Fu) + 0x01010101u;  // 0x7f + 1 reaches bit 7, nothing crosses into the next byte
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(nan_seen[kFp8 ? chunk : 0]) : "r"(carry), "n"(0x80808080), "r"(nan_seen[kFp8 ? chunk : 0]));
+    };
+    // the four B-fragment registers of one 16-byte chunk (r0: rows 0-7, r1: rows 8-15): even column -> tile 2 chunk, odd -> + 1
+    auto chunk_mmas = [&](uint32_t r0, uint32_t r1, int chunk, const uint32_t(&af)[4]) {
+        uint32_t e0, e1, o0, o1;
+        if (kFp8) {
+            note_nan(r0, chunk);
+            note_nan(r1, chunk);
+            e0 = deq_f8(r0 << N8::kF8Up, r0 << 8, 2 * chunk);
+            e1 = deq_f8(r1 << N8::kF8Up, r1 << 8, 2 * chunk);
+            o0 = deq_f8(r0 >> N8::kF8Down, r0, 2 * chunk + 1);
+            o1 = deq_f8(r1 >> N8::kF8Down, r1, 2 * chunk + 1);
+        } else {
+            e0 = deq(r0, 2 * chunk);
+            e1 = deq(r1, 2 * chunk);
+            o0 = deq(r0 >> 8, 2 * chunk + 1);
+            o1 = deq(r1 >> 8, 2 * chunk + 1);
+        }
+        N::mma_free(total[2 * chunk], af, e0, e1);
+        N::mma_free(total[2 * chunk + 1], af, o0, o1);
+    };
     // one k-step: 8 registers (two ldmatrix.x4.trans) -> 16 B-fragment registers -> 8 MMAs
     auto compute = [&](const uint32_t(&wa)[4], const uint32_t(&wb)[4], const uint32_t(&af)[4]) {
         // wa: chunks 0, 1 as (rows 0-7, rows 8-15) pairs; wb: chunks 2, 3
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-            const uint32_t e0 = deq(wa[2 * cc], 2 * cc), e1 = deq(wa[2 * cc + 1], 2 * cc);
-            const uint32_t o0 = deq(wa[2 * cc] >> 8, 2 * cc + 1), o1 = deq(wa[2 * cc + 1] >> 8, 2 * cc + 1);
-            N::mma_free(total[2 * cc], af, e0, e1);
-            N::mma_free(total[2 * cc + 1], af, o0, o1);
-        }
+        for (int cc = 0; cc < 2; ++cc) chunk_mmas(wa[2 * cc], wa[2 * cc + 1], cc, af);
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-            const uint32_t e0 = deq(wb[2 * cc], 4 + 2 * cc), e1 = deq(wb[2 * cc + 1], 4 + 2 * cc);
-            const uint32_t o0 = deq(wb[2 * cc] >> 8, 5 + 2 * cc), o1 = deq(wb[2 * cc + 1] >> 8, 5 + 2 * cc);
-            N::mma_free(total[4 + 2 * cc], af, e0, e1);
-            N::mma_free(total[5 + 2 * cc], af, o0, o1);
-        }
+        for (int cc = 0; cc < 2; ++cc) chunk_mmas(wb[2 * cc], wb[2 * cc + 1], 2 + cc, af);
     };
 
     // ---- per-lane ldmatrix addresses inside a stage (128-byte swizzle: 16-byte chunk index ^ (row & 7)) ----
@@ -308,6 +346,19 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         __syncthreads();
         if (!a.cluster) return;
     }
+    if (kFp8) {
+        // A column whose weights held a NaN encoding becomes NaN. The lanes 4 c .. 4 c + 3 hold column c of a tile's B fragments,
+        // lane (g, q) holds columns 2 q and 2 q + 1 of its accumulators (rows g and g + 8).
+        const float nan = __int_as_float(0x7FC00000);
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+            const uint32_t mine = nan_seen[kFp8 ? t >> 1 : 0] & ((t & 1) ? 0x80008000u : 0x00800080u);
+            const uint32_t cols = __ballot_sync(0xffffffffu, mine != 0u);
+            const uint32_t pair = (cols >> (8 * (lane & 3))) & 0xFFu;
+            if (pair & 0x0Fu) total[t][0] = total[t][2] = nan;
+            if (pair & 0xF0u) total[t][1] = total[t][3] = nan;
+        }
+    }
     // every warp is past its last stage (barrier above): the stage buffers are free to hold the fragments
     if (a.cluster) cluster_combine_and_store<kBf16, 2>(a, total, strip, warp, lane, tid, smem0, !aborted);
     else combine_and_store<kBf16, 2>(a, total, c, strip, warp, lane, tid, &s_reduce);
@@ -339,16 +390,18 @@ bool d8_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-std::atomic<uint64_t> g_d8_configured[4];
+std::atomic<uint64_t> g_d8_configured[6];
 
-// variant = 2 bf16 + has_offset
+// variant = 2 bf16 + has_offset for INT8 weights, 4 + bf16 for FLOAT8_E4M3FN weights
 const void* d8_kernel(int variant)
 {
     switch (variant) {
-        case 0: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false>);
-        case 1: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, true>);
-        case 2: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false>);
-        default: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, true>);
+        case 0: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false, false>);
+        case 1: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, true, false>);
+        case 2: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false, false>);
+        case 3: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, true, false>);
+        case 4: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false, true>);
+        default: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false, true>);
     }
 }
 
@@ -402,10 +455,12 @@ constexpr int k8MaxGrid = 148 * 4 * 2;
 
 uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
 
-// INT8 weight stored (k,n), m <= 16, scale (and offset) in x's dtype per channel / per tensor / per k-group of whole 64-row stages.
+// INT8 or FLOAT8_E4M3FN (no offset) weight stored (k,n), m <= 16, scale (and offset) in x's dtype per channel / per tensor / per
+// k-group of whole 64-row stages.
 bool wqbmm_decode8_eligible(const OpsnnWqbmmParams* p)
 {
-    if (p->w_dtype != ACL_INT8 || p->trans_w != 0 || p->nz_k0 != 0) return false;
+    if ((p->w_dtype != ACL_INT8 && p->w_dtype != ACL_FLOAT8_E4M3FN) || p->trans_w != 0 || p->nz_k0 != 0) return false;
+    if (p->w_dtype == ACL_FLOAT8_E4M3FN && p->offset != nullptr) return false;
     if (p->scale_dtype == ACL_FLOAT8_E8M0) return false;
     if (p->m < 1 || p->m > 16 || p->k < 16 || p->k % 16 != 0) return false;
     if (p->n % 16 != 0 || p->w_ld % 16 != 0 || p->x_ld % 8 != 0) return false;  // 16-byte tensor-map pitches; column pairs for the scale loads
@@ -443,7 +498,7 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / k8StageSteps);
     const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
 
-    const int variant = (bf16 ? 2 : 0) + (has_off ? 1 : 0);
+    const int variant = p->w_dtype == ACL_FLOAT8_E4M3FN ? 4 + (bf16 ? 1 : 0) : (bf16 ? 2 : 0) + (has_off ? 1 : 0);
     cudaError_t crc = d8_configure_variant(variant);
     if (crc != cudaSuccess) return (int32_t)crc;
     int64_t splits = (2 * (int64_t)current_sm_count()) / a.strips;

@@ -337,6 +337,118 @@ def test_narrow_output_is_planned_as_clusters(aclnn):
     assert strips == 48 and splits == 6 and cluster == 0
 
 
+F8_CASES = [
+    # x dtype, m, k, n, group, bias, NaN encodings planted
+    ("bfloat16", 16, 2048, 1024, 0, False, False),     # per-channel
+    ("float16", 16, 2048, 768, 128, False, False),     # per-group, fp16
+    ("bfloat16", 5, 4096, 1040, 0, True, True),        # ragged last strip, m < 16, bias, NaN weights
+    ("float16", 1, 8192, 512, 64, True, True),         # one group per stage, m = 1
+]
+
+
+def _f8_tensor(aclnn, codes):
+    import torch
+
+    from gpu_util import DEV
+
+    return aclnn.Tensor(codes.shape, "float8_e4m3fn", torch.from_numpy(codes.copy()).to(DEV))
+
+
+def _dev16(aclnn, a):
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV
+
+    if a is None:
+        return None
+    if a.dtype == np.dtype(ml_dtypes.bfloat16):
+        return aclnn.from_torch(torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV))
+    return aclnn.from_torch(torch.from_numpy(a.copy()).to(DEV))
+
+
+@pytest.mark.parametrize("case", F8_CASES, ids=[str(c) for c in F8_CASES])
+def test_a16f8_small_m_streaming_kernel(aclnn, case):
+    """FLOAT8_E4M3FN weights at m <= 16 run on the 8-bit streaming kernel. Every byte code occurs (subnormals, both zeros, +-448);
+    the dequantised weight rn(w * scale) is the golden's (wqbmmv2_kernel_golden.py:199-297), so only the fp32 summation order
+    differs: <= 1 ulp of the output dtype. Where NaN encodings (0x7f, 0xff) are planted, exactly the columns that hold one are NaN."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    xdt, m, k, n, group, has_bias, plant = case
+    rng = np.random.default_rng(case_seed(case))
+    np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(np_dt)
+    codes = rng.integers(0, 256, (k, n)).astype(np.uint8)
+    codes[(codes & 0x7F) == 0x7F] ^= 0x01                # no NaN by chance (0x7f -> 0x7e = 448)
+    nan_cols = []
+    if plant:
+        nan_cols = [0, 1, 17, 510, 511, n - 1, n - 16]
+        for i, c in enumerate(nan_cols):
+            codes[(i * 997 + 3) % k, c] = 0x7F if i % 2 == 0 else 0xFF
+        codes[k - 1, 2] = 0xFF
+        nan_cols.append(2)
+    w = codes.view(ml_dtypes.float8_e4m3fn)
+    groups = k // group if group else 1
+    sc = rng.uniform(0.002, 0.01, (groups, n)).astype(np.float32).astype(np_dt)
+    bias = rng.uniform(-1, 1, n).astype(np.float32).astype(np_dt) if has_bias else None
+
+    y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
+    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes), _dev16(aclnn, sc if group else sc[0]), aclnn.from_torch(y), None,
+                                    _dev16(aclnn, bias), group)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
+    with np.errstate(invalid="ignore"):
+        want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, None, bias, group).astype(np.float64)
+    got = out_to_np(y).astype(np.float64)
+    assert not np.any(got == -7777.0)
+    is_nan = np.zeros(n, dtype=bool)
+    is_nan[nan_cols] = True
+    assert np.array_equal(np.isnan(want), np.broadcast_to(is_nan, want.shape))
+    assert np.array_equal(np.isnan(got), np.isnan(want)), "NaN columns differ"
+    ok = ~np.isnan(want)
+    ulp = 2.0 ** -7 if xdt == "bfloat16" else 2.0 ** -10
+    rms = np.sqrt(np.mean(want[ok] ** 2))
+    assert np.all(np.abs(got[ok] - want[ok]) <= ulp * np.maximum(np.abs(want[ok]), 0.05 * rms) * 1.01)
+
+
+@pytest.mark.parametrize("xdt", ["bfloat16", "float16"])
+def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt):
+    """With one-hot rows of x the product is the dequantised weight row itself (every other term is a zero), so the streaming kernel's
+    e4m3 -> 16-bit conversion and its single rounding of w * scale are compared bit for bit with the oracle, for every finite byte
+    code in every selected row (subnormals and both zeros included) and for scales that push products into the 16-bit type's
+    subnormal range."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV, out_to_np
+
+    m, k, n, group = 16, 2048, 1024, 128
+    rng = np.random.default_rng(41 if xdt == "bfloat16" else 43)
+    np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
+    rows = rng.choice(k, m, replace=False)
+    x = np.zeros((m, k), dtype=np_dt)
+    x[np.arange(m), rows] = 1
+    codes = ((np.arange(k)[:, None] * 7 + np.arange(n)[None, :] * 13) % 256).astype(np.uint8)   # every code in every row
+    codes[(codes & 0x7F) == 0x7F] ^= 0x01
+    w = codes.view(ml_dtypes.float8_e4m3fn)
+    tiny = 2.0 ** -120 if xdt == "bfloat16" else 2.0 ** -14
+    sc = rng.uniform(0.002, 0.01, (k // group, n)).astype(np.float32)
+    sc[:, 0::5] *= -1
+    sc[:, 1::7] = tiny * rng.uniform(1, 2, sc[:, 1::7].shape)        # products in the subnormal range of the 16-bit type
+    sc = sc.astype(np_dt)
+    y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
+    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes), _dev16(aclnn, sc), aclnn.from_torch(y), None, None, group)
+    torch.cuda.synchronize()
+    assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, None, None, group)
+    got = out_to_np(y)
+    assert np.array_equal(got.astype(np.float32), want.astype(np.float32))
+    assert np.count_nonzero(want.astype(np.float32)) > m * n // 2
+
+
 W8_CASES = [
     # x dtype, m, k, n, group, offset, bias
     ("bfloat16", 16, 2048, 1024, 0, False, False),     # per-channel, symmetric: the common W8A16 form
