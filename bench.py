@@ -808,7 +808,9 @@ DEV_WORKLOADS = {
     "c2m32": (1, 32, 8192, 28672, "w4a16_prefill"),  # 16 < m <= 48: the decode kernel once per 16 rows
     "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
     "f8m16": (1, 16, 8192, 28672, "a16f8"),            # the same with FLOAT8_E4M3FN weights (random finite byte codes)
-    "w8m16": (1, 16, 8192, 28672, "w8a16"),            # the headline shape with INT8 weights (per-channel bf16 scale): streaming kernel, 235 MB
+    "w8m16": (1, 16, 8192, 28672, "w8a16"),
+    "w8m16t": (1, 16, 8192, 28672, "w8a16_t"),         # ... the weight stored (n,k)
+    "f8m16t": (1, 16, 8192, 28672, "a16f8_t"),            # the headline shape with INT8 weights (per-channel bf16 scale): streaming kernel, 235 MB
 }
 
 
@@ -883,20 +885,21 @@ def run_dev_workload(args):
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
         call = lambda i: aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128, workspace=workspace)  # noqa: E731
         nbytes = k * n // 2 + 2 * (k // 128) * n * 2 + 2 * m * k + 2 * m * n
-    elif kind in ("w8a16", "a16f8"):
+    elif kind in ("w8a16", "a16f8", "w8a16_t", "a16f8_t"):
         sets = 3  # 3 x 235 MB rotated
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         x = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
-        ws8 = [torch.randint(-128, 128, (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
+        tw = kind.endswith("_t")
+        ws8 = [torch.randint(-128, 128, (n, k) if tw else (k, n), generator=gen, device=dev, dtype=torch.int8) for _ in range(sets)]
         scale = (torch.rand((n,), generator=gen, device=dev) * 0.008 + 0.002).to(torch.bfloat16)
         dx, dsc, dout = aclnn.from_torch(x), aclnn.from_torch(scale), aclnn.from_torch(out)
-        if kind == "a16f8":
+        if kind.startswith("a16f8"):
             for t_ in ws8:  # every byte code but the two NaN encodings
                 u8 = t_.view(torch.uint8)
                 u8[(u8 & 0x7F) == 0x7F] = 0x7E
-            dws = [aclnn.Tensor((k, n), "float8_e4m3fn", t_.view(torch.uint8)) for t_ in ws8]
+            dws = [aclnn.Tensor((k, n), "float8_e4m3fn", t_.view(torch.uint8), (1, k) if tw else None) for t_ in ws8]
         else:
-            dws = [aclnn.from_torch(t_) for t_ in ws8]
+            dws = [aclnn.from_torch(t_.t() if tw else t_) for t_ in ws8]
         ws_bytes = aclnn.weight_quant_batch_matmul(dx, dws[0], dsc, dout, None, None, 0)
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
         call = lambda i: aclnn.weight_quant_batch_matmul(dx, dws[i % sets], dsc, dout, None, None, 0, workspace=workspace)  # noqa: E731
@@ -949,7 +952,7 @@ def run_dev_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w4a16_prefill_prepared", "w8a16", "a16f8") else 4500.0)
+    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w4a16_prefill_prepared", "w8a16", "a16f8", "w8a16_t", "a16f8_t") else 4500.0)
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
                       "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,

@@ -364,6 +364,266 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     else combine_and_store<kBf16, 2>(a, total, c, strip, warp, lane, tid, &s_reduce);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// The same regime with the weight stored (n,k), k contiguous - the transposed view of the API (weight.t() of an (n,k) tensor).
+//
+// Same grid, ring, refill duty, bounded waits and combine; what changes is the shape of a stage and the fragments. A stage is still
+// 64 k rows of the strip's 512 columns + x, 34 KB: eight boxes (one per warp) of 64 bytes of k x 64 weight rows in the 64-byte
+// swizzle (16-byte chunk index ^ ((row >> 1) & 3)). A row of a box is the 64 k values of one column, so plain ldmatrix (no
+// transposition) hands lane (g, q) the bytes k = 16 j + 4 q .. + 3 of column 8 t + g: four matrices per instruction = four tiles of
+// one 16-row k-step j. The two byte pairs the conversion works on are (4q, 4q+2) and (4q+1, 4q+3); they become the two B registers
+// of one MMA, and the A fragment is permuted to match: x[row][4q .. 4q+3] is one 8-byte shared load, its even elements feed the
+// first half of the MMA's k, its odd elements the second (a sum over k does not care in which order the MMA sees k). Tile t is
+// columns 8 t .. 8 t + 7 of the warp's 64: no column permutation to undo when y is written.
+constexpr int k8TBox = 64 * 64;  // one warp's 64 columns x 64 k
+
+template <bool kBf16, bool kHasOffset, bool kFp8>
+__global__ void __launch_bounds__(kThreads, 2)
+wqbmm_decode8t_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const D8Args ta)
+{
+    using N = Num<kBf16>;
+    using N8 = Num8<kBf16>;
+    const DecodeArgs& a = ta.d;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    __shared__ int s_reduce;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ int s_issued[k8Stages];
+    extern __shared__ uint8_t dyn_raw[];
+    const uint32_t smem0 = (ptx::smem_u32(dyn_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem0 + k8Stages * k8Stage;  // full[i] at bar0 + 8 i, empty[i] at bar0 + 64 + 8 i
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int64_t c = blockIdx.x;
+    const int64_t strip = a.cluster ? c / a.splits : c % a.strips;
+    const int64_t chunk = a.cluster ? c % a.splits : c / a.strips;
+    const int st_a = (int)((chunk * ta.total_stages) / a.splits);
+    const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
+    const int nst = st_b - st_a;
+    const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
+    const int32_t strip_row = (int32_t)(strip * kStripCols);
+
+    if (tid == 0) {
+        s_abort = 0u;
+        for (int i = 0; i < k8Stages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8u * i), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 64u + 8u * i), "r"((uint32_t)kWarps) : "memory");
+            s_issued[i] = -1;
+        }
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_x);
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    volatile uint32_t* abort_flag = &s_abort;
+
+    auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
+        const uint32_t fb = bar0 + 8u * buf;
+        const uint32_t dst = smem0 + (uint32_t)buf * k8Stage;
+        const int32_t krow = (st_a + t) * k8StageRows;
+        s_issued[buf] = t;
+        ptx::mbar_expect_tx_a(fb, (uint32_t)k8Stage);
+#pragma unroll
+        for (int b = 0; b < kWarps; ++b) d8_tma_2d(dst + b * k8TBox, &map_w, fb, krow, strip_row + kWarpCols * b);
+        d8_tma_2d(dst + kWarps * k8TBox, &map_x, fb, krow * 2, 0);
+    };
+    if (tid == 0) {
+        const int pro = nst < k8Stages ? nst : k8Stages;
+        for (int t = 0; t < pro; ++t) issue_stage(t, t);
+    }
+
+    float total[kTiles][4];
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) total[t][0] = total[t][1] = total[t][2] = total[t][3] = 0.f;
+
+    // ---- scale / offset of the current k-group: tile t is column 8 t + g for this lane; two tiles' values share a register until the
+    // group becomes current, any element strides (a scale stored (n, groups) is read in place) ----
+    const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+    const int64_t n_groups = (a.ksteps + spg - 1) / spg;
+    uint32_t sc[kTiles], of[kHasOffset ? kTiles : 1], rs_next[4], ro_next[kHasOffset ? 4 : 1];
+    auto fetch = [&](int64_t group) {
+        const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+        const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+#pragma unroll
+        for (int t2 = 0; t2 < 4; ++t2) {
+            const int64_t c0 = warp_col + 16 * t2 + g, c1 = c0 + 8;
+            const int64_t e0 = (c0 < a.n ? c0 : 0) * (int64_t)a.scale_sn, e1 = (c1 < a.n ? c1 : 0) * (int64_t)a.scale_sn;
+            rs_next[t2] = (uint32_t)__ldg(sp + e0) | ((uint32_t)__ldg(sp + e1) << 16);
+            if (kHasOffset) ro_next[kHasOffset ? t2 : 0] = (uint32_t)__ldg(op + e0) | ((uint32_t)__ldg(op + e1) << 16);
+        }
+    };
+    auto load_group = [&](int64_t group) {
+        if (group >= n_groups) group = n_groups - 1;
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {  // each value in both halves of a register: the halves are two k rows of one column
+            const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
+            sc[t] = prmt(rs_next[t >> 1], rs_next[t >> 1], sel);
+            if (kHasOffset) of[kHasOffset ? t : 0] = prmt(ro_next[kHasOffset ? t >> 1 : 0], ro_next[kHasOffset ? t >> 1 : 0], sel);
+        }
+        fetch(min(group + 1, n_groups - 1));
+    };
+    // two bytes (in the low byte of each half) -> two dequantised weights
+    auto deq = [&](uint32_t x, int t) {
+        uint32_t lo, v;
+        if (kBf16) {
+            uint32_t hi;
+            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(lo) : "r"(x), "n"(N8::kLowMask), "n"(N8::kMagic));   // (x & mask) | magic
+            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(hi) : "r"(x), "n"(N8::kHighMask), "n"(N8::kMagic));
+            v = N::sub(lo, hi);
+        } else {
+            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(lo) : "r"(x), "n"(N8::kLowMask), "n"(0x64806480));
+            v = N::sub(lo, 0x64806480u);
+        }
+        if (kHasOffset) v = N::add(v, of[kHasOffset ? t : 0]);
+        return N::mul(v, sc[t]);
+    };
+    auto deq_f8 = [&](uint32_t mag, uint32_t sgn, int t) {
+        uint32_t v;
+        mag &= N8::kF8Mag;
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(sgn), "n"(0x80008000), "r"(mag));  // (sgn & 0x8000) | mag
+        return N::mul(N::mul(v, N8::kF8Rebias), sc[t]);
+    };
+    // e4m3 NaN encodings: all four bytes of a register belong to the tile's one column of this lane
+    uint32_t nan_seen[kFp8 ? kTiles : 1];
+    if (kFp8) {
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) nan_seen[kFp8 ? t : 0] = 0u;
+    }
+    auto tile_mma = [&](uint32_t r, int t, const uint32_t(&af)[4]) {
+        uint32_t b0, b1;
+        if (kFp8) {
+            const uint32_t carry = (r & 0x7F7F7F7Fu) + 0x01010101u;
+            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(nan_seen[kFp8 ? t : 0]) : "r"(carry), "n"(0x80808080), "r"(nan_seen[kFp8 ? t : 0]));
+            b0 = deq_f8(r << N8::kF8Up, r << 8, t);
+            b1 = deq_f8(r >> N8::kF8Down, r, t);
+        } else {
+            b0 = deq(r, t);
+            b1 = deq(r >> 8, t);
+        }
+        N::mma_free(total[t], af, b0, b1);  // b0: k = 4q, 4q+2; b1: k = 4q+1, 4q+3 of this 16-row step
+    };
+    auto compute = [&](const uint32_t(&wa)[4], const uint32_t(&wb)[4], const uint32_t(&af)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile_mma(wa[i], i, af);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile_mma(wb[i], 4 + i, af);
+    };
+    // A fragment of one k-step, permuted like the B registers: rows g and g + 8, x[row][4q .. 4q+3]
+    auto load_a = [&](uint32_t addr, uint32_t(&af)[4]) {
+        uint32_t l0, h0, l1, h1;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(l0), "=r"(h0) : "r"(addr));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+1024];" : "=r"(l1), "=r"(h1) : "r"(addr));
+        af[0] = prmt(l0, h0, 0x5410u);
+        af[1] = prmt(l1, h1, 0x5410u);
+        af[2] = prmt(l0, h0, 0x7632u);
+        af[3] = prmt(l1, h1, 0x7632u);
+    };
+
+    // ---- per-lane addresses inside a stage; k-step j is the 16-byte chunk j of a weight row (address ^ 16 j: the swizzle only
+    // touches those two bits) and the chunk pair j of an x row (address ^ 32 j) ----
+    const int li = lane & 7, lj = lane >> 3;
+    const uint32_t wlane_a = (uint32_t)warp * k8TBox + (uint32_t)(8 * lj + li) * 64u + ((uint32_t)((li >> 1) & 3) << 4);  // tiles 0-3
+    const uint32_t wlane_b = wlane_a + 32u * 64u;                                                                        // tiles 4-7
+    const uint32_t xlane = (uint32_t)kWarps * k8TBox + (uint32_t)g * 128u + ((uint32_t)(((q >> 1) ^ g) & 7) << 4) + 8u * (uint32_t)(q & 1);
+
+    int64_t group = ((int64_t)st_a * k8StageSteps) / spg;
+    fetch(min(group, n_groups - 1));
+    load_group(group);
+    int until_change = ta.stages_per_group - (st_a % ta.stages_per_group);
+
+    uint32_t wa0[4], wb0[4], a0[4], wa1[4], wb1[4], a1[4];
+    int buf = 0;
+    uint32_t par = 0;
+    bool ok = nst > 0;
+    if (ok) {
+        ok = d8_wait(bar0, 0u, abort_flag, 1u);
+        d8_ldsm4(smem0 + wlane_a, wa0);
+        d8_ldsm4(smem0 + wlane_b, wb0);
+        load_a(smem0 + xlane, a0);
+    }
+    const int duty = (warp + 8 * 8 - (k8Stages - 1)) & 7;  // this warp refills when (stage index & 7) == duty
+    for (int j = 0; j < nst && ok; ++j) {
+        const uint32_t sbase = smem0 + (uint32_t)buf * k8Stage;
+        const uint32_t wba = sbase + wlane_a, wbb = sbase + wlane_b, xb = sbase + xlane;
+        if (j >= 1 && (j & 7) == duty && j + k8Stages - 1 < nst) {
+            if (lane == 0) {
+                const int pbuf = buf == 0 ? k8Stages - 1 : buf - 1;
+                const uint32_t ppar = buf == 0 ? par ^ 1u : par;
+                if (d8_wait(bar0 + 64u + 8u * pbuf, ppar, abort_flag, 2u)) issue_stage(j + k8Stages - 1, pbuf);
+            }
+            __syncwarp();
+        }
+        if (j > 0 && until_change == 0) {
+            load_group(++group);
+            until_change = ta.stages_per_group;
+        }
+        // step 0
+        d8_ldsm4(wba ^ 16u, wa1);
+        d8_ldsm4(wbb ^ 16u, wb1);
+        load_a(xb ^ 32u, a1);
+        compute(wa0, wb0, a0);
+        // step 1
+        d8_ldsm4(wba ^ 32u, wa0);
+        d8_ldsm4(wbb ^ 32u, wb0);
+        load_a(xb ^ 64u, a0);
+        compute(wa1, wb1, a1);
+        // step 2
+        d8_ldsm4(wba ^ 48u, wa1);
+        d8_ldsm4(wbb ^ 48u, wb1);
+        load_a(xb ^ 96u, a1);
+        compute(wa0, wb0, a0);
+        // step 3, after the first fragments of the next stage have been requested
+        int nbuf = buf + 1;
+        uint32_t npar = par;
+        if (nbuf == k8Stages) { nbuf = 0; npar ^= 1u; }
+        if (j + 1 < nst) {
+            ok = d8_wait(bar0 + 8u * nbuf, npar, abort_flag, 1u);
+            const uint32_t nb = smem0 + (uint32_t)nbuf * k8Stage;
+            d8_ldsm4(nb + wlane_a, wa0);
+            d8_ldsm4(nb + wlane_b, wb0);
+            load_a(nb + xlane, a0);
+        }
+        compute(wa1, wb1, a1);
+        --until_change;
+        __syncwarp();
+        if (lane == 0) d8_arrive(bar0 + 64u + 8u * buf);
+        buf = nbuf;
+        par = npar;
+    }
+
+    const bool aborted = __syncthreads_or(s_abort != 0u) != 0;
+    if (aborted) {
+        // A wait gave up. Nothing is written; the copies already issued get a bounded time to land before the CTA leaves.
+        if (tid == 0) {
+            for (int i = 0; i < k8Stages; ++i) {
+                const int t = s_issued[i];
+                if (t < 0) continue;
+                const uint32_t p = (uint32_t)(t / k8Stages) & 1u;
+                for (uint32_t it = 0; it < k8Polls; ++it)
+                    if (ptx::mbar_try_wait_a(bar0 + 8u * i, p)) break;
+            }
+        }
+        __syncthreads();
+        if (!a.cluster) return;
+    }
+    if (kFp8) {
+        // lanes 4 c .. 4 c + 3 hold column c of a tile's weights; lane (g, q) holds columns 2 q, 2 q + 1 of its accumulators
+        const float nan = __int_as_float(0x7FC00000);
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+            const uint32_t cols = __ballot_sync(0xffffffffu, nan_seen[kFp8 ? t : 0] != 0u);
+            const uint32_t pair = (cols >> (8 * q)) & 0xFFu;
+            if (pair & 0x0Fu) total[t][0] = total[t][2] = nan;
+            if (pair & 0xF0u) total[t][1] = total[t][3] = nan;
+        }
+    }
+    if (a.cluster) cluster_combine_and_store<kBf16, 3>(a, total, strip, warp, lane, tid, smem0, !aborted);
+    else combine_and_store<kBf16, 3>(a, total, c, strip, warp, lane, tid, &s_reduce);
+}
+
 using D8EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -378,30 +638,38 @@ D8EncodeFn d8_encoder()
     return fn;
 }
 
-bool d8_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows)
+bool d8_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows,
+               uint32_t box_inner = 128, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B)
 {
     D8EncodeFn enc = d8_encoder();
     if (enc == nullptr) return false;
     cuuint64_t dims[2] = {inner_bytes, rows};
     cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-std::atomic<uint64_t> g_d8_configured[6];
+std::atomic<uint64_t> g_d8_configured[12];
 
-// variant = 2 bf16 + has_offset for INT8 weights, 4 + bf16 for FLOAT8_E4M3FN weights
+// variant = 2 bf16 + has_offset for INT8 weights, 4 + bf16 for FLOAT8_E4M3FN weights; + 6 for a weight stored (n,k)
 const void* d8_kernel(int variant)
 {
     switch (variant) {
+        case 6: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<false, false, false>);
+        case 7: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<false, true, false>);
+        case 8: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<true, false, false>);
+        case 9: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<true, true, false>);
+        case 10: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<false, false, true>);
+        case 11: return reinterpret_cast<const void*>(&wqbmm_decode8t_tma_kernel<true, false, true>);
         case 0: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false, false>);
         case 1: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, true, false>);
         case 2: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false, false>);
         case 3: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, true, false>);
         case 4: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<false, false, true>);
-        default: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false, true>);
+        case 5: return reinterpret_cast<const void*>(&wqbmm_decode8_tma_kernel<true, false, true>);
+        default: return nullptr;
     }
 }
 
@@ -455,21 +723,25 @@ constexpr int k8MaxGrid = 148 * 4 * 2;
 
 uint64_t wqbmm_decode_workspace_size(const OpsnnWqbmmParams* p);
 
-// INT8 or FLOAT8_E4M3FN (no offset) weight stored (k,n), m <= 16, scale (and offset) in x's dtype per channel / per tensor / per
-// k-group of whole 64-row stages.
+// INT8 or FLOAT8_E4M3FN (no offset) weight stored (k,n) or (n,k), m <= 16, scale (and offset) in x's dtype per channel / per tensor /
+// per k-group of whole 64-row stages.
 bool wqbmm_decode8_eligible(const OpsnnWqbmmParams* p)
 {
-    if ((p->w_dtype != ACL_INT8 && p->w_dtype != ACL_FLOAT8_E4M3FN) || p->trans_w != 0 || p->nz_k0 != 0) return false;
+    if ((p->w_dtype != ACL_INT8 && p->w_dtype != ACL_FLOAT8_E4M3FN) || p->nz_k0 != 0) return false;
     if (p->w_dtype == ACL_FLOAT8_E4M3FN && p->offset != nullptr) return false;
     if (p->scale_dtype == ACL_FLOAT8_E8M0) return false;
     if (p->m < 1 || p->m > 16 || p->k < 16 || p->k % 16 != 0) return false;
     if (p->n % 16 != 0 || p->w_ld % 16 != 0 || p->x_ld % 8 != 0) return false;  // 16-byte tensor-map pitches; column pairs for the scale loads
     if (p->group_size != 0 && p->group_size % 64 != 0) return false;           // group changes at stage boundaries only
-    if (p->scale_sn != 0 && p->scale_sn != 1) return false;
-    if (p->scale_sn == 1 && p->group_size != 0 && p->scale_sg % 2 != 0) return false;
     auto aligned = [](const void* q, uintptr_t al) { return (reinterpret_cast<uintptr_t>(q) % al) == 0; };
     if (!aligned(p->w, 16) || !aligned(p->x, 16)) return false;
-    if (p->scale_sn == 1 && (!aligned(p->scale, 4) || (p->offset && !aligned(p->offset, 4)))) return false;
+    if (p->trans_w != 0) {  // scales are read one 16-bit element at a time, at any strides
+        if (p->scale_sn < 0 || p->scale_sn >= ((int64_t)1 << 31) || p->scale_sg < 0) return false;
+    } else {                // two adjacent columns per 32-bit load
+        if (p->scale_sn != 0 && p->scale_sn != 1) return false;
+        if (p->scale_sn == 1 && p->group_size != 0 && p->scale_sg % 2 != 0) return false;
+        if (p->scale_sn == 1 && (!aligned(p->scale, 4) || (p->offset && !aligned(p->offset, 4)))) return false;
+    }
     if (p->n >= ((int64_t)1 << 31) || p->k >= ((int64_t)1 << 30)) return false;
     return true;
 }
@@ -498,7 +770,7 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / k8StageSteps);
     const bool bf16 = p->x_dtype == ACL_BF16, has_off = p->offset != nullptr;
 
-    const int variant = p->w_dtype == ACL_FLOAT8_E4M3FN ? 4 + (bf16 ? 1 : 0) : (bf16 ? 2 : 0) + (has_off ? 1 : 0);
+    const int variant = (p->w_dtype == ACL_FLOAT8_E4M3FN ? 4 + (bf16 ? 1 : 0) : (bf16 ? 2 : 0) + (has_off ? 1 : 0)) + (p->trans_w != 0 ? 6 : 0);
     cudaError_t crc = d8_configure_variant(variant);
     if (crc != cudaSuccess) return (int32_t)crc;
     int64_t splits = (2 * (int64_t)current_sm_count()) / a.strips;
@@ -540,7 +812,9 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     a.nonce = next_nonce();
 
     CUtensorMap mw, mx;
-    if (!d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows) ||
+    const bool w_ok = p->trans_w != 0 ? d8_map_2d(&mw, p->w, (uint64_t)p->k, (uint64_t)p->n, (uint64_t)p->w_ld, kWarpCols, 64, CU_TENSOR_MAP_SWIZZLE_64B)
+                                      : d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows);
+    if (!w_ok ||
         !d8_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
     const cudaError_t rc = d8_launch_variant(variant, (int)grid64, cluster_policy, mw, mx, ta, stream);

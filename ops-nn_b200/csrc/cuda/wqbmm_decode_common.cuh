@@ -166,10 +166,11 @@ __device__ __forceinline__ void store_tile_y(const DecodeArgs& a, float (&acc)[k
                     for (int e = 0; e < 4; ++e) {
                         const int row = g + (e >> 1) * 8;
                         // kLayout 0: tile t is nibble t of the lane group's word; 1: the ldmatrix layout of the ring / TMA int4 kernels;
-                        // 2: the 8-bit kernel, tile t = (16-column chunk t / 2, even / odd columns of it)
+                        // 2: the 8-bit kernel, tile t = (16-column chunk t / 2, even / odd columns of it); 3: tile t = columns 8 t .. 8 t + 7
                 const int64_t col = colw + (kLayout == 0   ? 8 * (2 * q + (e & 1)) + t
                                             : kLayout == 1 ? 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3)
-                                                           : 16 * (t >> 1) + 2 * (2 * q + (e & 1)) + (t & 1));
+                                            : kLayout == 2 ? 16 * (t >> 1) + 2 * (2 * q + (e & 1)) + (t & 1)
+                                                           : 8 * t + 2 * q + (e & 1));
                         if (row < a.m && col < a.n) {
                             float f = acc[t][e];
                             if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));
@@ -324,7 +325,8 @@ __device__ __forceinline__ void cluster_combine_and_store(const DecodeArgs& a, f
                 const int row = g + (e >> 1) * 8;
                 const int64_t col = colw + (kLayout == 0   ? 8 * (2 * q + (e & 1)) + t
                                             : kLayout == 1 ? 32 * (t >> 2) + 4 * (2 * q + (e & 1)) + (t & 3)
-                                                           : 16 * (t >> 1) + 2 * (2 * q + (e & 1)) + (t & 1));
+                                            : kLayout == 2 ? 16 * (t >> 1) + 2 * (2 * q + (e & 1)) + (t & 1)
+                                                           : 8 * t + 2 * q + (e & 1));
                 if (row < a.m && col < a.n) {
                     float f = f4[e];
                     if (a.bias != nullptr) f = __fadd_rn(f, load_as_float(a.bias, col, a.bias_dtype));

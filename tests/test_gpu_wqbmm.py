@@ -338,33 +338,46 @@ def test_narrow_output_is_planned_as_clusters(aclnn):
 
 
 F8_CASES = [
-    # x dtype, m, k, n, group, bias, NaN encodings planted
-    ("bfloat16", 16, 2048, 1024, 0, False, False),     # per-channel
-    ("float16", 16, 2048, 768, 128, False, False),     # per-group, fp16
-    ("bfloat16", 5, 4096, 1040, 0, True, True),        # ragged last strip, m < 16, bias, NaN weights
-    ("float16", 1, 8192, 512, 64, True, True),         # one group per stage, m = 1
+    # x dtype, m, k, n, group, bias, NaN encodings planted, weight (and per-group scale) stored transposed
+    ("bfloat16", 16, 2048, 1024, 0, False, False, False),     # per-channel
+    ("float16", 16, 2048, 768, 128, False, False, False),     # per-group, fp16
+    ("bfloat16", 5, 4096, 1040, 0, True, True, False),        # ragged last strip, m < 16, bias, NaN weights
+    ("float16", 1, 8192, 512, 64, True, True, False),         # one group per stage, m = 1
+    ("float16", 16, 2048, 1024, 0, False, False, True),       # weight stored (n,k)
+    ("bfloat16", 16, 2048, 768, 128, False, True, True),
+    ("float16", 5, 4096, 1040, 0, True, True, True),
 ]
 
 
-def _f8_tensor(aclnn, codes):
+def _f8_tensor(aclnn, codes, trans=False):
     import torch
 
     from gpu_util import DEV
 
+    if trans:  # stored (n,k), described as the (k,n) view
+        stored = torch.from_numpy(np.ascontiguousarray(codes.T)).to(DEV)
+        return aclnn.Tensor(codes.shape, "float8_e4m3fn", stored, strides=(1, codes.shape[0]))
     return aclnn.Tensor(codes.shape, "float8_e4m3fn", torch.from_numpy(codes.copy()).to(DEV))
 
 
-def _dev16(aclnn, a):
+def _dev16_t(aclnn, a):
+    """A 2-D 16-bit array stored transposed, described as the view of its own shape."""
+    return aclnn.from_torch(_torch16(np.ascontiguousarray(a.T)).t())
+
+
+def _torch16(a):
     import ml_dtypes
     import torch
 
     from gpu_util import DEV
 
-    if a is None:
-        return None
     if a.dtype == np.dtype(ml_dtypes.bfloat16):
-        return aclnn.from_torch(torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV))
-    return aclnn.from_torch(torch.from_numpy(a.copy()).to(DEV))
+        return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV)
+    return torch.from_numpy(a.copy()).to(DEV)
+
+
+def _dev16(aclnn, a):
+    return None if a is None else aclnn.from_torch(_torch16(a))
 
 
 @pytest.mark.parametrize("case", F8_CASES, ids=[str(c) for c in F8_CASES])
@@ -377,7 +390,7 @@ def test_a16f8_small_m_streaming_kernel(aclnn, case):
 
     from gpu_util import DEV, out_to_np
 
-    xdt, m, k, n, group, has_bias, plant = case
+    xdt, m, k, n, group, has_bias, plant, trans = case
     rng = np.random.default_rng(case_seed(case))
     np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
     x = rng.standard_normal((m, k)).astype(np.float32).astype(np_dt)
@@ -396,8 +409,8 @@ def test_a16f8_small_m_streaming_kernel(aclnn, case):
     bias = rng.uniform(-1, 1, n).astype(np.float32).astype(np_dt) if has_bias else None
 
     y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
-    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes), _dev16(aclnn, sc if group else sc[0]), aclnn.from_torch(y), None,
-                                    _dev16(aclnn, bias), group)
+    d_sc = (_dev16_t(aclnn, sc) if trans else _dev16(aclnn, sc)) if group else _dev16(aclnn, sc[0])
+    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes, trans), d_sc, aclnn.from_torch(y), None, _dev16(aclnn, bias), group)
     torch.cuda.synchronize()
     assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
     with np.errstate(invalid="ignore"):
@@ -414,8 +427,9 @@ def test_a16f8_small_m_streaming_kernel(aclnn, case):
     assert np.all(np.abs(got[ok] - want[ok]) <= ulp * np.maximum(np.abs(want[ok]), 0.05 * rms) * 1.01)
 
 
+@pytest.mark.parametrize("trans", [False, True], ids=["(k,n)", "(n,k)"])
 @pytest.mark.parametrize("xdt", ["bfloat16", "float16"])
-def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt):
+def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt, trans):
     """With one-hot rows of x the product is the dequantised weight row itself (every other term is a zero), so the streaming kernel's
     e4m3 -> 16-bit conversion and its single rounding of w * scale are compared bit for bit with the oracle, for every finite byte
     code in every selected row (subnormals and both zeros included) and for scales that push products into the 16-bit type's
@@ -440,7 +454,8 @@ def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt):
     sc[:, 1::7] = tiny * rng.uniform(1, 2, sc[:, 1::7].shape)        # products in the subnormal range of the 16-bit type
     sc = sc.astype(np_dt)
     y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
-    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes), _dev16(aclnn, sc), aclnn.from_torch(y), None, None, group)
+    aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), _f8_tensor(aclnn, codes, trans), _dev16_t(aclnn, sc) if trans else _dev16(aclnn, sc),
+                                    aclnn.from_torch(y), None, None, group)
     torch.cuda.synchronize()
     assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
     want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, None, None, group)
@@ -450,11 +465,16 @@ def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt):
 
 
 W8_CASES = [
-    # x dtype, m, k, n, group, offset, bias
-    ("bfloat16", 16, 2048, 1024, 0, False, False),     # per-channel, symmetric: the common W8A16 form
-    ("bfloat16", 5, 4096, 1040, 0, True, True),        # ragged last strip, fewer than 16 rows, offset + bias
-    ("float16", 16, 2048, 768, 128, True, False),      # per-group (two stages per group), fp16
-    ("bfloat16", 1, 8192, 512, 64, False, True),       # one group per stage, m = 1
+    # x dtype, m, k, n, group, offset, bias, weight (and per-group scale / offset) stored transposed
+    ("bfloat16", 16, 2048, 1024, 0, False, False, False),     # per-channel, symmetric: the common W8A16 form
+    ("bfloat16", 5, 4096, 1040, 0, True, True, False),        # ragged last strip, fewer than 16 rows, offset + bias
+    ("float16", 16, 2048, 768, 128, True, False, False),      # per-group (two stages per group), fp16
+    ("bfloat16", 1, 8192, 512, 64, False, True, False),       # one group per stage, m = 1
+    ("bfloat16", 16, 2048, 1024, 0, False, False, True),      # weight stored (n,k), k contiguous
+    ("float16", 5, 4096, 1040, 0, True, True, True),
+    ("bfloat16", 16, 2048, 768, 128, True, False, True),      # scales stored (n, groups)
+    ("float16", 1, 8192, 512, 64, False, True, True),
+    ("bfloat16", 13, 4112, 2064, 0, True, False, True),       # k not a multiple of the 64-row stage, ragged strip
 ]
 
 
@@ -468,7 +488,7 @@ def test_w8a16_small_m_streaming_kernel(aclnn, case):
 
     from gpu_util import DEV, out_to_np
 
-    xdt, m, k, n, group, has_off, has_bias = case
+    xdt, m, k, n, group, has_off, has_bias, trans = case
     rng = np.random.default_rng(case_seed(case))
     np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
     x = rng.standard_normal((m, k)).astype(np.float32).astype(np_dt)
@@ -479,15 +499,18 @@ def test_w8a16_small_m_streaming_kernel(aclnn, case):
     bias = rng.uniform(-1, 1, n).astype(np.float32).astype(np_dt) if has_bias else None
 
     def dev(a):
-        if a is None:
-            return None
-        if a.dtype == np.dtype(ml_dtypes.bfloat16):
-            return aclnn.from_torch(torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16).to(DEV))
-        return aclnn.from_torch(torch.from_numpy(a.copy()).to(DEV))
+        return None if a is None else aclnn.from_torch(_torch16(a))
+
+    def dev_t(a):  # stored transposed, described as the (rows, cols) view the API takes
+        return None if a is None else aclnn.from_torch(_torch16(np.ascontiguousarray(a.T)).t())
 
     y = torch.full((m, n), -7777.0, dtype=torch.bfloat16 if xdt == "bfloat16" else torch.float16, device=DEV)
-    aclnn.weight_quant_batch_matmul(dev(x), dev(w), dev(sc if group else sc[0]), aclnn.from_torch(y), dev(of if (group or of is None) else of[0]),
-                                    dev(bias), group)
+    if trans:
+        aclnn.weight_quant_batch_matmul(dev(x), dev_t(w), dev_t(sc) if group else dev(sc[0]), aclnn.from_torch(y),
+                                        (dev_t(of) if group else dev(of[0])) if of is not None else None, dev(bias), group)
+    else:
+        aclnn.weight_quant_batch_matmul(dev(x), dev(w), dev(sc if group else sc[0]), aclnn.from_torch(y), dev(of if (group or of is None) else of[0]),
+                                        dev(bias), group)
     torch.cuda.synchronize()
     assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
     want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, bias, group).astype(np.float64)
