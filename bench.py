@@ -805,6 +805,7 @@ DEV_WORKLOADS = {
     "c2ps": (1, 256, 8192, 28672, "w4a16_prefill"),
     "c2pp": (1, 2048, 8192, 28672, "w4a16_prefill_prepared"),  # c2p with the weight dequantised once (opsnnWeightQuantPrepare)
     "c2pps": (1, 256, 8192, 28672, "w4a16_prefill_prepared"),
+    "c2nk": (1, 16, 8192, 28672, "w4a16_nk"),        # the headline shape with weight, scale and offset stored (n,k) / (n,groups)
     "c2m32": (1, 32, 8192, 28672, "w4a16_prefill"),  # 16 < m <= 48: the decode kernel once per 16 rows
     "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
     "f8m16": (1, 16, 8192, 28672, "a16f8"),            # the same with FLOAT8_E4M3FN weights (random finite byte codes)
@@ -885,6 +886,19 @@ def run_dev_workload(args):
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
         call = lambda i: aclnn.weight_quant_batch_matmul(d[0], d[1], d[2], d[4], d[3], None, 128, workspace=workspace)  # noqa: E731
         nbytes = k * n // 2 + 2 * (k // 128) * n * 2 + 2 * m * k + 2 * m * n
+    elif kind == "w4a16_nk":
+        sets = 4  # 4 x 117 MB rotated
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        x = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        wsets = [torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, device=dev, dtype=torch.int32) for _ in range(sets)]
+        scale = (torch.rand((n, k // 128), generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
+        offset = (torch.rand((n, k // 128), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
+        dx, dsc, dof, dout = aclnn.from_torch(x), aclnn.from_torch(scale.t()), aclnn.from_torch(offset.t()), aclnn.from_torch(out)
+        dws = [aclnn.from_torch(t_.t()) for t_ in wsets]
+        ws_bytes = aclnn.weight_quant_batch_matmul(dx, dws[0], dsc, dout, dof, None, 128)
+        workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        call = lambda i: aclnn.weight_quant_batch_matmul(dx, dws[i % sets], dsc, dout, dof, None, 128, workspace=workspace)  # noqa: E731
+        nbytes = k * n // 2 + 2 * (k // 128) * n * 2 + 2 * m * k + 2 * m * n
     elif kind in ("w8a16", "a16f8", "w8a16_t", "a16f8_t"):
         sets = 3  # 3 x 235 MB rotated
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
@@ -952,7 +966,7 @@ def run_dev_workload(args):
     ms = sum(ts) / len(ts)
     flops = 2.0 * b * m * k * n
     tf = flops / (ms * 1e-3) / 1e12
-    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w4a16_prefill_prepared", "w8a16", "a16f8", "w8a16_t", "a16f8_t") else 4500.0)
+    peak8 = 9000.0 if kind.startswith("mxfp4") else (2250.0 if kind in ("w4a16_prefill", "w4a16_prefill_prepared", "w8a16", "a16f8", "w8a16_t", "a16f8_t", "w4a16_nk") else 4500.0)
     print(json.dumps({"metric": "QBMM TFLOPS", "workload": args.workload, "kind": kind, "shape": [b, m, k, n], "value": tf,
                       "unit": "TOP/s" if kind.startswith("int8") else "TFLOP/s", "ms_per_step": ms, "ms_min": ts[0], "steps": steps,
                       "kernel": aclnn.last_kernel_name(), "frac_of_datasheet_dense_peak": tf / peak8, "datasheet_dense_peak": peak8,

@@ -63,6 +63,7 @@ static int32_t decode_stream_launch(const OpsnnWqbmmParams* p, cudaStream_t stre
     return wqbmm_decode_ring_launch(p, stream, exact);
 }
 
+bool wqbmm_decode_tma_nk_eligible(const OpsnnWqbmmParams* p);
 bool wqbmm_decode8_eligible(const OpsnnWqbmmParams* p);
 int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream);
 bool wqbmm_prefill_eligible(const OpsnnWqbmmParams* p);
@@ -199,6 +200,8 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
     if (wqbmm_decode_eligible(p)) return OPSNN_WQ_KERNEL_DECODE;
     // 8-bit weights (int8, e4m3) at small m: their own streaming kernel once the weight is large enough to be worth a k-split grid
     if (wqbmm_decode8_eligible(p) && p->k * p->n >= ((int64_t)1 << 20) && getenv("OPSNN_WQ_NO_DECODE8") == nullptr) return OPSNN_WQ_KERNEL_DECODE;
+    // 4-bit weights stored (n,k) at small m: the (n,k) form of the bulk-copy decode kernel, same threshold
+    if (wqbmm_decode_tma_nk_eligible(p) && p->k * p->n >= ((int64_t)1 << 20) && getenv("OPSNN_WQ_NO_DECODE_NK") == nullptr) return OPSNN_WQ_KERNEL_DECODE;
     // a weight prepared for the prefill path (dequantised once, kept by the caller): beyond the decode range the tensor-core matmul
     // alone beats streaming the packed weight once per 16 rows
     if (p->prep_w != nullptr && p->m > 16 && wqbmm_prefill_eligible(p)) return OPSNN_WQ_KERNEL_PREFILL;
@@ -282,7 +285,8 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
                               p->m <= 16 && !ring_only && wqbmm_decode_fast_eligible(p) && wqbmm_decode_tma_eligible(p) &&
                               getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr;
             const bool tma8 = kernel_choice == OPSNN_WQ_KERNEL_DECODE && wqbmm_decode8_eligible(p);
-            if (!tma4 && !tma8) {
+            const bool tma4nk = kernel_choice == OPSNN_WQ_KERNEL_DECODE && wqbmm_decode_tma_nk_eligible(p);
+            if (!tma4 && !tma8 && !tma4nk) {
                 set_err("opsnn_wqbmm_launch: y is bound to a communicator, but this call does not run on a streaming decode kernel that "
                         "stores into the peers' outputs (m <= 16, int4, int8 or e4m3 weight stored (k,n), aligned rows)");
                 return (int32_t)cudaErrorNotSupported;
@@ -294,6 +298,10 @@ int32_t opsnn_wqbmm_launch(const OpsnnWqbmmParams* p, int32_t kernel_choice, voi
         if (!decode_in_chunks(p, &chunk)) return (int32_t)cudaErrorInvalidValue;
         if (kernel_choice == OPSNN_WQ_KERNEL_DECODE_FAST && !wqbmm_decode_fast_eligible(&chunk)) return (int32_t)cudaErrorInvalidValue;
         return decode_chunk_launches(p, static_cast<cudaStream_t>(stream), kernel_choice);
+    }
+    if (kernel_choice == OPSNN_WQ_KERNEL_DECODE && p->w_dtype == ACL_INT4 && p->trans_w != 0) {
+        if (!wqbmm_decode_tma_nk_eligible(p)) return (int32_t)cudaErrorInvalidValue;
+        return wqbmm_decode_tma_launch(p, static_cast<cudaStream_t>(stream), true);
     }
     if (kernel_choice == OPSNN_WQ_KERNEL_DECODE && (p->w_dtype == ACL_INT8 || p->w_dtype == ACL_FLOAT8_E4M3FN)) {
         if (!wqbmm_decode8_eligible(p)) return (int32_t)cudaErrorInvalidValue;

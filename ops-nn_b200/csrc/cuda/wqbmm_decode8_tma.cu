@@ -439,29 +439,34 @@ wqbmm_decode8t_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
     for (int t = 0; t < kTiles; ++t) total[t][0] = total[t][1] = total[t][2] = total[t][3] = 0.f;
 
-    // ---- scale / offset of the current k-group: tile t is column 8 t + g for this lane; two tiles' values share a register until the
-    // group becomes current, any element strides (a scale stored (n, groups) is read in place) ----
+    // ---- scale / offset of the current k-group. Tile t is column 8 t + g for this lane. The warp reads its 64 columns once - lane l
+    // the columns l and 32 + l, scale and offset packed in one register each - a group ahead of use, and the lanes pick their eight
+    // columns out of those registers by shuffle when the group becomes current (any element strides: a scale stored (n, groups) is
+    // read in place) ----
     const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
     const int64_t n_groups = (a.ksteps + spg - 1) / spg;
-    uint32_t sc[kTiles], of[kHasOffset ? kTiles : 1], rs_next[4], ro_next[kHasOffset ? 4 : 1];
+    uint32_t sc[kTiles], of[kHasOffset ? kTiles : 1], raw_s0 = 0u, raw_s1 = 0u, raw_o0 = 0u, raw_o1 = 0u;
+    const int64_t el_lo = (warp_col + lane < a.n ? warp_col + lane : 0) * (int64_t)a.scale_sn;
+    const int64_t el_hi = (warp_col + 32 + lane < a.n ? warp_col + 32 + lane : 0) * (int64_t)a.scale_sn;
     auto fetch = [&](int64_t group) {
         const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
-        const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
-#pragma unroll
-        for (int t2 = 0; t2 < 4; ++t2) {
-            const int64_t c0 = warp_col + 16 * t2 + g, c1 = c0 + 8;
-            const int64_t e0 = (c0 < a.n ? c0 : 0) * (int64_t)a.scale_sn, e1 = (c1 < a.n ? c1 : 0) * (int64_t)a.scale_sn;
-            rs_next[t2] = (uint32_t)__ldg(sp + e0) | ((uint32_t)__ldg(sp + e1) << 16);
-            if (kHasOffset) ro_next[kHasOffset ? t2 : 0] = (uint32_t)__ldg(op + e0) | ((uint32_t)__ldg(op + e1) << 16);
+        // the loaded values stay untouched until the group becomes current: nothing here waits for the loads
+        raw_s0 = __ldg(sp + el_lo);
+        raw_s1 = __ldg(sp + el_hi);
+        if (kHasOffset) {
+            const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+            raw_o0 = __ldg(op + el_lo);
+            raw_o1 = __ldg(op + el_hi);
         }
     };
     auto load_group = [&](int64_t group) {
         if (group >= n_groups) group = n_groups - 1;
+        const uint32_t next_lo = raw_s0 | (raw_o0 << 16), next_hi = raw_s1 | (raw_o1 << 16);
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) {  // each value in both halves of a register: the halves are two k rows of one column
-            const uint32_t sel = (t & 1) ? 0x3232u : 0x1010u;
-            sc[t] = prmt(rs_next[t >> 1], rs_next[t >> 1], sel);
-            if (kHasOffset) of[kHasOffset ? t : 0] = prmt(ro_next[kHasOffset ? t >> 1 : 0], ro_next[kHasOffset ? t >> 1 : 0], sel);
+            const uint32_t v = __shfl_sync(0xffffffffu, t < 4 ? next_lo : next_hi, (8 * t + g) & 31);
+            sc[t] = prmt(v, v, 0x1010u);
+            if (kHasOffset) of[kHasOffset ? t : 0] = prmt(v, v, 0x3232u);
         }
         fetch(min(group + 1, n_groups - 1));
     };

@@ -443,6 +443,239 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 #endif
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// The default arithmetic for a weight stored (n,k): k contiguous, two nibbles per byte, the transposed view of the API.
+//
+// Same grid, ring size, refill duty, bounded waits and combine. A stage is 128 k rows of the strip's 512 columns: eight boxes (one
+// per warp) of 64 bytes of k x 64 weight rows in the 64-byte swizzle (16-byte chunk index ^ ((row >> 1) & 3)), and two boxes of x.
+// A box row is 128 k values of one column, so plain ldmatrix (no transposition) hands lane (g, q) the eight nibbles
+// k = 32 j + 8 q .. + 7 of column 8 t + g, four tiles per instruction. The nibble mask takes nibbles i and i + 4 of a register
+// together, so the register feeds two MMAs whose B registers are the k pairs (0,4), (1,5) and (2,6), (3,7); the A fragments are
+// permuted to match - x[row][32 j + 8 q .. + 7] is one 16-byte shared load, four byte permutes per row make the pairs (a sum over k
+// does not care in which order the MMA sees k). Tile t is columns 8 t .. 8 t + 7: no column permutation to undo at the store. Scales
+// and offsets are read one 16-bit element at a time at the tensor's own strides ((n, groups) storage is used in place); k-groups
+// are whole stages (multiples of 128) or a single group.
+constexpr int kNkStageRows = 128;
+constexpr int kNkWBox = 64 * 64;                                   // one warp's 64 columns x 64 bytes of k
+constexpr int kNkStageBytes = kWarps * kNkWBox + 2 * kXBoxBytes;   // 36864
+constexpr int kNkStages = 3;
+static_assert(kNkStages * kNkStageBytes == kNumStages * kStageBytes, "both layouts use the same ring size");
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 2)
+wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TmaArgs ta)
+{
+    using N = Num<kBf16>;
+    const DecodeArgs& a = ta.d;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, q = lane & 3;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    __shared__ int s_reduce;
+    __shared__ volatile uint32_t s_abort;
+    __shared__ int s_issued[kNkStages];
+    extern __shared__ uint8_t dyn_raw[];
+    const uint32_t smem0 = (ptx::smem_u32(dyn_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem0 + kNkStages * kNkStageBytes;  // full[i] at bar0 + 8 i, empty[i] at bar0 + 64 + 8 i
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int64_t c = blockIdx.x;
+    const int64_t strip = a.cluster ? c / a.splits : c % a.strips;
+    const int64_t chunk = a.cluster ? c % a.splits : c / a.strips;
+    const int st_a = (int)((chunk * ta.total_stages) / a.splits);
+    const int st_b = (int)(((chunk + 1) * ta.total_stages) / a.splits);
+    const int nst = st_b - st_a;
+    const int64_t warp_col = strip * kStripCols + warp * kWarpCols;
+    const int32_t strip_row = (int32_t)(strip * kStripCols);
+
+    if (tid == 0) {
+        s_abort = 0u;
+        for (int i = 0; i < kNkStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8u * i), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 64u + 8u * i), "r"((uint32_t)kWarps) : "memory");
+            s_issued[i] = -1;
+        }
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_x);
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    volatile uint32_t* abort_flag = &s_abort;
+
+    auto issue_stage = [&](int t, int buf) {  // one lane: stage t of this CTA's range into buffer buf
+        if (ta.test_stall_stage >= 0 && t >= ta.test_stall_stage) return;
+        const uint32_t fb = bar0 + 8u * buf;
+        const uint32_t dst = smem0 + (uint32_t)buf * kNkStageBytes;
+        const int32_t krow = (st_a + t) * kNkStageRows;
+        s_issued[buf] = t;
+        ptx::mbar_expect_tx_a(fb, (uint32_t)kNkStageBytes);
+#pragma unroll
+        for (int b = 0; b < kWarps; ++b) tma_load_2d(dst + b * kNkWBox, &map_w, fb, krow / 2, strip_row + kWarpCols * b);
+        tma_load_2d(dst + kWarps * kNkWBox, &map_x, fb, krow * 2, 0);
+        tma_load_2d(dst + kWarps * kNkWBox + kXBoxBytes, &map_x, fb, krow * 2 + 128, 0);
+    };
+    if (tid == 0) {
+        const int pro = nst < kNkStages ? nst : kNkStages;
+        for (int t = 0; t < pro; ++t) issue_stage(t, t);
+    }
+
+    float total[kTiles][4];
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) total[t][0] = total[t][1] = total[t][2] = total[t][3] = 0.f;
+
+    // ---- scale / offset of the current k-group. Tile t is column 8 t + g for this lane. The warp reads its 64 columns once - lane l
+    // the columns l and 32 + l, scale and offset packed in one register each - a group ahead of use, and the lanes pick their eight
+    // columns out of those registers by shuffle when the group becomes current (any element strides: (n, groups) storage is read
+    // in place) ----
+    const int spg = (int)min(a.steps_per_group, (int64_t)0x7FFFFFFF);
+    const int64_t n_groups = (a.ksteps + spg - 1) / spg;
+    const bool has_off = a.offset != nullptr;
+    uint32_t sc[kTiles], of[kTiles], raw_s0 = 0u, raw_s1 = 0u, raw_o0 = 0u, raw_o1 = 0u;
+    const int64_t el_lo = (warp_col + lane < a.n ? warp_col + lane : 0) * (int64_t)a.scale_sn;
+    const int64_t el_hi = (warp_col + 32 + lane < a.n ? warp_col + 32 + lane : 0) * (int64_t)a.scale_sn;
+    auto fetch = [&](int64_t group) {
+        const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.scale) + group * a.scale_sg;
+        // the loaded values stay untouched until the group becomes current: nothing here waits for the loads
+        raw_s0 = __ldg(sp + el_lo);
+        raw_s1 = __ldg(sp + el_hi);
+        if (has_off) {
+            const uint16_t* op = reinterpret_cast<const uint16_t*>(a.offset) + group * a.scale_sg;
+            raw_o0 = __ldg(op + el_lo);
+            raw_o1 = __ldg(op + el_hi);
+        }
+    };
+    auto load_group = [&](int64_t group) {
+        if (group >= n_groups) group = n_groups - 1;  // zero-filled stages past the end of k: any finite scale will do
+        const uint32_t next_lo = raw_s0 | (raw_o0 << 16), next_hi = raw_s1 | (raw_o1 << 16);
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {  // each value in both halves of a register: the halves are two k rows of one column
+            const uint32_t v = __shfl_sync(0xffffffffu, t < 4 ? next_lo : next_hi, (8 * t + g) & 31);
+            sc[t] = prmt(v, v, 0x1010u);
+            of[t] = prmt(v, v, 0x3232u);
+        }
+        fetch(min(group + 1, n_groups - 1));
+    };
+    // (nibble ^ 8) | magic == B + w exactly; then the reference's rounding points: w' = mul(add(sub(v, B), offset), scale)
+    auto deq = [&](uint32_t tw, int t) {
+        uint32_t v;
+        asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(v) : "r"(tw), "n"(0x000F000F), "n"(N::kMagic));
+        v = N::sub(v, a.c_bias);
+        v = N::add(v, of[t]);
+        return N::mul(v, sc[t]);
+    };
+    // four tiles, the k pairs (0,4), (1,5) of a register / the pairs (2,6), (3,7)
+    auto mma_lo = [&](const uint32_t(&w4)[4], int t0, const uint32_t(&af)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) N::mma_free(total[t0 + i], af, deq(w4[i], t0 + i), deq(w4[i] >> 4, t0 + i));
+    };
+    auto mma_hi = [&](const uint32_t(&w4)[4], int t0, const uint32_t(&af)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) N::mma_free(total[t0 + i], af, deq(w4[i] >> 8, t0 + i), deq(w4[i] >> 12, t0 + i));
+    };
+    auto load_x = [&](uint32_t addr, uint32_t(&X)[8]) {  // x[g][8 k], x[g + 8][8 k]
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(X[0]), "=r"(X[1]), "=r"(X[2]), "=r"(X[3]) : "r"(addr));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+1024];" : "=r"(X[4]), "=r"(X[5]), "=r"(X[6]), "=r"(X[7]) : "r"(addr));
+    };
+    auto make_a = [&](const uint32_t(&X)[8], uint32_t(&lo)[4], uint32_t(&hi)[4]) {
+        lo[0] = prmt(X[0], X[2], 0x5410u);  // row g:     (x0, x4)
+        lo[1] = prmt(X[4], X[6], 0x5410u);  // row g + 8
+        lo[2] = prmt(X[0], X[2], 0x7632u);  //            (x1, x5)
+        lo[3] = prmt(X[4], X[6], 0x7632u);
+        hi[0] = prmt(X[1], X[3], 0x5410u);  //            (x2, x6)
+        hi[1] = prmt(X[5], X[7], 0x5410u);
+        hi[2] = prmt(X[1], X[3], 0x7632u);  //            (x3, x7)
+        hi[3] = prmt(X[5], X[7], 0x7632u);
+    };
+
+    // ---- per-lane addresses inside a stage. Weights: chunk j (32 k) of a row is address ^ 16 j (the swizzle only touches those two
+    // bits). x: chunk j is box j / 2, 16-byte pieces 4 (j & 1) + q of a row in the 128-byte swizzle: address ^ 64 (j & 1) ----
+    const int li = lane & 7, lj = lane >> 3;
+    const uint32_t wlane_a = (uint32_t)warp * kNkWBox + (uint32_t)(8 * lj + li) * 64u + ((uint32_t)((li >> 1) & 3) << 4);  // tiles 0-3
+    const uint32_t wlane_b = wlane_a + 32u * 64u;                                                                         // tiles 4-7
+    const uint32_t xlane = (uint32_t)kWarps * kNkWBox + (uint32_t)g * 128u + ((uint32_t)((q ^ g) & 7) << 4);
+
+    int64_t group = ((int64_t)st_a * (kNkStageRows / 16)) / spg;
+    fetch(min(group, n_groups - 1));
+    load_group(group);
+    int until_change = ta.stages_per_group - (st_a % ta.stages_per_group);
+
+    uint32_t wa[4], wb[4], X[8], alo[4], ahi[4];
+    int buf = 0;
+    uint32_t par = 0;
+    bool ok = nst > 0;
+    if (ok) {
+        ok = wait_bar(bar0, 0u, abort_flag, 1u);
+        ldsm4(smem0 + wlane_a, wa);
+        ldsm4(smem0 + wlane_b, wb);
+        load_x(smem0 + xlane, X);
+    }
+    const int duty = (warp + 8 * 8 - (kNkStages - 1)) & 7;  // this warp refills when (stage index & 7) == duty
+    for (int j = 0; j < nst && ok; ++j) {
+        const uint32_t sbase = smem0 + (uint32_t)buf * kNkStageBytes;
+        const uint32_t wba = sbase + wlane_a, wbb = sbase + wlane_b, xb = sbase + xlane;
+        if (j >= 1 && (j & 7) == duty && j + kNkStages - 1 < nst) {
+            if (lane == 0) {
+                const int pbuf = buf == 0 ? kNkStages - 1 : buf - 1;
+                const uint32_t ppar = buf == 0 ? par ^ 1u : par;
+                if (wait_bar(bar0 + 64u + 8u * pbuf, ppar, abort_flag, 2u)) issue_stage(j + kNkStages - 1, pbuf);
+            }
+            __syncwarp();
+        }
+        if (j > 0 && until_change == 0) {
+            load_group(++group);
+            until_change = ta.stages_per_group;
+        }
+        int nbuf = buf + 1;
+        uint32_t npar = par;
+        if (nbuf == kNkStages) { nbuf = 0; npar ^= 1u; }
+        const uint32_t nb = smem0 + (uint32_t)nbuf * kNkStageBytes;
+#pragma unroll
+        for (int cj = 0; cj < 4; ++cj) {
+            // this chunk's A fragments; then the next chunk's operands are requested as this one's registers fall free
+            make_a(X, alo, ahi);
+            bool more = true;
+            if (cj == 3) {
+                more = j + 1 < nst;
+                if (more) ok = wait_bar(bar0 + 8u * nbuf, npar, abort_flag, 1u);
+            }
+            const uint32_t nwa = cj == 3 ? nb + wlane_a : wba ^ (16u * (cj + 1));
+            const uint32_t nwb = cj == 3 ? nb + wlane_b : wbb ^ (16u * (cj + 1));
+            const uint32_t nx = cj == 3 ? nb + xlane : (xb + 2048u * ((cj + 1) >> 1)) ^ (64u * ((cj + 1) & 1));
+            if (more) load_x(nx, X);
+            mma_lo(wa, 0, alo);
+            mma_lo(wb, 4, alo);
+            mma_hi(wa, 0, ahi);
+            if (more) ldsm4(nwa, wa);
+            mma_hi(wb, 4, ahi);
+            if (more) ldsm4(nwb, wb);
+        }
+        --until_change;
+        __syncwarp();
+        if (lane == 0) mbar_arrive_a(bar0 + 64u + 8u * buf);
+        buf = nbuf;
+        par = npar;
+    }
+
+    const bool aborted = __syncthreads_or(s_abort != 0u) != 0;
+    if (aborted) {
+        // A wait gave up. Nothing is written; the copies already issued get a bounded time to land before the CTA leaves.
+        if (tid == 0) {
+            for (int i = 0; i < kNkStages; ++i) {
+                const int t = s_issued[i];
+                if (t < 0) continue;
+                const uint32_t p = (uint32_t)(t / kNkStages) & 1u;
+                for (uint32_t it = 0; it < kWaitPolls; ++it)
+                    if (ptx::mbar_try_wait_a(bar0 + 8u * i, p)) break;
+            }
+        }
+        __syncthreads();
+        if (!a.cluster) return;
+    }
+    if (a.cluster) cluster_combine_and_store<kBf16, 3>(a, total, strip, warp, lane, tid, smem0, !aborted);
+    else combine_and_store<kBf16, 3>(a, total, c, strip, warp, lane, tid, &s_reduce);
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                               CUtensorMapFloatOOBfill);
@@ -458,25 +691,29 @@ EncodeFn tma_encoder()
     return fn;
 }
 
-// 2-D byte tensor (inner bytes, rows) with a (128, box_rows) box in the 128-byte swizzle; out-of-range bytes read as zero.
-bool make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows)
+// 2-D byte tensor (inner bytes, rows) with a (128, box_rows) box in the 128-byte swizzle (or the box width and swizzle given);
+// out-of-range bytes read as zero.
+bool make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows,
+                 uint32_t box_inner = 128, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B)
 {
     EncodeFn enc = tma_encoder();
     if (enc == nullptr) return false;
     cuuint64_t dims[2] = {inner_bytes, rows};
     cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-std::atomic<uint64_t> g_tma_configured[8];
+std::atomic<uint64_t> g_tma_configured[10];
 
-// variant = 4 exact + 2 bf16 + aligned
+// variant = 4 exact + 2 bf16 + aligned; 8 + bf16: weight stored (n,k)
 const void* tma_kernel(int variant)
 {
     switch (variant) {
+        case 8: return reinterpret_cast<const void*>(&wqbmm_decode_tma_nk_kernel<false>);
+        case 9: return reinterpret_cast<const void*>(&wqbmm_decode_tma_nk_kernel<true>);
         case 0: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, false, false>);
         case 1: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<false, false, true>);
         case 2: return reinterpret_cast<const void*>(&wqbmm_decode_tma_kernel<true, false, false>);
@@ -552,9 +789,27 @@ bool wqbmm_decode_tma_eligible(const OpsnnWqbmmParams* p)
     return true;
 }
 
-// exact = true: the reference's default arithmetic; false: the group-wise form of innerPrecise = 1.
+// The (n,k) kernel's conditions: INT4 weight stored k-contiguous with 16-byte aligned rows, m <= 16, k-groups of whole 128-row stages
+// (or one group), scale / offset in x's dtype at any non-negative strides.
+bool wqbmm_decode_tma_nk_eligible(const OpsnnWqbmmParams* p)
+{
+    if (p->w_dtype != ACL_INT4 || p->trans_w == 0 || p->nz_k0 != 0) return false;
+    if (p->scale_dtype == ACL_FLOAT8_E8M0) return false;
+    if (p->m < 1 || p->m > 16 || p->k < 32 || p->k % 32 != 0 || p->n % 8 != 0) return false;
+    if (p->w_ld % 32 != 0 || p->x_ld % 8 != 0) return false;
+    if (p->group_size != 0 && p->group_size % kNkStageRows != 0) return false;
+    if (p->scale_sn < 0 || p->scale_sn >= ((int64_t)1 << 31) || p->scale_sg < 0) return false;
+    if ((reinterpret_cast<uintptr_t>(p->w) % 16) != 0 || (reinterpret_cast<uintptr_t>(p->x) % 16) != 0) return false;
+    if (p->n >= ((int64_t)1 << 31) || p->k >= ((int64_t)1 << 30)) return false;
+    return tma_encoder() != nullptr;
+}
+
+// exact = true: the reference's default arithmetic; false: the group-wise form of innerPrecise = 1. A weight stored (n,k) always
+// runs the default arithmetic.
 int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, bool exact)
 {
+    const bool nk = p->trans_w != 0;
+    if (nk) exact = true;
     TmaArgs ta{};
     DecodeArgs& a = ta.d;
     a.w = reinterpret_cast<const uint32_t*>(p->w);
@@ -576,7 +831,8 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.strips = (p->n + kStripCols - 1) / kStripCols;
     a.ksteps = p->k / 16;
     a.steps_per_group = p->group_size > 0 ? p->group_size / 16 : a.ksteps;
-    ta.total_stages = (int32_t)((a.ksteps + kStageSteps - 1) / kStageSteps);
+    const int stage_steps = nk ? kNkStageRows / 16 : kStageSteps;
+    ta.total_stages = (int32_t)((a.ksteps + stage_steps - 1) / stage_steps);
     ta.test_stall_stage = -1;
     if (const char* e = getenv("OPSNN_TEST_DECODE_STALL_STAGE")) {  // tests of the give-up path only
         ta.test_stall_stage = atoi(e);
@@ -585,10 +841,10 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
         cudaMemcpyToSymbolAsync(g_wq_tma_poll_limit, &limit, sizeof(limit), 0, cudaMemcpyHostToDevice, stream);
     }
     const bool single_group = a.steps_per_group >= a.ksteps;
-    const bool aligned = single_group || a.steps_per_group % kStageSteps == 0;
-    ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / kStageSteps);
+    const bool aligned = single_group || a.steps_per_group % stage_steps == 0;
+    ta.stages_per_group = single_group ? 0x7FFFFFFF : (int32_t)(a.steps_per_group / stage_steps);
     const bool bf16 = p->x_dtype == ACL_BF16;
-    const int variant = (exact ? 4 : 0) + (bf16 ? 2 : 0) + (aligned ? 1 : 0);
+    const int variant = nk ? 8 + (bf16 ? 1 : 0) : (exact ? 4 : 0) + (bf16 ? 2 : 0) + (aligned ? 1 : 0);
 
     cudaError_t crc = configure_variant(variant);
     if (crc != cudaSuccess) return (int32_t)crc;
@@ -646,7 +902,9 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
 
     CUtensorMap mw, mx;
-    if (!make_map_2d(&mw, p->w, (uint64_t)p->n / 2, (uint64_t)p->k, (uint64_t)p->w_ld / 2, kStageRows) ||
+    const bool w_ok = nk ? make_map_2d(&mw, p->w, (uint64_t)p->k / 2, (uint64_t)p->n, (uint64_t)p->w_ld / 2, kWarpCols, 64, CU_TENSOR_MAP_SWIZZLE_64B)
+                         : make_map_2d(&mw, p->w, (uint64_t)p->n / 2, (uint64_t)p->k, (uint64_t)p->w_ld / 2, kStageRows);
+    if (!w_ok ||
         !make_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
         return (int32_t)cudaErrorInvalidValue;
 

@@ -337,6 +337,49 @@ def test_narrow_output_is_planned_as_clusters(aclnn):
     assert strips == 48 and splits == 6 and cluster == 0
 
 
+W4_NK_CASES = [
+    # x dtype, m, k, n, group, offset, bias, packed as int32 words
+    ("bfloat16", 16, 4096, 1024, 128, True, False, True),      # the benchmark's form with the weight stored (n,k)
+    ("float16", 16, 2048, 768, 256, True, True, False),        # two stages per group, fp16, int4 dtype
+    ("bfloat16", 5, 4096, 1048, 0, False, True, True),         # per-channel, ragged last strip, m < 16
+    ("float16", 1, 8192, 512, 128, False, False, True),        # m = 1, no offset
+    ("bfloat16", 13, 4128, 2056, 0, True, False, False),       # k not a multiple of the 128-row stage (the second x box runs out)
+]
+
+
+@pytest.mark.parametrize("case", W4_NK_CASES, ids=[str(c) for c in W4_NK_CASES])
+def test_w4a16_weight_stored_nk_streaming_kernel(aclnn, case):
+    """INT4 weights stored (n,k) - the transposed view of the API, k contiguous, scales stored (n, groups) - at m <= 16 run on the
+    (n,k) form of the bulk-copy decode kernel with the golden's two roundings per weight (wqbmmv2_kernel_golden.py:242-297): only the
+    fp32 summation order differs, <= 1 ulp of the output dtype."""
+    import ml_dtypes
+
+    from gpu_util import run_wq_fixture
+
+    xdt, m, k, n, group, has_off, has_bias, words = case
+    rng = np.random.default_rng(case_seed(case))
+    np_dt = ml_dtypes.bfloat16 if xdt == "bfloat16" else np.float16
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(np_dt)
+    w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+    groups = k // group if group else 1
+    sc = rng.uniform(0.005, 0.02, (groups, n)).astype(np.float32).astype(np_dt)
+    of = rng.uniform(-2, 2, (groups, n)).astype(np.float32).astype(np_dt) if has_off else None
+    bias = rng.uniform(-1, 1, n).astype(np.float32).astype(np_dt) if has_bias else None
+    want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, bias, group)
+    # the fixture runner takes the stored (transposed) arrays
+    a = dict(x=x, w=np.ascontiguousarray(w.T), scale=np.ascontiguousarray(sc.T) if group else sc[0],
+             offset=None if of is None else (np.ascontiguousarray(of.T) if group else of[0]), bias=bias, out=want)
+    meta = dict(transpose_weight=True, w_is_int4=True, packed_int32=words, group_size=group)
+    got = run_wq_fixture(aclnn, a, meta, kernel=0)
+    assert aclnn.last_kernel_name() == "wqbmm_decode", aclnn.last_kernel_name()
+    assert aclnn.lib().opsnn_wqbmm_decode_status(1) == 0
+    gv, wv = got.astype(np.float64), want.astype(np.float64)
+    assert not np.any(gv == -7777.0)
+    ulp = 2.0 ** -7 if xdt == "bfloat16" else 2.0 ** -10
+    rms = np.sqrt(np.mean(wv ** 2))
+    assert np.all(np.abs(gv - wv) <= ulp * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
+
+
 F8_CASES = [
     # x dtype, m, k, n, group, bias, NaN encodings planted, weight (and per-group scale) stored transposed
     ("bfloat16", 16, 2048, 1024, 0, False, False, False),     # per-channel
