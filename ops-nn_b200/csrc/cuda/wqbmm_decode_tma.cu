@@ -455,10 +455,18 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // does not care in which order the MMA sees k). Tile t is columns 8 t .. 8 t + 7: no column permutation to undo at the store. Scales
 // and offsets are read one 16-bit element at a time at the tensor's own strides ((n, groups) storage is used in place); k-groups
 // are whole stages (multiples of 128) or a single group.
-constexpr int kNkStageRows = 128;
-constexpr int kNkWBox = 64 * 64;                                   // one warp's 64 columns x 64 bytes of k
-constexpr int kNkStageBytes = kWarps * kNkWBox + 2 * kXBoxBytes;   // 36864
-constexpr int kNkStages = 3;
+#ifndef OPSNN_NK_STAGE_ROWS
+#define OPSNN_NK_STAGE_ROWS 128
+#endif
+// 128 (64-byte rows, 64-byte swizzle, three stages) or 64 (32-byte rows and swizzle, six stages; measured slower: 69.6 against
+// 64.2 us on k = 8192, n = 28672 - the narrower the rows of a box, the slower the copies deliver)
+constexpr int kNkStageRows = OPSNN_NK_STAGE_ROWS;
+constexpr int kNkRowBytes = kNkStageRows / 2;
+constexpr int kNkChunks = kNkStageRows / 32;                       // 16-byte chunks per weight row
+constexpr int kNkXBoxes = kNkStageRows / 64;
+constexpr int kNkWBox = 64 * kNkRowBytes;                          // one warp's 64 columns
+constexpr int kNkStageBytes = kWarps * kNkWBox + kNkXBoxes * kXBoxBytes;   // 36864 / 18432
+constexpr int kNkStages = kNkStageRows == 128 ? 3 : 6;
 static_assert(kNkStages * kNkStageBytes == kNumStages * kStageBytes, "both layouts use the same ring size");
 
 template <bool kBf16>
@@ -513,7 +521,7 @@ wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
         for (int b = 0; b < kWarps; ++b) tma_load_2d(dst + b * kNkWBox, &map_w, fb, krow / 2, strip_row + kWarpCols * b);
         tma_load_2d(dst + kWarps * kNkWBox, &map_x, fb, krow * 2, 0);
-        tma_load_2d(dst + kWarps * kNkWBox + kXBoxBytes, &map_x, fb, krow * 2 + 128, 0);
+        if (kNkXBoxes == 2) tma_load_2d(dst + kWarps * kNkWBox + kXBoxBytes, &map_x, fb, krow * 2 + 128, 0);
     };
     if (tid == 0) {
         const int pro = nst < kNkStages ? nst : kNkStages;
@@ -591,8 +599,9 @@ wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     // ---- per-lane addresses inside a stage. Weights: chunk j (32 k) of a row is address ^ 16 j (the swizzle only touches those two
     // bits). x: chunk j is box j / 2, 16-byte pieces 4 (j & 1) + q of a row in the 128-byte swizzle: address ^ 64 (j & 1) ----
     const int li = lane & 7, lj = lane >> 3;
-    const uint32_t wlane_a = (uint32_t)warp * kNkWBox + (uint32_t)(8 * lj + li) * 64u + ((uint32_t)((li >> 1) & 3) << 4);  // tiles 0-3
-    const uint32_t wlane_b = wlane_a + 32u * 64u;                                                                         // tiles 4-7
+    const uint32_t wswz = kNkRowBytes == 64 ? (uint32_t)((li >> 1) & 3) : (uint32_t)((li >> 2) & 1);  // 64- / 32-byte swizzle
+    const uint32_t wlane_a = (uint32_t)warp * kNkWBox + (uint32_t)(8 * lj + li) * (uint32_t)kNkRowBytes + (wswz << 4);  // tiles 0-3
+    const uint32_t wlane_b = wlane_a + 32u * (uint32_t)kNkRowBytes;                                                     // tiles 4-7
     const uint32_t xlane = (uint32_t)kWarps * kNkWBox + (uint32_t)g * 128u + ((uint32_t)((q ^ g) & 7) << 4);
 
     int64_t group = ((int64_t)st_a * (kNkStageRows / 16)) / spg;
@@ -631,17 +640,17 @@ wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         if (nbuf == kNkStages) { nbuf = 0; npar ^= 1u; }
         const uint32_t nb = smem0 + (uint32_t)nbuf * kNkStageBytes;
 #pragma unroll
-        for (int cj = 0; cj < 4; ++cj) {
+        for (int cj = 0; cj < kNkChunks; ++cj) {
             // this chunk's A fragments; then the next chunk's operands are requested as this one's registers fall free
             make_a(X, alo, ahi);
             bool more = true;
-            if (cj == 3) {
+            if (cj == kNkChunks - 1) {
                 more = j + 1 < nst;
                 if (more) ok = wait_bar(bar0 + 8u * nbuf, npar, abort_flag, 1u);
             }
-            const uint32_t nwa = cj == 3 ? nb + wlane_a : wba ^ (16u * (cj + 1));
-            const uint32_t nwb = cj == 3 ? nb + wlane_b : wbb ^ (16u * (cj + 1));
-            const uint32_t nx = cj == 3 ? nb + xlane : (xb + 2048u * ((cj + 1) >> 1)) ^ (64u * ((cj + 1) & 1));
+            const uint32_t nwa = cj == kNkChunks - 1 ? nb + wlane_a : wba ^ (16u * (cj + 1));
+            const uint32_t nwb = cj == kNkChunks - 1 ? nb + wlane_b : wbb ^ (16u * (cj + 1));
+            const uint32_t nx = cj == kNkChunks - 1 ? nb + xlane : (xb + 2048u * ((cj + 1) >> 1)) ^ (64u * ((cj + 1) & 1));
             if (more) load_x(nx, X);
             mma_lo(wa, 0, alo);
             mma_lo(wb, 4, alo);
@@ -902,7 +911,8 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
 
     CUtensorMap mw, mx;
-    const bool w_ok = nk ? make_map_2d(&mw, p->w, (uint64_t)p->k / 2, (uint64_t)p->n, (uint64_t)p->w_ld / 2, kWarpCols, 64, CU_TENSOR_MAP_SWIZZLE_64B)
+    const bool w_ok = nk ? make_map_2d(&mw, p->w, (uint64_t)p->k / 2, (uint64_t)p->n, (uint64_t)p->w_ld / 2, kWarpCols, kNkRowBytes,
+                                      kNkRowBytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B)
                          : make_map_2d(&mw, p->w, (uint64_t)p->n / 2, (uint64_t)p->k, (uint64_t)p->w_ld / 2, kStageRows);
     if (!w_ok ||
         !make_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))
