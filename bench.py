@@ -810,6 +810,7 @@ DEV_WORKLOADS = {
     "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
     "f8m16": (1, 16, 8192, 28672, "a16f8"),            # the same with FLOAT8_E4M3FN weights (random finite byte codes)
     "w8m16": (1, 16, 8192, 28672, "w8a16"),
+    "w8m32": (1, 32, 8192, 28672, "w8a16"),            # 16 < m <= 48: the 8-bit kernel once per 16 rows
     "w8m16t": (1, 16, 8192, 28672, "w8a16_t"),         # ... the weight stored (n,k)
     "f8m16t": (1, 16, 8192, 28672, "a16f8_t"),            # the headline shape with INT8 weights (per-channel bf16 scale): streaming kernel, 235 MB
 }

@@ -167,7 +167,11 @@ static bool decode_in_chunks(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* chunk)
     if (p->m <= 16 || p->m > 48 || p->k * p->n < ((int64_t)1 << 26)) return false;
     *chunk = *p;
     chunk->m = 16;
-    return wqbmm_decode_eligible(chunk);
+    if (wqbmm_decode_eligible(chunk)) return true;
+    // the 8-bit kernels and the (n,k) int4 kernel the same way: three launches of 55-65 us still beat the 0.3 ms of
+    // dequantise-then-matmul on such a weight
+    if (wqbmm_decode8_eligible(chunk) && getenv("OPSNN_WQ_NO_DECODE8") == nullptr) return true;
+    return wqbmm_decode_tma_nk_eligible(chunk) && getenv("OPSNN_WQ_NO_DECODE_NK") == nullptr;
 }
 
 // One decode launch per 16 rows; `fast` = the group-wise kernel of inner_precise = 1.
@@ -180,7 +184,9 @@ static int32_t decode_chunk_launches(const OpsnnWqbmmParams* p, cudaStream_t str
         q.x = static_cast<const uint8_t*>(p->x) + (size_t)r0 * (size_t)p->x_ld * esz;
         q.y = static_cast<uint8_t*>(p->y) + (size_t)r0 * (size_t)p->y_ld * esz;
         int32_t rc;
-        if (which == OPSNN_WQ_KERNEL_DECODE_FAST) rc = decode_stream_launch(&q, stream, false);
+        if (q.w_dtype == ACL_INT8 || q.w_dtype == ACL_FLOAT8_E4M3FN) rc = wqbmm_decode8_launch(&q, stream);
+        else if (q.trans_w != 0) rc = wqbmm_decode_tma_launch(&q, stream, true);
+        else if (which == OPSNN_WQ_KERNEL_DECODE_FAST) rc = decode_stream_launch(&q, stream, false);
         else if (wqbmm_decode_fast_eligible(&q) && getenv("OPSNN_WQ_DECODE_LEGACY") == nullptr) rc = decode_stream_launch(&q, stream, true);
         else rc = wqbmm_decode_launch(&q, stream);
         if (rc != 0) return rc;
@@ -209,8 +215,8 @@ int32_t opsnn_wqbmm_select_kernel(const OpsnnWqbmmParams* p)
     if (getenv("OPSNN_WQ_NO_CHUNKS") == nullptr && decode_in_chunks(p, &chunk))
         return (p->inner_precise == 1 && wqbmm_decode_fast_eligible(&chunk)) ? OPSNN_WQ_KERNEL_DECODE_FAST : OPSNN_WQ_KERNEL_DECODE;
     // m beyond the decode range: dequantise once, multiply on the tensor cores; tiny problems stay on the one-launch coverage kernel
-    // (also small m when the streaming decode kernel cannot take the layout - int8 / fp8 / transposed weights - and the weight is
-    // large: 0.95 ms against 4.7 ms of the coverage kernel for an int8 8192 x 28672 weight at m = 16)
+    // (also small m when no streaming decode kernel takes the layout - fp4 weights, unaligned pitches, odd group sizes - and the
+    // weight is large: 0.95 ms against 4.7 ms of the coverage kernel for an 8-bit 8192 x 28672 weight at m = 16)
     if ((p->m > 16 || p->k * p->n >= ((int64_t)1 << 22)) && wqbmm_prefill_eligible(p)) return OPSNN_WQ_KERNEL_PREFILL;
     return OPSNN_WQ_KERNEL_GENERIC;
 }

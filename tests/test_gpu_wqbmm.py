@@ -507,6 +507,57 @@ def test_a16f8_dequantisation_is_bit_exact(aclnn, xdt, trans):
     assert np.count_nonzero(want.astype(np.float32)) > m * n // 2
 
 
+CHUNK8_CASES = [
+    # weight kind, stored (n,k), m
+    ("int8", False, 40),
+    ("e4m3", True, 33),
+    ("int4", True, 48),
+]
+
+
+@pytest.mark.parametrize("case", CHUNK8_CASES, ids=[str(c) for c in CHUNK8_CASES])
+def test_8bit_and_nk_decode_kernels_in_chunks_of_16_rows(aclnn, case):
+    """16 < m <= 48 against a large weight: the 8-bit streaming kernels and the (n,k) int4 kernel run once per 16 rows of x, like the
+    (k,n) int4 kernel; same <= 1 ulp criterion as a single launch."""
+    import ml_dtypes
+    import torch
+
+    from gpu_util import DEV, out_to_np, run_wq_fixture
+
+    kind, trans, m = case
+    k, n, g = 4096, 16384, 128
+    rng = np.random.default_rng(case_seed(case))
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    sc = rng.uniform(0.005, 0.02, (k // g, n)).astype(np.float32).astype(ml_dtypes.bfloat16)
+    if kind == "int4":
+        w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+        of = rng.uniform(-1, 1, (k // g, n)).astype(np.float32).astype(ml_dtypes.bfloat16)
+        want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, of, None, g)
+        a = dict(x=x, w=np.ascontiguousarray(w.T), scale=np.ascontiguousarray(sc.T), offset=np.ascontiguousarray(of.T), bias=None, out=want)
+        got = run_wq_fixture(aclnn, a, dict(transpose_weight=True, w_is_int4=True, packed_int32=True, group_size=g), kernel=0)
+        assert aclnn.last_kernel_name() == "wqbmm_decode", aclnn.last_kernel_name()
+    else:
+        y = torch.full((m, n), -7777.0, dtype=torch.bfloat16, device=DEV)
+        d_sc = _dev16_t(aclnn, sc) if trans else _dev16(aclnn, sc)
+        if kind == "int8":
+            w = rng.integers(-128, 128, (k, n)).astype(np.int8)
+            d_w = aclnn.from_torch(torch.from_numpy(np.ascontiguousarray(w.T)).to(DEV).t() if trans else torch.from_numpy(w).to(DEV))
+        else:
+            codes = rng.integers(0, 256, (k, n)).astype(np.uint8)
+            codes[(codes & 0x7F) == 0x7F] ^= 0x01
+            w = codes.view(ml_dtypes.float8_e4m3fn)
+            d_w = _f8_tensor(aclnn, codes, trans)
+        want = wqbmm_oracle.weight_quant_batch_matmul(x, w, sc, None, None, g)
+        aclnn.weight_quant_batch_matmul(_dev16(aclnn, x), d_w, d_sc, aclnn.from_torch(y), None, None, g)
+        torch.cuda.synchronize()
+        assert aclnn.last_kernel_name() == "wqbmm_decode8", aclnn.last_kernel_name()
+        got = out_to_np(y)
+    gv, wv = got.astype(np.float64), want.astype(np.float64)
+    assert not np.any(gv == -7777.0)
+    rms = np.sqrt(np.mean(wv ** 2))
+    assert np.all(np.abs(gv - wv) <= 2.0 ** -7 * np.maximum(np.abs(wv), 0.05 * rms) * 1.01)
+
+
 W8_CASES = [
     # x dtype, m, k, n, group, offset, bias, weight (and per-group scale / offset) stored transposed
     ("bfloat16", 16, 2048, 1024, 0, False, False, False),     # per-channel, symmetric: the common W8A16 form
