@@ -76,6 +76,32 @@ def _fused_gather_check(aclnn, comm, dev, world, rank):
             comm.arrive_and_wait()
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(pushed, ref))
+        # the other streaming decode kernels store into the peers the same way: INT4 weight stored (n,k) with (n, groups) scales, and
+        # an INT8 weight with a per-channel scale
+        w_nk = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), generator=gen, device=dev, dtype=torch.int32)
+        sc_nk = (torch.rand((n, k // g), generator=gen, device=dev) * 0.01 + 0.005).to(torch.bfloat16)
+        of_nk = (torch.rand((n, k // g), generator=gen, device=dev) * 2 - 1).to(torch.bfloat16)
+        w8 = torch.randint(-128, 128, (k, n), generator=gen, device=dev, dtype=torch.int8)
+        sc8 = (torch.rand((n,), generator=gen, device=dev) * 0.01 + 0.002).to(torch.bfloat16)
+        calls = [
+            ("wqbmm_decode", lambda: aclnn.weight_quant_batch_matmul(
+                aclnn.from_torch(x), aclnn.from_torch(w_nk[b:e].contiguous().t()), aclnn.from_torch(sc_nk[b:e].contiguous().t()),
+                aclnn.from_torch(y_local), aclnn.from_torch(of_nk[b:e].contiguous().t()), None, g)),
+            ("wqbmm_decode8", lambda: aclnn.weight_quant_batch_matmul(
+                aclnn.from_torch(x), aclnn.from_torch(w8[:, b:e].contiguous()), aclnn.from_torch(sc8[b:e].contiguous()),
+                aclnn.from_torch(y_local), None, None, 0)),
+        ]
+        for name, call in calls:
+            call()
+            assert aclnn.last_kernel_name() == name, aclnn.last_kernel_name()
+            comm.arrive_and_wait()
+            torch.cuda.synchronize()
+            fused = y_full.clone()
+            comm.arrive_and_wait()
+            torch.cuda.synchronize()
+            ref = comm.gather_columns(y_local, n, 512)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(fused, ref)) and not bool((fused == 0).all())
         refused = False
         try:  # m = 32 runs as two decode launches on row chunks: not a path that stores into the peers
             x32 = torch.randn((32, k), generator=gen, device=dev).to(torch.bfloat16)
