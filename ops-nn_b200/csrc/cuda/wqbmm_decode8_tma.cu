@@ -150,10 +150,7 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         for (int b = 0; b < 4; ++b) d8_tma_2d(dst + b * k8WBox, &map_w, fb, wcol_bytes + 128 * b, krow);
         d8_tma_2d(dst + 4 * k8WBox, &map_x, fb, krow * 2, 0);
     };
-    if (tid == 0) {
-        const int pro = nst < k8Stages ? nst : k8Stages;
-        for (int t = 0; t < pro; ++t) issue_stage(t, t);
-    }
+    if (tid == 0 && nst > 0) issue_stage(0, 0);  // the first stage alone, the rest of the ring once it has landed
 
     float total[kTiles][4];
 #pragma unroll
@@ -277,6 +274,10 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     bool ok = nst > 0;
     if (ok) {
         ok = d8_wait(bar0, 0u, abort_flag, 1u);
+        if (tid == 0 && ok) {
+            const int pro = nst < k8Stages ? nst : k8Stages;
+            for (int t = 1; t < pro; ++t) issue_stage(t, t);
+        }
         d8_ldsm4_trans<0>(smem0 + wlane_a, wa0);
         d8_ldsm4_trans<0>(smem0 + wlane_b, wb0);
         d8_ldsm4(smem0 + xlane, a0);
@@ -368,8 +369,8 @@ wqbmm_decode8_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 // The same regime with the weight stored (n,k), k contiguous - the transposed view of the API (weight.t() of an (n,k) tensor).
 //
 // Same grid, ring, refill duty, bounded waits and combine; what changes is the shape of a stage and the fragments. A stage is still
-// 64 k rows of the strip's 512 columns + x, 34 KB: eight boxes (one per warp) of 64 bytes of k x 64 weight rows in the 64-byte
-// swizzle (16-byte chunk index ^ ((row >> 1) & 3)). A row of a box is the 64 k values of one column, so plain ldmatrix (no
+// 64 k rows of the strip's 512 columns + x, 34 KB: 64 bytes of k x 512 weight rows (two boxes of 256; warp w's 64 rows are 4 KB
+// number w) in the 64-byte swizzle (16-byte chunk index ^ ((row >> 1) & 3)). A row of a box is the 64 k values of one column, so plain ldmatrix (no
 // transposition) hands lane (g, q) the bytes k = 16 j + 4 q .. + 3 of column 8 t + g: four matrices per instruction = four tiles of
 // one 16-row k-step j. The two byte pairs the conversion works on are (4q, 4q+2) and (4q+1, 4q+3); they become the two B registers
 // of one MMA, and the A fragment is permuted to match: x[row][4q .. 4q+3] is one 8-byte shared load, its even elements feed the
@@ -426,14 +427,12 @@ wqbmm_decode8t_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         const int32_t krow = (st_a + t) * k8StageRows;
         s_issued[buf] = t;
         ptx::mbar_expect_tx_a(fb, (uint32_t)k8Stage);
+        // two boxes of 256 weight rows: rows are contiguous in shared memory, so warp w's 64 rows start at w * k8TBox all the same
 #pragma unroll
-        for (int b = 0; b < kWarps; ++b) d8_tma_2d(dst + b * k8TBox, &map_w, fb, krow, strip_row + kWarpCols * b);
+        for (int b = 0; b < 2; ++b) d8_tma_2d(dst + b * 4 * k8TBox, &map_w, fb, krow, strip_row + 256 * b);
         d8_tma_2d(dst + kWarps * k8TBox, &map_x, fb, krow * 2, 0);
     };
-    if (tid == 0) {
-        const int pro = nst < k8Stages ? nst : k8Stages;
-        for (int t = 0; t < pro; ++t) issue_stage(t, t);
-    }
+    if (tid == 0 && nst > 0) issue_stage(0, 0);  // the first stage alone, the rest of the ring once it has landed
 
     float total[kTiles][4];
 #pragma unroll
@@ -545,6 +544,10 @@ wqbmm_decode8t_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     bool ok = nst > 0;
     if (ok) {
         ok = d8_wait(bar0, 0u, abort_flag, 1u);
+        if (tid == 0 && ok) {
+            const int pro = nst < k8Stages ? nst : k8Stages;
+            for (int t = 1; t < pro; ++t) issue_stage(t, t);
+        }
         d8_ldsm4(smem0 + wlane_a, wa0);
         d8_ldsm4(smem0 + wlane_b, wb0);
         load_a(smem0 + xlane, a0);
@@ -817,7 +820,7 @@ int32_t wqbmm_decode8_launch(const OpsnnWqbmmParams* p, cudaStream_t stream)
     a.nonce = next_nonce();
 
     CUtensorMap mw, mx;
-    const bool w_ok = p->trans_w != 0 ? d8_map_2d(&mw, p->w, (uint64_t)p->k, (uint64_t)p->n, (uint64_t)p->w_ld, kWarpCols, 64, CU_TENSOR_MAP_SWIZZLE_64B)
+    const bool w_ok = p->trans_w != 0 ? d8_map_2d(&mw, p->w, (uint64_t)p->k, (uint64_t)p->n, (uint64_t)p->w_ld, 256, 64, CU_TENSOR_MAP_SWIZZLE_64B)
                                       : d8_map_2d(&mw, p->w, (uint64_t)p->n, (uint64_t)p->k, (uint64_t)p->w_ld, k8StageRows);
     if (!w_ok ||
         !d8_map_2d(&mx, p->x, (uint64_t)p->k * 2, (uint64_t)p->m, (uint64_t)p->x_ld * 2, 16))

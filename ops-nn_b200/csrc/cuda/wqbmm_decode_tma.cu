@@ -446,8 +446,9 @@ wqbmm_decode_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // ---------------------------------------------------------------------------------------------------------------------------------
 // The default arithmetic for a weight stored (n,k): k contiguous, two nibbles per byte, the transposed view of the API.
 //
-// Same grid, ring size, refill duty, bounded waits and combine. A stage is 128 k rows of the strip's 512 columns: eight boxes (one
-// per warp) of 64 bytes of k x 64 weight rows in the 64-byte swizzle (16-byte chunk index ^ ((row >> 1) & 3)), and two boxes of x.
+// Same grid, ring size, refill duty, bounded waits and combine. A stage is 128 k rows of the strip's 512 columns: 64 bytes of k x
+// 512 weight rows (two boxes of 256; warp w's 64 rows are 4 KB number w) in the 64-byte swizzle (16-byte chunk index ^ ((row >> 1) & 3)),
+// and two boxes of x.
 // A box row is 128 k values of one column, so plain ldmatrix (no transposition) hands lane (g, q) the eight nibbles
 // k = 32 j + 8 q .. + 7 of column 8 t + g, four tiles per instruction. The nibble mask takes nibbles i and i + 4 of a register
 // together, so the register feeds two MMAs whose B registers are the k pairs (0,4), (1,5) and (2,6), (3,7); the A fragments are
@@ -518,15 +519,13 @@ wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int32_t krow = (st_a + t) * kNkStageRows;
         s_issued[buf] = t;
         ptx::mbar_expect_tx_a(fb, (uint32_t)kNkStageBytes);
+        // two boxes of 256 weight rows: rows are contiguous in shared memory, so warp w's 64 rows start at w * kNkWBox all the same
 #pragma unroll
-        for (int b = 0; b < kWarps; ++b) tma_load_2d(dst + b * kNkWBox, &map_w, fb, krow / 2, strip_row + kWarpCols * b);
+        for (int b = 0; b < 2; ++b) tma_load_2d(dst + b * 4 * kNkWBox, &map_w, fb, krow / 2, strip_row + 256 * b);
         tma_load_2d(dst + kWarps * kNkWBox, &map_x, fb, krow * 2, 0);
         if (kNkXBoxes == 2) tma_load_2d(dst + kWarps * kNkWBox + kXBoxBytes, &map_x, fb, krow * 2 + 128, 0);
     };
-    if (tid == 0) {
-        const int pro = nst < kNkStages ? nst : kNkStages;
-        for (int t = 0; t < pro; ++t) issue_stage(t, t);
-    }
+    if (tid == 0 && nst > 0) issue_stage(0, 0);  // the first stage alone, the rest of the ring once it has landed (see the (k,n) kernel)
 
     float total[kTiles][4];
 #pragma unroll
@@ -615,6 +614,10 @@ wqbmm_decode_tma_nk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     bool ok = nst > 0;
     if (ok) {
         ok = wait_bar(bar0, 0u, abort_flag, 1u);
+        if (tid == 0 && ok) {
+            const int pro = nst < kNkStages ? nst : kNkStages;
+            for (int t = 1; t < pro; ++t) issue_stage(t, t);
+        }
         ldsm4(smem0 + wlane_a, wa);
         ldsm4(smem0 + wlane_b, wb);
         load_x(smem0 + xlane, X);
@@ -911,7 +914,7 @@ int32_t wqbmm_decode_tma_launch(const OpsnnWqbmmParams* p, cudaStream_t stream, 
     a.c_bias = bf16 ? Num<true>::kBias : Num<false>::kBias;
 
     CUtensorMap mw, mx;
-    const bool w_ok = nk ? make_map_2d(&mw, p->w, (uint64_t)p->k / 2, (uint64_t)p->n, (uint64_t)p->w_ld / 2, kWarpCols, kNkRowBytes,
+    const bool w_ok = nk ? make_map_2d(&mw, p->w, (uint64_t)p->k / 2, (uint64_t)p->n, (uint64_t)p->w_ld / 2, 256, kNkRowBytes,
                                       kNkRowBytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B)
                          : make_map_2d(&mw, p->w, (uint64_t)p->n / 2, (uint64_t)p->k, (uint64_t)p->w_ld / 2, kStageRows);
     if (!w_ok ||
