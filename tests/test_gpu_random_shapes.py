@@ -104,3 +104,67 @@ def test_weight_only_random_shapes(aclnn, seed):
         ulp = 2.0 ** -7 if xdt is ml_dtypes.bfloat16 else 2.0 ** -10
         rms = np.sqrt(np.mean(wv ** 2)) + 1e-30
         assert np.all(np.abs(got - wv) <= 2 * ulp * np.maximum(np.abs(wv), 0.05 * rms) * 1.01), tag
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_streaming_decode_kernels_random_shapes(aclnn, seed):
+    """Weights large enough (k n >= 2^20) for the streaming decode kernels at m <= 16, every kind they take - INT4 in int32 words,
+    INT8, FLOAT8_E4M3FN, each stored (k,n) or (n,k) with the scales stored the same way - ragged strips, k that is not a multiple of
+    a stage, per-channel and per-group scales, offsets, bias: within 1 ulp of the output dtype of the oracle (fp32 summation order
+    is the only difference), and most draws must really have run on a streaming kernel."""
+    import torch
+
+    from gpu_util import desc, out_tensor, out_to_np
+
+    rng = np.random.default_rng(seed)
+    streamed = 0
+    draws = 12
+    for _ in range(draws):
+        kind = str(rng.choice(["int4", "int8", "e4m3"]))
+        tw = bool(rng.integers(0, 2))
+        m = int(rng.integers(1, 17))
+        k = int(rng.integers(32, 130)) * 32
+        n = int(rng.integers(max(1, (1 << 20) // k // 16 + 1), 160)) * 16
+        g = int(rng.choice([0, 128, 256]))
+        if g and (k % g or g >= k):
+            g = 0
+        xdt = ml_dtypes.bfloat16 if rng.integers(0, 2) else np.float16
+        x = rng.standard_normal((m, k)).astype(np.float32).astype(xdt)
+        sshape = (k // g, n) if g else (n,)
+        scale = rng.uniform(0.005, 0.02, sshape).astype(np.float32).astype(xdt)
+        offset = rng.uniform(-1, 1, sshape).astype(np.float32).astype(xdt) if (kind != "e4m3" and rng.integers(0, 2)) else None
+        bias = rng.uniform(-1, 1, n).astype(np.float32).astype(xdt) if rng.integers(0, 2) else None
+        if kind == "int4":
+            w = rng.integers(-8, 8, (k, n)).astype(np.int8)
+            words = wqbmm_oracle.pack_int4_words(w.T.copy() if tw else w)  # packed along the stored inner axis
+            d_w = desc(aclnn, words, strides=(1, words.shape[1]), shape=(words.shape[1], words.shape[0])) if tw else desc(aclnn, words)
+        elif kind == "int8":
+            w = rng.integers(-128, 128, (k, n)).astype(np.int8)
+            d_w = desc(aclnn, w.T.copy(), strides=(1, k), shape=(k, n)) if tw else desc(aclnn, w)
+        else:
+            codes = rng.integers(0, 256, (k, n)).astype(np.uint8)
+            codes[(codes & 0x7F) == 0x7F] ^= 0x01
+            w = codes.view(ml_dtypes.float8_e4m3fn)
+            d_w = desc(aclnn, w.T.copy(), strides=(1, k), shape=(k, n)) if tw else desc(aclnn, w)
+
+        def sdesc(a):
+            if a is None:
+                return None
+            if tw and a.ndim == 2:  # stored (n, groups), described as (groups, n)
+                return desc(aclnn, a.T.copy(), strides=(1, a.shape[0]), shape=a.shape)
+            return desc(aclnn, a)
+
+        tag = f"seed={seed} {kind} tw={tw} m={m} k={k} n={n} g={g} {np.dtype(xdt).name} off={offset is not None} bias={bias is not None}"
+        want = wqbmm_oracle.weight_quant_batch_matmul(x, w, scale, offset, bias, g)
+        name = "bfloat16" if xdt is ml_dtypes.bfloat16 else "float16"
+        out = out_tensor((m, n), name)
+        aclnn.weight_quant_batch_matmul(desc(aclnn, x), d_w, sdesc(scale), aclnn.Tensor((m, n), name, out), sdesc(offset), desc(aclnn, bias), g)
+        torch.cuda.synchronize()
+        streamed += aclnn.last_kernel_name() in ("wqbmm_decode", "wqbmm_decode8")
+        assert aclnn.lib().opsnn_wqbmm_decode_status(1) == 0, tag
+        got, wv = out_to_np(out).astype(np.float64), want.astype(np.float64)
+        assert not np.any(got == -7777.0), tag
+        ulp = 2.0 ** -7 if xdt is ml_dtypes.bfloat16 else 2.0 ** -10
+        rms = np.sqrt(np.mean(wv ** 2)) + 1e-30
+        assert np.all(np.abs(got - wv) <= ulp * np.maximum(np.abs(wv), 0.05 * rms) * 1.01), tag
+    assert streamed >= draws * 2 // 3, streamed
