@@ -344,6 +344,7 @@ W4_NK_CASES = [
     ("bfloat16", 5, 4096, 1048, 0, False, True, True),         # per-channel, ragged last strip, m < 16
     ("float16", 1, 8192, 512, 128, False, False, True),        # m = 1, no offset
     ("bfloat16", 13, 4128, 2056, 0, True, False, False),       # k not a multiple of the 128-row stage (the second x box runs out)
+    ("bfloat16", 16, 16384, 64, 128, True, False, True),       # fewer columns than one copy box has rows
 ]
 
 
@@ -569,6 +570,7 @@ W8_CASES = [
     ("bfloat16", 16, 2048, 768, 128, True, False, True),      # scales stored (n, groups)
     ("float16", 1, 8192, 512, 64, False, True, True),
     ("bfloat16", 13, 4112, 2064, 0, True, False, True),       # k not a multiple of the 64-row stage, ragged strip
+    ("float16", 16, 16384, 64, 0, False, False, True),        # fewer columns than one copy box has rows
 ]
 
 
