@@ -808,6 +808,9 @@ DEV_WORKLOADS = {
     "c2nk": (1, 16, 8192, 28672, "w4a16_nk"),        # the headline shape with weight, scale and offset stored (n,k) / (n,groups)
     "c2m32": (1, 32, 8192, 28672, "w4a16_prefill"),  # 16 < m <= 48: the decode kernel once per 16 rows
     "c2m48": (1, 48, 8192, 28672, "w4a16_prefill"),
+    "w4m32s": (1, 32, 4096, 4096, "w4a16_prefill"),   # m = 32 against smaller weights (2^24, 2^25.8 elements)
+    "w4m32m": (1, 32, 4096, 14336, "w4a16_prefill"),
+    "w4m48m": (1, 48, 4096, 14336, "w4a16_prefill"),
     "f8m16": (1, 16, 8192, 28672, "a16f8"),            # the same with FLOAT8_E4M3FN weights (random finite byte codes)
     "w8m16": (1, 16, 8192, 28672, "w8a16"),
     "w8m32": (1, 32, 8192, 28672, "w8a16"),            # 16 < m <= 48: the 8-bit kernel once per 16 rows

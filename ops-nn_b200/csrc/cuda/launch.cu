@@ -159,12 +159,20 @@ int32_t opsnn_qmm_launch(const OpsnnQmmParams* p, int32_t kernel_choice, void* s
     return qmm_generic_launch(p, static_cast<cudaStream_t>(stream));
 }
 
-// 16 < m <= 48 against a large weight: the streaming decode kernel once per 16 rows of x (the weight is re-read from HBM
-// for every chunk, 62 us each on the m16 k8192 n28672 shape) still beats dequantising the whole weight into workspace
+// 16 < m <= 48 against a large enough weight: the streaming decode kernel once per 16 rows of x (the weight is re-read from
+// HBM for every chunk, 62 us each on the m16 k8192 n28672 shape) still beats dequantising the whole weight into workspace
 // first (0.19 ms for that weight before the matmul starts).
 static bool decode_in_chunks(const OpsnnWqbmmParams* p, OpsnnWqbmmParams* chunk)
 {
-    if (p->m <= 16 || p->m > 48 || p->k * p->n < ((int64_t)1 << 26)) return false;
+    // Measured against dequantise-then-matmul (int4, bf16): 4096 x 4096 at m = 32 31 us against 38; 4096 x 14336 44 against 89 at
+    // m = 32 and 63 against 89 at m = 48. Two launches pay from 2^24 weights on, three from 3 x 2^24.
+    // OPSNN_WQ_CHUNK_MIN_LOG2 replaces both thresholds by 2^value (tuning).
+    int64_t min_kn = (p->m <= 32 ? 1 : 3) * ((int64_t)1 << 24);
+    if (const char* e = getenv("OPSNN_WQ_CHUNK_MIN_LOG2")) {
+        const int v = atoi(e);
+        if (v > 0 && v < 62) min_kn = (int64_t)1 << v;
+    }
+    if (p->m <= 16 || p->m > 48 || p->k * p->n < min_kn) return false;
     *chunk = *p;
     chunk->m = 16;
     if (wqbmm_decode_eligible(chunk)) return true;

@@ -167,14 +167,15 @@ def test_prefill_dequant_then_tensor_core_matmul(aclnn, case):
     assert np.mean(g != wv) < 0.1
 
 
-@pytest.mark.parametrize("m,inner_precise", [(40, 0), (33, 1)])
-def test_decode_kernel_in_chunks_of_16_rows(aclnn, m, inner_precise):
-    """16 < m <= 48 against a large weight: one launch of the streaming decode kernel per 16 rows of x."""
+@pytest.mark.parametrize("m,inner_precise,n", [(40, 0, 16384), (33, 1, 16384), (32, 0, 4096)])
+def test_decode_kernel_in_chunks_of_16_rows(aclnn, m, inner_precise, n):
+    """16 < m <= 48 against a large weight: one launch of the streaming decode kernel per 16 rows of x (two launches from 2^24
+    weights on, three from 3 x 2^24)."""
     import ml_dtypes
 
     from gpu_util import run_wq_fixture
 
-    k, n, g = 4096, 16384, 128
+    k, g = 4096, 128
     rng = np.random.default_rng(100 + m)
     x = rng.standard_normal((m, k)).astype(ml_dtypes.bfloat16)
     w = rng.integers(-8, 8, (k, n)).astype(np.int8)
